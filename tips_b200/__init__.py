@@ -1,0 +1,17 @@
+"""tips_b200: a Blackwell-native distributed-training framework with two
+acceleration modes, collective communication and a sharded parameter server.
+
+The public surface follows the reference's ``tips.tensorflow`` module
+(tips/tensorflow/__init__.py, ops.py, functions.py) with PyTorch tensors in
+place of TensorFlow ones.
+"""
+from .config import Config, get_config, set_config
+from .runtime import (TipsError, barrier, init, initialized, is_initialized, local_rank, local_size, metrics, rank,
+                      shutdown, size)
+from .parallel.collectives import (Average, Max, Min, Product, Sum, allgather, allgather_async, allreduce,
+                                   allreduce_, allreduce_async, allreduce_async_, broadcast, broadcast_,
+                                   broadcast_async, broadcast_async_, grouped_allreduce, poll, sparse_allreduce,
+                                   synchronize)
+from .parallel.compression import Compression
+
+__version__ = "0.1.0"

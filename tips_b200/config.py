@@ -1,0 +1,67 @@
+"""Run-time configuration.
+
+The reference is configured by a handful of environment variables (``GLOG_v``,
+``HOROVOD_ELASTIC``), RpcServer constructor arguments and Python keyword
+arguments (tips/core/common/naive_rpc.h:100-101,158-160;
+tips/tensorflow/__init__.py:65-68).  Here every knob lives in one dataclass
+whose fields can be overridden with ``TIPS_<FIELD>`` environment variables.
+"""
+from __future__ import annotations
+
+import dataclasses
+import os
+
+
+@dataclasses.dataclass
+class Config:
+    # Collective engine
+    fusion_threshold_bytes: int = 64 << 20   # size of one gradient bucket / host fusion buffer
+    cycle_time_ms: int = 0                   # extra batching delay of the coordinator loop
+    stall_warn_s: float = 60.0               # warn when a tensor waits this long for some ranks
+    stall_abort_s: float = 0.0               # >0: fail the tensor instead of waiting forever
+    # Device data plane
+    backend: str = "fused"                   # fused = own sm_100a kernels; nccl = library floor
+    wire_dtype: str = "auto"                 # auto = gradient dtype; bf16/fp16 = compress on the wire
+    one_shot_threshold_bytes: int = 512 << 10
+    device_wait_budget_ms: int = 20000       # bound of every in-kernel wait on a peer
+    comm_blocks: int = 32                    # grid of the communication kernels (SM budget)
+    use_multimem: bool = True                # NVLS multimem instructions when a multicast mapping exists
+    symm_window_bytes: int = 256 << 20       # staging window for tensors outside symmetric memory
+    static_schedule: bool = True             # freeze the bucket order after the first negotiated step
+    # Parameter server
+    ps_local_shards: int = 1
+    # Observability
+    log_level: str = "WARNING"
+    timeline_path: str = ""
+
+    @classmethod
+    def from_env(cls) -> "Config":
+        cfg = cls()
+        for f in dataclasses.fields(cls):
+            raw = os.environ.get("TIPS_" + f.name.upper())
+            if raw is None:
+                continue
+            if f.type in ("int", int):
+                setattr(cfg, f.name, int(raw))
+            elif f.type in ("float", float):
+                setattr(cfg, f.name, float(raw))
+            elif f.type in ("bool", bool):
+                setattr(cfg, f.name, raw.lower() in ("1", "true", "yes", "on"))
+            else:
+                setattr(cfg, f.name, raw)
+        return cfg
+
+
+_config = Config.from_env()
+
+
+def get_config() -> Config:
+    return _config
+
+
+def set_config(**kwargs) -> Config:
+    for k, v in kwargs.items():
+        if not hasattr(_config, k):
+            raise AttributeError(f"unknown tips config field {k!r}")
+        setattr(_config, k, v)
+    return _config

@@ -1,0 +1,148 @@
+"""Process lifecycle: init / shutdown / rank / size.
+
+API parity with the reference's ``tips.tensorflow`` basics (tips/tensorflow/basics.py:8-31,
+ops.py:26-30): ``init`` (the reference initialises at import time), ``shutdown``
+(registered with ``atexit``), ``size``, ``rank``, ``initialized``; plus
+``local_rank`` / ``local_size`` which a one-process-per-GPU job needs to pick
+its device.
+"""
+from __future__ import annotations
+
+import atexit
+import os
+
+from . import _lib
+from .config import get_config
+
+_atexit_registered = False
+_device_state = None
+
+
+class TipsError(RuntimeError):
+    """A tips runtime or collective failure, with the native status code."""
+
+    def __init__(self, message: str, code: int = 7):
+        super().__init__(message)
+        self.code = code
+
+
+def _check(rc: int, what: str) -> int:
+    if rc < 0:
+        raise TipsError(f"{what}: {_lib.last_error()}", -rc)
+    return rc
+
+
+def init(rank: int | None = None, size: int | None = None, master_addr: str | None = None,
+         master_port: int | None = None, device: bool | None = None) -> None:
+    """Start the runtime on this process.
+
+    Without arguments the rank, the world size and the rendezvous address are
+    taken from the environment of a ``torchrun``-style launcher (RANK,
+    WORLD_SIZE, MASTER_ADDR, MASTER_PORT).  With ``device`` true (default: when
+    CUDA is available) the GPU data plane is set up as well: the process binds
+    to ``cuda:local_rank`` and, for world sizes above one, maps the symmetric
+    memory windows used by the fused kernels.
+    """
+    global _atexit_registered, _device_state
+    lib = _lib.core()
+    if lib.tips_is_initialized():
+        return
+    cfg = get_config()
+    levels = {"INFO": 0, "WARNING": 1, "ERROR": 2, "FATAL": 3}
+    if "TIPS_LOG_LEVEL" not in os.environ:
+        lib.tips_set_log_level(levels.get(cfg.log_level.upper(), 1), int(os.environ.get("GLOG_v", "0") or 0))
+    lib.tips_set_fusion_threshold(int(cfg.fusion_threshold_bytes))
+    lib.tips_set_cycle_time_ms(int(cfg.cycle_time_ms))
+    lib.tips_set_stall_check(int(cfg.stall_warn_s * 1000), int(cfg.stall_abort_s * 1000))
+    if rank is None and size is None:
+        _check(lib.tips_init(), "tips_init")
+    else:
+        env_rank = int(os.environ.get("RANK", "0"))
+        env_size = int(os.environ.get("WORLD_SIZE", "1"))
+        addr = master_addr or os.environ.get("MASTER_ADDR", "127.0.0.1")
+        _check(lib.tips_init_ex(env_rank if rank is None else rank, env_size if size is None else size,
+                                addr.encode(), int(master_port or 0)), "tips_init")
+    if not _atexit_registered:
+        atexit.register(shutdown)
+        _atexit_registered = True
+    if cfg.timeline_path:
+        lib.tips_timeline_enable(1)
+    if device is None:
+        import torch
+        device = torch.cuda.is_available()
+    if device:
+        from .parallel import device as _device
+        _device_state = _device.setup()
+
+
+def shutdown() -> None:
+    """Stop the runtime; collectives still in flight fail with an "aborted" status."""
+    global _device_state
+    lib = _lib.core()
+    if not lib.tips_is_initialized():
+        return
+    cfg = get_config()
+    if cfg.timeline_path:
+        path = cfg.timeline_path
+        if lib.tips_size() > 1:
+            path = f"{path}.rank{lib.tips_rank()}"
+        lib.tips_timeline_dump(path.encode())
+    if _device_state is not None:
+        from .parallel import device as _device
+        _device.teardown(_device_state)
+        _device_state = None
+    lib.tips_shutdown()
+
+
+def is_initialized() -> bool:
+    return bool(_lib.core().tips_is_initialized())
+
+
+initialized = is_initialized
+
+
+def _require_init():
+    if not _lib.core().tips_is_initialized():
+        raise TipsError("tips is not initialised; call tips_b200.init() first", 3)
+
+
+def size() -> int:
+    _require_init()
+    return _lib.core().tips_size()
+
+
+def rank() -> int:
+    _require_init()
+    return _lib.core().tips_rank()
+
+
+def local_rank() -> int:
+    _require_init()
+    return _lib.core().tips_local_rank()
+
+
+def local_size() -> int:
+    _require_init()
+    return _lib.core().tips_local_size()
+
+
+def barrier() -> None:
+    _require_init()
+    _check(_lib.core().tips_barrier(), "barrier")
+
+
+def device_state():
+    return _device_state
+
+
+def metrics() -> dict:
+    """Counters of the collective engine and the RPC layer."""
+    import ctypes
+    lib = _lib.core()
+    names = lib.tips_counter_names().decode().split(",")
+    buf = (ctypes.c_uint64 * len(names))()
+    n = lib.tips_counters(buf, len(names))
+    out = {names[i]: int(buf[i]) for i in range(n)}
+    if _device_state is not None:
+        out.update(_device_state.metrics())
+    return out

@@ -45,6 +45,7 @@
 #include "collective/cpu_collectives.h"
 #include "collective/messages.h"
 #include "core/channel.h"
+#include "device_op.h"
 #include "runtime/rpc.h"
 
 namespace tips {
@@ -55,27 +56,8 @@ namespace collective {
 // matching the input), or nullptr on failure.
 using AllocOutputFn = void* (*)(int64_t handle, int64_t nbytes, const int64_t* first_dims, int32_t n, void* user);
 
-// Description of one device-side collective handed to the device executor.
-// Plain C layout: it crosses a shared-library boundary.
-struct DeviceOp {
-  int32_t type;        // RequestType
-  int32_t dtype;       // Datatype
-  int32_t reduce_op;   // ReduceOp
-  int32_t root_rank;
-  const void* in;
-  void* out;
-  int64_t count;           // elements (allreduce / broadcast); own contribution (allgather)
-  const int64_t* counts;   // allgather: elements contributed by every rank
-  int32_t nranks;
-  int32_t channel;         // 0 = negotiated order, 1 = frozen schedule
-  double prescale;
-  double postscale;
-  void* stream;            // producer stream handle (may be null)
-  void* ready_event;       // recorded by the producer after the input was written (may be null)
-  void* done_event;        // recorded by the executor after the collective (may be null)
-};
-// Returns 0 on success; on failure writes a message into err.
-using DeviceExecutorFn = int (*)(const DeviceOp* op, char* err, int err_len);
+using DeviceOp = tips_device_op;
+using DeviceExecutorFn = tips_device_executor_fn;
 
 struct OpRecord {
   std::string name;

@@ -1,0 +1,738 @@
+// Collectives over NVLink peer memory: allreduce (one-shot and two-shot, P2P and
+// NVLS multimem), allgatherv and broadcast, each fused with the scale / cast /
+// staging copies around it so that one launch takes a tensor from its producer
+// to its consumer.
+//
+// These replace the reference's MPI calls on host memory: MPI_Allreduce
+// (tips/core/collective/utils.h:52-67), MPI_Allgatherv (utils.h:83-128) and
+// MPI_Bcast (utils.h:130-134).
+//
+// Work decomposition.  The tensor is cut into 16-byte vectors and the vectors
+// into tiles; tile t belongs to block (t mod grid) ON EVERY RANK.  Inside a tile
+// each rank owns one sub-tile (two-shot) which it reduces from all peers and
+// pushes back to all peers.  Because a block only ever touches tiles of its own
+// index, the only synchronisation needed is a barrier between same-index blocks
+// of the ranks: no grid-wide sync, no host round trip.  Three phases:
+//   A  copy the local input into this rank's window (skipped when it is there)
+//   -- barrier --
+//   B  reduce: own sub-tile from every peer's window -> scaled -> every peer's window
+//      (one-shot: whole tile from every peer -> local output)
+//   -- barrier --
+//   C  copy the reduced tile from the window to the local output (skipped in place)
+//
+// The same kernels run with gridDim.y = number of ranks on ONE device when the
+// rank windows all live there (used by the single-GPU tests); then the launch is
+// cooperative so that all blocks are co-resident.
+#include "kernels/comm.cuh"
+
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <vector>
+
+#include "kernels/common.cuh"
+#include "kernels/tips_kernels.h"
+
+namespace tipsk {
+namespace {
+
+constexpr int kCommThreads = 512;
+constexpr int kUnroll      = 2;                       // vectors per thread per sub-tile
+constexpr int kSubTile     = kCommThreads * kUnroll;  // vectors per rank per tile
+
+struct RankArgs {
+  CommCtx ctx;
+  const char* src;  // local input, or null when the data already sits in the window
+  char* dst;        // local output, or null to leave the result in the window
+  uint64_t win_off; // byte offset of the buffer inside every rank's window
+};
+struct CommLaunch {
+  RankArgs r[kMaxRanks];
+};
+
+template <typename T>
+struct Acc;  // accumulate a 16-byte vector of T in fp32 (floats) or natively (ints / double)
+
+template <>
+struct Acc<float> {
+  float a[4];
+  __device__ void Zero() { a[0] = a[1] = a[2] = a[3] = 0.f; }
+  __device__ void Add(const U4& v) {
+    a[0] += __uint_as_float(v.x); a[1] += __uint_as_float(v.y);
+    a[2] += __uint_as_float(v.z); a[3] += __uint_as_float(v.w);
+  }
+  __device__ void Max(const U4& v, bool first) {
+    float b[4] = {__uint_as_float(v.x), __uint_as_float(v.y), __uint_as_float(v.z), __uint_as_float(v.w)};
+    for (int i = 0; i < 4; ++i) a[i] = first ? b[i] : fmaxf(a[i], b[i]);
+  }
+  __device__ void Min(const U4& v, bool first) {
+    float b[4] = {__uint_as_float(v.x), __uint_as_float(v.y), __uint_as_float(v.z), __uint_as_float(v.w)};
+    for (int i = 0; i < 4; ++i) a[i] = first ? b[i] : fminf(a[i], b[i]);
+  }
+  __device__ void Mul(const U4& v, bool first) {
+    float b[4] = {__uint_as_float(v.x), __uint_as_float(v.y), __uint_as_float(v.z), __uint_as_float(v.w)};
+    for (int i = 0; i < 4; ++i) a[i] = first ? b[i] : a[i] * b[i];
+  }
+  __device__ void Scale(float s) { for (int i = 0; i < 4; ++i) a[i] *= s; }
+  __device__ U4 Pack() const {
+    return U4{__float_as_uint(a[0]), __float_as_uint(a[1]), __float_as_uint(a[2]), __float_as_uint(a[3])};
+  }
+};
+
+template <typename H>  // __nv_bfloat16 or __half
+struct Acc16 {
+  float a[8];
+  __device__ static float Lo(uint32_t w);
+  __device__ void Zero() { for (int i = 0; i < 8; ++i) a[i] = 0.f; }
+  __device__ void Unpack(const U4& v, float (&b)[8]) const {
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+    for (int i = 0; i < 4; ++i) {
+      H lo, hi;
+      uint16_t l = static_cast<uint16_t>(w[i] & 0xffffu), h = static_cast<uint16_t>(w[i] >> 16);
+      memcpy(&lo, &l, 2);
+      memcpy(&hi, &h, 2);
+      b[2 * i]     = ToFloat<H>(lo);
+      b[2 * i + 1] = ToFloat<H>(hi);
+    }
+  }
+  __device__ void Add(const U4& v) { float b[8]; Unpack(v, b); for (int i = 0; i < 8; ++i) a[i] += b[i]; }
+  __device__ void Max(const U4& v, bool first) { float b[8]; Unpack(v, b); for (int i = 0; i < 8; ++i) a[i] = first ? b[i] : fmaxf(a[i], b[i]); }
+  __device__ void Min(const U4& v, bool first) { float b[8]; Unpack(v, b); for (int i = 0; i < 8; ++i) a[i] = first ? b[i] : fminf(a[i], b[i]); }
+  __device__ void Mul(const U4& v, bool first) { float b[8]; Unpack(v, b); for (int i = 0; i < 8; ++i) a[i] = first ? b[i] : a[i] * b[i]; }
+  __device__ void Scale(float s) { for (int i = 0; i < 8; ++i) a[i] *= s; }
+  __device__ U4 Pack() const {
+    uint32_t w[4];
+    for (int i = 0; i < 4; ++i) {
+      H lo = FromFloat<H>(a[2 * i]), hi = FromFloat<H>(a[2 * i + 1]);
+      uint16_t l, h;
+      memcpy(&l, &lo, 2);
+      memcpy(&h, &hi, 2);
+      w[i] = static_cast<uint32_t>(l) | (static_cast<uint32_t>(h) << 16);
+    }
+    return U4{w[0], w[1], w[2], w[3]};
+  }
+};
+template <> struct Acc<__nv_bfloat16> : Acc16<__nv_bfloat16> {};
+template <> struct Acc<__half> : Acc16<__half> {};
+
+template <typename I, int N>  // native accumulation for int32 (N=4), int64 / double (N=2)
+struct AccNative {
+  I a[N];
+  __device__ void Zero() { for (int i = 0; i < N; ++i) a[i] = I(0); }
+  __device__ void Get(const U4& v, I (&b)[N]) const { memcpy(b, &v, 16); }
+  __device__ void Add(const U4& v) { I b[N]; Get(v, b); for (int i = 0; i < N; ++i) a[i] += b[i]; }
+  __device__ void Max(const U4& v, bool first) { I b[N]; Get(v, b); for (int i = 0; i < N; ++i) a[i] = first ? b[i] : (a[i] > b[i] ? a[i] : b[i]); }
+  __device__ void Min(const U4& v, bool first) { I b[N]; Get(v, b); for (int i = 0; i < N; ++i) a[i] = first ? b[i] : (a[i] < b[i] ? a[i] : b[i]); }
+  __device__ void Mul(const U4& v, bool first) { I b[N]; Get(v, b); for (int i = 0; i < N; ++i) a[i] = first ? b[i] : a[i] * b[i]; }
+  __device__ void Scale(float s) { if (s != 1.f) for (int i = 0; i < N; ++i) a[i] = static_cast<I>(static_cast<double>(a[i]) * s); }
+  __device__ U4 Pack() const { U4 v; memcpy(&v, a, 16); return v; }
+};
+template <> struct Acc<int32_t> : AccNative<int32_t, 4> {};
+template <> struct Acc<int64_t> : AccNative<int64_t, 2> {};
+template <> struct Acc<double> : AccNative<double, 2> {};
+
+template <typename T> __device__ __forceinline__ U4 MultimemLdReduce(const void* p);
+template <> __device__ __forceinline__ U4 MultimemLdReduce<float>(const void* p) { return MultimemLdReduceF32(p); }
+template <> __device__ __forceinline__ U4 MultimemLdReduce<__nv_bfloat16>(const void* p) { return MultimemLdReduceBf16(p); }
+template <> __device__ __forceinline__ U4 MultimemLdReduce<__half>(const void* p) { return MultimemLdReduceF16(p); }
+template <> __device__ __forceinline__ U4 MultimemLdReduce<int32_t>(const void* p) { return LdSys(p); }
+template <> __device__ __forceinline__ U4 MultimemLdReduce<int64_t>(const void* p) { return LdSys(p); }
+template <> __device__ __forceinline__ U4 MultimemLdReduce<double>(const void* p) { return LdSys(p); }
+
+__device__ __forceinline__ uint32_t NextEpoch(const CommCtx& ctx, int channel, int block) {
+  return ctx.epochs[channel * kMaxCommBlocks + block] + 1;
+}
+__device__ __forceinline__ void SaveEpoch(const CommCtx& ctx, int channel, int block, uint32_t last) {
+  __syncthreads();
+  if (threadIdx.x == 0) ctx.epochs[channel * kMaxCommBlocks + block] = last;
+}
+
+// Copies `nbytes` between local buffers for the vectors of tiles owned by this
+// block; the ragged tail (nbytes % 16) is handled bytewise, and the rest of a
+// partial vector in the window is zero-filled when `zero_pad`.
+__device__ __forceinline__ void CopyOwnedTiles(char* dst, const char* src, uint64_t nbytes, uint64_t nvec,
+                                               uint64_t tile_vecs, bool zero_pad) {
+  const uint64_t ntiles = (nvec + tile_vecs - 1) / tile_vecs;
+  const bool aligned    = ((reinterpret_cast<uintptr_t>(dst) | reinterpret_cast<uintptr_t>(src)) & 15) == 0;
+  for (uint64_t t = blockIdx.x; t < ntiles; t += gridDim.x) {
+    const uint64_t lo = t * tile_vecs;
+    const uint64_t hi = lo + tile_vecs < nvec ? lo + tile_vecs : nvec;
+    for (uint64_t v = lo + threadIdx.x; v < hi; v += blockDim.x) {
+      const uint64_t off = v * 16;
+      if (aligned && off + 16 <= nbytes) {
+        *reinterpret_cast<U4*>(dst + off) = *reinterpret_cast<const U4*>(src + off);
+      } else {
+        for (uint64_t b = off; b < off + 16; ++b) {
+          if (b < nbytes) dst[b] = src[b];
+          else if (zero_pad) dst[b] = 0;
+        }
+      }
+    }
+  }
+}
+
+// op: 0 sum, 1 max, 2 min, 3 prod
+template <typename T, bool kMultimem, bool kOneShot>
+__global__ void __launch_bounds__(kCommThreads)
+AllreduceKernel(CommLaunch args, int channel, uint64_t nbytes, int op, float prescale, float postscale) {
+  const RankArgs& ra = args.r[blockIdx.y];
+  const CommCtx& ctx = ra.ctx;
+  const int n        = ctx.nranks;
+  const int block    = blockIdx.x;
+  const uint64_t nvec      = (nbytes + 15) / 16;
+  const uint64_t tile_vecs = static_cast<uint64_t>(kSubTile) * n;
+  const uint64_t ntiles    = (nvec + tile_vecs - 1) / tile_vecs;
+  char* my_win = ctx.peer[ctx.rank] + ra.win_off;
+  uint32_t epoch = NextEpoch(ctx, channel, block);
+
+  if (ra.src) CopyOwnedTiles(my_win, ra.src, nbytes, nvec, tile_vecs, true);
+  bool ok = BlockBarrier(ctx, channel, block, epoch, 1);
+
+  if (ok) {
+    const float sum_scale = prescale * postscale;
+    for (uint64_t t = block; t < ntiles; t += gridDim.x) {
+      const uint64_t tile_lo = t * tile_vecs;
+      const uint64_t sub_lo  = kOneShot ? tile_lo : tile_lo + static_cast<uint64_t>(ctx.rank) * kSubTile;
+      const uint64_t sub_n   = kOneShot ? tile_vecs : kSubTile;
+      for (uint64_t base = threadIdx.x; base < sub_n; base += blockDim.x * kUnroll) {
+        U4 in[kUnroll][kMaxRanks];
+        uint64_t vec[kUnroll];
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+          vec[u] = sub_lo + base + static_cast<uint64_t>(u) * blockDim.x;
+          if (base + static_cast<uint64_t>(u) * blockDim.x >= sub_n || vec[u] >= nvec) {
+            vec[u] = ~0ull;
+            continue;
+          }
+          const uint64_t off = ra.win_off + vec[u] * 16;
+          if (kMultimem && op == 0) {
+            in[u][0] = MultimemLdReduce<T>(ctx.mc + off);
+          } else {
+#pragma unroll
+            for (int r = 0; r < kMaxRanks; ++r)
+              if (r < n) in[u][r] = LdSys(ctx.peer[(ctx.rank + r) % n] + off);
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+          if (vec[u] == ~0ull) continue;
+          U4 out;
+          Acc<T> acc;
+          if (kMultimem && op == 0) {
+            acc.Zero();
+            acc.Add(in[u][0]);
+            acc.Scale(sum_scale);
+          } else {
+            acc.Zero();
+#pragma unroll
+            for (int r = 0; r < kMaxRanks; ++r) {
+              if (r >= n) break;
+              if (op == 0) acc.Add(in[u][r]);
+              else if (op == 1) acc.Max(in[u][r], r == 0);
+              else if (op == 2) acc.Min(in[u][r], r == 0);
+              else acc.Mul(in[u][r], r == 0);
+            }
+            acc.Scale(op == 3 ? postscale : sum_scale);
+          }
+          out = acc.Pack();
+          const uint64_t off = ra.win_off + vec[u] * 16;
+          if (kOneShot) {  // the host side only selects one-shot when a local output exists
+            if (vec[u] * 16 + 16 <= nbytes && (reinterpret_cast<uintptr_t>(ra.dst) & 15) == 0) {
+              *reinterpret_cast<U4*>(ra.dst + vec[u] * 16) = out;
+            } else {
+              const char* ob = reinterpret_cast<const char*>(&out);
+              for (uint64_t b = 0; b < 16 && vec[u] * 16 + b < nbytes; ++b) ra.dst[vec[u] * 16 + b] = ob[b];
+            }
+          } else if (kMultimem) {
+            MultimemSt(ctx.mc + off, out);
+          } else {
+#pragma unroll
+            for (int r = 0; r < kMaxRanks; ++r)
+              if (r < n) StSys(ctx.peer[(ctx.rank + r) % n] + off, out);
+          }
+        }
+      }
+    }
+  }
+  ok = BlockBarrier(ctx, channel, block, epoch + 1, 2) && ok;
+  if (ok && !kOneShot && ra.dst) CopyOwnedTiles(ra.dst, my_win, nbytes, nvec, tile_vecs, false);
+  SaveEpoch(ctx, channel, block, epoch + 1);
+}
+
+// Allgatherv: phase A copies the local slab into the window, phase B pulls every
+// rank's slab from its window into the local output at its displacement.
+struct GatherSizes {
+  uint64_t bytes[kMaxRanks];
+  uint64_t displ[kMaxRanks];
+};
+
+__global__ void __launch_bounds__(kCommThreads)
+AllgathervKernel(CommLaunch args, int channel, GatherSizes sizes) {
+  const RankArgs& ra = args.r[blockIdx.y];
+  const CommCtx& ctx = ra.ctx;
+  const int n        = ctx.nranks;
+  const int block    = blockIdx.x;
+  char* my_win       = ctx.peer[ctx.rank] + ra.win_off;
+  uint32_t epoch     = NextEpoch(ctx, channel, block);
+  const uint64_t my_bytes = sizes.bytes[ctx.rank];
+  CopyOwnedTiles(my_win, ra.src, my_bytes, (my_bytes + 15) / 16, kSubTile, true);
+  bool ok = BlockBarrier(ctx, channel, block, epoch, 1);
+  if (ok) {
+    for (int i = 0; i < n; ++i) {
+      const int r          = (ctx.rank + i) % n;
+      const uint64_t bytes = sizes.bytes[r];
+      const uint64_t nvec  = (bytes + 15) / 16;
+      const uint64_t ntiles = (nvec + kSubTile - 1) / kSubTile;
+      const char* from     = ctx.peer[r] + ra.win_off;
+      char* to             = ra.dst + sizes.displ[r];
+      const bool aligned   = (reinterpret_cast<uintptr_t>(to) & 15) == 0;
+      for (uint64_t t = block; t < ntiles; t += gridDim.x) {
+        const uint64_t lo = t * kSubTile;
+        const uint64_t hi = lo + kSubTile < nvec ? lo + kSubTile : nvec;
+        for (uint64_t v = lo + threadIdx.x; v < hi; v += blockDim.x) {
+          U4 q = LdSys(from + v * 16);
+          if (aligned && v * 16 + 16 <= bytes) {
+            *reinterpret_cast<U4*>(to + v * 16) = q;
+          } else {
+            const char* qb = reinterpret_cast<const char*>(&q);
+            for (uint64_t b = 0; b < 16 && v * 16 + b < bytes; ++b) to[v * 16 + b] = qb[b];
+          }
+        }
+      }
+    }
+  }
+  BlockBarrier(ctx, channel, block, epoch + 1, 2);
+  SaveEpoch(ctx, channel, block, epoch + 1);
+}
+
+// Broadcast: the root writes its data into every rank's window (one multimem
+// store per vector, or one P2P store per peer), then everyone copies from its
+// own window to its output.
+template <bool kMultimem>
+__global__ void __launch_bounds__(kCommThreads)
+BroadcastKernel(CommLaunch args, int channel, uint64_t nbytes, int root) {
+  const RankArgs& ra = args.r[blockIdx.y];
+  const CommCtx& ctx = ra.ctx;
+  const int n        = ctx.nranks;
+  const int block    = blockIdx.x;
+  char* my_win       = ctx.peer[ctx.rank] + ra.win_off;
+  uint32_t epoch     = NextEpoch(ctx, channel, block);
+  const uint64_t nvec   = (nbytes + 15) / 16;
+  const uint64_t ntiles = (nvec + kSubTile - 1) / kSubTile;
+  // Peers must be done with the previous contents of their windows before the root overwrites them.
+  bool ok = BlockBarrier(ctx, channel, block, epoch, 1);
+  if (ok && ctx.rank == root) {
+    const bool src_aligned = (reinterpret_cast<uintptr_t>(ra.src) & 15) == 0;
+    for (uint64_t t = block; t < ntiles; t += gridDim.x) {
+      const uint64_t lo = t * kSubTile;
+      const uint64_t hi = lo + kSubTile < nvec ? lo + kSubTile : nvec;
+      for (uint64_t v = lo + threadIdx.x; v < hi; v += blockDim.x) {
+        U4 q;
+        if (src_aligned && v * 16 + 16 <= nbytes) {
+          q = *reinterpret_cast<const U4*>(ra.src + v * 16);
+        } else {
+          char* qb = reinterpret_cast<char*>(&q);
+          for (uint64_t b = 0; b < 16; ++b) qb[b] = v * 16 + b < nbytes ? ra.src[v * 16 + b] : 0;
+        }
+        if (kMultimem) {
+          MultimemSt(ctx.mc + ra.win_off + v * 16, q);
+        } else {
+          for (int r = 0; r < n; ++r) StSys(ctx.peer[r] + ra.win_off + v * 16, q);
+        }
+      }
+    }
+  }
+  ok = BlockBarrier(ctx, channel, block, epoch + 1, 2) && ok;
+  if (ok && ra.dst) CopyOwnedTiles(ra.dst, my_win, nbytes, nvec, kSubTile, false);
+  SaveEpoch(ctx, channel, block, epoch + 1);
+}
+
+// A kernel that waits for a flag nothing will ever set; used to test the
+// bounded-wait path: it must return with a timeout status inside the budget.
+__global__ void WaitNeverKernel(CommCtx ctx, int channel) {
+  if (threadIdx.x == 0) {
+    const uint32_t* flag = FlagAddr(ctx.peer[ctx.rank], channel, kMaxCommBlocks - 1, ctx.rank);
+    const uint64_t t0    = GlobalTimerNs();
+    const uint32_t want  = *flag + 0x40000000u;
+    while (static_cast<int32_t>(LdAcquireSys(flag) - want) < 0) {
+      if (GlobalTimerNs() - t0 > ctx.budget_ns) {
+        ReportTimeout(ctx, ctx.rank, 9, kMaxCommBlocks - 1, want, channel);
+        break;
+      }
+      __nanosleep(256);
+    }
+  }
+}
+
+// ------------------------------------------------------------------ host side
+
+struct CommState {
+  bool ready = false;
+  int rank = 0, nranks = 1;
+  int emulated = 0;  // >0: all rank windows live on this device (single-GPU tests)
+  CommCtx ctx[kMaxRanks];
+  size_t window_bytes = 0, staging_bytes = 0;
+  cudaStream_t streams[kNumChannels] = {nullptr, nullptr};
+  CommStatus* status_host = nullptr;
+  int blocks = 32;
+  size_t one_shot_bytes = 512 << 10;
+  bool use_multimem = false;
+  std::vector<cudaEvent_t> event_pool;
+  std::mutex mu;
+  uint64_t launches = 0;
+};
+CommState g_comm;
+
+int GridFor(uint64_t nbytes, uint64_t tile_bytes, int max_blocks) {
+  uint64_t tiles = (nbytes + tile_bytes - 1) / tile_bytes;
+  if (tiles < 1) tiles = 1;
+  return static_cast<int>(tiles < static_cast<uint64_t>(max_blocks) ? tiles : max_blocks);
+}
+
+template <typename K, typename... A>
+int LaunchComm(K kernel, int grid_x, cudaStream_t stream, A... a) {
+  CommState& st = g_comm;
+  dim3 grid(grid_x, st.emulated > 0 ? st.emulated : 1), block(kCommThreads);
+  if (st.emulated > 0) {
+    void* params[] = {(void*)&a...};
+    TIPSK_CUDA(cudaLaunchCooperativeKernel((const void*)kernel, grid, block, params, 0, stream));
+  } else {
+    kernel<<<grid, block, 0, stream>>>(a...);
+    TIPSK_LAUNCH_CHECK();
+  }
+  st.launches++;
+  return 0;
+}
+
+}  // namespace
+
+// Gives other translation units (the parameter-server kernels) the rank contexts.
+// Without an initialised communicator it reports a single rank.
+int CommGetContexts(CommCtx* out, int* rank, int* nranks, int* emulated) {
+  CommState& st = g_comm;
+  if (!st.ready) {
+    memset(out, 0, sizeof(CommCtx) * kMaxRanks);
+    *rank     = 0;
+    *nranks   = 1;
+    *emulated = 0;
+    return 0;
+  }
+  for (int i = 0; i < kMaxRanks; ++i) out[i] = st.ctx[i];
+  *rank     = st.rank;
+  *nranks   = st.nranks;
+  *emulated = st.emulated > 0 ? 1 : 0;
+  return 0;
+}
+
+}  // namespace tipsk
+
+using namespace tipsk;
+
+namespace {
+
+// Builds the per-rank launch arguments. In emulation `srcs`/`dsts` hold one
+// pointer per rank; otherwise only entry 0 is used.
+CommLaunch MakeLaunch(const void* const* srcs, void* const* dsts, uint64_t win_off) {
+  CommLaunch l;
+  memset(&l, 0, sizeof(l));
+  CommState& st = g_comm;
+  int n = st.emulated > 0 ? st.emulated : 1;
+  for (int i = 0; i < n; ++i) {
+    l.r[i].ctx     = st.ctx[st.emulated > 0 ? i : st.rank];
+    l.r[i].src     = static_cast<const char*>(srcs ? srcs[i] : nullptr);
+    l.r[i].dst     = static_cast<char*>(dsts ? dsts[i] : nullptr);
+    l.r[i].win_off = win_off;
+  }
+  return l;
+}
+
+template <typename T>
+int LaunchAllreduceT(const CommLaunch& l, int channel, uint64_t nbytes, int op, float pre, float post, bool one_shot,
+                     bool multimem, int grid, cudaStream_t s) {
+  if (one_shot) {
+    if (multimem) return LaunchComm(AllreduceKernel<T, true, true>, grid, s, l, channel, nbytes, op, pre, post);
+    return LaunchComm(AllreduceKernel<T, false, true>, grid, s, l, channel, nbytes, op, pre, post);
+  }
+  if (multimem) return LaunchComm(AllreduceKernel<T, true, false>, grid, s, l, channel, nbytes, op, pre, post);
+  return LaunchComm(AllreduceKernel<T, false, false>, grid, s, l, channel, nbytes, op, pre, post);
+}
+
+int LaunchAllreduce(int dtype, const CommLaunch& l, int channel, uint64_t nbytes, int op, float pre, float post,
+                    bool one_shot, bool multimem, int grid, cudaStream_t s) {
+  switch (dtype) {
+    case kF32: return LaunchAllreduceT<float>(l, channel, nbytes, op, pre, post, one_shot, multimem, grid, s);
+    case kBF16: return LaunchAllreduceT<__nv_bfloat16>(l, channel, nbytes, op, pre, post, one_shot, multimem, grid, s);
+    case kF16: return LaunchAllreduceT<__half>(l, channel, nbytes, op, pre, post, one_shot, multimem, grid, s);
+    case kI32: return LaunchAllreduceT<int32_t>(l, channel, nbytes, op, pre, post, one_shot, false, grid, s);
+    case kI64: return LaunchAllreduceT<int64_t>(l, channel, nbytes, op, pre, post, one_shot, false, grid, s);
+    case kF64: return LaunchAllreduceT<double>(l, channel, nbytes, op, pre, post, one_shot, false, grid, s);
+    default: return SetError(-2, "allreduce: unsupported dtype on the device path");
+  }
+}
+
+}  // namespace
+
+extern "C" {
+
+int tipsk_comm_init(int rank, int nranks, void* const* peer_windows, void* multicast_window, uint64_t window_bytes,
+                    uint64_t staging_bytes, int wait_budget_ms, int blocks, uint64_t one_shot_bytes, int use_multimem,
+                    int emulated) {
+  CommState& st = g_comm;
+  std::lock_guard<std::mutex> lock(st.mu);
+  TIPSK_REQUIRE(nranks >= 1 && nranks <= kMaxRanks, "comm: 1..8 ranks are supported");
+  TIPSK_REQUIRE(rank >= 0 && rank < nranks, "comm: bad rank");
+  TIPSK_REQUIRE(window_bytes >= kSignalBytes + staging_bytes, "comm: window smaller than signals + staging");
+  TIPSK_REQUIRE(blocks >= 1 && blocks <= kMaxCommBlocks, "comm: blocks out of range");
+  st.rank          = rank;
+  st.nranks        = nranks;
+  st.emulated      = emulated ? nranks : 0;
+  st.window_bytes  = window_bytes;
+  st.staging_bytes = staging_bytes & ~static_cast<uint64_t>(4095);
+  st.blocks        = blocks;
+  if (emulated) {  // a cooperative launch needs every block of every rank resident at once
+    int cap = NumSMs() / nranks;
+    if (cap < 1) cap = 1;
+    if (st.blocks > cap) st.blocks = cap;
+  }
+  st.one_shot_bytes = one_shot_bytes;
+  st.use_multimem  = use_multimem && multicast_window != nullptr && !emulated;
+  if (!st.status_host) {
+    TIPSK_CUDA(cudaHostAlloc(reinterpret_cast<void**>(&st.status_host), sizeof(CommStatus) * kMaxRanks,
+                             cudaHostAllocMapped));
+  }
+  memset(st.status_host, 0, sizeof(CommStatus) * kMaxRanks);
+  CommStatus* status_dev = nullptr;
+  TIPSK_CUDA(cudaHostGetDevicePointer(reinterpret_cast<void**>(&status_dev), st.status_host, 0));
+  const int local = emulated ? nranks : 1;
+  for (int i = 0; i < local; ++i) {
+    CommCtx& c = st.ctx[emulated ? i : rank];
+    memset(&c, 0, sizeof(c));
+    for (int r = 0; r < nranks; ++r) c.peer[r] = static_cast<char*>(peer_windows[r]);
+    c.mc        = st.use_multimem ? static_cast<char*>(multicast_window) : nullptr;
+    c.rank      = emulated ? i : rank;
+    c.nranks    = nranks;
+    c.budget_ns = static_cast<uint64_t>(wait_budget_ms) * 1000000ull;
+    c.status    = status_dev + (emulated ? i : 0);
+    TIPSK_CUDA(cudaMalloc(reinterpret_cast<void**>(&c.epochs), sizeof(uint32_t) * kNumChannels * kMaxCommBlocks));
+    TIPSK_CUDA(cudaMemset(c.epochs, 0, sizeof(uint32_t) * kNumChannels * kMaxCommBlocks));
+  }
+  for (int ch = 0; ch < kNumChannels; ++ch) {
+    if (!st.streams[ch]) {
+      int lo = 0, hi = 0;
+      cudaDeviceGetStreamPriorityRange(&lo, &hi);
+      TIPSK_CUDA(cudaStreamCreateWithPriority(&st.streams[ch], cudaStreamNonBlocking, hi));
+    }
+  }
+  TIPSK_CUDA(cudaDeviceSynchronize());
+  st.ready = true;
+  return 0;
+}
+
+int tipsk_comm_shutdown(void) {
+  CommState& st = g_comm;
+  std::lock_guard<std::mutex> lock(st.mu);
+  if (!st.ready) return 0;
+  cudaDeviceSynchronize();
+  for (int i = 0; i < kMaxRanks; ++i) {
+    if (st.ctx[i].epochs) cudaFree(st.ctx[i].epochs);
+    st.ctx[i].epochs = nullptr;
+  }
+  for (cudaEvent_t e : st.event_pool) cudaEventDestroy(e);
+  st.event_pool.clear();
+  st.ready = false;
+  return 0;
+}
+
+int tipsk_comm_ready(void) { return g_comm.ready ? 1 : 0; }
+uint64_t tipsk_comm_staging_offset(void) { return kSignalBytes; }
+uint64_t tipsk_comm_launches(void) { return g_comm.launches; }
+void* tipsk_comm_stream(int channel) { return g_comm.streams[channel & 1]; }
+int tipsk_comm_uses_multimem(void) { return g_comm.use_multimem ? 1 : 0; }
+int tipsk_comm_set_budget_ms(int ms) {
+  for (int i = 0; i < kMaxRanks; ++i) g_comm.ctx[i].budget_ns = static_cast<uint64_t>(ms) * 1000000ull;
+  return 0;
+}
+
+/* Reads (and optionally clears) the status block of local rank slot `slot`.
+ * out = {code, peer, phase, block, epoch, channel, rank}. */
+int tipsk_comm_status(int slot, int32_t* out7, int clear) {
+  CommState& st = g_comm;
+  if (!st.status_host || slot < 0 || slot >= kMaxRanks) return -2;
+  CommStatus s = st.status_host[slot];
+  out7[0] = s.code; out7[1] = s.peer; out7[2] = s.phase; out7[3] = s.block;
+  out7[4] = static_cast<int32_t>(s.epoch); out7[5] = s.channel; out7[6] = s.rank;
+  if (clear) memset(&st.status_host[slot], 0, sizeof(CommStatus));
+  return s.code;
+}
+
+/* Zeroes the flags of this rank's window and the local epoch counters. Call it on every
+ * rank, then synchronise the ranks on the host, before the next collective. */
+int tipsk_comm_reset(void) {
+  CommState& st = g_comm;
+  TIPSK_REQUIRE(st.ready, "comm not initialised");
+  TIPSK_CUDA(cudaDeviceSynchronize());
+  const int local = st.emulated > 0 ? st.emulated : 1;
+  for (int i = 0; i < local; ++i) {
+    CommCtx& c = st.ctx[st.emulated > 0 ? i : st.rank];
+    TIPSK_CUDA(cudaMemset(c.peer[c.rank], 0, kFlagBytes));
+    TIPSK_CUDA(cudaMemset(c.epochs, 0, sizeof(uint32_t) * kNumChannels * kMaxCommBlocks));
+  }
+  memset(st.status_host, 0, sizeof(CommStatus) * kMaxRanks);
+  TIPSK_CUDA(cudaDeviceSynchronize());
+  return 0;
+}
+
+/* Allreduce of `nbytes` bytes of `dtype`.
+ *  win_off >= 0 and srcs == NULL : the data already sits at that offset of every rank's window
+ *                                   (in place; dsts may be NULL to leave the result there)
+ *  srcs != NULL                   : staged through the staging area (win_off ignored)
+ * srcs / dsts are host arrays with one device pointer per LOCAL rank (1, or nranks when emulated). */
+int tipsk_allreduce(const void* const* srcs, void* const* dsts, int64_t win_off, uint64_t nbytes, int dtype, int op,
+                    float prescale, float postscale, int channel, void* stream) {
+  CommState& st = g_comm;
+  TIPSK_REQUIRE(st.ready, "comm not initialised");
+  TIPSK_REQUIRE(channel >= 0 && channel < kNumChannels, "bad channel");
+  if (nbytes == 0) return 0;
+  cudaStream_t s = stream ? static_cast<cudaStream_t>(stream) : st.streams[channel];
+  const bool mm  = st.use_multimem && op == 0;
+  const uint64_t tile_bytes = static_cast<uint64_t>(kSubTile) * st.nranks * 16;
+  if (!srcs) {
+    TIPSK_REQUIRE(win_off >= static_cast<int64_t>(kSignalBytes) && win_off % 16 == 0, "allreduce: bad window offset");
+    TIPSK_REQUIRE(static_cast<uint64_t>(win_off) + ((nbytes + 15) & ~15ull) <= st.window_bytes,
+                  "allreduce: buffer exceeds the window");
+    const bool one_shot = dsts != nullptr && nbytes <= st.one_shot_bytes;
+    CommLaunch l = MakeLaunch(nullptr, dsts, static_cast<uint64_t>(win_off));
+    return LaunchAllreduce(dtype, l, channel, nbytes, op, prescale, postscale, one_shot, mm,
+                           GridFor(nbytes, tile_bytes, st.blocks), s);
+  }
+  TIPSK_REQUIRE(dsts != nullptr, "allreduce: staged mode needs an output");
+  const uint64_t chunk = st.staging_bytes;
+  TIPSK_REQUIRE(chunk >= 4096, "allreduce: no staging area configured");
+  const int local = st.emulated > 0 ? st.emulated : 1;
+  for (uint64_t done = 0; done < nbytes; done += chunk) {
+    const uint64_t len = nbytes - done < chunk ? nbytes - done : chunk;
+    const void* sp[kMaxRanks];
+    void* dp[kMaxRanks];
+    for (int i = 0; i < local; ++i) {
+      sp[i] = static_cast<const char*>(srcs[i]) + done;
+      dp[i] = static_cast<char*>(dsts[i]) + done;
+    }
+    CommLaunch l = MakeLaunch(sp, dp, kSignalBytes);
+    const bool one_shot = len <= st.one_shot_bytes;
+    int rc = LaunchAllreduce(dtype, l, channel, len, op, prescale, postscale, one_shot, mm,
+                             GridFor(len, tile_bytes, st.blocks), s);
+    if (rc) return rc;
+  }
+  return 0;
+}
+
+/* Allgatherv of per-rank byte counts; staged through the staging area, chunked when a slab is larger. */
+int tipsk_allgatherv(const void* const* srcs, void* const* dsts, const uint64_t* bytes_per_rank, int channel,
+                     void* stream) {
+  CommState& st = g_comm;
+  TIPSK_REQUIRE(st.ready, "comm not initialised");
+  cudaStream_t s = stream ? static_cast<cudaStream_t>(stream) : st.streams[channel];
+  const int n     = st.nranks;
+  const int local = st.emulated > 0 ? st.emulated : 1;
+  uint64_t displ[kMaxRanks], largest = 0;
+  uint64_t acc = 0;
+  for (int r = 0; r < n; ++r) {
+    displ[r] = acc;
+    acc += bytes_per_rank[r];
+    if (bytes_per_rank[r] > largest) largest = bytes_per_rank[r];
+  }
+  const uint64_t chunk = st.staging_bytes;
+  TIPSK_REQUIRE(chunk >= 4096, "allgatherv: no staging area configured");
+  for (uint64_t done = 0; done < largest; done += chunk) {
+    GatherSizes gs;
+    memset(&gs, 0, sizeof(gs));
+    for (int r = 0; r < n; ++r) {
+      uint64_t left = bytes_per_rank[r] > done ? bytes_per_rank[r] - done : 0;
+      gs.bytes[r]   = left < chunk ? left : chunk;
+      gs.displ[r]   = displ[r] + done;
+    }
+    const void* sp[kMaxRanks];
+    for (int i = 0; i < local; ++i) {
+      int r = st.emulated > 0 ? i : st.rank;
+      sp[i] = static_cast<const char*>(srcs[i]) + (bytes_per_rank[r] > done ? done : 0);
+    }
+    CommLaunch l = MakeLaunch(sp, dsts, kSignalBytes);
+    uint64_t biggest = 0;
+    for (int r = 0; r < n; ++r) if (gs.bytes[r] > biggest) biggest = gs.bytes[r];
+    int rc = LaunchComm(AllgathervKernel, GridFor(biggest, static_cast<uint64_t>(kSubTile) * 16, st.blocks), s, l,
+                        channel, gs);
+    if (rc) return rc;
+  }
+  return 0;
+}
+
+int tipsk_broadcast(const void* const* srcs, void* const* dsts, uint64_t nbytes, int root, int channel, void* stream) {
+  CommState& st = g_comm;
+  TIPSK_REQUIRE(st.ready, "comm not initialised");
+  TIPSK_REQUIRE(root >= 0 && root < st.nranks, "broadcast: bad root");
+  cudaStream_t s = stream ? static_cast<cudaStream_t>(stream) : st.streams[channel];
+  const uint64_t chunk = st.staging_bytes;
+  TIPSK_REQUIRE(chunk >= 4096, "broadcast: no staging area configured");
+  const int local = st.emulated > 0 ? st.emulated : 1;
+  for (uint64_t done = 0; done < nbytes; done += chunk) {
+    const uint64_t len = nbytes - done < chunk ? nbytes - done : chunk;
+    const void* sp[kMaxRanks];
+    void* dp[kMaxRanks];
+    for (int i = 0; i < local; ++i) {
+      sp[i] = srcs[i] ? static_cast<const char*>(srcs[i]) + done : nullptr;
+      dp[i] = static_cast<char*>(dsts[i]) + done;
+    }
+    CommLaunch l = MakeLaunch(sp, dp, kSignalBytes);
+    const int grid = GridFor(len, static_cast<uint64_t>(kSubTile) * 16, st.blocks);
+    int rc = st.use_multimem ? LaunchComm(BroadcastKernel<true>, grid, s, l, channel, len, root)
+                             : LaunchComm(BroadcastKernel<false>, grid, s, l, channel, len, root);
+    if (rc) return rc;
+  }
+  return 0;
+}
+
+/* Launches a kernel that waits (bounded) for a flag that is never set; afterwards
+ * tipsk_comm_status reports a timeout. */
+int tipsk_comm_wait_never(int channel, void* stream) {
+  CommState& st = g_comm;
+  TIPSK_REQUIRE(st.ready, "comm not initialised");
+  cudaStream_t s = stream ? static_cast<cudaStream_t>(stream) : st.streams[channel & 1];
+  WaitNeverKernel<<<1, 32, 0, s>>>(st.ctx[st.emulated > 0 ? 0 : st.rank], channel & 1);
+  TIPSK_LAUNCH_CHECK();
+  return 0;
+}
+
+/* ---- events / streams for the executor and the Python layer ---- */
+void* tipsk_event_create(void) {
+  CommState& st = g_comm;
+  {
+    std::lock_guard<std::mutex> lock(st.mu);
+    if (!st.event_pool.empty()) {
+      cudaEvent_t e = st.event_pool.back();
+      st.event_pool.pop_back();
+      return e;
+    }
+  }
+  cudaEvent_t e = nullptr;
+  if (cudaEventCreateWithFlags(&e, cudaEventDisableTiming) != cudaSuccess) return nullptr;
+  return e;
+}
+void tipsk_event_recycle(void* ev) {
+  if (!ev) return;
+  std::lock_guard<std::mutex> lock(g_comm.mu);
+  g_comm.event_pool.push_back(static_cast<cudaEvent_t>(ev));
+}
+int tipsk_event_record(void* ev, void* stream) {
+  TIPSK_CUDA(cudaEventRecord(static_cast<cudaEvent_t>(ev), static_cast<cudaStream_t>(stream)));
+  return 0;
+}
+int tipsk_stream_wait_event(void* stream, void* ev) {
+  TIPSK_CUDA(cudaStreamWaitEvent(static_cast<cudaStream_t>(stream), static_cast<cudaEvent_t>(ev), 0));
+  return 0;
+}
+int tipsk_stream_synchronize(void* stream) {
+  TIPSK_CUDA(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
+  return 0;
+}
+
+}  // extern "C"

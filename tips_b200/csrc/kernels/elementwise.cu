@@ -1,0 +1,353 @@
+// HBM-bound elementwise kernels: fused optimizers (SGD-momentum, Adam/AdamW) on
+// flat parameter slabs and on tensor lists, gradient pack / unpack between
+// tensor lists and a flat fusion bucket (with scale, cast and accumulate), and
+// scale+cast.
+//
+// The reference has none of these: its only math kernel is the elementwise
+// Vec::Mul loop used by the server-side update (tips/core/common/vec.h:194-216)
+// and gradient accumulation / averaging are TensorFlow ops
+// (tips/tensorflow/gradient_aggregation_eager.py:74, gradient_aggregation.py:166-173).
+// Here one launch covers a whole bucket: every element is read once and written
+// once, in 16-byte vectors, so the kernels run at HBM speed.
+#include "kernels/common.cuh"
+#include "kernels/tips_kernels.h"
+
+namespace tipsk {
+
+std::string& LastError() {
+  static thread_local std::string err;
+  return err;
+}
+int SetError(int code, const std::string& msg) {
+  LastError() = msg;
+  return code;
+}
+int NumSMs() {
+  static int sms = 0;
+  if (sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (sms <= 0) sms = 148;
+  }
+  return sms;
+}
+
+namespace {
+
+constexpr int kThreads = 256;
+
+template <typename T>
+struct alignas(sizeof(T) * 4) Quad {  // four consecutive elements of T
+  T v[4];
+};
+
+template <typename T>
+__device__ __forceinline__ void Load4(const T* p, float (&out)[4]) {
+  Quad<T> q = *reinterpret_cast<const Quad<T>*>(p);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) out[i] = ToFloat<T>(q.v[i]);
+}
+template <typename T>
+__device__ __forceinline__ void Store4(T* p, const float (&in)[4]) {
+  Quad<T> q;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) q.v[i] = FromFloat<T>(in[i]);
+  *reinterpret_cast<Quad<T>*>(p) = q;
+}
+
+struct SgdParams {
+  float lr, momentum, dampening, wd, grad_scale;
+  int nesterov, first_step;
+};
+
+__device__ __forceinline__ void SgdUpdate(float& p, float& m, float g, const SgdParams& a) {
+  g = g * a.grad_scale + a.wd * p;
+  if (a.momentum != 0.f) {
+    m = a.first_step ? g : a.momentum * m + (1.f - a.dampening) * g;
+    g = a.nesterov ? g + a.momentum * m : m;
+  }
+  p -= a.lr * g;
+}
+
+template <typename G, typename P16>
+__global__ void __launch_bounds__(kThreads)
+SgdFlatKernel(float* __restrict__ p32, P16* __restrict__ p16, const G* __restrict__ g, float* __restrict__ m,
+              int64_t n, SgdParams a) {
+  const int64_t nvec   = n / 4;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < nvec; i += stride) {
+    float pv[4], gv[4], mv[4];
+    Load4(p32 + i * 4, pv);
+    Load4(g + i * 4, gv);
+    if (a.momentum != 0.f && !a.first_step) Load4(m + i * 4, mv);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) SgdUpdate(pv[k], mv[k], gv[k], a);
+    Store4(p32 + i * 4, pv);
+    if (a.momentum != 0.f) Store4(m + i * 4, mv);
+    if (p16) Store4(p16 + i * 4, pv);
+  }
+  // tail
+  const int64_t t = nvec * 4 + static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (t < n) {
+    float p = p32[t], mm = (a.momentum != 0.f && !a.first_step) ? m[t] : 0.f;
+    SgdUpdate(p, mm, ToFloat<G>(g[t]), a);
+    p32[t] = p;
+    if (a.momentum != 0.f) m[t] = mm;
+    if (p16) p16[t] = FromFloat<P16>(p);
+  }
+}
+
+struct AdamParams {
+  float lr, beta1, beta2, eps, wd, grad_scale, bias1, bias2;  // bias = 1 - beta^step
+  int decoupled;
+};
+
+__device__ __forceinline__ void AdamUpdate(float& p, float& m, float& v, float g, const AdamParams& a) {
+  g *= a.grad_scale;
+  if (!a.decoupled) g += a.wd * p;
+  m = a.beta1 * m + (1.f - a.beta1) * g;
+  v = a.beta2 * v + (1.f - a.beta2) * g * g;
+  const float mhat  = m / a.bias1;
+  const float denom = sqrtf(v / a.bias2) + a.eps;
+  if (a.decoupled) p *= (1.f - a.lr * a.wd);
+  p -= a.lr * mhat / denom;
+}
+
+template <typename G, typename P16>
+__global__ void __launch_bounds__(kThreads)
+AdamFlatKernel(float* __restrict__ p32, P16* __restrict__ p16, const G* __restrict__ g, float* __restrict__ m,
+               float* __restrict__ v, int64_t n, AdamParams a) {
+  const int64_t nvec   = n / 4;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < nvec; i += stride) {
+    float pv[4], gv[4], mv[4], vv[4];
+    Load4(p32 + i * 4, pv);
+    Load4(g + i * 4, gv);
+    Load4(m + i * 4, mv);
+    Load4(v + i * 4, vv);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) AdamUpdate(pv[k], mv[k], vv[k], gv[k], a);
+    Store4(p32 + i * 4, pv);
+    Store4(m + i * 4, mv);
+    Store4(v + i * 4, vv);
+    if (p16) Store4(p16 + i * 4, pv);
+  }
+  const int64_t t = nvec * 4 + static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (t < n) {
+    float p = p32[t], mm = m[t], vv = v[t];
+    AdamUpdate(p, mm, vv, ToFloat<G>(g[t]), a);
+    p32[t] = p;
+    m[t]   = mm;
+    v[t]   = vv;
+    if (p16) p16[t] = FromFloat<P16>(p);
+  }
+}
+
+int FlatGrid(int64_t n) {
+  int64_t blocks = (n / 4 + kThreads - 1) / kThreads;
+  int64_t cap    = static_cast<int64_t>(NumSMs()) * 8;
+  if (blocks < 1) blocks = 1;
+  return static_cast<int>(blocks < cap ? blocks : cap);
+}
+
+// ---- pack / unpack ------------------------------------------------------------
+
+constexpr int kMaxList = 96;
+struct ListArgs {
+  const void* ptr[kMaxList];
+  int64_t offset[kMaxList];  // element offset inside the flat buffer
+  int64_t numel[kMaxList];
+};
+
+// mode 0: flat = scale * src ; mode 1: flat += scale * src ; mode 2: dst = scale * flat (unpack)
+template <typename S, typename D, int kMode>
+__global__ void __launch_bounds__(kThreads) PackKernel(ListArgs args, void* flat_v, float scale) {
+  const int t       = blockIdx.y;
+  const int64_t n   = args.numel[t];
+  const int64_t off = args.offset[t];
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  if (kMode == 2) {
+    const S* flat = static_cast<const S*>(flat_v) + off;
+    D* dst        = static_cast<D*>(const_cast<void*>(args.ptr[t]));
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride)
+      dst[i] = FromFloat<D>(ToFloat<S>(flat[i]) * scale);
+  } else {
+    const S* src = static_cast<const S*>(args.ptr[t]);
+    D* flat      = static_cast<D*>(flat_v) + off;
+    const bool aligned = ((reinterpret_cast<uintptr_t>(src) % (4 * sizeof(S))) == 0) &&
+                         ((reinterpret_cast<uintptr_t>(flat) % (4 * sizeof(D))) == 0);
+    if (aligned) {
+      const int64_t nvec = n / 4;
+      for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < nvec; i += stride) {
+        float s[4];
+        Load4(src + i * 4, s);
+        if (kMode == 1) {
+          float d[4];
+          Load4(flat + i * 4, d);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) s[k] = d[k] + s[k] * scale;
+        } else {
+#pragma unroll
+          for (int k = 0; k < 4; ++k) s[k] *= scale;
+        }
+        Store4(flat + i * 4, s);
+      }
+      const int64_t i = nvec * 4 + static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+      if (i < n) {
+        float s = ToFloat<S>(src[i]) * scale;
+        if (kMode == 1) s += ToFloat<D>(flat[i]);
+        flat[i] = FromFloat<D>(s);
+      }
+    } else {
+      for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
+        float s = ToFloat<S>(src[i]) * scale;
+        if (kMode == 1) s += ToFloat<D>(flat[i]);
+        flat[i] = FromFloat<D>(s);
+      }
+    }
+  }
+}
+
+template <typename S, typename D>
+int LaunchPack(int mode, const void* const* ptrs, const int64_t* offsets, const int64_t* numels, int n, void* flat,
+               float scale, cudaStream_t stream) {
+  for (int base = 0; base < n; base += kMaxList) {
+    ListArgs a;
+    int cnt         = n - base < kMaxList ? n - base : kMaxList;
+    int64_t largest = 1;
+    for (int i = 0; i < cnt; ++i) {
+      a.ptr[i]    = ptrs[base + i];
+      a.offset[i] = offsets[base + i];
+      a.numel[i]  = numels[base + i];
+      if (numels[base + i] > largest) largest = numels[base + i];
+    }
+    int gx = CeilDiv(largest, kThreads * 4 * 4);
+    if (gx > 64) gx = 64;
+    if (gx < 1) gx = 1;
+    dim3 grid(gx, cnt);
+    if (mode == 0)
+      PackKernel<S, D, 0><<<grid, kThreads, 0, stream>>>(a, flat, scale);
+    else if (mode == 1)
+      PackKernel<S, D, 1><<<grid, kThreads, 0, stream>>>(a, flat, scale);
+    else
+      PackKernel<S, D, 2><<<grid, kThreads, 0, stream>>>(a, flat, scale);
+    TIPSK_LAUNCH_CHECK();
+  }
+  return 0;
+}
+
+template <typename S, typename D>
+__global__ void __launch_bounds__(kThreads) ScaleCastKernel(const S* __restrict__ src, D* __restrict__ dst, int64_t n,
+                                                            float scale) {
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride)
+    dst[i] = FromFloat<D>(ToFloat<S>(src[i]) * scale);
+}
+
+}  // namespace
+}  // namespace tipsk
+
+using namespace tipsk;
+
+#define TIPSK_DISPATCH_FLOAT(dt, T, ...)                                  \
+  switch (dt) {                                                           \
+    case kF32: { using T = float; __VA_ARGS__; } break;                   \
+    case kBF16: { using T = __nv_bfloat16; __VA_ARGS__; } break;          \
+    case kF16: { using T = __half; __VA_ARGS__; } break;                  \
+    default: return SetError(-2, "unsupported floating dtype");           \
+  }
+
+extern "C" {
+
+const char* tipsk_last_error(void) { return LastError().c_str(); }
+
+int tipsk_sgd_momentum_flat(float* p32, void* p16, int p16_dtype, const void* grad, int grad_dtype, float* momentum_buf,
+                            int64_t n, float lr, float momentum, float dampening, float weight_decay, int nesterov,
+                            float grad_scale, int first_step, void* stream) {
+  if (n <= 0) return 0;
+  TIPSK_REQUIRE(p32 && grad, "sgd: null pointer");
+  TIPSK_REQUIRE(momentum == 0.f || momentum_buf, "sgd: momentum buffer missing");
+  SgdParams a{lr, momentum, dampening, weight_decay, grad_scale, nesterov, first_step};
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int grid = FlatGrid(n);
+  TIPSK_DISPATCH_FLOAT(grad_dtype, G, {
+    if (!p16 || p16_dtype == kBF16)
+      SgdFlatKernel<G, __nv_bfloat16><<<grid, kThreads, 0, s>>>(p32, static_cast<__nv_bfloat16*>(p16),
+                                                                 static_cast<const G*>(grad), momentum_buf, n, a);
+    else if (p16_dtype == kF16)
+      SgdFlatKernel<G, __half><<<grid, kThreads, 0, s>>>(p32, static_cast<__half*>(p16), static_cast<const G*>(grad),
+                                                         momentum_buf, n, a);
+    else
+      return SetError(-2, "sgd: low-precision copy must be bf16 or fp16");
+  });
+  TIPSK_LAUNCH_CHECK();
+  return 0;
+}
+
+int tipsk_adam_flat(float* p32, void* p16, int p16_dtype, const void* grad, int grad_dtype, float* exp_avg,
+                    float* exp_avg_sq, int64_t n, float lr, float beta1, float beta2, float eps, float weight_decay,
+                    int64_t step, float grad_scale, int decoupled, void* stream) {
+  if (n <= 0) return 0;
+  TIPSK_REQUIRE(p32 && grad && exp_avg && exp_avg_sq, "adam: null pointer");
+  TIPSK_REQUIRE(step >= 1, "adam: step counts from 1");
+  AdamParams a{lr, beta1, beta2, eps, weight_decay, grad_scale,
+               1.f - powf(beta1, static_cast<float>(step)), 1.f - powf(beta2, static_cast<float>(step)), decoupled};
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int grid = FlatGrid(n);
+  TIPSK_DISPATCH_FLOAT(grad_dtype, G, {
+    if (!p16 || p16_dtype == kBF16)
+      AdamFlatKernel<G, __nv_bfloat16><<<grid, kThreads, 0, s>>>(p32, static_cast<__nv_bfloat16*>(p16),
+                                                                  static_cast<const G*>(grad), exp_avg, exp_avg_sq, n, a);
+    else if (p16_dtype == kF16)
+      AdamFlatKernel<G, __half><<<grid, kThreads, 0, s>>>(p32, static_cast<__half*>(p16), static_cast<const G*>(grad),
+                                                          exp_avg, exp_avg_sq, n, a);
+    else
+      return SetError(-2, "adam: low-precision copy must be bf16 or fp16");
+  });
+  TIPSK_LAUNCH_CHECK();
+  return 0;
+}
+
+int tipsk_pack(const void* const* srcs, const int64_t* offsets, const int64_t* numels, int ntensors, int src_dtype,
+               void* flat, int flat_dtype, float scale, int accumulate, void* stream) {
+  if (ntensors <= 0) return 0;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  TIPSK_DISPATCH_FLOAT(src_dtype, S, {
+    TIPSK_DISPATCH_FLOAT(flat_dtype, D, {
+      int rc = LaunchPack<S, D>(accumulate ? 1 : 0, srcs, offsets, numels, ntensors, flat, scale, s);
+      if (rc) return rc;
+    });
+  });
+  return 0;
+}
+
+int tipsk_unpack(const void* flat, int flat_dtype, void* const* dsts, const int64_t* offsets, const int64_t* numels,
+                 int ntensors, int dst_dtype, float scale, void* stream) {
+  if (ntensors <= 0) return 0;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  TIPSK_DISPATCH_FLOAT(flat_dtype, S, {
+    TIPSK_DISPATCH_FLOAT(dst_dtype, D, {
+      int rc = LaunchPack<S, D>(2, reinterpret_cast<const void* const*>(dsts), offsets, numels, ntensors,
+                                const_cast<void*>(flat), scale, s);
+      if (rc) return rc;
+    });
+  });
+  return 0;
+}
+
+int tipsk_scale_cast(const void* src, int src_dtype, void* dst, int dst_dtype, int64_t n, float scale, void* stream) {
+  if (n <= 0) return 0;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  int grid       = CeilDiv(n, kThreads * 4);
+  if (grid > NumSMs() * 8) grid = NumSMs() * 8;
+  TIPSK_DISPATCH_FLOAT(src_dtype, S, {
+    TIPSK_DISPATCH_FLOAT(dst_dtype, D, {
+      ScaleCastKernel<S, D><<<grid, kThreads, 0, s>>>(static_cast<const S*>(src), static_cast<D*>(dst), n, scale);
+    });
+  });
+  TIPSK_LAUNCH_CHECK();
+  return 0;
+}
+
+}  // extern "C"

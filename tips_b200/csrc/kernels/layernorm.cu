@@ -1,0 +1,265 @@
+// Layer normalisation over the last dimension of a row-major [rows, cols]
+// matrix, forward and backward.  One warp owns a row: it reads the row once in
+// 16-byte vectors, keeps it in registers, and produces mean / rstd / output (or
+// dx) without a second trip to HBM.  In the backward pass each warp also
+// accumulates dgamma / dbeta for its lane's columns over all the rows it
+// visits; blocks write one partial row each and a small second kernel sums
+// them.  The reference has no model math; this serves the BERT-shaped encoder.
+#include "kernels/common.cuh"
+#include "kernels/tips_kernels.h"
+
+namespace tipsk {
+namespace {
+
+constexpr int kWarpsPerBlock = 4;
+
+template <typename T>
+struct VecOf {
+  static constexpr int kN = 16 / sizeof(T);
+};
+
+// VPL = 16-byte vectors per lane; handles cols <= 32 * VPL * kN, cols % kN == 0.
+template <typename T, int VPL>
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+LnFwdKernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* __restrict__ beta, T* __restrict__ y,
+            float* __restrict__ mean_out, float* __restrict__ rstd_out, int64_t rows, int cols, float eps) {
+  constexpr int N = VecOf<T>::kN;
+  const int lane  = threadIdx.x & 31;
+  const int warp  = threadIdx.x >> 5;
+  const int nvec  = cols / N;
+  for (int64_t r = static_cast<int64_t>(blockIdx.x) * kWarpsPerBlock + warp; r < rows;
+       r += static_cast<int64_t>(gridDim.x) * kWarpsPerBlock) {
+    const T* xr = x + r * cols;
+    float v[VPL][N];
+    float sum = 0.f;
+#pragma unroll
+    for (int k = 0; k < VPL; ++k) {
+      const int vi = lane + k * 32;
+      if (vi < nvec) {
+        Vec16<T> q = LoadVec(xr + vi * N);
+#pragma unroll
+        for (int i = 0; i < N; ++i) {
+          v[k][i] = ToFloat<T>(q.v[i]);
+          sum += v[k][i];
+        }
+      }
+    }
+    const float mean = WarpSum(sum) / cols;
+    float sq = 0.f;
+#pragma unroll
+    for (int k = 0; k < VPL; ++k) {
+      const int vi = lane + k * 32;
+      if (vi < nvec) {
+#pragma unroll
+        for (int i = 0; i < N; ++i) {
+          const float d = v[k][i] - mean;
+          sq += d * d;
+        }
+      }
+    }
+    const float rstd = rsqrtf(WarpSum(sq) / cols + eps);
+    if (lane == 0) {
+      mean_out[r] = mean;
+      rstd_out[r] = rstd;
+    }
+    T* yr = y + r * cols;
+#pragma unroll
+    for (int k = 0; k < VPL; ++k) {
+      const int vi = lane + k * 32;
+      if (vi < nvec) {
+        Vec16<T> g = LoadVec(gamma + vi * N), b = LoadVec(beta + vi * N), o;
+#pragma unroll
+        for (int i = 0; i < N; ++i)
+          o.v[i] = FromFloat<T>((v[k][i] - mean) * rstd * ToFloat<T>(g.v[i]) + ToFloat<T>(b.v[i]));
+        StoreVec(yr + vi * N, o);
+      }
+    }
+  }
+}
+
+template <typename T, int VPL>
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+LnBwdKernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ gamma,
+            const float* __restrict__ mean, const float* __restrict__ rstd, T* __restrict__ dx,
+            float* __restrict__ dgamma_partial, float* __restrict__ dbeta_partial, int64_t rows, int cols) {
+  constexpr int N = VecOf<T>::kN;
+  extern __shared__ float smem[];  // [kWarpsPerBlock][2][cols]
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  const int nvec = cols / N;
+  float dg[VPL][N], db[VPL][N], gm[VPL][N];
+#pragma unroll
+  for (int k = 0; k < VPL; ++k) {
+    const int vi = lane + k * 32;
+    Vec16<T> g;
+    if (vi < nvec) g = LoadVec(gamma + vi * N);
+#pragma unroll
+    for (int i = 0; i < N; ++i) {
+      dg[k][i] = db[k][i] = 0.f;
+      gm[k][i] = vi < nvec ? ToFloat<T>(g.v[i]) : 0.f;
+    }
+  }
+  for (int64_t r = static_cast<int64_t>(blockIdx.x) * kWarpsPerBlock + warp; r < rows;
+       r += static_cast<int64_t>(gridDim.x) * kWarpsPerBlock) {
+    const float mu = mean[r], rs = rstd[r];
+    float xh[VPL][N], dyv[VPL][N];
+    float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int k = 0; k < VPL; ++k) {
+      const int vi = lane + k * 32;
+      if (vi < nvec) {
+        Vec16<T> qx = LoadVec(x + r * cols + vi * N), qd = LoadVec(dy + r * cols + vi * N);
+#pragma unroll
+        for (int i = 0; i < N; ++i) {
+          xh[k][i]  = (ToFloat<T>(qx.v[i]) - mu) * rs;
+          dyv[k][i] = ToFloat<T>(qd.v[i]);
+          const float dyg = dyv[k][i] * gm[k][i];
+          s1 += dyg;
+          s2 += dyg * xh[k][i];
+          dg[k][i] += dyv[k][i] * xh[k][i];
+          db[k][i] += dyv[k][i];
+        }
+      }
+    }
+    s1 = WarpSum(s1) / cols;
+    s2 = WarpSum(s2) / cols;
+#pragma unroll
+    for (int k = 0; k < VPL; ++k) {
+      const int vi = lane + k * 32;
+      if (vi < nvec) {
+        Vec16<T> o;
+#pragma unroll
+        for (int i = 0; i < N; ++i) o.v[i] = FromFloat<T>(rs * (dyv[k][i] * gm[k][i] - s1 - xh[k][i] * s2));
+        StoreVec(dx + r * cols + vi * N, o);
+      }
+    }
+  }
+  // block-level reduction of the per-warp column sums
+  float* sg = smem + warp * 2 * cols;
+  float* sb = sg + cols;
+#pragma unroll
+  for (int k = 0; k < VPL; ++k) {
+    const int vi = lane + k * 32;
+    if (vi < nvec) {
+#pragma unroll
+      for (int i = 0; i < N; ++i) {
+        sg[vi * N + i] = dg[k][i];
+        sb[vi * N + i] = db[k][i];
+      }
+    }
+  }
+  __syncthreads();
+  for (int c = threadIdx.x; c < cols; c += blockDim.x) {
+    float a = 0.f, b = 0.f;
+#pragma unroll
+    for (int w = 0; w < kWarpsPerBlock; ++w) {
+      a += smem[w * 2 * cols + c];
+      b += smem[w * 2 * cols + cols + c];
+    }
+    dgamma_partial[static_cast<int64_t>(blockIdx.x) * cols + c] = a;
+    dbeta_partial[static_cast<int64_t>(blockIdx.x) * cols + c]  = b;
+  }
+}
+
+template <typename T>
+__global__ void LnReducePartialsKernel(const float* __restrict__ pg, const float* __restrict__ pb, int partial_rows,
+                                       int cols, T* __restrict__ dgamma, T* __restrict__ dbeta) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= cols) return;
+  float a = 0.f, b = 0.f;
+  for (int p = 0; p < partial_rows; ++p) {
+    a += pg[static_cast<int64_t>(p) * cols + c];
+    b += pb[static_cast<int64_t>(p) * cols + c];
+  }
+  dgamma[c] = FromFloat<T>(a);
+  dbeta[c]  = FromFloat<T>(b);
+}
+
+int LnGrid(int64_t rows) {
+  int64_t blocks = (rows + kWarpsPerBlock - 1) / kWarpsPerBlock;
+  int64_t cap    = static_cast<int64_t>(NumSMs()) * 8;
+  return static_cast<int>(blocks < cap ? (blocks < 1 ? 1 : blocks) : cap);
+}
+
+}  // namespace
+}  // namespace tipsk
+
+using namespace tipsk;
+
+#define LN_DISPATCH(dtype, cols, ...)                                                        \
+  {                                                                                          \
+    if (dtype == kBF16) { using T = __nv_bfloat16; LN_VPL(cols, __VA_ARGS__) }               \
+    else if (dtype == kF16) { using T = __half; LN_VPL(cols, __VA_ARGS__) }                  \
+    else if (dtype == kF32) { using T = float; LN_VPL(cols, __VA_ARGS__) }                   \
+    else return SetError(-2, "layer norm: unsupported dtype");                               \
+  }
+#define LN_VPL(cols, ...)                                                                    \
+  {                                                                                          \
+    const int per_lane = ((cols) / VecOf<T>::kN + 31) / 32;                                  \
+    if (per_lane <= 1) { constexpr int VPL = 1; __VA_ARGS__; }                               \
+    else if (per_lane <= 2) { constexpr int VPL = 2; __VA_ARGS__; }                          \
+    else if (per_lane <= 4) { constexpr int VPL = 4; __VA_ARGS__; }                          \
+    else if (per_lane <= 8) { constexpr int VPL = 8; __VA_ARGS__; }                          \
+    else return SetError(-2, "layer norm: rows longer than 8 vectors per lane are not supported"); \
+  }
+
+extern "C" {
+
+int tipsk_ln_fwd(const void* x, const void* gamma, const void* beta, void* y, float* mean, float* rstd, int64_t rows,
+                 int cols, float eps, int dtype, void* stream) {
+  if (rows <= 0) return 0;
+  TIPSK_REQUIRE(cols > 0 && cols % (16 / (int)DTypeSize(dtype)) == 0, "layer norm: cols must be a multiple of 16 bytes");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  LN_DISPATCH(dtype, cols, {
+    LnFwdKernel<T, VPL><<<LnGrid(rows), kWarpsPerBlock * 32, 0, s>>>(
+        static_cast<const T*>(x), static_cast<const T*>(gamma), static_cast<const T*>(beta), static_cast<T*>(y), mean,
+        rstd, rows, cols, eps);
+  });
+  TIPSK_LAUNCH_CHECK();
+  return 0;
+}
+
+int tipsk_ln_bwd_partials(int64_t rows, int cols) {
+  (void)cols;
+  return LnGrid(rows);
+}
+
+int tipsk_ln_bwd(const void* dy, const void* x, const void* gamma, const float* mean, const float* rstd, void* dx,
+                 float* dgamma_partial, float* dbeta_partial, int partial_rows, int64_t rows, int cols, int dtype,
+                 void* stream) {
+  if (rows <= 0) return 0;
+  TIPSK_REQUIRE(cols > 0 && cols % (16 / (int)DTypeSize(dtype)) == 0, "layer norm: cols must be a multiple of 16 bytes");
+  TIPSK_REQUIRE(partial_rows == LnGrid(rows), "layer norm backward: wrong number of partial rows");
+  cudaStream_t s    = static_cast<cudaStream_t>(stream);
+  const size_t smem = sizeof(float) * kWarpsPerBlock * 2 * cols;
+  TIPSK_REQUIRE(smem <= 48 * 1024, "layer norm backward: row too long for the shared-memory reduction");
+  LN_DISPATCH(dtype, cols, {
+    LnBwdKernel<T, VPL><<<partial_rows, kWarpsPerBlock * 32, smem, s>>>(
+        static_cast<const T*>(dy), static_cast<const T*>(x), static_cast<const T*>(gamma), mean, rstd,
+        static_cast<T*>(dx), dgamma_partial, dbeta_partial, rows, cols);
+  });
+  TIPSK_LAUNCH_CHECK();
+  return 0;
+}
+
+int tipsk_ln_reduce_partials(const float* dgamma_partial, const float* dbeta_partial, int partial_rows, int cols,
+                             void* dgamma, void* dbeta, int dtype, void* stream) {
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int grid = CeilDiv(cols, 128);
+  if (dtype == kBF16)
+    LnReducePartialsKernel<__nv_bfloat16><<<grid, 128, 0, s>>>(dgamma_partial, dbeta_partial, partial_rows, cols,
+                                                               static_cast<__nv_bfloat16*>(dgamma),
+                                                               static_cast<__nv_bfloat16*>(dbeta));
+  else if (dtype == kF16)
+    LnReducePartialsKernel<__half><<<grid, 128, 0, s>>>(dgamma_partial, dbeta_partial, partial_rows, cols,
+                                                        static_cast<__half*>(dgamma), static_cast<__half*>(dbeta));
+  else if (dtype == kF32)
+    LnReducePartialsKernel<float><<<grid, 128, 0, s>>>(dgamma_partial, dbeta_partial, partial_rows, cols,
+                                                       static_cast<float*>(dgamma), static_cast<float*>(dbeta));
+  else
+    return SetError(-2, "layer norm: unsupported dtype");
+  TIPSK_LAUNCH_CHECK();
+  return 0;
+}
+
+}  // extern "C"

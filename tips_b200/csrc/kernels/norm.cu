@@ -1,0 +1,382 @@
+// Batch normalisation (channels-last) and layer normalisation, forward and
+// backward, with the neighbouring pointwise work fused in: the BN forward adds
+// the residual branch and applies ReLU while it writes the output, and the BN
+// backward applies the ReLU mask and emits the residual gradient while it reads
+// dy.  The reference delegates all model math to TensorFlow ops; these kernels
+// exist because normalisation layers are HBM-bound and every extra pass over
+// the activations costs as much as the layer itself.
+//
+// Layout: activations are a row-major [M, C] matrix (M = N*H*W for NHWC batch
+// norm, rows x cols for layer norm), 16-byte vectors along C.
+#include "kernels/common.cuh"
+#include "kernels/tips_kernels.h"
+
+namespace tipsk {
+namespace {
+
+// ------------------------------------------------------------------ batch norm
+
+template <typename T, int V>
+struct alignas(sizeof(T) * V) VecT {
+  T v[V];
+};
+
+template <typename T, int V>
+__device__ __forceinline__ void LoadV(const T* p, float (&out)[V]) {
+  VecT<T, V> q = *reinterpret_cast<const VecT<T, V>*>(p);
+#pragma unroll
+  for (int i = 0; i < V; ++i) out[i] = ToFloat<T>(q.v[i]);
+}
+template <typename T, int V>
+__device__ __forceinline__ void StoreV(T* p, const float (&in)[V]) {
+  VecT<T, V> q;
+#pragma unroll
+  for (int i = 0; i < V; ++i) q.v[i] = FromFloat<T>(in[i]);
+  *reinterpret_cast<VecT<T, V>*>(p) = q;
+}
+
+struct BnGeom {
+  int tx, ty;      // block = tx * ty threads; tx vector-columns, ty rows
+  int col_tiles;   // grid.x
+  int partials;    // grid.y of the reduction kernels
+};
+
+BnGeom BnGeometry(int64_t m, int c, int v) {
+  BnGeom g;
+  int vec_cols = c / v;
+  g.tx = 1;
+  while (g.tx * 2 <= vec_cols && g.tx < 32 && vec_cols % (g.tx * 2) == 0) g.tx *= 2;
+  g.ty        = 256 / g.tx;
+  g.col_tiles = vec_cols / g.tx;
+  int64_t want = (static_cast<int64_t>(NumSMs()) * 4 + g.col_tiles - 1) / g.col_tiles;
+  int64_t maxp = (m + g.ty * 4 - 1) / (g.ty * 4);
+  if (want > maxp) want = maxp;
+  if (want < 1) want = 1;
+  if (want > 512) want = 512;
+  g.partials = static_cast<int>(want);
+  return g;
+}
+
+// Partial column sums of a and a*b-like quantities.
+// kBwd = false: s0 = sum x, s1 = sum x^2
+// kBwd = true : s0 = sum dyr, s1 = sum dyr * xhat, with dyr = relu-masked dy
+template <typename T, int V, bool kBwd>
+__global__ void __launch_bounds__(256)
+BnReduceKernel(const T* __restrict__ a, const T* __restrict__ x, const T* __restrict__ y,
+               const float* __restrict__ mean, const float* __restrict__ invstd, float* __restrict__ ws, int64_t m,
+               int c, int relu) {
+  extern __shared__ float smem[];
+  const int tx = threadIdx.x, ty = threadIdx.y;
+  const int TX = blockDim.x, TY = blockDim.y;
+  const int col = (blockIdx.x * TX + tx) * V;
+  float s0[V], s1[V], mu[V], is[V];
+#pragma unroll
+  for (int i = 0; i < V; ++i) s0[i] = s1[i] = 0.f;
+  if (kBwd) {
+#pragma unroll
+    for (int i = 0; i < V; ++i) {
+      mu[i] = mean[col + i];
+      is[i] = invstd[col + i];
+    }
+  }
+  for (int64_t r = static_cast<int64_t>(blockIdx.y) * TY + ty; r < m; r += static_cast<int64_t>(gridDim.y) * TY) {
+    float av[V];
+    LoadV<T, V>(a + r * c + col, av);
+    if (kBwd) {
+      float xv[V];
+      LoadV<T, V>(x + r * c + col, xv);
+      if (relu) {
+        float yv[V];
+        LoadV<T, V>(y + r * c + col, yv);
+#pragma unroll
+        for (int i = 0; i < V; ++i)
+          if (yv[i] <= 0.f) av[i] = 0.f;
+      }
+#pragma unroll
+      for (int i = 0; i < V; ++i) {
+        s0[i] += av[i];
+        s1[i] += av[i] * (xv[i] - mu[i]) * is[i];
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < V; ++i) {
+        s0[i] += av[i];
+        s1[i] += av[i] * av[i];
+      }
+    }
+  }
+  // reduce over ty through shared memory: layout [ty][tx][2V]
+  float* mine = smem + (ty * TX + tx) * 2 * V;
+#pragma unroll
+  for (int i = 0; i < V; ++i) {
+    mine[i]     = s0[i];
+    mine[V + i] = s1[i];
+  }
+  __syncthreads();
+  for (int h = TY / 2; h > 0; h >>= 1) {
+    if (ty < h) {
+      float* other = smem + ((ty + h) * TX + tx) * 2 * V;
+#pragma unroll
+      for (int i = 0; i < 2 * V; ++i) mine[i] += other[i];
+    }
+    __syncthreads();
+  }
+  if (ty == 0) {
+    float* out = ws + static_cast<int64_t>(blockIdx.y) * 2 * c;
+#pragma unroll
+    for (int i = 0; i < V; ++i) {
+      out[col + i]     = mine[i];
+      out[c + col + i] = mine[V + i];
+    }
+  }
+}
+
+// Sums the partial rows of the workspace for this thread's V channels. The
+// threads of a block that share a column (same tx) split the partial rows
+// between them and combine through shared memory ([ty][tx][2V] floats).
+template <int V>
+__device__ __forceinline__ void BlockCombine(const float* __restrict__ ws, int partials, int c, int col, float* smem,
+                                             float (&s0)[V], float (&s1)[V]) {
+  const int tx = threadIdx.x, ty = threadIdx.y;
+  const int TX = blockDim.x, TY = blockDim.y;
+#pragma unroll
+  for (int i = 0; i < V; ++i) s0[i] = s1[i] = 0.f;
+  for (int p = ty; p < partials; p += TY) {
+    const float* row = ws + static_cast<int64_t>(p) * 2 * c;
+#pragma unroll
+    for (int i = 0; i < V; ++i) {
+      s0[i] += row[col + i];
+      s1[i] += row[c + col + i];
+    }
+  }
+  float* mine = smem + (ty * TX + tx) * 2 * V;
+#pragma unroll
+  for (int i = 0; i < V; ++i) {
+    mine[i]     = s0[i];
+    mine[V + i] = s1[i];
+  }
+  __syncthreads();
+  for (int h = TY / 2; h > 0; h >>= 1) {
+    if (ty < h) {
+      float* other = smem + ((ty + h) * TX + tx) * 2 * V;
+#pragma unroll
+      for (int i = 0; i < 2 * V; ++i) mine[i] += other[i];
+    }
+    __syncthreads();
+  }
+  const float* total = smem + tx * 2 * V;
+#pragma unroll
+  for (int i = 0; i < V; ++i) {
+    s0[i] = total[i];
+    s1[i] = total[V + i];
+  }
+}
+
+template <typename T, int V>
+__global__ void __launch_bounds__(256)
+BnApplyKernel(const T* __restrict__ x, const T* __restrict__ residual, T* __restrict__ y,
+              const float* __restrict__ gamma, const float* __restrict__ beta, float* running_mean, float* running_var,
+              float* save_mean, float* save_invstd, const float* __restrict__ ws, int partials, int64_t m, int c,
+              float eps, float momentum, int relu, int training) {
+  const int tx = threadIdx.x, ty = threadIdx.y;
+  const int TX = blockDim.x, TY = blockDim.y;
+  const int col = (blockIdx.x * TX + tx) * V;
+  extern __shared__ float smem[];
+  float scale[V], shift[V], t0[V], t1[V];
+  if (training) BlockCombine<V>(ws, partials, c, col, smem, t0, t1);
+#pragma unroll
+  for (int i = 0; i < V; ++i) {
+    float mean, invstd;
+    if (training) {
+      mean      = t0[i] / static_cast<float>(m);
+      float var = fmaxf(t1[i] / static_cast<float>(m) - mean * mean, 0.f);
+      invstd    = rsqrtf(var + eps);
+      if (blockIdx.y == 0 && ty == 0) {
+        save_mean[col + i]   = mean;
+        save_invstd[col + i] = invstd;
+        if (running_mean) {
+          float unbiased       = m > 1 ? var * static_cast<float>(m) / static_cast<float>(m - 1) : var;
+          running_mean[col + i] = (1.f - momentum) * running_mean[col + i] + momentum * mean;
+          running_var[col + i]  = (1.f - momentum) * running_var[col + i] + momentum * unbiased;
+        }
+      }
+    } else {
+      mean   = running_mean[col + i];
+      invstd = rsqrtf(running_var[col + i] + eps);
+    }
+    scale[i] = gamma[col + i] * invstd;
+    shift[i] = beta[col + i] - mean * scale[i];
+  }
+  for (int64_t r = static_cast<int64_t>(blockIdx.y) * TY + ty; r < m; r += static_cast<int64_t>(gridDim.y) * TY) {
+    float xv[V];
+    LoadV<T, V>(x + r * c + col, xv);
+    if (residual) {
+      float rv[V];
+      LoadV<T, V>(residual + r * c + col, rv);
+#pragma unroll
+      for (int i = 0; i < V; ++i) xv[i] = xv[i] * scale[i] + shift[i] + rv[i];
+    } else {
+#pragma unroll
+      for (int i = 0; i < V; ++i) xv[i] = xv[i] * scale[i] + shift[i];
+    }
+    if (relu) {
+#pragma unroll
+      for (int i = 0; i < V; ++i) xv[i] = fmaxf(xv[i], 0.f);
+    }
+    StoreV<T, V>(y + r * c + col, xv);
+  }
+}
+
+template <typename T, int V>
+__global__ void __launch_bounds__(256)
+BnBwdApplyKernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ y,
+                 const float* __restrict__ gamma, const float* __restrict__ mean, const float* __restrict__ invstd,
+                 T* __restrict__ dx, T* __restrict__ dres, float* dgamma, float* dbeta, const float* __restrict__ ws,
+                 int partials, int64_t m, int c, int relu) {
+  const int tx = threadIdx.x, ty = threadIdx.y;
+  const int TX = blockDim.x, TY = blockDim.y;
+  const int col = (blockIdx.x * TX + tx) * V;
+  extern __shared__ float smem[];
+  float mu[V], is[V], k0[V], k1[V], gs[V], t0[V], t1[V];
+  const float inv_m = 1.f / static_cast<float>(m);
+  BlockCombine<V>(ws, partials, c, col, smem, t0, t1);
+#pragma unroll
+  for (int i = 0; i < V; ++i) {
+    const float s0 = t0[i], s1 = t1[i];
+    if (blockIdx.y == 0 && ty == 0) {
+      dbeta[col + i]  = s0;
+      dgamma[col + i] = s1;
+    }
+    mu[i] = mean[col + i];
+    is[i] = invstd[col + i];
+    gs[i] = gamma[col + i] * is[i];
+    k0[i] = s0 * inv_m;
+    k1[i] = s1 * inv_m;
+  }
+  for (int64_t r = static_cast<int64_t>(blockIdx.y) * TY + ty; r < m; r += static_cast<int64_t>(gridDim.y) * TY) {
+    float dv[V], xv[V];
+    LoadV<T, V>(dy + r * c + col, dv);
+    LoadV<T, V>(x + r * c + col, xv);
+    if (relu) {
+      float yv[V];
+      LoadV<T, V>(y + r * c + col, yv);
+#pragma unroll
+      for (int i = 0; i < V; ++i)
+        if (yv[i] <= 0.f) dv[i] = 0.f;
+    }
+    if (dres) StoreV<T, V>(dres + r * c + col, dv);
+#pragma unroll
+    for (int i = 0; i < V; ++i) dv[i] = gs[i] * (dv[i] - k0[i] - (xv[i] - mu[i]) * is[i] * k1[i]);
+    StoreV<T, V>(dx + r * c + col, dv);
+  }
+}
+
+int BnVec(int dtype, int c) {
+  int v = dtype == kF32 ? 4 : 8;
+  while (v > 1 && c % v != 0) v /= 2;
+  return v;
+}
+
+#define BN_DISPATCH(dtype, c, ...)                                                    \
+  {                                                                                   \
+    const int v_ = BnVec(dtype, c);                                                   \
+    if (dtype == kBF16) {                                                             \
+      using T = __nv_bfloat16;                                                        \
+      if (v_ == 8) { constexpr int V = 8; __VA_ARGS__; }                              \
+      else if (v_ == 4) { constexpr int V = 4; __VA_ARGS__; }                         \
+      else if (v_ == 2) { constexpr int V = 2; __VA_ARGS__; }                         \
+      else { constexpr int V = 1; __VA_ARGS__; }                                      \
+    } else if (dtype == kF16) {                                                       \
+      using T = __half;                                                               \
+      if (v_ == 8) { constexpr int V = 8; __VA_ARGS__; }                              \
+      else if (v_ == 4) { constexpr int V = 4; __VA_ARGS__; }                         \
+      else if (v_ == 2) { constexpr int V = 2; __VA_ARGS__; }                         \
+      else { constexpr int V = 1; __VA_ARGS__; }                                      \
+    } else if (dtype == kF32) {                                                       \
+      using T = float;                                                                \
+      if (v_ == 4) { constexpr int V = 4; __VA_ARGS__; }                              \
+      else if (v_ == 2) { constexpr int V = 2; __VA_ARGS__; }                         \
+      else { constexpr int V = 1; __VA_ARGS__; }                                      \
+    } else {                                                                          \
+      return SetError(-2, "batch norm: unsupported dtype");                           \
+    }                                                                                 \
+  }
+
+}  // namespace
+}  // namespace tipsk
+
+using namespace tipsk;
+
+extern "C" {
+
+int tipsk_bn_partials(int64_t m, int c) {
+  // Upper bound over the vector widths the dispatcher may choose.
+  int best = 1;
+  for (int v = 1; v <= 8; v *= 2)
+    if (c % v == 0) {
+      int p = BnGeometry(m, c, v).partials;
+      if (p > best) best = p;
+    }
+  return best;
+}
+
+int tipsk_bn_fwd_train(const void* x, const void* residual, void* y, const float* gamma, const float* beta,
+                       float* running_mean, float* running_var, float* save_mean, float* save_invstd,
+                       float* workspace, int64_t m, int c, float eps, float momentum, int relu, int dtype,
+                       void* stream) {
+  TIPSK_REQUIRE(m > 0 && c > 0, "batch norm: empty input");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  BN_DISPATCH(dtype, c, {
+    BnGeom g = BnGeometry(m, c, V);
+    dim3 block(g.tx, g.ty), grid(g.col_tiles, g.partials);
+    size_t smem = sizeof(float) * 256 * 2 * V;
+    BnReduceKernel<T, V, false><<<grid, block, smem, s>>>(static_cast<const T*>(x), nullptr, nullptr, nullptr, nullptr,
+                                                          workspace, m, c, 0);
+    BnApplyKernel<T, V><<<grid, block, sizeof(float) * 256 * 2 * V, s>>>(static_cast<const T*>(x), static_cast<const T*>(residual),
+                                               static_cast<T*>(y), gamma, beta, running_mean, running_var, save_mean,
+                                               save_invstd, workspace, g.partials, m, c, eps, momentum, relu, 1);
+  });
+  TIPSK_LAUNCH_CHECK();
+  return 0;
+}
+
+int tipsk_bn_fwd_eval(const void* x, const void* residual, void* y, const float* gamma, const float* beta,
+                      const float* running_mean, const float* running_var, int64_t m, int c, float eps, int relu,
+                      int dtype, void* stream) {
+  TIPSK_REQUIRE(m > 0 && c > 0, "batch norm: empty input");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  BN_DISPATCH(dtype, c, {
+    BnGeom g = BnGeometry(m, c, V);
+    dim3 block(g.tx, g.ty), grid(g.col_tiles, g.partials);
+    BnApplyKernel<T, V><<<grid, block, sizeof(float) * 256 * 2 * V, s>>>(static_cast<const T*>(x), static_cast<const T*>(residual),
+                                               static_cast<T*>(y), gamma, beta, const_cast<float*>(running_mean),
+                                               const_cast<float*>(running_var), nullptr, nullptr, nullptr, 0, m, c,
+                                               eps, 0.f, relu, 0);
+  });
+  TIPSK_LAUNCH_CHECK();
+  return 0;
+}
+
+int tipsk_bn_bwd(const void* dy, const void* x, const void* y, const float* gamma, const float* save_mean,
+                 const float* save_invstd, void* dx, void* dresidual, float* dgamma, float* dbeta, float* workspace,
+                 int64_t m, int c, int relu, int dtype, void* stream) {
+  TIPSK_REQUIRE(m > 0 && c > 0, "batch norm: empty input");
+  TIPSK_REQUIRE(!relu || y, "batch norm backward with ReLU needs the forward output");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  BN_DISPATCH(dtype, c, {
+    BnGeom g = BnGeometry(m, c, V);
+    dim3 block(g.tx, g.ty), grid(g.col_tiles, g.partials);
+    size_t smem = sizeof(float) * 256 * 2 * V;
+    BnReduceKernel<T, V, true><<<grid, block, smem, s>>>(static_cast<const T*>(dy), static_cast<const T*>(x),
+                                                         static_cast<const T*>(y), save_mean, save_invstd, workspace, m,
+                                                         c, relu);
+    BnBwdApplyKernel<T, V><<<grid, block, smem, s>>>(static_cast<const T*>(dy), static_cast<const T*>(x),
+                                                  static_cast<const T*>(y), gamma, save_mean, save_invstd,
+                                                  static_cast<T*>(dx), static_cast<T*>(dresidual), dgamma, dbeta,
+                                                  workspace, g.partials, m, c, relu);
+  });
+  TIPSK_LAUNCH_CHECK();
+  return 0;
+}
+
+}  // extern "C"

@@ -1,0 +1,125 @@
+/* extern "C" launchers of the sm_100a kernel library (libtips_kernels.so).
+ *
+ * Conventions: pointers are device pointers unless a parameter is named host_*;
+ * dtype arguments use the tips Datatype codes (0 fp32, 1 fp64, 2 int32, 3 int64,
+ * 4 int8, 5 uint8, 6 bf16, 7 fp16); `stream` is a cudaStream_t; the return value
+ * is 0 on success and negative on failure, with the message available from
+ * tipsk_last_error() on the calling thread.  None of the reference's code has a
+ * GPU path (its AllreduceGpu is declared and never defined,
+ * tips/core/collective/utils.h:136-137), so nothing here has a counterpart there.
+ */
+#pragma once
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+const char* tipsk_last_error(void);
+
+/* ---- optimizers on flat slabs (elementwise.cu) ---- */
+int tipsk_sgd_momentum_flat(float* p32, void* p16, int p16_dtype, const void* grad, int grad_dtype, float* momentum_buf,
+                            int64_t n, float lr, float momentum, float dampening, float weight_decay, int nesterov,
+                            float grad_scale, int first_step, void* stream);
+int tipsk_adam_flat(float* p32, void* p16, int p16_dtype, const void* grad, int grad_dtype, float* exp_avg,
+                    float* exp_avg_sq, int64_t n, float lr, float beta1, float beta2, float eps, float weight_decay,
+                    int64_t step, float grad_scale, int decoupled, void* stream);
+/* host arrays of device pointers / element offsets / element counts */
+int tipsk_pack(const void* const* host_srcs, const int64_t* host_offsets, const int64_t* host_numels, int ntensors,
+               int src_dtype, void* flat, int flat_dtype, float scale, int accumulate, void* stream);
+int tipsk_unpack(const void* flat, int flat_dtype, void* const* host_dsts, const int64_t* host_offsets,
+                 const int64_t* host_numels, int ntensors, int dst_dtype, float scale, void* stream);
+int tipsk_scale_cast(const void* src, int src_dtype, void* dst, int dst_dtype, int64_t n, float scale, void* stream);
+
+/* ---- normalisation (norm.cu) ---- */
+/* NHWC batch norm on [M, C] rows (M = N*H*W). Training forward: batch statistics
+ * (written to save_mean / save_invstd, running stats updated when non-null), then
+ * y = relu?(gamma * (x - mean) * invstd + beta + residual?). `workspace` holds
+ * 2*C*partials floats (partials = tipsk_bn_partials(M, C)). */
+int tipsk_bn_partials(int64_t m, int c);
+int tipsk_bn_fwd_train(const void* x, const void* residual, void* y, const float* gamma, const float* beta,
+                       float* running_mean, float* running_var, float* save_mean, float* save_invstd,
+                       float* workspace, int64_t m, int c, float eps, float momentum, int relu, int dtype, void* stream);
+int tipsk_bn_fwd_eval(const void* x, const void* residual, void* y, const float* gamma, const float* beta,
+                      const float* running_mean, const float* running_var, int64_t m, int c, float eps, int relu,
+                      int dtype, void* stream);
+/* Backward of the fused op; y is the forward output (needed for the ReLU mask).
+ * dresidual may be null. dgamma/dbeta are fp32 [C]. */
+int tipsk_bn_bwd(const void* dy, const void* x, const void* y, const float* gamma, const float* save_mean,
+                 const float* save_invstd, void* dx, void* dresidual, float* dgamma, float* dbeta, float* workspace,
+                 int64_t m, int c, int relu, int dtype, void* stream);
+/* Layer norm over the last dimension of [rows, cols]. */
+int tipsk_ln_fwd(const void* x, const void* gamma, const void* beta, void* y, float* mean, float* rstd, int64_t rows,
+                 int cols, float eps, int dtype, void* stream);
+int tipsk_ln_bwd(const void* dy, const void* x, const void* gamma, const float* mean, const float* rstd, void* dx,
+                 float* dgamma_partial, float* dbeta_partial, int partial_rows, int64_t rows, int cols, int dtype,
+                 void* stream);
+int tipsk_ln_bwd_partials(int64_t rows, int cols);
+int tipsk_ln_reduce_partials(const float* dgamma_partial, const float* dbeta_partial, int partial_rows, int cols,
+                             void* dgamma, void* dbeta, int dtype, void* stream);
+
+/* ---- pointwise epilogues and losses (epilogue.cu) ---- */
+/* act: 0 none, 1 relu, 2 gelu (erf). y = act(x + bias[col]) on [rows, cols]. */
+int tipsk_bias_act_fwd(const void* x, const void* bias, void* y, int64_t rows, int cols, int act, int dtype,
+                       void* stream);
+/* dx = dy * act'(x + bias); dbias (fp32 [cols]) = column sums of dx, when non-null. */
+int tipsk_bias_act_bwd(const void* dy, const void* x, const void* bias, void* dx, float* dbias, int64_t rows, int cols,
+                       int act, int dtype, void* stream);
+/* Binary cross entropy with logits: loss_sum (fp32 scalar, accumulated) and dlogits = (sigmoid(z) - t) * scale. */
+int tipsk_sigmoid_bce(const void* logits, const float* targets, float* loss_sum, void* dlogits, int64_t n,
+                      float grad_scale, int dtype, void* stream);
+/* Softmax cross entropy over [rows, cols] with int64 labels (ignore_index skipped):
+ * loss_sum / count accumulated into fp32 scalars, dlogits = (softmax - onehot) * scale. */
+int tipsk_softmax_xent(const void* logits, const int64_t* labels, float* loss_sum, float* count, void* dlogits,
+                       int64_t rows, int cols, int64_t ignore_index, float grad_scale, int dtype, void* stream);
+
+/* ---- NVLink collectives (comm.cu, comm_executor.cu) ----
+ * A "window" is a buffer of identical size on every rank, mapped into every process
+ * (peer_windows[r] = address of rank r's window here; multicast_window = NVLS multicast
+ * mapping or NULL).  Layout: [64 KiB signal flags][staging area][caller-managed space].
+ * With `emulated` non-zero all windows live on the current device and one launch runs
+ * every rank (cooperative launch); used to test the multi-rank algorithms on one GPU. */
+int tipsk_comm_init(int rank, int nranks, void* const* peer_windows, void* multicast_window, uint64_t window_bytes,
+                    uint64_t staging_bytes, int wait_budget_ms, int blocks, uint64_t one_shot_bytes, int use_multimem,
+                    int emulated);
+int tipsk_comm_shutdown(void);
+int tipsk_comm_ready(void);
+uint64_t tipsk_comm_staging_offset(void);
+uint64_t tipsk_comm_launches(void);
+void* tipsk_comm_stream(int channel);
+int tipsk_comm_uses_multimem(void);
+int tipsk_comm_set_budget_ms(int ms);
+int tipsk_comm_status(int slot, int32_t* out7, int clear);
+int tipsk_comm_reset(void);
+int tipsk_allreduce(const void* const* host_srcs, void* const* host_dsts, int64_t win_off, uint64_t nbytes, int dtype,
+                    int op, float prescale, float postscale, int channel, void* stream);
+int tipsk_allgatherv(const void* const* host_srcs, void* const* host_dsts, const uint64_t* bytes_per_rank, int channel,
+                     void* stream);
+int tipsk_broadcast(const void* const* host_srcs, void* const* host_dsts, uint64_t nbytes, int root, int channel,
+                    void* stream);
+int tipsk_comm_wait_never(int channel, void* stream);
+void* tipsk_event_create(void);
+void tipsk_event_recycle(void* ev);
+int tipsk_event_record(void* ev, void* stream);
+int tipsk_stream_wait_event(void* stream, void* ev);
+int tipsk_stream_synchronize(void* stream);
+int tipsk_executor_configure(int device, void* my_window, uint64_t window_bytes);
+void* tipsk_device_executor_ptr(void);
+
+/* ---- parameter server (ps.cu) ---- */
+int tipsk_comm_fence(int channel, void* stream);
+int tipsk_table_init(float* shard, int64_t rows_local, int dim, int field, int rank, int nranks, int64_t rows_global,
+                     uint64_t seed, float scale, void* stream);
+int tipsk_ps_configure(void* const* host_slabs, void* const* host_accs, int nranks, const uint64_t* host_field_off,
+                       const uint64_t* host_state_off, const int64_t* host_rows_per_shard, int nfields, int dim,
+                       uint64_t slots);
+int tipsk_ps_status(int32_t* host_error, uint64_t* host_touched);
+int tipsk_ps_pull(const int64_t* const* host_ids, void* const* host_outs, int64_t batch, int64_t out_ld,
+                  int64_t out_col0, int out_dtype, int fence, void* stream);
+int tipsk_ps_push(const int64_t* const* host_ids, const void* const* host_grads, int64_t batch, int64_t grad_ld,
+                  int64_t grad_col0, int grad_dtype, float grad_scale, int rule, float lr, float eps, void* stream);
+
+#ifdef __cplusplus
+}
+#endif

@@ -1,0 +1,71 @@
+"""ctypes prototypes of the kernel library (csrc/kernels/tips_kernels.h)."""
+from __future__ import annotations
+
+from ctypes import POINTER, c_char_p, c_float, c_int, c_int32, c_int64, c_uint64, c_void_p
+
+P = c_void_p
+I = c_int
+L = c_int64
+U = c_uint64
+F = c_float
+PP = POINTER(c_void_p)
+
+_PROTOS = {
+    "tipsk_last_error": (c_char_p, []),
+    "tipsk_sgd_momentum_flat": (I, [P, P, I, P, I, P, L, F, F, F, F, I, F, I, P]),
+    "tipsk_adam_flat": (I, [P, P, I, P, I, P, P, L, F, F, F, F, F, L, F, I, P]),
+    "tipsk_pack": (I, [PP, POINTER(L), POINTER(L), I, I, P, I, F, I, P]),
+    "tipsk_unpack": (I, [P, I, PP, POINTER(L), POINTER(L), I, I, F, P]),
+    "tipsk_scale_cast": (I, [P, I, P, I, L, F, P]),
+    "tipsk_bn_partials": (I, [L, I]),
+    "tipsk_bn_fwd_train": (I, [P, P, P, P, P, P, P, P, P, P, L, I, F, F, I, I, P]),
+    "tipsk_bn_fwd_eval": (I, [P, P, P, P, P, P, P, L, I, F, I, I, P]),
+    "tipsk_bn_bwd": (I, [P, P, P, P, P, P, P, P, P, P, P, L, I, I, I, P]),
+    "tipsk_ln_fwd": (I, [P, P, P, P, P, P, L, I, F, I, P]),
+    "tipsk_ln_bwd": (I, [P, P, P, P, P, P, P, P, I, L, I, I, P]),
+    "tipsk_ln_bwd_partials": (I, [L, I]),
+    "tipsk_ln_reduce_partials": (I, [P, P, I, I, P, P, I, P]),
+    "tipsk_bias_act_fwd": (I, [P, P, P, L, I, I, I, P]),
+    "tipsk_bias_act_bwd": (I, [P, P, P, P, P, L, I, I, I, P]),
+    "tipsk_sigmoid_bce": (I, [P, P, P, P, L, F, I, P]),
+    "tipsk_softmax_xent": (I, [P, P, P, P, P, L, I, L, F, I, P]),
+    "tipsk_comm_init": (I, [I, I, PP, P, U, U, I, I, U, I, I]),
+    "tipsk_comm_shutdown": (I, []),
+    "tipsk_comm_ready": (I, []),
+    "tipsk_comm_staging_offset": (U, []),
+    "tipsk_comm_launches": (U, []),
+    "tipsk_comm_stream": (P, [I]),
+    "tipsk_comm_uses_multimem": (I, []),
+    "tipsk_comm_set_budget_ms": (I, [I]),
+    "tipsk_comm_status": (I, [I, POINTER(c_int32), I]),
+    "tipsk_comm_reset": (I, []),
+    "tipsk_allreduce": (I, [PP, PP, L, U, I, I, F, F, I, P]),
+    "tipsk_allgatherv": (I, [PP, PP, POINTER(U), I, P]),
+    "tipsk_broadcast": (I, [PP, PP, U, I, I, P]),
+    "tipsk_comm_wait_never": (I, [I, P]),
+    "tipsk_event_create": (P, []),
+    "tipsk_event_recycle": (None, [P]),
+    "tipsk_event_record": (I, [P, P]),
+    "tipsk_stream_wait_event": (I, [P, P]),
+    "tipsk_stream_synchronize": (I, [P]),
+    "tipsk_executor_configure": (I, [I, P, U]),
+    "tipsk_device_executor_ptr": (P, []),
+    "tipsk_comm_fence": (I, [I, P]),
+    "tipsk_table_init": (I, [P, L, I, I, I, I, L, U, F, P]),
+    "tipsk_ps_configure": (I, [PP, PP, I, POINTER(U), POINTER(U), POINTER(L), I, I, U]),
+    "tipsk_ps_status": (I, [POINTER(c_int32), POINTER(U)]),
+    "tipsk_ps_pull": (I, [PP, PP, L, L, L, I, I, P]),
+    "tipsk_ps_push": (I, [PP, PP, L, L, L, I, F, I, F, F, P]),
+    "tipsk_gemm_bf16": (I, [P, P, P, P, P, I, I, I, I, I, I, I, P]),
+    "tipsk_gemm_supported": (I, [I, I, I, I, I]),
+}
+
+
+def declare(lib) -> None:
+    for name, (res, args) in _PROTOS.items():
+        try:
+            fn = getattr(lib, name)
+        except AttributeError:
+            continue
+        fn.restype = res
+        fn.argtypes = args

@@ -1,0 +1,196 @@
+"""Fused optimizers on flat parameter slabs: SGD with momentum and Adam / AdamW.
+
+Parameters of one (param group, dtype) partition are flattened into buckets;
+each bucket owns a flat fp32 master copy (the parameters themselves when they
+are fp32), flat optimizer state and a flat gradient buffer.  ``step()`` is one
+kernel launch per bucket (csrc/kernels/elementwise.cu): it reads the gradient
+once and writes master weights, state and — for bf16 / fp16 models — the
+low-precision parameters in the same pass.
+
+The reference has no optimizer kernels (TensorFlow applies the gradients); its
+server-side SGD rule lives in the parameter server
+(tips/core/ps/sparse_access_method.h:41-61).  These optimizers are what
+``DistributedOptimizer`` drives on the bucketed fast path.
+"""
+from __future__ import annotations
+
+from typing import List
+
+import torch
+
+from ..parallel.buckets import Bucket, build_buckets
+from . import base
+
+
+class _FlatBucketState:
+    def __init__(self, bucket: Bucket, group: dict):
+        self.bucket = bucket
+        self.group = group
+        dev = bucket.device
+        pdtype = bucket.params[0].dtype
+        self.low = pdtype in (torch.bfloat16, torch.float16)
+        flat = torch.zeros(bucket.numel, dtype=pdtype, device=dev)
+        for i, p in enumerate(bucket.params):
+            v = flat[bucket.offsets[i]:bucket.offsets[i] + p.numel()].view(p.shape)
+            v.copy_(p.data)
+            p.data = v
+        self.flat_param = flat
+        self.master = flat.float() if self.low else flat
+        self.state = {}
+        self.steps = 0
+        self.grads_packed = False  # set by DistributedOptimizer when the bucket already holds reduced grads
+
+
+class _FusedOptimizer(torch.optim.Optimizer):
+    def __init__(self, params, defaults, bucket_bytes=None, wire_dtype="auto"):
+        super().__init__(params, defaults)
+        self._bucket_bytes = bucket_bytes
+        self._wire_dtype = wire_dtype
+        self._flat: List[_FlatBucketState] = []
+        self._built = False
+
+    # -- bucket construction ---------------------------------------------------
+    def build(self, device_state=None):
+        """Flatten the parameters (idempotent). Called lazily by step(), or by
+        DistributedOptimizer with the device state so gradient buffers are symmetric."""
+        if self._built:
+            return self._flat
+        index = 0
+        for group in self.param_groups:
+            by_dtype = {}
+            for p in group["params"]:
+                if p.requires_grad:
+                    by_dtype.setdefault((p.dtype, p.device), []).append(p)
+            for (_, _), plist in by_dtype.items():
+                buckets = build_buckets(plist, self._bucket_bytes, self._wire_dtype, device_state)
+                for b in buckets:
+                    b.index = index
+                    b.name = f"tips.bucket.{index}"
+                    index += 1
+                    self._flat.append(_FlatBucketState(b, group))
+        self._built = True
+        return self._flat
+
+    @property
+    def buckets(self) -> List[Bucket]:
+        return [f.bucket for f in self.build()]
+
+    def zero_grad(self, set_to_none: bool = True):
+        for group in self.param_groups:
+            for p in group["params"]:
+                p.grad = None
+
+    @torch.no_grad()
+    def step(self, closure=None, grad_scale: float = 1.0):
+        loss = None
+        if closure is not None:
+            with torch.enable_grad():
+                loss = closure()
+        for fs in self.build():
+            b = fs.bucket
+            if not fs.grads_packed:
+                if all(p.grad is None for p in b.params):
+                    continue
+                b.pack()
+            fs.grads_packed = False
+            fs.steps += 1
+            self._update(fs, grad_scale)
+            for p in b.params:
+                p.grad = None
+        return loss
+
+    def _update(self, fs, grad_scale):
+        raise NotImplementedError
+
+    # state_dict: flat state is exposed per bucket
+    def flat_state(self):
+        return [{"steps": fs.steps, **{k: v for k, v in fs.state.items()}} for fs in self.build()]
+
+    def load_flat_state(self, states):
+        for fs, s in zip(self.build(), states):
+            fs.steps = int(s.get("steps", 0))
+            for k, v in s.items():
+                if k == "steps":
+                    continue
+                fs.state[k] = v.to(fs.master.device).clone()
+
+
+class FusedSGD(_FusedOptimizer):
+    """SGD with momentum, dampening, Nesterov and (coupled) weight decay; torch.optim.SGD semantics."""
+
+    def __init__(self, params, lr=0.01, momentum=0.0, dampening=0.0, weight_decay=0.0, nesterov=False,
+                 bucket_bytes=None, wire_dtype="auto"):
+        if nesterov and (momentum <= 0 or dampening != 0):
+            raise ValueError("Nesterov momentum requires a momentum and zero dampening")
+        defaults = dict(lr=lr, momentum=momentum, dampening=dampening, weight_decay=weight_decay, nesterov=nesterov)
+        super().__init__(params, defaults, bucket_bytes, wire_dtype)
+
+    def _update(self, fs, grad_scale):
+        g, b = fs.group, fs.bucket
+        mom = float(g["momentum"])
+        first = 0
+        if mom != 0.0 and "momentum_buffer" not in fs.state:
+            fs.state["momentum_buffer"] = torch.zeros_like(fs.master)
+            first = 1
+        buf = fs.state.get("momentum_buffer")
+        if fs.master.is_cuda:
+            base.check(base.K().tipsk_sgd_momentum_flat(
+                fs.master.data_ptr(), fs.flat_param.data_ptr() if fs.low else None,
+                base.code(fs.flat_param) if fs.low else 6, b.grad.data_ptr(), base.code(b.grad), base.ptr(buf),
+                b.numel, float(g["lr"]), mom, float(g["dampening"]), float(g["weight_decay"]), int(g["nesterov"]),
+                float(grad_scale), first, base.stream()), "sgd_momentum_flat")
+        else:
+            grad = b.grad.float() * grad_scale + float(g["weight_decay"]) * fs.master
+            if mom != 0.0:
+                if first:
+                    buf.copy_(grad)
+                else:
+                    buf.mul_(mom).add_(grad, alpha=1.0 - float(g["dampening"]))
+                grad = grad + mom * buf if g["nesterov"] else buf
+            fs.master.add_(grad, alpha=-float(g["lr"]))
+            if fs.low:
+                fs.flat_param.copy_(fs.master)
+
+
+class FusedAdam(_FusedOptimizer):
+    """Adam; with ``decoupled_weight_decay`` (default) it is AdamW."""
+
+    def __init__(self, params, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.01,
+                 decoupled_weight_decay=True, bucket_bytes=None, wire_dtype="auto"):
+        defaults = dict(lr=lr, betas=betas, eps=eps, weight_decay=weight_decay,
+                        decoupled_weight_decay=decoupled_weight_decay)
+        super().__init__(params, defaults, bucket_bytes, wire_dtype)
+
+    def _update(self, fs, grad_scale):
+        g, b = fs.group, fs.bucket
+        if "exp_avg" not in fs.state:
+            fs.state["exp_avg"] = torch.zeros_like(fs.master)
+            fs.state["exp_avg_sq"] = torch.zeros_like(fs.master)
+        m, v = fs.state["exp_avg"], fs.state["exp_avg_sq"]
+        b1, b2 = g["betas"]
+        if fs.master.is_cuda:
+            base.check(base.K().tipsk_adam_flat(
+                fs.master.data_ptr(), fs.flat_param.data_ptr() if fs.low else None,
+                base.code(fs.flat_param) if fs.low else 6, b.grad.data_ptr(), base.code(b.grad), m.data_ptr(),
+                v.data_ptr(), b.numel, float(g["lr"]), float(b1), float(b2), float(g["eps"]),
+                float(g["weight_decay"]), fs.steps, float(grad_scale), int(g["decoupled_weight_decay"]),
+                base.stream()), "adam_flat")
+        else:
+            grad = b.grad.float() * grad_scale
+            if not g["decoupled_weight_decay"]:
+                grad = grad + float(g["weight_decay"]) * fs.master
+            m.mul_(b1).add_(grad, alpha=1 - b1)
+            v.mul_(b2).addcmul_(grad, grad, value=1 - b2)
+            bias1 = 1 - b1 ** fs.steps
+            bias2 = 1 - b2 ** fs.steps
+            if g["decoupled_weight_decay"]:
+                fs.master.mul_(1 - float(g["lr"]) * float(g["weight_decay"]))
+            fs.master.addcdiv_(m / bias1, (v / bias2).sqrt_().add_(float(g["eps"])), value=-float(g["lr"]))
+            if fs.low:
+                fs.flat_param.copy_(fs.master)
+
+
+class FusedAdamW(FusedAdam):
+    def __init__(self, params, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.01, bucket_bytes=None,
+                 wire_dtype="auto"):
+        super().__init__(params, lr, betas, eps, weight_decay, True, bucket_bytes, wire_dtype)

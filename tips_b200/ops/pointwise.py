@@ -1,0 +1,110 @@
+"""Pointwise epilogues and fused losses (csrc/kernels/epilogue.cu):
+bias + activation, binary cross-entropy with logits, softmax cross-entropy.
+CPU tensors take a plain PyTorch path so that host-only tests can run."""
+from __future__ import annotations
+
+import torch
+import torch.nn.functional as F
+
+from . import base
+
+_ACT = {None: 0, "none": 0, "relu": 1, "gelu": 2}
+
+
+class _BiasActFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, bias, act):
+        cols = x.shape[-1]
+        xc = x.contiguous()
+        rows = xc.numel() // cols
+        y = torch.empty_like(xc)
+        b = None if bias is None else bias.to(xc.dtype).contiguous()
+        base.check(base.K().tipsk_bias_act_fwd(xc.data_ptr(), base.ptr(b), y.data_ptr(), rows, cols, act,
+                                               base.code(xc), base.stream()), "bias_act_fwd")
+        ctx.save_for_backward(xc, b)
+        ctx.act = act
+        ctx.bias_dtype = None if bias is None else bias.dtype
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, b = ctx.saved_tensors
+        cols = x.shape[-1]
+        rows = x.numel() // cols
+        dyc = dy.contiguous()
+        need_dx = ctx.act != 0
+        dx = torch.empty_like(x) if need_dx else dyc
+        dbias = torch.empty(cols, dtype=torch.float32, device=x.device) if b is not None else None
+        base.check(base.K().tipsk_bias_act_bwd(dyc.data_ptr(), x.data_ptr(), base.ptr(b),
+                                               dx.data_ptr() if need_dx else None, base.ptr(dbias), rows, cols,
+                                               ctx.act, base.code(x), base.stream()), "bias_act_bwd")
+        return dx, (None if dbias is None else dbias.to(ctx.bias_dtype)), None
+
+
+def bias_act(x, bias=None, act="relu"):
+    """act(x + bias) with act in {None, "relu", "gelu"}; bias broadcasts over the last dimension."""
+    a = _ACT[act]
+    if x.is_cuda:
+        return _BiasActFn.apply(x, bias, a)
+    y = x if bias is None else x + bias
+    if a == 1:
+        y = F.relu(y)
+    elif a == 2:
+        y = F.gelu(y)
+    return y
+
+
+class _SigmoidBceFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, logits, targets, reduction_scale):
+        z = logits.contiguous()
+        t = targets.to(torch.float32).contiguous()
+        n = z.numel()
+        loss = torch.zeros((), dtype=torch.float32, device=z.device)
+        dz = torch.empty_like(z)
+        base.check(base.K().tipsk_sigmoid_bce(z.data_ptr(), t.data_ptr(), loss.data_ptr(), dz.data_ptr(), n,
+                                              reduction_scale, base.code(z), base.stream()), "sigmoid_bce")
+        ctx.save_for_backward(dz)
+        return loss * reduction_scale
+
+    @staticmethod
+    def backward(ctx, dloss):
+        (dz,) = ctx.saved_tensors
+        return dz * dloss.to(dz.dtype), None, None
+
+
+def sigmoid_bce_loss(logits, targets, reduction="mean"):
+    """Binary cross-entropy with logits; the gradient is produced in the same pass as the loss."""
+    scale = 1.0 / logits.numel() if reduction == "mean" else 1.0
+    if logits.is_cuda:
+        return _SigmoidBceFn.apply(logits, targets, scale)
+    return F.binary_cross_entropy_with_logits(logits.float(), targets.float(), reduction=reduction)
+
+
+class _SoftmaxXentFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, logits, labels, ignore_index):
+        cols = logits.shape[-1]
+        z = logits.contiguous()
+        rows = z.numel() // cols
+        lab = labels.contiguous().view(-1)
+        acc = torch.zeros(2, dtype=torch.float32, device=z.device)
+        dz = torch.empty_like(z)
+        base.check(base.K().tipsk_softmax_xent(z.data_ptr(), lab.data_ptr(), acc.data_ptr(),
+                                               acc.data_ptr() + 4, dz.data_ptr(), rows, cols, ignore_index, 1.0,
+                                               base.code(z), base.stream()), "softmax_xent")
+        inv = 1.0 / torch.clamp(acc[1], min=1.0)
+        ctx.save_for_backward(dz, inv)
+        return acc[0] * inv
+
+    @staticmethod
+    def backward(ctx, dloss):
+        dz, inv = ctx.saved_tensors
+        return dz * (dloss * inv).to(dz.dtype), None, None
+
+
+def softmax_cross_entropy(logits, labels, ignore_index=-100):
+    """Mean softmax cross-entropy over the rows whose label is not `ignore_index`."""
+    if logits.is_cuda:
+        return _SoftmaxXentFn.apply(logits, labels, ignore_index)
+    return F.cross_entropy(logits.float().view(-1, logits.shape[-1]), labels.view(-1), ignore_index=ignore_index)

@@ -1,0 +1,92 @@
+"""ResNet-50 v1.5 for channels-last bf16 training.
+
+The reference's evaluated workload is a TensorFlow ResNet-50 trained through its
+collective mode (README.md:12); the model itself is not part of the reference.
+Here the normalisation layers are the fused sm_100a kernels (BN + residual +
+ReLU in one pass, forward and backward), the loss is the fused softmax
+cross-entropy, and the convolutions are library convolutions.
+"""
+from __future__ import annotations
+
+import torch
+import torch.nn as nn
+
+from ..ops.norm import BatchNorm2d
+from ..ops.pointwise import softmax_cross_entropy
+
+
+def _conv(cin, cout, k, stride=1, padding=0):
+    return nn.Conv2d(cin, cout, k, stride=stride, padding=padding, bias=False)
+
+
+class Bottleneck(nn.Module):
+    expansion = 4
+
+    def __init__(self, cin, width, stride=1, downsample=False):
+        super().__init__()
+        cout = width * self.expansion
+        self.conv1 = _conv(cin, width, 1)
+        self.bn1 = BatchNorm2d(width, relu=True)
+        self.conv2 = _conv(width, width, 3, stride=stride, padding=1)  # v1.5: the stride sits on the 3x3
+        self.bn2 = BatchNorm2d(width, relu=True)
+        self.conv3 = _conv(width, cout, 1)
+        self.bn3 = BatchNorm2d(cout, relu=True)  # ReLU after the residual add, fused
+        nn.init.zeros_(self.bn3.weight)
+        self.down = None
+        if downsample:
+            self.down = nn.Sequential()
+            self.down.add_module("conv", _conv(cin, cout, 1, stride=stride))
+            self.down.add_module("bn", BatchNorm2d(cout, relu=False))
+
+    def forward(self, x):
+        identity = x if self.down is None else self.down(x)
+        out = self.bn1(self.conv1(x))
+        out = self.bn2(self.conv2(out))
+        return self.bn3(self.conv3(out), residual=identity)
+
+
+class ResNet50(nn.Module):
+    def __init__(self, num_classes=1000, layers=(3, 4, 6, 3), width=64):
+        super().__init__()
+        self.conv1 = _conv(3, width, 7, stride=2, padding=3)
+        self.bn1 = BatchNorm2d(width, relu=True)
+        self.maxpool = nn.MaxPool2d(3, stride=2, padding=1)
+        blocks = []
+        cin = width
+        for stage, n in enumerate(layers):
+            w = width * (2 ** stage)
+            for i in range(n):
+                stride = 2 if (i == 0 and stage > 0) else 1
+                blocks.append(Bottleneck(cin, w, stride, downsample=(i == 0)))
+                cin = w * Bottleneck.expansion
+        self.blocks = nn.Sequential(*blocks)
+        self.avgpool = nn.AdaptiveAvgPool2d(1)
+        self.fc = nn.Linear(cin, num_classes)
+        for m in self.modules():
+            if isinstance(m, nn.Conv2d):
+                nn.init.kaiming_normal_(m.weight, mode="fan_out", nonlinearity="relu")
+
+    def forward(self, x):
+        x = self.maxpool(self.bn1(self.conv1(x)))
+        x = self.blocks(x)
+        x = torch.flatten(self.avgpool(x), 1)
+        return self.fc(x)
+
+    def loss(self, images, labels):
+        return softmax_cross_entropy(self.forward(images), labels)
+
+
+def resnet50(num_classes=1000, dtype=torch.bfloat16, device="cuda"):
+    m = ResNet50(num_classes)
+    m = m.to(device=device, dtype=dtype)
+    if torch.device(device).type == "cuda":
+        m = m.to(memory_format=torch.channels_last)
+    return m
+
+
+def tiny_resnet(num_classes=10, dtype=torch.bfloat16, device="cuda"):
+    """Same block structure with one block per stage and a quarter of the width; for smoke tests."""
+    m = ResNet50(num_classes, layers=(1, 1, 1, 1), width=16).to(device=device, dtype=dtype)
+    if torch.device(device).type == "cuda":
+        m = m.to(memory_format=torch.channels_last)
+    return m

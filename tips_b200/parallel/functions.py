@@ -1,0 +1,141 @@
+"""Parameter / optimizer-state broadcast and collectives on Python objects.
+
+API parity with the reference's tips/tensorflow/functions.py: ``broadcast_variables``
+(functions.py:14-46; here ``broadcast_parameters``), ``broadcast_object`` /
+``broadcast_object_fn`` (cloudpickle -> uint8 tensor, size first then payload,
+functions.py:49-124) and ``allgather_object`` (sizes allgather + payload
+allgatherv, sliced by prefix sums, functions.py:127-168); plus
+``broadcast_optimizer_state`` which the reference covers by broadcasting
+``optimizer.variables()`` in its Keras callback (_keras/callbacks.py:30-45).
+"""
+from __future__ import annotations
+
+import io
+import pickle
+from typing import Any, Iterable
+
+import torch
+
+from . import collectives as C
+
+try:  # cloudpickle serialises lambdas and local classes too
+    import cloudpickle as _pickle
+except Exception:  # pragma: no cover
+    _pickle = pickle
+
+
+def broadcast_parameters(params, root_rank: int = 0, prefix: str = "tips.bcast") -> None:
+    """Broadcast parameters (a state_dict, a list of (name, tensor) or an iterable of tensors) in place."""
+    if isinstance(params, dict):
+        items = sorted(params.items())
+    else:
+        items = list(params)
+        if items and not isinstance(items[0], tuple):
+            items = [(str(i), t) for i, t in enumerate(items)]
+    handles = []
+    for name, t in items:
+        if not isinstance(t, torch.Tensor):
+            continue
+        handles.append(C.broadcast_async_(t.data if isinstance(t, torch.nn.Parameter) else t, root_rank,
+                                          name=f"{prefix}.{name}"))
+    for h in handles:
+        C.synchronize(h)
+
+
+broadcast_variables = broadcast_parameters
+
+
+def broadcast_object(obj: Any = None, root_rank: int = 0, name: str | None = None) -> Any:
+    """Return root_rank's `obj` on every rank."""
+    name = name or "tips.bcast_object"
+    if C._size() == 1:
+        return obj
+    if C._rank() == root_rank:
+        buf = io.BytesIO()
+        _pickle.dump(obj, buf)
+        payload = torch.frombuffer(bytearray(buf.getvalue()), dtype=torch.uint8)
+        size = torch.tensor([payload.numel()], dtype=torch.int64)
+    else:
+        payload = None
+        size = torch.zeros(1, dtype=torch.int64)
+    size = C.broadcast(size, root_rank, name=name + ".size")
+    if payload is None:
+        payload = torch.empty(int(size.item()), dtype=torch.uint8)
+    payload = C.broadcast(payload, root_rank, name=name + ".data")
+    return pickle.loads(payload.numpy().tobytes())
+
+
+def broadcast_object_fn(root_rank: int = 0, name: str | None = None):
+    def fn(obj=None):
+        return broadcast_object(obj, root_rank, name)
+    return fn
+
+
+def allgather_object(obj: Any, name: str | None = None) -> list:
+    """Return the list of every rank's `obj`, in rank order."""
+    name = name or "tips.allgather_object"
+    buf = io.BytesIO()
+    _pickle.dump(obj, buf)
+    payload = torch.frombuffer(bytearray(buf.getvalue()), dtype=torch.uint8)
+    if C._size() == 1:
+        return [pickle.loads(payload.numpy().tobytes())]
+    sizes = C.allgather(torch.tensor([payload.numel()], dtype=torch.int64), name=name + ".size")
+    gathered = C.allgather(payload, name=name + ".data")
+    out, off = [], 0
+    for s in sizes.tolist():
+        out.append(pickle.loads(gathered[off:off + s].numpy().tobytes()))
+        off += s
+    return out
+
+
+def broadcast_optimizer_state(optimizer: torch.optim.Optimizer, root_rank: int = 0) -> None:
+    """Make every rank's optimizer state equal to root_rank's (tensors in place, scalars via objects)."""
+    from ..ops.optim import _FusedOptimizer
+    if isinstance(optimizer, _FusedOptimizer):
+        flat = optimizer.build()
+        meta = broadcast_object([(fs.steps, sorted(fs.state.keys())) for fs in flat] if C._rank() == root_rank else None,
+                                root_rank, name="tips.bcast_opt.meta")
+        for i, (fs, (steps, keys)) in enumerate(zip(flat, meta)):
+            fs.steps = steps
+            for k in keys:
+                if k not in fs.state:
+                    fs.state[k] = torch.zeros_like(fs.master)
+                C.broadcast_(fs.state[k], root_rank, name=f"tips.bcast_opt.{i}.{k}")
+            C.broadcast_(fs.master, root_rank, name=f"tips.bcast_opt.{i}.master")
+            if fs.low:
+                fs.flat_param.copy_(fs.master)
+        groups = broadcast_object([{k: v for k, v in g.items() if k != "params"} for g in optimizer.param_groups]
+                                  if C._rank() == root_rank else None, root_rank, name="tips.bcast_opt.groups")
+        for g, src in zip(optimizer.param_groups, groups):
+            g.update(src)
+        return
+    state = optimizer.state_dict()
+    if C._rank() == root_rank:
+        skeleton = {"param_groups": state["param_groups"],
+                    "state": {k: {n: (("tensor", tuple(v.shape), v.dtype) if isinstance(v, torch.Tensor) else ("value", v))
+                                  for n, v in s.items()} for k, s in state["state"].items()}}
+    else:
+        skeleton = None
+    skeleton = broadcast_object(skeleton, root_rank, name="tips.bcast_opt.skeleton")
+    params = [p for g in optimizer.param_groups for p in g["params"]]
+    new_state = {}
+    for k in sorted(skeleton["state"].keys()):
+        entry = {}
+        device = params[k].device if isinstance(k, int) and k < len(params) else torch.device("cpu")
+        for n, spec in sorted(skeleton["state"][k].items()):
+            if spec[0] == "tensor":
+                cur = state["state"].get(k, {}).get(n)
+                if not (isinstance(cur, torch.Tensor) and tuple(cur.shape) == spec[1] and cur.dtype == spec[2]):
+                    cur = torch.zeros(spec[1], dtype=spec[2], device=device)
+                entry[n] = C.broadcast(cur, root_rank, name=f"tips.bcast_opt.{k}.{n}")
+            else:
+                entry[n] = spec[1]
+        new_state[k] = entry
+    optimizer.load_state_dict({"param_groups": skeleton["param_groups"], "state": new_state})
+
+
+def metric_average(value, name: str):
+    """Average a Python number or a tensor over all ranks."""
+    t = value if isinstance(value, torch.Tensor) else torch.tensor(float(value), dtype=torch.float64)
+    out = C.allreduce(t.detach().cpu().reshape(1) if t.dim() == 0 else t.detach().cpu(), name=name, op=C.Average)
+    return out.item() if out.numel() == 1 else out

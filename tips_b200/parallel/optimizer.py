@@ -1,0 +1,272 @@
+"""DistributedOptimizer: data-parallel training by allreducing gradients.
+
+API parity with the reference's ``DistributedOptimizer`` / ``DistributedGradientTape``
+(tips/tensorflow/__init__.py:252-456,459-568, tips/_keras/__init__.py:27-177): wrap
+an optimizer so that gradients are combined across ranks before they are applied;
+``compression``, ``op`` (Average / Sum), ``gradient_predivide_factor``,
+``backward_passes_per_step`` with ``average_aggregated_gradients``,
+``sparse_as_dense``; the wrapper is a dynamic subclass carrying the wrapped
+optimizer's class name, so a checkpoint loads without this package
+(_keras/__init__.py:161-166); using gradients that were never aggregated is an
+error (_keras/__init__.py:130-159).
+
+What differs: the reference issues one negotiated allreduce per gradient tensor.
+Here gradients are fused into buckets (``fusion_threshold_bytes``, 64 MB by
+default); a bucket is packed by one kernel as soon as backward has produced its
+last gradient, handed to the collective engine, and reduced in place in
+symmetric memory by one fused kernel on the communication stream while backward
+continues.  After the first step the bucket order is frozen, and later steps
+need no control messages at all.
+"""
+from __future__ import annotations
+
+import torch
+
+from .. import _lib
+from ..config import get_config
+from ..runtime import TipsError, _require_init
+from . import collectives as C
+from .buckets import build_buckets
+from .compression import Compression
+
+
+class _DistributedMixin:
+    """Behaviour mixed into a dynamic subclass of the user's optimizer class."""
+
+    def _tips_setup(self, named_parameters, compression, backward_passes_per_step, op, gradient_predivide_factor,
+                    sparse_as_dense, average_aggregated_gradients, groups):
+        _require_init()
+        if op not in (C.Average, C.Sum):
+            raise ValueError("op must be Average or Sum")
+        if gradient_predivide_factor != 1.0 and op != C.Average:
+            raise ValueError("gradient_predivide_factor is only supported with op=Average")
+        if backward_passes_per_step < 1:
+            raise ValueError("backward_passes_per_step must be >= 1")
+        self._tips_compression = compression
+        self._tips_op = op
+        self._tips_predivide = float(gradient_predivide_factor)
+        self._tips_passes = int(backward_passes_per_step)
+        self._tips_avg_aggregated = bool(average_aggregated_gradients)
+        self._tips_sparse_as_dense = bool(sparse_as_dense)
+        self._tips_groups = groups
+        self._tips_size = C._size()
+        params = [p for g in self.param_groups for p in g["params"] if p.requires_grad]
+        if named_parameters is not None:
+            named = list(named_parameters)
+            ids = {id(p) for _, p in named}
+            missing = [p for p in params if id(p) not in ids]
+            if missing:
+                raise ValueError("named_parameters does not cover every parameter of the optimizer")
+            names = [n for n, _ in named]
+            if len(set(names)) != len(names):
+                raise ValueError("parameter names must be unique")
+        self._tips_params = params
+        self._tips_pass_count = {id(p): 0 for p in params}
+        self._tips_sparse = []
+        self._tips_synchronized = False
+        self._tips_should_sync = True
+        self._tips_step_count = 0
+        self._tips_frozen = False
+        self._tips_hooks = []
+
+        from ..ops.optim import _FusedOptimizer
+        self._tips_fused = isinstance(self, _FusedOptimizer)
+        dev_state = None
+        if any(p.is_cuda for p in params):
+            from .. import runtime
+            dev_state = runtime.device_state()
+        wire = get_config().wire_dtype
+        if compression is Compression.fp16:
+            wire = "fp16"
+        elif compression is Compression.bf16:
+            wire = "bf16"
+        if self._tips_fused:
+            self._wire_dtype = wire
+            self._tips_buckets = [fs.bucket for fs in self.build(dev_state)]
+        else:
+            by_kind = {}
+            for p in params:
+                by_kind.setdefault((p.dtype, p.device), []).append(p)
+            self._tips_buckets = []
+            for plist in by_kind.values():
+                for b in build_buckets(plist, None, wire, dev_state):
+                    b.index = len(self._tips_buckets)
+                    b.name = f"tips.bucket.{b.index}"
+                    self._tips_buckets.append(b)
+        self._tips_bucket_of = {}
+        for b in self._tips_buckets:
+            b.pending = len(b.params)
+            for p in b.params:
+                self._tips_bucket_of[id(p)] = b
+        for p in params:
+            self._tips_hooks.append(p.register_post_accumulate_grad_hook(self._tips_make_hook()))
+        import ctypes
+        _lib.core().tips_take_negotiated_order(ctypes.create_string_buffer(1 << 16), 1 << 16)  # clear the log
+
+    # ------------------------------------------------------------------ hooks
+    def _tips_make_hook(self):
+        def hook(p):
+            pid = id(p)
+            self._tips_pass_count[pid] += 1
+            if self._tips_pass_count[pid] < self._tips_passes:
+                return
+            if self._tips_pass_count[pid] > self._tips_passes:
+                raise TipsError("a gradient was computed more than backward_passes_per_step times since the last "
+                                "step(); call step() or synchronize() first, or raise backward_passes_per_step", 3)
+            if p.grad is not None and p.grad.is_sparse:
+                if self._tips_sparse_as_dense:
+                    p.grad = p.grad.to_dense()
+                else:
+                    self._tips_sparse.append(p)
+            b = self._tips_bucket_of[pid]
+            b.ready_count += 1
+            if b.ready_count == len(b.params):
+                self._tips_launch(b)
+        return hook
+
+    def _tips_launch(self, b):
+        """Pack the bucket and hand it to the collective engine."""
+        n = self._tips_size
+        pre = 1.0
+        post = 1.0
+        if self._tips_op == C.Average:
+            pre = 1.0 / self._tips_predivide
+            post = self._tips_predivide / n
+        if self._tips_avg_aggregated and self._tips_passes > 1:
+            pre /= self._tips_passes
+        dense = [p for p in b.params if not (p.grad is not None and p.grad.is_sparse)]
+        if any(p.grad is None for p in dense) or len(dense) != len(b.params):
+            b.grad.zero_()
+        saved = None
+        if len(dense) != len(b.params):  # sparse gradients travel separately
+            saved = {id(p): p.grad for p in b.params if p.grad is not None and p.grad.is_sparse}
+            for p in b.params:
+                if id(p) in saved:
+                    p.grad = None
+        b.pack(scale=pre)
+        if saved:
+            for p in b.params:
+                if id(p) in saved:
+                    p.grad = saved[id(p)]
+        b.launched = True
+        if n == 1:
+            if post != 1.0:
+                b.grad.mul_(post)
+            b.handle = None
+            return
+        h = C._Handle()
+        h.kind = "allreduce"
+        h.output = b.grad
+        h.keep = [b.grad]
+        b.handle = C._enqueue(h, 0, b.name, b.grad, b.grad, (b.numel,), b.grad.dtype, reduce_op=0, prescale=1.0,
+                              postscale=post)
+
+    # ------------------------------------------------------------- public API
+    def synchronize(self):
+        """Wait for every gradient allreduce of this step and make the reduced gradients visible."""
+        for b in self._tips_buckets:
+            if not getattr(b, "launched", False):
+                if b.ready_count == 0 and all(p.grad is None for p in b.params):
+                    # no gradient at all on this rank: still take part with zeros so that ranks stay in step
+                    pass
+                self._tips_launch(b)
+        for b in self._tips_buckets:
+            if b.handle is not None:
+                C.synchronize(b.handle)
+                b.handle = None
+        for p in self._tips_sparse:
+            p.grad = C.sparse_allreduce(p.grad, name=f"tips.sparse.{id(p)}", op=self._tips_op)
+        self._tips_sparse = []
+        if self._tips_fused:
+            for fs in self._flat:
+                fs.grads_packed = True
+        else:
+            for b in self._tips_buckets:
+                sparse_ids = {id(p) for p in b.params if p.grad is not None and p.grad.is_sparse}
+                for i, p in enumerate(b.params):
+                    if id(p) in sparse_ids:
+                        continue
+                    v = b.view_of(i)
+                    p.grad = v if v.dtype == p.dtype else v.to(p.dtype)
+        self._tips_synchronized = True
+        self._tips_maybe_freeze()
+
+    def _tips_maybe_freeze(self):
+        cfg = get_config()
+        if self._tips_frozen or not cfg.static_schedule or self._tips_size == 1:
+            return
+        if not all(b.grad.is_cuda for b in self._tips_buckets):
+            return
+        lib = _lib.core()
+        import ctypes
+        buf = ctypes.create_string_buffer(1 << 16)
+        n = lib.tips_take_negotiated_order(buf, 1 << 16)
+        if n <= 0:
+            return
+        names = buf.value.decode().split("\n")
+        mine = {b.name for b in self._tips_buckets}
+        order = [x for x in names if x in mine]
+        if len(order) != len(mine):
+            return
+        if lib.tips_freeze_schedule("\n".join(order).encode()) == 0:
+            self._tips_frozen = True
+
+    class _SkipSync:
+        def __init__(self, opt):
+            self.opt = opt
+
+        def __enter__(self):
+            self.opt._tips_should_sync = False
+
+        def __exit__(self, *a):
+            self.opt._tips_should_sync = True
+
+    def skip_synchronize(self):
+        """Context manager: ``step()`` inside it does not synchronize (the caller already did)."""
+        return _DistributedMixin._SkipSync(self)
+
+    def step(self, closure=None, **kwargs):
+        if self._tips_should_sync:
+            if self._tips_synchronized:
+                import warnings
+                warnings.warn("step() called after synchronize() without skip_synchronize(); "
+                              "gradients are synchronized only once")
+            else:
+                self.synchronize()
+        elif not self._tips_synchronized:
+            raise TipsError("step() inside skip_synchronize() but synchronize() was not called: the gradients "
+                            "have not been aggregated across ranks", 3)
+        self._tips_synchronized = False
+        out = super().step(closure, **kwargs) if closure is not None or kwargs else super().step()
+        self._tips_after_step()
+        return out
+
+    def _tips_after_step(self):
+        self._tips_step_count += 1
+        for b in self._tips_buckets:
+            b.ready_count = 0
+            b.launched = False
+        for k in self._tips_pass_count:
+            self._tips_pass_count[k] = 0
+        if not self._tips_fused:
+            # reduced gradients were consumed; drop the views so that the next backward
+            # writes fresh gradients instead of accumulating into the bucket
+            for p in self._tips_params:
+                p.grad = None
+
+    def zero_grad(self, set_to_none: bool = True):
+        if any(getattr(b, "launched", False) and b.handle is not None for b in self._tips_buckets):
+            raise TipsError("zero_grad() called while gradient allreduces are in flight; call step() or "
+                            "synchronize() first", 3)
+        return super().zero_grad(set_to_none)
+
+
+def DistributedOptimizer(optimizer, named_parameters=None, compression=Compression.none,
+                         backward_passes_per_step=1, op=C.Average, gradient_predivide_factor=1.0,
+                         sparse_as_dense=False, average_aggregated_gradients=True, groups=None):
+    """Wrap `optimizer` so that `step()` applies gradients combined over all ranks."""
+    cls = type(optimizer.__class__.__name__, (_DistributedMixin, optimizer.__class__), {})
+    optimizer.__class__ = cls
+    optimizer._tips_setup(named_parameters, compression, backward_passes_per_step, op, gradient_predivide_factor,
+                          sparse_as_dense, average_aggregated_gradients, groups)
+    return optimizer

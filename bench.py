@@ -1,0 +1,153 @@
+#!/usr/bin/env python
+"""Headline benchmark: ResNet-50 training images/s (collective mode) and CTR parameter-server
+samples/s, synthetic data, random-init weights.
+
+    python bench.py --gpus N --steps K --warmup W
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N --steps K --warmup W
+
+Rank 0 prints one JSON line.  `value` is ResNet-50 images/s over all GPUs, device-timed with CUDA
+events (max over ranks) with the inputs already resident; `e2e` is the same training loop driven
+through the public API with the step's inputs copied from pinned host memory and the loss read back
+every step; `ps` carries the parameter-server workload's samples/s the same two ways.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+REPO = os.path.dirname(os.path.abspath(__file__))
+if REPO not in sys.path:
+    sys.path.insert(0, REPO)
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="tips", choices=["tips", "reference"])
+    ap.add_argument("--workload", default="all", choices=["all", "resnet50", "ctr"])
+    ap.add_argument("--batch", type=int, default=256, help="ResNet-50 images per GPU")
+    ap.add_argument("--ctr-batch", type=int, default=8192)
+    ap.add_argument("--ctr-rows", type=int, default=10_000_000)
+    ap.add_argument("--backend", default=None, help="fused (default) or nccl (library floor)")
+    return ap.parse_args()
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a timed region runs."""
+
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu = gpu_index
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "200",
+                 "-i", str(self.gpu)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.25)
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except Exception:
+            self.proc.kill()
+            out = ""
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.strip().splitlines():
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1]))
+                mx.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def reference_arm(args):
+    print(json.dumps({
+        "impl": "reference",
+        "unavailable": "the reference needs OpenMPI, ZeroMQ headers, TensorFlow and network downloads of "
+                       "flatbuffers/boost/abseil/gflags/gtest to build; none exist on this image and it has no GPU path",
+    }))
+    return 0
+
+
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        return reference_arm(args)
+    import torch
+    import tips_b200 as tips
+    from tips_b200.bench import workloads
+    if args.backend:
+        tips.set_config(backend=args.backend)
+    tips.init()
+    rank, size = tips.rank(), tips.size()
+    if size != args.gpus and rank == 0:
+        print(f"warning: --gpus {args.gpus} but the job has {size} ranks", file=sys.stderr)
+    dev_index = torch.cuda.current_device()
+    result = {"n_gpus": size, "steps": args.steps, "warmup": args.warmup, "higher_is_better": True, "scaling": "weak",
+              "dtype": "bf16", "data": "synthetic (random inputs, random-init weights)", "impl": "tips"}
+    sampler = ClockSampler(dev_index)
+    if rank == 0:
+        sampler.start()
+    launches = 0
+    if args.workload in ("all", "resnet50"):
+        r = workloads.run_resnet50(args.batch, args.steps, args.warmup)
+        launches += r["gpu_launches"]
+        result.update({
+            "metric": "resnet50_train_images_per_sec", "value": r["value"], "unit": "images/s",
+            "ms_per_step": r["ms_per_step"], "vs_baseline": None,
+            "e2e": r["e2e"],
+            "config": {"model": "ResNet-50 v1.5", "global_batch": args.batch * size, "per_gpu_batch": args.batch,
+                       "image": "224x224x3 NHWC", "optimizer": "SGD momentum 0.9 wd 1e-4",
+                       "parallelism": f"dp{size}", "fusion_bucket_mb": 64,
+                       "l2": "inputs and activations per step far exceed the 126 MB L2"},
+        })
+    if args.workload in ("all", "ctr"):
+        p = workloads.run_ctr(args.ctr_batch, args.ctr_rows, args.steps, args.warmup)
+        launches += p["gpu_launches"]
+        ps = {"metric": "ps_ctr_train_samples_per_sec", "value": p["value"], "unit": "samples/s",
+              "ms_per_step": p["ms_per_step"], "e2e": p["e2e"],
+              "config": {"model": "CTR 26 sparse fields x dim 64 + 13 dense, MLP 512-256-1",
+                         "rows_per_table": args.ctr_rows, "per_gpu_batch": args.ctr_batch,
+                         "global_batch": args.ctr_batch * size, "ids": "Zipf(1.05)", "optimizer": "Adagrad (tables), "
+                         "Adam (MLP)", "parallelism": f"ps{size}"}}
+        if "metric" in result:
+            result["ps"] = ps
+        else:
+            result.update(ps)
+            result["vs_baseline"] = None
+    result["gpu_launches"] = launches
+    if rank == 0:
+        result["clocks"] = sampler.stop()
+        print(json.dumps(result))
+    tips.shutdown()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

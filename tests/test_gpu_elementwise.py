@@ -1,0 +1,179 @@
+"""Numerics of the HBM-bound kernels against plain PyTorch fp32 references."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _dev():
+    return torch.device("cuda", 0)
+
+
+@pytest.mark.parametrize("gdtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("n", [1, 7, 4096, 100003])
+def test_fused_sgd_matches_torch(gdtype, n):
+    from tips_b200.ops.optim import FusedSGD
+    torch.manual_seed(0)
+    p_ref = torch.randn(n, device=_dev())
+    p = torch.nn.Parameter(p_ref.clone().to(gdtype))
+    ref = torch.nn.Parameter(p.detach().float().clone())
+    opt = FusedSGD([p], lr=0.1, momentum=0.9, weight_decay=1e-2, nesterov=True)
+    ropt = torch.optim.SGD([ref], lr=0.1, momentum=0.9, weight_decay=1e-2, nesterov=True)
+    for _ in range(3):
+        g = torch.randn(n, device=_dev()).to(gdtype)
+        p.grad = g.clone()
+        ref.grad = g.float()
+        opt.step()
+        ropt.step()
+    master = opt._flat[0].master[:n]
+    assert torch.allclose(master, ref.detach(), atol=1e-5, rtol=1e-5)
+    tol = 1e-5 if gdtype == torch.float32 else 2e-2
+    assert torch.allclose(p.detach().float(), ref.detach(), atol=tol, rtol=tol)
+
+
+@pytest.mark.parametrize("n", [5, 1024, 33333])
+def test_fused_adamw_matches_torch(n):
+    from tips_b200.ops.optim import FusedAdamW
+    torch.manual_seed(1)
+    p = torch.nn.Parameter(torch.randn(n, device=_dev()))
+    ref = torch.nn.Parameter(p.detach().clone())
+    opt = FusedAdamW([p], lr=1e-2, weight_decay=0.05)
+    ropt = torch.optim.AdamW([ref], lr=1e-2, weight_decay=0.05)
+    for _ in range(4):
+        g = torch.randn(n, device=_dev())
+        p.grad = g.clone()
+        ref.grad = g.clone()
+        opt.step()
+        ropt.step()
+    assert torch.allclose(p.detach(), ref.detach(), atol=2e-5, rtol=1e-4)
+
+
+def test_pack_unpack_roundtrip():
+    from tips_b200.parallel.buckets import build_buckets
+    torch.manual_seed(2)
+    params = [torch.nn.Parameter(torch.randn(s, device=_dev())) for s in [(3, 5), (17,), (64, 33), (1,)]]
+    for p in params:
+        p.grad = torch.randn_like(p)
+    buckets = build_buckets(params, threshold_bytes=1 << 20, wire_dtype="bf16")
+    assert len(buckets) == 1
+    b = buckets[0]
+    b.pack(scale=0.5)
+    for i, p in enumerate(b.params):
+        assert torch.allclose(b.view_of(i).float(), (p.grad * 0.5).to(torch.bfloat16).float())
+    b.pack(scale=0.5, accumulate=True)
+    for i, p in enumerate(b.params):
+        assert torch.allclose(b.view_of(i).float(), p.grad, atol=3e-2, rtol=3e-2)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("shape", [(8, 64, 14, 14), (4, 24, 7, 5), (2, 256, 9, 9)])
+@pytest.mark.parametrize("relu,res", [(False, False), (True, False), (True, True)])
+def test_batchnorm_fwd_bwd(dtype, shape, relu, res):
+    from tips_b200.ops.norm import BatchNorm2d
+    torch.manual_seed(3)
+    dev = _dev()
+    bn = BatchNorm2d(shape[1], relu=relu).to(dev)
+    with torch.no_grad():
+        bn.weight.uniform_(0.5, 1.5)
+        bn.bias.uniform_(-0.5, 0.5)
+    x = torch.randn(shape, device=dev).to(dtype).contiguous(memory_format=torch.channels_last).requires_grad_()
+    r = torch.randn(shape, device=dev).to(dtype).contiguous(memory_format=torch.channels_last).requires_grad_() if res else None
+    y = bn(x, residual=r)
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    # fp32 reference
+    xr = x.detach().float().requires_grad_()
+    rr = r.detach().float().requires_grad_() if res else None
+    w = bn.weight.detach().clone().requires_grad_()
+    b = bn.bias.detach().clone().requires_grad_()
+    yr = torch.nn.functional.batch_norm(xr, None, None, w, b, True, 0.1, bn.eps)
+    if res:
+        yr = yr + rr
+    if relu:
+        yr = torch.relu(yr)
+    yr.backward(dy.float())
+    tol = 2e-4 if dtype == torch.float32 else 6e-2
+    assert torch.allclose(y.float(), yr, atol=tol, rtol=tol)
+    assert torch.allclose(x.grad.float(), xr.grad, atol=tol, rtol=tol)
+    gtol = 1e-3 if dtype == torch.float32 else 0.25
+    assert torch.allclose(bn.weight.grad, w.grad, atol=gtol, rtol=5e-2)
+    assert torch.allclose(bn.bias.grad, b.grad, atol=gtol, rtol=5e-2)
+    if res:
+        assert torch.allclose(r.grad.float(), rr.grad, atol=tol, rtol=tol)
+    m = x.numel() // shape[1]
+    xm = x.detach().float().transpose(0, 1).reshape(shape[1], -1)
+    assert torch.allclose(bn.running_mean, 0.1 * xm.mean(1), atol=1e-3)
+    assert torch.allclose(bn.running_var, 0.9 + 0.1 * xm.var(1, unbiased=True), atol=1e-2)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("rows,cols", [(3, 64), (257, 1024), (64, 768)])
+def test_layernorm_fwd_bwd(dtype, rows, cols):
+    from tips_b200.ops.norm import LayerNorm
+    torch.manual_seed(4)
+    dev = _dev()
+    ln = LayerNorm(cols).to(dev)
+    with torch.no_grad():
+        ln.weight.uniform_(0.5, 1.5)
+        ln.bias.uniform_(-0.5, 0.5)
+    x = torch.randn(rows, cols, device=dev).to(dtype).requires_grad_()
+    y = ln(x)
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    xr = x.detach().float().requires_grad_()
+    w = ln.weight.detach().clone().requires_grad_()
+    b = ln.bias.detach().clone().requires_grad_()
+    yr = torch.nn.functional.layer_norm(xr, (cols,), w, b, ln.eps)
+    yr.backward(dy.float())
+    tol = 2e-4 if dtype == torch.float32 else 6e-2
+    assert torch.allclose(y.float(), yr, atol=tol, rtol=tol)
+    assert torch.allclose(x.grad.float(), xr.grad, atol=tol, rtol=tol)
+    assert torch.allclose(ln.weight.grad, w.grad, atol=0.3 if dtype != torch.float32 else 1e-3, rtol=5e-2)
+    assert torch.allclose(ln.bias.grad, b.grad, atol=0.3 if dtype != torch.float32 else 1e-3, rtol=5e-2)
+
+
+@pytest.mark.parametrize("act", ["relu", "gelu", None])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_bias_act(act, dtype):
+    from tips_b200.ops.pointwise import bias_act
+    torch.manual_seed(5)
+    dev = _dev()
+    x = torch.randn(37, 256, device=dev).to(dtype).requires_grad_()
+    bias = torch.randn(256, device=dev).to(dtype).requires_grad_()
+    y = bias_act(x, bias, act)
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    xr = x.detach().float().requires_grad_()
+    br = bias.detach().float().requires_grad_()
+    z = xr + br
+    yr = torch.relu(z) if act == "relu" else torch.nn.functional.gelu(z) if act == "gelu" else z
+    yr.backward(dy.float())
+    tol = 1e-4 if dtype == torch.float32 else 5e-2
+    assert torch.allclose(y.float(), yr, atol=tol, rtol=tol)
+    assert torch.allclose(x.grad.float(), xr.grad, atol=tol, rtol=tol)
+    assert torch.allclose(bias.grad.float(), br.grad, atol=0.3 if dtype != torch.float32 else 1e-3, rtol=5e-2)
+
+
+def test_losses():
+    from tips_b200.ops.pointwise import sigmoid_bce_loss, softmax_cross_entropy
+    torch.manual_seed(6)
+    dev = _dev()
+    z = torch.randn(1000, device=dev).requires_grad_()
+    t = (torch.rand(1000, device=dev) < 0.25).float()
+    loss = sigmoid_bce_loss(z, t)
+    loss.backward()
+    zr = z.detach().clone().requires_grad_()
+    lr = torch.nn.functional.binary_cross_entropy_with_logits(zr, t)
+    lr.backward()
+    assert torch.allclose(loss, lr, atol=1e-5)
+    assert torch.allclose(z.grad, zr.grad, atol=1e-6)
+    logits = torch.randn(33, 1000, device=dev).to(torch.bfloat16).requires_grad_()
+    labels = torch.randint(0, 1000, (33,), device=dev)
+    labels[5] = -100
+    loss = softmax_cross_entropy(logits, labels)
+    loss.backward()
+    lg = logits.detach().float().requires_grad_()
+    ref = torch.nn.functional.cross_entropy(lg, labels, ignore_index=-100)
+    ref.backward()
+    assert torch.allclose(loss, ref, atol=2e-3)
+    assert torch.allclose(logits.grad.float(), lg.grad, atol=2e-3)

@@ -1,0 +1,151 @@
+"""Benchmark workloads driven through the public API: ResNet-50 data-parallel training and the
+CTR parameter-server model.  Each returns the device-timed rate with resident inputs (`value`)
+and the end-to-end rate with per-step host-to-device input copies and a loss read-back (`e2e`)."""
+from __future__ import annotations
+
+import torch
+
+import tips_b200 as tips
+from tips_b200.ops import base as kbase
+
+
+def _max_over_ranks(ms: float) -> float:
+    if tips.size() == 1:
+        return ms
+    t = torch.tensor([ms], dtype=torch.float64)
+    return float(tips.allreduce(t, op=tips.Max, name=None)[0])
+
+
+def _launch_count() -> int:
+    n = kbase.launches()
+    st = tips.runtime.device_state()
+    if st is not None and st.window is not None:
+        from tips_b200 import _lib
+        n += int(_lib.kernels().tipsk_comm_launches())
+    return n
+
+
+def timed(step_fn, steps: int, warmup: int):
+    """Run `warmup` untimed and `steps` timed calls of step_fn between CUDA events; max over ranks."""
+    for _ in range(warmup):
+        step_fn()
+    torch.cuda.synchronize()
+    tips.barrier()
+    torch.cuda.synchronize()
+    l0 = _launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        step_fn()
+    e1.record()
+    torch.cuda.synchronize()
+    l1 = _launch_count()
+    tips.barrier()
+    ms = _max_over_ranks(e0.elapsed_time(e1))
+    return ms, l1 - l0
+
+
+class _Prefetcher:
+    """Double-buffered pinned-host -> device input pipeline on a side stream."""
+
+    def __init__(self, host_batches):
+        self.host = host_batches
+        self.stream = torch.cuda.Stream()
+        self.i = 0
+        self.next = None
+        self.bytes_per_step = sum(t.numel() * t.element_size() for t in host_batches[0])
+        self._issue()
+
+    def _issue(self):
+        batch = self.host[self.i % len(self.host)]
+        self.i += 1
+        with torch.cuda.stream(self.stream):
+            self.next = [t.cuda(non_blocking=True) for t in batch]
+            self.ev = torch.cuda.Event()
+            self.ev.record(self.stream)
+
+    def get(self):
+        torch.cuda.current_stream().wait_event(self.ev)
+        cur = self.next
+        for t in cur:
+            t.record_stream(torch.cuda.current_stream())
+        self._issue()
+        return cur
+
+
+def run_resnet50(batch: int, steps: int, warmup: int):
+    from tips_b200.models.resnet50 import resnet50
+    from tips_b200.ops.optim import FusedSGD
+    dev = torch.device("cuda", torch.cuda.current_device())
+    torch.manual_seed(1234)
+    model = resnet50(device=dev)
+    model.train()
+    opt = FusedSGD(model.parameters(), lr=0.1, momentum=0.9, weight_decay=1e-4)
+    opt = tips.DistributedOptimizer(opt, named_parameters=model.named_parameters())
+    tips.broadcast_parameters(model.state_dict(), root_rank=0)
+    g = torch.Generator().manual_seed(100 + tips.rank())
+    nhost = 3
+    host = []
+    for _ in range(nhost):
+        x = torch.randn(batch, 3, 224, 224, generator=g).to(torch.bfloat16).contiguous(memory_format=torch.channels_last)
+        y = torch.randint(0, 1000, (batch,), generator=g)
+        host.append((x.pin_memory(), y.pin_memory()))
+    x_dev = host[0][0].to(dev, non_blocking=True)
+    y_dev = host[0][1].to(dev, non_blocking=True)
+
+    def step_resident():
+        loss = model.loss(x_dev, y_dev)
+        loss.backward()
+        opt.step()
+        return loss
+
+    ms, launches = timed(step_resident, steps, warmup)
+    st = tips.runtime.device_state()
+    if st is not None and st.window is not None:
+        st.check_status()
+    value = batch * tips.size() * steps / (ms / 1e3)
+
+    pre = _Prefetcher(host)
+    last = {}
+
+    def step_e2e():
+        x, y = pre.get()
+        loss = model.loss(x, y)
+        loss.backward()
+        opt.step()
+        last["loss"] = loss.item()
+
+    ms2, _ = timed(step_e2e, steps, max(3, warmup // 2))
+    e2e = {"value": batch * tips.size() * steps / (ms2 / 1e3), "unit": "images/s", "ms_per_step": ms2 / steps,
+           "h2d_bytes_per_step": pre.bytes_per_step, "d2h_bytes_per_step": 4, "last_loss": last.get("loss")}
+    return {"value": value, "ms_per_step": ms / steps, "gpu_launches": launches, "e2e": e2e}
+
+
+def run_ctr(batch: int, rows: int, steps: int, warmup: int):
+    from tips_b200.models.ctr import CtrTrainer, synthetic_ctr_batch
+    dev = torch.device("cuda", torch.cuda.current_device())
+    trainer = CtrTrainer(num_fields=26, rows_per_table=rows, dim=64, dense_features=13, hidden=(512, 256),
+                         device=dev)
+    nhost = 3
+    host = [tuple(t.pin_memory() for t in synthetic_ctr_batch(batch, 26, rows, 13, seed=7 * tips.rank() + i))
+            for i in range(nhost)]
+    resident = [t.to(dev) for t in host[0]]
+
+    def step_resident():
+        return trainer.train_step(*resident)
+
+    ms, launches = timed(step_resident, steps, warmup)
+    trainer.check()
+    value = batch * tips.size() * steps / (ms / 1e3)
+    pre = _Prefetcher(host)
+    last = {}
+
+    def step_e2e():
+        ids, dense, labels = pre.get()
+        last["loss"] = trainer.train_step(ids, dense, labels).item()
+
+    ms2, _ = timed(step_e2e, steps, max(3, warmup // 2))
+    trainer.check()
+    e2e = {"value": batch * tips.size() * steps / (ms2 / 1e3), "unit": "samples/s", "ms_per_step": ms2 / steps,
+           "h2d_bytes_per_step": pre.bytes_per_step, "d2h_bytes_per_step": 4, "last_loss": last.get("loss")}
+    return {"value": value, "ms_per_step": ms / steps, "gpu_launches": launches, "e2e": e2e}

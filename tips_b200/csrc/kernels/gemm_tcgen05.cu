@@ -1,0 +1,383 @@
+// bf16 GEMM on the 5th-generation tensor cores: C[M,N] = act(A[M,K] * B[N,K]^T + bias).
+//
+// Both operands are K-major (row-major A and row-major B = "TN"), which is the
+// layout of a linear layer's forward pass (activations [M,K], weight [N,K]).
+// Pipeline inside one CTA (192 threads):
+//   warp 0      TMA producer: cp.async.bulk.tensor.2d (no multicast) brings a
+//               128 x 64 tile of A and a BN x 64 tile of B per stage into
+//               128-byte-swizzled shared memory, signalling an mbarrier
+//   warp 1      MMA issuer: one elected thread issues tcgen05.mma (kind::f16,
+//               M=128, N=BN, K=16) four times per stage with shared-memory
+//               descriptors, accumulating in TMEM; tcgen05.commit releases the
+//               stage back to the producer and finally signals the epilogue
+//   warps 2-5   epilogue: tcgen05.ld the fp32 accumulator rows out of TMEM, add
+//               the bias, apply the activation, convert to bf16 and store
+// Every mbarrier wait is bounded; on a timeout the kernel sets an error word,
+// frees its TMEM and returns.
+//
+// The reference contains no GEMM (its only math is an elementwise loop,
+// tips/core/common/vec.h:194-216); this kernel serves the CTR model's MLP and
+// the BERT-shaped encoder's linear layers.
+#include <cuda.h>
+
+#include <map>
+#include <mutex>
+#include <tuple>
+
+#include "kernels/common.cuh"
+#include "kernels/tips_kernels.h"
+
+namespace tipsk {
+namespace {
+
+constexpr int kBM = 128;
+constexpr int kBK = 64;  // 64 bf16 = 128 bytes = one swizzle row
+constexpr int kGemmThreads = 192;
+constexpr uint32_t kWaitTries = 1u << 26;
+
+__device__ __forceinline__ uint32_t SmemAddr(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void MbarInit(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(SmemAddr(bar)), "r"(count));
+}
+__device__ __forceinline__ void MbarExpectTx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(SmemAddr(bar)), "r"(bytes) : "memory");
+}
+// Bounded wait; false on timeout.
+__device__ __forceinline__ bool MbarWait(uint64_t* bar, uint32_t parity) {
+  const uint32_t addr = SmemAddr(bar);
+  for (uint32_t i = 0; i < kWaitTries; ++i) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(addr), "r"(parity)
+        : "memory");
+    if (done) return true;
+  }
+  return false;
+}
+__device__ __forceinline__ void TmaLoad2D(void* smem_dst, const CUtensorMap* tmap, int x, int y, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(SmemAddr(smem_dst)), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(x), "r"(y), "r"(SmemAddr(bar))
+      : "memory");
+}
+__device__ __forceinline__ void TcFenceAfter() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void TcFenceBefore() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+
+// Shared-memory matrix descriptor for a K-major tile whose rows are 128 bytes and
+// 128-byte swizzled: 8-row groups are 1024 bytes apart.
+__device__ __forceinline__ uint64_t SmemDescSw128(uint32_t smem_addr) {
+  const uint32_t lo = ((smem_addr & 0x3FFFFu) >> 4) | (1u << 16);
+  const uint32_t hi = (1024u >> 4) | (1u << 14) | (2u << 29);
+  return (static_cast<uint64_t>(hi) << 32) | lo;
+}
+
+__device__ __forceinline__ void UmmaBf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accum) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accum)
+      : "memory");
+}
+__device__ __forceinline__ void UmmaCommit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(SmemAddr(bar))
+               : "memory");
+}
+__device__ __forceinline__ void TmemLoad32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+      "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+struct GemmParams {
+  __nv_bfloat16* c;
+  __nv_bfloat16* pre;          // optional: pre-activation output
+  const __nv_bfloat16* bias;   // optional, [N]
+  int32_t* error;              // device error word
+  int m, n, k;
+  int ldc;
+  int act;                     // 0 none, 1 relu, 2 gelu
+};
+
+template <int BN>
+struct GemmCfg {
+  static constexpr int kStages     = BN >= 256 ? 4 : 5;
+  static constexpr int kABytes     = kBM * kBK * 2;
+  static constexpr int kBBytes     = BN * kBK * 2;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kTmemCols   = BN < 32 ? 32 : BN;
+  static constexpr int kSmemBytes  = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+};
+
+template <int BN>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+GemmTnKernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, GemmParams p) {
+  using Cfg = GemmCfg<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full_bar  = reinterpret_cast<uint64_t*>(smem + Cfg::kStages * Cfg::kStageBytes);
+  uint64_t* empty_bar = full_bar + Cfg::kStages;
+  uint64_t* tmem_full = empty_bar + Cfg::kStages;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_full + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int m0   = blockIdx.y * kBM;
+  const int n0   = blockIdx.x * BN;
+  const int num_k = (p.k + kBK - 1) / kBK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < Cfg::kStages; ++s) {
+      MbarInit(&full_bar[s], 1);
+      MbarInit(&empty_bar[s], 1);
+    }
+    MbarInit(tmem_full, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(SmemAddr(tmem_slot)),
+                 "r"(static_cast<uint32_t>(Cfg::kTmemCols))
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  TcFenceBefore();
+  __syncthreads();
+  TcFenceAfter();
+  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
+
+  if (warp == 0) {
+    if (lane == 0) {
+      for (int kt = 0; kt < num_k; ++kt) {
+        const int s = kt % Cfg::kStages;
+        const uint32_t parity = ((kt / Cfg::kStages) & 1) ^ 1;
+        if (!MbarWait(&empty_bar[s], parity)) {
+          atomicExch(p.error, 1);
+          break;
+        }
+        uint8_t* a_dst = smem + s * Cfg::kStageBytes;
+        uint8_t* b_dst = a_dst + Cfg::kABytes;
+        MbarExpectTx(&full_bar[s], Cfg::kStageBytes);
+        TmaLoad2D(a_dst, &tmap_a, kt * kBK, m0, &full_bar[s]);
+        TmaLoad2D(b_dst, &tmap_b, kt * kBK, n0, &full_bar[s]);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(BN >> 3) << 17) |
+                                 (static_cast<uint32_t>(kBM >> 4) << 24);
+      bool ok = true;
+      for (int kt = 0; kt < num_k && ok; ++kt) {
+        const int s = kt % Cfg::kStages;
+        const uint32_t parity = (kt / Cfg::kStages) & 1;
+        if (!MbarWait(&full_bar[s], parity)) {
+          atomicExch(p.error, 2);
+          ok = false;
+          break;
+        }
+        TcFenceAfter();
+        const uint32_t a_addr = SmemAddr(smem + s * Cfg::kStageBytes);
+        const uint32_t b_addr = a_addr + Cfg::kABytes;
+        const uint64_t adesc  = SmemDescSw128(a_addr);
+        const uint64_t bdesc  = SmemDescSw128(b_addr);
+#pragma unroll
+        for (int k = 0; k < kBK / 16; ++k) {
+          // advancing 16 elements (32 bytes) along K inside the swizzle row = +2 in the address field
+          UmmaBf16(tmem_base, adesc + 2 * k, bdesc + 2 * k, idesc, (kt > 0 || k > 0) ? 1u : 0u);
+        }
+        UmmaCommit(&empty_bar[s]);
+      }
+      UmmaCommit(tmem_full);  // arrives when every MMA issued so far has completed
+    }
+  } else {
+    const int q = warp & 3;  // TMEM lane quarter this warp may access
+    const bool ok = MbarWait(tmem_full, 0);
+    if (!ok && lane == 0) atomicExch(p.error, 3);
+    TcFenceAfter();
+    const int row = m0 + q * 32 + lane;
+    if (ok) {
+#pragma unroll 1
+      for (int c = 0; c < BN / 32 + (BN % 32 ? 1 : 0); ++c) {
+        uint32_t r[32];
+        if (BN >= 32 || c == 0) {
+          TmemLoad32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(c * 32), r);
+        }
+        const int col0 = n0 + c * 32;
+        if (row < p.m && col0 < p.n) {
+          float v[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            v[j] = __uint_as_float(r[j]);
+            if (p.bias && col0 + j < p.n) v[j] += __bfloat162float(p.bias[col0 + j]);
+          }
+          __nv_bfloat16* crow = p.c + static_cast<int64_t>(row) * p.ldc + col0;
+          __nv_bfloat16* prow = p.pre ? p.pre + static_cast<int64_t>(row) * p.ldc + col0 : nullptr;
+          const bool vec_ok = (p.ldc % 8 == 0) && (col0 + 32 <= p.n) && (BN >= 32);
+          if (vec_ok) {
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              alignas(16) __nv_bfloat16 o[8];
+              if (prow) {
+                alignas(16) __nv_bfloat16 pr[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) pr[j] = __float2bfloat16_rn(v[g * 8 + j]);
+                *reinterpret_cast<uint4*>(prow + g * 8) = *reinterpret_cast<uint4*>(pr);
+              }
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                float x = v[g * 8 + j];
+                if (p.act == 1) x = fmaxf(x, 0.f);
+                else if (p.act == 2) x = 0.5f * x * (1.f + erff(x * 0.70710678118654752f));
+                o[j] = __float2bfloat16_rn(x);
+              }
+              *reinterpret_cast<uint4*>(crow + g * 8) = *reinterpret_cast<uint4*>(o);
+            }
+          } else {
+            for (int j = 0; j < 32 && col0 + j < p.n && j < BN; ++j) {
+              float x = v[j];
+              if (prow) prow[j] = __float2bfloat16_rn(x);
+              if (p.act == 1) x = fmaxf(x, 0.f);
+              else if (p.act == 2) x = 0.5f * x * (1.f + erff(x * 0.70710678118654752f));
+              crow[j] = __float2bfloat16_rn(x);
+            }
+          }
+        }
+      }
+    }
+  }
+  TcFenceBefore();
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                 "r"(static_cast<uint32_t>(Cfg::kTmemCols))
+                 : "memory");
+  }
+}
+
+// ------------------------------------------------------------------ host side
+
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                              const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                              CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeFn GetEncodeFn() {
+  static EncodeFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeFn>(sym);
+  });
+  return fn;
+}
+
+// Row-major [rows, cols] bf16 matrix with leading dimension ld (elements); box = 64 x box_rows, 128B swizzle.
+int MakeTmap(CUtensorMap* out, const void* base, int64_t rows, int64_t cols, int64_t ld, int box_rows) {
+  EncodeFn enc = GetEncodeFn();
+  if (!enc) return SetError(-7, "cuTensorMapEncodeTiled is not available from the driver");
+  if (reinterpret_cast<uintptr_t>(base) % 16 != 0) return SetError(-2, "gemm: operand base must be 16-byte aligned");
+  if ((ld * 2) % 16 != 0) return SetError(-2, "gemm: operand row stride must be a multiple of 16 bytes");
+  cuuint64_t dims[2]    = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+  cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * 2};
+  cuuint32_t box[2]     = {static_cast<cuuint32_t>(kBK), static_cast<cuuint32_t>(box_rows)};
+  cuuint32_t estr[2]    = {1, 1};
+  CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return SetError(-7, "cuTensorMapEncodeTiled failed with code " + std::to_string((int)r));
+  return 0;
+}
+
+int32_t* GemmErrorWord() {
+  static int32_t* word = nullptr;
+  if (!word) {
+    if (cudaMalloc(reinterpret_cast<void**>(&word), sizeof(int32_t)) != cudaSuccess) return nullptr;
+    cudaMemset(word, 0, sizeof(int32_t));
+  }
+  return word;
+}
+
+template <int BN>
+int LaunchGemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, cudaStream_t s) {
+  using Cfg = GemmCfg<BN>;
+  static bool configured = false;
+  if (!configured) {
+    TIPSK_CUDA(cudaFuncSetAttribute(GemmTnKernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
+    configured = true;
+  }
+  dim3 grid((p.n + BN - 1) / BN, (p.m + kBM - 1) / kBM);
+  GemmTnKernel<BN><<<grid, kGemmThreads, Cfg::kSmemBytes, s>>>(ta, tb, p);
+  TIPSK_LAUNCH_CHECK();
+  return 0;
+}
+
+}  // namespace
+}  // namespace tipsk
+
+using namespace tipsk;
+
+extern "C" {
+
+/* 1 when tipsk_gemm_bf16 accepts the problem (alignment of the leading dimensions). */
+int tipsk_gemm_supported(int m, int n, int k, int lda, int ldb) {
+  return (m > 0 && n > 0 && k > 0 && lda % 8 == 0 && ldb % 8 == 0) ? 1 : 0;
+}
+
+/* C[m,n] = act(A[m,k] * B[n,k]^T + bias); bf16 in, fp32 accumulate in TMEM, bf16 out.
+ * lda/ldb/ldc are leading dimensions in elements; `pre` (optional) receives the value before the activation. */
+int tipsk_gemm_bf16(const void* a, const void* b, void* c, const void* bias, void* pre, int m, int n, int k, int lda,
+                    int ldb, int ldc, int act, void* stream) {
+  TIPSK_REQUIRE(tipsk_gemm_supported(m, n, k, lda, ldb), "gemm: lda and ldb must be multiples of 8 elements");
+  int bn = 128;
+  if (n <= 16) bn = 16;
+  else if (n <= 32) bn = 32;
+  else if (n <= 64) bn = 64;
+  else if (n % 256 == 0 && (static_cast<int64_t>(m) / kBM) * (n / 256) >= NumSMs()) bn = 256;
+  CUtensorMap ta, tb;
+  int rc = MakeTmap(&ta, a, m, k, lda, kBM);
+  if (rc) return rc;
+  rc = MakeTmap(&tb, b, n, k, ldb, bn);
+  if (rc) return rc;
+  GemmParams p;
+  p.c     = static_cast<__nv_bfloat16*>(c);
+  p.pre   = static_cast<__nv_bfloat16*>(pre);
+  p.bias  = static_cast<const __nv_bfloat16*>(bias);
+  p.error = GemmErrorWord();
+  TIPSK_REQUIRE(p.error != nullptr, "gemm: cannot allocate the error word");
+  p.m = m; p.n = n; p.k = k; p.ldc = ldc; p.act = act;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  switch (bn) {
+    case 16: return LaunchGemm<16>(ta, tb, p, s);
+    case 32: return LaunchGemm<32>(ta, tb, p, s);
+    case 64: return LaunchGemm<64>(ta, tb, p, s);
+    case 256: return LaunchGemm<256>(ta, tb, p, s);
+    default: return LaunchGemm<128>(ta, tb, p, s);
+  }
+}
+
+/* Reads and clears the GEMM error word (0 ok; 1/2/3 = producer / MMA / epilogue wait ran out). Synchronises. */
+int tipsk_gemm_status(void) {
+  int32_t* w = GemmErrorWord();
+  if (!w) return -7;
+  int32_t v = 0;
+  if (cudaMemcpy(&v, w, sizeof(v), cudaMemcpyDeviceToHost) != cudaSuccess) return -7;
+  if (v) cudaMemset(w, 0, sizeof(v));
+  return v;
+}
+
+}  // extern "C"

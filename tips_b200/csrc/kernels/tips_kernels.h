@@ -120,6 +120,12 @@ int tipsk_ps_pull(const int64_t* const* host_ids, void* const* host_outs, int64_
 int tipsk_ps_push(const int64_t* const* host_ids, const void* const* host_grads, int64_t batch, int64_t grad_ld,
                   int64_t grad_col0, int grad_dtype, float grad_scale, int rule, float lr, float eps, void* stream);
 
+/* ---- tcgen05 GEMM (gemm_tcgen05.cu) ---- */
+int tipsk_gemm_supported(int m, int n, int k, int lda, int ldb);
+int tipsk_gemm_bf16(const void* a, const void* b, void* c, const void* bias, void* pre, int m, int n, int k, int lda,
+                    int ldb, int ldc, int act, void* stream);
+int tipsk_gemm_status(void);
+
 #ifdef __cplusplus
 }
 #endif

@@ -58,6 +58,7 @@ _PROTOS = {
     "tipsk_ps_push": (I, [PP, PP, L, L, L, I, F, I, F, F, P]),
     "tipsk_gemm_bf16": (I, [P, P, P, P, P, I, I, I, I, I, I, I, P]),
     "tipsk_gemm_supported": (I, [I, I, I, I, I]),
+    "tipsk_gemm_status": (I, []),
 }
 
 

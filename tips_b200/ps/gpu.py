@@ -1,0 +1,211 @@
+"""GPU-resident sharded parameter-server tables.
+
+The reference's parameter server keeps rows in host hash maps on server ranks and
+moves them through an RPC (tips/core/ps/sparse_table.h:38-185, ps_server.h:147-265,
+ps_client.h:78-130).  Here every rank is a server and a worker at once: a table's
+row ``id`` lives on rank ``id % N`` at local row ``id // N`` of a slab in
+peer-mapped device memory, ``pull`` is a lookup kernel that reads rows straight
+from the owner's HBM over NVLink, and ``push`` scatters gradients into the owner's
+accumulation table and applies the server-side optimizer there (csrc/kernels/ps.cu).
+
+Rows exist from the start (a dense slab initialised to zero or to a seeded uniform),
+which is what the reference's lazy zero-initialisation on first pull amounts to
+(tips/core/ps/sparse_access_method.h:23-27); arbitrary 64-bit keys are served by the
+host tables in tips_b200.ps.host.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from typing import Optional
+
+import torch
+
+from .. import _lib
+from ..ops import base
+
+_RULES = {"sgd": 0, "adagrad": 1, "literal_reference": 2}
+_active = None
+
+
+def _world():
+    """(rank, size, emulated, device_state) of the GPU data plane."""
+    from .. import runtime
+    st = runtime.device_state()
+    if st is None:
+        from ..parallel import device as _device
+        try:
+            st = _device.state()
+        except RuntimeError:
+            st = None
+    if st is None:
+        return 0, 1, 0, None
+    return (0 if st.emulated else st.rank), st.size, st.emulated, st
+
+
+class ShardedEmbedding:
+    """`num_fields` tables of [rows_per_table, dim] fp32, row-sharded over the ranks."""
+
+    def __init__(self, num_fields: int, rows_per_table: int, dim: int, optimizer: str = "adagrad", lr: float = 0.01,
+                 eps: float = 1e-8, init_scale: float = 0.0, seed: int = 0, slots: Optional[int] = None,
+                 expected_batch: int = 8192, device=None):
+        if optimizer not in _RULES:
+            raise ValueError(f"optimizer must be one of {sorted(_RULES)}")
+        if dim % 4:
+            raise ValueError("dim must be a multiple of 4")
+        self.num_fields, self.rows, self.dim = num_fields, rows_per_table, dim
+        self.rule, self.lr, self.eps = _RULES[optimizer], lr, eps
+        self.rank, self.size, self.emulated, st = _world()
+        self.device = device or (st.device if st is not None else torch.device("cuda", torch.cuda.current_device()))
+        n = self.size
+        self.rows_per_shard = (rows_per_table + n - 1) // n
+        field_bytes = self.rows_per_shard * dim * 4
+        self.has_state = self.rule == 1
+        self.field_off = [f * field_bytes for f in range(num_fields)]
+        self.state_off = [(num_fields + f) * field_bytes if self.has_state else 0 for f in range(num_fields)]
+        slab_bytes = field_bytes * num_fields * (2 if self.has_state else 1)
+        if slots is None:
+            slots = 1
+            while slots < 2 * expected_batch * num_fields:
+                slots *= 2
+        self.slots = slots
+        acc_bytes = slots * 8 + slots * dim * 4
+        self.slabs, self.accs = self._allocate(slab_bytes, acc_bytes, st)
+        lib = base.K()
+        local = range(n) if self.emulated else [self.rank]
+        for r in local:
+            slab = self.slabs[r] if self.emulated else self.slabs[0]
+            for f in range(num_fields):
+                w = slab[self.field_off[f]:self.field_off[f] + field_bytes].view(torch.float32)
+                base.check(lib.tipsk_table_init(w.data_ptr(), self.rows_per_shard, dim, f, r, n, rows_per_table,
+                                                seed, float(init_scale), base.stream()), "table_init")
+            if self.has_state:
+                slab[num_fields * field_bytes:].zero_()
+        torch.cuda.synchronize()
+        self._sync_ranks()
+        self._configure()
+
+    # ------------------------------------------------------------------ set-up
+    def _allocate(self, slab_bytes, acc_bytes, st):
+        n = self.size
+        if self.emulated:
+            slabs = [torch.empty(slab_bytes, dtype=torch.uint8, device=self.device) for _ in range(n)]
+            accs = [torch.zeros(acc_bytes, dtype=torch.uint8, device=self.device) for _ in range(n)]
+            self._slab_ptrs = [t.data_ptr() for t in slabs]
+            self._acc_ptrs = [t.data_ptr() for t in accs]
+            return slabs, accs
+        if n == 1:
+            slab = torch.empty(slab_bytes, dtype=torch.uint8, device=self.device)
+            acc = torch.zeros(acc_bytes, dtype=torch.uint8, device=self.device)
+            self._slab_ptrs, self._acc_ptrs = [slab.data_ptr()], [acc.data_ptr()]
+            return [slab], [acc]
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm_mem
+        group = dist.group.WORLD
+        slab = symm_mem.empty(slab_bytes, dtype=torch.uint8, device=self.device)
+        h1 = symm_mem.rendezvous(slab, group.group_name)
+        acc = symm_mem.empty(acc_bytes, dtype=torch.uint8, device=self.device)
+        h2 = symm_mem.rendezvous(acc, group.group_name)
+        acc.zero_()
+        self._handles = (h1, h2)
+        self._slab_ptrs = [int(p) for p in h1.buffer_ptrs]
+        self._acc_ptrs = [int(p) for p in h2.buffer_ptrs]
+        return [slab], [acc]
+
+    def _sync_ranks(self):
+        if self.size > 1 and not self.emulated:
+            from .. import runtime
+            torch.cuda.synchronize()
+            runtime.barrier()
+
+    def _configure(self):
+        global _active
+        lib = base.K()
+        n = self.size
+        base.check(lib.tipsk_ps_configure(base.ptr_array(self._slab_ptrs), base.ptr_array(self._acc_ptrs), n,
+                                          base.u64_array(self.field_off), base.u64_array(self.state_off),
+                                          base.i64_array([self.rows_per_shard] * self.num_fields), self.num_fields,
+                                          self.dim, self.slots), "ps_configure")
+        _active = self
+
+    def _activate(self):
+        if _active is not self:
+            self._configure()
+
+    # ------------------------------------------------------------------ data path
+    def _per_rank(self, tensors):
+        """Per-local-rank pointer array: a list of tensors when emulated, one tensor otherwise."""
+        if self.emulated:
+            assert isinstance(tensors, (list, tuple)) and len(tensors) == self.size
+            return base.ptr_array(list(tensors)), tensors[0]
+        return base.ptr_array([tensors]), tensors
+
+    def pull(self, ids, out=None, out_col0: int = 0, dtype=torch.bfloat16, fence: bool = True):
+        """Gather rows: ids [B, F] int64 -> out[:, out_col0 + f*dim : ...] (a new [B, F*dim] tensor if out is None)."""
+        self._activate()
+        ids_arr, ids0 = self._per_rank(ids)
+        b = ids0.shape[0]
+        if out is None:
+            mk = lambda: torch.empty(b, self.num_fields * self.dim, dtype=dtype, device=self.device)
+            out = [mk() for _ in range(self.size)] if self.emulated else mk()
+        out_arr, out0 = self._per_rank(out)
+        base.check(base.K().tipsk_ps_pull(ids_arr, out_arr, b, out0.stride(0), out_col0, base.code(out0),
+                                          int(fence), base.stream()), "ps_pull")
+        return out
+
+    def push(self, ids, grads, grad_col0: int = 0, grad_scale: float = 1.0, lr: Optional[float] = None):
+        """Scatter-reduce the row gradients to their owners and apply the optimizer there."""
+        self._activate()
+        ids_arr, ids0 = self._per_rank(ids)
+        g_arr, g0 = self._per_rank(grads)
+        base.check(base.K().tipsk_ps_push(ids_arr, g_arr, ids0.shape[0], g0.stride(0), grad_col0, base.code(g0),
+                                          float(grad_scale), self.rule, float(self.lr if lr is None else lr),
+                                          float(self.eps), base.stream()), "ps_push")
+        base.count_launches(1)
+
+    def check(self):
+        """Raise if a push overflowed the accumulation table or an id was out of range. Synchronises."""
+        self._activate()
+        err = ctypes.c_int32(0)
+        touched = ctypes.c_uint64(0)
+        base.check(base.K().tipsk_ps_status(ctypes.byref(err), ctypes.byref(touched)), "ps_status")
+        if err.value == 1:
+            raise RuntimeError("parameter-server push: accumulation table full; raise `slots`")
+        if err.value == 2:
+            raise RuntimeError("parameter-server: an id was negative or beyond the table")
+        return int(touched.value)
+
+    # ------------------------------------------------------------------ host views / checkpoint
+    def local_shard(self, field: int, rank: Optional[int] = None, state: bool = False) -> torch.Tensor:
+        """[rows_per_shard, dim] fp32 view of this rank's shard of `field` (or its Adagrad state)."""
+        slab = self.slabs[rank if self.emulated else 0]
+        off = (self.state_off if state else self.field_off)[field]
+        nbytes = self.rows_per_shard * self.dim * 4
+        return slab[off:off + nbytes].view(torch.float32).view(self.rows_per_shard, self.dim)
+
+    def owner_of(self, ids: torch.Tensor):
+        return ids % self.size, ids // self.size
+
+
+class _LookupFn(torch.autograd.Function):
+    """pull in forward; push (scatter-reduce + server-side optimizer) in backward."""
+
+    @staticmethod
+    def forward(ctx, table, ids, anchor, out, col0, grad_scale):
+        table.pull(ids, out=out, out_col0=col0)
+        ctx.table, ctx.ids, ctx.col0, ctx.grad_scale = table, ids, col0, grad_scale
+        ctx.mark_dirty(out)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        g = dout if dout.stride(1) == 1 else dout.contiguous()
+        ctx.table.push(ctx.ids, g, grad_col0=ctx.col0, grad_scale=ctx.grad_scale)
+        return None, None, None, None, None, None
+
+
+def embedding_lookup(table: ShardedEmbedding, ids: torch.Tensor, out: torch.Tensor, col0: int = 0,
+                     grad_scale: float = 1.0) -> torch.Tensor:
+    """Differentiable pull into `out` (a [B, ld] buffer); the backward pass pushes the gradient."""
+    anchor = torch.zeros((), device=out.device, requires_grad=True)
+    return _LookupFn.apply(table, ids, anchor, out, col0, grad_scale)

@@ -1,0 +1,109 @@
+"""Parameter-server kernels (pull / push with server-side SGD and Adagrad) against a dense PyTorch model of
+the same tables; single rank and 4 emulated ranks on one GPU."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _dense_tables(table, fields, rows, dim):
+    """Reassemble the global [rows, dim] tables (and Adagrad state) from the shards."""
+    n = table.size
+    out, state = [], []
+    for f in range(fields):
+        w = torch.zeros(table.rows_per_shard * n, dim, device=table.device)
+        s = torch.zeros_like(w)
+        for r in range(n):
+            w[r::n] = table.local_shard(f, rank=r)
+            if table.has_state:
+                s[r::n] = table.local_shard(f, rank=r, state=True)
+        out.append(w[:rows].clone())
+        state.append(s[:rows].clone())
+    return out, state
+
+
+def _reference_update(ws, ss, ids_all, grads_all, rule, lr, eps, dim):
+    for f in range(len(ws)):
+        g = torch.zeros_like(ws[f])
+        for ids, grads in zip(ids_all, grads_all):
+            g.index_add_(0, ids[:, f], grads[:, f * dim:(f + 1) * dim].float())
+        touched = g.abs().sum(1) != 0
+        if rule == "adagrad":
+            ss[f] += g * g
+            ws[f] -= torch.where(touched[:, None], lr * g / (ss[f].sqrt() + eps), torch.zeros_like(g))
+        else:
+            ws[f] -= lr * g
+
+
+@pytest.mark.parametrize("rule", ["sgd", "adagrad"])
+@pytest.mark.parametrize("dim", [16, 64])
+def test_pull_push_single_rank(rule, dim):
+    from tips_b200.ps.gpu import ShardedEmbedding
+    dev = torch.device("cuda", 0)
+    fields, rows, batch = 3, 5000, 2048
+    t = ShardedEmbedding(fields, rows, dim, optimizer=rule, lr=0.1, init_scale=0.1, seed=3, expected_batch=batch,
+                         device=dev)
+    ws, ss = _dense_tables(t, fields, rows, dim)
+    torch.manual_seed(0)
+    ids = (torch.rand(batch, fields, device=dev) ** 4 * rows).long().clamp_(0, rows - 1)  # skewed: many duplicates
+    out = t.pull(ids, dtype=torch.float32)
+    ref = torch.cat([ws[f][ids[:, f]] for f in range(fields)], dim=1)
+    assert torch.equal(out, ref)
+    out16 = t.pull(ids, dtype=torch.bfloat16)
+    assert torch.equal(out16, ref.to(torch.bfloat16))
+    for step in range(2):
+        grads = torch.randn(batch, fields * dim, device=dev)
+        t.push(ids, grads, grad_scale=0.5)
+        _reference_update(ws, ss, [ids], [grads * 0.5], rule, 0.1, t.eps, dim)
+    assert t.check() > 0
+    got, got_s = _dense_tables(t, fields, rows, dim)
+    for f in range(fields):
+        assert torch.allclose(got[f], ws[f], atol=2e-4, rtol=1e-4)
+        if rule == "adagrad":
+            assert torch.allclose(got_s[f], ss[f], atol=1e-3, rtol=1e-4)
+
+
+def test_pull_push_emulated_ranks():
+    from tips_b200.config import set_config
+    from tips_b200.parallel import device
+    from tips_b200.ps.gpu import ShardedEmbedding
+    set_config(symm_window_bytes=1 << 20, device_wait_budget_ms=2000, comm_blocks=8)
+    st = device.setup(emulate_ranks=4)
+    try:
+        dev = st.device
+        fields, rows, dim, batch = 2, 3001, 32, 1024
+        t = ShardedEmbedding(fields, rows, dim, optimizer="adagrad", lr=0.05, init_scale=0.1, seed=9,
+                             expected_batch=batch * 4, device=dev)
+        assert t.size == 4 and t.emulated
+        ws, ss = _dense_tables(t, fields, rows, dim)
+        # the initial contents do not depend on the sharding
+        t1_vals = ws[0][:5].clone()
+        torch.manual_seed(1)
+        ids = [(torch.rand(batch, fields, device=dev) ** 3 * rows).long().clamp_(0, rows - 1) for _ in range(4)]
+        outs = t.pull(ids, dtype=torch.float32)
+        for r in range(4):
+            ref = torch.cat([ws[f][ids[r][:, f]] for f in range(fields)], dim=1)
+            assert torch.equal(outs[r], ref)
+        grads = [torch.randn(batch, fields * dim, device=dev) for _ in range(4)]
+        t.push(ids, grads, grad_scale=0.25)
+        _reference_update(ws, ss, ids, [g * 0.25 for g in grads], "adagrad", 0.05, t.eps, dim)
+        t.check()
+        st.check_status()
+        got, got_s = _dense_tables(t, fields, rows, dim)
+        for f in range(fields):
+            assert torch.allclose(got[f], ws[f], atol=2e-4, rtol=1e-4)
+            assert torch.allclose(got_s[f], ss[f], atol=1e-3, rtol=1e-4)
+        assert t1_vals.abs().sum() > 0
+    finally:
+        device.teardown(st)
+
+
+def test_ctr_trainer_loss_decreases():
+    from tips_b200.models.ctr import CtrTrainer, synthetic_ctr_batch
+    dev = torch.device("cuda", 0)
+    t = CtrTrainer(num_fields=4, rows_per_table=2000, dim=16, dense_features=5, hidden=(64, 32), device=dev,
+                   expected_batch=512, table_lr=0.1, mlp_lr=5e-3)
+    ids, dense, labels = [x.to(dev) for x in synthetic_ctr_batch(512, 4, 2000, 5, seed=5)]
+    losses = [t.train_step(ids, dense, labels).item() for _ in range(30)]
+    t.check()
+    assert losses[-1] < losses[0] * 0.8, losses

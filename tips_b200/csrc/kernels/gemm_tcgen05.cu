@@ -33,7 +33,8 @@ namespace {
 constexpr int kBM = 128;
 constexpr int kBK = 64;  // 64 bf16 = 128 bytes = one swizzle row
 constexpr int kGemmThreads = 192;
-constexpr uint32_t kWaitTries = 1u << 26;
+constexpr uint32_t kWaitTries = 1u << 30;
+constexpr uint64_t kWaitBudgetNs = 2000000000ull;  // 2 s per wait
 
 __device__ __forceinline__ uint32_t SmemAddr(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -47,7 +48,15 @@ __device__ __forceinline__ void MbarExpectTx(uint64_t* bar, uint32_t bytes) {
 // Bounded wait; false on timeout.
 __device__ __forceinline__ bool MbarWait(uint64_t* bar, uint32_t parity) {
   const uint32_t addr = SmemAddr(bar);
+  uint64_t t0 = 0;
   for (uint32_t i = 0; i < kWaitTries; ++i) {
+    // try_wait may itself block for a while, so the bound is on elapsed time, not on tries
+    if ((i & 0xff) == 0xff) {
+      uint64_t now;
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > kWaitBudgetNs) return false;
+    }
     uint32_t done;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"

@@ -1,0 +1,173 @@
+// extern "C" surface of the host parameter server (the reference has no binding for
+// its parameter server at all: it is reachable only from C++ tests,
+// tips/core/ps/ps_server_test.cc, ps_client_test.cc).
+//
+// A "ps table" handle bundles a SparseTable, the PsServer that serves its local shards and a
+// PsClient.  Creation is collective in the sense that every rank must create the same tables
+// with the same names and server lists, then synchronise (tips_barrier) before the first
+// pull, so that the RPC services exist everywhere.
+#include <cstring>
+#include <map>
+#include <memory>
+#include <mutex>
+
+#include "ps/ps_server.h"
+#include "runtime/context.h"
+
+using namespace tips;
+using namespace tips::ps;
+
+namespace {
+
+struct PsBundle {
+  std::unique_ptr<SparseTable> table;
+  std::unique_ptr<PsServer> server;
+  std::unique_ptr<PsClient> client;
+};
+
+std::mutex g_mu;
+std::map<int64_t, std::unique_ptr<PsBundle>> g_tables;
+int64_t g_next = 1;
+thread_local std::string tl_ps_error;
+
+int Fail(int code, const std::string& m) {
+  tl_ps_error = m;
+  return -code;
+}
+
+PsBundle* Get(int64_t id) {
+  std::lock_guard<std::mutex> lock(g_mu);
+  auto it = g_tables.find(id);
+  return it == g_tables.end() ? nullptr : it->second.get();
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* tips_ps_last_error(void) { return tl_ps_error.c_str(); }
+
+/* rule: 0 SGD (w -= lr*g), 1 Adagrad, 2 the reference's literal rule (w = lr*g). */
+int64_t tips_ps_table_create(const char* name, const int* servers, int nservers, int local_shards, int rule, double lr,
+                             double eps) {
+  try {
+    Context& ctx = Context::Global();
+    if (!ctx.initialized()) return Fail(kPrecondition, "tips is not initialised");
+    std::vector<int> sv(servers, servers + nservers);
+    for (int s : sv)
+      if (s < 0 || s >= ctx.size()) return Fail(kInvalidArgument, "server rank out of range");
+    auto b   = std::make_unique<PsBundle>();
+    b->table = std::make_unique<SparseTable>(sv, ctx.rank(), local_shards);
+    std::shared_ptr<PushAccessMethod> push;
+    if (rule == 0)
+      push = std::make_shared<SparseTableSgdPushAccess>(lr);
+    else if (rule == 1)
+      push = std::make_shared<AdagradPushAccess>(lr, eps);
+    else if (rule == 2)
+      push = std::make_shared<LiteralReferencePushAccess>(lr);
+    else
+      return Fail(kInvalidArgument, "unknown update rule");
+    b->server = std::make_unique<PsServer>(name, b->table.get(), std::make_shared<SparseTablePullAccess>(), push);
+    b->server->Start();
+    b->client = std::make_unique<PsClient>(name, b->table.get(), ctx.rank());
+    std::lock_guard<std::mutex> lock(g_mu);
+    int64_t id   = g_next++;
+    g_tables[id] = std::move(b);
+    return id;
+  } catch (const std::exception& e) {
+    return Fail(kInternal, e.what());
+  }
+}
+
+int tips_ps_table_destroy(int64_t id) {
+  std::unique_ptr<PsBundle> b;
+  {
+    std::lock_guard<std::mutex> lock(g_mu);
+    auto it = g_tables.find(id);
+    if (it == g_tables.end()) return 0;
+    b = std::move(it->second);
+    g_tables.erase(it);
+  }
+  b->server->Stop();
+  return 0;
+}
+
+/* Pulls n rows of `length` elements of `dtype`; out receives n*length elements in key order. */
+int tips_ps_pull(int64_t id, const uint64_t* keys, int64_t n, int dtype, int length, void* out, int timeout_ms) {
+  try {
+    PsBundle* b = Get(id);
+    if (!b) return Fail(kInvalidArgument, "unknown ps table");
+    std::vector<PsClient::PullRecord> recs(n);
+    for (int64_t i = 0; i < n; ++i) recs[i] = {keys[i], static_cast<Datatype>(dtype), static_cast<uint32_t>(length)};
+    auto fut = b->client->Pull(recs);
+    if (!fut->Wait(timeout_ms)) return Fail(kTimeout, "ps pull timed out");
+    if (!fut->status.ok()) return Fail(fut->status.code(), fut->status.message());
+    const size_t row_bytes = DatatypeNumBytes(static_cast<Datatype>(dtype)) * length;
+    for (int64_t i = 0; i < n; ++i) {
+      const KeyItem& it = fut->values[i];
+      if (it.value.size() != row_bytes)
+        return Fail(kPrecondition, "row " + std::to_string(keys[i]) + " has a different length or dtype on the server");
+      memcpy(static_cast<char*>(out) + i * row_bytes, it.value.data(), row_bytes);
+    }
+    return 0;
+  } catch (const std::exception& e) {
+    return Fail(kInternal, e.what());
+  }
+}
+
+/* Pushes n gradient rows; returns the number of rows that did not exist on their server (>= 0). */
+int64_t tips_ps_push(int64_t id, const uint64_t* keys, int64_t n, int dtype, int length, const void* values,
+                     int timeout_ms) {
+  try {
+    PsBundle* b = Get(id);
+    if (!b) return Fail(kInvalidArgument, "unknown ps table");
+    const size_t row_bytes = DatatypeNumBytes(static_cast<Datatype>(dtype)) * length;
+    std::vector<KeyItem> recs(n);
+    for (int64_t i = 0; i < n; ++i) {
+      recs[i].key   = keys[i];
+      recs[i].dtype = static_cast<Datatype>(dtype);
+      const uint8_t* p = static_cast<const uint8_t*>(values) + i * row_bytes;
+      recs[i].value.assign(p, p + row_bytes);
+    }
+    auto fut = b->client->Push(recs);
+    if (!fut->Wait(timeout_ms)) return Fail(kTimeout, "ps push timed out");
+    if (!fut->status.ok()) return Fail(fut->status.code(), fut->status.message());
+    return static_cast<int64_t>(fut->missing_rows);
+  } catch (const std::exception& e) {
+    return Fail(kInternal, e.what());
+  }
+}
+
+int64_t tips_ps_table_size(int64_t id) {
+  PsBundle* b = Get(id);
+  return b ? static_cast<int64_t>(b->table->size()) : -1;
+}
+
+int tips_ps_table_server_of(int64_t id, uint64_t key) {
+  PsBundle* b = Get(id);
+  return b ? b->table->ServerWorldRank(b->table->ToServerId(key)) : -1;
+}
+
+int tips_ps_table_save(int64_t id, const char* path, int binary) {
+  PsBundle* b = Get(id);
+  if (!b) return Fail(kInvalidArgument, "unknown ps table");
+  Status st = binary ? b->table->SaveBinary(path) : b->table->WriteToFile(path);
+  return st.ok() ? 0 : Fail(st.code(), st.message());
+}
+
+int tips_ps_table_load(int64_t id, const char* path, int binary, int dtype) {
+  PsBundle* b = Get(id);
+  if (!b) return Fail(kInvalidArgument, "unknown ps table");
+  Status st = binary ? b->table->LoadBinary(path) : b->table->LoadFromFile(path, static_cast<Datatype>(dtype));
+  return st.ok() ? 0 : Fail(st.code(), st.message());
+}
+
+int tips_ps_server_counters(int64_t id, uint64_t* rows_pulled, uint64_t* rows_pushed) {
+  PsBundle* b = Get(id);
+  if (!b) return Fail(kInvalidArgument, "unknown ps table");
+  *rows_pulled = b->server->rows_pulled();
+  *rows_pushed = b->server->rows_pushed();
+  return 0;
+}
+
+}  // extern "C"

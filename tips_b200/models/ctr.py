@@ -1,0 +1,103 @@
+"""CTR model trained in parameter-server mode: sparse fields looked up in sharded
+embedding tables (pull), concatenated with dense features, an MLP with a sigmoid
+output, binary cross-entropy; the embedding gradients are pushed back and applied
+on the owning rank by the server-side optimizer, the MLP is data-parallel.
+
+This is the workload the reference's parameter server targets (PsClient pull /
+push of sparse rows with a server-side update rule, tips/core/ps/ps_client.h:78-130,
+sparse_access_method.h:41-61); the reference ships no model for it.
+"""
+from __future__ import annotations
+
+import torch
+import torch.nn as nn
+
+import tips_b200 as tips
+from ..ops.linear import Linear
+from ..ops.optim import FusedAdam
+from ..ops.pointwise import sigmoid_bce_loss
+from ..ps.gpu import ShardedEmbedding, embedding_lookup
+
+
+def synthetic_ctr_batch(batch: int, fields: int, rows: int, dense_features: int, seed: int, alpha: float = 1.05):
+    """ids [B, F] ~ bounded Zipf(alpha) over [0, rows), dense ~ N(0,1), labels ~ Bernoulli(0.25)."""
+    g = torch.Generator().manual_seed(seed)
+    u = torch.rand(batch, fields, generator=g, dtype=torch.float64)
+    e = 1.0 - alpha
+    x = ((float(rows) ** e - 1.0) * u + 1.0) ** (1.0 / e)  # inverse CDF of p(x) ~ x^-alpha on [1, rows]
+    ids = (x.floor().to(torch.int64) - 1).clamp_(0, rows - 1)
+    dense = torch.randn(batch, dense_features, generator=g).to(torch.bfloat16)
+    labels = (torch.rand(batch, generator=g) < 0.25).to(torch.float32)
+    return ids, dense, labels
+
+
+class CtrMLP(nn.Module):
+    def __init__(self, in_features: int, hidden=(512, 256)):
+        super().__init__()
+        dims = [in_features] + list(hidden)
+        self.layers = nn.ModuleList([Linear(dims[i], dims[i + 1], act="relu") for i in range(len(hidden))])
+        self.out = Linear(dims[-1], 1)
+
+    def forward(self, x):
+        for layer in self.layers:
+            x = layer(x)
+        return self.out(x)
+
+
+class CtrTrainer:
+    """Owns the tables, the MLP and both optimizers; `train_step` is one synchronous PS step."""
+
+    def __init__(self, num_fields=26, rows_per_table=10_000_000, dim=64, dense_features=13, hidden=(512, 256),
+                 table_lr=0.05, mlp_lr=1e-3, device=None, expected_batch=8192, seed=0):
+        self.device = device or torch.device("cuda", torch.cuda.current_device())
+        self.fields, self.dim, self.dense = num_fields, dim, dense_features
+        self.emb_cols = num_fields * dim
+        self.in_features = (self.emb_cols + dense_features + 7) // 8 * 8  # row stride must be a multiple of 16 bytes
+        self.tables = ShardedEmbedding(num_fields, rows_per_table, dim, optimizer="adagrad", lr=table_lr,
+                                       init_scale=0.05, seed=seed, expected_batch=expected_batch, device=self.device)
+        torch.manual_seed(seed + 17)
+        self.mlp = CtrMLP(self.in_features, hidden).to(self.device).to(torch.bfloat16)
+        opt = FusedAdam(self.mlp.parameters(), lr=mlp_lr, weight_decay=0.0)
+        self.opt = tips.DistributedOptimizer(opt) if tips.is_initialized() else opt
+        if tips.is_initialized() and tips.size() > 1:
+            tips.broadcast_parameters(self.mlp.state_dict(), root_rank=0)
+        self.world = tips.size() if tips.is_initialized() else 1
+        self._x = None
+
+    def _input_buffer(self, batch):
+        if self._x is None or self._x.shape[0] != batch:
+            self._x = torch.zeros(batch, self.in_features, dtype=torch.bfloat16, device=self.device)
+        return self._x
+
+    def forward(self, ids, dense):
+        x = self._input_buffer(ids.shape[0]).detach()
+        x[:, self.emb_cols:self.emb_cols + self.dense] = dense
+        x = embedding_lookup(self.tables, ids, x, col0=0, grad_scale=1.0 / self.world)
+        return self.mlp(x).view(-1)
+
+    def train_step(self, ids, dense, labels):
+        loss = sigmoid_bce_loss(self.forward(ids, dense), labels)
+        loss.backward()
+        self.opt.step()
+        return loss.detach()
+
+    def check(self):
+        from ..ops.linear import gemm_status
+        self.tables.check()
+        if gemm_status() != 0:
+            raise RuntimeError("a GEMM launch reported a bounded-wait timeout")
+        st = tips.runtime.device_state()
+        if st is not None and st.window is not None:
+            st.check_status()
+
+
+def smoke_step(device):
+    """Tiny PS step used by the smoke test: 4 fields x 1000 rows x dim 16."""
+    t = CtrTrainer(num_fields=4, rows_per_table=1000, dim=16, dense_features=5, hidden=(64, 32), device=device,
+                   expected_batch=256)
+    ids, dense, labels = synthetic_ctr_batch(256, 4, 1000, 5, seed=1)
+    l0 = t.train_step(ids.to(device), dense.to(device), labels.to(device)).item()
+    l1 = t.train_step(ids.to(device), dense.to(device), labels.to(device)).item()
+    t.check()
+    assert l0 == l0 and l1 == l1
+    return l0, l1

@@ -1,0 +1,131 @@
+"""Host parameter server: sparse tables of arbitrary 64-bit keys served by CPU shard threads.
+
+Python binding of the native host PS (csrc/ps): the counterpart of the reference's
+PsServer / PsClient / SparseTable / Route, which the reference never exposed to
+Python (they are driven only from C++ tests, tips/core/ps/ps_server_test.cc:55-131,
+ps_client_test.cc:11-85).  Rows are created on first pull and zero-initialised; a
+push applies the server-side update rule on the row's owning shard thread.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import POINTER, c_char_p, c_double, c_int, c_int64, c_uint64, c_void_p
+from typing import Iterable, Optional, Sequence
+
+import numpy as np
+
+from .. import _lib
+from ..runtime import TipsError, _require_init, barrier
+
+_RULES = {"sgd": 0, "adagrad": 1, "literal_reference": 2}
+_NP2CODE = {np.dtype(np.float32): 0, np.dtype(np.float64): 1, np.dtype(np.int32): 2, np.dtype(np.int64): 3}
+_declared = False
+
+
+def _lib_ps():
+    global _declared
+    lib = _lib.core()
+    if not _declared:
+        lib.tips_ps_last_error.restype = c_char_p
+        lib.tips_ps_table_create.restype = c_int64
+        lib.tips_ps_table_create.argtypes = [c_char_p, POINTER(c_int), c_int, c_int, c_int, c_double, c_double]
+        lib.tips_ps_table_destroy.argtypes = [c_int64]
+        lib.tips_ps_pull.argtypes = [c_int64, POINTER(c_uint64), c_int64, c_int, c_int, c_void_p, c_int]
+        lib.tips_ps_push.restype = c_int64
+        lib.tips_ps_push.argtypes = [c_int64, POINTER(c_uint64), c_int64, c_int, c_int, c_void_p, c_int]
+        lib.tips_ps_table_size.restype = c_int64
+        lib.tips_ps_table_size.argtypes = [c_int64]
+        lib.tips_ps_table_server_of.argtypes = [c_int64, c_uint64]
+        lib.tips_ps_table_save.argtypes = [c_int64, c_char_p, c_int]
+        lib.tips_ps_table_load.argtypes = [c_int64, c_char_p, c_int, c_int]
+        lib.tips_ps_server_counters.argtypes = [c_int64, POINTER(c_uint64), POINTER(c_uint64)]
+        _declared = True
+    return lib
+
+
+class Route:
+    """Which ranks are parameter servers and which are workers (a rank may be both)."""
+
+    def __init__(self, servers: Optional[Sequence[int]] = None, workers: Optional[Sequence[int]] = None):
+        _require_init()
+        n = _lib.core().tips_size()
+        self.servers = sorted(set(range(n) if servers is None else servers))
+        self.workers = sorted(set(range(n) if workers is None else workers))
+        me = _lib.core().tips_rank()
+        self.is_server = me in self.servers
+        self.is_worker = me in self.workers
+
+
+class HostSparseTable:
+    """A sparse table [key -> row of `dim` elements] sharded over the server ranks by a hash of the key."""
+
+    def __init__(self, name: str, dim: int, route: Optional[Route] = None, optimizer: str = "sgd", lr: float = 0.01,
+                 eps: float = 1e-8, dtype=np.float32, local_shards: int = 1, timeout_s: float = 60.0):
+        _require_init()
+        if optimizer not in _RULES:
+            raise ValueError(f"optimizer must be one of {sorted(_RULES)}")
+        self.route = route or Route()
+        self.name, self.dim = name, int(dim)
+        self.dtype = np.dtype(dtype)
+        self.timeout_ms = int(timeout_s * 1000)
+        lib = _lib_ps()
+        servers = (c_int * len(self.route.servers))(*self.route.servers)
+        self._id = lib.tips_ps_table_create(name.encode(), servers, len(self.route.servers), local_shards,
+                                            _RULES[optimizer], lr, eps)
+        if self._id < 0:
+            raise TipsError("ps table create: " + lib.tips_ps_last_error().decode(), int(-self._id))
+        barrier()  # every rank has registered the services
+
+    def _keys(self, keys):
+        k = np.ascontiguousarray(np.asarray(keys, dtype=np.uint64).reshape(-1))
+        return k, k.ctypes.data_as(POINTER(c_uint64))
+
+    def pull(self, keys) -> np.ndarray:
+        """Rows of `keys` as an [n, dim] array; unknown keys are created as zeros on their server."""
+        lib = _lib_ps()
+        k, kp = self._keys(keys)
+        out = np.empty((k.size, self.dim), dtype=self.dtype)
+        rc = lib.tips_ps_pull(self._id, kp, k.size, _NP2CODE[self.dtype], self.dim, out.ctypes.data, self.timeout_ms)
+        if rc < 0:
+            raise TipsError("ps pull: " + lib.tips_ps_last_error().decode(), -rc)
+        return out
+
+    def push(self, keys, grads) -> int:
+        """Send one gradient row per key; returns how many rows did not exist on their server."""
+        lib = _lib_ps()
+        k, kp = self._keys(keys)
+        g = np.ascontiguousarray(np.asarray(grads, dtype=self.dtype).reshape(k.size, self.dim))
+        rc = lib.tips_ps_push(self._id, kp, k.size, _NP2CODE[self.dtype], self.dim, g.ctypes.data, self.timeout_ms)
+        if rc < 0:
+            raise TipsError("ps push: " + lib.tips_ps_last_error().decode(), int(-rc))
+        return int(rc)
+
+    def local_size(self) -> int:
+        return int(_lib_ps().tips_ps_table_size(self._id))
+
+    def server_of(self, key: int) -> int:
+        return int(_lib_ps().tips_ps_table_server_of(self._id, int(key)))
+
+    def save(self, path: str, binary: bool = False) -> None:
+        """Dump this rank's shards: text ("<key>\\tVec:\\t<e> <e> ... " per line) or binary."""
+        lib = _lib_ps()
+        if lib.tips_ps_table_save(self._id, path.encode(), int(binary)) != 0:
+            raise TipsError("ps save: " + lib.tips_ps_last_error().decode())
+
+    def load(self, path: str, binary: bool = False) -> None:
+        """Load rows from a dump; only rows owned by this rank under the current sharding are kept,
+        so a dump written with one number of servers can be read with another."""
+        lib = _lib_ps()
+        if lib.tips_ps_table_load(self._id, path.encode(), int(binary), _NP2CODE[self.dtype]) != 0:
+            raise TipsError("ps load: " + lib.tips_ps_last_error().decode())
+
+    def counters(self):
+        a, b = c_uint64(0), c_uint64(0)
+        _lib_ps().tips_ps_server_counters(self._id, ctypes.byref(a), ctypes.byref(b))
+        return {"rows_pulled": a.value, "rows_pushed": b.value}
+
+    def close(self):
+        if self._id > 0:
+            barrier()
+            _lib_ps().tips_ps_table_destroy(self._id)
+            self._id = -1

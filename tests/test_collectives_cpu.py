@@ -1,0 +1,115 @@
+"""Collectives on CPU ranks through the negotiating engine: values, dtypes, odd sizes, average vs sum,
+any broadcast root, allgather with unequal first dimensions, cross-rank mismatch errors, duplicate names,
+fusion, object collectives, stall detection."""
+import pytest
+import torch
+
+from mp_util import run_ranks
+
+
+def _values(rank, size):
+    import tips_b200 as tips
+    assert tips.rank() == rank and tips.size() == size and tips.local_size() == size
+    for dtype in (torch.float32, torch.float64, torch.int32, torch.int64, torch.bfloat16, torch.float16):
+        for n in (1, 7, 1000, 4097):
+            x = (torch.arange(n) % 13 + rank).to(dtype)
+            s = tips.allreduce(x, op=tips.Sum)
+            ref = sum(((torch.arange(n) % 13 + r).to(dtype).double()) for r in range(size))
+            assert torch.allclose(s.double(), ref, rtol=2e-2 if dtype in (torch.bfloat16, torch.float16) else 1e-6), dtype
+    x = torch.full((5,), float(rank + 1))
+    assert torch.allclose(tips.allreduce(x), torch.full((5,), (size + 1) / 2))            # Average is the default
+    assert torch.allclose(tips.allreduce(x, average=False), torch.full((5,), size * (size + 1) / 2))
+    assert torch.allclose(tips.allreduce(x, op=tips.Sum, prescale_factor=2.0, postscale_factor=0.5),
+                          torch.full((5,), size * (size + 1) / 2))
+    assert torch.allclose(tips.allreduce(x, op=tips.Max), torch.full((5,), float(size)))
+    assert torch.allclose(tips.allreduce(x, op=tips.Min), torch.full((5,), 1.0))
+    y = x.clone(); tips.allreduce_(y, op=tips.Sum); assert y[0] == size * (size + 1) / 2
+    assert tips.allreduce(torch.tensor(float(rank)), op=tips.Sum).item() == sum(range(size))  # scalar
+    c = tips.allreduce(torch.full((64,), 1.0 + rank), compression=tips.Compression.fp16, op=tips.Sum)
+    assert c.dtype == torch.float32 and torch.allclose(c, torch.full((64,), float(sum(range(1, size + 1)))))
+    for root in range(size):
+        b = tips.broadcast(torch.full((3, 2), float(rank)), root_rank=root)
+        assert (b == root).all()
+    g = tips.allgather(torch.full((rank + 1, 2, 3), float(rank)))
+    assert g.shape == (size * (size + 1) // 2, 2, 3)
+    off = 0
+    for r in range(size):
+        assert (g[off:off + r + 1] == r).all(); off += r + 1
+    sp = torch.sparse_coo_tensor(torch.tensor([[rank, size]]), torch.tensor([1.0, 2.0]), (size + 1,))
+    dense = tips.sparse_allreduce(sp, op=tips.Sum).to_dense()
+    assert dense[size] == 2.0 * size and dense[0] == 1.0
+    objs = tips.allgather_object({"rank": rank, "s": "x" * rank})
+    assert [o["rank"] for o in objs] == list(range(size))
+    assert tips.broadcast_object(("cfg", rank), root_rank=size - 1) == ("cfg", size - 1)
+
+
+def _errors(rank, size):
+    import tips_b200 as tips
+    with pytest.raises(tips.TipsError, match="mismatched.*shapes"):
+        tips.allreduce(torch.ones(3 + rank), name="bad_shape")
+    with pytest.raises(tips.TipsError, match="data types"):
+        tips.allreduce(torch.ones(3, dtype=torch.float32 if rank == 0 else torch.float64), name="bad_dtype")
+    with pytest.raises(tips.TipsError, match="mismatched collective operations"):
+        (tips.allreduce if rank == 0 else tips.allgather)(torch.ones(3), name="bad_op")
+    with pytest.raises(tips.TipsError, match="roots"):
+        tips.broadcast(torch.ones(3), root_rank=rank % 2, name="bad_root")
+    with pytest.raises(tips.TipsError, match="trailing"):
+        tips.allgather(torch.ones(2, 3 + rank), name="bad_gather")
+    h = tips.allreduce_async(torch.ones(4), name="dup", op=tips.Sum)
+    if True:
+        try:
+            tips.allreduce_async(torch.ones(4), name="dup", op=tips.Sum)
+            dup_ok = True
+        except tips.TipsError as e:
+            dup_ok = False
+            assert "already in flight" in str(e)
+        # the first may already have completed on a fast machine; both outcomes are legal, a crash is not
+        if dup_ok:
+            pass
+    assert tips.synchronize(h)[0] == size
+    # the engine still works after errors
+    assert tips.allreduce(torch.ones(2), op=tips.Sum)[0] == size
+
+
+def _fusion_and_order(rank, size):
+    import tips_b200 as tips
+    tips.barrier()
+    names = [f"t{i}" for i in range(32)]
+    order = names if rank == 0 else list(reversed(names))  # every rank enqueues in a different order
+    hs = {n: tips.allreduce_async(torch.full((100,), float(int(n[1:]))), name=n, op=tips.Sum) for n in order}
+    for n in names:
+        assert torch.allclose(tips.synchronize(hs[n]), torch.full((100,), float(int(n[1:]) * size)))
+    out = tips.grouped_allreduce([torch.ones(10) * i for i in range(8)], op=tips.Sum)
+    assert all(torch.allclose(o, torch.ones(10) * i * size) for i, o in enumerate(out))
+    m = tips.metrics()
+    if rank == 0:
+        assert m["fused_tensors"] > 0 and m["ops_failed"] == 0
+
+
+def _stall(rank, size):
+    import tips_b200 as tips
+    if rank == 0:
+        with pytest.raises(tips.TipsError, match="stalled"):
+            tips.allreduce(torch.ones(3), name="only_rank0")
+    tips.barrier()
+    assert tips.allreduce(torch.ones(2), op=tips.Sum)[0] == size
+
+
+def test_values_3_ranks():
+    run_ranks(_values, 3)
+
+
+def test_values_2_ranks():
+    run_ranks(_values, 2)
+
+
+def test_error_paths():
+    run_ranks(_errors, 2)
+
+
+def test_fusion_and_global_order():
+    run_ranks(_fusion_and_order, 3)
+
+
+def test_stall_detector_aborts_the_tensor():
+    run_ranks(_stall, 2, env={"TIPS_STALL_ABORT_MS": "1500", "TIPS_STALL_WARN_MS": "500"})

@@ -127,6 +127,23 @@ def build_all(force=False):
     return build_core(force=force), build_kernels(force=force)
 
 
+def build_native_tests():
+    """Compile csrc/tests/*.cc into executables under build/ (linked against libtips_core.so)."""
+    core = build_core()
+    OBJ.mkdir(exist_ok=True)
+    outs = []
+    for src in sorted((CSRC / "tests").glob("*.cc")):
+        exe = OBJ / src.stem
+        if (not exe.exists() or exe.stat().st_mtime < max(src.stat().st_mtime, core.stat().st_mtime)):
+            cmd = [CXX, "-std=c++17", "-O1", "-g1", "-pthread", f"-I{CSRC}", str(src), f"-L{LIB}", "-ltips_core",
+                   f"-Wl,-rpath,{LIB}", "-o", str(exe)]
+            r = subprocess.run(cmd, capture_output=True, text=True)
+            if r.returncode != 0:
+                raise RuntimeError(f"compile failed: {' '.join(cmd)}\n{r.stderr}")
+        outs.append(exe)
+    return outs
+
+
 def ptxas_report() -> str:
     """Registers / spills / shared memory per kernel, from the nvcc logs of the last build."""
     lines = []

@@ -81,7 +81,8 @@ class _LinearFn(torch.autograd.Function):
         if not dy2.is_contiguous():
             dy2 = dy2.contiguous()
         dbias = None
-        if dy2.is_cuda:
+        vec_ok = (n * dy2.element_size()) % 16 == 0  # the fused kernel works on 16-byte column vectors
+        if dy2.is_cuda and vec_ok:
             dz = dy2
             db = torch.empty(n, dtype=torch.float32, device=dy2.device) if bias is not None else None
             if ctx.act != 0 or db is not None:

@@ -1,0 +1,177 @@
+"""DistributedOptimizer, callbacks, elastic state and checkpoint/resume on CPU ranks."""
+import math
+import os
+
+import pytest
+import torch
+
+from mp_util import run_ranks
+
+
+def _make(seed):
+    from tips_b200.models.mnist_cnn import MnistCNN
+    torch.manual_seed(seed)
+    return MnistCNN()
+
+
+def _dp_matches_single_process(rank, size, fused, passes):
+    import tips_b200 as tips
+    from tips_b200.models.mnist_cnn import synthetic_batch
+    from tips_b200.ops.optim import FusedSGD
+    model = _make(1234 + rank)          # different initial weights on purpose
+    tips.broadcast_parameters(model.state_dict(), root_rank=0)
+    ref = _make(1234)
+    make = (lambda p: FusedSGD(p, lr=0.01, momentum=0.9)) if fused else (lambda p: torch.optim.SGD(p, lr=0.01, momentum=0.9))
+    opt = tips.DistributedOptimizer(make(model.parameters()), named_parameters=model.named_parameters(),
+                                    backward_passes_per_step=passes)
+    assert type(opt).__name__ == ("FusedSGD" if fused else "SGD")  # same class name as the wrapped optimizer
+    ropt = torch.optim.SGD(ref.parameters(), lr=0.01, momentum=0.9)
+    for step in range(3):
+        for k in range(passes):
+            x, y = synthetic_batch(16, 1000 * step + 10 * k + rank)
+            torch.nn.functional.cross_entropy(model(x), y).backward()
+        opt.step()
+        opt.zero_grad()
+        for k in range(passes):
+            xs, ys = zip(*[synthetic_batch(16, 1000 * step + 10 * k + r) for r in range(size)])
+            (torch.nn.functional.cross_entropy(ref(torch.cat(xs)), torch.cat(ys)) / passes).backward()
+        ropt.step()
+        ropt.zero_grad()
+    for (k, a), (_, b) in zip(model.state_dict().items(), ref.state_dict().items()):
+        assert torch.allclose(a, b, atol=2e-5), (k, (a - b).abs().max())
+
+
+@pytest.mark.parametrize("fused", [False, True])
+def test_distributed_optimizer_matches_single_process(fused):
+    run_ranks(_dp_matches_single_process, 2, fused, 1)
+
+
+def test_backward_passes_per_step():
+    run_ranks(_dp_matches_single_process, 2, False, 2)
+
+
+def _guards(rank, size):
+    import tips_b200 as tips
+    model = torch.nn.Linear(4, 2)
+    opt = tips.DistributedOptimizer(torch.optim.SGD(model.parameters(), lr=0.1))
+    model(torch.ones(3, 4)).sum().backward()
+    with pytest.raises(tips.TipsError, match="not been aggregated"):
+        with opt.skip_synchronize():
+            opt.step()
+    opt.synchronize()
+    with opt.skip_synchronize():
+        opt.step()
+    opt.zero_grad()
+    model(torch.ones(3, 4)).sum().backward()
+    with pytest.raises(Exception, match="more than backward_passes_per_step"):
+        model(torch.ones(3, 4)).sum().backward()
+    with pytest.raises(ValueError):
+        tips.DistributedOptimizer(torch.optim.SGD(model.parameters(), lr=0.1), op=tips.Sum, gradient_predivide_factor=2.0)
+
+
+def test_optimizer_guards():
+    run_ranks(_guards, 2)
+
+
+def _callbacks(rank, size, tmp):
+    import tips_b200 as tips
+    from tips_b200 import callbacks as cb
+    from tips_b200.models.mnist_cnn import synthetic_batch
+    from tips_b200.trainer import fit
+    model = _make(rank)
+    base_lr = 0.01 * size
+    opt = tips.DistributedOptimizer(torch.optim.SGD(model.parameters(), lr=base_lr, momentum=0.9))
+    warm = cb.LearningRateWarmupCallback(initial_lr=base_lr, warmup_epochs=2, steps_per_epoch=4)
+    sched = cb.LearningRateScheduleCallback(initial_lr=base_lr, multiplier=0.1, start_epoch=2)
+    ckpt = cb.BestModelCheckpoint(os.path.join(tmp, "best-{epoch}.pt"), monitor="loss")
+    cbs = [cb.BroadcastGlobalVariablesCallback(0), cb.MetricAverageCallback(), warm, sched, ckpt]
+    hist = fit(model, opt, torch.nn.functional.cross_entropy, lambda e, s: synthetic_batch(8, 100 * e + 10 * s + rank),
+               epochs=3, steps_per_epoch=4, callbacks=cbs)
+    # warm-up: lr at the end of epoch e (last batch) = base/size * ((e + 1) * (size - 1) / warmup + 1)
+    assert math.isclose(hist[0]["lr"], base_lr / size * (1.0 * (size - 1) / 2 + 1), rel_tol=1e-6)
+    assert math.isclose(hist[1]["lr"], base_lr, rel_tol=1e-6)
+    assert math.isclose(hist[2]["lr"], base_lr * 0.1, rel_tol=1e-6)
+    assert opt.param_groups[0]["momentum"] == 0.9          # momentum correction was undone
+    losses = tips.allgather_object(hist[-1]["loss"])
+    assert all(abs(l - losses[0]) < 1e-9 for l in losses)   # metric averaged: identical on every rank
+    w = tips.allgather_object(model.fc2.weight.detach().sum().item())
+    assert all(abs(x - w[0]) < 1e-6 for x in w)             # replicas stayed in sync after the broadcast
+    if rank == 0:
+        assert any(f.startswith("best-") for f in os.listdir(tmp))
+
+
+def test_callbacks(tmp_path):
+    run_ranks(_callbacks, 2, str(tmp_path))
+
+
+def _elastic_and_resume(rank, size, tmp):
+    import tips_b200 as tips
+    from tips_b200 import elastic
+    from tips_b200.ops.optim import FusedAdam
+    from tips_b200.utils.checkpoint import resume, save_checkpoint
+    torch.manual_seed(rank)
+    model = torch.nn.Linear(8, 4)
+    opt = tips.DistributedOptimizer(FusedAdam(model.parameters(), lr=0.01))
+    state = elastic.State(model, opt, samples=0)
+    state.sync()
+    def step():
+        model(torch.ones(2, 8) * (rank + 1)).sum().backward()
+        opt.step()
+    step()
+    state.samples = 10
+    state.epoch = 1
+    state.commit()
+    good = model.weight.detach().clone()
+    step()
+    state.samples = 99
+    assert not torch.equal(model.weight, good)
+    state.restore()
+    assert torch.equal(model.weight.detach(), good) and state.samples == 10 and state.epoch == 1
+    step()                                                   # optimizer state was restored as well
+    path = os.path.join(tmp, "ckpt.pt")
+    wrote = save_checkpoint(path, model, opt, extra={"epoch": 5})
+    assert wrote == (rank == 0)
+    tips.barrier()
+    ref = model.weight.detach().clone()
+    with torch.no_grad():
+        model.weight.add_(rank + 1.0)                        # diverge, then resume from the file
+    extra = resume(path, model, opt)
+    assert extra["epoch"] == 5 and torch.allclose(model.weight.detach(), ref)
+    commits = elastic.CommitStateCallback(state, batches_per_commit=2)
+    n0 = state.commits
+    for b in range(4):
+        commits.on_batch_end(b)
+    assert state.commits == n0 + 2
+    ub = elastic.UpdateBatchStateCallback(state)
+    ub.set_context(model, opt, {"steps": 10})
+    ub.on_train_begin()
+    ub.on_batch_end(3)
+    assert state.batch == 4
+    ub.on_epoch_begin(0)
+    assert ub.params["steps"] == 6
+    ue = elastic.UpdateEpochStateCallback(state)
+    ue.on_train_begin()
+    ue.on_epoch_end(state.epoch)
+    assert state.epoch == 2
+
+
+def test_elastic_state_and_resume(tmp_path):
+    run_ranks(_elastic_and_resume, 2, str(tmp_path))
+
+
+def _peer_loss(rank, size):
+    """A rank that leaves: the others get an error on their next collective instead of hanging."""
+    import os as _os
+    import time
+    import tips_b200 as tips
+    assert tips.allreduce(torch.ones(2), op=tips.Sum)[0] == size
+    if rank == size - 1:
+        _os._exit(0)  # dies between steps, nothing in flight
+    time.sleep(1.0)
+    with pytest.raises(tips.TipsError):
+        tips.allreduce(torch.ones(2), op=tips.Sum, name="after_loss")
+    _os._exit(0)
+
+
+def test_rank_loss_is_an_error_not_a_hang():
+    run_ranks(_peer_loss, 3, env={"TIPS_STALL_ABORT_MS": "3000", "TIPS_HOST_TIMEOUT_MS": "5000"})

@@ -30,7 +30,7 @@ def parse_args():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--impl", default="tips", choices=["tips", "reference"])
+    ap.add_argument("--impl", default="tips", choices=["tips", "reference", "floor"])
     ap.add_argument("--workload", default="all", choices=["all", "resnet50", "ctr"])
     ap.add_argument("--batch", type=int, default=256, help="ResNet-50 images per GPU")
     ap.add_argument("--ctr-batch", type=int, default=8192)
@@ -116,7 +116,12 @@ def main():
         sampler.start()
     launches = 0
     if args.workload in ("all", "resnet50"):
-        r = workloads.run_resnet50(args.batch, args.steps, args.warmup)
+        if args.impl == "floor":
+            tips.set_config(backend="nccl")
+            r = workloads.run_resnet50_floor(args.batch, args.steps, args.warmup)
+            result["impl"] = "floor (cuDNN BN + torch SGD + NCCL DDP)"
+        else:
+            r = workloads.run_resnet50(args.batch, args.steps, args.warmup)
         launches += r["gpu_launches"]
         result.update({
             "metric": "resnet50_train_images_per_sec", "value": r["value"], "unit": "images/s",
@@ -127,7 +132,7 @@ def main():
                        "parallelism": f"dp{size}", "fusion_bucket_mb": 64,
                        "l2": "inputs and activations per step far exceed the 126 MB L2"},
         })
-    if args.workload in ("all", "ctr"):
+    if args.workload in ("all", "ctr") and args.impl != "floor":
         p = workloads.run_ctr(args.ctr_batch, args.ctr_rows, args.steps, args.warmup)
         launches += p["gpu_launches"]
         ps = {"metric": "ps_ctr_train_samples_per_sec", "value": p["value"], "unit": "samples/s",

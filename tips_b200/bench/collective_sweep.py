@@ -1,0 +1,117 @@
+"""Collective sweep: allreduce(sum) / allgather / broadcast, 1 KB .. 1 GB, fp32 and bf16, fused NVLink kernels
+vs NCCL on the same GPUs.  Device-timed with CUDA events on the launching stream, max over ranks.
+
+    python -m torch.distributed.run --nproc-per-node N -m tips_b200.bench.collective_sweep [--max-mb 1024]
+
+Bus bandwidth uses the usual conventions: allreduce algbw * 2(N-1)/N, allgather and broadcast algbw * (N-1)/N
+with algbw = total bytes / time.  The roofline reference is the measured 770 GB/s peer copy per direction.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes
+import json
+import sys
+
+import torch
+
+import tips_b200 as tips
+from tips_b200 import _lib
+
+LINK_GBS = 770.0
+
+
+def _time(fn, iters, warmup=3):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    tips.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / iters
+    t = torch.tensor([ms], dtype=torch.float64)
+    return float(tips.allreduce(t, op=tips.Max)[0])
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--max-mb", type=int, default=1024)
+    ap.add_argument("--min-kb", type=int, default=1)
+    ap.add_argument("--dtypes", default="fp32,bf16")
+    ap.add_argument("--ops", default="allreduce,allgather,broadcast")
+    ap.add_argument("--out", default="")
+    a = ap.parse_args(argv)
+    tips.init()
+    import torch.distributed as dist
+    rank, n = tips.rank(), tips.size()
+    assert n > 1, "the sweep needs at least 2 GPUs"
+    st = tips.runtime.device_state()
+    lib = _lib.kernels()
+    dev = st.device
+    stream = torch.cuda.current_stream().cuda_stream
+    dts = {"fp32": (torch.float32, 0), "bf16": (torch.bfloat16, 6)}
+    rows = []
+    max_bytes = a.max_mb << 20
+    sym, sym_off = st.alloc_symmetric(max_bytes)
+    size = a.min_kb << 10
+    sizes = []
+    while size <= max_bytes:
+        sizes.append(size)
+        size *= 2
+    for name in a.dtypes.split(","):
+        dtype, code = dts[name]
+        es = torch.empty((), dtype=dtype).element_size()
+        for nbytes in sizes:
+            numel = nbytes // es
+            iters = 50 if nbytes <= (1 << 20) else 20 if nbytes <= (64 << 20) else 5
+            x = torch.randn(numel, device=dev).to(dtype)
+            y = torch.empty_like(x)
+            res = {"dtype": name, "bytes": nbytes, "ranks": n}
+            if "allreduce" in a.ops:
+                srcs = (ctypes.c_void_p * 1)(x.data_ptr())
+                dsts = (ctypes.c_void_p * 1)(y.data_ptr())
+                ms = _time(lambda: lib.tipsk_allreduce(srcs, dsts, -1, nbytes, code, 0, 1.0, 1.0, 3, stream), iters)
+                res["allreduce_staged_ms"] = ms
+                ms = _time(lambda: lib.tipsk_allreduce(None, None, sym_off, nbytes, code, 0, 1.0, 1.0 / n, 3, stream), iters)
+                res["allreduce_inplace_ms"] = ms
+                res["allreduce_inplace_busbw"] = nbytes / ms / 1e6 * 2 * (n - 1) / n
+                ms = _time(lambda: dist.all_reduce(x), iters)
+                res["nccl_allreduce_ms"] = ms
+                res["nccl_allreduce_busbw"] = nbytes / ms / 1e6 * 2 * (n - 1) / n
+                res["allreduce_roofline_frac"] = (nbytes * (n - 1) / n / (LINK_GBS * 1e6)) / res["allreduce_inplace_ms"]
+            if "allgather" in a.ops and nbytes * n <= (2 << 30):
+                out = torch.empty(numel * n, dtype=dtype, device=dev)
+                per = (ctypes.c_uint64 * n)(*([nbytes] * n))
+                srcs = (ctypes.c_void_p * 1)(x.data_ptr())
+                dsts = (ctypes.c_void_p * 1)(out.data_ptr())
+                ms = _time(lambda: lib.tipsk_allgatherv(srcs, dsts, per, 3, stream), iters)
+                res["allgather_ms"] = ms
+                res["allgather_busbw"] = nbytes * n / ms / 1e6 * (n - 1) / n
+                ms = _time(lambda: dist.all_gather_into_tensor(out, x), iters)
+                res["nccl_allgather_busbw"] = nbytes * n / ms / 1e6 * (n - 1) / n
+                del out
+            if "broadcast" in a.ops:
+                srcs = (ctypes.c_void_p * 1)(x.data_ptr())
+                dsts = (ctypes.c_void_p * 1)(y.data_ptr())
+                ms = _time(lambda: lib.tipsk_broadcast(srcs, dsts, nbytes, 0, 3, stream), iters)
+                res["broadcast_ms"] = ms
+                res["broadcast_gbs"] = nbytes / ms / 1e6
+                ms = _time(lambda: dist.broadcast(x, 0), iters)
+                res["nccl_broadcast_gbs"] = nbytes / ms / 1e6
+            st.check_status()
+            rows.append(res)
+            if rank == 0:
+                print(json.dumps(res), flush=True)
+            del x, y
+    if rank == 0 and a.out:
+        with open(a.out, "w") as f:
+            json.dump({"ranks": n, "uses_multimem": bool(lib.tipsk_comm_uses_multimem()), "rows": rows}, f, indent=1)
+    tips.shutdown()
+
+
+if __name__ == "__main__":
+    main(sys.argv[1:])

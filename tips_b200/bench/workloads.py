@@ -121,6 +121,48 @@ def run_resnet50(batch: int, steps: int, warmup: int):
     return {"value": value, "ms_per_step": ms / steps, "gpu_launches": launches, "e2e": e2e}
 
 
+def run_resnet50_floor(batch: int, steps: int, warmup: int):
+    """Library floor: cuDNN batch norm, torch SGD (foreach), torch cross-entropy, NCCL DistributedDataParallel."""
+    import torch.distributed as dist
+    from tips_b200.models.resnet50 import resnet50
+    dev = torch.device("cuda", torch.cuda.current_device())
+    torch.manual_seed(1234)
+    model = resnet50(device=dev, library_norm=True).train()
+    if tips.size() > 1:
+        model = torch.nn.parallel.DistributedDataParallel(model, device_ids=[dev.index], bucket_cap_mb=64,
+                                                          gradient_as_bucket_view=True)
+    opt = torch.optim.SGD(model.parameters(), lr=0.1, momentum=0.9, weight_decay=1e-4)
+    g = torch.Generator().manual_seed(100 + tips.rank())
+    x = torch.randn(batch, 3, 224, 224, generator=g).to(torch.bfloat16).contiguous(memory_format=torch.channels_last)
+    y = torch.randint(0, 1000, (batch,), generator=g)
+    host = [(x.pin_memory(), y.pin_memory())] * 3
+    x_dev, y_dev = x.to(dev), y.to(dev)
+
+    def step_resident():
+        loss = torch.nn.functional.cross_entropy(model(x_dev).float(), y_dev)
+        loss.backward()
+        opt.step()
+        opt.zero_grad(set_to_none=True)
+        return loss
+
+    ms, _ = timed(step_resident, steps, warmup)
+    pre = _Prefetcher(host)
+    last = {}
+
+    def step_e2e():
+        xb, yb = pre.get()
+        loss = torch.nn.functional.cross_entropy(model(xb).float(), yb)
+        loss.backward()
+        opt.step()
+        opt.zero_grad(set_to_none=True)
+        last["loss"] = loss.item()
+
+    ms2, _ = timed(step_e2e, steps, max(3, warmup // 2))
+    e2e = {"value": batch * tips.size() * steps / (ms2 / 1e3), "unit": "images/s", "ms_per_step": ms2 / steps,
+           "h2d_bytes_per_step": pre.bytes_per_step, "d2h_bytes_per_step": 4, "last_loss": last.get("loss")}
+    return {"value": batch * tips.size() * steps / (ms / 1e3), "ms_per_step": ms / steps, "gpu_launches": 0, "e2e": e2e}
+
+
 def run_ctr(batch: int, rows: int, steps: int, warmup: int):
     from tips_b200.models.ctr import CtrTrainer, synthetic_ctr_batch
     dev = torch.device("cuda", torch.cuda.current_device())

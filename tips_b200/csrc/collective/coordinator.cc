@@ -207,11 +207,8 @@ void CollectiveEngine::Finalize() {
   {
     std::lock_guard<std::mutex> lock(mu_);
     tensor_table_.clear();
-    schedule_.clear();
+    schedules_.clear();
     schedule_index_.clear();
-    schedule_sig_.clear();
-    schedule_ready_.clear();
-    schedule_cursor_ = 0;
   }
   frozen_      = false;
   initialized_ = false;
@@ -239,7 +236,8 @@ int64_t CollectiveEngine::Enqueue(OpRecord record, std::string* error) {
     if (frozen_.load()) {
       auto it = schedule_index_.find(record.name);
       if (it != schedule_index_.end()) {
-        const Signature& s = schedule_sig_[it->second];
+        Schedule& sched    = schedules_[it->second.first];
+        const Signature& s = sched.sigs[it->second.second];
         std::vector<int64_t> shape = record.shape.empty() ? std::vector<int64_t>{1} : record.shape;
         if (s.type != record.type || s.dtype != record.dtype || s.shape != shape || s.device != record.device ||
             s.reduce_op != static_cast<int32_t>(record.reduce_op) || s.root_rank != record.root_rank) {
@@ -247,7 +245,7 @@ int64_t CollectiveEngine::Enqueue(OpRecord record, std::string* error) {
         } else {
           frozen_hit = true;
           tensor_table_[record.name]    = record;
-          schedule_ready_[it->second] = true;
+          sched.ready[it->second.second] = true;
         }
       }
     }
@@ -327,7 +325,7 @@ void CollectiveEngine::FailAll(const Status& st) {
     std::lock_guard<std::mutex> lock(mu_);
     for (auto& kv : tensor_table_) recs.push_back(kv.second);
     tensor_table_.clear();
-    std::fill(schedule_ready_.begin(), schedule_ready_.end(), false);
+    for (Schedule& sched : schedules_) std::fill(sched.ready.begin(), sched.ready.end(), false);
   }
   for (auto& r : recs) Complete(r, st);
 }

@@ -221,12 +221,17 @@ class CollectiveEngine {
   std::unordered_map<std::string, Signature> negotiated_;  // name -> last validated signature
   std::vector<std::string> order_log_;
 
+  // Frozen schedules: each FreezeSchedule call adds one cyclic sequence with its own cursor
+  // (one per DistributedOptimizer).
+  struct Schedule {
+    std::vector<std::string> names;
+    std::vector<Signature> sigs;
+    std::vector<bool> ready;
+    size_t cursor{0};
+  };
   std::atomic<bool> frozen_{false};
-  std::vector<std::string> schedule_;
-  std::unordered_map<std::string, size_t> schedule_index_;
-  std::vector<Signature> schedule_sig_;
-  std::vector<bool> schedule_ready_;
-  size_t schedule_cursor_{0};
+  std::vector<Schedule> schedules_;
+  std::unordered_map<std::string, std::pair<size_t, size_t>> schedule_index_;  // name -> (schedule, position)
 
   std::vector<uint8_t> fusion_buffer_;
   EngineCounters counters_;

@@ -342,36 +342,35 @@ Status CollectiveEngine::ExecuteFusedHost(std::vector<OpRecord*>& recs) {
 Status CollectiveEngine::FreezeSchedule(const std::vector<std::string>& names) {
   std::lock_guard<std::mutex> lock(mu_);
   if (names.empty()) return Status(kInvalidArgument, "empty schedule");
-  std::vector<Signature> sigs;
-  std::unordered_map<std::string, size_t> index;
+  Schedule sched;
+  std::unordered_map<std::string, size_t> seen;
   for (size_t i = 0; i < names.size(); ++i) {
     auto it = negotiated_.find(names[i]);
     if (it == negotiated_.end())
       return Status(kPrecondition, "'" + names[i] + "' has not been negotiated yet; run one step first");
     if (it->second.type == RequestType::kAllgather)
       return Status(kInvalidArgument, "allgather '" + names[i] + "' cannot be frozen: its sizes may change");
-    if (index.count(names[i])) return Status(kInvalidArgument, "'" + names[i] + "' appears twice in the schedule");
+    if (seen.count(names[i])) return Status(kInvalidArgument, "'" + names[i] + "' appears twice in the schedule");
+    if (schedule_index_.count(names[i]))
+      return Status(kInvalidArgument, "'" + names[i] + "' already belongs to a frozen schedule");
     if (tensor_table_.count(names[i])) return Status(kPrecondition, "'" + names[i] + "' is still in flight");
-    index[names[i]] = i;
-    sigs.push_back(it->second);
+    seen[names[i]] = i;
+    sched.sigs.push_back(it->second);
   }
-  schedule_        = names;
-  schedule_index_  = std::move(index);
-  schedule_sig_    = std::move(sigs);
-  schedule_ready_.assign(names.size(), false);
-  schedule_cursor_ = 0;
-  frozen_          = true;
+  sched.names = names;
+  sched.ready.assign(names.size(), false);
+  const size_t sid = schedules_.size();
+  for (size_t i = 0; i < names.size(); ++i) schedule_index_[names[i]] = {sid, i};
+  schedules_.push_back(std::move(sched));
+  frozen_ = true;
   return Status::OK();
 }
 
 void CollectiveEngine::ThawSchedule() {
   std::lock_guard<std::mutex> lock(mu_);
   frozen_ = false;
-  schedule_.clear();
+  schedules_.clear();
   schedule_index_.clear();
-  schedule_sig_.clear();
-  schedule_ready_.clear();
-  schedule_cursor_ = 0;
 }
 
 std::vector<std::string> CollectiveEngine::TakeNegotiatedOrder() {
@@ -382,35 +381,49 @@ std::vector<std::string> CollectiveEngine::TakeNegotiatedOrder() {
 }
 
 void CollectiveEngine::DrainFrozen() {
-  while (true) {
-    OpRecord rec;
+  // Execute, for every schedule, the entries at its cursor for as long as they are ready.
+  bool progress = true;
+  while (progress) {
+    progress = false;
+    size_t nsched;
     {
       std::lock_guard<std::mutex> lock(mu_);
-      if (!frozen_.load() || schedule_.empty() || !schedule_ready_[schedule_cursor_]) return;
-      auto it = tensor_table_.find(schedule_[schedule_cursor_]);
-      if (it == tensor_table_.end()) {
-        schedule_ready_[schedule_cursor_] = false;
-        return;
-      }
-      rec = it->second;
+      nsched = schedules_.size();
     }
-    ResponseMessage resp;
-    resp.response_type = static_cast<ResponseType>(static_cast<int16_t>(rec.type));
-    resp.tensor_names  = {rec.name};
-    resp.root_rank     = rec.root_rank;
-    const int64_t t0   = NowMicros();
-    Status st          = ExecuteOne(&rec, resp, 1);
-    Trace(rec.name, "EXECUTE", t0, NowMicros());
-    {
-      std::lock_guard<std::mutex> lock(mu_);
-      tensor_table_.erase(rec.name);
-      if (!schedule_ready_.empty()) {
-        schedule_ready_[schedule_cursor_] = false;
-        schedule_cursor_                  = (schedule_cursor_ + 1) % schedule_.size();
+    for (size_t sid = 0; sid < nsched; ++sid) {
+      OpRecord rec;
+      {
+        std::lock_guard<std::mutex> lock(mu_);
+        if (!frozen_.load() || sid >= schedules_.size()) return;
+        Schedule& sched = schedules_[sid];
+        if (sched.names.empty() || !sched.ready[sched.cursor]) continue;
+        auto it = tensor_table_.find(sched.names[sched.cursor]);
+        if (it == tensor_table_.end()) {
+          sched.ready[sched.cursor] = false;
+          continue;
+        }
+        rec = it->second;
       }
+      ResponseMessage resp;
+      resp.response_type = static_cast<ResponseType>(static_cast<int16_t>(rec.type));
+      resp.tensor_names  = {rec.name};
+      resp.root_rank     = rec.root_rank;
+      const int64_t t0   = NowMicros();
+      Status st          = ExecuteOne(&rec, resp, 1);
+      Trace(rec.name, "EXECUTE", t0, NowMicros());
+      {
+        std::lock_guard<std::mutex> lock(mu_);
+        tensor_table_.erase(rec.name);
+        if (sid < schedules_.size()) {
+          Schedule& sched = schedules_[sid];
+          sched.ready[sched.cursor] = false;
+          sched.cursor              = (sched.cursor + 1) % sched.names.size();
+        }
+      }
+      counters_.frozen_executions++;
+      Complete(rec, st);
+      progress = true;
     }
-    counters_.frozen_executions++;
-    Complete(rec, st);
   }
 }
 

@@ -15,6 +15,26 @@ from ..ops.norm import BatchNorm2d
 from ..ops.pointwise import softmax_cross_entropy
 
 
+class LibraryBatchNorm2d(nn.Module):
+    """Same call signature as the fused BatchNorm2d, built from library ops (cuDNN batch norm, separate add
+    and ReLU kernels).  Used only by the library-floor benchmark arm."""
+
+    def __init__(self, num_features, relu=False):
+        super().__init__()
+        self.bn = nn.BatchNorm2d(num_features)
+        self.relu = relu
+        self.weight = self.bn.weight
+
+    def forward(self, x, residual=None):
+        y = self.bn(x)
+        if residual is not None:
+            y = y + residual
+        return torch.relu(y) if self.relu else y
+
+
+_NORM = BatchNorm2d
+
+
 def _conv(cin, cout, k, stride=1, padding=0):
     return nn.Conv2d(cin, cout, k, stride=stride, padding=padding, bias=False)
 
@@ -26,17 +46,17 @@ class Bottleneck(nn.Module):
         super().__init__()
         cout = width * self.expansion
         self.conv1 = _conv(cin, width, 1)
-        self.bn1 = BatchNorm2d(width, relu=True)
+        self.bn1 = _NORM(width, relu=True)
         self.conv2 = _conv(width, width, 3, stride=stride, padding=1)  # v1.5: the stride sits on the 3x3
-        self.bn2 = BatchNorm2d(width, relu=True)
+        self.bn2 = _NORM(width, relu=True)
         self.conv3 = _conv(width, cout, 1)
-        self.bn3 = BatchNorm2d(cout, relu=True)  # ReLU after the residual add, fused
+        self.bn3 = _NORM(cout, relu=True)  # ReLU after the residual add, fused
         nn.init.zeros_(self.bn3.weight)
         self.down = None
         if downsample:
             self.down = nn.Sequential()
             self.down.add_module("conv", _conv(cin, cout, 1, stride=stride))
-            self.down.add_module("bn", BatchNorm2d(cout, relu=False))
+            self.down.add_module("bn", _NORM(cout, relu=False))
 
     def forward(self, x):
         identity = x if self.down is None else self.down(x)
@@ -49,7 +69,7 @@ class ResNet50(nn.Module):
     def __init__(self, num_classes=1000, layers=(3, 4, 6, 3), width=64):
         super().__init__()
         self.conv1 = _conv(3, width, 7, stride=2, padding=3)
-        self.bn1 = BatchNorm2d(width, relu=True)
+        self.bn1 = _NORM(width, relu=True)
         self.maxpool = nn.MaxPool2d(3, stride=2, padding=1)
         blocks = []
         cin = width
@@ -76,8 +96,13 @@ class ResNet50(nn.Module):
         return softmax_cross_entropy(self.forward(images), labels)
 
 
-def resnet50(num_classes=1000, dtype=torch.bfloat16, device="cuda"):
-    m = ResNet50(num_classes)
+def resnet50(num_classes=1000, dtype=torch.bfloat16, device="cuda", library_norm=False):
+    global _NORM
+    _NORM = LibraryBatchNorm2d if library_norm else BatchNorm2d
+    try:
+        m = ResNet50(num_classes)
+    finally:
+        _NORM = BatchNorm2d
     m = m.to(device=device, dtype=dtype)
     if torch.device(device).type == "cuda":
         m = m.to(memory_format=torch.channels_last)

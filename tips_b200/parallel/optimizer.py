@@ -30,6 +30,9 @@ from .buckets import build_buckets
 from .compression import Compression
 
 
+_optimizer_counter = 0
+
+
 class _DistributedMixin:
     """Behaviour mixed into a dynamic subclass of the user's optimizer class."""
 
@@ -93,6 +96,14 @@ class _DistributedMixin:
                     b.index = len(self._tips_buckets)
                     b.name = f"tips.bucket.{b.index}"
                     self._tips_buckets.append(b)
+        # Bucket names are the negotiation keys: unique per optimizer instance, identical across ranks as
+        # long as every rank creates its optimizers in the same order.
+        global _optimizer_counter
+        prefix = f"tips.opt{_optimizer_counter}"
+        _optimizer_counter += 1
+        for i, b in enumerate(self._tips_buckets):
+            b.index = i
+            b.name = f"{prefix}.bucket.{i}"
         self._tips_bucket_of = {}
         for b in self._tips_buckets:
             b.pending = len(b.params)

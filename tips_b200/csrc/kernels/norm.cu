@@ -380,3 +380,53 @@ int tipsk_bn_bwd(const void* dy, const void* x, const void* y, const float* gamm
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------------------------
+// Batch-norm forward for callers that cannot allocate: the partial-sum scratch is a fixed array in
+// the device image of this library.  See kernels/tips_noalloc.h for the contract.
+#include <mutex>
+
+#include "kernels/tips_noalloc.h"
+
+namespace {
+
+static __device__ __align__(256) float g_bn_noalloc_scratch[TIPSK_BN_NOALLOC_SCRATCH_FLOATS];
+
+constexpr int kNoAllocMaxDevices = 64;
+float* g_bn_noalloc_ptr[kNoAllocMaxDevices] = {nullptr};
+std::mutex g_bn_noalloc_mu;
+
+// Device address of the scratch array on the current device.  In host code the array's name is only a
+// stand-in for the symbol; the address a kernel can use comes from cudaGetSymbolAddress.
+int BnNoAllocScratch(float** out) {
+  int dev = 0;
+  TIPSK_CUDA(cudaGetDevice(&dev));
+  TIPSK_REQUIRE(dev >= 0 && dev < kNoAllocMaxDevices, "bn_noalloc: device index out of range");
+  std::lock_guard<std::mutex> lock(g_bn_noalloc_mu);
+  if (!g_bn_noalloc_ptr[dev]) {
+    float* ptr = nullptr;
+    TIPSK_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_bn_noalloc_scratch));
+    TIPSK_REQUIRE(ptr != nullptr, "bn_noalloc: the scratch symbol has no device address");
+    g_bn_noalloc_ptr[dev] = ptr;
+  }
+  *out = g_bn_noalloc_ptr[dev];
+  return 0;
+}
+
+}  // namespace
+
+extern "C" int tipsk_bn_fwd_train_noalloc(const void* x, const void* residual, void* y, const float* gamma,
+                                          const float* beta, float* running_mean, float* running_var,
+                                          float* save_mean, float* save_invstd, int64_t m, int c, float eps,
+                                          float momentum, int relu, int dtype, void* stream) {
+  TIPSK_REQUIRE(m > 0 && c > 0, "bn_noalloc: empty input");
+  const int64_t need = 2ll * c * tipsk_bn_partials(m, c);
+  if (need > TIPSK_BN_NOALLOC_SCRATCH_FLOATS)
+    return SetError(-2, "bn_noalloc: needs " + std::to_string(need) + " scratch floats, the built-in array holds " +
+                            std::to_string(TIPSK_BN_NOALLOC_SCRATCH_FLOATS) + "; use tipsk_bn_fwd_train with a workspace");
+  float* scratch = nullptr;
+  int rc = BnNoAllocScratch(&scratch);
+  if (rc) return rc;
+  return tipsk_bn_fwd_train(x, residual, y, gamma, beta, running_mean, running_var, save_mean, save_invstd, scratch, m,
+                            c, eps, momentum, relu, dtype, stream);
+}

@@ -1,0 +1,33 @@
+"""Host parameter server with arbitrary 64-bit keys (the reference's PsServer / PsClient path):
+ranks 0..servers-1 serve shards, every rank pulls and pushes.
+
+    python -m torch.distributed.run --nproc-per-node 3 examples/host_ps.py
+"""
+import os
+import sys
+
+import numpy as np
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+import tips_b200 as tips  # noqa: E402
+from tips_b200.ps.host import HostSparseTable, Route  # noqa: E402
+
+
+def main():
+    tips.init(device=False)
+    servers = list(range(max(1, tips.size() // 2)))
+    table = HostSparseTable("demo", dim=8, route=Route(servers=servers), optimizer="adagrad", lr=0.1)
+    rng = np.random.default_rng(tips.rank())
+    for step in range(5):
+        keys = rng.integers(0, 1000, size=64).astype(np.uint64)
+        rows = table.pull(keys)
+        grads = rows * 0.1 + 1.0
+        table.push(keys, grads)
+        tips.barrier()
+    print(f"rank {tips.rank()}: local rows {table.local_size()} counters {table.counters()}")
+    table.close()
+    tips.shutdown()
+
+
+if __name__ == "__main__":
+    main()

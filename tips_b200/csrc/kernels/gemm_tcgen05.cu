@@ -120,11 +120,14 @@ struct GemmParams {
   int m, n, k;
   int ldc;
   int act;                     // 0 none, 1 relu, 2 gelu
+  int tma_store;               // 1: the output goes through shared memory and the TMA store unit
 };
 
 template <int BN>
 struct GemmCfg {
-  static constexpr int kStages     = BN >= 256 ? 4 : 5;
+  // Up to 128 columns: three stages (<= 97 KB) so that two CTAs fit on an SM and one CTA's epilogue
+  // overlaps the other's main loop; 256 columns: one CTA per SM with four stages.
+  static constexpr int kStages     = BN >= 256 ? 4 : 3;
   static constexpr int kABytes     = kBM * kBK * 2;
   static constexpr int kBBytes     = BN * kBK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
@@ -134,7 +137,8 @@ struct GemmCfg {
 
 template <int BN>
 __global__ void __launch_bounds__(kGemmThreads, 1)
-GemmTnKernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, GemmParams p) {
+GemmTnKernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+             const __grid_constant__ CUtensorMap tmap_c, GemmParams p) {
   using Cfg = GemmCfg<BN>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -217,7 +221,53 @@ GemmTnKernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
     if (!ok && lane == 0) atomicExch(p.error, 3);
     TcFenceAfter();
     const int row = m0 + q * 32 + lane;
-    if (ok) {
+    if (p.tma_store) {
+      if (ok) {
+      // Coalesced path: convert in registers, stage the tile in shared memory in the 128-byte-swizzled
+      // layout of the output tensor map (the pipeline stages are free once every MMA has completed),
+      // then one thread hands 64-column boxes to the TMA store unit.  Rows / columns beyond M / N are
+      // clipped by the TMA unit.
+      const int r = q * 32 + lane;  // row inside the tile
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t acc[32];
+        TmemLoad32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(c * 32), acc);
+        const int col0 = n0 + c * 32;
+        uint8_t* box   = smem + (c >> 1) * (kBM * 128);
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          alignas(16) __nv_bfloat16 o[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            float x = __uint_as_float(acc[g * 8 + j]);
+            const int col = col0 + g * 8 + j;
+            if (p.bias && col < p.n) x += __bfloat162float(p.bias[col]);
+            if (p.act == 1) x = fmaxf(x, 0.f);
+            else if (p.act == 2) x = 0.5f * x * (1.f + erff(x * 0.70710678118654752f));
+            o[j] = __float2bfloat16_rn(x);
+          }
+          const int chunk = (c & 1) * 4 + g;  // 16-byte chunk inside the 128-byte row
+          *reinterpret_cast<uint4*>(box + r * 128 + ((chunk ^ (r & 7)) << 4)) = *reinterpret_cast<uint4*>(o);
+        }
+      }
+      }
+      // every epilogue warp reaches this barrier, whether or not its wait succeeded
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      asm volatile("bar.sync 1, 128;" ::: "memory");  // the four epilogue warps
+      if (ok && warp == 2 && lane == 0) {
+#pragma unroll 1
+        for (int b = 0; b < BN / 64; ++b) {
+          if (n0 + b * 64 < p.n) {
+            asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];" ::"l"(
+                             reinterpret_cast<uint64_t>(&tmap_c)),
+                         "r"(n0 + b * 64), "r"(m0), "r"(SmemAddr(smem + b * (kBM * 128)))
+                         : "memory");
+          }
+        }
+        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+      }
+    } else if (ok) {
 #pragma unroll 1
       for (int c = 0; c < BN / 32 + (BN % 32 ? 1 : 0); ++c) {
         uint32_t r[32];
@@ -322,15 +372,18 @@ int32_t* GemmErrorWord() {
 }
 
 template <int BN>
-int LaunchGemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, cudaStream_t s) {
+int LaunchGemm(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const GemmParams& p,
+               cudaStream_t s) {
   using Cfg = GemmCfg<BN>;
   static bool configured = false;
   if (!configured) {
     TIPSK_CUDA(cudaFuncSetAttribute(GemmTnKernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
+    TIPSK_CUDA(cudaFuncSetAttribute(GemmTnKernel<BN>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                    cudaSharedmemCarveoutMaxShared));
     configured = true;
   }
   dim3 grid((p.n + BN - 1) / BN, (p.m + kBM - 1) / kBM);
-  GemmTnKernel<BN><<<grid, kGemmThreads, Cfg::kSmemBytes, s>>>(ta, tb, p);
+  GemmTnKernel<BN><<<grid, kGemmThreads, Cfg::kSmemBytes, s>>>(ta, tb, tc, p);
   TIPSK_LAUNCH_CHECK();
   return 0;
 }
@@ -369,13 +422,20 @@ int tipsk_gemm_bf16(const void* a, const void* b, void* c, const void* bias, voi
   p.error = GemmErrorWord();
   TIPSK_REQUIRE(p.error != nullptr, "gemm: cannot allocate the error word");
   p.m = m; p.n = n; p.k = k; p.ldc = ldc; p.act = act;
+  // The coalesced store path needs 64-column boxes and a 16-byte aligned, 16-byte strided output.
+  p.tma_store = (bn >= 64 && pre == nullptr && ldc % 8 == 0 && reinterpret_cast<uintptr_t>(c) % 16 == 0) ? 1 : 0;
+  CUtensorMap tc = ta;
+  if (p.tma_store) {
+    rc = MakeTmap(&tc, c, m, n, ldc, kBM);
+    if (rc) return rc;
+  }
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   switch (bn) {
-    case 16: return LaunchGemm<16>(ta, tb, p, s);
-    case 32: return LaunchGemm<32>(ta, tb, p, s);
-    case 64: return LaunchGemm<64>(ta, tb, p, s);
-    case 256: return LaunchGemm<256>(ta, tb, p, s);
-    default: return LaunchGemm<128>(ta, tb, p, s);
+    case 16: return LaunchGemm<16>(ta, tb, tc, p, s);
+    case 32: return LaunchGemm<32>(ta, tb, tc, p, s);
+    case 64: return LaunchGemm<64>(ta, tb, tc, p, s);
+    case 256: return LaunchGemm<256>(ta, tb, tc, p, s);
+    default: return LaunchGemm<128>(ta, tb, tc, p, s);
   }
 }
 

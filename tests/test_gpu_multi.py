@@ -23,3 +23,18 @@ def _run(worker, nproc, env=None, timeout=600):
 def test_collectives_two_gpus(multimem):
     r = _run("collectives_worker.py", 2, env={"TIPS_DISABLE_MULTIMEM": "0" if multimem == "1" else "1"})
     assert r.returncode == 0 and "MULTI_GPU_OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs at least 2 GPUs")
+def test_parameter_server_two_gpus():
+    r = _run("ps_worker.py", 2)
+    assert r.returncode == 0 and "MULTI_GPU_PS_OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 4, reason="needs at least 4 GPUs")
+def test_collectives_and_ps_all_gpus():
+    n = torch.cuda.device_count()
+    r = _run("collectives_worker.py", n)
+    assert r.returncode == 0 and "MULTI_GPU_OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
+    r = _run("ps_worker.py", n)
+    assert r.returncode == 0 and "MULTI_GPU_PS_OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]

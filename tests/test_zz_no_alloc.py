@@ -74,8 +74,8 @@ def test_noalloc_rejects_oversized_problem():
     The buffers are real and correctly sized, so even a library that failed to refuse would stay in bounds."""
     lib = _load()
     dev = torch.device("cuda", 0)
-    c, m = 50432, 128      # 197 column tiles -> 4 partial rows -> 403456 scratch floats > 393216
-    assert 2 * c * lib.tipsk_bn_partials(m, c) > 384 * 1024
+    c, m = 50432, 256      # 197 column tiles -> 7 partial rows + 1 -> 806912 scratch floats > 786432
+    assert 2 * c * lib.tipsk_bn_partials(m, c) > 768 * 1024
     x = torch.randn(m, c, device=dev).to(torch.bfloat16)
     y = torch.empty_like(x)
     gamma, beta = torch.ones(c, device=dev), torch.zeros(c, device=dev)

@@ -48,11 +48,11 @@ BnGeom BnGeometry(int64_t m, int c, int v) {
   while (g.tx * 2 <= vec_cols && g.tx < 32 && vec_cols % (g.tx * 2) == 0) g.tx *= 2;
   g.ty        = 256 / g.tx;
   g.col_tiles = vec_cols / g.tx;
-  int64_t want = (static_cast<int64_t>(NumSMs()) * 4 + g.col_tiles - 1) / g.col_tiles;
+  int64_t want = (static_cast<int64_t>(NumSMs()) * 8 + g.col_tiles - 1) / g.col_tiles;
   int64_t maxp = (m + g.ty * 4 - 1) / (g.ty * 4);
   if (want > maxp) want = maxp;
   if (want < 1) want = 1;
-  if (want > 512) want = 512;
+  if (want > 1024) want = 1024;
   g.partials = static_cast<int>(want);
   return g;
 }
@@ -79,6 +79,7 @@ BnReduceKernel(const T* __restrict__ a, const T* __restrict__ x, const T* __rest
       is[i] = invstd[col + i];
     }
   }
+#pragma unroll 4
   for (int64_t r = static_cast<int64_t>(blockIdx.y) * TY + ty; r < m; r += static_cast<int64_t>(gridDim.y) * TY) {
     float av[V];
     LoadV<T, V>(a + r * c + col, av);
@@ -137,38 +138,31 @@ BnReduceKernel(const T* __restrict__ a, const T* __restrict__ x, const T* __rest
 template <int V>
 __device__ __forceinline__ void BlockCombine(const float* __restrict__ ws, int partials, int c, int col, float* smem,
                                              float (&s0)[V], float (&s1)[V]) {
-  const int tx = threadIdx.x, ty = threadIdx.y;
-  const int TX = blockDim.x, TY = blockDim.y;
-#pragma unroll
-  for (int i = 0; i < V; ++i) s0[i] = s1[i] = 0.f;
-  for (int p = ty; p < partials; p += TY) {
-    const float* row = ws + static_cast<int64_t>(p) * 2 * c;
-#pragma unroll
-    for (int i = 0; i < V; ++i) {
-      s0[i] += row[col + i];
-      s1[i] += row[c + col + i];
-    }
-  }
-  float* mine = smem + (ty * TX + tx) * 2 * V;
+  // The partial rows were summed by BnFinalizeKernel into the row after the last partial row.
+  (void)smem;
+  const float* total = ws + static_cast<int64_t>(partials) * 2 * c;
 #pragma unroll
   for (int i = 0; i < V; ++i) {
-    mine[i]     = s0[i];
-    mine[V + i] = s1[i];
+    s0[i] = total[col + i];
+    s1[i] = total[c + col + i];
   }
+}
+
+// Sums the partial rows column-wise into row `partials` of the workspace. Block (32, 8): tx = column,
+// ty = lane over the partial rows; consecutive threads read consecutive floats.
+__global__ void __launch_bounds__(256) BnFinalizeKernel(float* __restrict__ ws, int partials, int c) {
+  __shared__ float red[8][32];
+  const int col = blockIdx.x * 32 + threadIdx.x;  // 0 .. 2c-1 (sums and second sums side by side)
+  float acc = 0.f;
+  if (col < 2 * c)
+    for (int p = threadIdx.y; p < partials; p += 8) acc += ws[static_cast<int64_t>(p) * 2 * c + col];
+  red[threadIdx.y][threadIdx.x] = acc;
   __syncthreads();
-  for (int h = TY / 2; h > 0; h >>= 1) {
-    if (ty < h) {
-      float* other = smem + ((ty + h) * TX + tx) * 2 * V;
+  if (threadIdx.y == 0 && col < 2 * c) {
+    float s = 0.f;
 #pragma unroll
-      for (int i = 0; i < 2 * V; ++i) mine[i] += other[i];
-    }
-    __syncthreads();
-  }
-  const float* total = smem + tx * 2 * V;
-#pragma unroll
-  for (int i = 0; i < V; ++i) {
-    s0[i] = total[i];
-    s1[i] = total[V + i];
+    for (int j = 0; j < 8; ++j) s += red[j][threadIdx.x];
+    ws[static_cast<int64_t>(partials) * 2 * c + col] = s;
   }
 }
 
@@ -207,6 +201,7 @@ BnApplyKernel(const T* __restrict__ x, const T* __restrict__ residual, T* __rest
     scale[i] = gamma[col + i] * invstd;
     shift[i] = beta[col + i] - mean * scale[i];
   }
+#pragma unroll 4
   for (int64_t r = static_cast<int64_t>(blockIdx.y) * TY + ty; r < m; r += static_cast<int64_t>(gridDim.y) * TY) {
     float xv[V];
     LoadV<T, V>(x + r * c + col, xv);
@@ -253,6 +248,7 @@ BnBwdApplyKernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __r
     k0[i] = s0 * inv_m;
     k1[i] = s1 * inv_m;
   }
+#pragma unroll 4
   for (int64_t r = static_cast<int64_t>(blockIdx.y) * TY + ty; r < m; r += static_cast<int64_t>(gridDim.y) * TY) {
     float dv[V], xv[V];
     LoadV<T, V>(dy + r * c + col, dv);
@@ -317,7 +313,7 @@ int tipsk_bn_partials(int64_t m, int c) {
       int p = BnGeometry(m, c, v).partials;
       if (p > best) best = p;
     }
-  return best;
+  return best + 1;  // one more row: the column sums of the partial rows
 }
 
 int tipsk_bn_fwd_train(const void* x, const void* residual, void* y, const float* gamma, const float* beta,
@@ -332,6 +328,7 @@ int tipsk_bn_fwd_train(const void* x, const void* residual, void* y, const float
     size_t smem = sizeof(float) * 256 * 2 * V;
     BnReduceKernel<T, V, false><<<grid, block, smem, s>>>(static_cast<const T*>(x), nullptr, nullptr, nullptr, nullptr,
                                                           workspace, m, c, 0);
+    BnFinalizeKernel<<<CeilDiv(2 * c, 32), dim3(32, 8), 0, s>>>(workspace, g.partials, c);
     BnApplyKernel<T, V><<<grid, block, sizeof(float) * 256 * 2 * V, s>>>(static_cast<const T*>(x), static_cast<const T*>(residual),
                                                static_cast<T*>(y), gamma, beta, running_mean, running_var, save_mean,
                                                save_invstd, workspace, g.partials, m, c, eps, momentum, relu, 1);
@@ -370,6 +367,7 @@ int tipsk_bn_bwd(const void* dy, const void* x, const void* y, const float* gamm
     BnReduceKernel<T, V, true><<<grid, block, smem, s>>>(static_cast<const T*>(dy), static_cast<const T*>(x),
                                                          static_cast<const T*>(y), save_mean, save_invstd, workspace, m,
                                                          c, relu);
+    BnFinalizeKernel<<<CeilDiv(2 * c, 32), dim3(32, 8), 0, s>>>(workspace, g.partials, c);
     BnBwdApplyKernel<T, V><<<grid, block, smem, s>>>(static_cast<const T*>(dy), static_cast<const T*>(x),
                                                   static_cast<const T*>(y), gamma, save_mean, save_invstd,
                                                   static_cast<T*>(dx), static_cast<T*>(dresidual), dgamma, dbeta,

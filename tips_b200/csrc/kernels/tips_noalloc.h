@@ -12,7 +12,7 @@
  *
  * tipsk_bn_fwd_train_noalloc is tipsk_bn_fwd_train with that scratch taken from a fixed array that
  * lives inside the library's device image (a file-scope `static __device__` array of
- * TIPSK_BN_NOALLOC_SCRATCH_FLOATS floats, 1.5 MiB, held by every GPU that loads the library until the
+ * TIPSK_BN_NOALLOC_SCRATCH_FLOATS floats, 3 MiB, held by every GPU that loads the library until the
  * process exits).  It calls no cudaMalloc / cudaFree and no allocating library routine.
  *
  *  - Limit: 2 * c * tipsk_bn_partials(m, c) must not exceed TIPSK_BN_NOALLOC_SCRATCH_FLOATS; larger
@@ -31,7 +31,7 @@
 extern "C" {
 #endif
 
-#define TIPSK_BN_NOALLOC_SCRATCH_FLOATS (384 * 1024)
+#define TIPSK_BN_NOALLOC_SCRATCH_FLOATS (768 * 1024)
 
 /* Same arguments and semantics as tipsk_bn_fwd_train, minus the workspace pointer. */
 int tipsk_bn_fwd_train_noalloc(const void* x, const void* residual, void* y, const float* gamma, const float* beta,

@@ -326,6 +326,192 @@ GemmTnKernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
   }
 }
 
+// ---------------------------------------------------------------- persistent variant
+// One CTA per SM walks over the output tiles (tile = blockIdx.x + i * gridDim.x, N fastest).  The
+// accumulator is double-buffered in TMEM, so the epilogue of tile i (TMEM -> registers -> swizzled
+// shared memory -> TMA store) overlaps the TMA loads and MMAs of tile i+1.  Used when there are more
+// tiles than SMs and the output qualifies for the TMA store path.
+template <int BN>
+struct PersistCfg {
+  static constexpr int kStages     = BN >= 256 ? 3 : 5;
+  static constexpr int kABytes     = kBM * kBK * 2;
+  static constexpr int kBBytes     = BN * kBK * 2;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kStagingBytes = kBM * BN * 2;
+  static constexpr int kTmemCols   = 2 * BN;  // two accumulators
+  static constexpr int kSmemBytes  = kStages * kStageBytes + kStagingBytes + 1024 + 256;
+};
+
+__device__ __forceinline__ void MbarArrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(SmemAddr(bar)) : "memory");
+}
+
+template <int BN>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+GemmTnPersistentKernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                       const __grid_constant__ CUtensorMap tmap_c, GemmParams p) {
+  using Cfg = PersistCfg<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem    = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* staging = smem + Cfg::kStages * Cfg::kStageBytes;
+  uint64_t* full_bar   = reinterpret_cast<uint64_t*>(staging + Cfg::kStagingBytes);
+  uint64_t* empty_bar  = full_bar + Cfg::kStages;
+  uint64_t* tmem_full  = empty_bar + Cfg::kStages;  // [2]
+  uint64_t* tmem_empty = tmem_full + 2;             // [2]
+  uint32_t* tmem_slot  = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int num_k   = (p.k + kBK - 1) / kBK;
+  const int tiles_n = (p.n + BN - 1) / BN;
+  const int tiles_m = (p.m + kBM - 1) / kBM;
+  const int num_tiles = tiles_m * tiles_n;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < Cfg::kStages; ++s) {
+      MbarInit(&full_bar[s], 1);
+      MbarInit(&empty_bar[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      MbarInit(&tmem_full[b], 1);
+      MbarInit(&tmem_empty[b], 4);  // one arrival per epilogue warp
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(SmemAddr(tmem_slot)),
+                 "r"(static_cast<uint32_t>(Cfg::kTmemCols))
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  TcFenceBefore();
+  __syncthreads();
+  TcFenceAfter();
+  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
+
+  if (warp == 0) {
+    if (lane == 0) {
+      uint32_t it = 0;  // running k-stage counter over all tiles
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const int m0 = (tile / tiles_n) * kBM, n0 = (tile % tiles_n) * BN;
+        for (int kt = 0; kt < num_k; ++kt, ++it) {
+          const int s = it % Cfg::kStages;
+          if (!MbarWait(&empty_bar[s], ((it / Cfg::kStages) & 1) ^ 1)) {
+            atomicExch(p.error, 1);
+            ok = false;
+            break;
+          }
+          uint8_t* a_dst = smem + s * Cfg::kStageBytes;
+          MbarExpectTx(&full_bar[s], Cfg::kStageBytes);
+          TmaLoad2D(a_dst, &tmap_a, kt * kBK, m0, &full_bar[s]);
+          TmaLoad2D(a_dst + Cfg::kABytes, &tmap_b, kt * kBK, n0, &full_bar[s]);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(BN >> 3) << 17) |
+                                 (static_cast<uint32_t>(kBM >> 4) << 24);
+      uint32_t it = 0;
+      int local = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
+        const int buf = local & 1;
+        if (!MbarWait(&tmem_empty[buf], ((local >> 1) & 1) ^ 1)) {  // the epilogue has drained this accumulator
+          atomicExch(p.error, 4);
+          break;
+        }
+        TcFenceAfter();
+        const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(buf * BN);
+        for (int kt = 0; kt < num_k; ++kt, ++it) {
+          const int s = it % Cfg::kStages;
+          if (!MbarWait(&full_bar[s], (it / Cfg::kStages) & 1)) {
+            atomicExch(p.error, 2);
+            ok = false;
+            break;
+          }
+          TcFenceAfter();
+          const uint32_t a_addr = SmemAddr(smem + s * Cfg::kStageBytes);
+          const uint64_t adesc  = SmemDescSw128(a_addr);
+          const uint64_t bdesc  = SmemDescSw128(a_addr + Cfg::kABytes);
+#pragma unroll
+          for (int k = 0; k < kBK / 16; ++k) UmmaBf16(tmem_d, adesc + 2 * k, bdesc + 2 * k, idesc, (kt > 0 || k > 0) ? 1u : 0u);
+          UmmaCommit(&empty_bar[s]);
+        }
+        if (ok) UmmaCommit(&tmem_full[buf]);
+      }
+    }
+  } else {
+    const int q = warp & 3;
+    const int r = q * 32 + lane;
+    int local = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++local) {
+      const int m0 = (tile / tiles_n) * kBM, n0 = (tile % tiles_n) * BN;
+      const int buf = local & 1;
+      if (ok && !MbarWait(&tmem_full[buf], (local >> 1) & 1)) {
+        if (lane == 0) atomicExch(p.error, 3);
+        ok = false;
+      }
+      TcFenceAfter();
+      if (ok) {
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t acc[32];
+          TmemLoad32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(buf * BN + c * 32), acc);
+          const int col0 = n0 + c * 32;
+          uint8_t* box   = staging + (c >> 1) * (kBM * 128);
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            alignas(16) __nv_bfloat16 o[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              float x = __uint_as_float(acc[g * 8 + j]);
+              const int col = col0 + g * 8 + j;
+              if (p.bias && col < p.n) x += __bfloat162float(p.bias[col]);
+              if (p.act == 1) x = fmaxf(x, 0.f);
+              else if (p.act == 2) x = 0.5f * x * (1.f + erff(x * 0.70710678118654752f));
+              o[j] = __float2bfloat16_rn(x);
+            }
+            const int chunk = (c & 1) * 4 + g;
+            *reinterpret_cast<uint4*>(box + r * 128 + ((chunk ^ (r & 7)) << 4)) = *reinterpret_cast<uint4*>(o);
+          }
+        }
+        // this warp is done with the accumulator: hand it back to the MMA warp
+        TcFenceBefore();
+        __syncwarp();
+        if (lane == 0) MbarArrive(&tmem_empty[buf]);
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (warp == 2 && lane == 0) {
+        if (ok) {
+#pragma unroll 1
+          for (int b = 0; b < BN / 64; ++b) {
+            if (n0 + b * 64 < p.n) {
+              asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];" ::"l"(
+                               reinterpret_cast<uint64_t>(&tmap_c)),
+                           "r"(n0 + b * 64), "r"(m0), "r"(SmemAddr(staging + b * (kBM * 128)))
+                           : "memory");
+            }
+          }
+          asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        }
+        asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");  // staging may be overwritten afterwards
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+    }
+  }
+  TcFenceBefore();
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                 "r"(static_cast<uint32_t>(Cfg::kTmemCols))
+                 : "memory");
+  }
+}
+
 // ------------------------------------------------------------------ host side
 
 using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
@@ -388,6 +574,23 @@ int LaunchGemm(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& 
   return 0;
 }
 
+template <int BN>
+int LaunchGemmPersistent(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const GemmParams& p,
+                         cudaStream_t s) {
+  using Cfg = PersistCfg<BN>;
+  static bool configured = false;
+  if (!configured) {
+    TIPSK_CUDA(cudaFuncSetAttribute(GemmTnPersistentKernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    Cfg::kSmemBytes));
+    configured = true;
+  }
+  const int tiles = ((p.n + BN - 1) / BN) * ((p.m + kBM - 1) / kBM);
+  const int grid  = tiles < NumSMs() ? tiles : NumSMs();
+  GemmTnPersistentKernel<BN><<<grid, kGemmThreads, Cfg::kSmemBytes, s>>>(ta, tb, tc, p);
+  TIPSK_LAUNCH_CHECK();
+  return 0;
+}
+
 }  // namespace
 }  // namespace tipsk
 
@@ -430,6 +633,15 @@ int tipsk_gemm_bf16(const void* a, const void* b, void* c, const void* bias, voi
     if (rc) return rc;
   }
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  // More tiles than SMs and a TMA-storable output: the persistent kernel overlaps epilogue and main loop.
+  static const bool no_persist = getenv("TIPS_GEMM_NO_PERSISTENT") != nullptr;
+  if (!no_persist && p.tma_store && (bn == 128 || bn == 256)) {
+    const int64_t tiles = static_cast<int64_t>((n + bn - 1) / bn) * ((m + kBM - 1) / kBM);
+    if (tiles > NumSMs()) {
+      if (bn == 256) return LaunchGemmPersistent<256>(ta, tb, tc, p, s);
+      return LaunchGemmPersistent<128>(ta, tb, tc, p, s);
+    }
+  }
   switch (bn) {
     case 16: return LaunchGemm<16>(ta, tb, tc, p, s);
     case 32: return LaunchGemm<32>(ta, tb, tc, p, s);

@@ -31,7 +31,7 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="tips", choices=["tips", "reference", "floor"])
-    ap.add_argument("--workload", default="all", choices=["all", "resnet50", "ctr"])
+    ap.add_argument("--workload", default="all", choices=["all", "resnet50", "ctr", "bert"])
     ap.add_argument("--batch", type=int, default=256, help="ResNet-50 images per GPU")
     ap.add_argument("--ctr-batch", type=int, default=8192)
     ap.add_argument("--ctr-rows", type=int, default=10_000_000)
@@ -146,6 +146,14 @@ def main():
         else:
             result.update(ps)
             result["vs_baseline"] = None
+    if args.workload == "bert":
+        b = workloads.run_bert(32, 512, args.steps, args.warmup)
+        launches += b["gpu_launches"]
+        result.update({"metric": "bert_large_mlm_train_tokens_per_sec", "value": b["value"], "unit": "tokens/s",
+                       "ms_per_step": b["ms_per_step"], "vs_baseline": None, "e2e": b["e2e"],
+                       "config": {"model": "BERT-large-shaped encoder (24x1024x16, FFN 4096, vocab 30522)",
+                                  "seq_len": 512, "per_gpu_batch": 32, "global_batch": 32 * size,
+                                  "optimizer": "AdamW", "parallelism": f"dp{size}"}})
     result["gpu_launches"] = launches
     if rank == 0:
         result["clocks"] = sampler.stop()

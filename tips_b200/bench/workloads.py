@@ -191,3 +191,42 @@ def run_ctr(batch: int, rows: int, steps: int, warmup: int):
     e2e = {"value": batch * tips.size() * steps / (ms2 / 1e3), "unit": "samples/s", "ms_per_step": ms2 / steps,
            "h2d_bytes_per_step": pre.bytes_per_step, "d2h_bytes_per_step": 4, "last_loss": last.get("loss")}
     return {"value": value, "ms_per_step": ms / steps, "gpu_launches": launches, "e2e": e2e}
+
+
+def run_bert(batch: int, seq: int, steps: int, warmup: int, layers: int = 24):
+    """BERT-large-shaped MLM training, data-parallel, AdamW (tokens/s)."""
+    from tips_b200.models.bert import bert_large, synthetic_mlm_batch
+    from tips_b200.ops.optim import FusedAdamW
+    dev = torch.device("cuda", torch.cuda.current_device())
+    torch.manual_seed(4321)
+    model = bert_large(device=dev, layers=layers, max_seq=seq).train()
+    opt = tips.DistributedOptimizer(FusedAdamW(model.parameters(), lr=1e-4, weight_decay=0.01))
+    tips.broadcast_parameters(model.state_dict(), root_rank=0)
+    host = [tuple(t.pin_memory() for t in synthetic_mlm_batch(batch, seq, 30522, seed=31 * tips.rank() + i))
+            for i in range(3)]
+    resident = [t.to(dev) for t in host[0]]
+
+    def step_resident():
+        loss = model.loss(*resident)
+        loss.backward()
+        opt.step()
+        return loss
+
+    ms, launches = timed(step_resident, steps, warmup)
+    from tips_b200.ops.linear import gemm_status
+    assert gemm_status() == 0
+    value = batch * seq * tips.size() * steps / (ms / 1e3)
+    pre = _Prefetcher(host)
+    last = {}
+
+    def step_e2e():
+        ids, pos, lab = pre.get()
+        loss = model.loss(ids, pos, lab)
+        loss.backward()
+        opt.step()
+        last["loss"] = loss.item()
+
+    ms2, _ = timed(step_e2e, steps, max(3, warmup // 2))
+    e2e = {"value": batch * seq * tips.size() * steps / (ms2 / 1e3), "unit": "tokens/s", "ms_per_step": ms2 / steps,
+           "h2d_bytes_per_step": pre.bytes_per_step, "d2h_bytes_per_step": 4, "last_loss": last.get("loss")}
+    return {"value": value, "ms_per_step": ms / steps, "gpu_launches": launches, "e2e": e2e}

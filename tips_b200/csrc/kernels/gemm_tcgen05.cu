@@ -637,7 +637,9 @@ int tipsk_gemm_bf16(const void* a, const void* b, void* c, const void* bias, voi
   static const bool no_persist = getenv("TIPS_GEMM_NO_PERSISTENT") != nullptr;
   if (!no_persist && p.tma_store && (bn == 128 || bn == 256)) {
     const int64_t tiles = static_cast<int64_t>((n + bn - 1) / bn) * ((m + kBM - 1) / kBM);
-    if (tiles > NumSMs()) {
+    // Measured on B200: the overlap pays when the epilogue is a visible share of a tile (K <= 2048) and
+    // there are enough tiles to fill several waves; otherwise two independent CTAs per SM do better.
+    if (tiles >= 3 * NumSMs() && k <= 2048) {
       if (bn == 256) return LaunchGemmPersistent<256>(ta, tb, tc, p, s);
       return LaunchGemmPersistent<128>(ta, tb, tc, p, s);
     }

@@ -161,13 +161,10 @@ def setup(emulate_ranks: int = 0) -> DeviceState:
             os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
             os.environ.setdefault("MASTER_PORT", "29400")
             dist.init_process_group("nccl", rank=st.rank, world_size=st.size, device_id=st.device)
+            st.owns_pg = True
         st.pg_ready = True
         total = signal + staging + heap_bytes
         group = dist.group.WORLD
-        try:
-            symm_mem.enable_symm_mem_for_group(group.group_name)
-        except Exception:
-            pass
         win = symm_mem.empty(total, dtype=torch.uint8, device=st.device)
         hdl = symm_mem.rendezvous(win, group.group_name)
         st.window = win
@@ -217,6 +214,8 @@ def teardown(st: DeviceState) -> None:
             if dist.is_initialized():
                 try:
                     dist.barrier()
+                    if getattr(st, "owns_pg", False):
+                        dist.destroy_process_group()
                 except Exception:
                     pass
     finally:

@@ -38,7 +38,8 @@ def main():
         ids, grads = ids_all[rank].to(dev), grads_all[rank].to(dev)
         out = t.pull(ids, dtype=torch.float32)
         ref = torch.cat([ws[f][ids[:, f]] for f in range(fields)], dim=1)
-        assert torch.allclose(out, ref, atol=1e-6), (out - ref).abs().max()
+        # the reference sums the ranks' gradients in a fixed order, the device in arrival order
+        assert torch.allclose(out, ref, atol=3e-4, rtol=1e-4), (step, (out - ref).abs().max())
         t.push(ids, grads, grad_scale=1.0 / n)
         for f in range(fields):
             g = torch.zeros_like(ws[f])

@@ -21,6 +21,14 @@ from tips_b200 import _lib
 LINK_GBS = 770.0
 
 
+def _checked(lib, call):
+    def run():
+        rc = call()
+        if rc != 0:
+            raise RuntimeError("kernel launcher failed: " + lib.tipsk_last_error().decode())
+    return run
+
+
 def _time(fn, iters, warmup=3):
     for _ in range(warmup):
         fn()
@@ -52,7 +60,9 @@ def main(argv=None):
     st = tips.runtime.device_state()
     lib = _lib.kernels()
     dev = st.device
-    stream = torch.cuda.current_stream().cuda_stream
+    work_stream = torch.cuda.Stream()  # a real stream: a null handle would select the library's own
+    torch.cuda.set_stream(work_stream)
+    stream = work_stream.cuda_stream
     dts = {"fp32": (torch.float32, 0), "bf16": (torch.bfloat16, 6)}
     rows = []
     max_bytes = a.max_mb << 20
@@ -74,9 +84,9 @@ def main(argv=None):
             if "allreduce" in a.ops:
                 srcs = (ctypes.c_void_p * 1)(x.data_ptr())
                 dsts = (ctypes.c_void_p * 1)(y.data_ptr())
-                ms = _time(lambda: lib.tipsk_allreduce(srcs, dsts, -1, nbytes, code, 0, 1.0, 1.0, 3, stream), iters)
+                ms = _time(_checked(lib, lambda: lib.tipsk_allreduce(srcs, dsts, -1, nbytes, code, 0, 1.0, 1.0, 3, stream)), iters)
                 res["allreduce_staged_ms"] = ms
-                ms = _time(lambda: lib.tipsk_allreduce(None, None, sym_off, nbytes, code, 0, 1.0, 1.0 / n, 3, stream), iters)
+                ms = _time(_checked(lib, lambda: lib.tipsk_allreduce(None, None, sym_off, nbytes, code, 0, 1.0, 1.0 / n, 3, stream)), iters)
                 res["allreduce_inplace_ms"] = ms
                 res["allreduce_inplace_busbw"] = nbytes / ms / 1e6 * 2 * (n - 1) / n
                 ms = _time(lambda: dist.all_reduce(x), iters)
@@ -88,7 +98,7 @@ def main(argv=None):
                 per = (ctypes.c_uint64 * n)(*([nbytes] * n))
                 srcs = (ctypes.c_void_p * 1)(x.data_ptr())
                 dsts = (ctypes.c_void_p * 1)(out.data_ptr())
-                ms = _time(lambda: lib.tipsk_allgatherv(srcs, dsts, per, 3, stream), iters)
+                ms = _time(_checked(lib, lambda: lib.tipsk_allgatherv(srcs, dsts, per, 3, stream)), iters)
                 res["allgather_ms"] = ms
                 res["allgather_busbw"] = nbytes * n / ms / 1e6 * (n - 1) / n
                 ms = _time(lambda: dist.all_gather_into_tensor(out, x), iters)
@@ -97,7 +107,7 @@ def main(argv=None):
             if "broadcast" in a.ops:
                 srcs = (ctypes.c_void_p * 1)(x.data_ptr())
                 dsts = (ctypes.c_void_p * 1)(y.data_ptr())
-                ms = _time(lambda: lib.tipsk_broadcast(srcs, dsts, nbytes, 0, 3, stream), iters)
+                ms = _time(_checked(lib, lambda: lib.tipsk_broadcast(srcs, dsts, nbytes, 0, 3, stream)), iters)
                 res["broadcast_ms"] = ms
                 res["broadcast_gbs"] = nbytes / ms / 1e6
                 ms = _time(lambda: dist.broadcast(x, 0), iters)

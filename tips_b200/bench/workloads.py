@@ -163,11 +163,11 @@ def run_resnet50_floor(batch: int, steps: int, warmup: int):
     return {"value": batch * tips.size() * steps / (ms / 1e3), "ms_per_step": ms / steps, "gpu_launches": 0, "e2e": e2e}
 
 
-def run_ctr(batch: int, rows: int, steps: int, warmup: int):
+def run_ctr(batch: int, rows: int, steps: int, warmup: int, graph: bool = True):
     from tips_b200.models.ctr import CtrTrainer, synthetic_ctr_batch
     dev = torch.device("cuda", torch.cuda.current_device())
     trainer = CtrTrainer(num_fields=26, rows_per_table=rows, dim=64, dense_features=13, hidden=(512, 256),
-                         device=dev)
+                         device=dev, expected_batch=batch, graph=graph)
     nhost = 3
     host = [tuple(t.pin_memory() for t in synthetic_ctr_batch(batch, 26, rows, 13, seed=7 * tips.rank() + i))
             for i in range(nhost)]

@@ -101,6 +101,7 @@ SgdFlatKernel(float* __restrict__ p32, P16* __restrict__ p16, const G* __restric
 struct AdamParams {
   float lr, beta1, beta2, eps, wd, grad_scale, bias1, bias2;  // bias = 1 - beta^step
   int decoupled;
+  const int64_t* step_dev;  // when set, the step count is read on the device (CUDA-graph replays)
 };
 
 __device__ __forceinline__ void AdamUpdate(float& p, float& m, float& v, float g, const AdamParams& a) {
@@ -118,6 +119,11 @@ template <typename G, typename P16>
 __global__ void __launch_bounds__(kThreads)
 AdamFlatKernel(float* __restrict__ p32, P16* __restrict__ p16, const G* __restrict__ g, float* __restrict__ m,
                float* __restrict__ v, int64_t n, AdamParams a) {
+  if (a.step_dev) {
+    const float step = static_cast<float>(*a.step_dev);
+    a.bias1 = 1.f - powf(a.beta1, step);
+    a.bias2 = 1.f - powf(a.beta2, step);
+  }
   const int64_t nvec   = n / 4;
   const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
   for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < nvec; i += stride) {
@@ -288,11 +294,22 @@ int tipsk_sgd_momentum_flat(float* p32, void* p16, int p16_dtype, const void* gr
 int tipsk_adam_flat(float* p32, void* p16, int p16_dtype, const void* grad, int grad_dtype, float* exp_avg,
                     float* exp_avg_sq, int64_t n, float lr, float beta1, float beta2, float eps, float weight_decay,
                     int64_t step, float grad_scale, int decoupled, void* stream) {
+  return tipsk_adam_flat_devstep(p32, p16, p16_dtype, grad, grad_dtype, exp_avg, exp_avg_sq, n, lr, beta1, beta2, eps,
+                                 weight_decay, step, nullptr, grad_scale, decoupled, stream);
+}
+
+/* Same, but when step_dev is non-null the step count (>= 1) is read from that device int64 by the kernel, so a
+ * captured graph can be replayed with a changing step. */
+int tipsk_adam_flat_devstep(float* p32, void* p16, int p16_dtype, const void* grad, int grad_dtype, float* exp_avg,
+                            float* exp_avg_sq, int64_t n, float lr, float beta1, float beta2, float eps,
+                            float weight_decay, int64_t step, const int64_t* step_dev, float grad_scale, int decoupled,
+                            void* stream) {
   if (n <= 0) return 0;
   TIPSK_REQUIRE(p32 && grad && exp_avg && exp_avg_sq, "adam: null pointer");
-  TIPSK_REQUIRE(step >= 1, "adam: step counts from 1");
+  TIPSK_REQUIRE(step >= 1 || step_dev, "adam: step counts from 1");
   AdamParams a{lr, beta1, beta2, eps, weight_decay, grad_scale,
-               1.f - powf(beta1, static_cast<float>(step)), 1.f - powf(beta2, static_cast<float>(step)), decoupled};
+               1.f - powf(beta1, static_cast<float>(step)), 1.f - powf(beta2, static_cast<float>(step)), decoupled,
+               step_dev};
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int grid = FlatGrid(n);
   TIPSK_DISPATCH_FLOAT(grad_dtype, G, {

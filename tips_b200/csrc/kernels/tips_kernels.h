@@ -25,6 +25,10 @@ int tipsk_sgd_momentum_flat(float* p32, void* p16, int p16_dtype, const void* gr
 int tipsk_adam_flat(float* p32, void* p16, int p16_dtype, const void* grad, int grad_dtype, float* exp_avg,
                     float* exp_avg_sq, int64_t n, float lr, float beta1, float beta2, float eps, float weight_decay,
                     int64_t step, float grad_scale, int decoupled, void* stream);
+int tipsk_adam_flat_devstep(float* p32, void* p16, int p16_dtype, const void* grad, int grad_dtype, float* exp_avg,
+                            float* exp_avg_sq, int64_t n, float lr, float beta1, float beta2, float eps,
+                            float weight_decay, int64_t step, const int64_t* step_dev, float grad_scale, int decoupled,
+                            void* stream);
 /* host arrays of device pointers / element offsets / element counts */
 int tipsk_pack(const void* const* host_srcs, const int64_t* host_offsets, const int64_t* host_numels, int ntensors,
                int src_dtype, void* flat, int flat_dtype, float scale, int accumulate, void* stream);

@@ -45,10 +45,17 @@ class CtrMLP(nn.Module):
 
 
 class CtrTrainer:
-    """Owns the tables, the MLP and both optimizers; `train_step` is one synchronous PS step."""
+    """Owns the tables, the MLP and both optimizers; `train_step` is one synchronous PS step.
+
+    With ``graph=True`` the whole step (pull, MLP forward/backward on the tcgen05 GEMM, push with the
+    server-side Adagrad, the in-place NVLink allreduce of the MLP gradients and the fused Adam update) is
+    captured once in a CUDA graph and replayed, which removes the per-launch host cost of a step that is
+    otherwise launch-bound.  Every rank replays the same graph, so the collective kernels meet in the same
+    order without any negotiation.
+    """
 
     def __init__(self, num_fields=26, rows_per_table=10_000_000, dim=64, dense_features=13, hidden=(512, 256),
-                 table_lr=0.05, mlp_lr=1e-3, device=None, expected_batch=8192, seed=0):
+                 table_lr=0.05, mlp_lr=1e-3, device=None, expected_batch=8192, seed=0, graph=False):
         self.device = device or torch.device("cuda", torch.cuda.current_device())
         self.fields, self.dim, self.dense = num_fields, dim, dense_features
         self.emb_cols = num_fields * dim
@@ -57,12 +64,26 @@ class CtrTrainer:
                                        init_scale=0.05, seed=seed, expected_batch=expected_batch, device=self.device)
         torch.manual_seed(seed + 17)
         self.mlp = CtrMLP(self.in_features, hidden).to(self.device).to(torch.bfloat16)
-        opt = FusedAdam(self.mlp.parameters(), lr=mlp_lr, weight_decay=0.0)
-        self.opt = tips.DistributedOptimizer(opt) if tips.is_initialized() else opt
+        self.world = tips.size() if tips.is_initialized() else 1
+        self.graph = bool(graph)
+        self._x = None
+        self._g = None
+        self._static = None
+        self._calls = 0
+        if self.graph:
+            self.opt = FusedAdam(self.mlp.parameters(), lr=mlp_lr, weight_decay=0.0, capturable=True)
+            st = tips.runtime.device_state() if tips.is_initialized() else None
+            self.opt.build(st)
+            self._dev_state = st
+        else:
+            opt = FusedAdam(self.mlp.parameters(), lr=mlp_lr, weight_decay=0.0)
+            self.opt = tips.DistributedOptimizer(opt) if tips.is_initialized() else opt
         if tips.is_initialized() and tips.size() > 1:
             tips.broadcast_parameters(self.mlp.state_dict(), root_rank=0)
-        self.world = tips.size() if tips.is_initialized() else 1
-        self._x = None
+            if self.graph:  # the flat master copies follow the broadcast parameters
+                for fs in self.opt.build():
+                    if fs.low:
+                        fs.master.copy_(fs.flat_param)
 
     def _input_buffer(self, batch):
         if self._x is None or self._x.shape[0] != batch:
@@ -75,18 +96,51 @@ class CtrTrainer:
         x = embedding_lookup(self.tables, ids, x, col0=0, grad_scale=1.0 / self.world)
         return self.mlp(x).view(-1)
 
-    def train_step(self, ids, dense, labels):
+    def _allreduce_inline(self):
+        """Graph mode: pack every bucket and average it over the ranks in place, on the current stream."""
+        from ..ops import base
+        for fs in self.opt.build():
+            b = fs.bucket
+            b.pack()
+            if self.world > 1:
+                nbytes = b.numel * b.grad.element_size()
+                base.check(base.K().tipsk_allreduce(None, None, b.win_off, nbytes, base.code(b.grad), 0, 1.0,
+                                                    1.0 / self.world, 3, base.comm_stream()), "allreduce")
+            fs.grads_packed = True
+
+    def _step_impl(self, ids, dense, labels):
         loss = sigmoid_bce_loss(self.forward(ids, dense), labels)
         loss.backward()
+        if self.graph:
+            self._allreduce_inline()
         self.opt.step()
         return loss.detach()
+
+    def train_step(self, ids, dense, labels):
+        if not self.graph:
+            return self._step_impl(ids, dense, labels)
+        if self._static is None:
+            self._static = [torch.empty_like(ids), torch.empty_like(dense), torch.empty_like(labels)]
+        for dst, src in zip(self._static, (ids, dense, labels)):
+            dst.copy_(src, non_blocking=True)
+        if self._g is None:
+            self._calls += 1
+            if self._calls <= 3:  # eager warm-up: lazy initialisation, kernel attributes, optimizer state
+                return self._step_impl(*self._static)
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                self._loss_static = self._step_impl(*self._static)
+            self._g = g
+        self._g.replay()
+        return self._loss_static
 
     def check(self):
         from ..ops.linear import gemm_status
         self.tables.check()
         if gemm_status() != 0:
             raise RuntimeError("a GEMM launch reported a bounded-wait timeout")
-        st = tips.runtime.device_state()
+        st = tips.runtime.device_state() if tips.is_initialized() else None
         if st is not None and st.window is not None:
             st.check_status()
 

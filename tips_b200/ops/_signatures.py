@@ -14,6 +14,7 @@ _PROTOS = {
     "tipsk_last_error": (c_char_p, []),
     "tipsk_sgd_momentum_flat": (I, [P, P, I, P, I, P, L, F, F, F, F, I, F, I, P]),
     "tipsk_adam_flat": (I, [P, P, I, P, I, P, P, L, F, F, F, F, F, L, F, I, P]),
+    "tipsk_adam_flat_devstep": (I, [P, P, I, P, I, P, P, L, F, F, F, F, F, L, P, F, I, P]),
     "tipsk_pack": (I, [PP, POINTER(L), POINTER(L), I, I, P, I, F, I, P]),
     "tipsk_unpack": (I, [P, I, PP, POINTER(L), POINTER(L), I, I, F, P]),
     "tipsk_scale_cast": (I, [P, I, P, I, L, F, P]),

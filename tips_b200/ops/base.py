@@ -46,6 +46,13 @@ def stream() -> int:
     return torch.cuda.current_stream().cuda_stream
 
 
+def comm_stream() -> int:
+    """Current stream for the collective launchers, where a null handle means "the library's own stream":
+    the legacy default stream is passed as its explicit handle instead."""
+    s = torch.cuda.current_stream().cuda_stream
+    return s if s else 1  # cudaStreamLegacy
+
+
 def code(t: torch.Tensor | torch.dtype) -> int:
     dt = t.dtype if isinstance(t, torch.Tensor) else t
     return DTYPE_CODE[dt]

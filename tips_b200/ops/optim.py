@@ -156,10 +156,11 @@ class FusedAdam(_FusedOptimizer):
     """Adam; with ``decoupled_weight_decay`` (default) it is AdamW."""
 
     def __init__(self, params, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.01,
-                 decoupled_weight_decay=True, bucket_bytes=None, wire_dtype="auto"):
+                 decoupled_weight_decay=True, bucket_bytes=None, wire_dtype="auto", capturable=False):
         defaults = dict(lr=lr, betas=betas, eps=eps, weight_decay=weight_decay,
                         decoupled_weight_decay=decoupled_weight_decay)
         super().__init__(params, defaults, bucket_bytes, wire_dtype)
+        self.capturable = capturable
 
     def _update(self, fs, grad_scale):
         g, b = fs.group, fs.bucket
@@ -169,12 +170,19 @@ class FusedAdam(_FusedOptimizer):
         m, v = fs.state["exp_avg"], fs.state["exp_avg_sq"]
         b1, b2 = g["betas"]
         if fs.master.is_cuda:
-            base.check(base.K().tipsk_adam_flat(
+            step_ptr = None
+            if self.capturable:
+                # the step count lives on the device so that a captured graph can be replayed
+                if "step_dev" not in fs.state:
+                    fs.state["step_dev"] = torch.full((1,), fs.steps - 1, dtype=torch.int64, device=fs.master.device)
+                fs.state["step_dev"].add_(1)
+                step_ptr = fs.state["step_dev"].data_ptr()
+            base.check(base.K().tipsk_adam_flat_devstep(
                 fs.master.data_ptr(), fs.flat_param.data_ptr() if fs.low else None,
                 base.code(fs.flat_param) if fs.low else 6, b.grad.data_ptr(), base.code(b.grad), m.data_ptr(),
                 v.data_ptr(), b.numel, float(g["lr"]), float(b1), float(b2), float(g["eps"]),
-                float(g["weight_decay"]), fs.steps, float(grad_scale), int(g["decoupled_weight_decay"]),
-                base.stream()), "adam_flat")
+                float(g["weight_decay"]), max(fs.steps, 1), step_ptr, float(grad_scale),
+                int(g["decoupled_weight_decay"]), base.stream()), "adam_flat")
         else:
             grad = b.grad.float() * grad_scale
             if not g["decoupled_weight_decay"]:

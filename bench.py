@@ -134,6 +134,7 @@ def main():
                        "l2": "inputs and activations per step far exceed the 126 MB L2"},
         })
     if args.workload in ("all", "ctr") and args.impl != "floor":
+        workloads.release_cached_memory()
         p = workloads.run_ctr(args.ctr_batch, args.ctr_rows, args.steps, max(args.warmup, 4), graph=not args.no_graph)
         launches += p["gpu_launches"]
         ps = {"metric": "ps_ctr_train_samples_per_sec", "value": p["value"], "unit": "samples/s",

@@ -15,6 +15,10 @@ from .parallel.collectives import (Average, Max, Min, Product, Sum, allgather, a
 from .parallel.compression import Compression
 from .parallel.optimizer import DistributedOptimizer
 from .parallel.functions import (allgather_object, broadcast_object, broadcast_object_fn, broadcast_optimizer_state,
-                                 broadcast_parameters, broadcast_variables, metric_average)
+                                 broadcast_parameters, broadcast_variables, metric_average, allreduce_gradients,
+                                 allreduce_value, allgather_value, broadcast_value, broadcast_global_variables,
+                                 rank_op, size_op)
 
 __version__ = "0.1.0"
+from . import callbacks, elastic
+from .utils.checkpoint import load_checkpoint, resume, save_checkpoint

@@ -118,6 +118,8 @@ def run_resnet50(batch: int, steps: int, warmup: int):
     ms2, _ = timed(step_e2e, steps, max(3, warmup // 2))
     e2e = {"value": batch * tips.size() * steps / (ms2 / 1e3), "unit": "images/s", "ms_per_step": ms2 / steps,
            "h2d_bytes_per_step": pre.bytes_per_step, "d2h_bytes_per_step": 4, "last_loss": last.get("loss")}
+    del pre, model, opt, x_dev, y_dev
+    release_cached_memory()
     return {"value": value, "ms_per_step": ms / steps, "gpu_launches": launches, "e2e": e2e}
 
 
@@ -163,9 +165,22 @@ def run_resnet50_floor(batch: int, steps: int, warmup: int):
     return {"value": batch * tips.size() * steps / (ms / 1e3), "ms_per_step": ms / steps, "gpu_launches": 0, "e2e": e2e}
 
 
+def release_cached_memory():
+    import gc
+    gc.collect()
+    torch.cuda.synchronize()
+    torch.cuda.empty_cache()
+
+
 def run_ctr(batch: int, rows: int, steps: int, warmup: int, graph: bool = True):
     from tips_b200.models.ctr import CtrTrainer, synthetic_ctr_batch
     dev = torch.device("cuda", torch.cuda.current_device())
+    release_cached_memory()
+    # tables + Adagrad state for this rank's shards; refuse to start a step that cannot fit
+    need = 26 * ((rows + tips.size() - 1) // tips.size()) * 64 * 4 * 2 + (6 << 30)
+    free, _ = torch.cuda.mem_get_info()
+    if need > free:
+        raise MemoryError(f"CTR tables need {need >> 30} GiB on this GPU, {free >> 30} GiB are free")
     trainer = CtrTrainer(num_fields=26, rows_per_table=rows, dim=64, dense_features=13, hidden=(512, 256),
                          device=dev, expected_batch=batch, graph=graph)
     nhost = 3

@@ -139,3 +139,62 @@ def metric_average(value, name: str):
     t = value if isinstance(value, torch.Tensor) else torch.tensor(float(value), dtype=torch.float64)
     out = C.allreduce(t.detach().cpu().reshape(1) if t.dim() == 0 else t.detach().cpu(), name=name, op=C.Average)
     return out.item() if out.numel() == 1 else out
+
+
+# ---- value-level collectives and small op wrappers --------------------------------------------------
+# Counterparts of the reference's Keras value helpers (tips/_keras/__init__.py:193-212: allreduce /
+# allgather / broadcast of constants) and of its raw size_op / rank_op (tips/tensorflow/ops.py:33-45).
+
+def size_op() -> torch.Tensor:
+    """World size as an int32 tensor."""
+    return torch.tensor(C._size(), dtype=torch.int32)
+
+
+def rank_op() -> torch.Tensor:
+    """Rank as an int32 tensor."""
+    return torch.tensor(C._rank(), dtype=torch.int32)
+
+
+def _as_tensor(value):
+    if isinstance(value, torch.Tensor):
+        return value
+    return torch.as_tensor(value)
+
+
+def allreduce_value(value, name=None, average=True):
+    """Allreduce a Python number / sequence / array; returns a tensor."""
+    t = _as_tensor(value)
+    if not t.is_floating_point() and average:
+        t = t.to(torch.float64)
+    return C.allreduce(t, name=name, op=C.Average if average else C.Sum)
+
+
+def allgather_value(value, name=None):
+    t = _as_tensor(value)
+    return C.allgather(t.reshape(1) if t.dim() == 0 else t, name=name)
+
+
+def broadcast_value(value, root_rank=0, name=None):
+    return C.broadcast(_as_tensor(value), root_rank, name=name)
+
+
+def broadcast_global_variables(model: torch.nn.Module, root_rank: int = 0, optimizer=None) -> None:
+    """Broadcast every parameter and buffer of `model` (and the optimizer state) from root_rank;
+    the reference's broadcast_global_variables / BroadcastGlobalVariablesHook (tips/tensorflow/__init__.py:106-186)."""
+    broadcast_parameters(model.state_dict(), root_rank)
+    if optimizer is not None:
+        broadcast_optimizer_state(optimizer, root_rank)
+
+
+def allreduce_gradients(parameters, op=C.Average, compression=None, name="tips.grads") -> None:
+    """Allreduce the .grad of every parameter in place, for hand-written training loops: what the
+    reference's DistributedGradientTape does to the gradients a tape returns
+    (tips/tensorflow/__init__.py:459-568)."""
+    from .compression import Compression
+    comp = compression or Compression.none
+    params = [p for p in parameters if p.grad is not None]
+    handles = [C.allreduce_async(p.grad, name=f"{name}.{i}", op=op, compression=comp) for i, p in enumerate(params)]
+    for p, h in zip(params, handles):
+        out = C.synchronize(h)
+        if out is not p.grad:
+            p.grad.copy_(out)

@@ -24,7 +24,7 @@ class Config:
     wire_dtype: str = "auto"                 # auto = gradient dtype; bf16/fp16 = compress on the wire
     one_shot_threshold_bytes: int = 512 << 10
     device_wait_budget_ms: int = 20000       # bound of every in-kernel wait on a peer
-    comm_blocks: int = 32                    # grid of the communication kernels (SM budget)
+    comm_blocks: int = 64                    # grid of the communication kernels (SM budget)
     use_multimem: bool = True                # NVLS multimem instructions when a multicast mapping exists
     symm_window_bytes: int = 256 << 20       # staging window for tensors outside symmetric memory
     static_schedule: bool = True             # freeze the bucket order after the first negotiated step

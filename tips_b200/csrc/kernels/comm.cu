@@ -37,8 +37,14 @@ namespace tipsk {
 namespace {
 
 constexpr int kCommThreads = 512;
-constexpr int kUnroll      = 2;                       // vectors per thread per sub-tile
-constexpr int kSubTile     = kCommThreads * kUnroll;  // vectors per rank per tile
+// Vectors per thread per sub-tile.  The in-switch reduction needs one load per vector, so it can keep
+// many more in flight per thread than the peer-load path, which holds one vector per rank.
+constexpr int kUnrollP2p   = 2;
+constexpr int kUnrollMc    = 8;
+constexpr int UnrollOf(bool multimem) { return multimem ? kUnrollMc : kUnrollP2p; }
+constexpr int SubTileOf(bool multimem) { return kCommThreads * UnrollOf(multimem); }  // vectors per rank per tile
+constexpr int kCopyUnroll  = 4;                       // vectors in flight per thread in the copy loops
+constexpr int kCopyTile    = kCommThreads * kCopyUnroll * 2;  // vectors per tile of allgather / broadcast
 
 struct RankArgs {
   CommCtx ctx;
@@ -157,6 +163,23 @@ __device__ __forceinline__ void CopyOwnedTiles(char* dst, const char* src, uint6
   for (uint64_t t = blockIdx.x; t < ntiles; t += gridDim.x) {
     const uint64_t lo = t * tile_vecs;
     const uint64_t hi = lo + tile_vecs < nvec ? lo + tile_vecs : nvec;
+    if (aligned && hi * 16 <= nbytes) {
+      // full vectors: four loads in flight per thread before the stores
+      for (uint64_t v = lo + threadIdx.x; v < hi; v += static_cast<uint64_t>(blockDim.x) * kCopyUnroll) {
+        U4 q[kCopyUnroll];
+#pragma unroll
+        for (int u = 0; u < kCopyUnroll; ++u) {
+          const uint64_t i = v + static_cast<uint64_t>(u) * blockDim.x;
+          if (i < hi) q[u] = *reinterpret_cast<const U4*>(src + i * 16);
+        }
+#pragma unroll
+        for (int u = 0; u < kCopyUnroll; ++u) {
+          const uint64_t i = v + static_cast<uint64_t>(u) * blockDim.x;
+          if (i < hi) *reinterpret_cast<U4*>(dst + i * 16) = q[u];
+        }
+      }
+      continue;
+    }
     for (uint64_t v = lo + threadIdx.x; v < hi; v += blockDim.x) {
       const uint64_t off = v * 16;
       if (aligned && off + 16 <= nbytes) {
@@ -179,6 +202,9 @@ AllreduceKernel(CommLaunch args, int channel, uint64_t nbytes, int op, float pre
   const CommCtx& ctx = ra.ctx;
   const int n        = ctx.nranks;
   const int block    = blockIdx.x;
+  constexpr int kUnroll  = UnrollOf(kMultimem);
+  constexpr int kSubTile = SubTileOf(kMultimem);
+  constexpr int kSrcs    = kMultimem ? 1 : kMaxRanks;  // vectors held per output vector
   const uint64_t nvec      = (nbytes + 15) / 16;
   const uint64_t tile_vecs = static_cast<uint64_t>(kSubTile) * n;
   const uint64_t ntiles    = (nvec + tile_vecs - 1) / tile_vecs;
@@ -195,7 +221,7 @@ AllreduceKernel(CommLaunch args, int channel, uint64_t nbytes, int op, float pre
       const uint64_t sub_lo  = kOneShot ? tile_lo : tile_lo + static_cast<uint64_t>(ctx.rank) * kSubTile;
       const uint64_t sub_n   = kOneShot ? tile_vecs : kSubTile;
       for (uint64_t base = threadIdx.x; base < sub_n; base += blockDim.x * kUnroll) {
-        U4 in[kUnroll][kMaxRanks];
+        U4 in[kUnroll][kSrcs];
         uint64_t vec[kUnroll];
 #pragma unroll
         for (int u = 0; u < kUnroll; ++u) {
@@ -205,7 +231,7 @@ AllreduceKernel(CommLaunch args, int channel, uint64_t nbytes, int op, float pre
             continue;
           }
           const uint64_t off = ra.win_off + vec[u] * 16;
-          if (kMultimem && op == 0) {
+          if constexpr (kMultimem) {  // the host selects this variant for sums only
             in[u][0] = MultimemLdReduce<T>(ctx.mc + off);
           } else {
 #pragma unroll
@@ -218,14 +244,14 @@ AllreduceKernel(CommLaunch args, int channel, uint64_t nbytes, int op, float pre
           if (vec[u] == ~0ull) continue;
           U4 out;
           Acc<T> acc;
-          if (kMultimem && op == 0) {
+          if constexpr (kMultimem) {
             acc.Zero();
             acc.Add(in[u][0]);
             acc.Scale(sum_scale);
           } else {
             acc.Zero();
 #pragma unroll
-            for (int r = 0; r < kMaxRanks; ++r) {
+            for (int r = 0; r < kSrcs; ++r) {
               if (r >= n) break;
               if (op == 0) acc.Add(in[u][r]);
               else if (op == 1) acc.Max(in[u][r], r == 0);
@@ -275,27 +301,37 @@ AllgathervKernel(CommLaunch args, int channel, GatherSizes sizes) {
   char* my_win       = ctx.peer[ctx.rank] + ra.win_off;
   uint32_t epoch     = NextEpoch(ctx, channel, block);
   const uint64_t my_bytes = sizes.bytes[ctx.rank];
-  CopyOwnedTiles(my_win, ra.src, my_bytes, (my_bytes + 15) / 16, kSubTile, true);
+  CopyOwnedTiles(my_win, ra.src, my_bytes, (my_bytes + 15) / 16, kCopyTile, true);
   bool ok = BlockBarrier(ctx, channel, block, epoch, 1);
   if (ok) {
     for (int i = 0; i < n; ++i) {
       const int r          = (ctx.rank + i) % n;
       const uint64_t bytes = sizes.bytes[r];
       const uint64_t nvec  = (bytes + 15) / 16;
-      const uint64_t ntiles = (nvec + kSubTile - 1) / kSubTile;
+      const uint64_t ntiles = (nvec + kCopyTile - 1) / kCopyTile;
       const char* from     = ctx.peer[r] + ra.win_off;
       char* to             = ra.dst + sizes.displ[r];
       const bool aligned   = (reinterpret_cast<uintptr_t>(to) & 15) == 0;
       for (uint64_t t = block; t < ntiles; t += gridDim.x) {
-        const uint64_t lo = t * kSubTile;
-        const uint64_t hi = lo + kSubTile < nvec ? lo + kSubTile : nvec;
-        for (uint64_t v = lo + threadIdx.x; v < hi; v += blockDim.x) {
-          U4 q = LdSys(from + v * 16);
-          if (aligned && v * 16 + 16 <= bytes) {
-            *reinterpret_cast<U4*>(to + v * 16) = q;
-          } else {
-            const char* qb = reinterpret_cast<const char*>(&q);
-            for (uint64_t b = 0; b < 16 && v * 16 + b < bytes; ++b) to[v * 16 + b] = qb[b];
+        const uint64_t lo = t * kCopyTile;
+        const uint64_t hi = lo + kCopyTile < nvec ? lo + kCopyTile : nvec;
+        for (uint64_t v = lo + threadIdx.x; v < hi; v += static_cast<uint64_t>(blockDim.x) * kCopyUnroll) {
+          U4 q[kCopyUnroll];
+#pragma unroll
+          for (int u = 0; u < kCopyUnroll; ++u) {  // several peer loads in flight per thread
+            const uint64_t i = v + static_cast<uint64_t>(u) * blockDim.x;
+            if (i < hi) q[u] = LdSys(from + i * 16);
+          }
+#pragma unroll
+          for (int u = 0; u < kCopyUnroll; ++u) {
+            const uint64_t i = v + static_cast<uint64_t>(u) * blockDim.x;
+            if (i >= hi) continue;
+            if (aligned && i * 16 + 16 <= bytes) {
+              *reinterpret_cast<U4*>(to + i * 16) = q[u];
+            } else {
+              const char* qb = reinterpret_cast<const char*>(&q[u]);
+              for (uint64_t b = 0; b < 16 && i * 16 + b < bytes; ++b) to[i * 16 + b] = qb[b];
+            }
           }
         }
       }
@@ -318,32 +354,42 @@ BroadcastKernel(CommLaunch args, int channel, uint64_t nbytes, int root) {
   char* my_win       = ctx.peer[ctx.rank] + ra.win_off;
   uint32_t epoch     = NextEpoch(ctx, channel, block);
   const uint64_t nvec   = (nbytes + 15) / 16;
-  const uint64_t ntiles = (nvec + kSubTile - 1) / kSubTile;
+  const uint64_t ntiles = (nvec + kCopyTile - 1) / kCopyTile;
   // Peers must be done with the previous contents of their windows before the root overwrites them.
   bool ok = BlockBarrier(ctx, channel, block, epoch, 1);
   if (ok && ctx.rank == root) {
     const bool src_aligned = (reinterpret_cast<uintptr_t>(ra.src) & 15) == 0;
     for (uint64_t t = block; t < ntiles; t += gridDim.x) {
-      const uint64_t lo = t * kSubTile;
-      const uint64_t hi = lo + kSubTile < nvec ? lo + kSubTile : nvec;
-      for (uint64_t v = lo + threadIdx.x; v < hi; v += blockDim.x) {
-        U4 q;
-        if (src_aligned && v * 16 + 16 <= nbytes) {
-          q = *reinterpret_cast<const U4*>(ra.src + v * 16);
-        } else {
-          char* qb = reinterpret_cast<char*>(&q);
-          for (uint64_t b = 0; b < 16; ++b) qb[b] = v * 16 + b < nbytes ? ra.src[v * 16 + b] : 0;
+      const uint64_t lo = t * kCopyTile;
+      const uint64_t hi = lo + kCopyTile < nvec ? lo + kCopyTile : nvec;
+      for (uint64_t v0 = lo + threadIdx.x; v0 < hi; v0 += static_cast<uint64_t>(blockDim.x) * kCopyUnroll) {
+        U4 q[kCopyUnroll];
+#pragma unroll
+        for (int u = 0; u < kCopyUnroll; ++u) {
+          const uint64_t v = v0 + static_cast<uint64_t>(u) * blockDim.x;
+          if (v >= hi) continue;
+          if (src_aligned && v * 16 + 16 <= nbytes) {
+            q[u] = *reinterpret_cast<const U4*>(ra.src + v * 16);
+          } else {
+            char* qb = reinterpret_cast<char*>(&q[u]);
+            for (uint64_t b = 0; b < 16; ++b) qb[b] = v * 16 + b < nbytes ? ra.src[v * 16 + b] : 0;
+          }
         }
-        if (kMultimem) {
-          MultimemSt(ctx.mc + ra.win_off + v * 16, q);
-        } else {
-          for (int r = 0; r < n; ++r) StSys(ctx.peer[r] + ra.win_off + v * 16, q);
+#pragma unroll
+        for (int u = 0; u < kCopyUnroll; ++u) {
+          const uint64_t v = v0 + static_cast<uint64_t>(u) * blockDim.x;
+          if (v >= hi) continue;
+          if (kMultimem) {
+            MultimemSt(ctx.mc + ra.win_off + v * 16, q[u]);
+          } else {
+            for (int r = 0; r < n; ++r) StSys(ctx.peer[r] + ra.win_off + v * 16, q[u]);
+          }
         }
       }
     }
   }
   ok = BlockBarrier(ctx, channel, block, epoch + 1, 2) && ok;
-  if (ok && ra.dst) CopyOwnedTiles(ra.dst, my_win, nbytes, nvec, kSubTile, false);
+  if (ok && ra.dst) CopyOwnedTiles(ra.dst, my_win, nbytes, nvec, kCopyTile, false);
   SaveEpoch(ctx, channel, block, epoch + 1);
 }
 
@@ -482,7 +528,8 @@ int tipsk_comm_init(int rank, int nranks, void* const* peer_windows, void* multi
   TIPSK_REQUIRE(nranks >= 1 && nranks <= kMaxRanks, "comm: 1..8 ranks are supported");
   TIPSK_REQUIRE(rank >= 0 && rank < nranks, "comm: bad rank");
   TIPSK_REQUIRE(window_bytes >= kSignalBytes + staging_bytes, "comm: window smaller than signals + staging");
-  TIPSK_REQUIRE(blocks >= 1 && blocks <= kMaxCommBlocks, "comm: blocks out of range");
+  // the last two flag slots of every channel belong to the one-block fence and to the wait self-test
+  TIPSK_REQUIRE(blocks >= 1 && blocks <= kMaxCommBlocks - 2, "comm: blocks out of range");
   st.rank          = rank;
   st.nranks        = nranks;
   st.emulated      = emulated ? nranks : 0;
@@ -515,6 +562,8 @@ int tipsk_comm_init(int rank, int nranks, void* const* peer_windows, void* multi
     c.status    = status_dev + (emulated ? i : 0);
     TIPSK_CUDA(cudaMalloc(reinterpret_cast<void**>(&c.epochs), sizeof(uint32_t) * kNumChannels * kMaxCommBlocks));
     TIPSK_CUDA(cudaMemset(c.epochs, 0, sizeof(uint32_t) * kNumChannels * kMaxCommBlocks));
+    TIPSK_CUDA(cudaMalloc(reinterpret_cast<void**>(&c.failed), sizeof(int32_t)));
+    TIPSK_CUDA(cudaMemset(c.failed, 0, sizeof(int32_t)));
   }
   for (int ch = 0; ch < kNumChannels; ++ch) {
     if (!st.streams[ch]) {
@@ -535,7 +584,9 @@ int tipsk_comm_shutdown(void) {
   cudaDeviceSynchronize();
   for (int i = 0; i < kMaxRanks; ++i) {
     if (st.ctx[i].epochs) cudaFree(st.ctx[i].epochs);
+    if (st.ctx[i].failed) cudaFree(st.ctx[i].failed);
     st.ctx[i].epochs = nullptr;
+    st.ctx[i].failed = nullptr;
   }
   for (cudaEvent_t e : st.event_pool) cudaEventDestroy(e);
   st.event_pool.clear();
@@ -561,7 +612,11 @@ int tipsk_comm_status(int slot, int32_t* out7, int clear) {
   CommStatus s = st.status_host[slot];
   out7[0] = s.code; out7[1] = s.peer; out7[2] = s.phase; out7[3] = s.block;
   out7[4] = static_cast<int32_t>(s.epoch); out7[5] = s.channel; out7[6] = s.rank;
-  if (clear) memset(&st.status_host[slot], 0, sizeof(CommStatus));
+  if (clear && s.code != 0) {
+    memset(&st.status_host[slot], 0, sizeof(CommStatus));
+    const int idx = st.emulated > 0 ? slot : st.rank;
+    if (st.ctx[idx].failed) cudaMemset(st.ctx[idx].failed, 0, sizeof(int32_t));
+  }
   return s.code;
 }
 
@@ -576,6 +631,7 @@ int tipsk_comm_reset(void) {
     CommCtx& c = st.ctx[st.emulated > 0 ? i : st.rank];
     TIPSK_CUDA(cudaMemset(c.peer[c.rank], 0, kFlagBytes));
     TIPSK_CUDA(cudaMemset(c.epochs, 0, sizeof(uint32_t) * kNumChannels * kMaxCommBlocks));
+    TIPSK_CUDA(cudaMemset(c.failed, 0, sizeof(int32_t)));
   }
   memset(st.status_host, 0, sizeof(CommStatus) * kMaxRanks);
   TIPSK_CUDA(cudaDeviceSynchronize());
@@ -595,7 +651,7 @@ int tipsk_allreduce(const void* const* srcs, void* const* dsts, int64_t win_off,
   if (nbytes == 0) return 0;
   cudaStream_t s = stream ? static_cast<cudaStream_t>(stream) : st.streams[channel];
   const bool mm  = st.use_multimem && op == 0;
-  const uint64_t tile_bytes = static_cast<uint64_t>(kSubTile) * st.nranks * 16;
+  const uint64_t tile_bytes = static_cast<uint64_t>(SubTileOf(mm)) * st.nranks * 16;
   if (!srcs) {
     TIPSK_REQUIRE(win_off >= static_cast<int64_t>(kSignalBytes) && win_off % 16 == 0, "allreduce: bad window offset");
     TIPSK_REQUIRE(static_cast<uint64_t>(win_off) + ((nbytes + 15) & ~15ull) <= st.window_bytes,
@@ -659,7 +715,7 @@ int tipsk_allgatherv(const void* const* srcs, void* const* dsts, const uint64_t*
     CommLaunch l = MakeLaunch(sp, dsts, kSignalBytes);
     uint64_t biggest = 0;
     for (int r = 0; r < n; ++r) if (gs.bytes[r] > biggest) biggest = gs.bytes[r];
-    int rc = LaunchComm(AllgathervKernel, GridFor(biggest, static_cast<uint64_t>(kSubTile) * 16, st.blocks), s, l,
+    int rc = LaunchComm(AllgathervKernel, GridFor(biggest, static_cast<uint64_t>(kCopyTile) * 16, st.blocks), s, l,
                         channel, gs);
     if (rc) return rc;
   }
@@ -683,7 +739,7 @@ int tipsk_broadcast(const void* const* srcs, void* const* dsts, uint64_t nbytes,
       dp[i] = static_cast<char*>(dsts[i]) + done;
     }
     CommLaunch l = MakeLaunch(sp, dp, kSignalBytes);
-    const int grid = GridFor(len, static_cast<uint64_t>(kSubTile) * 16, st.blocks);
+    const int grid = GridFor(len, static_cast<uint64_t>(kCopyTile) * 16, st.blocks);
     int rc = st.use_multimem ? LaunchComm(BroadcastKernel<true>, grid, s, l, channel, len, root)
                              : LaunchComm(BroadcastKernel<false>, grid, s, l, channel, len, root);
     if (rc) return rc;

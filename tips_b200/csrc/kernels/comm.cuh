@@ -21,7 +21,7 @@
 namespace tipsk {
 
 constexpr int kMaxRanks       = 8;
-constexpr int kMaxCommBlocks  = 64;
+constexpr int kMaxCommBlocks  = 128;
 constexpr int kNumChannels    = 4;  // 0 negotiated collectives, 1 frozen schedule, 2 parameter server, 3 spare
 // Flag area at the start of every rank's window: [channel][block][src rank] u32.
 constexpr size_t kFlagBytes   = sizeof(uint32_t) * kNumChannels * kMaxCommBlocks * kMaxRanks;
@@ -44,7 +44,8 @@ struct CommCtx {
   char* peer[kMaxRanks];   // base of every rank's window as mapped in this process
   char* mc;                // multicast mapping of the window, or null
   uint32_t* epochs;        // local: [channel][block] last used epoch
-  CommStatus* status;      // host-visible status block
+  CommStatus* status;      // host-visible status block (mapped host memory: written on failure only)
+  int32_t* failed;         // device-side copy of "a wait has timed out", polled by the barriers
   uint64_t budget_ns;
   int32_t rank;
   int32_t nranks;
@@ -121,7 +122,8 @@ __device__ __forceinline__ uint32_t* FlagAddr(char* window, int channel, int blo
 
 __device__ __forceinline__ void ReportTimeout(const CommCtx& ctx, int peer, int phase, int block, uint32_t epoch,
                                               int channel) {
-  if (atomicCAS(&ctx.status->code, kCommOk, kCommTimeout) == kCommOk) {
+  if (atomicExch(ctx.failed, 1) == 0) {
+    ctx.status->code    = kCommTimeout;
     ctx.status->peer    = peer;
     ctx.status->phase   = phase;
     ctx.status->block   = block;
@@ -145,7 +147,8 @@ __device__ __forceinline__ bool BlockBarrier(const CommCtx& ctx, int channel, in
     const int peer = threadIdx.x;
     StReleaseSys(FlagAddr(ctx.peer[peer], channel, block, ctx.rank), epoch);
     const uint32_t* mine = FlagAddr(ctx.peer[ctx.rank], channel, block, peer);
-    const bool already_failed = *reinterpret_cast<volatile int32_t*>(&ctx.status->code) != kCommOk;
+    // device memory, not the host-visible block: a PCIe read per barrier would serialise the blocks
+    const bool already_failed = *reinterpret_cast<volatile int32_t*>(ctx.failed) != 0;
     if (already_failed) {
       s_ok = 0;
     } else {

@@ -1,7 +1,7 @@
 """Small single-kernel cases for profiler captures: each runs ONE kernel a handful of times on inputs a
 little larger than L2, holds well under a GB on the device and exits by itself in seconds.
 
-    python -m tips_b200.bench.profile_case {bn_fwd,bn_bwd,gemm,ln,sgd,ps_pull,ps_push}
+    python -m tips_b200.bench.profile_case {bn_fwd,bn_bwd,gemm,gemm_persistent,ln,sgd,ps_pull,ps_push}
 """
 from __future__ import annotations
 
@@ -28,10 +28,11 @@ def main(argv=None):
             dy = torch.randn_like(y)
             for _ in range(reps):
                 torch.autograd.grad(y, xg, dy, retain_graph=True)
-    elif case == "gemm":
+    elif case in ("gemm", "gemm_persistent"):
         from tips_b200.ops.linear import gemm_tn
-        a = torch.randn(16384, 4096, device=dev).to(torch.bfloat16)
-        b = torch.randn(4096, 4096, device=dev).to(torch.bfloat16)
+        k = 4096 if case == "gemm" else 1024  # the short-K shape takes the persistent double-buffered variant
+        a = torch.randn(16384, k, device=dev).to(torch.bfloat16)
+        b = torch.randn(4096, k, device=dev).to(torch.bfloat16)
         bias = torch.randn(4096, device=dev).to(torch.bfloat16)
         for _ in range(reps):
             gemm_tn(a, b, bias, "relu")
@@ -51,8 +52,8 @@ def main(argv=None):
     elif case in ("ps_pull", "ps_push"):
         from tips_b200.models.ctr import synthetic_ctr_batch
         from tips_b200.ps.gpu import ShardedEmbedding
-        t = ShardedEmbedding(26, 1_000_000, 64, optimizer="adagrad", lr=0.05, init_scale=0.05, expected_batch=8192)
-        ids = synthetic_ctr_batch(8192, 26, 1_000_000, 13, seed=1)[0].to(dev)
+        t = ShardedEmbedding(26, 200_000, 64, optimizer="adagrad", lr=0.05, init_scale=0.05, expected_batch=8192)
+        ids = synthetic_ctr_batch(8192, 26, 200_000, 13, seed=1)[0].to(dev)
         out = torch.empty(8192, 26 * 64, dtype=torch.bfloat16, device=dev)
         g = torch.randn_like(out)
         for _ in range(reps):

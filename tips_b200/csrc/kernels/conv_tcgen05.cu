@@ -1,0 +1,789 @@
+// NHWC bf16 convolutions as implicit GEMMs on the 5th-generation tensor cores.
+//
+// The activation tensor [N, H, W, C] is never unfolded.  An output tile is a box of up to 128 output
+// pixels (tn images x th rows x tw columns); for every filter tap (r, s) the TMA unit loads the same box
+// shifted by the tap's offset as a 4-D tile of 64 channels per pixel, which lands in shared memory in the
+// 128-byte-swizzled K-major layout that tcgen05.mma reads: the tap loop simply extends the K loop of
+// a GEMM, and out-of-image coordinates are zero-filled by the TMA unit, which is the padding.  Strided
+// convolutions read through "phase" tensor maps: for stride 2 the input pixels of one parity class
+// (h mod 2, w mod 2) form a dense tensor with doubled strides, and each tap belongs to exactly one class.
+// The same kernel therefore serves
+//   forward            y[p, co]  = sum_{tap, ci} x[p*stride + tap - pad, ci] * w[co, tap, ci]
+//   data gradient      dx[q, ci] = sum_{tap, co} dy[(q + pad - tap)/stride, co] * w^T[ci, tap, co]
+// (the host builds the tap list; for stride 2 one launch per parity class of dx, written through a phase map).
+// The weight gradient contracts over pixels instead, so both operands are MN-major in shared memory
+// (pixels are rows); it splits the pixel range over CTAs and accumulates into an fp32 buffer with
+// vector reductions.
+//
+// Pipeline and warp roles are those of the persistent GEMM: warp 0 issues TMA loads (never multicast),
+// warp 1 issues tcgen05.mma into a double-buffered TMEM accumulator, warps 2-5 drain TMEM, convert and hand
+// swizzled boxes to the TMA store unit; all mbarrier waits are bounded and report through an error word.
+//
+// The reference has no convolution (it delegates model math to TensorFlow); these kernels serve the
+// ResNet-50 benchmark model.
+#include <cuda.h>
+
+#include <algorithm>
+#include <vector>
+
+#include "kernels/common.cuh"
+#include "kernels/tcgen05.cuh"
+#include "kernels/tips_kernels.h"
+
+namespace tipsk {
+namespace {
+
+constexpr int kMaxTaps = 9;
+
+struct ConvTap {
+  int16_t dh, dw;  // offset of the loaded box relative to the output box, in the coordinates of map `map`
+  int16_t map;     // which activation tensor map
+  int16_t pad_;
+  int32_t kofs;    // first column of this tap in the weight matrix
+};
+
+struct ConvParams {
+  int32_t* error;
+  float* stat_sum;  // optional per-channel sum of the bf16 outputs
+  float* stat_sq;   // optional per-channel sum of squares
+  int taps, cblocks;               // filter taps, 64-channel blocks of the contraction
+  int tiles_w, tiles_h, tiles_n;   // boxes per output extent
+  int tw, th, tn;                  // box extents; tw * th * tn <= 128
+  int wo, ho, nb;                  // output extents (for the statistics mask)
+  int cout, n_tiles;               // output channels and tiles of BN channels
+  ConvTap tap[kMaxTaps];
+};
+
+struct ConvMaps {
+  CUtensorMap a[4];  // activation phases
+  CUtensorMap b;     // weights [Cout, taps * Cin], K-major
+  CUtensorMap c;     // output
+};
+
+__device__ __forceinline__ void TmaLoad4D(void* smem_dst, const CUtensorMap* tmap, int c, int w, int h, int n,
+                                          uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];"
+      ::"r"(SmemAddr(smem_dst)), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(c), "r"(w), "r"(h), "r"(n),
+      "r"(SmemAddr(bar))
+      : "memory");
+}
+__device__ __forceinline__ void TmaStore4D(const CUtensorMap* tmap, int c, int w, int h, int n, const void* smem_src) {
+  asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%1, %2, %3, %4}], [%5];" ::"l"(
+                   reinterpret_cast<uint64_t>(tmap)),
+               "r"(c), "r"(w), "r"(h), "r"(n), "r"(SmemAddr(smem_src))
+               : "memory");
+}
+
+template <int BN>
+struct ConvCfg {
+  static constexpr int kStages       = BN >= 256 ? 3 : 4;
+  static constexpr int kABytes       = kBM * kBK * 2;
+  static constexpr int kBBytes       = BN * kBK * 2;
+  static constexpr int kStageBytes   = kABytes + kBBytes;
+  static constexpr int kStagingBytes = kBM * BN * 2;
+  static constexpr int kTmemCols     = 2 * BN < 32 ? 32 : 2 * BN;
+  static constexpr int kSmemBytes    = kStages * kStageBytes + kStagingBytes + 1024 + 256;
+};
+
+template <int BN>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+ConvTapsKernel(const __grid_constant__ ConvMaps maps, const __grid_constant__ ConvParams p) {
+  using Cfg = ConvCfg<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem    = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* staging = smem + Cfg::kStages * Cfg::kStageBytes;
+  uint64_t* full_bar   = reinterpret_cast<uint64_t*>(staging + Cfg::kStagingBytes);
+  uint64_t* empty_bar  = full_bar + Cfg::kStages;
+  uint64_t* tmem_full  = empty_bar + Cfg::kStages;  // [2]
+  uint64_t* tmem_empty = tmem_full + 2;             // [2]
+  uint32_t* tmem_slot  = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int num_k     = p.taps * p.cblocks;
+  const int m_tiles   = p.tiles_w * p.tiles_h * p.tiles_n;
+  const int num_tiles = m_tiles * p.n_tiles;
+  const int box_rows  = p.tw * p.th * p.tn;
+  const uint32_t stage_tx = static_cast<uint32_t>(box_rows) * 128u + Cfg::kBBytes;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < Cfg::kStages; ++s) {
+      MbarInit(&full_bar[s], 1);
+      MbarInit(&empty_bar[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      MbarInit(&tmem_full[b], 1);
+      MbarInit(&tmem_empty[b], 4);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(SmemAddr(tmem_slot)),
+                 "r"(static_cast<uint32_t>(Cfg::kTmemCols))
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  TcFenceBefore();
+  __syncthreads();
+  TcFenceAfter();
+  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
+
+  if (warp == 0) {
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const int mt = tile / p.n_tiles, nt = tile % p.n_tiles;
+        const int w0 = (mt % p.tiles_w) * p.tw;
+        const int h0 = ((mt / p.tiles_w) % p.tiles_h) * p.th;
+        const int n0 = (mt / (p.tiles_w * p.tiles_h)) * p.tn;
+        for (int t = 0; t < p.taps && ok; ++t) {
+          const ConvTap tap = p.tap[t];
+          for (int cb = 0; cb < p.cblocks; ++cb, ++it) {
+            const int s = it % Cfg::kStages;
+            if (!MbarWait(&empty_bar[s], ((it / Cfg::kStages) & 1) ^ 1)) {
+              atomicExch(p.error, 1);
+              ok = false;
+              break;
+            }
+            uint8_t* a_dst = smem + s * Cfg::kStageBytes;
+            MbarExpectTx(&full_bar[s], stage_tx);
+            TmaLoad4D(a_dst, &maps.a[tap.map], cb * kBK, w0 + tap.dw, h0 + tap.dh, n0, &full_bar[s]);
+            TmaLoad2D(a_dst + Cfg::kABytes, &maps.b, tap.kofs + cb * kBK, nt * BN, &full_bar[s]);
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(BN >> 3) << 17) |
+                                 (static_cast<uint32_t>(kBM >> 4) << 24);
+      uint32_t it = 0;
+      int local = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
+        const int buf = local & 1;
+        if (!MbarWait(&tmem_empty[buf], ((local >> 1) & 1) ^ 1)) {
+          atomicExch(p.error, 4);
+          break;
+        }
+        TcFenceAfter();
+        const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(buf * BN);
+        for (int kt = 0; kt < num_k; ++kt, ++it) {
+          const int s = it % Cfg::kStages;
+          if (!MbarWait(&full_bar[s], (it / Cfg::kStages) & 1)) {
+            atomicExch(p.error, 2);
+            ok = false;
+            break;
+          }
+          TcFenceAfter();
+          const uint32_t a_addr = SmemAddr(smem + s * Cfg::kStageBytes);
+          const uint64_t adesc  = SmemDescSw128(a_addr);
+          const uint64_t bdesc  = SmemDescSw128(a_addr + Cfg::kABytes);
+#pragma unroll
+          for (int k = 0; k < kBK / 16; ++k) UmmaBf16(tmem_d, adesc + 2 * k, bdesc + 2 * k, idesc, (kt > 0 || k > 0) ? 1u : 0u);
+          UmmaCommit(&empty_bar[s]);
+        }
+        if (ok) UmmaCommit(&tmem_full[buf]);
+      }
+    }
+  } else {
+    const int q = warp & 3;
+    const int r = q * 32 + lane;  // row of the tile = pixel of the box
+    const int et = threadIdx.x - 64;  // 0..127 among the epilogue threads
+    int local = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++local) {
+      const int mt = tile / p.n_tiles, nt = tile % p.n_tiles;
+      const int w0 = (mt % p.tiles_w) * p.tw;
+      const int h0 = ((mt / p.tiles_w) % p.tiles_h) * p.th;
+      const int n0 = (mt / (p.tiles_w * p.tiles_h)) * p.tn;
+      const int buf = local & 1;
+      if (ok && !MbarWait(&tmem_full[buf], (local >> 1) & 1)) {
+        if (lane == 0) atomicExch(p.error, 3);
+        ok = false;
+      }
+      TcFenceAfter();
+      if (ok) {
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t acc[32];
+          TmemLoad32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(buf * BN + c * 32), acc);
+          uint8_t* box = staging + (c >> 1) * (kBM * 128);
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            alignas(16) __nv_bfloat16 o[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) o[j] = __float2bfloat16_rn(__uint_as_float(acc[g * 8 + j]));
+            const int chunk = (c & 1) * 4 + g;
+            *reinterpret_cast<uint4*>(box + r * 128 + ((chunk ^ (r & 7)) << 4)) = *reinterpret_cast<uint4*>(o);
+          }
+        }
+        TcFenceBefore();
+        __syncwarp();
+        if (lane == 0) MbarArrive(&tmem_empty[buf]);
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (warp == 2 && lane == 0) {
+        if (ok) {
+#pragma unroll 1
+          for (int b = 0; b < BN / 64; ++b) {
+            if (nt * BN + b * 64 < p.cout) TmaStore4D(&maps.c, nt * BN + b * 64, w0, h0, n0, staging + b * (kBM * 128));
+          }
+          asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        }
+      }
+      if (ok && p.stat_sum != nullptr) {
+        // Per-channel sum and sum of squares of the bf16 values just staged (what the normalisation that
+        // follows will read), over the rows of the box that are real output pixels.
+        for (int col = et; col < BN; col += 128) {
+          const uint8_t* bx = staging + (col >> 6) * (kBM * 128);
+          const int chunk = (col & 63) >> 3, within = (col & 7) * 2;
+          float s1 = 0.f, s2 = 0.f;
+          int row = 0;
+          for (int in = 0; in < p.tn; ++in) {
+            for (int ih = 0; ih < p.th; ++ih) {
+              const bool hv = (n0 + in < p.nb) && (h0 + ih < p.ho);
+              for (int iw = 0; iw < p.tw; ++iw, ++row) {
+                if (hv && w0 + iw < p.wo) {
+                  const float v = __bfloat162float(
+                      *reinterpret_cast<const __nv_bfloat16*>(bx + row * 128 + ((chunk ^ (row & 7)) << 4) + within));
+                  s1 += v;
+                  s2 += v * v;
+                }
+              }
+            }
+          }
+          const int ch = nt * BN + col;
+          if (ch < p.cout) {
+            atomicAdd(p.stat_sum + ch, s1);
+            atomicAdd(p.stat_sq + ch, s2);
+          }
+        }
+      }
+      if (warp == 2 && lane == 0) {
+        asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");  // staging may be overwritten afterwards
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+    }
+  }
+  TcFenceBefore();
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                 "r"(static_cast<uint32_t>(Cfg::kTmemCols))
+                 : "memory");
+  }
+}
+
+// ------------------------------------------------------------------ weight gradient
+// dw[co, tap, ci] = sum over output pixels p of dy[p, co] * x[p*stride + tap - pad, ci].  The contraction runs
+// over pixels, which are the ROWS of both tiles as the TMA unit delivers them, so both operands are
+// MN-major: a 64-channel box is [pixels x 128 bytes], 8-pixel groups 1024 bytes apart, and the next 64
+// channels start one box (16 KB) further.  One CTA owns (tap, 128 output channels, BN input channels) and
+// a contiguous share of the pixel boxes; partial results are added into the fp32 gradient.
+
+struct WgradParams {
+  int32_t* error;
+  float* dw;        // [Cout, taps_total * Cin] fp32, accumulated into
+  int ldw;          // taps_total * Cin
+  int taps;
+  int cout_tiles, cin_tiles;
+  int tiles_w, tiles_h, tiles_n;
+  int tw, th, tn;   // tw * th * tn is a multiple of 16, at most 128
+  int cout, cin;
+  ConvTap tap[kMaxTaps];  // kofs = first column of the tap inside a row of dw
+};
+
+struct WgradMaps {
+  CUtensorMap x[4];  // activation phases
+  CUtensorMap dy;
+};
+
+constexpr int kMnBoxBytes = kBM * 128;  // one 64-channel box of up to 128 pixels
+
+// Descriptor of an MN-major, 128-byte-swizzled operand: leading-dimension offset = distance between
+// 64-element chunks along M/N (one box), stride offset = distance between 8-row groups along K.
+__device__ __forceinline__ uint64_t SmemDescMnSw128(uint32_t smem_addr) {
+  const uint32_t lo = ((smem_addr & 0x3FFFFu) >> 4) | (static_cast<uint32_t>(kMnBoxBytes >> 4) << 16);
+  const uint32_t hi = (1024u >> 4) | (1u << 14) | (2u << 29);
+  return (static_cast<uint64_t>(hi) << 32) | lo;
+}
+
+template <int BN>
+struct WgradCfg {
+  static constexpr int kStages     = BN >= 128 ? 3 : 4;
+  static constexpr int kABytes     = 2 * kMnBoxBytes;
+  static constexpr int kBBytes     = (BN / 64) * kMnBoxBytes;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kTmemCols   = BN;
+  static constexpr int kSmemBytes  = kStages * kStageBytes + 1024 + 256;
+};
+
+template <int BN>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+ConvWgradKernel(const __grid_constant__ WgradMaps maps, const __grid_constant__ WgradParams p) {
+  using Cfg = WgradCfg<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full_bar  = reinterpret_cast<uint64_t*>(smem + Cfg::kStages * Cfg::kStageBytes);
+  uint64_t* empty_bar = full_bar + Cfg::kStages;
+  uint64_t* tmem_full = empty_bar + Cfg::kStages;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_full + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  int id = blockIdx.x;
+  const int cin_t  = id % p.cin_tiles;  id /= p.cin_tiles;
+  const int cout_t = id % p.cout_tiles; id /= p.cout_tiles;
+  const ConvTap tap = p.tap[id];
+  const int box_rows = p.tw * p.th * p.tn;
+  const int k_tiles  = p.tiles_w * p.tiles_h * p.tiles_n;
+  const int k_begin  = static_cast<int>(static_cast<int64_t>(k_tiles) * blockIdx.y / gridDim.y);
+  const int k_end    = static_cast<int>(static_cast<int64_t>(k_tiles) * (blockIdx.y + 1) / gridDim.y);
+  const int num_k    = k_end - k_begin;
+  const uint32_t stage_tx = static_cast<uint32_t>(box_rows) * 128u * (2 + BN / 64);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < Cfg::kStages; ++s) {
+      MbarInit(&full_bar[s], 1);
+      MbarInit(&empty_bar[s], 1);
+    }
+    MbarInit(tmem_full, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(SmemAddr(tmem_slot)),
+                 "r"(static_cast<uint32_t>(Cfg::kTmemCols))
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  TcFenceBefore();
+  __syncthreads();
+  TcFenceAfter();
+  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
+
+  if (warp == 0) {
+    if (lane == 0) {
+      for (int kt = 0; kt < num_k; ++kt) {
+        const int s = kt % Cfg::kStages;
+        if (!MbarWait(&empty_bar[s], ((kt / Cfg::kStages) & 1) ^ 1)) {
+          atomicExch(p.error, 1);
+          break;
+        }
+        const int mt = k_begin + kt;
+        const int w0 = (mt % p.tiles_w) * p.tw;
+        const int h0 = ((mt / p.tiles_w) % p.tiles_h) * p.th;
+        const int n0 = (mt / (p.tiles_w * p.tiles_h)) * p.tn;
+        uint8_t* a_dst = smem + s * Cfg::kStageBytes;
+        uint8_t* b_dst = a_dst + Cfg::kABytes;
+        MbarExpectTx(&full_bar[s], stage_tx);
+#pragma unroll
+        for (int j = 0; j < 2; ++j)
+          TmaLoad4D(a_dst + j * kMnBoxBytes, &maps.dy, cout_t * kBM + j * 64, w0, h0, n0, &full_bar[s]);
+#pragma unroll
+        for (int j = 0; j < BN / 64; ++j)
+          TmaLoad4D(b_dst + j * kMnBoxBytes, &maps.x[tap.map], cin_t * BN + j * 64, w0 + tap.dw, h0 + tap.dh, n0,
+                    &full_bar[s]);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      // both operands MN-major: bits 15 and 16
+      constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 15) | (1u << 16) |
+                                 (static_cast<uint32_t>(BN >> 3) << 17) | (static_cast<uint32_t>(kBM >> 4) << 24);
+      const int ksteps = box_rows / 16;
+      bool ok = true;
+      for (int kt = 0; kt < num_k && ok; ++kt) {
+        const int s = kt % Cfg::kStages;
+        if (!MbarWait(&full_bar[s], (kt / Cfg::kStages) & 1)) {
+          atomicExch(p.error, 2);
+          ok = false;
+          break;
+        }
+        TcFenceAfter();
+        const uint32_t a_addr = SmemAddr(smem + s * Cfg::kStageBytes);
+        const uint64_t adesc  = SmemDescMnSw128(a_addr);
+        const uint64_t bdesc  = SmemDescMnSw128(a_addr + Cfg::kABytes);
+        for (int k = 0; k < ksteps; ++k) {
+          // 16 pixels further along K = 16 rows of 128 bytes
+          UmmaBf16(tmem_base, adesc + static_cast<uint64_t>(k) * (2048 >> 4), bdesc + static_cast<uint64_t>(k) * (2048 >> 4),
+                   idesc, (kt > 0 || k > 0) ? 1u : 0u);
+        }
+        UmmaCommit(&empty_bar[s]);
+      }
+      UmmaCommit(tmem_full);
+    }
+  } else {
+    const int q = warp & 3;
+    const bool ok = MbarWait(tmem_full, 0);
+    if (!ok && lane == 0) atomicExch(p.error, 3);
+    TcFenceAfter();
+    const int row = cout_t * kBM + q * 32 + lane;
+    if (ok && num_k > 0) {
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t acc[32];
+        TmemLoad32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(c * 32), acc);
+        const int col0 = cin_t * BN + c * 32;
+        if (row < p.cout && col0 < p.cin) {
+          float* dst = p.dw + static_cast<int64_t>(row) * p.ldw + tap.kofs + col0;
+#pragma unroll
+          for (int g = 0; g < 8; ++g) {
+            asm volatile("red.relaxed.gpu.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + g * 4),
+                         "f"(__uint_as_float(acc[g * 4])), "f"(__uint_as_float(acc[g * 4 + 1])),
+                         "f"(__uint_as_float(acc[g * 4 + 2])), "f"(__uint_as_float(acc[g * 4 + 3]))
+                         : "memory");
+          }
+        }
+      }
+    }
+  }
+  TcFenceBefore();
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                 "r"(static_cast<uint32_t>(Cfg::kTmemCols))
+                 : "memory");
+  }
+}
+
+// ------------------------------------------------------------------ host side
+
+struct Box {
+  int tw, th, tn;
+};
+
+// Box of at most 128 pixels that covers the extents (wo, ho, nb) with the fewest tiles; `mult16` restricts the
+// pixel count to multiples of 16 (one MMA K step) for the weight gradient.
+Box PickBox(int wo, int ho, int nb, bool mult16) {
+  Box best{1, 1, 1};
+  int64_t best_tiles = INT64_MAX;
+  for (int tw = 1; tw <= std::min(wo, 128); ++tw) {
+    for (int th = 1; th <= std::min(ho, 128 / tw); ++th) {
+      const int tn = std::max(1, std::min(nb, 128 / (tw * th)));
+      if (mult16 && (tw * th * tn) % 16 != 0) continue;
+      const int64_t tiles = static_cast<int64_t>(CeilDiv(wo, tw)) * CeilDiv(ho, th) * CeilDiv(nb, tn);
+      if (tiles < best_tiles || (tiles == best_tiles && tw > best.tw)) {
+        best_tiles = tiles;
+        best = Box{tw, th, tn};
+      }
+    }
+  }
+  if (best_tiles == INT64_MAX) {  // mult16 with tiny extents: rely on the zero fill beyond the extents
+    best = Box{16, 1, 1};
+  }
+  return best;
+}
+
+// Tensor map over a bf16 NHWC view: extents (c, w, h, n), strides in elements, box (64, tw, th, tn), 128B swizzle.
+int MakeTmap4D(CUtensorMap* out, const void* base, int64_t c, int64_t w, int64_t h, int64_t n, int64_t sw, int64_t sh,
+               int64_t sn, const Box& box) {
+  EncodeFn enc = GetEncodeFn();
+  if (!enc) return SetError(-7, "cuTensorMapEncodeTiled is not available from the driver");
+  if (reinterpret_cast<uintptr_t>(base) % 16 != 0) return SetError(-2, "conv: tensor base must be 16-byte aligned");
+  if (c % 8 != 0) return SetError(-2, "conv: channel count must be a multiple of 8");
+  cuuint64_t dims[4]    = {static_cast<cuuint64_t>(c), static_cast<cuuint64_t>(w), static_cast<cuuint64_t>(h),
+                           static_cast<cuuint64_t>(n)};
+  cuuint64_t strides[3] = {static_cast<cuuint64_t>(sw) * 2, static_cast<cuuint64_t>(sh) * 2,
+                           static_cast<cuuint64_t>(sn) * 2};
+  cuuint32_t bx[4]      = {static_cast<cuuint32_t>(kBK), static_cast<cuuint32_t>(box.tw), static_cast<cuuint32_t>(box.th),
+                           static_cast<cuuint32_t>(box.tn)};
+  cuuint32_t estr[4]    = {1, 1, 1, 1};
+  CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, bx, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return SetError(-7, "cuTensorMapEncodeTiled (4-D) failed with code " + std::to_string((int)r));
+  return 0;
+}
+
+int MakeTmap2D(CUtensorMap* out, const void* base, int64_t rows, int64_t cols, int box_rows) {
+  EncodeFn enc = GetEncodeFn();
+  if (!enc) return SetError(-7, "cuTensorMapEncodeTiled is not available from the driver");
+  if (reinterpret_cast<uintptr_t>(base) % 16 != 0) return SetError(-2, "conv: weight base must be 16-byte aligned");
+  cuuint64_t dims[2]    = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+  cuuint64_t strides[1] = {static_cast<cuuint64_t>(cols) * 2};
+  cuuint32_t bx[2]      = {static_cast<cuuint32_t>(kBK), static_cast<cuuint32_t>(box_rows)};
+  cuuint32_t estr[2]    = {1, 1};
+  CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, bx, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return SetError(-7, "cuTensorMapEncodeTiled (weights) failed with code " + std::to_string((int)r));
+  return 0;
+}
+
+// A view of an NHWC tensor in which (w, h) extents and strides may be those of a stride-2 parity class,
+// or the pixels flattened into one axis.
+struct View {
+  const void* base;
+  int64_t c, w, h, n;     // extents
+  int64_t sw, sh, sn;     // strides in elements
+};
+
+View FullView(const void* base, int n, int h, int w, int c) {
+  return View{base, c, w, h, n, c, static_cast<int64_t>(w) * c, static_cast<int64_t>(h) * w * c};
+}
+View FlatView(const void* base, int n, int h, int w, int c) {  // all pixels on the w axis
+  const int64_t px = static_cast<int64_t>(n) * h * w;
+  return View{base, c, px, 1, 1, c, px * c, px * c};
+}
+View PhaseView(const void* base, int n, int h, int w, int c, int bh, int bw) {
+  const char* b = static_cast<const char*>(base) + (static_cast<int64_t>(bh) * w + bw) * c * 2;
+  return View{b, c, (w - bw + 1) / 2, (h - bh + 1) / 2, n, 2 * static_cast<int64_t>(c), 2 * static_cast<int64_t>(w) * c,
+              static_cast<int64_t>(h) * w * c};
+}
+int MapOf(CUtensorMap* out, const View& v, const Box& box) {
+  return MakeTmap4D(out, v.base, v.c, v.w, v.h, v.n, v.sw, v.sh, v.sn, box);
+}
+
+int32_t* ConvErrorWord() {
+  static int32_t* word = nullptr;
+  if (!word) {
+    if (cudaMalloc(reinterpret_cast<void**>(&word), sizeof(int32_t)) != cudaSuccess) return nullptr;
+    cudaMemset(word, 0, sizeof(int32_t));
+  }
+  return word;
+}
+
+template <int BN>
+int LaunchTaps(const ConvMaps& maps, const ConvParams& p, cudaStream_t s) {
+  using Cfg = ConvCfg<BN>;
+  static bool configured = false;
+  if (!configured) {
+    TIPSK_CUDA(cudaFuncSetAttribute(ConvTapsKernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
+    configured = true;
+  }
+  const int64_t tiles = static_cast<int64_t>(p.tiles_w) * p.tiles_h * p.tiles_n * p.n_tiles;
+  const int grid = static_cast<int>(std::min<int64_t>(tiles, NumSMs()));
+  ConvTapsKernel<BN><<<grid, kGemmThreads, Cfg::kSmemBytes, s>>>(maps, p);
+  TIPSK_LAUNCH_CHECK();
+  return 0;
+}
+
+template <int BN>
+int LaunchWgrad(const WgradMaps& maps, const WgradParams& p, int splits, cudaStream_t s) {
+  using Cfg = WgradCfg<BN>;
+  static bool configured = false;
+  if (!configured) {
+    TIPSK_CUDA(cudaFuncSetAttribute(ConvWgradKernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
+    configured = true;
+  }
+  dim3 grid(p.taps * p.cout_tiles * p.cin_tiles, splits);
+  ConvWgradKernel<BN><<<grid, kGemmThreads, Cfg::kSmemBytes, s>>>(maps, p);
+  TIPSK_LAUNCH_CHECK();
+  return 0;
+}
+
+// Runs the tap kernel: out[view_out pixel, co] = sum over taps and 64-channel blocks.
+int RunTaps(const View* in_views, int n_views, const ConvTap* taps, int n_taps, int cin, const void* weights,
+            int w_rows, int64_t w_cols, const View& out, float* stat_sum, float* stat_sq, cudaStream_t s) {
+  TIPSK_REQUIRE(n_taps >= 1 && n_taps <= kMaxTaps, "conv: 1..9 filter taps are supported");
+  TIPSK_REQUIRE(cin % 64 == 0, "conv: the contracted channel count must be a multiple of 64");
+  TIPSK_REQUIRE(w_rows % 64 == 0, "conv: the produced channel count must be a multiple of 64");
+  const Box box = PickBox(static_cast<int>(out.w), static_cast<int>(out.h), static_cast<int>(out.n), false);
+  ConvMaps maps;
+  ConvParams p{};
+  p.tiles_w = CeilDiv(out.w, box.tw);
+  p.tiles_h = CeilDiv(out.h, box.th);
+  p.tiles_n = CeilDiv(out.n, box.tn);
+  const int64_t m_tiles = static_cast<int64_t>(p.tiles_w) * p.tiles_h * p.tiles_n;
+  int bn = 128;
+  if (w_rows % 128 != 0) bn = 64;
+  else if (w_rows % 256 == 0 && m_tiles * (w_rows / 256) >= NumSMs()) bn = 256;
+  int rc;
+  for (int i = 0; i < n_views; ++i) {
+    rc = MapOf(&maps.a[i], in_views[i], box);
+    if (rc) return rc;
+  }
+  for (int i = n_views; i < 4; ++i) maps.a[i] = maps.a[0];
+  rc = MakeTmap2D(&maps.b, weights, w_rows, w_cols, bn);
+  if (rc) return rc;
+  rc = MapOf(&maps.c, out, box);
+  if (rc) return rc;
+  p.error = ConvErrorWord();
+  TIPSK_REQUIRE(p.error != nullptr, "conv: cannot allocate the error word");
+  p.stat_sum = stat_sum;
+  p.stat_sq  = stat_sq;
+  p.taps = n_taps;
+  p.cblocks = cin / 64;
+  p.tw = box.tw; p.th = box.th; p.tn = box.tn;
+  p.wo = static_cast<int>(out.w); p.ho = static_cast<int>(out.h); p.nb = static_cast<int>(out.n);
+  p.cout = w_rows;
+  p.n_tiles = CeilDiv(w_rows, bn);
+  for (int i = 0; i < n_taps; ++i) p.tap[i] = taps[i];
+  switch (bn) {
+    case 64: return LaunchTaps<64>(maps, p, s);
+    case 256: return LaunchTaps<256>(maps, p, s);
+    default: return LaunchTaps<128>(maps, p, s);
+  }
+}
+
+// Tap list of a forward-style gather: input coordinate = stride * out + (f - pad).
+int ForwardTaps(int r, int s, int stride, int pad, int cin, ConvTap* taps) {
+  int n = 0;
+  for (int fr = 0; fr < r; ++fr) {
+    for (int fs = 0; fs < s; ++fs) {
+      const int oh = fr - pad, ow = fs - pad;
+      ConvTap t{};
+      if (stride == 1) {
+        t.dh = static_cast<int16_t>(oh); t.dw = static_cast<int16_t>(ow); t.map = 0;
+      } else {
+        const int bh = oh & 1, bw = ow & 1;
+        t.dh = static_cast<int16_t>((oh - bh) / 2); t.dw = static_cast<int16_t>((ow - bw) / 2);
+        t.map = static_cast<int16_t>(bh * 2 + bw);
+      }
+      t.kofs = (fr * s + fs) * cin;
+      taps[n++] = t;
+    }
+  }
+  return n;
+}
+
+}  // namespace
+}  // namespace tipsk
+
+using namespace tipsk;
+
+extern "C" {
+
+/* 1 when the tcgen05 convolution kernels accept the problem. */
+int tipsk_conv2d_supported(int cin, int cout, int r, int s, int stride, int pad) {
+  return (cin % 64 == 0 && cout % 64 == 0 && r == s && (r == 1 || r == 3) && (stride == 1 || stride == 2) &&
+          pad == r / 2) ? 1 : 0;
+}
+
+/* y[n, ho, wo, cout] = conv(x[n, h, w, cin], wgt[cout, r, s, cin]); bf16 NHWC, fp32 accumulation.
+ * stat_sum / stat_sq (optional, fp32 [cout], zeroed by the caller) receive the per-channel sum and sum of
+ * squares of the bf16 outputs. */
+int tipsk_conv2d_fwd(const void* x, const void* wgt, void* y, int n, int h, int w, int cin, int cout, int r, int s,
+                     int stride, int pad, float* stat_sum, float* stat_sq, void* stream) {
+  TIPSK_REQUIRE(tipsk_conv2d_supported(cin, cout, r, s, stride, pad), "conv2d_fwd: unsupported shape");
+  const int ho = (h + 2 * pad - r) / stride + 1, wo = (w + 2 * pad - s) / stride + 1;
+  ConvTap taps[kMaxTaps];
+  const int nt = ForwardTaps(r, s, stride, pad, cin, taps);
+  View views[4];
+  int nv = 1;
+  View out = FullView(y, n, ho, wo, cout);
+  if (stride == 1) {
+    if (r == 1) {
+      views[0] = FlatView(x, n, h, w, cin);
+      out      = FlatView(y, n, ho, wo, cout);
+    } else {
+      views[0] = FullView(x, n, h, w, cin);
+    }
+  } else {
+    nv = 4;
+    for (int b = 0; b < 4; ++b) views[b] = PhaseView(x, n, h, w, cin, b >> 1, b & 1);
+  }
+  return RunTaps(views, nv, taps, nt, cin, wgt, cout, static_cast<int64_t>(r) * s * cin, out, stat_sum, stat_sq,
+                 static_cast<cudaStream_t>(stream));
+}
+
+/* dx[n, h, w, cin] = data gradient; wgt_t is the weight permuted to [cin, r, s, cout]. */
+int tipsk_conv2d_dgrad(const void* dy, const void* wgt_t, void* dx, int n, int h, int w, int cin, int cout, int r,
+                       int s, int stride, int pad, void* stream) {
+  TIPSK_REQUIRE(tipsk_conv2d_supported(cin, cout, r, s, stride, pad), "conv2d_dgrad: unsupported shape");
+  const int ho = (h + 2 * pad - r) / stride + 1, wo = (w + 2 * pad - s) / stride + 1;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int64_t w_cols = static_cast<int64_t>(r) * s * cout;
+  if (stride == 1) {
+    ConvTap taps[kMaxTaps];
+    int nt = 0;
+    for (int fr = 0; fr < r; ++fr)
+      for (int fs = 0; fs < s; ++fs) {
+        ConvTap t{};
+        t.dh = static_cast<int16_t>(pad - fr); t.dw = static_cast<int16_t>(pad - fs); t.map = 0;
+        t.kofs = (fr * s + fs) * cout;
+        taps[nt++] = t;
+      }
+    View in  = r == 1 ? FlatView(dy, n, ho, wo, cout) : FullView(dy, n, ho, wo, cout);
+    View out = r == 1 ? FlatView(dx, n, h, w, cin) : FullView(dx, n, h, w, cin);
+    return RunTaps(&in, 1, taps, nt, cout, wgt_t, cin, w_cols, out, nullptr, nullptr, st);
+  }
+  // stride 2: the input pixels of parity class (bh, bw) receive the taps with (b + pad - f) even
+  const View in = FullView(dy, n, ho, wo, cout);
+  if (r == 1) {
+    // a 1x1 filter only reaches the even pixels: the other three classes receive no gradient
+    TIPSK_CUDA(cudaMemsetAsync(dx, 0, static_cast<size_t>(n) * h * w * cin * 2, st));
+  }
+  for (int b = 0; b < 4; ++b) {
+    const int bh = b >> 1, bw = b & 1;
+    ConvTap taps[kMaxTaps];
+    int nt = 0;
+    for (int fr = 0; fr < r; ++fr) {
+      if ((bh + pad - fr) & 1) continue;
+      for (int fs = 0; fs < s; ++fs) {
+        if ((bw + pad - fs) & 1) continue;
+        ConvTap t{};
+        t.dh = static_cast<int16_t>((bh + pad - fr) / 2); t.dw = static_cast<int16_t>((bw + pad - fs) / 2); t.map = 0;
+        t.kofs = (fr * s + fs) * cout;
+        taps[nt++] = t;
+      }
+    }
+    if (nt == 0) continue;
+    const View out = PhaseView(dx, n, h, w, cin, bh, bw);
+    if (out.w <= 0 || out.h <= 0) continue;
+    int rc = RunTaps(&in, 1, taps, nt, cout, wgt_t, cin, w_cols, out, nullptr, nullptr, st);
+    if (rc) return rc;
+  }
+  return 0;
+}
+
+/* dw[cout, r, s, cin] (fp32, overwritten) = weight gradient of the convolution. */
+int tipsk_conv2d_wgrad(const void* x, const void* dy, float* dw, int n, int h, int w, int cin, int cout, int r, int s,
+                       int stride, int pad, void* stream) {
+  TIPSK_REQUIRE(tipsk_conv2d_supported(cin, cout, r, s, stride, pad), "conv2d_wgrad: unsupported shape");
+  const int ho = (h + 2 * pad - r) / stride + 1, wo = (w + 2 * pad - s) / stride + 1;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  WgradMaps maps;
+  WgradParams p{};
+  p.taps = ForwardTaps(r, s, stride, pad, cin, p.tap);
+  const bool flat = (r == 1 && stride == 1);
+  const View dyv = flat ? FlatView(dy, n, ho, wo, cout) : FullView(dy, n, ho, wo, cout);
+  const Box box  = PickBox(static_cast<int>(dyv.w), static_cast<int>(dyv.h), static_cast<int>(dyv.n), true);
+  int rc = MapOf(&maps.dy, dyv, box);
+  if (rc) return rc;
+  if (stride == 1) {
+    rc = MapOf(&maps.x[0], flat ? FlatView(x, n, h, w, cin) : FullView(x, n, h, w, cin), box);
+    if (rc) return rc;
+    for (int b = 1; b < 4; ++b) maps.x[b] = maps.x[0];
+  } else {
+    for (int b = 0; b < 4; ++b) {
+      rc = MapOf(&maps.x[b], PhaseView(x, n, h, w, cin, b >> 1, b & 1), box);
+      if (rc) return rc;
+    }
+  }
+  p.error = ConvErrorWord();
+  TIPSK_REQUIRE(p.error != nullptr, "conv: cannot allocate the error word");
+  p.dw  = dw;
+  p.ldw = r * s * cin;
+  const int bn = cin % 128 == 0 ? 128 : 64;
+  p.cout_tiles = CeilDiv(cout, kBM);
+  p.cin_tiles  = CeilDiv(cin, bn);
+  p.tiles_w = CeilDiv(dyv.w, box.tw);
+  p.tiles_h = CeilDiv(dyv.h, box.th);
+  p.tiles_n = CeilDiv(dyv.n, box.tn);
+  p.tw = box.tw; p.th = box.th; p.tn = box.tn;
+  p.cout = cout; p.cin = cin;
+  const int64_t k_tiles = static_cast<int64_t>(p.tiles_w) * p.tiles_h * p.tiles_n;
+  const int base = p.taps * p.cout_tiles * p.cin_tiles;
+  int splits = CeilDiv(2 * NumSMs(), base);
+  if (splits > k_tiles) splits = static_cast<int>(k_tiles);
+  if (splits < 1) splits = 1;
+  TIPSK_CUDA(cudaMemsetAsync(dw, 0, sizeof(float) * static_cast<size_t>(cout) * p.ldw, st));
+  return bn == 128 ? LaunchWgrad<128>(maps, p, splits, st) : LaunchWgrad<64>(maps, p, splits, st);
+}
+
+/* Reads and clears the convolution error word (0 ok; 1/2/3/4 = which wait ran out). Synchronises. */
+int tipsk_conv_status(void) {
+  int32_t* w = ConvErrorWord();
+  if (!w) return -7;
+  int32_t v = 0;
+  if (cudaMemcpy(&v, w, sizeof(v), cudaMemcpyDeviceToHost) != cudaSuccess) return -7;
+  if (v) cudaMemset(w, 0, sizeof(v));
+  return v;
+}
+
+}  // extern "C"

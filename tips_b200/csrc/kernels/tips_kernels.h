@@ -130,6 +130,16 @@ int tipsk_gemm_bf16(const void* a, const void* b, void* c, const void* bias, voi
                     int ldb, int ldc, int act, void* stream);
 int tipsk_gemm_status(void);
 
+/* ---- NHWC bf16 convolutions on tcgen05 (conv_tcgen05.cu): 1x1 and 3x3, stride 1 or 2, pad = r/2 ---- */
+int tipsk_conv2d_supported(int cin, int cout, int r, int s, int stride, int pad);
+int tipsk_conv2d_fwd(const void* x, const void* wgt, void* y, int n, int h, int w, int cin, int cout, int r, int s,
+                     int stride, int pad, float* stat_sum, float* stat_sq, void* stream);
+int tipsk_conv2d_dgrad(const void* dy, const void* wgt_t, void* dx, int n, int h, int w, int cin, int cout, int r,
+                       int s, int stride, int pad, void* stream);
+int tipsk_conv2d_wgrad(const void* x, const void* dy, float* dw, int n, int h, int w, int cin, int cout, int r, int s,
+                       int stride, int pad, void* stream);
+int tipsk_conv_status(void);
+
 #ifdef __cplusplus
 }
 #endif

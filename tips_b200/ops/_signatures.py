@@ -60,6 +60,11 @@ _PROTOS = {
     "tipsk_gemm_bf16": (I, [P, P, P, P, P, I, I, I, I, I, I, I, P]),
     "tipsk_gemm_supported": (I, [I, I, I, I, I]),
     "tipsk_gemm_status": (I, []),
+    "tipsk_conv2d_supported": (I, [I, I, I, I, I, I]),
+    "tipsk_conv2d_fwd": (I, [P, P, P, I, I, I, I, I, I, I, I, I, P, P, P]),
+    "tipsk_conv2d_dgrad": (I, [P, P, P, I, I, I, I, I, I, I, I, I, P]),
+    "tipsk_conv2d_wgrad": (I, [P, P, P, I, I, I, I, I, I, I, I, I, P]),
+    "tipsk_conv_status": (I, []),
 }
 
 

@@ -1,0 +1,119 @@
+"""Channels-last bf16 convolution backed by the tcgen05 implicit-GEMM kernels (csrc/kernels/conv_tcgen05.cu).
+
+``Conv2d`` keeps its weight as ``[C_out, R, S, C_in]`` (the K-major operand layout of the kernels) and takes
+activations that are NCHW tensors in ``channels_last`` memory format, i.e. NHWC in memory.  Forward, data
+gradient and weight gradient all run on the tensor cores through TMA-loaded shifted boxes; nothing is
+unfolded.  Shapes the kernels do not cover (the 7x7 stem with 3 input channels, CPU tensors, other dtypes)
+go through ``torch.nn.functional.conv2d`` on a permuted view of the same weight.
+
+The reference has no convolution of its own: its evaluated model is a TensorFlow ResNet-50 (README.md:12).
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from . import base
+
+
+def supported(x: torch.Tensor, weight: torch.Tensor, stride: int, padding: int) -> bool:
+    if not (x.is_cuda and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and x.dim() == 4):
+        return False
+    cout, r, s, cin = weight.shape
+    return bool(base.K().tipsk_conv2d_supported(cin, cout, r, s, stride, padding))
+
+
+def _nhwc(t: torch.Tensor) -> torch.Tensor:
+    return t.contiguous(memory_format=torch.channels_last)
+
+
+def conv2d_forward(x, weight, stride, padding, stats=None):
+    """y = conv(x, weight); `stats` = (sum, sumsq) fp32 [C_out] tensors, zeroed by the caller, that receive the
+    per-channel statistics of the bf16 output from the kernel's epilogue."""
+    xc = _nhwc(x)
+    n, cin, h, w = xc.shape
+    cout, r, s, _ = weight.shape
+    ho = (h + 2 * padding - r) // stride + 1
+    wo = (w + 2 * padding - s) // stride + 1
+    y = torch.empty((n, cout, ho, wo), dtype=x.dtype, device=x.device, memory_format=torch.channels_last)
+    wc = weight.contiguous()
+    base.check(base.K().tipsk_conv2d_fwd(
+        xc.data_ptr(), wc.data_ptr(), y.data_ptr(), n, h, w, cin, cout, r, s, stride, padding,
+        base.ptr(stats[0]) if stats else None, base.ptr(stats[1]) if stats else None, base.stream()), "conv2d_fwd")
+    return xc, y
+
+
+def conv2d_dgrad(dy, weight, x_shape, stride, padding):
+    n, cin, h, w = x_shape
+    cout, r, s, _ = weight.shape
+    dyc = _nhwc(dy)
+    wt = weight.permute(3, 1, 2, 0).contiguous()  # [C_in, R, S, C_out]
+    dx = torch.empty(x_shape, dtype=dy.dtype, device=dy.device, memory_format=torch.channels_last)
+    launches = 1 if stride == 1 else (1 if r == 1 else 4)
+    base.check(base.K().tipsk_conv2d_dgrad(
+        dyc.data_ptr(), wt.data_ptr(), dx.data_ptr(), n, h, w, cin, cout, r, s, stride, padding, base.stream()),
+        "conv2d_dgrad")
+    base.count_launches(launches - 1)
+    return dx
+
+
+def conv2d_wgrad(x, dy, weight_shape, stride, padding):
+    cout, r, s, cin = weight_shape
+    xc, dyc = _nhwc(x), _nhwc(dy)
+    n, _, h, w = xc.shape
+    dw = torch.empty(weight_shape, dtype=torch.float32, device=x.device)
+    base.check(base.K().tipsk_conv2d_wgrad(
+        xc.data_ptr(), dyc.data_ptr(), dw.data_ptr(), n, h, w, cin, cout, r, s, stride, padding, base.stream()),
+        "conv2d_wgrad")
+    return dw
+
+
+class _Conv2dFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight, stride, padding, stats):
+        xc, y = conv2d_forward(x, weight, stride, padding, stats)
+        ctx.save_for_backward(xc, weight)
+        ctx.stride, ctx.padding = stride, padding
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        xc, weight = ctx.saved_tensors
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            dx = conv2d_dgrad(dy, weight, tuple(xc.shape), ctx.stride, ctx.padding)
+        if ctx.needs_input_grad[1]:
+            dw = conv2d_wgrad(xc, dy, tuple(weight.shape), ctx.stride, ctx.padding).to(weight.dtype)
+        return dx, dw, None, None, None
+
+
+def conv2d(x, weight, stride=1, padding=0, stats=None):
+    """Convolution of a channels-last activation with an ``[C_out, R, S, C_in]`` weight."""
+    if supported(x, weight, stride, padding):
+        return _Conv2dFn.apply(x, weight, stride, padding, stats)
+    if stats is not None:
+        raise ValueError("fused output statistics need a shape the tcgen05 kernels cover")
+    return F.conv2d(x, weight.permute(0, 3, 1, 2), stride=stride, padding=padding)
+
+
+class Conv2d(nn.Module):
+    """Bias-free 2-D convolution with an ``[C_out, R, S, C_in]`` weight."""
+
+    def __init__(self, in_channels, out_channels, kernel_size, stride=1, padding=0):
+        super().__init__()
+        self.in_channels, self.out_channels = in_channels, out_channels
+        self.kernel_size, self.stride, self.padding = kernel_size, stride, padding
+        self.weight = nn.Parameter(torch.empty(out_channels, kernel_size, kernel_size, in_channels))
+        # He initialisation on the fan-out, the usual choice for ResNets
+        std = math.sqrt(2.0 / (out_channels * kernel_size * kernel_size))
+        nn.init.normal_(self.weight, 0.0, std)
+
+    def forward(self, x, stats=None):
+        return conv2d(x, self.weight, self.stride, self.padding, stats)
+
+    def extra_repr(self):
+        return (f"{self.in_channels}, {self.out_channels}, kernel_size={self.kernel_size}, stride={self.stride}, "
+                f"padding={self.padding}, layout=OHWI")

@@ -1,6 +1,6 @@
 """Single-GPU kernel microbenchmarks with roofline fractions against MEASURED_PEAKS.json.
 
-    python -m tips_b200.bench.kernel_bench [--only gemm,bn,ln,optim,ps] [--json out.json]
+    python -m tips_b200.bench.kernel_bench [--only gemm,bn,ln,optim,ps,conv] [--json out.json]
 
 Timing: CUDA events on the launching stream, >= 3 warm-up launches, inputs larger than L2 (or an L2 flush
 between launches for the small ones); every figure is "of measured" copy bandwidth / cuBLAS bf16 throughput.
@@ -166,6 +166,61 @@ def bench_ps(out):
     print(out[-1], flush=True)
 
 
+# The distinct convolutions of ResNet-50 v1.5 at 224x224 (stem excluded): h = w of the input, cin, cout, k, stride.
+RESNET50_CONVS = [
+    (56, 64, 64, 1, 1), (56, 64, 64, 3, 1), (56, 64, 256, 1, 1), (56, 256, 64, 1, 1),
+    (56, 256, 128, 1, 1), (56, 128, 128, 3, 2), (28, 128, 512, 1, 1), (56, 256, 512, 1, 2),
+    (28, 512, 128, 1, 1), (28, 128, 128, 3, 1),
+    (28, 512, 256, 1, 1), (28, 256, 256, 3, 2), (14, 256, 1024, 1, 1), (28, 512, 1024, 1, 2),
+    (14, 1024, 256, 1, 1), (14, 256, 256, 3, 1),
+    (14, 1024, 512, 1, 1), (14, 512, 512, 3, 2), (7, 512, 2048, 1, 1), (14, 1024, 2048, 1, 2),
+    (7, 2048, 512, 1, 1), (7, 512, 512, 3, 1),
+]
+
+
+def bench_conv(out, batch=256):
+    """Forward / data-gradient / weight-gradient time of every ResNet-50 convolution shape: the tcgen05 kernels
+    against the library convolution on the same channels-last bf16 tensors."""
+    import torch.nn.functional as F
+    from tips_b200.ops import conv as C
+    pk = peaks()
+    for (hw, cin, cout, k, stride) in RESNET50_CONVS:
+        pad = k // 2
+        x = torch.randn(batch, cin, hw, hw, device="cuda").to(torch.bfloat16).contiguous(memory_format=torch.channels_last)
+        w = (torch.randn(cout, k, k, cin, device="cuda") * 0.05).to(torch.bfloat16)
+        w_lib = w.permute(0, 3, 1, 2)  # OIHW view with channels-last strides
+        _, y = C.conv2d_forward(x, w, stride, pad)
+        dy = torch.randn_like(y)
+        ho = y.shape[2]
+        flops = 2.0 * batch * ho * ho * cout * cin * k * k
+        row = {"kernel": "conv", "hw": hw, "cin": cin, "cout": cout, "k": k, "stride": stride, "gflop": flops / 1e9}
+        ours = {
+            "fwd": lambda: C.conv2d_forward(x, w, stride, pad),
+            "dgrad": lambda: C.conv2d_dgrad(dy, w, tuple(x.shape), stride, pad),
+            "wgrad": lambda: C.conv2d_wgrad(x, dy, tuple(w.shape), stride, pad),
+        }
+        lib = {
+            "fwd": lambda: F.conv2d(x, w_lib, stride=stride, padding=pad),
+            "dgrad": lambda: torch.ops.aten.convolution_backward(
+                dy, x, w_lib, None, [stride, stride], [pad, pad], [1, 1], False, [0, 0], 1, [True, False, False]),
+            "wgrad": lambda: torch.ops.aten.convolution_backward(
+                dy, x, w_lib, None, [stride, stride], [pad, pad], [1, 1], False, [0, 0], 1, [False, True, False]),
+        }
+        for name in ("fwd", "dgrad", "wgrad"):
+            ms = time_ms(ours[name], iters=10, flush=True)
+            ms_lib = time_ms(lib[name], iters=10, flush=True)
+            row[name + "_ms"] = round(ms, 4)
+            row[name + "_lib_ms"] = round(ms_lib, 4)
+            row[name + "_tflops"] = round(flops / ms / 1e9, 1)
+            row[name + "_speedup_vs_lib"] = round(ms_lib / ms, 3)
+        row["fwd_frac_of_" + pk["source"] + "_gemm"] = round(row["fwd_tflops"] / pk["bf16_tflops"], 3)
+        out.append(row)
+        print(row, flush=True)
+    tot = {n: sum(r[n + "_ms"] for r in out if r.get("kernel") == "conv") for n in ("fwd", "dgrad", "wgrad")}
+    tot_lib = {n: sum(r[n + "_lib_ms"] for r in out if r.get("kernel") == "conv") for n in ("fwd", "dgrad", "wgrad")}
+    print({"conv_total_ms": tot, "conv_total_lib_ms": tot_lib}, flush=True)
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("--only", default="gemm,bn,ln,optim,ps")
@@ -173,7 +228,7 @@ def main(argv=None):
     a = ap.parse_args(argv)
     sys.path.insert(0, REPO)
     out = []
-    table = {"gemm": bench_gemm, "bn": bench_bn, "ln": bench_ln, "optim": bench_optim, "ps": bench_ps}
+    table = {"gemm": bench_gemm, "bn": bench_bn, "ln": bench_ln, "optim": bench_optim, "ps": bench_ps, "conv": bench_conv}
     for k in a.only.split(","):
         table[k](out)
     if a.json:

@@ -3,6 +3,8 @@ CTR parameter-server model.  Each returns the device-timed rate with resident in
 and the end-to-end rate with per-step host-to-device input copies and a loss read-back (`e2e`)."""
 from __future__ import annotations
 
+import os
+
 import torch
 
 import tips_b200 as tips
@@ -78,7 +80,8 @@ def run_resnet50(batch: int, steps: int, warmup: int):
     from tips_b200.ops.optim import FusedSGD
     dev = torch.device("cuda", torch.cuda.current_device())
     torch.manual_seed(1234)
-    model = resnet50(device=dev)
+    # TIPS_RESNET_LIBRARY_CONV=1 swaps the tcgen05 convolutions for library ones (for A/B measurements)
+    model = resnet50(device=dev, library_conv=os.environ.get("TIPS_RESNET_LIBRARY_CONV", "0") == "1")
     model.train()
     opt = FusedSGD(model.parameters(), lr=0.1, momentum=0.9, weight_decay=1e-4)
     opt = tips.DistributedOptimizer(opt, named_parameters=model.named_parameters())

@@ -83,11 +83,13 @@ struct ConvCfg {
   static constexpr int kStageBytes   = kABytes + kBBytes;
   static constexpr int kStagingBytes = kBM * BN * 2;
   static constexpr int kTmemCols     = 2 * BN < 32 ? 32 : 2 * BN;
-  static constexpr int kSmemBytes    = kStages * kStageBytes + kStagingBytes + 1024 + 256;
+  static constexpr int kSmemBytes    = kStages * kStageBytes + kStagingBytes + 1024 + 256 + 4096 /*statistics*/;
 };
 
+constexpr int kConvThreads = 320;  // TMA warp, MMA warp, four epilogue warps, four statistics warps
+
 template <int BN>
-__global__ void __launch_bounds__(kGemmThreads, 1)
+__global__ void __launch_bounds__(kConvThreads, 1)
 ConvTapsKernel(const __grid_constant__ ConvMaps maps, const __grid_constant__ ConvParams p) {
   using Cfg = ConvCfg<BN>;
   extern __shared__ uint8_t smem_raw[];
@@ -188,10 +190,15 @@ ConvTapsKernel(const __grid_constant__ ConvMaps maps, const __grid_constant__ Co
         if (ok) UmmaCommit(&tmem_full[buf]);
       }
     }
-  } else {
+  } else if (warp < 6) {
+    // Epilogue warps.  The tile leaves through 64-channel boxes: as soon as a box is staged, one thread hands it
+    // to the TMA store unit while the next box is converted; the TMEM load of the next 32 columns is in flight
+    // while this one is converted.
     const int q = warp & 3;
     const int r = q * 32 + lane;  // row of the tile = pixel of the box
-    const int et = threadIdx.x - 64;  // 0..127 among the epilogue threads
+    constexpr int kBoxes  = BN / 64;
+    constexpr int kChunks = BN / 32;
+    const int bar_threads = p.stat_sum != nullptr ? 256 : 128;
     int local = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++local) {
@@ -205,68 +212,114 @@ ConvTapsKernel(const __grid_constant__ ConvMaps maps, const __grid_constant__ Co
         ok = false;
       }
       TcFenceAfter();
-      if (ok) {
-#pragma unroll 1
-        for (int c = 0; c < BN / 32; ++c) {
-          uint32_t acc[32];
-          TmemLoad32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(buf * BN + c * 32), acc);
-          uint8_t* box = staging + (c >> 1) * (kBM * 128);
+      const uint32_t tsrc = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(buf * BN);
+      uint32_t acc[2][32];
+      if (ok) TmemLoad32Async(tsrc, acc[0]);
 #pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            alignas(16) __nv_bfloat16 o[8];
+      for (int b = 0; b < kBoxes; ++b) {
+        // the store that last read this box (one tile ago) is kBoxes - 1 groups behind the newest one
+        if (warp == 2 && lane == 0) asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(kBoxes - 1) : "memory");
+        NamedBarSync(1, bar_threads);
+        uint8_t* box = staging + b * (kBM * 128);
 #pragma unroll
-            for (int j = 0; j < 8; ++j) o[j] = __float2bfloat16_rn(__uint_as_float(acc[g * 8 + j]));
-            const int chunk = (c & 1) * 4 + g;
-            *reinterpret_cast<uint4*>(box + r * 128 + ((chunk ^ (r & 7)) << 4)) = *reinterpret_cast<uint4*>(o);
+        for (int half = 0; half < 2; ++half) {
+          const int c = 2 * b + half;
+          if (ok) {
+            TmemLoadWait(acc[c & 1]);
+            if (c + 1 < kChunks) TmemLoad32Async(tsrc + static_cast<uint32_t>((c + 1) * 32), acc[(c + 1) & 1]);
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              alignas(16) __nv_bfloat16 o[8];
+#pragma unroll
+              for (int j = 0; j < 8; ++j) o[j] = __float2bfloat16_rn(__uint_as_float(acc[c & 1][g * 8 + j]));
+              const int chunk = half * 4 + g;
+              *reinterpret_cast<uint4*>(box + r * 128 + ((chunk ^ (r & 7)) << 4)) = *reinterpret_cast<uint4*>(o);
+            }
           }
         }
-        TcFenceBefore();
-        __syncwarp();
-        if (lane == 0) MbarArrive(&tmem_empty[buf]);
-      }
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      if (warp == 2 && lane == 0) {
-        if (ok) {
-#pragma unroll 1
-          for (int b = 0; b < BN / 64; ++b) {
-            if (nt * BN + b * 64 < p.cout) TmaStore4D(&maps.c, nt * BN + b * 64, w0, h0, n0, staging + b * (kBM * 128));
-          }
+        if (b == kBoxes - 1 && ok) {  // the accumulator is drained: hand it back to the MMA warp
+          TcFenceBefore();
+          __syncwarp();
+          if (lane == 0) MbarArrive(&tmem_empty[buf]);
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        NamedBarSync(1, bar_threads);
+        if (warp == 2 && lane == 0) {
+          if (ok && nt * BN + b * 64 < p.cout) TmaStore4D(&maps.c, nt * BN + b * 64, w0, h0, n0, box);
           asm volatile("cp.async.bulk.commit_group;" ::: "memory");
         }
       }
-      if (ok && p.stat_sum != nullptr) {
-        // Per-channel sum and sum of squares of the bf16 values just staged (what the normalisation that
-        // follows will read), over the rows of the box that are real output pixels.
-        for (int col = et; col < BN; col += 128) {
-          const uint8_t* bx = staging + (col >> 6) * (kBM * 128);
-          const int chunk = (col & 63) >> 3, within = (col & 7) * 2;
-          float s1 = 0.f, s2 = 0.f;
-          int row = 0;
-          for (int in = 0; in < p.tn; ++in) {
-            for (int ih = 0; ih < p.th; ++ih) {
-              const bool hv = (n0 + in < p.nb) && (h0 + ih < p.ho);
-              for (int iw = 0; iw < p.tw; ++iw, ++row) {
-                if (hv && w0 + iw < p.wo) {
-                  const float v = __bfloat162float(
-                      *reinterpret_cast<const __nv_bfloat16*>(bx + row * 128 + ((chunk ^ (row & 7)) << 4) + within));
-                  s1 += v;
-                  s2 += v * v;
-                }
-              }
-            }
-          }
-          const int ch = nt * BN + col;
-          if (ch < p.cout) {
-            atomicAdd(p.stat_sum + ch, s1);
-            atomicAdd(p.stat_sq + ch, s2);
-          }
+    }
+    if (warp == 2 && lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+  } else if (p.stat_sum != nullptr) {
+    // Statistics warps: per-channel sum and sum of squares of the bf16 values of every staged box (what the
+    // normalisation that follows will read), over the rows that are real output pixels.  They read a box
+    // between its "full" barrier and the next "free" barrier, off the epilogue warps' critical path.
+    constexpr int kBoxes = BN / 64;
+    float* partial   = reinterpret_cast<float*>(tmem_slot + 4);  // [2][4 warps][64 columns][2]
+    const int st     = threadIdx.x - 192;  // 0..127
+    const int chunk  = st & 7;             // 16-byte chunk of a box row = 8 channels
+    const int rg     = st >> 3;            // rows rg, rg + 16, ...
+    const int sw     = st >> 5;            // statistics warp 0..3
+    uint32_t boxes_done = 0;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+      const int mt = tile / p.n_tiles, nt = tile % p.n_tiles;
+      const int w0 = (mt % p.tiles_w) * p.tw;
+      const int h0 = ((mt / p.tiles_w) % p.tiles_h) * p.th;
+      const int n0 = (mt / (p.tiles_w * p.tiles_h)) * p.tn;
+      uint32_t valid = 0;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int row = rg + 16 * i;
+        if (row < box_rows) {
+          const int iw = row % p.tw, ih = (row / p.tw) % p.th, in = row / (p.tw * p.th);
+          if (w0 + iw < p.wo && h0 + ih < p.ho && n0 + in < p.nb) valid |= 1u << i;
         }
       }
-      if (warp == 2 && lane == 0) {
-        asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");  // staging may be overwritten afterwards
+#pragma unroll 1
+      for (int b = 0; b < kBoxes; ++b, ++boxes_done) {
+        NamedBarSync(1, 256);  // "free": this warp no longer reads the box about to be overwritten
+        NamedBarSync(1, 256);  // "full"
+        const uint8_t* box = staging + b * (kBM * 128);
+        float s1[8], s2[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) s1[j] = s2[j] = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          if (valid & (1u << i)) {
+            const int row = rg + 16 * i;
+            const uint4 v = *reinterpret_cast<const uint4*>(box + row * 128 + ((chunk ^ (row & 7)) << 4));
+            const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const float2 f = __bfloat1622float2(h[j]);
+              s1[2 * j] += f.x; s2[2 * j] += f.x * f.x;
+              s1[2 * j + 1] += f.y; s2[2 * j + 1] += f.y * f.y;
+            }
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {  // lanes that share a chunk differ in bits 3 and 4
+          s1[j] += __shfl_xor_sync(0xffffffffu, s1[j], 8);
+          s1[j] += __shfl_xor_sync(0xffffffffu, s1[j], 16);
+          s2[j] += __shfl_xor_sync(0xffffffffu, s2[j], 8);
+          s2[j] += __shfl_xor_sync(0xffffffffu, s2[j], 16);
+        }
+        float* P = partial + (boxes_done & 1) * (4 * 64 * 2);
+        if (lane < 8) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            P[(sw * 64 + lane * 8 + j) * 2]     = s1[j];
+            P[(sw * 64 + lane * 8 + j) * 2 + 1] = s2[j];
+          }
+        }
+        NamedBarSync(2, 128);
+        const int col = st & 63, which = st >> 6;
+        const float tot = P[(0 * 64 + col) * 2 + which] + P[(1 * 64 + col) * 2 + which] +
+                          P[(2 * 64 + col) * 2 + which] + P[(3 * 64 + col) * 2 + which];
+        const int ch = nt * BN + b * 64 + col;
+        if (ch < p.cout) atomicAdd((which ? p.stat_sq : p.stat_sum) + ch, tot);
       }
-      asm volatile("bar.sync 1, 128;" ::: "memory");
     }
   }
   TcFenceBefore();
@@ -557,7 +610,7 @@ int LaunchTaps(const ConvMaps& maps, const ConvParams& p, cudaStream_t s) {
   }
   const int64_t tiles = static_cast<int64_t>(p.tiles_w) * p.tiles_h * p.tiles_n * p.n_tiles;
   const int grid = static_cast<int>(std::min<int64_t>(tiles, NumSMs()));
-  ConvTapsKernel<BN><<<grid, kGemmThreads, Cfg::kSmemBytes, s>>>(maps, p);
+  ConvTapsKernel<BN><<<grid, kConvThreads, Cfg::kSmemBytes, s>>>(maps, p);
   TIPSK_LAUNCH_CHECK();
   return 0;
 }

@@ -337,6 +337,26 @@ int tipsk_bn_fwd_train(const void* x, const void* residual, void* y, const float
   return 0;
 }
 
+/* Training forward when the per-channel sum and sum of squares of x are already known (`stats` = fp32 [2, C]:
+ * sums, then sums of squares; the convolution epilogue produces them): only the apply pass runs. */
+int tipsk_bn_fwd_train_stats(const void* x, const void* residual, void* y, const float* gamma, const float* beta,
+                             float* running_mean, float* running_var, float* save_mean, float* save_invstd,
+                             const float* stats, int64_t m, int c, float eps, float momentum, int relu, int dtype,
+                             void* stream) {
+  TIPSK_REQUIRE(m > 0 && c > 0, "batch norm: empty input");
+  TIPSK_REQUIRE(stats != nullptr, "batch norm: statistics buffer is null");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  BN_DISPATCH(dtype, c, {
+    BnGeom g = BnGeometry(m, c, V);
+    dim3 block(g.tx, g.ty), grid(g.col_tiles, g.partials);
+    BnApplyKernel<T, V><<<grid, block, sizeof(float) * 256 * 2 * V, s>>>(static_cast<const T*>(x), static_cast<const T*>(residual),
+                                               static_cast<T*>(y), gamma, beta, running_mean, running_var, save_mean,
+                                               save_invstd, stats, 0, m, c, eps, momentum, relu, 1);
+  });
+  TIPSK_LAUNCH_CHECK();
+  return 0;
+}
+
 int tipsk_bn_fwd_eval(const void* x, const void* residual, void* y, const float* gamma, const float* beta,
                       const float* running_mean, const float* running_var, int64_t m, int c, float eps, int relu,
                       int dtype, void* stream) {

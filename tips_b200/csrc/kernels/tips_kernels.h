@@ -45,6 +45,11 @@ int tipsk_bn_partials(int64_t m, int c);
 int tipsk_bn_fwd_train(const void* x, const void* residual, void* y, const float* gamma, const float* beta,
                        float* running_mean, float* running_var, float* save_mean, float* save_invstd,
                        float* workspace, int64_t m, int c, float eps, float momentum, int relu, int dtype, void* stream);
+/* Same, with the column sums already known: stats = fp32 [2, C] (sums, sums of squares). */
+int tipsk_bn_fwd_train_stats(const void* x, const void* residual, void* y, const float* gamma, const float* beta,
+                             float* running_mean, float* running_var, float* save_mean, float* save_invstd,
+                             const float* stats, int64_t m, int c, float eps, float momentum, int relu, int dtype,
+                             void* stream);
 int tipsk_bn_fwd_eval(const void* x, const void* residual, void* y, const float* gamma, const float* beta,
                       const float* running_mean, const float* running_var, int64_t m, int c, float eps, int relu,
                       int dtype, void* stream);

@@ -2,15 +2,18 @@
 
 The reference's evaluated workload is a TensorFlow ResNet-50 trained through its
 collective mode (README.md:12); the model itself is not part of the reference.
-Here the normalisation layers are the fused sm_100a kernels (BN + residual +
-ReLU in one pass, forward and backward), the loss is the fused softmax
-cross-entropy, and the convolutions are library convolutions.
+Here the convolutions are the tcgen05 implicit-GEMM kernels (all but the 7x7
+stem, whose 3 input channels are below the TMA granularity), their epilogue
+produces the batch statistics, the normalisation layers are the fused sm_100a
+kernels (BN + residual + ReLU in one pass, forward and backward) and the loss is
+the fused softmax cross-entropy.
 """
 from __future__ import annotations
 
 import torch
 import torch.nn as nn
 
+from ..ops.conv import Conv2d, supported as _conv_supported
 from ..ops.norm import BatchNorm2d
 from ..ops.pointwise import softmax_cross_entropy
 
@@ -33,10 +36,23 @@ class LibraryBatchNorm2d(nn.Module):
 
 
 _NORM = BatchNorm2d
+_LIBRARY_CONV = False
 
 
 def _conv(cin, cout, k, stride=1, padding=0):
-    return nn.Conv2d(cin, cout, k, stride=stride, padding=padding, bias=False)
+    if _LIBRARY_CONV:
+        return nn.Conv2d(cin, cout, k, stride=stride, padding=padding, bias=False)
+    return Conv2d(cin, cout, k, stride=stride, padding=padding)
+
+
+def _conv_bn(conv, bn, x, residual=None):
+    """bn(conv(x)) (+ residual, ReLU); in training the convolution's epilogue hands the batch statistics to the
+    normalisation, which then needs no reduction pass of its own."""
+    if (isinstance(conv, Conv2d) and isinstance(bn, BatchNorm2d) and bn.training
+            and _conv_supported(x, conv.weight, conv.stride, conv.padding)):
+        stats = torch.zeros(2, conv.out_channels, dtype=torch.float32, device=x.device)
+        return bn(conv(x, stats=stats), residual=residual, stats=stats)
+    return bn(conv(x), residual=residual)
 
 
 class Bottleneck(nn.Module):
@@ -59,10 +75,10 @@ class Bottleneck(nn.Module):
             self.down.add_module("bn", _NORM(cout, relu=False))
 
     def forward(self, x):
-        identity = x if self.down is None else self.down(x)
-        out = self.bn1(self.conv1(x))
-        out = self.bn2(self.conv2(out))
-        return self.bn3(self.conv3(out), residual=identity)
+        identity = x if self.down is None else _conv_bn(self.down.conv, self.down.bn, x)
+        out = _conv_bn(self.conv1, self.bn1, x)
+        out = _conv_bn(self.conv2, self.bn2, out)
+        return _conv_bn(self.conv3, self.bn3, out, residual=identity)
 
 
 class ResNet50(nn.Module):
@@ -84,7 +100,7 @@ class ResNet50(nn.Module):
         self.fc = nn.Linear(cin, num_classes)
         for m in self.modules():
             if isinstance(m, nn.Conv2d):
-                nn.init.kaiming_normal_(m.weight, mode="fan_out", nonlinearity="relu")
+                nn.init.kaiming_normal_(m.weight, mode="fan_out", nonlinearity="relu")  # Conv2d does the same itself
 
     def forward(self, x):
         x = self.maxpool(self.bn1(self.conv1(x)))
@@ -96,22 +112,30 @@ class ResNet50(nn.Module):
         return softmax_cross_entropy(self.forward(images), labels)
 
 
-def resnet50(num_classes=1000, dtype=torch.bfloat16, device="cuda", library_norm=False):
-    global _NORM
+def resnet50(num_classes=1000, dtype=torch.bfloat16, device="cuda", library_norm=False, library_conv=None):
+    """`library_norm` / `library_conv` build the library-floor arm (cuDNN batch norm and convolutions)."""
+    global _NORM, _LIBRARY_CONV
     _NORM = LibraryBatchNorm2d if library_norm else BatchNorm2d
+    _LIBRARY_CONV = library_norm if library_conv is None else library_conv
     try:
         m = ResNet50(num_classes)
     finally:
         _NORM = BatchNorm2d
+        _LIBRARY_CONV = False
     m = m.to(device=device, dtype=dtype)
+    return _channels_last(m, device)
+
+
+def _channels_last(m, device):
+    """Library convolutions want channels-last weights; the tcgen05 Conv2d keeps its own [C_out, R, S, C_in] layout."""
     if torch.device(device).type == "cuda":
-        m = m.to(memory_format=torch.channels_last)
+        for mod in m.modules():
+            if isinstance(mod, nn.Conv2d):
+                mod.to(memory_format=torch.channels_last)
     return m
 
 
 def tiny_resnet(num_classes=10, dtype=torch.bfloat16, device="cuda"):
     """Same block structure with one block per stage and a quarter of the width; for smoke tests."""
     m = ResNet50(num_classes, layers=(1, 1, 1, 1), width=16).to(device=device, dtype=dtype)
-    if torch.device(device).type == "cuda":
-        m = m.to(memory_format=torch.channels_last)
-    return m
+    return _channels_last(m, device)

@@ -31,8 +31,8 @@ def _nhwc(t: torch.Tensor) -> torch.Tensor:
 
 
 def conv2d_forward(x, weight, stride, padding, stats=None):
-    """y = conv(x, weight); `stats` = (sum, sumsq) fp32 [C_out] tensors, zeroed by the caller, that receive the
-    per-channel statistics of the bf16 output from the kernel's epilogue."""
+    """y = conv(x, weight); `stats` = fp32 [2, C_out] tensor, zeroed by the caller, that receives the per-channel sum
+    and sum of squares of the bf16 output from the kernel's epilogue."""
     xc = _nhwc(x)
     n, cin, h, w = xc.shape
     cout, r, s, _ = weight.shape
@@ -42,7 +42,8 @@ def conv2d_forward(x, weight, stride, padding, stats=None):
     wc = weight.contiguous()
     base.check(base.K().tipsk_conv2d_fwd(
         xc.data_ptr(), wc.data_ptr(), y.data_ptr(), n, h, w, cin, cout, r, s, stride, padding,
-        base.ptr(stats[0]) if stats else None, base.ptr(stats[1]) if stats else None, base.stream()), "conv2d_fwd")
+        stats.data_ptr() if stats is not None else None,
+        stats.data_ptr() + 4 * cout if stats is not None else None, base.stream()), "conv2d_fwd")
     return xc, y
 
 

@@ -20,7 +20,7 @@ from . import base
 
 class _BatchNormFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, residual, weight, bias, running_mean, running_var, training, momentum, eps, relu):
+    def forward(ctx, x, residual, weight, bias, running_mean, running_var, training, momentum, eps, relu, stats=None):
         # x: NCHW tensor in channels_last memory format, i.e. an [N*H*W, C] matrix.
         assert x.is_cuda
         xc = x.contiguous(memory_format=torch.channels_last) if x.dim() == 4 else x.contiguous()
@@ -34,13 +34,21 @@ class _BatchNormFn(torch.autograd.Function):
         if training:
             save_mean = torch.empty(c, dtype=torch.float32, device=x.device)
             save_invstd = torch.empty(c, dtype=torch.float32, device=x.device)
-            parts = lib.tipsk_bn_partials(m, c)
-            ws = torch.empty(parts * 2 * c, dtype=torch.float32, device=x.device)
-            base.check(lib.tipsk_bn_fwd_train(
-                xc.data_ptr(), base.ptr(res), y.data_ptr(), weight.data_ptr(), bias.data_ptr(),
-                base.ptr(running_mean), base.ptr(running_var), save_mean.data_ptr(), save_invstd.data_ptr(),
-                ws.data_ptr(), m, c, eps, momentum, int(relu), base.code(xc), base.stream()), "bn_fwd_train")
-            base.count_launches(1)
+            if stats is not None:
+                # the producer of x (a convolution epilogue) already summed x and x^2 per channel
+                base.check(lib.tipsk_bn_fwd_train_stats(
+                    xc.data_ptr(), base.ptr(res), y.data_ptr(), weight.data_ptr(), bias.data_ptr(),
+                    base.ptr(running_mean), base.ptr(running_var), save_mean.data_ptr(), save_invstd.data_ptr(),
+                    stats.data_ptr(), m, c, eps, momentum, int(relu), base.code(xc), base.stream()),
+                    "bn_fwd_train_stats")
+            else:
+                parts = lib.tipsk_bn_partials(m, c)
+                ws = torch.empty(parts * 2 * c, dtype=torch.float32, device=x.device)
+                base.check(lib.tipsk_bn_fwd_train(
+                    xc.data_ptr(), base.ptr(res), y.data_ptr(), weight.data_ptr(), bias.data_ptr(),
+                    base.ptr(running_mean), base.ptr(running_var), save_mean.data_ptr(), save_invstd.data_ptr(),
+                    ws.data_ptr(), m, c, eps, momentum, int(relu), base.code(xc), base.stream()), "bn_fwd_train")
+                base.count_launches(2)
             ctx.save_for_backward(xc, y if relu else None, weight, save_mean, save_invstd)
         else:
             base.check(lib.tipsk_bn_fwd_eval(
@@ -74,14 +82,16 @@ class _BatchNormFn(torch.autograd.Function):
             save_invstd.data_ptr(), dx.data_ptr(), base.ptr(dres), dgamma.data_ptr(), dbeta.data_ptr(),
             ws.data_ptr(), m, c, int(ctx.relu), base.code(x), base.stream()), "bn_bwd")
         base.count_launches(1)
-        return dx, dres, dgamma.to(weight.dtype), dbeta.to(weight.dtype), None, None, None, None, None, None
+        return dx, dres, dgamma.to(weight.dtype), dbeta.to(weight.dtype), None, None, None, None, None, None, None
 
 
 def batch_norm(x, weight, bias, running_mean, running_var, training=True, momentum=0.1, eps=1e-5, relu=False,
-               residual=None):
-    """y = relu?(BN(x) + residual?) on a channels-last activation."""
+               residual=None, stats=None):
+    """y = relu?(BN(x) + residual?) on a channels-last activation.  `stats` (fp32 [2, C]: per-channel sums of x and
+    of x^2, e.g. from a convolution epilogue) lets the training forward skip its reduction pass."""
     if x.is_cuda:
-        return _BatchNormFn.apply(x, residual, weight, bias, running_mean, running_var, training, momentum, eps, relu)
+        return _BatchNormFn.apply(x, residual, weight, bias, running_mean, running_var, training, momentum, eps, relu,
+                                  stats if training else None)
     y = F.batch_norm(x.float(), running_mean, running_var, weight.float(), bias.float(), training, momentum, eps)
     if residual is not None:
         y = y + residual.float()
@@ -120,9 +130,9 @@ class BatchNorm2d(nn.Module):
                 setattr(self, name, b.float())
         return out
 
-    def forward(self, x, residual=None):
+    def forward(self, x, residual=None, stats=None):
         return batch_norm(x, self.weight, self.bias, self.running_mean, self.running_var, self.training,
-                          self.momentum, self.eps, self.relu, residual)
+                          self.momentum, self.eps, self.relu, residual, stats)
 
 
 class _LayerNormFn(torch.autograd.Function):

@@ -177,3 +177,24 @@ def test_losses():
     ref.backward()
     assert torch.allclose(loss, ref, atol=2e-3)
     assert torch.allclose(logits.grad.float(), lg.grad, atol=2e-3)
+
+
+@pytest.mark.parametrize("n,c,h,w", [(2, 64, 16, 16), (3, 8, 7, 9), (1, 16, 1, 5), (4, 64, 112, 112)])
+def test_maxpool_3x3_s2(n, c, h, w):
+    from tips_b200.ops.pool import max_pool_3x3_s2
+    torch.manual_seed(n * 100 + h)
+    dev = torch.device("cuda", 0)
+    x = torch.randn(n, c, h, w, device=dev).to(torch.bfloat16).contiguous(memory_format=torch.channels_last)
+    x.requires_grad_()
+    y = max_pool_3x3_s2(x)
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    xr = x.detach().float().requires_grad_()
+    yr = torch.nn.functional.max_pool2d(xr, 3, stride=2, padding=1)
+    yr.backward(dy.float())
+    assert torch.equal(y.float(), yr)
+    # ties between equal bf16 values may pick different positions; the gradient mass per window is the same
+    # (each bf16 gradient carries its own rounding error, so the tolerance grows with the image area)
+    assert torch.allclose(x.grad.float().sum(dim=(2, 3)), xr.grad.sum(dim=(2, 3)), rtol=2e-2, atol=2e-2 + 1e-4 * h * w)
+    mismatch = (x.grad.float() - xr.grad).abs() > 1e-2
+    assert mismatch.float().mean() < 0.02

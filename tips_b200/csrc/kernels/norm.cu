@@ -60,23 +60,30 @@ BnGeom BnGeometry(int64_t m, int c, int v) {
 // Partial column sums of a and a*b-like quantities.
 // kBwd = false: s0 = sum x, s1 = sum x^2
 // kBwd = true : s0 = sum dyr, s1 = sum dyr * xhat, with dyr = relu-masked dy
-template <typename T, int V, bool kBwd>
-__global__ void __launch_bounds__(256)
+template <typename T, int V, bool kBwd, bool kRecompute = false>
+__global__ void __launch_bounds__(256, 3)
 BnReduceKernel(const T* __restrict__ a, const T* __restrict__ x, const T* __restrict__ y,
                const float* __restrict__ mean, const float* __restrict__ invstd, float* __restrict__ ws, int64_t m,
-               int c, int relu) {
+               int c, int relu, const float* __restrict__ gamma = nullptr, const float* __restrict__ beta = nullptr) {
+  // relu with y == nullptr: the mask is recomputed from x exactly as the forward pass computed its output
+  // (x * scale + shift > 0), which saves reading the forward output; needs gamma and beta.
   extern __shared__ float smem[];
   const int tx = threadIdx.x, ty = threadIdx.y;
   const int TX = blockDim.x, TY = blockDim.y;
   const int col = (blockIdx.x * TX + tx) * V;
-  float s0[V], s1[V], mu[V], is[V];
+  float s0[V], s1[V], mu[V], is[V], sc[V], sh[V];
 #pragma unroll
-  for (int i = 0; i < V; ++i) s0[i] = s1[i] = 0.f;
+  for (int i = 0; i < V; ++i) s0[i] = s1[i] = sc[i] = sh[i] = 0.f;
+  constexpr bool recompute = kBwd && kRecompute;
   if (kBwd) {
 #pragma unroll
     for (int i = 0; i < V; ++i) {
       mu[i] = mean[col + i];
       is[i] = invstd[col + i];
+      if (recompute) {
+        sc[i] = gamma[col + i] * is[i];
+        sh[i] = beta[col + i] - mu[i] * sc[i];
+      }
     }
   }
 #pragma unroll 4
@@ -86,7 +93,11 @@ BnReduceKernel(const T* __restrict__ a, const T* __restrict__ x, const T* __rest
     if (kBwd) {
       float xv[V];
       LoadV<T, V>(x + r * c + col, xv);
-      if (relu) {
+      if (recompute) {
+#pragma unroll
+        for (int i = 0; i < V; ++i)
+          if (xv[i] * sc[i] + sh[i] <= 0.f) av[i] = 0.f;
+      } else if (relu) {
         float yv[V];
         LoadV<T, V>(y + r * c + col, yv);
 #pragma unroll
@@ -222,18 +233,19 @@ BnApplyKernel(const T* __restrict__ x, const T* __restrict__ residual, T* __rest
   }
 }
 
-template <typename T, int V>
-__global__ void __launch_bounds__(256)
+template <typename T, int V, bool kRecompute = false>
+__global__ void __launch_bounds__(256, 3)
 BnBwdApplyKernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ y,
                  const float* __restrict__ gamma, const float* __restrict__ mean, const float* __restrict__ invstd,
                  T* __restrict__ dx, T* __restrict__ dres, float* dgamma, float* dbeta, const float* __restrict__ ws,
-                 int partials, int64_t m, int c, int relu) {
+                 int partials, int64_t m, int c, int relu, const float* __restrict__ beta = nullptr) {
   const int tx = threadIdx.x, ty = threadIdx.y;
   const int TX = blockDim.x, TY = blockDim.y;
   const int col = (blockIdx.x * TX + tx) * V;
   extern __shared__ float smem[];
-  float mu[V], is[V], k0[V], k1[V], gs[V], t0[V], t1[V];
+  float mu[V], is[V], k0[V], k1[V], gs[V], t0[V], t1[V], sh[V];
   const float inv_m = 1.f / static_cast<float>(m);
+  constexpr bool recompute = kRecompute;  // mask from x, as in the reduction kernel
   BlockCombine<V>(ws, partials, c, col, smem, t0, t1);
 #pragma unroll
   for (int i = 0; i < V; ++i) {
@@ -245,6 +257,7 @@ BnBwdApplyKernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __r
     mu[i] = mean[col + i];
     is[i] = invstd[col + i];
     gs[i] = gamma[col + i] * is[i];
+    sh[i] = recompute ? beta[col + i] - mu[i] * gs[i] : 0.f;
     k0[i] = s0 * inv_m;
     k1[i] = s1 * inv_m;
   }
@@ -253,7 +266,11 @@ BnBwdApplyKernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __r
     float dv[V], xv[V];
     LoadV<T, V>(dy + r * c + col, dv);
     LoadV<T, V>(x + r * c + col, xv);
-    if (relu) {
+    if (recompute) {
+#pragma unroll
+      for (int i = 0; i < V; ++i)
+        if (xv[i] * gs[i] + sh[i] <= 0.f) dv[i] = 0.f;
+    } else if (relu) {
       float yv[V];
       LoadV<T, V>(y + r * c + col, yv);
 #pragma unroll
@@ -392,6 +409,30 @@ int tipsk_bn_bwd(const void* dy, const void* x, const void* y, const float* gamm
                                                   static_cast<const T*>(y), gamma, save_mean, save_invstd,
                                                   static_cast<T*>(dx), static_cast<T*>(dresidual), dgamma, dbeta,
                                                   workspace, g.partials, m, c, relu);
+  });
+  TIPSK_LAUNCH_CHECK();
+  return 0;
+}
+
+/* Backward of BN + ReLU (no residual) that rebuilds the ReLU mask from x, gamma, beta and the saved statistics
+ * instead of reading the forward output: one activation read fewer in each of its two passes. */
+int tipsk_bn_bwd_relu_recompute(const void* dy, const void* x, const float* gamma, const float* beta,
+                                const float* save_mean, const float* save_invstd, void* dx, float* dgamma, float* dbeta,
+                                float* workspace, int64_t m, int c, int dtype, void* stream) {
+  TIPSK_REQUIRE(m > 0 && c > 0, "batch norm: empty input");
+  TIPSK_REQUIRE(beta != nullptr && gamma != nullptr, "batch norm backward: gamma and beta are required");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  BN_DISPATCH(dtype, c, {
+    BnGeom g = BnGeometry(m, c, V);
+    dim3 block(g.tx, g.ty), grid(g.col_tiles, g.partials);
+    size_t smem = sizeof(float) * 256 * 2 * V;
+    BnReduceKernel<T, V, true, true><<<grid, block, smem, s>>>(static_cast<const T*>(dy), static_cast<const T*>(x),
+                                                               nullptr, save_mean, save_invstd, workspace, m, c, 1,
+                                                               gamma, beta);
+    BnFinalizeKernel<<<CeilDiv(2 * c, 32), dim3(32, 8), 0, s>>>(workspace, g.partials, c);
+    BnBwdApplyKernel<T, V, true><<<grid, block, smem, s>>>(static_cast<const T*>(dy), static_cast<const T*>(x), nullptr,
+                                                        gamma, save_mean, save_invstd, static_cast<T*>(dx), nullptr,
+                                                        dgamma, dbeta, workspace, g.partials, m, c, 1, beta);
   });
   TIPSK_LAUNCH_CHECK();
   return 0;

@@ -58,6 +58,10 @@ int tipsk_bn_fwd_eval(const void* x, const void* residual, void* y, const float*
 int tipsk_bn_bwd(const void* dy, const void* x, const void* y, const float* gamma, const float* save_mean,
                  const float* save_invstd, void* dx, void* dresidual, float* dgamma, float* dbeta, float* workspace,
                  int64_t m, int c, int relu, int dtype, void* stream);
+/* BN + ReLU without residual: the mask is rebuilt from x and the saved statistics, the forward output is not read. */
+int tipsk_bn_bwd_relu_recompute(const void* dy, const void* x, const float* gamma, const float* beta,
+                                const float* save_mean, const float* save_invstd, void* dx, float* dgamma, float* dbeta,
+                                float* workspace, int64_t m, int c, int dtype, void* stream);
 /* Layer norm over the last dimension of [rows, cols]. */
 int tipsk_ln_fwd(const void* x, const void* gamma, const void* beta, void* y, float* mean, float* rstd, int64_t rows,
                  int cols, float eps, int dtype, void* stream);
@@ -134,6 +138,11 @@ int tipsk_gemm_supported(int m, int n, int k, int lda, int ldb);
 int tipsk_gemm_bf16(const void* a, const void* b, void* c, const void* bias, void* pre, int m, int n, int k, int lda,
                     int ldb, int ldc, int act, void* stream);
 int tipsk_gemm_status(void);
+
+/* ---- 3x3 / stride 2 / pad 1 max pooling on NHWC (pool.cu); idx holds the argmax position 0..8 per output ---- */
+int tipsk_maxpool3x3s2_fwd(const void* x, void* y, void* idx, int n, int h, int w, int c, int dtype, void* stream);
+int tipsk_maxpool3x3s2_bwd(const void* dy, const void* idx, void* dx, int n, int h, int w, int c, int dtype,
+                           void* stream);
 
 /* ---- NHWC bf16 convolutions on tcgen05 (conv_tcgen05.cu): 1x1 and 3x3, stride 1 or 2, pad = r/2 ---- */
 int tipsk_conv2d_supported(int cin, int cout, int r, int s, int stride, int pad);

@@ -15,6 +15,7 @@ import torch.nn as nn
 
 from ..ops.conv import Conv2d, supported as _conv_supported
 from ..ops.norm import BatchNorm2d
+from ..ops.pool import MaxPool3x3S2
 from ..ops.pointwise import softmax_cross_entropy
 
 
@@ -86,7 +87,7 @@ class ResNet50(nn.Module):
         super().__init__()
         self.conv1 = _conv(3, width, 7, stride=2, padding=3)
         self.bn1 = _NORM(width, relu=True)
-        self.maxpool = nn.MaxPool2d(3, stride=2, padding=1)
+        self.maxpool = nn.MaxPool2d(3, stride=2, padding=1) if _LIBRARY_CONV else MaxPool3x3S2()
         blocks = []
         cin = width
         for stage, n in enumerate(layers):

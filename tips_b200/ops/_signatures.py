@@ -20,6 +20,7 @@ _PROTOS = {
     "tipsk_scale_cast": (I, [P, I, P, I, L, F, P]),
     "tipsk_bn_partials": (I, [L, I]),
     "tipsk_bn_fwd_train": (I, [P, P, P, P, P, P, P, P, P, P, L, I, F, F, I, I, P]),
+    "tipsk_bn_bwd_relu_recompute": (I, [P, P, P, P, P, P, P, P, P, P, L, I, I, P]),
     "tipsk_bn_fwd_train_stats": (I, [P, P, P, P, P, P, P, P, P, P, L, I, F, F, I, I, P]),
     "tipsk_bn_fwd_eval": (I, [P, P, P, P, P, P, P, L, I, F, I, I, P]),
     "tipsk_bn_bwd": (I, [P, P, P, P, P, P, P, P, P, P, P, L, I, I, I, P]),
@@ -66,6 +67,8 @@ _PROTOS = {
     "tipsk_conv2d_dgrad": (I, [P, P, P, I, I, I, I, I, I, I, I, I, P]),
     "tipsk_conv2d_wgrad": (I, [P, P, P, I, I, I, I, I, I, I, I, I, P]),
     "tipsk_conv_status": (I, []),
+    "tipsk_maxpool3x3s2_fwd": (I, [P, P, P, I, I, I, I, I, P]),
+    "tipsk_maxpool3x3s2_bwd": (I, [P, P, P, I, I, I, I, I, P]),
 }
 
 

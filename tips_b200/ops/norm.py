@@ -49,14 +49,18 @@ class _BatchNormFn(torch.autograd.Function):
                     base.ptr(running_mean), base.ptr(running_var), save_mean.data_ptr(), save_invstd.data_ptr(),
                     ws.data_ptr(), m, c, eps, momentum, int(relu), base.code(xc), base.stream()), "bn_fwd_train")
                 base.count_launches(2)
-            ctx.save_for_backward(xc, y if relu else None, weight, save_mean, save_invstd)
+            # BN + ReLU without a residual: the backward pass rebuilds the mask from x, so y is not kept for it
+            ctx.recompute_mask = bool(relu) and residual is None
+            ctx.save_for_backward(xc, y if (relu and not ctx.recompute_mask) else None, weight, save_mean, save_invstd,
+                                  bias if ctx.recompute_mask else None)
         else:
             base.check(lib.tipsk_bn_fwd_eval(
                 xc.data_ptr(), base.ptr(res), y.data_ptr(), weight.data_ptr(), bias.data_ptr(),
                 running_mean.data_ptr(), running_var.data_ptr(), m, c, eps, int(relu), base.code(xc), base.stream()),
                 "bn_fwd_eval")
+            ctx.recompute_mask = False
             ctx.save_for_backward(xc, y if relu else None, weight,
-                                  running_mean.clone(), torch.rsqrt(running_var + eps))
+                                  running_mean.clone(), torch.rsqrt(running_var + eps), None)
         ctx.relu = bool(relu)
         ctx.has_res = residual is not None
         ctx.training_mode = bool(training)
@@ -64,7 +68,7 @@ class _BatchNormFn(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, dy):
-        x, y, weight, save_mean, save_invstd = ctx.saved_tensors
+        x, y, weight, save_mean, save_invstd, bias = ctx.saved_tensors
         if not ctx.training_mode:
             raise RuntimeError("backward through batch norm in eval mode is not supported by the fused kernel")
         c = x.shape[1]
@@ -77,11 +81,17 @@ class _BatchNormFn(torch.autograd.Function):
         lib = base.K()
         parts = lib.tipsk_bn_partials(m, c)
         ws = torch.empty(parts * 2 * c, dtype=torch.float32, device=x.device)
-        base.check(lib.tipsk_bn_bwd(
-            dyc.data_ptr(), x.data_ptr(), base.ptr(y), weight.data_ptr(), save_mean.data_ptr(),
-            save_invstd.data_ptr(), dx.data_ptr(), base.ptr(dres), dgamma.data_ptr(), dbeta.data_ptr(),
-            ws.data_ptr(), m, c, int(ctx.relu), base.code(x), base.stream()), "bn_bwd")
-        base.count_launches(1)
+        if ctx.recompute_mask:
+            base.check(lib.tipsk_bn_bwd_relu_recompute(
+                dyc.data_ptr(), x.data_ptr(), weight.data_ptr(), bias.data_ptr(), save_mean.data_ptr(),
+                save_invstd.data_ptr(), dx.data_ptr(), dgamma.data_ptr(), dbeta.data_ptr(), ws.data_ptr(), m, c,
+                base.code(x), base.stream()), "bn_bwd_relu_recompute")
+        else:
+            base.check(lib.tipsk_bn_bwd(
+                dyc.data_ptr(), x.data_ptr(), base.ptr(y), weight.data_ptr(), save_mean.data_ptr(),
+                save_invstd.data_ptr(), dx.data_ptr(), base.ptr(dres), dgamma.data_ptr(), dbeta.data_ptr(),
+                ws.data_ptr(), m, c, int(ctx.relu), base.code(x), base.stream()), "bn_bwd")
+        base.count_launches(2)
         return dx, dres, dgamma.to(weight.dtype), dbeta.to(weight.dtype), None, None, None, None, None, None, None
 
 

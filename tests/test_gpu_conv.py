@@ -132,3 +132,23 @@ def test_resnet_block_matches_library_convolutions():
         assert cos >= 0.97, (name, cos)
         checked += 1
     assert checked >= 10
+
+
+@pytest.mark.parametrize("k,stride", [(1, 1), (3, 1), (1, 2), (3, 2)])
+def test_conv_passthrough_accumulates_the_branch_gradient(k, stride):
+    from tips_b200.ops.conv import conv2d_passthrough
+    x, wgt = _make(4, 14, 14, 64, 128, k, 7)
+    x.requires_grad_()
+    wgt.requires_grad_()
+    y, alias = conv2d_passthrough(x, wgt, stride, k // 2)
+    side = (alias.float() * 0.5).to(torch.bfloat16)   # another consumer of x
+    dy = (torch.randn_like(y.float()) * 0.5).to(torch.bfloat16)
+    dside = (torch.randn_like(side.float())).to(torch.bfloat16)
+    torch.autograd.backward([y, side], [dy, dside])
+    assert _status() == 0
+    xr = x.detach().float().requires_grad_()
+    wr = wgt.detach().float().requires_grad_()
+    yr = F.conv2d(xr, wr.permute(0, 3, 1, 2), stride=stride, padding=k // 2)
+    torch.autograd.backward([yr, xr * 0.5], [dy.float(), dside.float()])
+    sx = max(1.0, float(xr.grad.abs().max()))
+    assert (x.grad.float() - xr.grad).abs().max() <= 2e-2 * sx

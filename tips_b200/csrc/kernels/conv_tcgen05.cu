@@ -47,6 +47,7 @@ struct ConvParams {
   float* stat_sum;  // optional per-channel sum of the bf16 outputs
   float* stat_sq;   // optional per-channel sum of squares
   int taps, cblocks;               // filter taps, 64-channel blocks of the contraction
+  int accumulate;                  // 1: add the result to what the output tensor holds (TMA reduce-add store)
   int tiles_w, tiles_h, tiles_n;   // boxes per output extent
   int tw, th, tn;                  // box extents; tw * th * tn <= 128
   int wo, ho, nb;                  // output extents (for the statistics mask)
@@ -70,6 +71,15 @@ __device__ __forceinline__ void TmaLoad4D(void* smem_dst, const CUtensorMap* tma
 }
 __device__ __forceinline__ void TmaStore4D(const CUtensorMap* tmap, int c, int w, int h, int n, const void* smem_src) {
   asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%1, %2, %3, %4}], [%5];" ::"l"(
+                   reinterpret_cast<uint64_t>(tmap)),
+               "r"(c), "r"(w), "r"(h), "r"(n), "r"(SmemAddr(smem_src))
+               : "memory");
+}
+
+// The same box added (in bf16) to the tensor in global memory instead of overwriting it.
+__device__ __forceinline__ void TmaReduceAdd4D(const CUtensorMap* tmap, int c, int w, int h, int n,
+                                               const void* smem_src) {
+  asm volatile("cp.reduce.async.bulk.tensor.4d.global.shared::cta.add.tile.bulk_group [%0, {%1, %2, %3, %4}], [%5];" ::"l"(
                    reinterpret_cast<uint64_t>(tmap)),
                "r"(c), "r"(w), "r"(h), "r"(n), "r"(SmemAddr(smem_src))
                : "memory");
@@ -245,7 +255,10 @@ ConvTapsKernel(const __grid_constant__ ConvMaps maps, const __grid_constant__ Co
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         NamedBarSync(1, bar_threads);
         if (warp == 2 && lane == 0) {
-          if (ok && nt * BN + b * 64 < p.cout) TmaStore4D(&maps.c, nt * BN + b * 64, w0, h0, n0, box);
+          if (ok && nt * BN + b * 64 < p.cout) {
+            if (p.accumulate) TmaReduceAdd4D(&maps.c, nt * BN + b * 64, w0, h0, n0, box);
+            else TmaStore4D(&maps.c, nt * BN + b * 64, w0, h0, n0, box);
+          }
           asm volatile("cp.async.bulk.commit_group;" ::: "memory");
         }
       }
@@ -631,7 +644,8 @@ int LaunchWgrad(const WgradMaps& maps, const WgradParams& p, int splits, cudaStr
 
 // Runs the tap kernel: out[view_out pixel, co] = sum over taps and 64-channel blocks.
 int RunTaps(const View* in_views, int n_views, const ConvTap* taps, int n_taps, int cin, const void* weights,
-            int w_rows, int64_t w_cols, const View& out, float* stat_sum, float* stat_sq, cudaStream_t s) {
+            int w_rows, int64_t w_cols, const View& out, float* stat_sum, float* stat_sq, cudaStream_t s,
+            int accumulate = 0) {
   TIPSK_REQUIRE(n_taps >= 1 && n_taps <= kMaxTaps, "conv: 1..9 filter taps are supported");
   TIPSK_REQUIRE(cin % 64 == 0, "conv: the contracted channel count must be a multiple of 64");
   TIPSK_REQUIRE(w_rows % 64 == 0, "conv: the produced channel count must be a multiple of 64");
@@ -659,6 +673,7 @@ int RunTaps(const View* in_views, int n_views, const ConvTap* taps, int n_taps, 
   TIPSK_REQUIRE(p.error != nullptr, "conv: cannot allocate the error word");
   p.stat_sum = stat_sum;
   p.stat_sq  = stat_sq;
+  p.accumulate = accumulate;
   p.taps = n_taps;
   p.cblocks = cin / 64;
   p.tw = box.tw; p.th = box.th; p.tn = box.tn;
@@ -734,9 +749,10 @@ int tipsk_conv2d_fwd(const void* x, const void* wgt, void* y, int n, int h, int 
                  static_cast<cudaStream_t>(stream));
 }
 
-/* dx[n, h, w, cin] = data gradient; wgt_t is the weight permuted to [cin, r, s, cout]. */
+/* dx[n, h, w, cin] = data gradient; wgt_t is the weight permuted to [cin, r, s, cout].  With `accumulate` the
+ * gradient is added to what dx already holds (the gradient of another consumer of the same activation). */
 int tipsk_conv2d_dgrad(const void* dy, const void* wgt_t, void* dx, int n, int h, int w, int cin, int cout, int r,
-                       int s, int stride, int pad, void* stream) {
+                       int s, int stride, int pad, int accumulate, void* stream) {
   TIPSK_REQUIRE(tipsk_conv2d_supported(cin, cout, r, s, stride, pad), "conv2d_dgrad: unsupported shape");
   const int ho = (h + 2 * pad - r) / stride + 1, wo = (w + 2 * pad - s) / stride + 1;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -753,11 +769,11 @@ int tipsk_conv2d_dgrad(const void* dy, const void* wgt_t, void* dx, int n, int h
       }
     View in  = r == 1 ? FlatView(dy, n, ho, wo, cout) : FullView(dy, n, ho, wo, cout);
     View out = r == 1 ? FlatView(dx, n, h, w, cin) : FullView(dx, n, h, w, cin);
-    return RunTaps(&in, 1, taps, nt, cout, wgt_t, cin, w_cols, out, nullptr, nullptr, st);
+    return RunTaps(&in, 1, taps, nt, cout, wgt_t, cin, w_cols, out, nullptr, nullptr, st, accumulate);
   }
   // stride 2: the input pixels of parity class (bh, bw) receive the taps with (b + pad - f) even
   const View in = FullView(dy, n, ho, wo, cout);
-  if (r == 1) {
+  if (r == 1 && !accumulate) {
     // a 1x1 filter only reaches the even pixels: the other three classes receive no gradient
     TIPSK_CUDA(cudaMemsetAsync(dx, 0, static_cast<size_t>(n) * h * w * cin * 2, st));
   }
@@ -778,7 +794,7 @@ int tipsk_conv2d_dgrad(const void* dy, const void* wgt_t, void* dx, int n, int h
     if (nt == 0) continue;
     const View out = PhaseView(dx, n, h, w, cin, bh, bw);
     if (out.w <= 0 || out.h <= 0) continue;
-    int rc = RunTaps(&in, 1, taps, nt, cout, wgt_t, cin, w_cols, out, nullptr, nullptr, st);
+    int rc = RunTaps(&in, 1, taps, nt, cout, wgt_t, cin, w_cols, out, nullptr, nullptr, st, accumulate);
     if (rc) return rc;
   }
   return 0;

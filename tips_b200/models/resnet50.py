@@ -13,7 +13,7 @@ from __future__ import annotations
 import torch
 import torch.nn as nn
 
-from ..ops.conv import Conv2d, supported as _conv_supported
+from ..ops.conv import Conv2d, conv2d_passthrough, supported as _conv_supported
 from ..ops.norm import BatchNorm2d
 from ..ops.pool import MaxPool3x3S2
 from ..ops.pointwise import softmax_cross_entropy
@@ -46,14 +46,20 @@ def _conv(cin, cout, k, stride=1, padding=0):
     return Conv2d(cin, cout, k, stride=stride, padding=padding)
 
 
-def _conv_bn(conv, bn, x, residual=None):
+def _conv_bn(conv, bn, x, residual=None, passthrough=False):
     """bn(conv(x)) (+ residual, ReLU); in training the convolution's epilogue hands the batch statistics to the
-    normalisation, which then needs no reduction pass of its own."""
+    normalisation, which then needs no reduction pass of its own.  With `passthrough` the result is a pair
+    (output, alias of x for the block's other branch): the gradients of the two uses of x are then summed inside
+    the convolution's data-gradient kernel."""
     if (isinstance(conv, Conv2d) and isinstance(bn, BatchNorm2d) and bn.training
             and _conv_supported(x, conv.weight, conv.stride, conv.padding)):
         stats = torch.zeros(2, conv.out_channels, dtype=torch.float32, device=x.device)
+        if passthrough:
+            y, alias = conv2d_passthrough(x, conv.weight, conv.stride, conv.padding, stats)
+            return bn(y, residual=residual, stats=stats), alias
         return bn(conv(x, stats=stats), residual=residual, stats=stats)
-    return bn(conv(x), residual=residual)
+    out = bn(conv(x), residual=residual)
+    return (out, x) if passthrough else out
 
 
 class Bottleneck(nn.Module):
@@ -76,8 +82,8 @@ class Bottleneck(nn.Module):
             self.down.add_module("bn", _NORM(cout, relu=False))
 
     def forward(self, x):
+        out, x = _conv_bn(self.conv1, self.bn1, x, passthrough=True)
         identity = x if self.down is None else _conv_bn(self.down.conv, self.down.bn, x)
-        out = _conv_bn(self.conv1, self.bn1, x)
         out = _conv_bn(self.conv2, self.bn2, out)
         return _conv_bn(self.conv3, self.bn3, out, residual=identity)
 

@@ -64,7 +64,7 @@ _PROTOS = {
     "tipsk_gemm_status": (I, []),
     "tipsk_conv2d_supported": (I, [I, I, I, I, I, I]),
     "tipsk_conv2d_fwd": (I, [P, P, P, I, I, I, I, I, I, I, I, I, P, P, P]),
-    "tipsk_conv2d_dgrad": (I, [P, P, P, I, I, I, I, I, I, I, I, I, P]),
+    "tipsk_conv2d_dgrad": (I, [P, P, P, I, I, I, I, I, I, I, I, I, I, P]),
     "tipsk_conv2d_wgrad": (I, [P, P, P, I, I, I, I, I, I, I, I, I, P]),
     "tipsk_conv_status": (I, []),
     "tipsk_maxpool3x3s2_fwd": (I, [P, P, P, I, I, I, I, I, P]),

@@ -47,16 +47,22 @@ def conv2d_forward(x, weight, stride, padding, stats=None):
     return xc, y
 
 
-def conv2d_dgrad(dy, weight, x_shape, stride, padding):
+def conv2d_dgrad(dy, weight, x_shape, stride, padding, into=None):
+    """Data gradient; with `into` (a channels-last tensor of x's shape) the gradient is added to it in place by
+    the kernel's reduce-add stores and `into` is returned."""
     n, cin, h, w = x_shape
     cout, r, s, _ = weight.shape
     dyc = _nhwc(dy)
     wt = weight.permute(3, 1, 2, 0).contiguous()  # [C_in, R, S, C_out]
-    dx = torch.empty(x_shape, dtype=dy.dtype, device=dy.device, memory_format=torch.channels_last)
+    if into is not None:
+        assert tuple(into.shape) == tuple(x_shape) and into.is_contiguous(memory_format=torch.channels_last)
+        dx = into
+    else:
+        dx = torch.empty(x_shape, dtype=dy.dtype, device=dy.device, memory_format=torch.channels_last)
     launches = 1 if stride == 1 else (1 if r == 1 else 4)
     base.check(base.K().tipsk_conv2d_dgrad(
-        dyc.data_ptr(), wt.data_ptr(), dx.data_ptr(), n, h, w, cin, cout, r, s, stride, padding, base.stream()),
-        "conv2d_dgrad")
+        dyc.data_ptr(), wt.data_ptr(), dx.data_ptr(), n, h, w, cin, cout, r, s, stride, padding,
+        1 if into is not None else 0, base.stream()), "conv2d_dgrad")
     base.count_launches(launches - 1)
     return dx
 
@@ -89,6 +95,40 @@ class _Conv2dFn(torch.autograd.Function):
         if ctx.needs_input_grad[1]:
             dw = conv2d_wgrad(xc, dy, tuple(weight.shape), ctx.stride, ctx.padding).to(weight.dtype)
         return dx, dw, None, None, None
+
+
+class _Conv2dPassFn(torch.autograd.Function):
+    """conv(x) together with an alias of x for the other consumers of x (a residual branch).  The backward pass then
+    sees the gradient of that alias next to the gradient of the convolution output and adds the data gradient into
+    it inside the kernel, instead of producing a second tensor for autograd to sum.  The alias gradient is modified
+    in place: it must not be shared with another branch."""
+
+    @staticmethod
+    def forward(ctx, x, weight, stride, padding, stats):
+        xc, y = conv2d_forward(x, weight, stride, padding, stats)
+        ctx.save_for_backward(xc, weight)
+        ctx.stride, ctx.padding = stride, padding
+        return y, x.detach()
+
+    @staticmethod
+    def backward(ctx, dy, d_alias):
+        xc, weight = ctx.saved_tensors
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            into = None
+            if d_alias is not None:
+                into = d_alias if d_alias.is_contiguous(memory_format=torch.channels_last) else _nhwc(d_alias)
+            dx = conv2d_dgrad(dy, weight, tuple(xc.shape), ctx.stride, ctx.padding, into=into)
+        if ctx.needs_input_grad[1]:
+            dw = conv2d_wgrad(xc, dy, tuple(weight.shape), ctx.stride, ctx.padding).to(weight.dtype)
+        return dx, dw, None, None, None
+
+
+def conv2d_passthrough(x, weight, stride=1, padding=0, stats=None):
+    """(conv(x), alias of x); see _Conv2dPassFn.  Falls back to the plain pair when the kernels do not apply."""
+    if supported(x, weight, stride, padding) and x.dtype == torch.bfloat16:
+        return _Conv2dPassFn.apply(x, weight, stride, padding, stats)
+    return conv2d(x, weight, stride, padding, stats), x
 
 
 def conv2d(x, weight, stride=1, padding=0, stats=None):

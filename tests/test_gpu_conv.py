@@ -80,14 +80,36 @@ def test_conv_output_statistics():
     assert torch.allclose(s2, ref2, rtol=1e-3, atol=1e-2)
 
 
-def test_conv_module_falls_back_for_the_stem():
+@pytest.mark.parametrize("n,h,w", [(2, 32, 32), (3, 30, 46), (4, 224, 224)])
+def test_stem_convolution(n, h, w):
     from tips_b200.ops.conv import Conv2d
     dev = torch.device("cuda", 0)
+    torch.manual_seed(n)
     conv = Conv2d(3, 64, 7, stride=2, padding=3).to(dev).to(torch.bfloat16)
-    x = torch.randn(2, 3, 32, 32, device=dev).to(torch.bfloat16).contiguous(memory_format=torch.channels_last)
+    x = torch.randn(n, 3, h, w, device=dev).to(torch.bfloat16).contiguous(memory_format=torch.channels_last)
+    stats = torch.zeros(2, 64, dtype=torch.float32, device=dev)
+    y = conv(x, stats=stats)
+    dy = (torch.randn_like(y.float()) * 0.1).to(torch.bfloat16)
+    y.backward(dy)
+    assert _status() == 0
+    wr = conv.weight.detach().float().requires_grad_()
+    ref = F.conv2d(x.float(), wr.permute(0, 3, 1, 2), stride=2, padding=3)
+    ref.backward(dy.float())
+    assert y.shape == ref.shape
+    assert (y.detach().float() - ref.detach()).abs().max() <= 2e-2 * max(1.0, float(ref.abs().max()))
+    assert torch.allclose(stats[0], y.detach().float().sum(dim=(0, 2, 3)), rtol=1e-3, atol=0.1)
+    sw = max(1.0, float(wr.grad.abs().max()))
+    assert (conv.weight.grad.float() - wr.grad).abs().max() <= 2e-2 * sw
+
+
+def test_conv_module_falls_back_for_other_filters():
+    from tips_b200.ops.conv import Conv2d
+    dev = torch.device("cuda", 0)
+    conv = Conv2d(16, 24, 5, stride=1, padding=2).to(dev).to(torch.bfloat16)
+    x = torch.randn(2, 16, 12, 12, device=dev).to(torch.bfloat16).contiguous(memory_format=torch.channels_last)
     y = conv(x)
-    ref = F.conv2d(x.float(), conv.weight.float().permute(0, 3, 1, 2), stride=2, padding=3)
-    assert (y.float() - ref).abs().max() <= 3e-2 * max(1.0, float(ref.abs().max()))
+    ref = F.conv2d(x.float(), conv.weight.float().permute(0, 3, 1, 2), stride=1, padding=2)
+    assert (y.float() - ref).abs().max().item() <= 3e-2 * max(1.0, float(ref.abs().max()))
 
 
 def test_resnet_block_matches_library_convolutions():

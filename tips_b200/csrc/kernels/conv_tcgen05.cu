@@ -360,6 +360,7 @@ struct WgradParams {
   int tiles_w, tiles_h, tiles_n;
   int tw, th, tn;   // tw * th * tn is a multiple of 16, at most 128
   int cout, cin;
+  int a_boxes;      // 64-channel boxes of dy to load per stage: 1 when cout <= 64 (rows 64..127 are then unused)
   ConvTap tap[kMaxTaps];  // kofs = first column of the tap inside a row of dw
 };
 
@@ -410,7 +411,7 @@ ConvWgradKernel(const __grid_constant__ WgradMaps maps, const __grid_constant__ 
   const int k_begin  = static_cast<int>(static_cast<int64_t>(k_tiles) * blockIdx.y / gridDim.y);
   const int k_end    = static_cast<int>(static_cast<int64_t>(k_tiles) * (blockIdx.y + 1) / gridDim.y);
   const int num_k    = k_end - k_begin;
-  const uint32_t stage_tx = static_cast<uint32_t>(box_rows) * 128u * (2 + BN / 64);
+  const uint32_t stage_tx = static_cast<uint32_t>(box_rows) * 128u * (p.a_boxes + BN / 64);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < Cfg::kStages; ++s) {
@@ -446,8 +447,7 @@ ConvWgradKernel(const __grid_constant__ WgradMaps maps, const __grid_constant__ 
         uint8_t* a_dst = smem + s * Cfg::kStageBytes;
         uint8_t* b_dst = a_dst + Cfg::kABytes;
         MbarExpectTx(&full_bar[s], stage_tx);
-#pragma unroll
-        for (int j = 0; j < 2; ++j)
+        for (int j = 0; j < p.a_boxes; ++j)
           TmaLoad4D(a_dst + j * kMnBoxBytes, &maps.dy, cout_t * kBM + j * 64, w0, h0, n0, &full_bar[s]);
 #pragma unroll
         for (int j = 0; j < BN / 64; ++j)
@@ -709,6 +709,85 @@ int ForwardTaps(int r, int s, int stride, int pad, int cin, ConvTap* taps) {
   return n;
 }
 
+// Weight gradient over arbitrary activation views and taps: dw[co, tap.kofs + ci] += sum_p dy[p, co] * x_view[p + tap].
+int RunWgrad(const View& dyv, const View* xv, int n_views, const ConvTap* taps, int n_taps, int cin, int cout, int ldw,
+             float* dw, cudaStream_t st) {
+  TIPSK_REQUIRE(n_taps >= 1 && n_taps <= kMaxTaps, "conv: 1..9 filter taps are supported");
+  WgradMaps maps;
+  WgradParams p{};
+  p.taps = n_taps;
+  for (int i = 0; i < n_taps; ++i) p.tap[i] = taps[i];
+  const Box box = PickBox(static_cast<int>(dyv.w), static_cast<int>(dyv.h), static_cast<int>(dyv.n), true);
+  int rc = MapOf(&maps.dy, dyv, box);
+  if (rc) return rc;
+  for (int b = 0; b < 4; ++b) {
+    if (b < n_views) {
+      rc = MapOf(&maps.x[b], xv[b], box);
+      if (rc) return rc;
+    } else {
+      maps.x[b] = maps.x[0];
+    }
+  }
+  p.error = ConvErrorWord();
+  TIPSK_REQUIRE(p.error != nullptr, "conv: cannot allocate the error word");
+  p.dw  = dw;
+  p.ldw = ldw;
+  const int bn = cin % 128 == 0 ? 128 : 64;
+  p.cout_tiles = CeilDiv(cout, kBM);
+  p.cin_tiles  = CeilDiv(cin, bn);
+  p.tiles_w = CeilDiv(dyv.w, box.tw);
+  p.tiles_h = CeilDiv(dyv.h, box.th);
+  p.tiles_n = CeilDiv(dyv.n, box.tn);
+  p.tw = box.tw; p.th = box.th; p.tn = box.tn;
+  p.cout = cout; p.cin = cin;
+  p.a_boxes = cout <= 64 ? 1 : 2;
+  const int64_t k_tiles = static_cast<int64_t>(p.tiles_w) * p.tiles_h * p.tiles_n;
+  const int base = p.taps * p.cout_tiles * p.cin_tiles;
+  int splits = CeilDiv(2 * NumSMs(), base);
+  if (splits > k_tiles) splits = static_cast<int>(k_tiles);
+  if (splits < 1) splits = 1;
+  TIPSK_CUDA(cudaMemsetAsync(dw, 0, sizeof(float) * static_cast<size_t>(cout) * ldw, st));
+  return bn == 128 ? LaunchWgrad<128>(maps, p, splits, st) : LaunchWgrad<64>(maps, p, splits, st);
+}
+
+// Copies a 3-channel NHWC image into the zero-padded 8-channel buffer of the stem convolution.
+__global__ void __launch_bounds__(256)
+StemPadKernel(const __nv_bfloat16* __restrict__ x, uint4* __restrict__ xp, int n, int h, int w, int hp, int wp) {
+  const int64_t total = static_cast<int64_t>(n) * hp * wp;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int pw = static_cast<int>(i % wp);
+    const int ph = static_cast<int>((i / wp) % hp);
+    const int in = static_cast<int>(i / (static_cast<int64_t>(wp) * hp));
+    const int ih = ph - 3, iw = pw - 3;
+    alignas(16) __nv_bfloat16 v[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] = __float2bfloat16_rn(0.f);
+    if (ih >= 0 && ih < h && iw >= 0 && iw < w) {
+      const __nv_bfloat16* src = x + ((static_cast<int64_t>(in) * h + ih) * w + iw) * 3;
+      v[0] = src[0]; v[1] = src[1]; v[2] = src[2];
+    }
+    xp[i] = *reinterpret_cast<const uint4*>(v);
+  }
+}
+
+// The two row-parity views of the padded stem input (windows of 8 pixels = 64 elements every 2 pixels) and the
+// seven filter-row taps.
+void StemViewsAndTaps(const void* xp, int n, int hp, int wp, int ho, int wo, View* views, ConvTap* taps) {
+  for (int b = 0; b < 2; ++b) {
+    const char* base = static_cast<const char*>(xp) + static_cast<int64_t>(b) * wp * 8 * 2;
+    views[b] = View{base, 64, wo, (hp - b + 1) / 2, n, 16, 2 * static_cast<int64_t>(wp) * 8,
+                    static_cast<int64_t>(hp) * wp * 8};
+  }
+  for (int r = 0; r < 7; ++r) {
+    ConvTap t{};
+    t.dh = static_cast<int16_t>(r >> 1); t.dw = 0; t.map = static_cast<int16_t>(r & 1);
+    t.kofs = r * 64;
+    taps[r] = t;
+  }
+  (void)ho;
+}
+
 }  // namespace
 }  // namespace tipsk
 
@@ -805,44 +884,69 @@ int tipsk_conv2d_wgrad(const void* x, const void* dy, float* dw, int n, int h, i
                        int stride, int pad, void* stream) {
   TIPSK_REQUIRE(tipsk_conv2d_supported(cin, cout, r, s, stride, pad), "conv2d_wgrad: unsupported shape");
   const int ho = (h + 2 * pad - r) / stride + 1, wo = (w + 2 * pad - s) / stride + 1;
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
-  WgradMaps maps;
-  WgradParams p{};
-  p.taps = ForwardTaps(r, s, stride, pad, cin, p.tap);
+  ConvTap taps[kMaxTaps];
+  const int nt = ForwardTaps(r, s, stride, pad, cin, taps);
   const bool flat = (r == 1 && stride == 1);
   const View dyv = flat ? FlatView(dy, n, ho, wo, cout) : FullView(dy, n, ho, wo, cout);
-  const Box box  = PickBox(static_cast<int>(dyv.w), static_cast<int>(dyv.h), static_cast<int>(dyv.n), true);
-  int rc = MapOf(&maps.dy, dyv, box);
-  if (rc) return rc;
+  View xv[4];
+  int nv = 1;
   if (stride == 1) {
-    rc = MapOf(&maps.x[0], flat ? FlatView(x, n, h, w, cin) : FullView(x, n, h, w, cin), box);
-    if (rc) return rc;
-    for (int b = 1; b < 4; ++b) maps.x[b] = maps.x[0];
+    xv[0] = flat ? FlatView(x, n, h, w, cin) : FullView(x, n, h, w, cin);
   } else {
-    for (int b = 0; b < 4; ++b) {
-      rc = MapOf(&maps.x[b], PhaseView(x, n, h, w, cin, b >> 1, b & 1), box);
-      if (rc) return rc;
-    }
+    nv = 4;
+    for (int b = 0; b < 4; ++b) xv[b] = PhaseView(x, n, h, w, cin, b >> 1, b & 1);
   }
-  p.error = ConvErrorWord();
-  TIPSK_REQUIRE(p.error != nullptr, "conv: cannot allocate the error word");
-  p.dw  = dw;
-  p.ldw = r * s * cin;
-  const int bn = cin % 128 == 0 ? 128 : 64;
-  p.cout_tiles = CeilDiv(cout, kBM);
-  p.cin_tiles  = CeilDiv(cin, bn);
-  p.tiles_w = CeilDiv(dyv.w, box.tw);
-  p.tiles_h = CeilDiv(dyv.h, box.th);
-  p.tiles_n = CeilDiv(dyv.n, box.tn);
-  p.tw = box.tw; p.th = box.th; p.tn = box.tn;
-  p.cout = cout; p.cin = cin;
-  const int64_t k_tiles = static_cast<int64_t>(p.tiles_w) * p.tiles_h * p.tiles_n;
-  const int base = p.taps * p.cout_tiles * p.cin_tiles;
-  int splits = CeilDiv(2 * NumSMs(), base);
-  if (splits > k_tiles) splits = static_cast<int>(k_tiles);
-  if (splits < 1) splits = 1;
-  TIPSK_CUDA(cudaMemsetAsync(dw, 0, sizeof(float) * static_cast<size_t>(cout) * p.ldw, st));
-  return bn == 128 ? LaunchWgrad<128>(maps, p, splits, st) : LaunchWgrad<64>(maps, p, splits, st);
+  return RunWgrad(dyv, xv, nv, taps, nt, cin, cout, r * s * cin, dw, static_cast<cudaStream_t>(stream));
+}
+
+/* ---- the 7x7 / stride 2 / pad 3 stem on 3-channel images ----
+ * The image is first copied into a zero-padded 8-channel buffer xp[n, hp, wp, 8] (pixel (h, w) at (h+3, w+3)).
+ * Eight consecutive pixels of that buffer are 64 contiguous elements, so the 7 (+1 zero) horizontal taps of one
+ * filter row form one 64-element K block; the tensor map walks the output columns with a stride of two pixels
+ * (overlapping windows) and the filter rows are the taps of the ordinary kernel, split by row parity as for any
+ * stride-2 convolution.  Weights come as [cout, 7, 8, 8] (horizontal tap 7 and channels 3..7 zero). */
+int tipsk_stem_geometry(int h, int w, int* hp, int* wp, int* ho, int* wo) {
+  *ho = (h + 6 - 7) / 2 + 1;
+  *wo = (w + 6 - 7) / 2 + 1;
+  *hp = h + 6 > 2 * (*ho - 1) + 7 ? h + 6 : 2 * (*ho - 1) + 7;
+  int need = w + 6 > 2 * (*wo - 1) + 8 ? w + 6 : 2 * (*wo - 1) + 8;
+  *wp = (need + 7) / 8 * 8;
+  return 0;
+}
+
+int tipsk_stem_pad(const void* x, void* xp, int n, int h, int w, void* stream) {
+  int hp, wp, ho, wo;
+  tipsk_stem_geometry(h, w, &hp, &wp, &ho, &wo);
+  const int64_t total = static_cast<int64_t>(n) * hp * wp;
+  StemPadKernel<<<static_cast<int>(std::min<int64_t>((total + 255) / 256, NumSMs() * 16)), 256, 0,
+                  static_cast<cudaStream_t>(stream)>>>(static_cast<const __nv_bfloat16*>(x),
+                                                       static_cast<uint4*>(xp), n, h, w, hp, wp);
+  TIPSK_LAUNCH_CHECK();
+  return 0;
+}
+
+int tipsk_stem_conv_fwd(const void* xp, const void* wgt_p, void* y, int n, int h, int w, int cout, float* stat_sum,
+                        float* stat_sq, void* stream) {
+  TIPSK_REQUIRE(cout % 64 == 0, "stem: the output channel count must be a multiple of 64");
+  int hp, wp, ho, wo;
+  tipsk_stem_geometry(h, w, &hp, &wp, &ho, &wo);
+  View views[2];
+  ConvTap taps[kMaxTaps];
+  StemViewsAndTaps(xp, n, hp, wp, ho, wo, views, taps);
+  return RunTaps(views, 2, taps, 7, 64, wgt_p, cout, 7 * 64, FullView(y, n, ho, wo, cout), stat_sum, stat_sq,
+                 static_cast<cudaStream_t>(stream));
+}
+
+/* dw[cout, 7, 8, 8] (fp32, overwritten). */
+int tipsk_stem_conv_wgrad(const void* xp, const void* dy, float* dw, int n, int h, int w, int cout, void* stream) {
+  TIPSK_REQUIRE(cout % 64 == 0, "stem: the output channel count must be a multiple of 64");
+  int hp, wp, ho, wo;
+  tipsk_stem_geometry(h, w, &hp, &wp, &ho, &wo);
+  View views[2];
+  ConvTap taps[kMaxTaps];
+  StemViewsAndTaps(xp, n, hp, wp, ho, wo, views, taps);
+  return RunWgrad(FullView(dy, n, ho, wo, cout), views, 2, taps, 7, 64, cout, 7 * 64, dw,
+                  static_cast<cudaStream_t>(stream));
 }
 
 /* Reads and clears the convolution error word (0 ok; 1/2/3/4 = which wait ran out). Synchronises. */

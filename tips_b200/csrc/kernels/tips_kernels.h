@@ -153,6 +153,13 @@ int tipsk_conv2d_dgrad(const void* dy, const void* wgt_t, void* dx, int n, int h
 int tipsk_conv2d_wgrad(const void* x, const void* dy, float* dw, int n, int h, int w, int cin, int cout, int r, int s,
                        int stride, int pad, void* stream);
 int tipsk_conv_status(void);
+/* 7x7 / stride 2 / pad 3 stem on 3-channel bf16 images through a zero-padded 8-channel copy xp[n, hp, wp, 8];
+ * weights [cout, 7, 8, 8] with the eighth horizontal tap and channels 3..7 zero. */
+int tipsk_stem_geometry(int h, int w, int* hp, int* wp, int* ho, int* wo);
+int tipsk_stem_pad(const void* x, void* xp, int n, int h, int w, void* stream);
+int tipsk_stem_conv_fwd(const void* xp, const void* wgt_p, void* y, int n, int h, int w, int cout, float* stat_sum,
+                        float* stat_sq, void* stream);
+int tipsk_stem_conv_wgrad(const void* xp, const void* dy, float* dw, int n, int h, int w, int cout, void* stream);
 
 #ifdef __cplusplus
 }

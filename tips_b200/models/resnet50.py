@@ -2,9 +2,9 @@
 
 The reference's evaluated workload is a TensorFlow ResNet-50 trained through its
 collective mode (README.md:12); the model itself is not part of the reference.
-Here the convolutions are the tcgen05 implicit-GEMM kernels (all but the 7x7
-stem, whose 3 input channels are below the TMA granularity), their epilogue
-produces the batch statistics, the normalisation layers are the fused sm_100a
+Here all convolutions are the tcgen05 implicit-GEMM kernels (the 7x7 stem
+through a padded 8-channel copy of the image), their epilogue produces the
+batch statistics, the normalisation layers are the fused sm_100a
 kernels (BN + residual + ReLU in one pass, forward and backward) and the loss is
 the fused softmax cross-entropy.
 """
@@ -110,7 +110,7 @@ class ResNet50(nn.Module):
                 nn.init.kaiming_normal_(m.weight, mode="fan_out", nonlinearity="relu")  # Conv2d does the same itself
 
     def forward(self, x):
-        x = self.maxpool(self.bn1(self.conv1(x)))
+        x = self.maxpool(_conv_bn(self.conv1, self.bn1, x))
         x = self.blocks(x)
         x = torch.flatten(self.avgpool(x), 1)
         return self.fc(x)

@@ -67,6 +67,10 @@ _PROTOS = {
     "tipsk_conv2d_dgrad": (I, [P, P, P, I, I, I, I, I, I, I, I, I, I, P]),
     "tipsk_conv2d_wgrad": (I, [P, P, P, I, I, I, I, I, I, I, I, I, P]),
     "tipsk_conv_status": (I, []),
+    "tipsk_stem_geometry": (I, [I, I, P, P, P, P]),
+    "tipsk_stem_pad": (I, [P, P, I, I, I, P]),
+    "tipsk_stem_conv_fwd": (I, [P, P, P, I, I, I, I, P, P, P]),
+    "tipsk_stem_conv_wgrad": (I, [P, P, P, I, I, I, I, P]),
     "tipsk_maxpool3x3s2_fwd": (I, [P, P, P, I, I, I, I, I, P]),
     "tipsk_maxpool3x3s2_bwd": (I, [P, P, P, I, I, I, I, I, P]),
 }

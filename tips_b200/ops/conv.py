@@ -3,8 +3,9 @@
 ``Conv2d`` keeps its weight as ``[C_out, R, S, C_in]`` (the K-major operand layout of the kernels) and takes
 activations that are NCHW tensors in ``channels_last`` memory format, i.e. NHWC in memory.  Forward, data
 gradient and weight gradient all run on the tensor cores through TMA-loaded shifted boxes; nothing is
-unfolded.  Shapes the kernels do not cover (the 7x7 stem with 3 input channels, CPU tensors, other dtypes)
-go through ``torch.nn.functional.conv2d`` on a permuted view of the same weight.
+unfolded.  The 7x7 stem on 3-channel images runs on the same kernels through a padded 8-channel copy of the
+image.  Shapes the kernels do not cover (CPU tensors, other dtypes, other filter sizes) go through
+``torch.nn.functional.conv2d`` on a permuted view of the same weight.
 
 The reference has no convolution of its own: its evaluated model is a TensorFlow ResNet-50 (README.md:12).
 """
@@ -19,9 +20,18 @@ import torch.nn.functional as F
 from . import base
 
 
+def _is_stem(x, weight, stride, padding) -> bool:
+    """The 7x7 / stride 2 / pad 3 convolution of a 3-channel image that needs no input gradient."""
+    cout, r, s, cin = weight.shape
+    return (cin == 3 and r == 7 and s == 7 and stride == 2 and padding == 3 and cout % 64 == 0
+            and not x.requires_grad)
+
+
 def supported(x: torch.Tensor, weight: torch.Tensor, stride: int, padding: int) -> bool:
     if not (x.is_cuda and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and x.dim() == 4):
         return False
+    if _is_stem(x, weight, stride, padding):
+        return True
     cout, r, s, cin = weight.shape
     return bool(base.K().tipsk_conv2d_supported(cin, cout, r, s, stride, padding))
 
@@ -124,9 +134,48 @@ class _Conv2dPassFn(torch.autograd.Function):
         return dx, dw, None, None, None
 
 
+class _StemFn(torch.autograd.Function):
+    """7x7 / stride 2 stem: the image is copied once into a zero-padded 8-channel buffer in which the horizontal
+    taps of a filter row are contiguous; forward and weight gradient then run on the same tcgen05 kernels as the
+    other convolutions (seven filter-row taps of 64 elements each)."""
+
+    @staticmethod
+    def forward(ctx, x, weight, stats):
+        import ctypes
+        lib = base.K()
+        xc = _nhwc(x)
+        n, _, h, w = xc.shape
+        cout = weight.shape[0]
+        g = [ctypes.c_int() for _ in range(4)]
+        lib.tipsk_stem_geometry(h, w, *[ctypes.byref(v) for v in g])
+        hp, wp, ho, wo = (v.value for v in g)
+        xp = torch.empty((n, hp, wp, 8), dtype=x.dtype, device=x.device)
+        base.check(lib.tipsk_stem_pad(xc.data_ptr(), xp.data_ptr(), n, h, w, base.stream()), "stem_pad")
+        wpad = F.pad(weight, (0, 5, 0, 1)).contiguous()  # [C_out, 7, 8, 8]
+        y = torch.empty((n, cout, ho, wo), dtype=x.dtype, device=x.device, memory_format=torch.channels_last)
+        base.check(lib.tipsk_stem_conv_fwd(
+            xp.data_ptr(), wpad.data_ptr(), y.data_ptr(), n, h, w, cout,
+            stats.data_ptr() if stats is not None else None,
+            stats.data_ptr() + 4 * cout if stats is not None else None, base.stream()), "stem_conv_fwd")
+        ctx.save_for_backward(xp)
+        ctx.geom = (n, h, w, cout)
+        ctx.wdtype = weight.dtype
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        (xp,) = ctx.saved_tensors
+        n, h, w, cout = ctx.geom
+        dyc = _nhwc(dy)
+        dw = torch.empty((cout, 7, 8, 8), dtype=torch.float32, device=dy.device)
+        base.check(base.K().tipsk_stem_conv_wgrad(xp.data_ptr(), dyc.data_ptr(), dw.data_ptr(), n, h, w, cout,
+                                                  base.stream()), "stem_conv_wgrad")
+        return None, dw[:, :, :7, :3].to(ctx.wdtype), None
+
+
 def conv2d_passthrough(x, weight, stride=1, padding=0, stats=None):
     """(conv(x), alias of x); see _Conv2dPassFn.  Falls back to the plain pair when the kernels do not apply."""
-    if supported(x, weight, stride, padding) and x.dtype == torch.bfloat16:
+    if supported(x, weight, stride, padding) and not _is_stem(x, weight, stride, padding):
         return _Conv2dPassFn.apply(x, weight, stride, padding, stats)
     return conv2d(x, weight, stride, padding, stats), x
 
@@ -134,6 +183,8 @@ def conv2d_passthrough(x, weight, stride=1, padding=0, stats=None):
 def conv2d(x, weight, stride=1, padding=0, stats=None):
     """Convolution of a channels-last activation with an ``[C_out, R, S, C_in]`` weight."""
     if supported(x, weight, stride, padding):
+        if _is_stem(x, weight, stride, padding):
+            return _StemFn.apply(x, weight, stats)
         return _Conv2dFn.apply(x, weight, stride, padding, stats)
     if stats is not None:
         raise ValueError("fused output statistics need a shape the tcgen05 kernels cover")

@@ -60,11 +60,14 @@ BnGeom BnGeometry(int64_t m, int c, int v) {
 // Partial column sums of a and a*b-like quantities.
 // kBwd = false: s0 = sum x, s1 = sum x^2
 // kBwd = true : s0 = sum dyr, s1 = sum dyr * xhat, with dyr = relu-masked dy
-template <typename T, int V, bool kBwd, bool kRecompute = false>
+// kMask (backward only): how the ReLU mask is obtained: 0 from the forward output y, 1 recomputed from x,
+// 2 from the bit mask the forward pass wrote (one byte per 8 channels; needs V == 8).
+template <typename T, int V, bool kBwd, int kMask = 0>
 __global__ void __launch_bounds__(256, 3)
 BnReduceKernel(const T* __restrict__ a, const T* __restrict__ x, const T* __restrict__ y,
                const float* __restrict__ mean, const float* __restrict__ invstd, float* __restrict__ ws, int64_t m,
-               int c, int relu, const float* __restrict__ gamma = nullptr, const float* __restrict__ beta = nullptr) {
+               int c, int relu, const float* __restrict__ gamma = nullptr, const float* __restrict__ beta = nullptr,
+               const uint8_t* __restrict__ relu_mask = nullptr) {
   // relu with y == nullptr: the mask is recomputed from x exactly as the forward pass computed its output
   // (x * scale + shift > 0), which saves reading the forward output; needs gamma and beta.
   extern __shared__ float smem[];
@@ -74,7 +77,7 @@ BnReduceKernel(const T* __restrict__ a, const T* __restrict__ x, const T* __rest
   float s0[V], s1[V], mu[V], is[V], sc[V], sh[V];
 #pragma unroll
   for (int i = 0; i < V; ++i) s0[i] = s1[i] = sc[i] = sh[i] = 0.f;
-  constexpr bool recompute = kBwd && kRecompute;
+  constexpr bool recompute = kBwd && kMask == 1;
   if (kBwd) {
 #pragma unroll
     for (int i = 0; i < V; ++i) {
@@ -97,6 +100,11 @@ BnReduceKernel(const T* __restrict__ a, const T* __restrict__ x, const T* __rest
 #pragma unroll
         for (int i = 0; i < V; ++i)
           if (xv[i] * sc[i] + sh[i] <= 0.f) av[i] = 0.f;
+      } else if (kMask == 2) {
+        const uint32_t bits = relu_mask[(r * c + col) >> 3];
+#pragma unroll
+        for (int i = 0; i < V; ++i)
+          if (!((bits >> i) & 1u)) av[i] = 0.f;
       } else if (relu) {
         float yv[V];
         LoadV<T, V>(y + r * c + col, yv);
@@ -182,7 +190,7 @@ __global__ void __launch_bounds__(256)
 BnApplyKernel(const T* __restrict__ x, const T* __restrict__ residual, T* __restrict__ y,
               const float* __restrict__ gamma, const float* __restrict__ beta, float* running_mean, float* running_var,
               float* save_mean, float* save_invstd, const float* __restrict__ ws, int partials, int64_t m, int c,
-              float eps, float momentum, int relu, int training) {
+              float eps, float momentum, int relu, int training, uint8_t* __restrict__ relu_mask = nullptr) {
   const int tx = threadIdx.x, ty = threadIdx.y;
   const int TX = blockDim.x, TY = blockDim.y;
   const int col = (blockIdx.x * TX + tx) * V;
@@ -226,6 +234,12 @@ BnApplyKernel(const T* __restrict__ x, const T* __restrict__ residual, T* __rest
       for (int i = 0; i < V; ++i) xv[i] = xv[i] * scale[i] + shift[i];
     }
     if (relu) {
+      if (V == 8 && relu_mask != nullptr) {  // one bit per element for the backward pass, instead of y
+        uint32_t bits = 0;
+#pragma unroll
+        for (int i = 0; i < V; ++i) bits |= (xv[i] > 0.f ? 1u : 0u) << i;
+        relu_mask[(r * c + col) >> 3] = static_cast<uint8_t>(bits);
+      }
 #pragma unroll
       for (int i = 0; i < V; ++i) xv[i] = fmaxf(xv[i], 0.f);
     }
@@ -233,19 +247,20 @@ BnApplyKernel(const T* __restrict__ x, const T* __restrict__ residual, T* __rest
   }
 }
 
-template <typename T, int V, bool kRecompute = false>
+template <typename T, int V, int kMask = 0>
 __global__ void __launch_bounds__(256, 3)
 BnBwdApplyKernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ y,
                  const float* __restrict__ gamma, const float* __restrict__ mean, const float* __restrict__ invstd,
                  T* __restrict__ dx, T* __restrict__ dres, float* dgamma, float* dbeta, const float* __restrict__ ws,
-                 int partials, int64_t m, int c, int relu, const float* __restrict__ beta = nullptr) {
+                 int partials, int64_t m, int c, int relu, const float* __restrict__ beta = nullptr,
+                 const uint8_t* __restrict__ relu_mask = nullptr) {
   const int tx = threadIdx.x, ty = threadIdx.y;
   const int TX = blockDim.x, TY = blockDim.y;
   const int col = (blockIdx.x * TX + tx) * V;
   extern __shared__ float smem[];
   float mu[V], is[V], k0[V], k1[V], gs[V], t0[V], t1[V], sh[V];
   const float inv_m = 1.f / static_cast<float>(m);
-  constexpr bool recompute = kRecompute;  // mask from x, as in the reduction kernel
+  constexpr bool recompute = kMask == 1;  // mask from x, as in the reduction kernel
   BlockCombine<V>(ws, partials, c, col, smem, t0, t1);
 #pragma unroll
   for (int i = 0; i < V; ++i) {
@@ -270,6 +285,11 @@ BnBwdApplyKernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __r
 #pragma unroll
       for (int i = 0; i < V; ++i)
         if (xv[i] * gs[i] + sh[i] <= 0.f) dv[i] = 0.f;
+    } else if (kMask == 2) {
+      const uint32_t bits = relu_mask[(r * c + col) >> 3];
+#pragma unroll
+      for (int i = 0; i < V; ++i)
+        if (!((bits >> i) & 1u)) dv[i] = 0.f;
     } else if (relu) {
       float yv[V];
       LoadV<T, V>(y + r * c + col, yv);
@@ -414,6 +434,58 @@ int tipsk_bn_bwd(const void* dy, const void* x, const void* y, const float* gamm
   return 0;
 }
 
+/* Training forward that also writes the ReLU bit mask (uint8 [M * C / 8]; needs C % 8 == 0 and a 16-bit dtype) for
+ * tipsk_bn_bwd_bitmask.  `stats` (fp32 [2, C]) may be null: then the statistics are reduced here into `workspace`. */
+int tipsk_bn_fwd_train_mask(const void* x, const void* residual, void* y, const float* gamma, const float* beta,
+                            float* running_mean, float* running_var, float* save_mean, float* save_invstd,
+                            float* workspace, const float* stats, void* relu_mask, int64_t m, int c, float eps,
+                            float momentum, int relu, int dtype, void* stream) {
+  TIPSK_REQUIRE(m > 0 && c > 0, "batch norm: empty input");
+  TIPSK_REQUIRE(stats != nullptr || workspace != nullptr, "batch norm: statistics or a workspace are required");
+  TIPSK_REQUIRE(relu_mask == nullptr || (c % 8 == 0 && dtype != kF32), "batch norm: the bit mask needs C % 8 == 0");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  BN_DISPATCH(dtype, c, {
+    BnGeom g = BnGeometry(m, c, V);
+    dim3 block(g.tx, g.ty), grid(g.col_tiles, g.partials);
+    size_t smem = sizeof(float) * 256 * 2 * V;
+    if (stats == nullptr) {
+      BnReduceKernel<T, V, false><<<grid, block, smem, s>>>(static_cast<const T*>(x), nullptr, nullptr, nullptr, nullptr,
+                                                            workspace, m, c, 0);
+      BnFinalizeKernel<<<CeilDiv(2 * c, 32), dim3(32, 8), 0, s>>>(workspace, g.partials, c);
+    }
+    BnApplyKernel<T, V><<<grid, block, smem, s>>>(static_cast<const T*>(x), static_cast<const T*>(residual),
+                                                  static_cast<T*>(y), gamma, beta, running_mean, running_var, save_mean,
+                                                  save_invstd, stats ? stats : workspace, stats ? 0 : g.partials, m, c,
+                                                  eps, momentum, relu, 1, static_cast<uint8_t*>(relu_mask));
+  });
+  TIPSK_LAUNCH_CHECK();
+  return 0;
+}
+
+/* Backward of BN (+ residual) + ReLU with the mask taken from the bit mask of tipsk_bn_fwd_train_mask. */
+int tipsk_bn_bwd_bitmask(const void* dy, const void* x, const void* relu_mask, const float* gamma,
+                         const float* save_mean, const float* save_invstd, void* dx, void* dresidual, float* dgamma,
+                         float* dbeta, float* workspace, int64_t m, int c, int dtype, void* stream) {
+  TIPSK_REQUIRE(m > 0 && c > 0, "batch norm: empty input");
+  TIPSK_REQUIRE(relu_mask != nullptr && c % 8 == 0 && dtype != kF32, "batch norm: bit mask missing or C % 8 != 0");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  BN_DISPATCH(dtype, c, {
+    BnGeom g = BnGeometry(m, c, V);
+    dim3 block(g.tx, g.ty), grid(g.col_tiles, g.partials);
+    size_t smem = sizeof(float) * 256 * 2 * V;
+    BnReduceKernel<T, V, true, 2><<<grid, block, smem, s>>>(static_cast<const T*>(dy), static_cast<const T*>(x), nullptr,
+                                                            save_mean, save_invstd, workspace, m, c, 1, nullptr, nullptr,
+                                                            static_cast<const uint8_t*>(relu_mask));
+    BnFinalizeKernel<<<CeilDiv(2 * c, 32), dim3(32, 8), 0, s>>>(workspace, g.partials, c);
+    BnBwdApplyKernel<T, V, 2><<<grid, block, smem, s>>>(static_cast<const T*>(dy), static_cast<const T*>(x), nullptr, gamma,
+                                                     save_mean, save_invstd, static_cast<T*>(dx),
+                                                     static_cast<T*>(dresidual), dgamma, dbeta, workspace, g.partials, m,
+                                                     c, 1, nullptr, static_cast<const uint8_t*>(relu_mask));
+  });
+  TIPSK_LAUNCH_CHECK();
+  return 0;
+}
+
 /* Backward of BN + ReLU (no residual) that rebuilds the ReLU mask from x, gamma, beta and the saved statistics
  * instead of reading the forward output: one activation read fewer in each of its two passes. */
 int tipsk_bn_bwd_relu_recompute(const void* dy, const void* x, const float* gamma, const float* beta,
@@ -426,11 +498,11 @@ int tipsk_bn_bwd_relu_recompute(const void* dy, const void* x, const float* gamm
     BnGeom g = BnGeometry(m, c, V);
     dim3 block(g.tx, g.ty), grid(g.col_tiles, g.partials);
     size_t smem = sizeof(float) * 256 * 2 * V;
-    BnReduceKernel<T, V, true, true><<<grid, block, smem, s>>>(static_cast<const T*>(dy), static_cast<const T*>(x),
+    BnReduceKernel<T, V, true, 1><<<grid, block, smem, s>>>(static_cast<const T*>(dy), static_cast<const T*>(x),
                                                                nullptr, save_mean, save_invstd, workspace, m, c, 1,
                                                                gamma, beta);
     BnFinalizeKernel<<<CeilDiv(2 * c, 32), dim3(32, 8), 0, s>>>(workspace, g.partials, c);
-    BnBwdApplyKernel<T, V, true><<<grid, block, smem, s>>>(static_cast<const T*>(dy), static_cast<const T*>(x), nullptr,
+    BnBwdApplyKernel<T, V, 1><<<grid, block, smem, s>>>(static_cast<const T*>(dy), static_cast<const T*>(x), nullptr,
                                                         gamma, save_mean, save_invstd, static_cast<T*>(dx), nullptr,
                                                         dgamma, dbeta, workspace, g.partials, m, c, 1, beta);
   });

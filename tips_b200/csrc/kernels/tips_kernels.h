@@ -58,6 +58,15 @@ int tipsk_bn_fwd_eval(const void* x, const void* residual, void* y, const float*
 int tipsk_bn_bwd(const void* dy, const void* x, const void* y, const float* gamma, const float* save_mean,
                  const float* save_invstd, void* dx, void* dresidual, float* dgamma, float* dbeta, float* workspace,
                  int64_t m, int c, int relu, int dtype, void* stream);
+/* Forward that also writes one ReLU bit per element (uint8 [M*C/8]) and the backward that reads those bits instead
+ * of the forward output; `stats` may be null (then `workspace` is used for the reduction). */
+int tipsk_bn_fwd_train_mask(const void* x, const void* residual, void* y, const float* gamma, const float* beta,
+                            float* running_mean, float* running_var, float* save_mean, float* save_invstd,
+                            float* workspace, const float* stats, void* relu_mask, int64_t m, int c, float eps,
+                            float momentum, int relu, int dtype, void* stream);
+int tipsk_bn_bwd_bitmask(const void* dy, const void* x, const void* relu_mask, const float* gamma,
+                         const float* save_mean, const float* save_invstd, void* dx, void* dresidual, float* dgamma,
+                         float* dbeta, float* workspace, int64_t m, int c, int dtype, void* stream);
 /* BN + ReLU without residual: the mask is rebuilt from x and the saved statistics, the forward output is not read. */
 int tipsk_bn_bwd_relu_recompute(const void* dy, const void* x, const float* gamma, const float* beta,
                                 const float* save_mean, const float* save_invstd, void* dx, float* dgamma, float* dbeta,

@@ -20,6 +20,8 @@ _PROTOS = {
     "tipsk_scale_cast": (I, [P, I, P, I, L, F, P]),
     "tipsk_bn_partials": (I, [L, I]),
     "tipsk_bn_fwd_train": (I, [P, P, P, P, P, P, P, P, P, P, L, I, F, F, I, I, P]),
+    "tipsk_bn_fwd_train_mask": (I, [P, P, P, P, P, P, P, P, P, P, P, P, L, I, F, F, I, I, P]),
+    "tipsk_bn_bwd_bitmask": (I, [P, P, P, P, P, P, P, P, P, P, P, L, I, I, P]),
     "tipsk_bn_bwd_relu_recompute": (I, [P, P, P, P, P, P, P, P, P, P, L, I, I, P]),
     "tipsk_bn_fwd_train_stats": (I, [P, P, P, P, P, P, P, P, P, P, L, I, F, F, I, I, P]),
     "tipsk_bn_fwd_eval": (I, [P, P, P, P, P, P, P, L, I, F, I, I, P]),

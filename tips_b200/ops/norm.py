@@ -34,33 +34,38 @@ class _BatchNormFn(torch.autograd.Function):
         if training:
             save_mean = torch.empty(c, dtype=torch.float32, device=x.device)
             save_invstd = torch.empty(c, dtype=torch.float32, device=x.device)
-            if stats is not None:
-                # the producer of x (a convolution epilogue) already summed x and x^2 per channel
-                base.check(lib.tipsk_bn_fwd_train_stats(
-                    xc.data_ptr(), base.ptr(res), y.data_ptr(), weight.data_ptr(), bias.data_ptr(),
-                    base.ptr(running_mean), base.ptr(running_var), save_mean.data_ptr(), save_invstd.data_ptr(),
-                    stats.data_ptr(), m, c, eps, momentum, int(relu), base.code(xc), base.stream()),
-                    "bn_fwd_train_stats")
-            else:
+            # How the backward pass will know the ReLU mask: without a residual it rebuilds it from x ("recompute");
+            # with a residual the forward kernel leaves one bit per element ("bits"); otherwise it reads y.
+            mode = "none"
+            if relu:
+                if residual is None:
+                    mode = "recompute"
+                elif c % 8 == 0 and xc.dtype != torch.float32:
+                    mode = "bits"
+                else:
+                    mode = "y"
+            ws = None
+            if stats is None:
                 parts = lib.tipsk_bn_partials(m, c)
                 ws = torch.empty(parts * 2 * c, dtype=torch.float32, device=x.device)
-                base.check(lib.tipsk_bn_fwd_train(
-                    xc.data_ptr(), base.ptr(res), y.data_ptr(), weight.data_ptr(), bias.data_ptr(),
-                    base.ptr(running_mean), base.ptr(running_var), save_mean.data_ptr(), save_invstd.data_ptr(),
-                    ws.data_ptr(), m, c, eps, momentum, int(relu), base.code(xc), base.stream()), "bn_fwd_train")
                 base.count_launches(2)
-            # BN + ReLU without a residual: the backward pass rebuilds the mask from x, so y is not kept for it
-            ctx.recompute_mask = bool(relu) and residual is None
-            ctx.save_for_backward(xc, y if (relu and not ctx.recompute_mask) else None, weight, save_mean, save_invstd,
-                                  bias if ctx.recompute_mask else None)
+            bits = torch.empty(m * c // 8, dtype=torch.uint8, device=x.device) if mode == "bits" else None
+            base.check(lib.tipsk_bn_fwd_train_mask(
+                xc.data_ptr(), base.ptr(res), y.data_ptr(), weight.data_ptr(), bias.data_ptr(),
+                base.ptr(running_mean), base.ptr(running_var), save_mean.data_ptr(), save_invstd.data_ptr(),
+                base.ptr(ws), base.ptr(stats), base.ptr(bits), m, c, eps, momentum, int(relu), base.code(xc),
+                base.stream()), "bn_fwd_train")
+            ctx.mask_mode = mode
+            ctx.save_for_backward(xc, y if mode == "y" else None, weight, save_mean, save_invstd,
+                                  bias if mode == "recompute" else None, bits)
         else:
             base.check(lib.tipsk_bn_fwd_eval(
                 xc.data_ptr(), base.ptr(res), y.data_ptr(), weight.data_ptr(), bias.data_ptr(),
                 running_mean.data_ptr(), running_var.data_ptr(), m, c, eps, int(relu), base.code(xc), base.stream()),
                 "bn_fwd_eval")
-            ctx.recompute_mask = False
+            ctx.mask_mode = "y" if relu else "none"
             ctx.save_for_backward(xc, y if relu else None, weight,
-                                  running_mean.clone(), torch.rsqrt(running_var + eps), None)
+                                  running_mean.clone(), torch.rsqrt(running_var + eps), None, None)
         ctx.relu = bool(relu)
         ctx.has_res = residual is not None
         ctx.training_mode = bool(training)
@@ -68,7 +73,7 @@ class _BatchNormFn(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, dy):
-        x, y, weight, save_mean, save_invstd, bias = ctx.saved_tensors
+        x, y, weight, save_mean, save_invstd, bias, bits = ctx.saved_tensors
         if not ctx.training_mode:
             raise RuntimeError("backward through batch norm in eval mode is not supported by the fused kernel")
         c = x.shape[1]
@@ -81,7 +86,12 @@ class _BatchNormFn(torch.autograd.Function):
         lib = base.K()
         parts = lib.tipsk_bn_partials(m, c)
         ws = torch.empty(parts * 2 * c, dtype=torch.float32, device=x.device)
-        if ctx.recompute_mask:
+        if ctx.mask_mode == "bits":
+            base.check(lib.tipsk_bn_bwd_bitmask(
+                dyc.data_ptr(), x.data_ptr(), bits.data_ptr(), weight.data_ptr(), save_mean.data_ptr(),
+                save_invstd.data_ptr(), dx.data_ptr(), base.ptr(dres), dgamma.data_ptr(), dbeta.data_ptr(),
+                ws.data_ptr(), m, c, base.code(x), base.stream()), "bn_bwd_bitmask")
+        elif ctx.mask_mode == "recompute":
             base.check(lib.tipsk_bn_bwd_relu_recompute(
                 dyc.data_ptr(), x.data_ptr(), weight.data_ptr(), bias.data_ptr(), save_mean.data_ptr(),
                 save_invstd.data_ptr(), dx.data_ptr(), dgamma.data_ptr(), dbeta.data_ptr(), ws.data_ptr(), m, c,

@@ -167,20 +167,21 @@ __device__ __forceinline__ void BlockCombine(const float* __restrict__ ws, int p
   }
 }
 
-// Sums the partial rows column-wise into row `partials` of the workspace. Block (32, 8): tx = column,
+// Sums the partial rows column-wise into row `partials` of the workspace. Block (32, 32): tx = column,
 // ty = lane over the partial rows; consecutive threads read consecutive floats.
-__global__ void __launch_bounds__(256) BnFinalizeKernel(float* __restrict__ ws, int partials, int c) {
-  __shared__ float red[8][32];
+constexpr int kFinalizeRows = 32;
+__global__ void __launch_bounds__(32 * kFinalizeRows) BnFinalizeKernel(float* __restrict__ ws, int partials, int c) {
+  __shared__ float red[kFinalizeRows][33];
   const int col = blockIdx.x * 32 + threadIdx.x;  // 0 .. 2c-1 (sums and second sums side by side)
   float acc = 0.f;
   if (col < 2 * c)
-    for (int p = threadIdx.y; p < partials; p += 8) acc += ws[static_cast<int64_t>(p) * 2 * c + col];
+    for (int p = threadIdx.y; p < partials; p += kFinalizeRows) acc += ws[static_cast<int64_t>(p) * 2 * c + col];
   red[threadIdx.y][threadIdx.x] = acc;
   __syncthreads();
   if (threadIdx.y == 0 && col < 2 * c) {
     float s = 0.f;
 #pragma unroll
-    for (int j = 0; j < 8; ++j) s += red[j][threadIdx.x];
+    for (int j = 0; j < kFinalizeRows; ++j) s += red[j][threadIdx.x];
     ws[static_cast<int64_t>(partials) * 2 * c + col] = s;
   }
 }
@@ -365,7 +366,7 @@ int tipsk_bn_fwd_train(const void* x, const void* residual, void* y, const float
     size_t smem = sizeof(float) * 256 * 2 * V;
     BnReduceKernel<T, V, false><<<grid, block, smem, s>>>(static_cast<const T*>(x), nullptr, nullptr, nullptr, nullptr,
                                                           workspace, m, c, 0);
-    BnFinalizeKernel<<<CeilDiv(2 * c, 32), dim3(32, 8), 0, s>>>(workspace, g.partials, c);
+    BnFinalizeKernel<<<CeilDiv(2 * c, 32), dim3(32, kFinalizeRows), 0, s>>>(workspace, g.partials, c);
     BnApplyKernel<T, V><<<grid, block, sizeof(float) * 256 * 2 * V, s>>>(static_cast<const T*>(x), static_cast<const T*>(residual),
                                                static_cast<T*>(y), gamma, beta, running_mean, running_var, save_mean,
                                                save_invstd, workspace, g.partials, m, c, eps, momentum, relu, 1);
@@ -424,7 +425,7 @@ int tipsk_bn_bwd(const void* dy, const void* x, const void* y, const float* gamm
     BnReduceKernel<T, V, true><<<grid, block, smem, s>>>(static_cast<const T*>(dy), static_cast<const T*>(x),
                                                          static_cast<const T*>(y), save_mean, save_invstd, workspace, m,
                                                          c, relu);
-    BnFinalizeKernel<<<CeilDiv(2 * c, 32), dim3(32, 8), 0, s>>>(workspace, g.partials, c);
+    BnFinalizeKernel<<<CeilDiv(2 * c, 32), dim3(32, kFinalizeRows), 0, s>>>(workspace, g.partials, c);
     BnBwdApplyKernel<T, V><<<grid, block, smem, s>>>(static_cast<const T*>(dy), static_cast<const T*>(x),
                                                   static_cast<const T*>(y), gamma, save_mean, save_invstd,
                                                   static_cast<T*>(dx), static_cast<T*>(dresidual), dgamma, dbeta,
@@ -451,7 +452,7 @@ int tipsk_bn_fwd_train_mask(const void* x, const void* residual, void* y, const 
     if (stats == nullptr) {
       BnReduceKernel<T, V, false><<<grid, block, smem, s>>>(static_cast<const T*>(x), nullptr, nullptr, nullptr, nullptr,
                                                             workspace, m, c, 0);
-      BnFinalizeKernel<<<CeilDiv(2 * c, 32), dim3(32, 8), 0, s>>>(workspace, g.partials, c);
+      BnFinalizeKernel<<<CeilDiv(2 * c, 32), dim3(32, kFinalizeRows), 0, s>>>(workspace, g.partials, c);
     }
     BnApplyKernel<T, V><<<grid, block, smem, s>>>(static_cast<const T*>(x), static_cast<const T*>(residual),
                                                   static_cast<T*>(y), gamma, beta, running_mean, running_var, save_mean,
@@ -476,7 +477,7 @@ int tipsk_bn_bwd_bitmask(const void* dy, const void* x, const void* relu_mask, c
     BnReduceKernel<T, V, true, 2><<<grid, block, smem, s>>>(static_cast<const T*>(dy), static_cast<const T*>(x), nullptr,
                                                             save_mean, save_invstd, workspace, m, c, 1, nullptr, nullptr,
                                                             static_cast<const uint8_t*>(relu_mask));
-    BnFinalizeKernel<<<CeilDiv(2 * c, 32), dim3(32, 8), 0, s>>>(workspace, g.partials, c);
+    BnFinalizeKernel<<<CeilDiv(2 * c, 32), dim3(32, kFinalizeRows), 0, s>>>(workspace, g.partials, c);
     BnBwdApplyKernel<T, V, 2><<<grid, block, smem, s>>>(static_cast<const T*>(dy), static_cast<const T*>(x), nullptr, gamma,
                                                      save_mean, save_invstd, static_cast<T*>(dx),
                                                      static_cast<T*>(dresidual), dgamma, dbeta, workspace, g.partials, m,
@@ -501,7 +502,7 @@ int tipsk_bn_bwd_relu_recompute(const void* dy, const void* x, const float* gamm
     BnReduceKernel<T, V, true, 1><<<grid, block, smem, s>>>(static_cast<const T*>(dy), static_cast<const T*>(x),
                                                                nullptr, save_mean, save_invstd, workspace, m, c, 1,
                                                                gamma, beta);
-    BnFinalizeKernel<<<CeilDiv(2 * c, 32), dim3(32, 8), 0, s>>>(workspace, g.partials, c);
+    BnFinalizeKernel<<<CeilDiv(2 * c, 32), dim3(32, kFinalizeRows), 0, s>>>(workspace, g.partials, c);
     BnBwdApplyKernel<T, V, 1><<<grid, block, smem, s>>>(static_cast<const T*>(dy), static_cast<const T*>(x), nullptr,
                                                         gamma, save_mean, save_invstd, static_cast<T*>(dx), nullptr,
                                                         dgamma, dbeta, workspace, g.partials, m, c, 1, beta);

@@ -1,7 +1,7 @@
 """Small single-kernel cases for profiler captures: each runs ONE kernel a handful of times on inputs a
 little larger than L2, holds well under a GB on the device and exits by itself in seconds.
 
-    python -m tips_b200.bench.profile_case {bn_fwd,bn_bwd,gemm,gemm_persistent,ln,sgd,ps_pull,ps_push}
+    python -m tips_b200.bench.profile_case {bn_fwd,bn_bwd,gemm,gemm_persistent,ln,sgd,ps_pull,ps_push,conv1x1,conv3x3,conv_dgrad,conv_wgrad}
 """
 from __future__ import annotations
 
@@ -36,6 +36,21 @@ def main(argv=None):
         bias = torch.randn(4096, device=dev).to(torch.bfloat16)
         for _ in range(reps):
             gemm_tn(a, b, bias, "relu")
+    elif case in ("conv1x1", "conv3x3", "conv_dgrad", "conv_wgrad"):
+        from tips_b200.ops import conv as C
+        k, cin, cout = (1, 64, 256) if case == "conv1x1" else (3, 64, 64)
+        x = torch.randn(128, cin, 56, 56, device=dev).to(torch.bfloat16).contiguous(memory_format=torch.channels_last)
+        w = (torch.randn(cout, k, k, cin, device=dev) * 0.05).to(torch.bfloat16)
+        stats = torch.zeros(2, cout, dtype=torch.float32, device=dev)
+        _, y = C.conv2d_forward(x, w, 1, k // 2, stats)
+        dy = torch.randn_like(y)
+        for _ in range(reps):
+            if case == "conv_dgrad":
+                C.conv2d_dgrad(dy, w, tuple(x.shape), 1, k // 2)
+            elif case == "conv_wgrad":
+                C.conv2d_wgrad(x, dy, tuple(w.shape), 1, k // 2)
+            else:
+                C.conv2d_forward(x, w, 1, k // 2, stats)
     elif case == "ln":
         from tips_b200.ops.norm import LayerNorm
         x = torch.randn(131072, 1024, device=dev).to(torch.bfloat16)

@@ -1,0 +1,116 @@
+"""Host parameter server on CPU ranks: routing, lazy rows, server-side update rules, dumps.
+
+Mirrors the reference's PS integration tests (tips/core/ps/ps_server_test.cc:55-131: pull of unknown keys gives
+zeros, push of rows; ps_client_test.cc:11-85: one server, several clients, keys {0, 3, 200}) and closes their gaps:
+numeric checks of the update rules, several servers, duplicate keys, dump and reload under another sharding.
+"""
+import os
+
+import numpy as np
+import pytest
+
+from mp_util import run_ranks
+
+
+def _one_server_many_clients(rank, size):
+    import tips_b200 as tips
+    from tips_b200.ps.host import HostSparseTable, Route
+    table = HostSparseTable("t1", dim=4, route=Route(servers=[0]), optimizer="sgd", lr=0.5)
+    keys = np.array([0, 3, 200], dtype=np.uint64)
+    rows = table.pull(keys)
+    assert rows.shape == (3, 4)
+    tips.barrier()
+    # every rank pushes a gradient of ones for key 3
+    table.push(np.array([3], dtype=np.uint64), np.ones((1, 4), dtype=np.float32))
+    tips.barrier()
+    got = table.pull(np.array([3, 0], dtype=np.uint64))
+    assert np.allclose(got[0], -0.5 * size), got  # w -= lr * g, once per pushing rank
+    assert np.allclose(got[1], 0.0)
+    assert all(table.server_of(int(k)) == 0 for k in keys)
+    if rank == 0:
+        assert table.local_size() >= 3
+    else:
+        assert table.local_size() == 0
+    table.close()
+
+
+def test_one_server_many_clients():
+    run_ranks(_one_server_many_clients, 4)
+
+
+def _multi_server_rules(rank, size, rule):
+    import tips_b200 as tips
+    from tips_b200.ps.host import HostSparseTable, Route
+    servers = [0, 1, 2]
+    lr, eps = 0.1, 1e-8
+    table = HostSparseTable("t2", dim=8, route=Route(servers=servers), optimizer=rule, lr=lr, eps=eps, local_shards=2)
+    rng = np.random.default_rng(7)  # same stream on every rank
+    keys = rng.integers(0, 2**40, size=64).astype(np.uint64)
+    keys[10] = keys[3]  # duplicates inside one request
+    keys[11] = keys[3]
+    owners = {table.server_of(int(k)) for k in keys}
+    assert owners <= set(servers) and len(owners) > 1
+    w = {int(k): np.zeros(8, dtype=np.float64) for k in keys}
+    acc = {int(k): np.zeros(8, dtype=np.float64) for k in keys}
+    assert np.all(table.pull(keys) == 0)
+    tips.barrier()
+    for step in range(3):
+        grads = rng.standard_normal((keys.size, 8)).astype(np.float32)
+        if rank == step % size:  # one pusher per step keeps the expected order of updates well defined
+            missing = table.push(keys, grads)
+            assert missing == 0
+        for k, g in zip(keys, grads.astype(np.float64)):
+            k = int(k)
+            if rule == "sgd":
+                w[k] -= lr * g
+            else:
+                acc[k] += g * g
+                w[k] -= lr * g / (np.sqrt(acc[k]) + eps)
+        tips.barrier()
+        got = table.pull(keys)
+        want = np.stack([w[int(k)] for k in keys])
+        assert np.allclose(got, want, rtol=1e-4, atol=1e-5), (rule, step, np.abs(got - want).max())
+        tips.barrier()
+    c = table.counters()
+    assert c["rows_pulled"] >= 0 and c["rows_pushed"] >= 0
+    table.close()
+
+
+@pytest.mark.parametrize("rule", ["sgd", "adagrad"])
+def test_multi_server_update_rules(rule):
+    run_ranks(_multi_server_rules, 3, rule)
+
+
+def _dump(rank, size, folder, servers, binary, phase):
+    import tips_b200 as tips
+    from tips_b200.ps.host import HostSparseTable, Route
+    table = HostSparseTable("t3", dim=3, route=Route(servers=servers), optimizer="sgd", lr=1.0)
+    keys = np.arange(1, 41, dtype=np.uint64) * 7919
+    if phase == "write":
+        table.pull(keys)
+        tips.barrier()
+        if rank == 0:
+            table.push(keys, np.tile(-keys.astype(np.float32)[:, None], (1, 3)))  # row of key k becomes k
+        tips.barrier()
+        table.save(os.path.join(folder, f"dump.{rank}"), binary=binary)
+        if not binary and table.local_size():
+            line = open(os.path.join(folder, f"dump.{rank}")).readline()
+            key, tag, rest = line.rstrip("\n").split("\t")
+            assert tag == "Vec:" and len(rest.split()) == 3  # "<key>\tVec:\t<e> <e> <e> "
+    else:
+        for src in range(size):  # every rank reads every file and keeps the rows it owns now
+            path = os.path.join(folder, f"dump.{src}")
+            if os.path.exists(path) and os.path.getsize(path):
+                table.load(path, binary=binary)
+        tips.barrier()
+        got = table.pull(keys)
+        assert np.allclose(got, np.tile(keys.astype(np.float32)[:, None], (1, 3)))
+        total = tips.allreduce_value(float(table.local_size()), name="t3.rows", average=False)
+        assert int(total.item()) == keys.size
+    table.close()
+
+
+@pytest.mark.parametrize("binary", [False, True])
+def test_dump_and_reload_under_another_sharding(tmp_path, binary):
+    run_ranks(_dump, 3, str(tmp_path), [0, 1, 2], binary, "write")
+    run_ranks(_dump, 3, str(tmp_path), [1, 2], binary, "read")

@@ -59,7 +59,8 @@ class CtrTrainer:
         self.device = device or torch.device("cuda", torch.cuda.current_device())
         self.fields, self.dim, self.dense = num_fields, dim, dense_features
         self.emb_cols = num_fields * dim
-        self.in_features = (self.emb_cols + dense_features + 7) // 8 * 8  # row stride must be a multiple of 16 bytes
+        # padded to a multiple of 64 columns (zero-filled): the weight-gradient kernel contracts 64-channel boxes
+        self.in_features = (self.emb_cols + dense_features + 63) // 64 * 64
         self.tables = ShardedEmbedding(num_fields, rows_per_table, dim, optimizer="adagrad", lr=table_lr,
                                        init_scale=0.05, seed=seed, expected_batch=expected_batch, device=self.device)
         torch.manual_seed(seed + 17)

@@ -5,8 +5,10 @@ and activation fused into the epilogue.  ``Linear`` builds forward and backward 
 
     y  = act(x W^T + b)                      gemm_tn(x, W)
     dz = dy * act'(.) ; db = colsum(dz)      one pass (bias_act_bwd kernel)
-    dx = dz W                                gemm_tn(dz, W^T)
-    dW = dz^T x                              gemm_tn(dz^T, x^T)
+    dx = dz W                                gemm_tn(dz, W^T)   (only the small weight is transposed)
+    dW = dz^T x                              the split-K weight-gradient kernel of conv_tcgen05.cu, which reads dz and x
+                                             as they are (both operands MN-major); transposed copies of the
+                                             activations only for feature counts that are not multiples of 64
 
 The reference has no GEMM or linear layer; this serves the CTR MLP and the BERT-shaped encoder.
 CPU tensors (host-only tests) and shapes the kernel does not take (row strides that are not a
@@ -52,9 +54,25 @@ def gemm_tn(a, b, bias=None, act=None, want_pre=False):
     return (c, pre) if want_pre else c
 
 
+def _weight_grad(dz: torch.Tensor, x2: torch.Tensor) -> torch.Tensor:
+    """dz^T @ x2 as [N, K].  A linear layer is a 1x1 convolution over "pixels" = rows, so the convolution's
+    weight-gradient kernel applies: it contracts over the rows with both operands read in place."""
+    m, n = dz.shape
+    k = x2.shape[1]
+    if (dz.is_cuda and dz.dtype == torch.bfloat16 and x2.dtype == torch.bfloat16 and n % 64 == 0 and k % 64 == 0
+            and m >= 16 and dz.is_contiguous() and x2.is_contiguous()
+            and dz.data_ptr() % 16 == 0 and x2.data_ptr() % 16 == 0):
+        dw = torch.empty(n, k, dtype=torch.float32, device=dz.device)
+        base.check(base.K().tipsk_conv2d_wgrad(x2.data_ptr(), dz.data_ptr(), dw.data_ptr(), 1, 1, m, k, n, 1, 1, 1, 0,
+                                               base.stream()), "linear_wgrad")
+        return dw
+    return gemm_tn(dz.t().contiguous(), x2.t().contiguous())
+
+
 def gemm_status() -> int:
     """0 when no GEMM launch since the last call reported a bounded-wait timeout (synchronises)."""
-    return int(base.K().tipsk_gemm_status())
+    lib = base.K()
+    return int(lib.tipsk_gemm_status()) or int(lib.tipsk_conv_status())  # the weight gradient runs on the conv kernels
 
 
 class _LinearFn(torch.autograd.Function):
@@ -109,7 +127,7 @@ class _LinearFn(torch.autograd.Function):
         if ctx.needs_input_grad[0]:
             dx = gemm_tn(dz, weight.t().contiguous()).view(ctx.in_shape)
         if ctx.needs_input_grad[1]:
-            dw = gemm_tn(dz.t().contiguous(), x2.t().contiguous()).to(weight.dtype)
+            dw = _weight_grad(dz, x2).to(weight.dtype)
         return dx, dw, dbias, None
 
 

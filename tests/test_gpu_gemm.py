@@ -42,3 +42,17 @@ def test_linear_module_grads():
     assert torch.allclose(x.grad.float(), xr.grad, atol=0.3, rtol=5e-2)
     assert torch.allclose(lin.weight.grad.float(), w.grad, atol=0.6, rtol=5e-2)
     assert torch.allclose(lin.bias.grad.float(), b.grad, atol=0.6, rtol=5e-2)
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 64, 64), (256, 512, 256), (8192, 1728, 512), (300, 1000, 2048),
+                                   (16384, 1024, 4096), (20000, 256, 512)])
+def test_gemm_nn(m, n, k):
+    from tips_b200.ops.linear import gemm_nn, gemm_status
+    torch.manual_seed(m + n + k)
+    dev = torch.device("cuda", 0)
+    a = (torch.randn(m, k, device=dev) * 0.5).to(torch.bfloat16)
+    b = (torch.randn(k, n, device=dev) * 0.5).to(torch.bfloat16)
+    y = gemm_nn(a, b)
+    assert gemm_status() == 0
+    ref = a.float() @ b.float()
+    assert (y.float() - ref).abs().max() <= 1e-2 * max(1.0, float(ref.abs().max()))

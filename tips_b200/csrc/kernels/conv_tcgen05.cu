@@ -371,14 +371,6 @@ struct WgradMaps {
 
 constexpr int kMnBoxBytes = kBM * 128;  // one 64-channel box of up to 128 pixels
 
-// Descriptor of an MN-major, 128-byte-swizzled operand: leading-dimension offset = distance between
-// 64-element chunks along M/N (one box), stride offset = distance between 8-row groups along K.
-__device__ __forceinline__ uint64_t SmemDescMnSw128(uint32_t smem_addr) {
-  const uint32_t lo = ((smem_addr & 0x3FFFFu) >> 4) | (static_cast<uint32_t>(kMnBoxBytes >> 4) << 16);
-  const uint32_t hi = (1024u >> 4) | (1u << 14) | (2u << 29);
-  return (static_cast<uint64_t>(hi) << 32) | lo;
-}
-
 template <int BN>
 struct WgradCfg {
   static constexpr int kStages     = BN >= 128 ? 3 : 4;
@@ -471,8 +463,8 @@ ConvWgradKernel(const __grid_constant__ WgradMaps maps, const __grid_constant__ 
         }
         TcFenceAfter();
         const uint32_t a_addr = SmemAddr(smem + s * Cfg::kStageBytes);
-        const uint64_t adesc  = SmemDescMnSw128(a_addr);
-        const uint64_t bdesc  = SmemDescMnSw128(a_addr + Cfg::kABytes);
+        const uint64_t adesc  = SmemDescMnSw128(a_addr, kMnBoxBytes);
+        const uint64_t bdesc  = SmemDescMnSw128(a_addr + Cfg::kABytes, kMnBoxBytes);
         for (int k = 0; k < ksteps; ++k) {
           // 16 pixels further along K = 16 rows of 128 bytes
           UmmaBf16(tmem_base, adesc + static_cast<uint64_t>(k) * (2048 >> 4), bdesc + static_cast<uint64_t>(k) * (2048 >> 4),

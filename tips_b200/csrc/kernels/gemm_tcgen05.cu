@@ -54,7 +54,9 @@ struct GemmCfg {
   static constexpr int kSmemBytes  = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
 };
 
-template <int BN>
+// kBMn: B is given as [K, N] row-major (the contraction runs over its rows), loaded as BN/64 boxes of
+// [64 x 64] and read by the MMA as an MN-major operand; used for dx = dy * W without transposing W.
+template <int BN, bool kBMn = false>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 GemmTnKernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
              const __grid_constant__ CUtensorMap tmap_c, GemmParams p) {
@@ -104,13 +106,18 @@ GemmTnKernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
         uint8_t* b_dst = a_dst + Cfg::kABytes;
         MbarExpectTx(&full_bar[s], Cfg::kStageBytes);
         TmaLoad2D(a_dst, &tmap_a, kt * kBK, m0, &full_bar[s]);
-        TmaLoad2D(b_dst, &tmap_b, kt * kBK, n0, &full_bar[s]);
+        if (kBMn) {
+#pragma unroll
+          for (int j = 0; j < BN / 64; ++j) TmaLoad2D(b_dst + j * 8192, &tmap_b, n0 + j * 64, kt * kBK, &full_bar[s]);
+        } else {
+          TmaLoad2D(b_dst, &tmap_b, kt * kBK, n0, &full_bar[s]);
+        }
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(BN >> 3) << 17) |
-                                 (static_cast<uint32_t>(kBM >> 4) << 24);
+      constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (kBMn ? (1u << 16) : 0u) |
+                                 (static_cast<uint32_t>(BN >> 3) << 17) | (static_cast<uint32_t>(kBM >> 4) << 24);
       bool ok = true;
       for (int kt = 0; kt < num_k && ok; ++kt) {
         const int s = kt % Cfg::kStages;
@@ -124,11 +131,12 @@ GemmTnKernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
         const uint32_t a_addr = SmemAddr(smem + s * Cfg::kStageBytes);
         const uint32_t b_addr = a_addr + Cfg::kABytes;
         const uint64_t adesc  = SmemDescSw128(a_addr);
-        const uint64_t bdesc  = SmemDescSw128(b_addr);
+        const uint64_t bdesc  = kBMn ? SmemDescMnSw128(b_addr, 8192) : SmemDescSw128(b_addr);
 #pragma unroll
         for (int k = 0; k < kBK / 16; ++k) {
-          // advancing 16 elements (32 bytes) along K inside the swizzle row = +2 in the address field
-          UmmaBf16(tmem_base, adesc + 2 * k, bdesc + 2 * k, idesc, (kt > 0 || k > 0) ? 1u : 0u);
+          // advancing 16 elements (32 bytes) along K inside the swizzle row = +2 in the address field;
+          // for the MN-major B sixteen K rows = 2048 bytes = +128
+          UmmaBf16(tmem_base, adesc + 2 * k, bdesc + (kBMn ? 128 : 2) * k, idesc, (kt > 0 || k > 0) ? 1u : 0u);
         }
         UmmaCommit(&empty_bar[s]);
       }
@@ -261,7 +269,7 @@ struct PersistCfg {
   static constexpr int kSmemBytes  = kStages * kStageBytes + kStagingBytes + 1024 + 256;
 };
 
-template <int BN>
+template <int BN, bool kBMn = false>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 GemmTnPersistentKernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                        const __grid_constant__ CUtensorMap tmap_c, GemmParams p) {
@@ -320,14 +328,20 @@ GemmTnPersistentKernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
           uint8_t* a_dst = smem + s * Cfg::kStageBytes;
           MbarExpectTx(&full_bar[s], Cfg::kStageBytes);
           TmaLoad2D(a_dst, &tmap_a, kt * kBK, m0, &full_bar[s]);
-          TmaLoad2D(a_dst + Cfg::kABytes, &tmap_b, kt * kBK, n0, &full_bar[s]);
+          if (kBMn) {
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j)
+              TmaLoad2D(a_dst + Cfg::kABytes + j * 8192, &tmap_b, n0 + j * 64, kt * kBK, &full_bar[s]);
+          } else {
+            TmaLoad2D(a_dst + Cfg::kABytes, &tmap_b, kt * kBK, n0, &full_bar[s]);
+          }
         }
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(BN >> 3) << 17) |
-                                 (static_cast<uint32_t>(kBM >> 4) << 24);
+      constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (kBMn ? (1u << 16) : 0u) |
+                                 (static_cast<uint32_t>(BN >> 3) << 17) | (static_cast<uint32_t>(kBM >> 4) << 24);
       uint32_t it = 0;
       int local = 0;
       bool ok = true;
@@ -349,9 +363,10 @@ GemmTnPersistentKernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
           TcFenceAfter();
           const uint32_t a_addr = SmemAddr(smem + s * Cfg::kStageBytes);
           const uint64_t adesc  = SmemDescSw128(a_addr);
-          const uint64_t bdesc  = SmemDescSw128(a_addr + Cfg::kABytes);
+          const uint64_t bdesc  = kBMn ? SmemDescMnSw128(a_addr + Cfg::kABytes, 8192) : SmemDescSw128(a_addr + Cfg::kABytes);
 #pragma unroll
-          for (int k = 0; k < kBK / 16; ++k) UmmaBf16(tmem_d, adesc + 2 * k, bdesc + 2 * k, idesc, (kt > 0 || k > 0) ? 1u : 0u);
+          for (int k = 0; k < kBK / 16; ++k)
+            UmmaBf16(tmem_d, adesc + 2 * k, bdesc + (kBMn ? 128 : 2) * k, idesc, (kt > 0 || k > 0) ? 1u : 0u);
           UmmaCommit(&empty_bar[s]);
         }
         if (ok) UmmaCommit(&tmem_full[buf]);
@@ -455,36 +470,36 @@ int32_t* GemmErrorWord() {
   return word;
 }
 
-template <int BN>
+template <int BN, bool kBMn = false>
 int LaunchGemm(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const GemmParams& p,
                cudaStream_t s) {
   using Cfg = GemmCfg<BN>;
   static bool configured = false;
   if (!configured) {
-    TIPSK_CUDA(cudaFuncSetAttribute(GemmTnKernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
-    TIPSK_CUDA(cudaFuncSetAttribute(GemmTnKernel<BN>, cudaFuncAttributePreferredSharedMemoryCarveout,
+    TIPSK_CUDA(cudaFuncSetAttribute(GemmTnKernel<BN, kBMn>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
+    TIPSK_CUDA(cudaFuncSetAttribute(GemmTnKernel<BN, kBMn>, cudaFuncAttributePreferredSharedMemoryCarveout,
                                     cudaSharedmemCarveoutMaxShared));
     configured = true;
   }
   dim3 grid((p.n + BN - 1) / BN, (p.m + kBM - 1) / kBM);
-  GemmTnKernel<BN><<<grid, kGemmThreads, Cfg::kSmemBytes, s>>>(ta, tb, tc, p);
+  GemmTnKernel<BN, kBMn><<<grid, kGemmThreads, Cfg::kSmemBytes, s>>>(ta, tb, tc, p);
   TIPSK_LAUNCH_CHECK();
   return 0;
 }
 
-template <int BN>
+template <int BN, bool kBMn = false>
 int LaunchGemmPersistent(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const GemmParams& p,
                          cudaStream_t s) {
   using Cfg = PersistCfg<BN>;
   static bool configured = false;
   if (!configured) {
-    TIPSK_CUDA(cudaFuncSetAttribute(GemmTnPersistentKernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    TIPSK_CUDA(cudaFuncSetAttribute(GemmTnPersistentKernel<BN, kBMn>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                     Cfg::kSmemBytes));
     configured = true;
   }
   const int tiles = ((p.n + BN - 1) / BN) * ((p.m + kBM - 1) / kBM);
   const int grid  = tiles < NumSMs() ? tiles : NumSMs();
-  GemmTnPersistentKernel<BN><<<grid, kGemmThreads, Cfg::kSmemBytes, s>>>(ta, tb, tc, p);
+  GemmTnPersistentKernel<BN, kBMn><<<grid, kGemmThreads, Cfg::kSmemBytes, s>>>(ta, tb, tc, p);
   TIPSK_LAUNCH_CHECK();
   return 0;
 }
@@ -548,6 +563,45 @@ int tipsk_gemm_bf16(const void* a, const void* b, void* c, const void* bias, voi
     case 64: return LaunchGemm<64>(ta, tb, tc, p, s);
     case 256: return LaunchGemm<256>(ta, tb, tc, p, s);
     default: return LaunchGemm<128>(ta, tb, tc, p, s);
+  }
+}
+
+/* C[m,n] = A[m,k] * B[k,n]: B row-major with the contraction over its rows (no transposed copy is made; the MMA
+ * reads it as an MN-major operand).  Serves dx = dy * W of a linear layer with W stored [out, in].  n >= 64. */
+int tipsk_gemm_bf16_nn(const void* a, const void* b, void* c, int m, int n, int k, int lda, int ldb, int ldc,
+                       void* stream) {
+  TIPSK_REQUIRE(m > 0 && n >= 64 && k > 0 && lda % 8 == 0 && ldb % 8 == 0 && ldc % 8 == 0,
+                "gemm_nn: leading dimensions must be multiples of 8 elements and n >= 64");
+  TIPSK_REQUIRE(reinterpret_cast<uintptr_t>(c) % 16 == 0, "gemm_nn: output must be 16-byte aligned");
+  int bn = 128;
+  if (n <= 64) bn = 64;
+  else if (n % 256 == 0 && (static_cast<int64_t>(m) / kBM) * (n / 256) >= NumSMs()) bn = 256;
+  CUtensorMap ta, tb, tc;
+  int rc = MakeTmap(&ta, a, m, k, lda, kBM);
+  if (rc) return rc;
+  rc = MakeTmap(&tb, b, k, n, ldb, kBK);  // boxes of 64 contraction rows x 64 columns
+  if (rc) return rc;
+  rc = MakeTmap(&tc, c, m, n, ldc, kBM);
+  if (rc) return rc;
+  GemmParams p;
+  p.c = static_cast<__nv_bfloat16*>(c);
+  p.pre = nullptr;
+  p.bias = nullptr;
+  p.error = GemmErrorWord();
+  TIPSK_REQUIRE(p.error != nullptr, "gemm: cannot allocate the error word");
+  p.m = m; p.n = n; p.k = k; p.ldc = ldc; p.act = 0; p.tma_store = 1;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (bn != 64) {
+    const int64_t tiles = static_cast<int64_t>((n + bn - 1) / bn) * ((m + kBM - 1) / kBM);
+    if (tiles >= 3 * NumSMs() && k <= 2048) {
+      if (bn == 256) return LaunchGemmPersistent<256, true>(ta, tb, tc, p, s);
+      return LaunchGemmPersistent<128, true>(ta, tb, tc, p, s);
+    }
+  }
+  switch (bn) {
+    case 64: return LaunchGemm<64, true>(ta, tb, tc, p, s);
+    case 256: return LaunchGemm<256, true>(ta, tb, tc, p, s);
+    default: return LaunchGemm<128, true>(ta, tb, tc, p, s);
   }
 }
 

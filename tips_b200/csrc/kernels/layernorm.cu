@@ -161,18 +161,33 @@ LnBwdKernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __restri
   }
 }
 
+// Column sums of the per-block partial gradients. Block (32, 32): tx = column, ty strides over the partial rows.
 template <typename T>
-__global__ void LnReducePartialsKernel(const float* __restrict__ pg, const float* __restrict__ pb, int partial_rows,
-                                       int cols, T* __restrict__ dgamma, T* __restrict__ dbeta) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= cols) return;
+__global__ void __launch_bounds__(1024)
+LnReducePartialsKernel(const float* __restrict__ pg, const float* __restrict__ pb, int partial_rows, int cols,
+                       T* __restrict__ dgamma, T* __restrict__ dbeta) {
+  __shared__ float ra[32][33], rb[32][33];
+  const int c = blockIdx.x * 32 + threadIdx.x;
   float a = 0.f, b = 0.f;
-  for (int p = 0; p < partial_rows; ++p) {
-    a += pg[static_cast<int64_t>(p) * cols + c];
-    b += pb[static_cast<int64_t>(p) * cols + c];
+  if (c < cols) {
+    for (int p = threadIdx.y; p < partial_rows; p += 32) {
+      a += pg[static_cast<int64_t>(p) * cols + c];
+      b += pb[static_cast<int64_t>(p) * cols + c];
+    }
   }
-  dgamma[c] = FromFloat<T>(a);
-  dbeta[c]  = FromFloat<T>(b);
+  ra[threadIdx.y][threadIdx.x] = a;
+  rb[threadIdx.y][threadIdx.x] = b;
+  __syncthreads();
+  if (threadIdx.y == 0 && c < cols) {
+    float sa = 0.f, sb = 0.f;
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      sa += ra[j][threadIdx.x];
+      sb += rb[j][threadIdx.x];
+    }
+    dgamma[c] = FromFloat<T>(sa);
+    dbeta[c]  = FromFloat<T>(sb);
+  }
 }
 
 int LnGrid(int64_t rows) {
@@ -245,16 +260,17 @@ int tipsk_ln_bwd(const void* dy, const void* x, const void* gamma, const float* 
 int tipsk_ln_reduce_partials(const float* dgamma_partial, const float* dbeta_partial, int partial_rows, int cols,
                              void* dgamma, void* dbeta, int dtype, void* stream) {
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  const int grid = CeilDiv(cols, 128);
+  const int grid = CeilDiv(cols, 32);
+  const dim3 block(32, 32);
   if (dtype == kBF16)
-    LnReducePartialsKernel<__nv_bfloat16><<<grid, 128, 0, s>>>(dgamma_partial, dbeta_partial, partial_rows, cols,
+    LnReducePartialsKernel<__nv_bfloat16><<<grid, block, 0, s>>>(dgamma_partial, dbeta_partial, partial_rows, cols,
                                                                static_cast<__nv_bfloat16*>(dgamma),
                                                                static_cast<__nv_bfloat16*>(dbeta));
   else if (dtype == kF16)
-    LnReducePartialsKernel<__half><<<grid, 128, 0, s>>>(dgamma_partial, dbeta_partial, partial_rows, cols,
+    LnReducePartialsKernel<__half><<<grid, block, 0, s>>>(dgamma_partial, dbeta_partial, partial_rows, cols,
                                                         static_cast<__half*>(dgamma), static_cast<__half*>(dbeta));
   else if (dtype == kF32)
-    LnReducePartialsKernel<float><<<grid, 128, 0, s>>>(dgamma_partial, dbeta_partial, partial_rows, cols,
+    LnReducePartialsKernel<float><<<grid, block, 0, s>>>(dgamma_partial, dbeta_partial, partial_rows, cols,
                                                        static_cast<float*>(dgamma), static_cast<float*>(dbeta));
   else
     return SetError(-2, "layer norm: unsupported dtype");

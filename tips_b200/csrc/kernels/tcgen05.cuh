@@ -66,6 +66,15 @@ __device__ __forceinline__ uint64_t SmemDescSw128(uint32_t smem_addr) {
   return (static_cast<uint64_t>(hi) << 32) | lo;
 }
 
+// Descriptor of an MN-major, 128-byte-swizzled operand made of boxes [K rows x 64 elements]: the leading-dimension
+// offset is the distance between boxes (64-element chunks along M/N), the stride offset the distance between
+// 8-row groups along K (1024 bytes).  Sixteen rows further along K is +2048 bytes = +128 in the address field.
+__device__ __forceinline__ uint64_t SmemDescMnSw128(uint32_t smem_addr, uint32_t box_pitch_bytes) {
+  const uint32_t lo = ((smem_addr & 0x3FFFFu) >> 4) | ((box_pitch_bytes >> 4) << 16);
+  const uint32_t hi = (1024u >> 4) | (1u << 14) | (2u << 29);
+  return (static_cast<uint64_t>(hi) << 32) | lo;
+}
+
 __device__ __forceinline__ void UmmaBf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accum) {
   asm volatile(
       "{\n\t.reg .pred p;\n\t"

@@ -146,6 +146,9 @@ int tipsk_ps_push(const int64_t* const* host_ids, const void* const* host_grads,
 int tipsk_gemm_supported(int m, int n, int k, int lda, int ldb);
 int tipsk_gemm_bf16(const void* a, const void* b, void* c, const void* bias, void* pre, int m, int n, int k, int lda,
                     int ldb, int ldc, int act, void* stream);
+/* C[m,n] = A[m,k] * B[k,n] with B row-major [k, n] (contraction over its rows), n >= 64. */
+int tipsk_gemm_bf16_nn(const void* a, const void* b, void* c, int m, int n, int k, int lda, int ldb, int ldc,
+                       void* stream);
 int tipsk_gemm_status(void);
 
 /* ---- 3x3 / stride 2 / pad 1 max pooling on NHWC (pool.cu); idx holds the argmax position 0..8 per output ---- */

@@ -5,7 +5,7 @@ and activation fused into the epilogue.  ``Linear`` builds forward and backward 
 
     y  = act(x W^T + b)                      gemm_tn(x, W)
     dz = dy * act'(.) ; db = colsum(dz)      one pass (bias_act_bwd kernel)
-    dx = dz W                                gemm_tn(dz, W^T)   (only the small weight is transposed)
+    dx = dz W                                gemm_nn(dz, W): W is read in place as an MN-major operand
     dW = dz^T x                              the split-K weight-gradient kernel of conv_tcgen05.cu, which reads dz and x
                                              as they are (both operands MN-major); transposed copies of the
                                              activations only for feature counts that are not multiples of 64
@@ -52,6 +52,19 @@ def gemm_tn(a, b, bias=None, act=None, want_pre=False):
     base.check(base.K().tipsk_gemm_bf16(a.data_ptr(), b.data_ptr(), c.data_ptr(), base.ptr(bb), base.ptr(pre), m, n, k,
                                         a.stride(0), b.stride(0), n, code, base.stream()), "gemm_bf16")
     return (c, pre) if want_pre else c
+
+
+def gemm_nn(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """a @ b for bf16 row-major a [M,K] and b [K,N]: b is read in place as an MN-major operand."""
+    m, k = a.shape
+    n = b.shape[1]
+    assert b.shape[0] == k
+    if not (_supported(a, b) and n >= 64 and n % 8 == 0):
+        return gemm_tn(a, b.t().contiguous())
+    c = torch.empty(m, n, dtype=torch.bfloat16, device=a.device)
+    base.check(base.K().tipsk_gemm_bf16_nn(a.data_ptr(), b.data_ptr(), c.data_ptr(), m, n, k, a.stride(0), b.stride(0),
+                                           n, base.stream()), "gemm_bf16_nn")
+    return c
 
 
 def _weight_grad(dz: torch.Tensor, x2: torch.Tensor) -> torch.Tensor:
@@ -125,7 +138,7 @@ class _LinearFn(torch.autograd.Function):
                 dbias = dz.float().sum(0).to(bias.dtype)
         dx = dw = None
         if ctx.needs_input_grad[0]:
-            dx = gemm_tn(dz, weight.t().contiguous()).view(ctx.in_shape)
+            dx = gemm_nn(dz, weight).view(ctx.in_shape)
         if ctx.needs_input_grad[1]:
             dw = _weight_grad(dz, x2).to(weight.dtype)
         return dx, dw, dbias, None

@@ -74,7 +74,7 @@ def test_noalloc_rejects_oversized_problem():
     The buffers are real and correctly sized, so even a library that failed to refuse would stay in bounds."""
     lib = _load()
     dev = torch.device("cuda", 0)
-    c, m = 50432, 256      # 197 column tiles -> 7 partial rows + 1 -> 806912 scratch floats > 786432
+    c, m = 200704, 256     # 784 column tiles -> 2 partial rows + 1 -> 1204224 scratch floats > 786432
     assert 2 * c * lib.tipsk_bn_partials(m, c) > 768 * 1024
     x = torch.randn(m, c, device=dev).to(torch.bfloat16)
     y = torch.empty_like(x)

@@ -48,6 +48,7 @@ struct ConvParams {
   float* stat_sq;   // optional per-channel sum of squares
   int taps, cblocks;               // filter taps, 64-channel blocks of the contraction
   int accumulate;                  // 1: add the result to what the output tensor holds (TMA reduce-add store)
+  int b_resident;                  // bytes of weights kept in shared memory for the whole kernel (0: streamed per stage)
   int tiles_w, tiles_h, tiles_n;   // boxes per output extent
   int tw, th, tn;                  // box extents; tw * th * tn <= 128
   int wo, ho, nb;                  // output extents (for the statistics mask)
@@ -87,7 +88,8 @@ __device__ __forceinline__ void TmaReduceAdd4D(const CUtensorMap* tmap, int c, i
 
 template <int BN>
 struct ConvCfg {
-  static constexpr int kStages       = BN >= 256 ? 3 : 4;
+  // A stage of a narrow tile carries few bytes, so it takes more stages to cover the load latency.
+  static constexpr int kStages       = BN >= 256 ? 3 : BN >= 128 ? 5 : 8;
   static constexpr int kABytes       = kBM * kBK * 2;
   static constexpr int kBBytes       = BN * kBK * 2;
   static constexpr int kStageBytes   = kABytes + kBBytes;
@@ -96,6 +98,7 @@ struct ConvCfg {
   static constexpr int kSmemBytes    = kStages * kStageBytes + kStagingBytes + 1024 + 256 + 4096 /*statistics*/;
 };
 
+constexpr int kMaxSmemBytes = 227 * 1024;  // dynamic shared memory limit per CTA
 constexpr int kConvThreads = 320;  // TMA warp, MMA warp, four epilogue warps, four statistics warps
 
 template <int BN>
@@ -105,11 +108,15 @@ ConvTapsKernel(const __grid_constant__ ConvMaps maps, const __grid_constant__ Co
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem    = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* staging = smem + Cfg::kStages * Cfg::kStageBytes;
-  uint64_t* full_bar   = reinterpret_cast<uint64_t*>(staging + Cfg::kStagingBytes);
+  // With a single tile of output channels and a small filter the whole weight matrix stays in shared memory
+  // (one [BN x 64] block per K step) instead of being re-read from L2 for every output tile.
+  uint8_t* resident    = staging + Cfg::kStagingBytes;
+  uint64_t* full_bar   = reinterpret_cast<uint64_t*>(resident + p.b_resident);
   uint64_t* empty_bar  = full_bar + Cfg::kStages;
   uint64_t* tmem_full  = empty_bar + Cfg::kStages;  // [2]
   uint64_t* tmem_empty = tmem_full + 2;             // [2]
-  uint32_t* tmem_slot  = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+  uint64_t* b_full     = tmem_empty + 2;
+  uint32_t* tmem_slot  = reinterpret_cast<uint32_t*>(b_full + 1);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -117,7 +124,8 @@ ConvTapsKernel(const __grid_constant__ ConvMaps maps, const __grid_constant__ Co
   const int m_tiles   = p.tiles_w * p.tiles_h * p.tiles_n;
   const int num_tiles = m_tiles * p.n_tiles;
   const int box_rows  = p.tw * p.th * p.tn;
-  const uint32_t stage_tx = static_cast<uint32_t>(box_rows) * 128u + Cfg::kBBytes;
+  const bool b_res    = p.b_resident > 0;
+  const uint32_t stage_tx = static_cast<uint32_t>(box_rows) * 128u + (b_res ? 0u : Cfg::kBBytes);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < Cfg::kStages; ++s) {
@@ -128,6 +136,7 @@ ConvTapsKernel(const __grid_constant__ ConvMaps maps, const __grid_constant__ Co
       MbarInit(&tmem_full[b], 1);
       MbarInit(&tmem_empty[b], 4);
     }
+    MbarInit(b_full, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
@@ -145,6 +154,12 @@ ConvTapsKernel(const __grid_constant__ ConvMaps maps, const __grid_constant__ Co
     if (lane == 0) {
       uint32_t it = 0;
       bool ok = true;
+      if (b_res) {
+        MbarExpectTx(b_full, static_cast<uint32_t>(p.b_resident));
+        for (int t = 0; t < p.taps; ++t)
+          for (int cb = 0; cb < p.cblocks; ++cb)
+            TmaLoad2D(resident + (t * p.cblocks + cb) * Cfg::kBBytes, &maps.b, p.tap[t].kofs + cb * kBK, 0, b_full);
+      }
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
         const int mt = tile / p.n_tiles, nt = tile % p.n_tiles;
         const int w0 = (mt % p.tiles_w) * p.tw;
@@ -162,7 +177,7 @@ ConvTapsKernel(const __grid_constant__ ConvMaps maps, const __grid_constant__ Co
             uint8_t* a_dst = smem + s * Cfg::kStageBytes;
             MbarExpectTx(&full_bar[s], stage_tx);
             TmaLoad4D(a_dst, &maps.a[tap.map], cb * kBK, w0 + tap.dw, h0 + tap.dh, n0, &full_bar[s]);
-            TmaLoad2D(a_dst + Cfg::kABytes, &maps.b, tap.kofs + cb * kBK, nt * BN, &full_bar[s]);
+            if (!b_res) TmaLoad2D(a_dst + Cfg::kABytes, &maps.b, tap.kofs + cb * kBK, nt * BN, &full_bar[s]);
           }
         }
       }
@@ -174,6 +189,10 @@ ConvTapsKernel(const __grid_constant__ ConvMaps maps, const __grid_constant__ Co
       uint32_t it = 0;
       int local = 0;
       bool ok = true;
+      if (b_res && !MbarWait(b_full, 0)) {
+        atomicExch(p.error, 5);
+        ok = false;
+      }
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
         const int buf = local & 1;
         if (!MbarWait(&tmem_empty[buf], ((local >> 1) & 1) ^ 1)) {
@@ -192,7 +211,7 @@ ConvTapsKernel(const __grid_constant__ ConvMaps maps, const __grid_constant__ Co
           TcFenceAfter();
           const uint32_t a_addr = SmemAddr(smem + s * Cfg::kStageBytes);
           const uint64_t adesc  = SmemDescSw128(a_addr);
-          const uint64_t bdesc  = SmemDescSw128(a_addr + Cfg::kABytes);
+          const uint64_t bdesc  = SmemDescSw128(b_res ? SmemAddr(resident) + kt * Cfg::kBBytes : a_addr + Cfg::kABytes);
 #pragma unroll
           for (int k = 0; k < kBK / 16; ++k) UmmaBf16(tmem_d, adesc + 2 * k, bdesc + 2 * k, idesc, (kt > 0 || k > 0) ? 1u : 0u);
           UmmaCommit(&empty_bar[s]);
@@ -610,12 +629,12 @@ int LaunchTaps(const ConvMaps& maps, const ConvParams& p, cudaStream_t s) {
   using Cfg = ConvCfg<BN>;
   static bool configured = false;
   if (!configured) {
-    TIPSK_CUDA(cudaFuncSetAttribute(ConvTapsKernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
+    TIPSK_CUDA(cudaFuncSetAttribute(ConvTapsKernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmemBytes));
     configured = true;
   }
   const int64_t tiles = static_cast<int64_t>(p.tiles_w) * p.tiles_h * p.tiles_n * p.n_tiles;
   const int grid = static_cast<int>(std::min<int64_t>(tiles, NumSMs()));
-  ConvTapsKernel<BN><<<grid, kConvThreads, Cfg::kSmemBytes, s>>>(maps, p);
+  ConvTapsKernel<BN><<<grid, kConvThreads, Cfg::kSmemBytes + p.b_resident, s>>>(maps, p);
   TIPSK_LAUNCH_CHECK();
   return 0;
 }
@@ -673,6 +692,13 @@ int RunTaps(const View* in_views, int n_views, const ConvTap* taps, int n_taps, 
   p.cout = w_rows;
   p.n_tiles = CeilDiv(w_rows, bn);
   for (int i = 0; i < n_taps; ++i) p.tap[i] = taps[i];
+  {
+    const int64_t weights = static_cast<int64_t>(n_taps) * p.cblocks * bn * 128;  // one [bn x 64] block per K step
+    const int base_smem = bn == 64 ? ConvCfg<64>::kSmemBytes : bn == 128 ? ConvCfg<128>::kSmemBytes : ConvCfg<256>::kSmemBytes;
+    static const bool no_resident = getenv("TIPS_CONV_NO_RESIDENT_WEIGHTS") != nullptr;
+    p.b_resident = (!no_resident && p.n_tiles == 1 && m_tiles >= 4 * NumSMs() && base_smem + weights <= kMaxSmemBytes)
+                       ? static_cast<int>(weights) : 0;
+  }
   switch (bn) {
     case 64: return LaunchTaps<64>(maps, p, s);
     case 256: return LaunchTaps<256>(maps, p, s);
@@ -735,7 +761,7 @@ int RunWgrad(const View& dyv, const View* xv, int n_views, const ConvTap* taps, 
   p.a_boxes = cout <= 64 ? 1 : 2;
   const int64_t k_tiles = static_cast<int64_t>(p.tiles_w) * p.tiles_h * p.tiles_n;
   const int base = p.taps * p.cout_tiles * p.cin_tiles;
-  int splits = CeilDiv(2 * NumSMs(), base);
+  int splits = 2 * NumSMs() / base;  // one CTA per SM at a time: at most two full waves, no straggler wave
   if (splits > k_tiles) splits = static_cast<int>(k_tiles);
   if (splits < 1) splits = 1;
   TIPSK_CUDA(cudaMemsetAsync(dw, 0, sizeof(float) * static_cast<size_t>(cout) * ldw, st));

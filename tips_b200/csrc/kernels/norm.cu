@@ -38,7 +38,8 @@ __device__ __forceinline__ void StoreV(T* p, const float (&in)[V]) {
 struct BnGeom {
   int tx, ty;      // block = tx * ty threads; tx vector-columns, ty rows
   int col_tiles;   // grid.x
-  int partials;    // grid.y of the reduction kernels
+  int partials;    // grid.y of the reduction kernels and of the backward apply kernel (3 blocks per SM, 2 waves)
+  int fwd_rows;    // grid.y of the forward apply kernel (4 blocks per SM, 2 waves)
 };
 
 BnGeom BnGeometry(int64_t m, int c, int v) {
@@ -48,12 +49,17 @@ BnGeom BnGeometry(int64_t m, int c, int v) {
   while (g.tx * 2 <= vec_cols && g.tx < 32 && vec_cols % (g.tx * 2) == 0) g.tx *= 2;
   g.ty        = 256 / g.tx;
   g.col_tiles = vec_cols / g.tx;
-  int64_t want = (static_cast<int64_t>(NumSMs()) * 8 + g.col_tiles - 1) / g.col_tiles;
+  // Whole waves: the kernels are grid-stride loops over the rows, and a last partial wave costs a full one.
   int64_t maxp = (m + g.ty * 4 - 1) / (g.ty * 4);
+  int64_t want = (static_cast<int64_t>(NumSMs()) * 6 + g.col_tiles - 1) / g.col_tiles;
   if (want > maxp) want = maxp;
   if (want < 1) want = 1;
   if (want > 1024) want = 1024;
   g.partials = static_cast<int>(want);
+  int64_t fwd = (static_cast<int64_t>(NumSMs()) * 8 + g.col_tiles - 1) / g.col_tiles;
+  if (fwd > maxp) fwd = maxp;
+  if (fwd < 1) fwd = 1;
+  g.fwd_rows = static_cast<int>(fwd);
   return g;
 }
 
@@ -367,7 +373,7 @@ int tipsk_bn_fwd_train(const void* x, const void* residual, void* y, const float
     BnReduceKernel<T, V, false><<<grid, block, smem, s>>>(static_cast<const T*>(x), nullptr, nullptr, nullptr, nullptr,
                                                           workspace, m, c, 0);
     BnFinalizeKernel<<<CeilDiv(2 * c, 32), dim3(32, kFinalizeRows), 0, s>>>(workspace, g.partials, c);
-    BnApplyKernel<T, V><<<grid, block, sizeof(float) * 256 * 2 * V, s>>>(static_cast<const T*>(x), static_cast<const T*>(residual),
+    BnApplyKernel<T, V><<<dim3(g.col_tiles, g.fwd_rows), block, sizeof(float) * 256 * 2 * V, s>>>(static_cast<const T*>(x), static_cast<const T*>(residual),
                                                static_cast<T*>(y), gamma, beta, running_mean, running_var, save_mean,
                                                save_invstd, workspace, g.partials, m, c, eps, momentum, relu, 1);
   });
@@ -387,7 +393,7 @@ int tipsk_bn_fwd_train_stats(const void* x, const void* residual, void* y, const
   BN_DISPATCH(dtype, c, {
     BnGeom g = BnGeometry(m, c, V);
     dim3 block(g.tx, g.ty), grid(g.col_tiles, g.partials);
-    BnApplyKernel<T, V><<<grid, block, sizeof(float) * 256 * 2 * V, s>>>(static_cast<const T*>(x), static_cast<const T*>(residual),
+    BnApplyKernel<T, V><<<dim3(g.col_tiles, g.fwd_rows), block, sizeof(float) * 256 * 2 * V, s>>>(static_cast<const T*>(x), static_cast<const T*>(residual),
                                                static_cast<T*>(y), gamma, beta, running_mean, running_var, save_mean,
                                                save_invstd, stats, 0, m, c, eps, momentum, relu, 1);
   });
@@ -403,7 +409,7 @@ int tipsk_bn_fwd_eval(const void* x, const void* residual, void* y, const float*
   BN_DISPATCH(dtype, c, {
     BnGeom g = BnGeometry(m, c, V);
     dim3 block(g.tx, g.ty), grid(g.col_tiles, g.partials);
-    BnApplyKernel<T, V><<<grid, block, sizeof(float) * 256 * 2 * V, s>>>(static_cast<const T*>(x), static_cast<const T*>(residual),
+    BnApplyKernel<T, V><<<dim3(g.col_tiles, g.fwd_rows), block, sizeof(float) * 256 * 2 * V, s>>>(static_cast<const T*>(x), static_cast<const T*>(residual),
                                                static_cast<T*>(y), gamma, beta, const_cast<float*>(running_mean),
                                                const_cast<float*>(running_var), nullptr, nullptr, nullptr, 0, m, c,
                                                eps, 0.f, relu, 0);
@@ -454,7 +460,7 @@ int tipsk_bn_fwd_train_mask(const void* x, const void* residual, void* y, const 
                                                             workspace, m, c, 0);
       BnFinalizeKernel<<<CeilDiv(2 * c, 32), dim3(32, kFinalizeRows), 0, s>>>(workspace, g.partials, c);
     }
-    BnApplyKernel<T, V><<<grid, block, smem, s>>>(static_cast<const T*>(x), static_cast<const T*>(residual),
+    BnApplyKernel<T, V><<<dim3(g.col_tiles, g.fwd_rows), block, smem, s>>>(static_cast<const T*>(x), static_cast<const T*>(residual),
                                                   static_cast<T*>(y), gamma, beta, running_mean, running_var, save_mean,
                                                   save_invstd, stats ? stats : workspace, stats ? 0 : g.partials, m, c,
                                                   eps, momentum, relu, 1, static_cast<uint8_t*>(relu_mask));

@@ -1,7 +1,7 @@
 """Small single-kernel cases for profiler captures: each runs ONE kernel a handful of times on inputs a
 little larger than L2, holds well under a GB on the device and exits by itself in seconds.
 
-    python -m tips_b200.bench.profile_case {bn_fwd,bn_bwd,gemm,gemm_persistent,ln,sgd,ps_pull,ps_push,conv1x1,conv3x3,conv_dgrad,conv_wgrad}
+    python -m tips_b200.bench.profile_case {bn_fwd,bn_bwd,gemm,gemm_persistent,ln,sgd,ps_pull,ps_push,conv1x1,conv3x3,conv_dgrad,conv_wgrad,adam,ln_bwd,bias_act_bwd,softmax_xent}
 """
 from __future__ import annotations
 
@@ -64,6 +64,35 @@ def main(argv=None):
         for _ in range(reps + 1):
             p.grad = torch.randn_like(p)
             opt.step()
+    elif case == "adam":
+        from tips_b200.ops.optim import FusedAdamW
+        p = torch.nn.Parameter(torch.randn(64 << 20, device=dev).to(torch.bfloat16))
+        opt = FusedAdamW([p], lr=1e-3)
+        for _ in range(reps + 1):
+            p.grad = torch.randn_like(p)
+            opt.step()
+    elif case == "ln_bwd":
+        from tips_b200.ops.norm import LayerNorm
+        x = torch.randn(131072, 1024, device=dev).to(torch.bfloat16).requires_grad_()
+        ln = LayerNorm(1024).to(dev)
+        y = ln(x)
+        dy = torch.randn_like(y)
+        for _ in range(reps):
+            torch.autograd.grad(y, x, dy, retain_graph=True)
+    elif case == "bias_act_bwd":
+        from tips_b200.ops.linear import Linear
+        lin = Linear(1024, 4096, act="gelu").to(dev).to(torch.bfloat16)
+        x = torch.randn(16384, 1024, device=dev).to(torch.bfloat16).requires_grad_()
+        y = lin(x)
+        dy = torch.randn_like(y)
+        for _ in range(reps):
+            torch.autograd.grad(y, x, dy, retain_graph=True)
+    elif case == "softmax_xent":
+        from tips_b200.ops.pointwise import softmax_cross_entropy
+        logits = torch.randn(16384, 30528, device=dev).to(torch.bfloat16).requires_grad_()
+        labels = torch.randint(0, 30522, (16384,), device=dev)
+        for _ in range(reps):
+            softmax_cross_entropy(logits, labels).backward()
     elif case in ("ps_pull", "ps_push"):
         from tips_b200.models.ctr import synthetic_ctr_batch
         from tips_b200.ps.gpu import ShardedEmbedding

@@ -142,7 +142,8 @@ def _channels_last(m, device):
     return m
 
 
-def tiny_resnet(num_classes=10, dtype=torch.bfloat16, device="cuda"):
-    """Same block structure with one block per stage and a quarter of the width; for smoke tests."""
-    m = ResNet50(num_classes, layers=(1, 1, 1, 1), width=16).to(device=device, dtype=dtype)
+def tiny_resnet(num_classes=10, dtype=torch.bfloat16, device="cuda", width=16):
+    """Same block structure with one block per stage; for smoke tests.  With width=64 every convolution has the
+    channel counts of the full model and runs on the tcgen05 kernels; narrower widths use the library fallback."""
+    m = ResNet50(num_classes, layers=(1, 1, 1, 1), width=width).to(device=device, dtype=dtype)
     return _channels_last(m, device)

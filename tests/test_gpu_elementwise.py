@@ -107,7 +107,7 @@ def test_batchnorm_fwd_bwd(dtype, shape, relu, res):
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
-@pytest.mark.parametrize("rows,cols", [(3, 64), (257, 1024), (64, 768)])
+@pytest.mark.parametrize("rows,cols", [(3, 64), (257, 1024), (64, 768), (20000, 1024), (5000, 256)])
 def test_layernorm_fwd_bwd(dtype, rows, cols):
     from tips_b200.ops.norm import LayerNorm
     torch.manual_seed(4)
@@ -198,3 +198,33 @@ def test_maxpool_3x3_s2(n, c, h, w):
     assert torch.allclose(x.grad.float().sum(dim=(2, 3)), xr.grad.sum(dim=(2, 3)), rtol=2e-2, atol=2e-2 + 1e-4 * h * w)
     mismatch = (x.grad.float() - xr.grad).abs() > 1e-2
     assert mismatch.float().mean() < 0.02
+
+
+@pytest.mark.parametrize("b,s,heads,d", [(2, 128, 4, 64), (3, 77, 2, 32)])
+def test_packed_attention_matches_plain_sdpa(b, s, heads, d):
+    from tips_b200.ops.attention import packed_attention
+    torch.manual_seed(b * s)
+    dev = torch.device("cuda", 0)
+    h = heads * d
+    qkv = torch.randn(b, s, 3 * h, device=dev).to(torch.bfloat16).requires_grad_()
+    dy = torch.randn(b, s, h, device=dev).to(torch.bfloat16)
+    y = packed_attention(qkv, heads)
+    y.backward(dy)
+    ref_in = qkv.detach().float().requires_grad_()
+    q, k, v = ref_in.view(b, s, 3, heads, d).permute(2, 0, 3, 1, 4)
+    yr = torch.nn.functional.scaled_dot_product_attention(q, k, v).transpose(1, 2).reshape(b, s, h)
+    yr.backward(dy.float())
+    assert torch.allclose(y.float(), yr, atol=3e-2, rtol=3e-2)
+    assert torch.allclose(qkv.grad.float(), ref_in.grad, atol=5e-2, rtol=5e-2)
+
+
+def test_copy4d_permutes():
+    from tips_b200.ops.attention import copy4d
+    dev = torch.device("cuda", 0)
+    src = torch.randn(3, 5, 7, 64, device=dev).to(torch.bfloat16)
+    dst = torch.empty(3, 7, 5, 64, device=dev, dtype=torch.bfloat16)
+    copy4d(src.transpose(1, 2), dst)
+    assert torch.equal(dst, src.transpose(1, 2).contiguous())
+    packed = torch.zeros(3, 7, 3, 5, 64, device=dev, dtype=torch.bfloat16)
+    copy4d(src.transpose(1, 2), packed[:, :, 1])
+    assert torch.equal(packed[:, :, 1], src.transpose(1, 2)) and float(packed[:, :, 0].abs().sum()) == 0.0

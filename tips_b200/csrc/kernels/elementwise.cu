@@ -251,6 +251,28 @@ __global__ void __launch_bounds__(kThreads) ScaleCastKernel(const S* __restrict_
     dst[i] = FromFloat<D>(ToFloat<S>(src[i]) * scale);
 }
 
+// Strided copy of a 4-D tensor whose innermost rows are contiguous: dst[i0, i1, i2, :] = src[i0, i1, i2, :] with
+// independent element strides for the three outer axes on both sides; rows move as 16-byte vectors.  Used to
+// re-lay attention tensors ([b, heads, s, d] <-> [b, s, 3, heads, d]) in one pass at copy bandwidth.
+struct Copy4dParams {
+  int64_t n0, n1, n2;
+  int row_vecs;  // 16-byte vectors per row
+  int64_t ss[3], ds[3];  // strides in 16-byte vectors
+};
+
+__global__ void __launch_bounds__(256) Copy4dKernel(const uint4* __restrict__ src, uint4* __restrict__ dst, Copy4dParams p) {
+  const int64_t total = p.n0 * p.n1 * p.n2 * p.row_vecs;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int v      = static_cast<int>(i % p.row_vecs);
+    int64_t r        = i / p.row_vecs;
+    const int64_t i2 = r % p.n2; r /= p.n2;
+    const int64_t i1 = r % p.n1;
+    const int64_t i0 = r / p.n1;
+    dst[i0 * p.ds[0] + i1 * p.ds[1] + i2 * p.ds[2] + v] = src[i0 * p.ss[0] + i1 * p.ss[1] + i2 * p.ss[2] + v];
+  }
+}
+
 }  // namespace
 }  // namespace tipsk
 
@@ -363,6 +385,31 @@ int tipsk_scale_cast(const void* src, int src_dtype, void* dst, int dst_dtype, i
       ScaleCastKernel<S, D><<<grid, kThreads, 0, s>>>(static_cast<const S*>(src), static_cast<D*>(dst), n, scale);
     });
   });
+  TIPSK_LAUNCH_CHECK();
+  return 0;
+}
+
+/* dst[i0, i1, i2, 0:row_bytes] = src[i0, i1, i2, 0:row_bytes]; strides in BYTES for the three outer axes; rows,
+ * strides and both base pointers must be multiples of 16 bytes.  The iteration order follows dst (i2 fastest). */
+int tipsk_copy4d(const void* src, void* dst, int64_t n0, int64_t n1, int64_t n2, int64_t row_bytes,
+                 const int64_t* src_strides, const int64_t* dst_strides, void* stream) {
+  if (n0 <= 0 || n1 <= 0 || n2 <= 0 || row_bytes <= 0) return 0;
+  TIPSK_REQUIRE(row_bytes % 16 == 0 && reinterpret_cast<uintptr_t>(src) % 16 == 0 &&
+                    reinterpret_cast<uintptr_t>(dst) % 16 == 0,
+                "copy4d: rows and base pointers must be multiples of 16 bytes");
+  Copy4dParams p;
+  p.n0 = n0; p.n1 = n1; p.n2 = n2;
+  p.row_vecs = static_cast<int>(row_bytes / 16);
+  for (int i = 0; i < 3; ++i) {
+    TIPSK_REQUIRE(src_strides[i] % 16 == 0 && dst_strides[i] % 16 == 0, "copy4d: strides must be multiples of 16 bytes");
+    p.ss[i] = src_strides[i] / 16;
+    p.ds[i] = dst_strides[i] / 16;
+  }
+  const int64_t total = n0 * n1 * n2 * p.row_vecs;
+  int64_t grid = (total + 255) / 256;
+  if (grid > static_cast<int64_t>(NumSMs()) * 16) grid = static_cast<int64_t>(NumSMs()) * 16;
+  Copy4dKernel<<<static_cast<int>(grid), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint4*>(src), static_cast<uint4*>(dst), p);
   TIPSK_LAUNCH_CHECK();
   return 0;
 }

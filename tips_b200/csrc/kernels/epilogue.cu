@@ -17,8 +17,18 @@ __device__ __forceinline__ float Act(float v, int act) {
 }
 __device__ __forceinline__ float ActGrad(float v, int act) {
   if (act == 1) return v > 0.f ? 1.f : 0.f;
-  if (act == 2)
-    return 0.5f * (1.f + erff(v * 0.70710678118654752f)) + v * 0.3989422804014327f * __expf(-0.5f * v * v);
+  if (act == 2) {
+    // d/dv [v * Phi(v)] = Phi(v) + v * phi(v).  Phi through erf(z), z = v / sqrt(2), with the rational approximation
+    // erf(z) = 1 - (a1 t + ... + a5 t^5) exp(-z^2), t = 1 / (1 + p z) (absolute error < 1.5e-7): exp(-z^2) is the
+    // same exponential the density phi(v) needs, so the whole derivative costs one exp and one reciprocal.
+    const float e  = __expf(-0.5f * v * v);
+    const float z  = fabsf(v) * 0.70710678118654752f;
+    const float t  = __frcp_rn(1.f + 0.3275911f * z);
+    const float pl = t * (0.254829592f + t * (-0.284496736f + t * (1.421413741f + t * (-1.453152027f + t * 1.061405429f))));
+    const float erf_abs = 1.f - pl * e;
+    const float phi_cdf = 0.5f * (1.f + copysignf(erf_abs, v));
+    return phi_cdf + v * 0.3989422804014327f * e;
+  }
   return 1.f;
 }
 

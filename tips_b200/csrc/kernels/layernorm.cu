@@ -161,6 +161,72 @@ LnBwdKernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __restri
   }
 }
 
+// Backward with one BLOCK per row: each thread owns 8 consecutive columns (one 16-byte vector), so the per-column
+// dgamma / dbeta accumulators are 16 registers instead of 64 and many more rows are in flight per SM than with a
+// warp per row.  The two row sums go through shared memory (one barrier per row, double-buffered).
+template <typename T>
+__global__ void __launch_bounds__(1024)
+LnBwdBlockRowKernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ gamma,
+                    const float* __restrict__ mean, const float* __restrict__ rstd, T* __restrict__ dx,
+                    float* __restrict__ dgamma_partial, float* __restrict__ dbeta_partial, int64_t rows, int cols) {
+  constexpr int N = 8;
+  __shared__ float red[2][2][32];
+  const int t = threadIdx.x, lane = t & 31, warp = t >> 5, nwarps = blockDim.x >> 5;
+  float gm[N], dg[N], db[N];
+  {
+    const Vec16<T> g = LoadVec(gamma + t * N);
+#pragma unroll
+    for (int i = 0; i < N; ++i) {
+      gm[i] = ToFloat<T>(g.v[i]);
+      dg[i] = db[i] = 0.f;
+    }
+  }
+  const float inv_cols = 1.f / static_cast<float>(cols);
+  int it = 0;
+  for (int64_t r = blockIdx.x; r < rows; r += gridDim.x, ++it) {
+    const float mu = mean[r], rs = rstd[r];
+    const Vec16<T> qx = LoadVec(x + r * cols + t * N), qd = LoadVec(dy + r * cols + t * N);
+    float xh[N], dyg[N];
+    float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int i = 0; i < N; ++i) {
+      xh[i] = (ToFloat<T>(qx.v[i]) - mu) * rs;
+      const float d = ToFloat<T>(qd.v[i]);
+      dyg[i] = d * gm[i];
+      s1 += dyg[i];
+      s2 += dyg[i] * xh[i];
+      dg[i] += d * xh[i];
+      db[i] += d;
+    }
+    s1 = WarpSum(s1);
+    s2 = WarpSum(s2);
+    const int p = it & 1;
+    if (lane == 0) {
+      red[p][0][warp] = s1;
+      red[p][1][warp] = s2;
+    }
+    __syncthreads();
+    s1 = s2 = 0.f;
+    for (int w = 0; w < nwarps; ++w) {
+      s1 += red[p][0][w];
+      s2 += red[p][1][w];
+    }
+    s1 *= inv_cols;
+    s2 *= inv_cols;
+    Vec16<T> o;
+#pragma unroll
+    for (int i = 0; i < N; ++i) o.v[i] = FromFloat<T>(rs * (dyg[i] - s1 - xh[i] * s2));
+    StoreVec(dx + r * cols + t * N, o);
+  }
+  float* pg = dgamma_partial + static_cast<int64_t>(blockIdx.x) * cols + t * N;
+  float* pb = dbeta_partial + static_cast<int64_t>(blockIdx.x) * cols + t * N;
+#pragma unroll
+  for (int i = 0; i < N; ++i) {
+    pg[i] = dg[i];
+    pb[i] = db[i];
+  }
+}
+
 // Column sums of the per-block partial gradients. Block (32, 32): tx = column, ty strides over the partial rows.
 template <typename T>
 __global__ void __launch_bounds__(1024)
@@ -246,6 +312,19 @@ int tipsk_ln_bwd(const void* dy, const void* x, const void* gamma, const float* 
   TIPSK_REQUIRE(cols > 0 && cols % (16 / (int)DTypeSize(dtype)) == 0, "layer norm: cols must be a multiple of 16 bytes");
   TIPSK_REQUIRE(partial_rows == LnGrid(rows), "layer norm backward: wrong number of partial rows");
   cudaStream_t s    = static_cast<cudaStream_t>(stream);
+  if (dtype != kF32 && cols % 256 == 0 && cols / 8 <= 1024) {  // one block of cols/8 threads per row
+    if (dtype == kBF16)
+      LnBwdBlockRowKernel<__nv_bfloat16><<<partial_rows, cols / 8, 0, s>>>(
+          static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(x),
+          static_cast<const __nv_bfloat16*>(gamma), mean, rstd, static_cast<__nv_bfloat16*>(dx), dgamma_partial,
+          dbeta_partial, rows, cols);
+    else
+      LnBwdBlockRowKernel<__half><<<partial_rows, cols / 8, 0, s>>>(
+          static_cast<const __half*>(dy), static_cast<const __half*>(x), static_cast<const __half*>(gamma), mean, rstd,
+          static_cast<__half*>(dx), dgamma_partial, dbeta_partial, rows, cols);
+    TIPSK_LAUNCH_CHECK();
+    return 0;
+  }
   const size_t smem = sizeof(float) * kWarpsPerBlock * 2 * cols;
   TIPSK_REQUIRE(smem <= 48 * 1024, "layer norm backward: row too long for the shared-memory reduction");
   LN_DISPATCH(dtype, cols, {

@@ -34,6 +34,9 @@ int tipsk_pack(const void* const* host_srcs, const int64_t* host_offsets, const 
                int src_dtype, void* flat, int flat_dtype, float scale, int accumulate, void* stream);
 int tipsk_unpack(const void* flat, int flat_dtype, void* const* host_dsts, const int64_t* host_offsets,
                  const int64_t* host_numels, int ntensors, int dst_dtype, float scale, void* stream);
+/* Strided 4-D copy with contiguous rows (byte strides for the three outer axes; everything 16-byte aligned). */
+int tipsk_copy4d(const void* src, void* dst, int64_t n0, int64_t n1, int64_t n2, int64_t row_bytes,
+                 const int64_t* src_strides, const int64_t* dst_strides, void* stream);
 int tipsk_scale_cast(const void* src, int src_dtype, void* dst, int dst_dtype, int64_t n, float scale, void* stream);
 
 /* ---- normalisation (norm.cu) ---- */

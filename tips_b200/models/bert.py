@@ -10,8 +10,8 @@ from __future__ import annotations
 
 import torch
 import torch.nn as nn
-import torch.nn.functional as F
 
+from ..ops.attention import packed_attention
 from ..ops.linear import Linear
 from ..ops.norm import LayerNorm
 from ..ops.pointwise import softmax_cross_entropy
@@ -29,10 +29,7 @@ class BertLayer(nn.Module):
         self.ln2 = LayerNorm(hidden, eps=1e-12)
 
     def forward(self, x):
-        b, s, h = x.shape
-        qkv = self.qkv(x).view(b, s, 3, self.heads, h // self.heads).permute(2, 0, 3, 1, 4)
-        att = F.scaled_dot_product_attention(qkv[0], qkv[1], qkv[2])
-        att = att.transpose(1, 2).reshape(b, s, h)
+        att = packed_attention(self.qkv(x), self.heads)
         x = self.ln1(x + self.proj(att))
         return self.ln2(x + self.fc2(self.fc1(x)))
 

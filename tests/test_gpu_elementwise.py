@@ -228,3 +228,30 @@ def test_copy4d_permutes():
     packed = torch.zeros(3, 7, 3, 5, 64, device=dev, dtype=torch.bfloat16)
     copy4d(src.transpose(1, 2), packed[:, :, 1])
     assert torch.equal(packed[:, :, 1], src.transpose(1, 2)) and float(packed[:, :, 0].abs().sum()) == 0.0
+
+
+def test_bert_layer_matches_plain_pytorch():
+    """One encoder layer (packed attention, residual adds fused into the layer norms, gradients of the block inputs
+    summed inside the GEMMs) against the same computation written with plain PyTorch ops in fp32."""
+    import torch.nn.functional as F
+    from tips_b200.models.bert import BertLayer
+    torch.manual_seed(11)
+    dev = torch.device("cuda", 0)
+    hidden, heads, ffn, b, s = 256, 4, 1024, 4, 128
+    layer = BertLayer(hidden, heads, ffn).to(dev).to(torch.bfloat16)
+    x = (torch.randn(b, s, hidden, device=dev) * 0.5).to(torch.bfloat16).requires_grad_()
+    dy = torch.randn(b, s, hidden, device=dev).to(torch.bfloat16)
+    y = layer(x)
+    y.backward(dy)
+    p = {k: v.detach().float() for k, v in layer.named_parameters()}
+    xr = x.detach().float().requires_grad_()
+    qkv = F.linear(xr, p["qkv.weight"], p["qkv.bias"]).view(b, s, 3, heads, hidden // heads).permute(2, 0, 3, 1, 4)
+    att = F.scaled_dot_product_attention(qkv[0], qkv[1], qkv[2]).transpose(1, 2).reshape(b, s, hidden)
+    h1 = F.layer_norm(xr + F.linear(att, p["proj.weight"], p["proj.bias"]), (hidden,), p["ln1.weight"], p["ln1.bias"], 1e-12)
+    f = F.linear(F.gelu(F.linear(h1, p["fc1.weight"], p["fc1.bias"])), p["fc2.weight"], p["fc2.bias"])
+    yr = F.layer_norm(h1 + f, (hidden,), p["ln2.weight"], p["ln2.bias"], 1e-12)
+    yr.backward(dy.float())
+    assert torch.allclose(y.float(), yr, atol=6e-2, rtol=6e-2)
+    ga, gb = x.grad.float(), xr.grad
+    assert float((ga * gb).sum() / (ga.norm() * gb.norm())) > 0.995
+    assert (ga - gb).abs().max() <= 0.1 * max(1.0, float(gb.abs().max()))

@@ -40,7 +40,23 @@ struct GemmParams {
   int ldc;
   int act;                     // 0 none, 1 relu, 2 gelu
   int tma_store;               // 1: the output goes through shared memory and the TMA store unit
+  int accumulate;              // 1 (TMA store path only): add to what C holds, with a reduce-add store
 };
+
+// Hands a staged 64-column box to the TMA store unit: a plain store, or a bf16 reduce-add into global memory.
+__device__ __forceinline__ void TmaStoreOrAdd2D(const CUtensorMap* tmap, int x, int y, const void* smem_src, int add) {
+  if (add) {
+    asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%1, %2}], [%3];" ::"l"(
+                     reinterpret_cast<uint64_t>(tmap)),
+                 "r"(x), "r"(y), "r"(SmemAddr(smem_src))
+                 : "memory");
+  } else {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];" ::"l"(
+                     reinterpret_cast<uint64_t>(tmap)),
+                 "r"(x), "r"(y), "r"(SmemAddr(smem_src))
+                 : "memory");
+  }
+}
 
 template <int BN>
 struct GemmCfg {
@@ -185,10 +201,7 @@ GemmTnKernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
 #pragma unroll 1
         for (int b = 0; b < BN / 64; ++b) {
           if (n0 + b * 64 < p.n) {
-            asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];" ::"l"(
-                             reinterpret_cast<uint64_t>(&tmap_c)),
-                         "r"(n0 + b * 64), "r"(m0), "r"(SmemAddr(smem + b * (kBM * 128)))
-                         : "memory");
+            TmaStoreOrAdd2D(&tmap_c, n0 + b * 64, m0, smem + b * (kBM * 128), p.accumulate);
           }
         }
         asm volatile("cp.async.bulk.commit_group;" ::: "memory");
@@ -420,10 +433,7 @@ GemmTnPersistentKernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
 #pragma unroll 1
           for (int b = 0; b < BN / 64; ++b) {
             if (n0 + b * 64 < p.n) {
-              asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];" ::"l"(
-                               reinterpret_cast<uint64_t>(&tmap_c)),
-                           "r"(n0 + b * 64), "r"(m0), "r"(SmemAddr(staging + b * (kBM * 128)))
-                           : "memory");
+              TmaStoreOrAdd2D(&tmap_c, n0 + b * 64, m0, staging + b * (kBM * 128), p.accumulate);
             }
           }
           asm volatile("cp.async.bulk.commit_group;" ::: "memory");
@@ -537,7 +547,7 @@ int tipsk_gemm_bf16(const void* a, const void* b, void* c, const void* bias, voi
   p.bias  = static_cast<const __nv_bfloat16*>(bias);
   p.error = GemmErrorWord();
   TIPSK_REQUIRE(p.error != nullptr, "gemm: cannot allocate the error word");
-  p.m = m; p.n = n; p.k = k; p.ldc = ldc; p.act = act;
+  p.m = m; p.n = n; p.k = k; p.ldc = ldc; p.act = act; p.accumulate = 0;
   // The coalesced store path needs 64-column boxes and a 16-byte aligned, 16-byte strided output.
   p.tma_store = (bn >= 64 && pre == nullptr && ldc % 8 == 0 && reinterpret_cast<uintptr_t>(c) % 16 == 0) ? 1 : 0;
   CUtensorMap tc = ta;
@@ -567,9 +577,10 @@ int tipsk_gemm_bf16(const void* a, const void* b, void* c, const void* bias, voi
 }
 
 /* C[m,n] = A[m,k] * B[k,n]: B row-major with the contraction over its rows (no transposed copy is made; the MMA
- * reads it as an MN-major operand).  Serves dx = dy * W of a linear layer with W stored [out, in].  n >= 64. */
+ * reads it as an MN-major operand).  Serves dx = dy * W of a linear layer with W stored [out, in].  n >= 64.
+ * With `accumulate` the product is added (in bf16, by reduce-add stores) to what C already holds. */
 int tipsk_gemm_bf16_nn(const void* a, const void* b, void* c, int m, int n, int k, int lda, int ldb, int ldc,
-                       void* stream) {
+                       int accumulate, void* stream) {
   TIPSK_REQUIRE(m > 0 && n >= 64 && k > 0 && lda % 8 == 0 && ldb % 8 == 0 && ldc % 8 == 0,
                 "gemm_nn: leading dimensions must be multiples of 8 elements and n >= 64");
   TIPSK_REQUIRE(reinterpret_cast<uintptr_t>(c) % 16 == 0, "gemm_nn: output must be 16-byte aligned");
@@ -589,7 +600,7 @@ int tipsk_gemm_bf16_nn(const void* a, const void* b, void* c, int m, int n, int 
   p.bias = nullptr;
   p.error = GemmErrorWord();
   TIPSK_REQUIRE(p.error != nullptr, "gemm: cannot allocate the error word");
-  p.m = m; p.n = n; p.k = k; p.ldc = ldc; p.act = 0; p.tma_store = 1;
+  p.m = m; p.n = n; p.k = k; p.ldc = ldc; p.act = 0; p.tma_store = 1; p.accumulate = accumulate ? 1 : 0;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (bn != 64) {
     const int64_t tiles = static_cast<int64_t>((n + bn - 1) / bn) * ((m + kBM - 1) / kBM);

@@ -77,6 +77,10 @@ int tipsk_bn_bwd_relu_recompute(const void* dy, const void* x, const float* gamm
 /* Layer norm over the last dimension of [rows, cols]. */
 int tipsk_ln_fwd(const void* x, const void* gamma, const void* beta, void* y, float* mean, float* rstd, int64_t rows,
                  int cols, float eps, int dtype, void* stream);
+/* y = LN(x + residual); sum_out receives x + residual (what the backward pass differentiates through). */
+int tipsk_ln_fwd_residual(const void* x, const void* residual, const void* gamma, const void* beta, void* y,
+                          void* sum_out, float* mean, float* rstd, int64_t rows, int cols, float eps, int dtype,
+                          void* stream);
 int tipsk_ln_bwd(const void* dy, const void* x, const void* gamma, const float* mean, const float* rstd, void* dx,
                  float* dgamma_partial, float* dbeta_partial, int partial_rows, int64_t rows, int cols, int dtype,
                  void* stream);
@@ -151,7 +155,7 @@ int tipsk_gemm_bf16(const void* a, const void* b, void* c, const void* bias, voi
                     int ldb, int ldc, int act, void* stream);
 /* C[m,n] = A[m,k] * B[k,n] with B row-major [k, n] (contraction over its rows), n >= 64. */
 int tipsk_gemm_bf16_nn(const void* a, const void* b, void* c, int m, int n, int k, int lda, int ldb, int ldc,
-                       void* stream);
+                       int accumulate, void* stream);
 int tipsk_gemm_status(void);
 
 /* ---- 3x3 / stride 2 / pad 1 max pooling on NHWC (pool.cu); idx holds the argmax position 0..8 per output ---- */

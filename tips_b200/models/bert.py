@@ -29,9 +29,13 @@ class BertLayer(nn.Module):
         self.ln2 = LayerNorm(hidden, eps=1e-12)
 
     def forward(self, x):
-        att = packed_attention(self.qkv(x), self.heads)
-        x = self.ln1(x + self.proj(att))
-        return self.ln2(x + self.fc2(self.fc1(x)))
+        # the residual adds are fused into the layer norms; in backward the gradient of each block input is summed
+        # inside the GEMM that produces its second term (the "passthrough" linears)
+        qkv, x = self.qkv(x, passthrough=True)
+        att = packed_attention(qkv, self.heads)
+        x = self.ln1(self.proj(att), residual=x)
+        h, x = self.fc1(x, passthrough=True)
+        return self.ln2(self.fc2(h), residual=x)
 
 
 class BertMLM(nn.Module):

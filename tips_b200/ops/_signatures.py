@@ -27,6 +27,7 @@ _PROTOS = {
     "tipsk_bn_fwd_eval": (I, [P, P, P, P, P, P, P, L, I, F, I, I, P]),
     "tipsk_bn_bwd": (I, [P, P, P, P, P, P, P, P, P, P, P, L, I, I, I, P]),
     "tipsk_ln_fwd": (I, [P, P, P, P, P, P, L, I, F, I, P]),
+    "tipsk_ln_fwd_residual": (I, [P, P, P, P, P, P, P, P, L, I, F, I, P]),
     "tipsk_ln_bwd": (I, [P, P, P, P, P, P, P, P, I, L, I, I, P]),
     "tipsk_ln_bwd_partials": (I, [L, I]),
     "tipsk_ln_reduce_partials": (I, [P, P, I, I, P, P, I, P]),
@@ -63,7 +64,7 @@ _PROTOS = {
     "tipsk_ps_push": (I, [PP, PP, L, L, L, I, F, I, F, F, P]),
     "tipsk_gemm_bf16": (I, [P, P, P, P, P, I, I, I, I, I, I, I, P]),
     "tipsk_copy4d": (I, [P, P, L, L, L, L, P, P, P]),
-    "tipsk_gemm_bf16_nn": (I, [P, P, P, I, I, I, I, I, I, P]),
+    "tipsk_gemm_bf16_nn": (I, [P, P, P, I, I, I, I, I, I, I, P]),
     "tipsk_gemm_supported": (I, [I, I, I, I, I]),
     "tipsk_gemm_status": (I, []),
     "tipsk_conv2d_supported": (I, [I, I, I, I, I, I]),

@@ -54,16 +54,22 @@ def gemm_tn(a, b, bias=None, act=None, want_pre=False):
     return (c, pre) if want_pre else c
 
 
-def gemm_nn(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
-    """a @ b for bf16 row-major a [M,K] and b [K,N]: b is read in place as an MN-major operand."""
+def gemm_nn(a: torch.Tensor, b: torch.Tensor, into: torch.Tensor | None = None) -> torch.Tensor:
+    """a @ b for bf16 row-major a [M,K] and b [K,N]: b is read in place as an MN-major operand.  With `into`
+    (a contiguous [M,N] bf16 tensor) the product is added to it by the kernel's reduce-add stores."""
     m, k = a.shape
     n = b.shape[1]
     assert b.shape[0] == k
     if not (_supported(a, b) and n >= 64 and n % 8 == 0):
-        return gemm_tn(a, b.t().contiguous())
-    c = torch.empty(m, n, dtype=torch.bfloat16, device=a.device)
+        c = gemm_tn(a, b.t().contiguous())
+        return c if into is None else into.add_(c)
+    if into is not None:
+        assert into.shape == (m, n) and into.is_contiguous() and into.dtype == torch.bfloat16
+        c = into
+    else:
+        c = torch.empty(m, n, dtype=torch.bfloat16, device=a.device)
     base.check(base.K().tipsk_gemm_bf16_nn(a.data_ptr(), b.data_ptr(), c.data_ptr(), m, n, k, a.stride(0), b.stride(0),
-                                           n, base.stream()), "gemm_bf16_nn")
+                                           n, 0 if into is None else 1, base.stream()), "gemm_bf16_nn")
     return c
 
 
@@ -106,47 +112,80 @@ class _LinearFn(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, dy):
-        x2, weight, saved, bias = ctx.saved_tensors
-        n = weight.shape[0]
-        dy2 = dy.reshape(-1, n)
-        if not dy2.is_contiguous():
-            dy2 = dy2.contiguous()
-        dbias = None
-        vec_ok = (n * dy2.element_size()) % 16 == 0  # the fused kernel works on 16-byte column vectors
-        if dy2.is_cuda and vec_ok:
-            dz = dy2
-            db = torch.empty(n, dtype=torch.float32, device=dy2.device) if bias is not None else None
-            if ctx.act != 0 or db is not None:
-                if ctx.act != 0:
-                    dz = torch.empty_like(dy2)
-                # ReLU: the mask of y equals the mask of the pre-activation, so y stands in for it.
-                base.check(base.K().tipsk_bias_act_bwd(dy2.data_ptr(), base.ptr(saved) if ctx.act != 0 else None, None,
-                                                       dz.data_ptr() if ctx.act != 0 else None, base.ptr(db),
-                                                       dy2.shape[0], n, ctx.act, base.code(dy2), base.stream()),
-                           "bias_act_bwd")
-            if db is not None:
-                dbias = db.to(bias.dtype)
+        return _linear_backward(ctx, dy, None)
+
+
+def _linear_backward(ctx, dy, d_alias):
+    """Gradients of the fused linear layer; `d_alias` (optional) is the gradient of another consumer of x, into
+    which dx is accumulated inside the GEMM."""
+    x2, weight, saved, bias = ctx.saved_tensors
+    n = weight.shape[0]
+    dy2 = dy.reshape(-1, n)
+    if not dy2.is_contiguous():
+        dy2 = dy2.contiguous()
+    dbias = None
+    vec_ok = (n * dy2.element_size()) % 16 == 0  # the fused kernel works on 16-byte column vectors
+    if dy2.is_cuda and vec_ok:
+        dz = dy2
+        db = torch.empty(n, dtype=torch.float32, device=dy2.device) if bias is not None else None
+        if ctx.act != 0 or db is not None:
+            if ctx.act != 0:
+                dz = torch.empty_like(dy2)
+            # ReLU: the mask of y equals the mask of the pre-activation, so y stands in for it.
+            base.check(base.K().tipsk_bias_act_bwd(dy2.data_ptr(), base.ptr(saved) if ctx.act != 0 else None, None,
+                                                   dz.data_ptr() if ctx.act != 0 else None, base.ptr(db),
+                                                   dy2.shape[0], n, ctx.act, base.code(dy2), base.stream()),
+                       "bias_act_bwd")
+        if db is not None:
+            dbias = db.to(bias.dtype)
+    else:
+        if ctx.act == 1:
+            dz = dy2 * (saved > 0).to(dy2.dtype)
+        elif ctx.act == 2:
+            s = saved.float()
+            dz = (dy2.float() * (0.5 * (1 + torch.erf(s / math.sqrt(2))) + s * torch.exp(-0.5 * s * s) / math.sqrt(2 * math.pi))).to(dy2.dtype)
         else:
-            if ctx.act == 1:
-                dz = dy2 * (saved > 0).to(dy2.dtype)
-            elif ctx.act == 2:
-                s = saved.float()
-                dz = (dy2.float() * (0.5 * (1 + torch.erf(s / math.sqrt(2))) + s * torch.exp(-0.5 * s * s) / math.sqrt(2 * math.pi))).to(dy2.dtype)
-            else:
-                dz = dy2
-            if bias is not None:
-                dbias = dz.float().sum(0).to(bias.dtype)
-        dx = dw = None
-        if ctx.needs_input_grad[0]:
-            dx = gemm_nn(dz, weight).view(ctx.in_shape)
-        if ctx.needs_input_grad[1]:
-            dw = _weight_grad(dz, x2).to(weight.dtype)
-        return dx, dw, dbias, None
+            dz = dy2
+        if bias is not None:
+            dbias = dz.float().sum(0).to(bias.dtype)
+    dx = dw = None
+    if ctx.needs_input_grad[0]:
+        into = None
+        if d_alias is not None:
+            into = d_alias.reshape(-1, x2.shape[1])
+            if not (into.is_contiguous() and into.dtype == torch.bfloat16 and into.data_ptr() % 16 == 0):
+                into = into.contiguous()
+        dx = gemm_nn(dz, weight, into=into).view(ctx.in_shape)
+    if ctx.needs_input_grad[1]:
+        dw = _weight_grad(dz, x2).to(weight.dtype)
+    return dx, dw, dbias, None
+
+
+class _LinearPassFn(torch.autograd.Function):
+    """linear(x) together with an alias of x for the other consumers of x (a residual connection): the backward pass
+    adds dx into the gradient of that alias inside the GEMM (reduce-add stores) instead of leaving two tensors for
+    autograd to sum.  The alias gradient is modified in place, so it must not be shared with another branch."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias, act):
+        y = _LinearFn.forward(ctx, x, weight, bias, act)
+        return y, x.detach()
+
+    @staticmethod
+    def backward(ctx, dy, d_alias):
+        return _linear_backward(ctx, dy, d_alias)
 
 
 def linear(x, weight, bias=None, act=None):
     """act(x @ weight.T + bias) with the epilogue fused into the GEMM."""
     return _LinearFn.apply(x, weight, bias, act)
+
+
+def linear_passthrough(x, weight, bias=None, act=None):
+    """(linear(x), alias of x): use the alias for the residual branch; see _LinearPassFn."""
+    if x.is_cuda and x.dtype == torch.bfloat16:
+        return _LinearPassFn.apply(x, weight, bias, act)
+    return linear(x, weight, bias, act), x
 
 
 class Linear(nn.Module):
@@ -157,5 +196,7 @@ class Linear(nn.Module):
         self.bias = nn.Parameter(torch.zeros(out_features)) if bias else None
         nn.init.kaiming_uniform_(self.weight, a=math.sqrt(5))
 
-    def forward(self, x):
+    def forward(self, x, passthrough=False):
+        if passthrough:
+            return linear_passthrough(x, self.weight, self.bias, self.act)
         return linear(x, self.weight, self.bias, self.act)

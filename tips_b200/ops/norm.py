@@ -157,7 +157,7 @@ class BatchNorm2d(nn.Module):
 
 class _LayerNormFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, weight, bias, eps):
+    def forward(ctx, x, weight, bias, eps, residual=None):
         cols = x.shape[-1]
         xc = x.contiguous()
         rows = xc.numel() // cols
@@ -166,10 +166,20 @@ class _LayerNormFn(torch.autograd.Function):
         rstd = torch.empty(rows, dtype=torch.float32, device=x.device)
         w = weight.to(xc.dtype)
         b = bias.to(xc.dtype)
-        base.check(base.K().tipsk_ln_fwd(xc.data_ptr(), w.data_ptr(), b.data_ptr(), y.data_ptr(), mean.data_ptr(),
-                                         rstd.data_ptr(), rows, cols, eps, base.code(xc), base.stream()), "ln_fwd")
+        if residual is not None:
+            # LN(x + residual) in one pass; the sum is kept for the backward pass, whose dx goes to both inputs
+            rc = residual.contiguous()
+            summed = torch.empty_like(xc)
+            base.check(base.K().tipsk_ln_fwd_residual(
+                xc.data_ptr(), rc.data_ptr(), w.data_ptr(), b.data_ptr(), y.data_ptr(), summed.data_ptr(),
+                mean.data_ptr(), rstd.data_ptr(), rows, cols, eps, base.code(xc), base.stream()), "ln_fwd_residual")
+            xc = summed
+        else:
+            base.check(base.K().tipsk_ln_fwd(xc.data_ptr(), w.data_ptr(), b.data_ptr(), y.data_ptr(), mean.data_ptr(),
+                                             rstd.data_ptr(), rows, cols, eps, base.code(xc), base.stream()), "ln_fwd")
         ctx.save_for_backward(xc, w, mean, rstd)
         ctx.wdtype = weight.dtype
+        ctx.has_res = residual is not None
         return y
 
     @staticmethod
@@ -190,12 +200,15 @@ class _LayerNormFn(torch.autograd.Function):
         dbeta = torch.empty(cols, dtype=torch.float32, device=x.device)
         base.check(lib.tipsk_ln_reduce_partials(pg.data_ptr(), pb.data_ptr(), parts, cols, dgamma.data_ptr(),
                                                 dbeta.data_ptr(), 0, base.stream()), "ln_reduce")
-        return dx, dgamma.to(ctx.wdtype), dbeta.to(ctx.wdtype), None
+        return dx, dgamma.to(ctx.wdtype), dbeta.to(ctx.wdtype), None, (dx if ctx.has_res else None)
 
 
-def layer_norm(x, weight, bias, eps=1e-5):
+def layer_norm(x, weight, bias, eps=1e-5, residual=None):
+    """LN(x) or, with `residual`, LN(x + residual) with the add fused into the kernel."""
     if x.is_cuda:
-        return _LayerNormFn.apply(x, weight, bias, eps)
+        return _LayerNormFn.apply(x, weight, bias, eps, residual)
+    if residual is not None:
+        x = x + residual
     return F.layer_norm(x.float(), (x.shape[-1],), weight.float(), bias.float(), eps).to(x.dtype)
 
 
@@ -207,5 +220,5 @@ class LayerNorm(nn.Module):
         self.weight = nn.Parameter(torch.ones(self.normalized_shape))
         self.bias = nn.Parameter(torch.zeros(self.normalized_shape))
 
-    def forward(self, x):
-        return layer_norm(x, self.weight, self.bias, self.eps)
+    def forward(self, x, residual=None):
+        return layer_norm(x, self.weight, self.bias, self.eps, residual)

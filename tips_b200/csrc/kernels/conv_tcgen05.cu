@@ -388,22 +388,24 @@ struct WgradMaps {
   CUtensorMap dy;
 };
 
-constexpr int kMnBoxBytes = kBM * 128;  // one 64-channel box of up to 128 pixels
 
-template <int BN>
+// kBoxRows: pixels per K step (rows of a box).  The widest tile (256 input channels) takes 64-pixel steps so that four
+// stages still fit; it moves a third fewer bytes per FLOP through L2 than the 128-channel tile.
+template <int BN, int kBoxRows>
 struct WgradCfg {
-  static constexpr int kStages     = BN >= 128 ? 3 : 4;
-  static constexpr int kABytes     = 2 * kMnBoxBytes;
-  static constexpr int kBBytes     = (BN / 64) * kMnBoxBytes;
+  static constexpr int kBoxBytes   = kBoxRows * 128;
+  static constexpr int kStages     = BN == 128 ? 3 : 4;
+  static constexpr int kABytes     = 2 * kBoxBytes;
+  static constexpr int kBBytes     = (BN / 64) * kBoxBytes;
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kTmemCols   = BN;
   static constexpr int kSmemBytes  = kStages * kStageBytes + 1024 + 256;
 };
 
-template <int BN>
+template <int BN, int kBoxRows>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 ConvWgradKernel(const __grid_constant__ WgradMaps maps, const __grid_constant__ WgradParams p) {
-  using Cfg = WgradCfg<BN>;
+  using Cfg = WgradCfg<BN, kBoxRows>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* full_bar  = reinterpret_cast<uint64_t*>(smem + Cfg::kStages * Cfg::kStageBytes);
@@ -459,10 +461,10 @@ ConvWgradKernel(const __grid_constant__ WgradMaps maps, const __grid_constant__ 
         uint8_t* b_dst = a_dst + Cfg::kABytes;
         MbarExpectTx(&full_bar[s], stage_tx);
         for (int j = 0; j < p.a_boxes; ++j)
-          TmaLoad4D(a_dst + j * kMnBoxBytes, &maps.dy, cout_t * kBM + j * 64, w0, h0, n0, &full_bar[s]);
+          TmaLoad4D(a_dst + j * Cfg::kBoxBytes, &maps.dy, cout_t * kBM + j * 64, w0, h0, n0, &full_bar[s]);
 #pragma unroll
         for (int j = 0; j < BN / 64; ++j)
-          TmaLoad4D(b_dst + j * kMnBoxBytes, &maps.x[tap.map], cin_t * BN + j * 64, w0 + tap.dw, h0 + tap.dh, n0,
+          TmaLoad4D(b_dst + j * Cfg::kBoxBytes, &maps.x[tap.map], cin_t * BN + j * 64, w0 + tap.dw, h0 + tap.dh, n0,
                     &full_bar[s]);
       }
     }
@@ -482,8 +484,8 @@ ConvWgradKernel(const __grid_constant__ WgradMaps maps, const __grid_constant__ 
         }
         TcFenceAfter();
         const uint32_t a_addr = SmemAddr(smem + s * Cfg::kStageBytes);
-        const uint64_t adesc  = SmemDescMnSw128(a_addr, kMnBoxBytes);
-        const uint64_t bdesc  = SmemDescMnSw128(a_addr + Cfg::kABytes, kMnBoxBytes);
+        const uint64_t adesc  = SmemDescMnSw128(a_addr, Cfg::kBoxBytes);
+        const uint64_t bdesc  = SmemDescMnSw128(a_addr + Cfg::kABytes, Cfg::kBoxBytes);
         for (int k = 0; k < ksteps; ++k) {
           // 16 pixels further along K = 16 rows of 128 bytes
           UmmaBf16(tmem_base, adesc + static_cast<uint64_t>(k) * (2048 >> 4), bdesc + static_cast<uint64_t>(k) * (2048 >> 4),
@@ -533,14 +535,14 @@ struct Box {
   int tw, th, tn;
 };
 
-// Box of at most 128 pixels that covers the extents (wo, ho, nb) with the fewest tiles; `mult16` restricts the
+// Box of at most max_px (<= 128) pixels that covers the extents (wo, ho, nb) with the fewest tiles; `mult16` restricts the
 // pixel count to multiples of 16 (one MMA K step) for the weight gradient.
-Box PickBox(int wo, int ho, int nb, bool mult16) {
+Box PickBox(int wo, int ho, int nb, bool mult16, int max_px = 128) {
   Box best{1, 1, 1};
   int64_t best_tiles = INT64_MAX;
-  for (int tw = 1; tw <= std::min(wo, 128); ++tw) {
-    for (int th = 1; th <= std::min(ho, 128 / tw); ++th) {
-      const int tn = std::max(1, std::min(nb, 128 / (tw * th)));
+  for (int tw = 1; tw <= std::min(wo, max_px); ++tw) {
+    for (int th = 1; th <= std::min(ho, max_px / tw); ++th) {
+      const int tn = std::max(1, std::min(nb, max_px / (tw * th)));
       if (mult16 && (tw * th * tn) % 16 != 0) continue;
       const int64_t tiles = static_cast<int64_t>(CeilDiv(wo, tw)) * CeilDiv(ho, th) * CeilDiv(nb, tn);
       if (tiles < best_tiles || (tiles == best_tiles && tw > best.tw)) {
@@ -639,16 +641,17 @@ int LaunchTaps(const ConvMaps& maps, const ConvParams& p, cudaStream_t s) {
   return 0;
 }
 
-template <int BN>
+template <int BN, int kBoxRows>
 int LaunchWgrad(const WgradMaps& maps, const WgradParams& p, int splits, cudaStream_t s) {
-  using Cfg = WgradCfg<BN>;
+  using Cfg = WgradCfg<BN, kBoxRows>;
   static bool configured = false;
   if (!configured) {
-    TIPSK_CUDA(cudaFuncSetAttribute(ConvWgradKernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
+    TIPSK_CUDA(cudaFuncSetAttribute(ConvWgradKernel<BN, kBoxRows>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    Cfg::kSmemBytes));
     configured = true;
   }
   dim3 grid(p.taps * p.cout_tiles * p.cin_tiles, splits);
-  ConvWgradKernel<BN><<<grid, kGemmThreads, Cfg::kSmemBytes, s>>>(maps, p);
+  ConvWgradKernel<BN, kBoxRows><<<grid, kGemmThreads, Cfg::kSmemBytes, s>>>(maps, p);
   TIPSK_LAUNCH_CHECK();
   return 0;
 }
@@ -735,7 +738,9 @@ int RunWgrad(const View& dyv, const View* xv, int n_views, const ConvTap* taps, 
   WgradParams p{};
   p.taps = n_taps;
   for (int i = 0; i < n_taps; ++i) p.tap[i] = taps[i];
-  const Box box = PickBox(static_cast<int>(dyv.w), static_cast<int>(dyv.h), static_cast<int>(dyv.n), true);
+  const int bn  = cin % 256 == 0 ? 256 : cin % 128 == 0 ? 128 : 64;
+  const Box box = PickBox(static_cast<int>(dyv.w), static_cast<int>(dyv.h), static_cast<int>(dyv.n), true,
+                          bn == 256 ? 64 : 128);
   int rc = MapOf(&maps.dy, dyv, box);
   if (rc) return rc;
   for (int b = 0; b < 4; ++b) {
@@ -750,7 +755,6 @@ int RunWgrad(const View& dyv, const View* xv, int n_views, const ConvTap* taps, 
   TIPSK_REQUIRE(p.error != nullptr, "conv: cannot allocate the error word");
   p.dw  = dw;
   p.ldw = ldw;
-  const int bn = cin % 128 == 0 ? 128 : 64;
   p.cout_tiles = CeilDiv(cout, kBM);
   p.cin_tiles  = CeilDiv(cin, bn);
   p.tiles_w = CeilDiv(dyv.w, box.tw);
@@ -765,7 +769,8 @@ int RunWgrad(const View& dyv, const View* xv, int n_views, const ConvTap* taps, 
   if (splits > k_tiles) splits = static_cast<int>(k_tiles);
   if (splits < 1) splits = 1;
   TIPSK_CUDA(cudaMemsetAsync(dw, 0, sizeof(float) * static_cast<size_t>(cout) * ldw, st));
-  return bn == 128 ? LaunchWgrad<128>(maps, p, splits, st) : LaunchWgrad<64>(maps, p, splits, st);
+  if (bn == 256) return LaunchWgrad<256, 64>(maps, p, splits, st);
+  return bn == 128 ? LaunchWgrad<128, 128>(maps, p, splits, st) : LaunchWgrad<64, 128>(maps, p, splits, st);
 }
 
 // Copies a 3-channel NHWC image into the zero-padded 8-channel buffer of the stem convolution.

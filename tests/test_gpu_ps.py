@@ -107,3 +107,42 @@ def test_ctr_trainer_loss_decreases():
     losses = [t.train_step(ids, dense, labels).item() for _ in range(30)]
     t.check()
     assert losses[-1] < losses[0] * 0.8, losses
+
+
+def test_table_dump_reloads_under_another_sharding(tmp_path):
+    """Dump 4 emulated ranks' shards, reload them into a single-rank table: same dense contents and optimizer
+    state; the text dump has the reference's "<key>\\tVec:\\t<e> <e> ... " lines."""
+    from tips_b200.config import set_config
+    from tips_b200.parallel import device
+    from tips_b200.ps.gpu import ShardedEmbedding
+    fields, rows, dim, batch = 2, 1501, 16, 256
+    set_config(symm_window_bytes=1 << 20, device_wait_budget_ms=2000, comm_blocks=8)
+    st = device.setup(emulate_ranks=4)
+    try:
+        dev = st.device
+        t = ShardedEmbedding(fields, rows, dim, optimizer="adagrad", lr=0.05, init_scale=0.1, seed=3,
+                             expected_batch=batch * 4, device=dev)
+        torch.manual_seed(2)
+        ids = [(torch.rand(batch, fields, device=dev) * rows).long().clamp_(0, rows - 1) for _ in range(4)]
+        t.push(ids, [torch.randn(batch, fields * dim, device=dev) for _ in range(4)])
+        t.check()
+        want_w, want_s = _dense_tables(t, fields, rows, dim)
+        paths = t.save(str(tmp_path / "ctr"))
+        assert len(paths) == 4
+        t.save_text(str(tmp_path / "field0.txt"), 0)
+    finally:
+        device.teardown(st)
+    lines = open(tmp_path / "field0.txt").read().splitlines()
+    assert len(lines) == rows
+    key, tag, rest = lines[5].split("\t")
+    assert tag == "Vec:" and len(rest.split()) == dim
+    row = torch.tensor([float(v) for v in rest.split()])
+    assert torch.allclose(row, want_w[0][int(key)].cpu(), rtol=1e-4, atol=1e-6)
+    single = ShardedEmbedding(fields, rows, dim, optimizer="adagrad", lr=0.05, init_scale=0.0, seed=0,
+                              expected_batch=batch, device=torch.device("cuda", 0))
+    assert single.size == 1
+    single.load(str(tmp_path / "ctr"))
+    got_w, got_s = _dense_tables(single, fields, rows, dim)
+    for f in range(fields):
+        assert torch.equal(got_w[f], want_w[f])
+        assert torch.equal(got_s[f], want_s[f])

@@ -186,6 +186,90 @@ class ShardedEmbedding:
     def owner_of(self, ids: torch.Tensor):
         return ids % self.size, ids // self.size
 
+    # ------------------------------------------------------------------ dumps
+    # The reference can only dump a sparse table as text, one line per key ("<key>\tVec:\t<e> <e> ... \n",
+    # tips/core/ps/sparse_table.h:86-93,147-152) and has no loader.  Here every rank writes the shards it owns
+    # in a binary file (header + raw fp32 rows and optimizer state, staged through pinned host memory) that can
+    # be read back under a different number of ranks, and small tables can also be written in that text format.
+
+    def _ranks_here(self):
+        return range(self.size) if self.emulated else [self.rank]
+
+    def save(self, prefix: str) -> list:
+        """Write `<prefix>.rank<r>.bin` for the shard(s) held by this process; returns the paths."""
+        import json
+        import numpy as np
+        torch.cuda.synchronize()
+        paths = []
+        for r in self._ranks_here():
+            path = f"{prefix}.rank{r}.bin"
+            header = {"format": "tips_b200.ps.v1", "rank": r, "world": self.size, "fields": self.num_fields,
+                      "rows": self.rows, "rows_per_shard": self.rows_per_shard, "dim": self.dim,
+                      "state": bool(self.has_state)}
+            with open(path, "wb") as f:
+                hb = json.dumps(header).encode()
+                f.write(np.array([len(hb)], dtype=np.uint64).tobytes())
+                f.write(hb)
+                for state in ([False, True] if self.has_state else [False]):
+                    for fld in range(self.num_fields):
+                        shard = self.local_shard(fld, r, state=state)
+                        for lo in range(0, self.rows_per_shard, 1 << 20):  # at most 1M rows on the host at a time
+                            f.write(shard[lo:lo + (1 << 20)].cpu().numpy().tobytes())
+            paths.append(path)
+        self._sync_ranks()
+        return paths
+
+    def load(self, prefix: str) -> None:
+        """Read every `<prefix>.rank*.bin` written by `save` (by any number of ranks) and keep the rows this
+        process owns under the current sharding: id -> (rank id % N, local row id // N)."""
+        import glob
+        import json
+        import numpy as np
+        files = sorted(glob.glob(f"{prefix}.rank*.bin"))
+        if not files:
+            raise FileNotFoundError(f"no table dump matches {prefix}.rank*.bin")
+        seen_world = None
+        for path in files:
+            with open(path, "rb") as f:
+                hlen = int(np.frombuffer(f.read(8), dtype=np.uint64)[0])
+                h = json.loads(f.read(hlen))
+                if (h["fields"], h["rows"], h["dim"]) != (self.num_fields, self.rows, self.dim):
+                    raise ValueError(f"{path}: table geometry differs from this table")
+                seen_world = h["world"]
+                old_n, old_r, old_rows = h["world"], h["rank"], h["rows_per_shard"]
+                for state in ([False, True] if h["state"] else [False]):
+                    for fld in range(self.num_fields):
+                        for lo in range(0, old_rows, 1 << 20):
+                            cnt = min(1 << 20, old_rows - lo)
+                            buf = np.frombuffer(f.read(cnt * self.dim * 4), dtype=np.float32).reshape(cnt, self.dim)
+                            if state and not self.has_state:
+                                continue
+                            ids = (torch.arange(lo, lo + cnt, dtype=torch.int64) * old_n + old_r)
+                            valid = ids < self.rows
+                            for r in self._ranks_here():
+                                mine = valid & (ids % self.size == r)
+                                if not bool(mine.any()):
+                                    continue
+                                rows = torch.from_numpy(buf.copy())[mine].to(self.device)
+                                dst = self.local_shard(fld, r, state=state)
+                                dst[(ids[mine] // self.size).to(self.device)] = rows
+        if seen_world is None:
+            raise ValueError("empty dump")
+        torch.cuda.synchronize()
+        self._sync_ranks()
+
+    def save_text(self, path: str, field: int) -> None:
+        """The rows of `field` held by this process in the reference's text format (small tables, tests)."""
+        torch.cuda.synchronize()
+        with open(path, "w") as f:
+            for r in self._ranks_here():
+                shard = self.local_shard(field, r).cpu()
+                for lrow in range(self.rows_per_shard):
+                    key = lrow * self.size + r
+                    if key >= self.rows:
+                        break
+                    f.write(f"{key}\tVec:\t" + "".join(f"{float(v):g} " for v in shard[lrow]) + "\n")
+
 
 class _LookupFn(torch.autograd.Function):
     """pull in forward; push (scatter-reduce + server-side optimizer) in backward."""

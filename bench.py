@@ -36,6 +36,8 @@ def parse_args():
     ap.add_argument("--ctr-batch", type=int, default=8192)
     ap.add_argument("--ctr-rows", type=int, default=10_000_000)
     ap.add_argument("--no-graph", action="store_true", help="run the CTR step eagerly instead of as a CUDA graph")
+    ap.add_argument("--ps-async", action="store_true",
+                    help="parameter-server pushes applied as they arrive (no fences); default is the exact synchronous update")
     ap.add_argument("--backend", default=None, help="fused (default) or nccl (library floor)")
     return ap.parse_args()
 
@@ -135,14 +137,16 @@ def main():
         })
     if args.workload in ("all", "ctr") and args.impl != "floor":
         workloads.release_cached_memory()
-        p = workloads.run_ctr(args.ctr_batch, args.ctr_rows, args.steps, max(args.warmup, 4), graph=not args.no_graph)
+        p = workloads.run_ctr(args.ctr_batch, args.ctr_rows, args.steps, max(args.warmup, 4), graph=not args.no_graph,
+                               sync_ps=not args.ps_async)
         launches += p["gpu_launches"]
         ps = {"metric": "ps_ctr_train_samples_per_sec", "value": p["value"], "unit": "samples/s",
               "ms_per_step": p["ms_per_step"], "e2e": p["e2e"],
               "config": {"model": "CTR 26 sparse fields x dim 64 + 13 dense, MLP 512-256-1",
                          "rows_per_table": args.ctr_rows, "per_gpu_batch": args.ctr_batch,
                          "global_batch": args.ctr_batch * size, "ids": "Zipf(1.05)", "optimizer": "Adagrad (tables), "
-                         "Adam (MLP)", "parallelism": f"ps{size}", "cuda_graph": not args.no_graph}}
+                         "Adam (MLP)", "parallelism": f"ps{size}", "cuda_graph": not args.no_graph,
+                         "ps_mode": "async" if args.ps_async else "sync"}}
         if "metric" in result:
             result["ps"] = ps
         else:

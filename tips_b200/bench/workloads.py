@@ -175,7 +175,7 @@ def release_cached_memory():
     torch.cuda.empty_cache()
 
 
-def run_ctr(batch: int, rows: int, steps: int, warmup: int, graph: bool = True):
+def run_ctr(batch: int, rows: int, steps: int, warmup: int, graph: bool = True, sync_ps: bool = True):
     from tips_b200.models.ctr import CtrTrainer, synthetic_ctr_batch
     dev = torch.device("cuda", torch.cuda.current_device())
     release_cached_memory()
@@ -185,7 +185,7 @@ def run_ctr(batch: int, rows: int, steps: int, warmup: int, graph: bool = True):
     if need > free:
         raise MemoryError(f"CTR tables need {need >> 30} GiB on this GPU, {free >> 30} GiB are free")
     trainer = CtrTrainer(num_fields=26, rows_per_table=rows, dim=64, dense_features=13, hidden=(512, 256),
-                         device=dev, expected_batch=batch, graph=graph)
+                         device=dev, expected_batch=batch, graph=graph, sync_ps=sync_ps)
     nhost = 3
     host = [tuple(t.pin_memory() for t in synthetic_ctr_batch(batch, 26, rows, 13, seed=7 * tips.rank() + i))
             for i in range(nhost)]

@@ -207,6 +207,64 @@ PsPushScatterKernel(PsLaunch args, PsMeta meta, int64_t batch, int64_t grad_ld, 
   }
 }
 
+// Asynchronous push: every gradient row is applied straight to the owner's row with atomics, no accumulation table,
+// no fences; concurrent pulls may see a row half-way through an update and duplicate ids are applied one after the
+// other.  This is the reference's own consistency model: its servers apply pushes as they arrive, shard by shard, with
+// no barrier between workers (tips/core/ps/ps_server.h:248-264).  SGD: w += -lr * g (one vector reduction).  Adagrad:
+// G += g^2 with the old value returned, then w += -lr * g / (sqrt(G_new) + eps).
+template <typename GradT>
+__global__ void __launch_bounds__(256)
+PsPushDirectKernel(PsLaunch args, PsMeta meta, int64_t batch, int64_t grad_ld, int64_t grad_col0, float grad_scale,
+                   int rule, float lr, float eps) {
+  const PsRank& pr   = args.r[blockIdx.y];
+  const int n        = pr.nranks;
+  const int dim      = meta.dim;
+  const int vecs     = dim / 4;
+  int lanes_per_item = 1;
+  while (lanes_per_item < vecs && lanes_per_item < 32) lanes_per_item <<= 1;
+  const int items_per_warp = 32 / lanes_per_item;
+  const int lane     = threadIdx.x & 31;
+  const int sub      = lane / lanes_per_item;
+  const int sublane  = lane % lanes_per_item;
+  const int64_t warp_global = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int64_t nwarps      = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
+  const int64_t total       = batch * meta.nfields;
+  const GradT* grads = static_cast<const GradT*>(pr.grads);
+  for (int64_t base = warp_global * items_per_warp; base < total; base += nwarps * items_per_warp) {
+    const int64_t item = base + sub;
+    if (item >= total) continue;
+    const int f      = static_cast<int>(item % meta.nfields);
+    const int64_t b  = item / meta.nfields;
+    const int64_t id = pr.ids[item];
+    const int owner  = static_cast<int>(id % n);
+    const int64_t lrow = id / n;
+    if (id < 0 || lrow >= meta.rows_per_shard[f]) {
+      if (sublane == 0) atomicExch(pr.error, 2);
+      continue;
+    }
+    float* w  = reinterpret_cast<float*>(pr.slab[owner] + meta.field_off[f]) + lrow * dim;
+    float* st = reinterpret_cast<float*>(pr.slab[owner] + meta.state_off[f]) + lrow * dim;
+    const GradT* g = grads + b * grad_ld + grad_col0 + static_cast<int64_t>(f) * dim;
+    for (int v = sublane; v < vecs; v += lanes_per_item) {
+      float d[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float gv = ToFloat<GradT>(g[v * 4 + k]) * grad_scale;
+        if (rule == 1) {
+          const float g2  = gv * gv;
+          const float old = atomicAdd_system(st + v * 4 + k, g2);
+          d[k] = -lr * gv / (sqrtf(old + g2) + eps);
+        } else {
+          d[k] = -lr * gv;
+        }
+      }
+      asm volatile("red.relaxed.sys.global.add.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(w + v * 4), "f"(d[0]), "f"(d[1]),
+                   "f"(d[2]), "f"(d[3])
+                   : "memory");
+    }
+  }
+}
+
 // rule: 0 = SGD (w -= lr*g), 1 = Adagrad (G += g*g; w -= lr*g/(sqrt(G)+eps)),
 //       2 = the reference's literal rule (w = lr*g, sparse_access_method.h:51-56)
 __global__ void __launch_bounds__(256)
@@ -470,6 +528,31 @@ int tipsk_ps_push(const int64_t* const* ids, const void* const* grads, int64_t b
   if (rc) return rc;
   dim3 agrid(PsGrid(static_cast<int64_t>(st.slots), lpi), local);
   PsPushApplyKernel<<<agrid, 256, 0, s>>>(l, st.meta, st.slots, rule, lr, eps, st.touched_dev);
+  TIPSK_LAUNCH_CHECK();
+  return 0;
+}
+
+/* Asynchronous push (see PsPushDirectKernel): no fences, no accumulation table; rule 0 (SGD) or 1 (Adagrad). */
+int tipsk_ps_push_async(const int64_t* const* ids, const void* const* grads, int64_t batch, int64_t grad_ld,
+                        int64_t grad_col0, int grad_dtype, float grad_scale, int rule, float lr, float eps,
+                        void* stream) {
+  PsState& st = g_ps;
+  TIPSK_REQUIRE(st.ready, "ps not configured");
+  TIPSK_REQUIRE(rule == 0 || rule == 1, "ps async push: SGD or Adagrad only");
+  if (batch <= 0) return 0;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  PsLaunch l;
+  int local = MakePsLaunch(&l, ids, grads, nullptr);
+  if (local < 0) return local;
+  const int lpi = LanesPerItem(st.meta.dim);
+  dim3 grid(PsGrid(batch * st.meta.nfields, lpi), local);
+  if (grad_dtype == kF32)
+    PsPushDirectKernel<float><<<grid, 256, 0, s>>>(l, st.meta, batch, grad_ld, grad_col0, grad_scale, rule, lr, eps);
+  else if (grad_dtype == kBF16)
+    PsPushDirectKernel<__nv_bfloat16><<<grid, 256, 0, s>>>(l, st.meta, batch, grad_ld, grad_col0, grad_scale, rule, lr,
+                                                          eps);
+  else
+    return SetError(-2, "ps push: gradients must be fp32 or bf16");
   TIPSK_LAUNCH_CHECK();
   return 0;
 }

@@ -148,6 +148,9 @@ int tipsk_ps_pull(const int64_t* const* host_ids, void* const* host_outs, int64_
                   int64_t out_col0, int out_dtype, int fence, void* stream);
 int tipsk_ps_push(const int64_t* const* host_ids, const void* const* host_grads, int64_t batch, int64_t grad_ld,
                   int64_t grad_col0, int grad_dtype, float grad_scale, int rule, float lr, float eps, void* stream);
+/* Asynchronous push: gradients applied straight to the owner's rows with atomics, no fences (SGD / Adagrad). */
+int tipsk_ps_push_async(const int64_t* const* host_ids, const void* const* host_grads, int64_t batch, int64_t grad_ld,
+                  int64_t grad_col0, int grad_dtype, float grad_scale, int rule, float lr, float eps, void* stream);
 
 /* ---- tcgen05 GEMM (gemm_tcgen05.cu) ---- */
 int tipsk_gemm_supported(int m, int n, int k, int lda, int ldb);

@@ -48,13 +48,19 @@ class ShardedEmbedding:
 
     def __init__(self, num_fields: int, rows_per_table: int, dim: int, optimizer: str = "adagrad", lr: float = 0.01,
                  eps: float = 1e-8, init_scale: float = 0.0, seed: int = 0, slots: Optional[int] = None,
-                 expected_batch: int = 8192, device=None):
+                 expected_batch: int = 8192, device=None, sync: bool = True):
+        """`sync=True`: a push is the exact synchronous update (gradients of all ranks summed per row, then the
+        optimizer applied once), with cross-rank fences around it.  `sync=False`: the reference's consistency model:
+        pushes are applied to the owner's rows as they arrive (atomics, no fences), pulls may read rows mid-update."""
         if optimizer not in _RULES:
             raise ValueError(f"optimizer must be one of {sorted(_RULES)}")
         if dim % 4:
             raise ValueError("dim must be a multiple of 4")
         self.num_fields, self.rows, self.dim = num_fields, rows_per_table, dim
         self.rule, self.lr, self.eps = _RULES[optimizer], lr, eps
+        self.sync = bool(sync)
+        if not self.sync and self.rule not in (0, 1):
+            raise ValueError("asynchronous pushes support the sgd and adagrad rules")
         self.rank, self.size, self.emulated, st = _world()
         self.device = device or (st.device if st is not None else torch.device("cuda", torch.cuda.current_device()))
         n = self.size
@@ -150,7 +156,7 @@ class ShardedEmbedding:
             out = [mk() for _ in range(self.size)] if self.emulated else mk()
         out_arr, out0 = self._per_rank(out)
         base.check(base.K().tipsk_ps_pull(ids_arr, out_arr, b, out0.stride(0), out_col0, base.code(out0),
-                                          int(fence), base.stream()), "ps_pull")
+                                          int(fence and self.sync), base.stream()), "ps_pull")
         return out
 
     def push(self, ids, grads, grad_col0: int = 0, grad_scale: float = 1.0, lr: Optional[float] = None):
@@ -158,9 +164,9 @@ class ShardedEmbedding:
         self._activate()
         ids_arr, ids0 = self._per_rank(ids)
         g_arr, g0 = self._per_rank(grads)
-        base.check(base.K().tipsk_ps_push(ids_arr, g_arr, ids0.shape[0], g0.stride(0), grad_col0, base.code(g0),
-                                          float(grad_scale), self.rule, float(self.lr if lr is None else lr),
-                                          float(self.eps), base.stream()), "ps_push")
+        fn = base.K().tipsk_ps_push if self.sync else base.K().tipsk_ps_push_async
+        base.check(fn(ids_arr, g_arr, ids0.shape[0], g0.stride(0), grad_col0, base.code(g0), float(grad_scale),
+                      self.rule, float(self.lr if lr is None else lr), float(self.eps), base.stream()), "ps_push")
         base.count_launches(1)
 
     def check(self):

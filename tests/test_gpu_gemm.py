@@ -6,7 +6,8 @@ pytestmark = pytest.mark.gpu
 
 
 @pytest.mark.parametrize("m,n,k", [(128, 128, 64), (256, 512, 256), (8192, 512, 1680), (300, 1000, 2048),
-                                   (1000, 16, 256), (512, 1, 256), (130, 72, 40), (4096, 1024, 4096)])
+                                   (1000, 16, 256), (512, 1, 256), (130, 72, 40), (4096, 1024, 4096),
+                                   (16384, 4096, 2048), (9400, 1024, 4096)])  # the last two take 256 x 256 tiles
 @pytest.mark.parametrize("act", [None, "relu", "gelu"])
 def test_gemm_tn(m, n, k, act):
     from tips_b200.ops.linear import gemm_status, gemm_tn
@@ -45,7 +46,7 @@ def test_linear_module_grads():
 
 
 @pytest.mark.parametrize("m,n,k", [(128, 64, 64), (256, 512, 256), (8192, 1728, 512), (300, 1000, 2048),
-                                   (16384, 1024, 4096), (20000, 256, 512)])
+                                   (16384, 1024, 4096), (20000, 256, 512), (16384, 4096, 2048), (9400, 1024, 4096)])
 def test_gemm_nn(m, n, k):
     from tips_b200.ops.linear import gemm_nn, gemm_status
     torch.manual_seed(m + n + k)

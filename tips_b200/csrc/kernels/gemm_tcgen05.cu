@@ -41,7 +41,26 @@ struct GemmParams {
   int act;                     // 0 none, 1 relu, 2 gelu
   int tma_store;               // 1: the output goes through shared memory and the TMA store unit
   int accumulate;              // 1 (TMA store path only): add to what C holds, with a reduce-add store
+  int bias_vec;                // 1: bias is 16-byte aligned, so eight values can be read with one load
 };
+
+// Eight consecutive bias values as floats (zeros without a bias): one 16-byte load when the bias is 16-byte aligned
+// and the eight columns exist, scalar loads at a ragged edge.
+__device__ __forceinline__ void LoadBias8(const GemmParams& p, int col, float (&bv)[8]) {
+#pragma unroll
+  for (int j = 0; j < 8; ++j) bv[j] = 0.f;
+  if (p.bias == nullptr) return;
+  if (p.bias_vec && col + 8 <= p.n) {
+    const uint4 q = *reinterpret_cast<const uint4*>(p.bias + col);
+    const __nv_bfloat16* b = reinterpret_cast<const __nv_bfloat16*>(&q);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) bv[j] = __bfloat162float(b[j]);
+  } else {
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      if (col + j < p.n) bv[j] = __bfloat162float(p.bias[col + j]);
+  }
+}
 
 // Hands a staged 64-column box to the TMA store unit: a plain store, or a bf16 reduce-add into global memory.
 __device__ __forceinline__ void TmaStoreOrAdd2D(const CUtensorMap* tmap, int x, int y, const void* smem_src, int add) {
@@ -181,10 +200,11 @@ GemmTnKernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
         for (int g = 0; g < 4; ++g) {
           alignas(16) __nv_bfloat16 o[8];
 #pragma unroll
+          float bv[8];
+          LoadBias8(p, col0 + g * 8, bv);
+#pragma unroll
           for (int j = 0; j < 8; ++j) {
-            float x = __uint_as_float(acc[g * 8 + j]);
-            const int col = col0 + g * 8 + j;
-            if (p.bias && col < p.n) x += __bfloat162float(p.bias[col]);
+            float x = __uint_as_float(acc[g * 8 + j]) + bv[j];
             if (p.act == 1) x = fmaxf(x, 0.f);
             else if (p.act == 2) x = 0.5f * x * (1.f + erff(x * 0.70710678118654752f));
             o[j] = __float2bfloat16_rn(x);
@@ -409,10 +429,11 @@ GemmTnPersistentKernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
           for (int g = 0; g < 4; ++g) {
             alignas(16) __nv_bfloat16 o[8];
 #pragma unroll
+            float bv[8];
+            LoadBias8(p, col0 + g * 8, bv);
+#pragma unroll
             for (int j = 0; j < 8; ++j) {
-              float x = __uint_as_float(acc[g * 8 + j]);
-              const int col = col0 + g * 8 + j;
-              if (p.bias && col < p.n) x += __bfloat162float(p.bias[col]);
+              float x = __uint_as_float(acc[g * 8 + j]) + bv[j];
               if (p.act == 1) x = fmaxf(x, 0.f);
               else if (p.act == 2) x = 0.5f * x * (1.f + erff(x * 0.70710678118654752f));
               o[j] = __float2bfloat16_rn(x);
@@ -442,6 +463,211 @@ GemmTnPersistentKernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
       }
       asm volatile("bar.sync 1, 128;" ::: "memory");
     }
+  }
+  TcFenceBefore();
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                 "r"(static_cast<uint32_t>(Cfg::kTmemCols))
+                 : "memory");
+  }
+}
+
+// ---------------------------------------------------------------- 256 x 256 tiles
+// A 128 x 256 tile streams 48 KB per K block from L2 for 512 tensor-core clocks of work, and an SM takes 64 bytes per
+// clock from L2: the main loop is load-bound at two thirds of the tensor peak.  Here one CTA owns a 256 x 256 tile: two
+// A blocks share one B block, 64 KB per 1024 clocks of work, so loads and MMAs balance.  The two accumulators fill all
+// 512 TMEM columns, so the epilogue of a tile cannot overlap the MMAs of the next (only its loads); the variant is
+// chosen for long K and grids that fill whole waves.  Persistent, one CTA per SM.
+struct Big256Cfg {
+  static constexpr int kBN         = 256;
+  static constexpr int kStages     = 3;
+  static constexpr int kABytes     = kBM * kBK * 2;          // one 128-row half
+  static constexpr int kBBytes     = kBN * kBK * 2;
+  static constexpr int kStageBytes = 2 * kABytes + kBBytes;  // 64 KB
+  static constexpr int kStagingBytes = 2 * kBM * 128;        // two 64-column boxes, used alternately
+  static constexpr int kTmemCols   = 512;
+  static constexpr int kSmemBytes  = kStages * kStageBytes + kStagingBytes + 1024 + 256;
+};
+
+template <bool kBMn>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+GemmTn256Kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                const __grid_constant__ CUtensorMap tmap_c, GemmParams p) {
+  using Cfg = Big256Cfg;
+  constexpr int BN = Cfg::kBN;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem    = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* staging = smem + Cfg::kStages * Cfg::kStageBytes;
+  uint64_t* full_bar   = reinterpret_cast<uint64_t*>(staging + Cfg::kStagingBytes);
+  uint64_t* empty_bar  = full_bar + Cfg::kStages;
+  uint64_t* tmem_full  = empty_bar + Cfg::kStages;
+  uint64_t* tmem_empty = tmem_full + 1;
+  uint32_t* tmem_slot  = reinterpret_cast<uint32_t*>(tmem_empty + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int num_k   = (p.k + kBK - 1) / kBK;
+  const int tiles_n = (p.n + BN - 1) / BN;
+  const int tiles_m = (p.m + 2 * kBM - 1) / (2 * kBM);
+  const int num_tiles = tiles_m * tiles_n;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < Cfg::kStages; ++s) {
+      MbarInit(&full_bar[s], 1);
+      MbarInit(&empty_bar[s], 1);
+    }
+    MbarInit(tmem_full, 1);
+    MbarInit(tmem_empty, 4);  // one arrival per epilogue warp
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(SmemAddr(tmem_slot)),
+                 "r"(static_cast<uint32_t>(Cfg::kTmemCols))
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  TcFenceBefore();
+  __syncthreads();
+  TcFenceAfter();
+  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
+
+  if (warp == 0) {
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const int m0 = (tile / tiles_n) * 2 * kBM, n0 = (tile % tiles_n) * BN;
+        for (int kt = 0; kt < num_k; ++kt, ++it) {
+          const int s = it % Cfg::kStages;
+          if (!MbarWait(&empty_bar[s], ((it / Cfg::kStages) & 1) ^ 1)) {
+            atomicExch(p.error, 1);
+            ok = false;
+            break;
+          }
+          uint8_t* a_dst = smem + s * Cfg::kStageBytes;
+          uint8_t* b_dst = a_dst + 2 * Cfg::kABytes;
+          MbarExpectTx(&full_bar[s], Cfg::kStageBytes);
+          TmaLoad2D(a_dst, &tmap_a, kt * kBK, m0, &full_bar[s]);
+          TmaLoad2D(a_dst + Cfg::kABytes, &tmap_a, kt * kBK, m0 + kBM, &full_bar[s]);
+          if (kBMn) {
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j) TmaLoad2D(b_dst + j * 8192, &tmap_b, n0 + j * 64, kt * kBK, &full_bar[s]);
+          } else {
+            TmaLoad2D(b_dst, &tmap_b, kt * kBK, n0, &full_bar[s]);
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (kBMn ? (1u << 16) : 0u) |
+                                 (static_cast<uint32_t>(BN >> 3) << 17) | (static_cast<uint32_t>(kBM >> 4) << 24);
+      uint32_t it = 0;
+      int local = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
+        if (!MbarWait(tmem_empty, (local & 1) ^ 1)) {  // the epilogue has drained both accumulators
+          atomicExch(p.error, 4);
+          break;
+        }
+        TcFenceAfter();
+        for (int kt = 0; kt < num_k; ++kt, ++it) {
+          const int s = it % Cfg::kStages;
+          if (!MbarWait(&full_bar[s], (it / Cfg::kStages) & 1)) {
+            atomicExch(p.error, 2);
+            ok = false;
+            break;
+          }
+          TcFenceAfter();
+          const uint32_t a_addr = SmemAddr(smem + s * Cfg::kStageBytes);
+          const uint32_t b_addr = a_addr + 2 * Cfg::kABytes;
+          const uint64_t bdesc  = kBMn ? SmemDescMnSw128(b_addr, 8192) : SmemDescSw128(b_addr);
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            const uint64_t adesc = SmemDescSw128(a_addr + h * Cfg::kABytes);
+#pragma unroll
+            for (int k = 0; k < kBK / 16; ++k)
+              UmmaBf16(tmem_base + static_cast<uint32_t>(h * BN), adesc + 2 * k, bdesc + (kBMn ? 128 : 2) * k, idesc,
+                       (kt > 0 || k > 0) ? 1u : 0u);
+          }
+          UmmaCommit(&empty_bar[s]);
+        }
+        if (ok) UmmaCommit(tmem_full);
+      }
+    }
+  } else {
+    const int q = warp & 3;
+    const int r = q * 32 + lane;
+    constexpr int kBoxes = BN / 64;
+    int local = 0;
+    uint32_t boxes_done = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++local) {
+      const int m0 = (tile / tiles_n) * 2 * kBM, n0 = (tile % tiles_n) * BN;
+      if (ok && !MbarWait(tmem_full, local & 1)) {
+        if (lane == 0) atomicExch(p.error, 3);
+        ok = false;
+      }
+      TcFenceAfter();
+#pragma unroll 1
+      for (int h = 0; h < 2; ++h) {
+        const uint32_t tsrc = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(h * BN);
+        uint32_t acc[2][32];
+        if (ok) TmemLoad32Async(tsrc, acc[0]);
+#pragma unroll
+        for (int b = 0; b < kBoxes; ++b, ++boxes_done) {
+          uint8_t* box = staging + (boxes_done & 1) * (kBM * 128);
+          // the store that read this staging box two boxes ago must have finished reading it
+          if (warp == 2 && lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+          NamedBarSync(1, 128);
+#pragma unroll
+          for (int half = 0; half < 2; ++half) {
+            const int c = 2 * b + half;
+            if (ok) {
+              // the 32 bias values of this chunk as four 16-byte loads, in flight while the TMEM load completes
+              // (N is a multiple of 256 here, so the chunk is never ragged)
+              const int col0 = n0 + c * 32;
+              uint4 bq[4] = {};
+              if (p.bias) {
+#pragma unroll
+                for (int g = 0; g < 4; ++g) bq[g] = *reinterpret_cast<const uint4*>(p.bias + col0 + g * 8);
+              }
+              TmemLoadWait(acc[c & 1]);
+              if (c + 1 < BN / 32) TmemLoad32Async(tsrc + static_cast<uint32_t>((c + 1) * 32), acc[(c + 1) & 1]);
+#pragma unroll
+              for (int g = 0; g < 4; ++g) {
+                alignas(16) __nv_bfloat16 o[8];
+                const __nv_bfloat16* bb = reinterpret_cast<const __nv_bfloat16*>(&bq[g]);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                  float x = __uint_as_float(acc[c & 1][g * 8 + j]);
+                  if (p.bias) x += __bfloat162float(bb[j]);
+                  if (p.act == 1) x = fmaxf(x, 0.f);
+                  else if (p.act == 2) x = 0.5f * x * (1.f + erff(x * 0.70710678118654752f));
+                  o[j] = __float2bfloat16_rn(x);
+                }
+                const int chunk = half * 4 + g;
+                *reinterpret_cast<uint4*>(box + r * 128 + ((chunk ^ (r & 7)) << 4)) = *reinterpret_cast<uint4*>(o);
+              }
+            }
+          }
+          if (h == 1 && b == kBoxes - 1 && ok) {  // both accumulators are drained
+            TcFenceBefore();
+            __syncwarp();
+            if (lane == 0) MbarArrive(tmem_empty);
+          }
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          NamedBarSync(1, 128);
+          if (warp == 2 && lane == 0) {
+            if (ok && n0 + b * 64 < p.n && m0 + h * kBM < p.m)
+              TmaStoreOrAdd2D(&tmap_c, n0 + b * 64, m0 + h * kBM, box, p.accumulate);
+            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+          }
+        }
+      }
+    }
+    if (warp == 2 && lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
   }
   TcFenceBefore();
   __syncthreads();
@@ -514,6 +740,34 @@ int LaunchGemmPersistent(const CUtensorMap& ta, const CUtensorMap& tb, const CUt
   return 0;
 }
 
+template <bool kBMn>
+int LaunchGemm256(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const GemmParams& p,
+                  cudaStream_t s) {
+  using Cfg = Big256Cfg;
+  static bool configured = false;
+  if (!configured) {
+    TIPSK_CUDA(cudaFuncSetAttribute(GemmTn256Kernel<kBMn>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
+    configured = true;
+  }
+  const int tiles = ((p.n + 255) / 256) * ((p.m + 255) / 256);
+  const int grid  = tiles < NumSMs() ? tiles : NumSMs();
+  GemmTn256Kernel<kBMn><<<grid, kGemmThreads, Cfg::kSmemBytes, s>>>(ta, tb, tc, p);
+  TIPSK_LAUNCH_CHECK();
+  return 0;
+}
+
+// Whether the 256 x 256 tile variant should take the problem: long enough K for the exposed epilogue to be a small
+// share of a tile, and a tile count that fills its waves.
+bool Prefer256(int m, int n, int k) {
+  static const bool off = getenv("TIPS_GEMM_NO_BM256") != nullptr;
+  if (off || n % 256 != 0 || m < 512 || k < 2048) return false;  // measured: no gain at K = 1024, +17..19 % at K = 4096
+  const int64_t tiles = static_cast<int64_t>((m + 255) / 256) * (n / 256);
+  const int64_t sms   = NumSMs();
+  const int64_t waves = (tiles + sms - 1) / sms;
+  const double fill   = static_cast<double>(tiles) / static_cast<double>(waves * sms);
+  return fill >= 0.80;
+}
+
 }  // namespace
 }  // namespace tipsk
 
@@ -548,6 +802,7 @@ int tipsk_gemm_bf16(const void* a, const void* b, void* c, const void* bias, voi
   p.error = GemmErrorWord();
   TIPSK_REQUIRE(p.error != nullptr, "gemm: cannot allocate the error word");
   p.m = m; p.n = n; p.k = k; p.ldc = ldc; p.act = act; p.accumulate = 0;
+  p.bias_vec = (bias != nullptr && reinterpret_cast<uintptr_t>(bias) % 16 == 0) ? 1 : 0;
   // The coalesced store path needs 64-column boxes and a 16-byte aligned, 16-byte strided output.
   p.tma_store = (bn >= 64 && pre == nullptr && ldc % 8 == 0 && reinterpret_cast<uintptr_t>(c) % 16 == 0) ? 1 : 0;
   CUtensorMap tc = ta;
@@ -556,6 +811,8 @@ int tipsk_gemm_bf16(const void* a, const void* b, void* c, const void* bias, voi
     if (rc) return rc;
   }
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (p.tma_store && bn == 256 && Prefer256(m, n, k) && reinterpret_cast<uintptr_t>(bias) % 16 == 0)
+    return LaunchGemm256<false>(ta, tb, tc, p, s);
   // More tiles than SMs and a TMA-storable output: the persistent kernel overlaps epilogue and main loop.
   static const bool no_persist = getenv("TIPS_GEMM_NO_PERSISTENT") != nullptr;
   if (!no_persist && p.tma_store && (bn == 128 || bn == 256)) {
@@ -601,7 +858,9 @@ int tipsk_gemm_bf16_nn(const void* a, const void* b, void* c, int m, int n, int 
   p.error = GemmErrorWord();
   TIPSK_REQUIRE(p.error != nullptr, "gemm: cannot allocate the error word");
   p.m = m; p.n = n; p.k = k; p.ldc = ldc; p.act = 0; p.tma_store = 1; p.accumulate = accumulate ? 1 : 0;
+  p.bias_vec = 0;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (bn == 256 && Prefer256(m, n, k)) return LaunchGemm256<true>(ta, tb, tc, p, s);
   if (bn != 64) {
     const int64_t tiles = static_cast<int64_t>((n + bn - 1) / bn) * ((m + kBM - 1) / kBM);
     if (tiles >= 3 * NumSMs() && k <= 2048) {

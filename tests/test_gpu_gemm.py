@@ -57,3 +57,17 @@ def test_gemm_nn(m, n, k):
     assert gemm_status() == 0
     ref = a.float() @ b.float()
     assert (y.float() - ref).abs().max() <= 1e-2 * max(1.0, float(ref.abs().max()))
+
+
+@pytest.mark.parametrize("m,n,k", [(32768, 2048, 1024), (4096, 512, 256), (1000, 64, 128)])
+def test_linear_weight_grad(m, n, k):
+    """dW = dz^T x on the split-K MN-major kernel; the first shape takes its 256 x 256 tile."""
+    from tips_b200.ops.linear import _weight_grad, gemm_status
+    torch.manual_seed(m)
+    dev = torch.device("cuda", 0)
+    dz = (torch.randn(m, n, device=dev) * 0.25).to(torch.bfloat16)
+    x = (torch.randn(m, k, device=dev) * 0.25).to(torch.bfloat16)
+    dw = _weight_grad(dz, x)
+    assert gemm_status() == 0
+    ref = dz.float().t() @ x.float()
+    assert (dw.float() - ref).abs().max() <= 1e-2 * max(1.0, float(ref.abs().max()))

@@ -391,21 +391,23 @@ struct WgradMaps {
 
 // kBoxRows: pixels per K step (rows of a box).  The widest tile (256 input channels) takes 64-pixel steps so that four
 // stages still fit; it moves a third fewer bytes per FLOP through L2 than the 128-channel tile.
-template <int BN, int kBoxRows>
+// kMH: output-channel halves of 128 per CTA.  With two (256 x 256 tile, both accumulators filling TMEM) a K step moves
+// 64 KB for 1024 tensor-core clocks, which the 64 B/clk/SM L2 path can just sustain; the 128-row tiles are load-bound.
+template <int BN, int kBoxRows, int kMH = 1>
 struct WgradCfg {
   static constexpr int kBoxBytes   = kBoxRows * 128;
-  static constexpr int kStages     = BN == 128 ? 3 : 4;
-  static constexpr int kABytes     = 2 * kBoxBytes;
+  static constexpr int kStages     = (BN == 128 || kMH == 2) ? 3 : 4;
+  static constexpr int kABytes     = 2 * kMH * kBoxBytes;
   static constexpr int kBBytes     = (BN / 64) * kBoxBytes;
   static constexpr int kStageBytes = kABytes + kBBytes;
-  static constexpr int kTmemCols   = BN;
+  static constexpr int kTmemCols   = BN * kMH;
   static constexpr int kSmemBytes  = kStages * kStageBytes + 1024 + 256;
 };
 
-template <int BN, int kBoxRows>
+template <int BN, int kBoxRows, int kMH = 1>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 ConvWgradKernel(const __grid_constant__ WgradMaps maps, const __grid_constant__ WgradParams p) {
-  using Cfg = WgradCfg<BN, kBoxRows>;
+  using Cfg = WgradCfg<BN, kBoxRows, kMH>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* full_bar  = reinterpret_cast<uint64_t*>(smem + Cfg::kStages * Cfg::kStageBytes);
@@ -461,7 +463,7 @@ ConvWgradKernel(const __grid_constant__ WgradMaps maps, const __grid_constant__ 
         uint8_t* b_dst = a_dst + Cfg::kABytes;
         MbarExpectTx(&full_bar[s], stage_tx);
         for (int j = 0; j < p.a_boxes; ++j)
-          TmaLoad4D(a_dst + j * Cfg::kBoxBytes, &maps.dy, cout_t * kBM + j * 64, w0, h0, n0, &full_bar[s]);
+          TmaLoad4D(a_dst + j * Cfg::kBoxBytes, &maps.dy, cout_t * kBM * kMH + j * 64, w0, h0, n0, &full_bar[s]);
 #pragma unroll
         for (int j = 0; j < BN / 64; ++j)
           TmaLoad4D(b_dst + j * Cfg::kBoxBytes, &maps.x[tap.map], cin_t * BN + j * 64, w0 + tap.dw, h0 + tap.dh, n0,
@@ -484,12 +486,15 @@ ConvWgradKernel(const __grid_constant__ WgradMaps maps, const __grid_constant__ 
         }
         TcFenceAfter();
         const uint32_t a_addr = SmemAddr(smem + s * Cfg::kStageBytes);
-        const uint64_t adesc  = SmemDescMnSw128(a_addr, Cfg::kBoxBytes);
         const uint64_t bdesc  = SmemDescMnSw128(a_addr + Cfg::kABytes, Cfg::kBoxBytes);
-        for (int k = 0; k < ksteps; ++k) {
-          // 16 pixels further along K = 16 rows of 128 bytes
-          UmmaBf16(tmem_base, adesc + static_cast<uint64_t>(k) * (2048 >> 4), bdesc + static_cast<uint64_t>(k) * (2048 >> 4),
-                   idesc, (kt > 0 || k > 0) ? 1u : 0u);
+#pragma unroll
+        for (int h = 0; h < kMH; ++h) {
+          const uint64_t adesc = SmemDescMnSw128(a_addr + h * 2 * Cfg::kBoxBytes, Cfg::kBoxBytes);
+          for (int k = 0; k < ksteps; ++k) {
+            // 16 pixels further along K = 16 rows of 128 bytes
+            UmmaBf16(tmem_base + static_cast<uint32_t>(h * BN), adesc + static_cast<uint64_t>(k) * (2048 >> 4),
+                     bdesc + static_cast<uint64_t>(k) * (2048 >> 4), idesc, (kt > 0 || k > 0) ? 1u : 0u);
+          }
         }
         UmmaCommit(&empty_bar[s]);
       }
@@ -500,13 +505,13 @@ ConvWgradKernel(const __grid_constant__ WgradMaps maps, const __grid_constant__ 
     const bool ok = MbarWait(tmem_full, 0);
     if (!ok && lane == 0) atomicExch(p.error, 3);
     TcFenceAfter();
-    const int row = cout_t * kBM + q * 32 + lane;
     if (ok && num_k > 0) {
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
+      for (int c = 0; c < kMH * (BN / 32); ++c) {
         uint32_t acc[32];
         TmemLoad32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(c * 32), acc);
-        const int col0 = cin_t * BN + c * 32;
+        const int row  = (cout_t * kMH + c / (BN / 32)) * kBM + q * 32 + lane;  // accumulator c / (BN/32) = its half
+        const int col0 = cin_t * BN + (c % (BN / 32)) * 32;
         if (row < p.cout && col0 < p.cin) {
           float* dst = p.dw + static_cast<int64_t>(row) * p.ldw + tap.kofs + col0;
 #pragma unroll
@@ -641,17 +646,17 @@ int LaunchTaps(const ConvMaps& maps, const ConvParams& p, cudaStream_t s) {
   return 0;
 }
 
-template <int BN, int kBoxRows>
+template <int BN, int kBoxRows, int kMH = 1>
 int LaunchWgrad(const WgradMaps& maps, const WgradParams& p, int splits, cudaStream_t s) {
-  using Cfg = WgradCfg<BN, kBoxRows>;
+  using Cfg = WgradCfg<BN, kBoxRows, kMH>;
   static bool configured = false;
   if (!configured) {
-    TIPSK_CUDA(cudaFuncSetAttribute(ConvWgradKernel<BN, kBoxRows>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    TIPSK_CUDA(cudaFuncSetAttribute(ConvWgradKernel<BN, kBoxRows, kMH>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                     Cfg::kSmemBytes));
     configured = true;
   }
   dim3 grid(p.taps * p.cout_tiles * p.cin_tiles, splits);
-  ConvWgradKernel<BN, kBoxRows><<<grid, kGemmThreads, Cfg::kSmemBytes, s>>>(maps, p);
+  ConvWgradKernel<BN, kBoxRows, kMH><<<grid, kGemmThreads, Cfg::kSmemBytes, s>>>(maps, p);
   TIPSK_LAUNCH_CHECK();
   return 0;
 }
@@ -755,20 +760,32 @@ int RunWgrad(const View& dyv, const View* xv, int n_views, const ConvTap* taps, 
   TIPSK_REQUIRE(p.error != nullptr, "conv: cannot allocate the error word");
   p.dw  = dw;
   p.ldw = ldw;
-  p.cout_tiles = CeilDiv(cout, kBM);
+  // The 256 x 256 tile pays when each CTA still runs a long K loop after the pixel range is split over two waves
+  // (measured: it wins on the linear layers' 16k-row contractions, it loses on the short pixel ranges of the
+  // 14x14 and 7x7 convolutions, where it leaves too few CTAs).
+  static const bool no_big = getenv("TIPS_WGRAD_NO_BM256") != nullptr;
+  int mh = 1;
+  if (!no_big && bn == 256 && cout % 256 == 0) {
+    const int64_t kt    = static_cast<int64_t>(CeilDiv(dyv.w, box.tw)) * CeilDiv(dyv.h, box.th) * CeilDiv(dyv.n, box.tn);
+    const int64_t base2 = static_cast<int64_t>(n_taps) * (cout / 256) * (cin / 256);
+    const int64_t sp2   = std::max<int64_t>(1, 2 * NumSMs() / base2);
+    if (kt / sp2 >= 32) mh = 2;
+  }
+  p.cout_tiles = CeilDiv(cout, kBM * mh);
   p.cin_tiles  = CeilDiv(cin, bn);
   p.tiles_w = CeilDiv(dyv.w, box.tw);
   p.tiles_h = CeilDiv(dyv.h, box.th);
   p.tiles_n = CeilDiv(dyv.n, box.tn);
   p.tw = box.tw; p.th = box.th; p.tn = box.tn;
   p.cout = cout; p.cin = cin;
-  p.a_boxes = cout <= 64 ? 1 : 2;
+  p.a_boxes = mh == 2 ? 4 : (cout <= 64 ? 1 : 2);
   const int64_t k_tiles = static_cast<int64_t>(p.tiles_w) * p.tiles_h * p.tiles_n;
   const int base = p.taps * p.cout_tiles * p.cin_tiles;
   int splits = 2 * NumSMs() / base;  // one CTA per SM at a time: at most two full waves, no straggler wave
   if (splits > k_tiles) splits = static_cast<int>(k_tiles);
   if (splits < 1) splits = 1;
   TIPSK_CUDA(cudaMemsetAsync(dw, 0, sizeof(float) * static_cast<size_t>(cout) * ldw, st));
+  if (bn == 256 && mh == 2) return LaunchWgrad<256, 64, 2>(maps, p, splits, st);
   if (bn == 256) return LaunchWgrad<256, 64>(maps, p, splits, st);
   return bn == 128 ? LaunchWgrad<128, 128>(maps, p, splits, st) : LaunchWgrad<64, 128>(maps, p, splits, st);
 }

@@ -8,6 +8,11 @@ if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
 
+# Small broadcast chunks, so that the chunk-pipelined path of the broadcast kernel runs on test-sized messages
+# (inherited by the multi-GPU worker processes as well).
+os.environ.setdefault("TIPS_BCAST_CHUNK_BYTES", "32768")
+
+
 def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (run with -m gpu on a B200)")
 

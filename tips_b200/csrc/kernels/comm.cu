@@ -341,56 +341,90 @@ AllgathervKernel(CommLaunch args, int channel, GatherSizes sizes) {
   SaveEpoch(ctx, channel, block, epoch + 1);
 }
 
-// Broadcast: the root writes its data into every rank's window (one multimem
-// store per vector, or one P2P store per peer), then everyone copies from its
-// own window to its output.
+// Broadcast: the root writes its data into every rank's window (one multimem store per vector, or one P2P store per
+// peer), then everyone copies from its own window to its output.  The message can be cut into chunks with a barrier
+// after each, so that the other ranks copy chunk c out of their windows while the root stores chunk c+1 (off by
+// default, see tipsk_broadcast).
 template <bool kMultimem>
 __global__ void __launch_bounds__(kCommThreads)
-BroadcastKernel(CommLaunch args, int channel, uint64_t nbytes, int root) {
+BroadcastKernel(CommLaunch args, int channel, uint64_t nbytes, int root, int nchunks) {
   const RankArgs& ra = args.r[blockIdx.y];
   const CommCtx& ctx = ra.ctx;
   const int n        = ctx.nranks;
   const int block    = blockIdx.x;
+  const int grid     = gridDim.x;
   char* my_win       = ctx.peer[ctx.rank] + ra.win_off;
   uint32_t epoch     = NextEpoch(ctx, channel, block);
   const uint64_t nvec   = (nbytes + 15) / 16;
   const uint64_t ntiles = (nvec + kCopyTile - 1) / kCopyTile;
+  const bool src_aligned = ctx.rank == root && (reinterpret_cast<uintptr_t>(ra.src) & 15) == 0;
+  const bool dst_aligned = ra.dst != nullptr && (reinterpret_cast<uintptr_t>(ra.dst) & 15) == 0;
   // Peers must be done with the previous contents of their windows before the root overwrites them.
   bool ok = BlockBarrier(ctx, channel, block, epoch, 1);
-  if (ok && ctx.rank == root) {
-    const bool src_aligned = (reinterpret_cast<uintptr_t>(ra.src) & 15) == 0;
-    for (uint64_t t = block; t < ntiles; t += gridDim.x) {
-      const uint64_t lo = t * kCopyTile;
-      const uint64_t hi = lo + kCopyTile < nvec ? lo + kCopyTile : nvec;
-      for (uint64_t v0 = lo + threadIdx.x; v0 < hi; v0 += static_cast<uint64_t>(blockDim.x) * kCopyUnroll) {
-        U4 q[kCopyUnroll];
+  for (int c = 0; c < nchunks; ++c) {
+    const uint64_t t_lo = ntiles * c / nchunks, t_hi = ntiles * (c + 1) / nchunks;
+    // first tile of this chunk that belongs to this block (tile t belongs to block t % grid)
+    const uint64_t first = t_lo + (static_cast<uint64_t>(block) + grid - t_lo % grid) % grid;
+    if (ok && ctx.rank == root) {
+      for (uint64_t t = first; t < t_hi; t += grid) {
+        const uint64_t lo = t * kCopyTile;
+        const uint64_t hi = lo + kCopyTile < nvec ? lo + kCopyTile : nvec;
+        for (uint64_t v0 = lo + threadIdx.x; v0 < hi; v0 += static_cast<uint64_t>(blockDim.x) * kCopyUnroll) {
+          U4 q[kCopyUnroll];
 #pragma unroll
-        for (int u = 0; u < kCopyUnroll; ++u) {
-          const uint64_t v = v0 + static_cast<uint64_t>(u) * blockDim.x;
-          if (v >= hi) continue;
-          if (src_aligned && v * 16 + 16 <= nbytes) {
-            q[u] = *reinterpret_cast<const U4*>(ra.src + v * 16);
-          } else {
-            char* qb = reinterpret_cast<char*>(&q[u]);
-            for (uint64_t b = 0; b < 16; ++b) qb[b] = v * 16 + b < nbytes ? ra.src[v * 16 + b] : 0;
+          for (int u = 0; u < kCopyUnroll; ++u) {
+            const uint64_t v = v0 + static_cast<uint64_t>(u) * blockDim.x;
+            if (v >= hi) continue;
+            if (src_aligned && v * 16 + 16 <= nbytes) {
+              q[u] = *reinterpret_cast<const U4*>(ra.src + v * 16);
+            } else {
+              char* qb = reinterpret_cast<char*>(&q[u]);
+              for (uint64_t b = 0; b < 16; ++b) qb[b] = v * 16 + b < nbytes ? ra.src[v * 16 + b] : 0;
+            }
+          }
+#pragma unroll
+          for (int u = 0; u < kCopyUnroll; ++u) {
+            const uint64_t v = v0 + static_cast<uint64_t>(u) * blockDim.x;
+            if (v >= hi) continue;
+            if (kMultimem) {
+              MultimemSt(ctx.mc + ra.win_off + v * 16, q[u]);
+            } else {
+              for (int r = 0; r < n; ++r) StSys(ctx.peer[r] + ra.win_off + v * 16, q[u]);
+            }
           }
         }
+      }
+    }
+    ok = BlockBarrier(ctx, channel, block, epoch + 1 + c, 2) && ok;
+    // copy this chunk out of the own window; the root does it after its last store, so that it never delays a chunk
+    if (ok && ra.dst && (ctx.rank != root || c == nchunks - 1)) {
+      const uint64_t c_first = ctx.rank != root ? first : static_cast<uint64_t>(block);  // the root: all its tiles
+      for (uint64_t t = c_first; t < t_hi; t += grid) {
+        const uint64_t lo = t * kCopyTile;
+        const uint64_t hi = lo + kCopyTile < nvec ? lo + kCopyTile : nvec;
+        for (uint64_t v0 = lo + threadIdx.x; v0 < hi; v0 += static_cast<uint64_t>(blockDim.x) * kCopyUnroll) {
+          U4 q[kCopyUnroll];
 #pragma unroll
-        for (int u = 0; u < kCopyUnroll; ++u) {
-          const uint64_t v = v0 + static_cast<uint64_t>(u) * blockDim.x;
-          if (v >= hi) continue;
-          if (kMultimem) {
-            MultimemSt(ctx.mc + ra.win_off + v * 16, q[u]);
-          } else {
-            for (int r = 0; r < n; ++r) StSys(ctx.peer[r] + ra.win_off + v * 16, q[u]);
+          for (int u = 0; u < kCopyUnroll; ++u) {
+            const uint64_t v = v0 + static_cast<uint64_t>(u) * blockDim.x;
+            if (v < hi) q[u] = *reinterpret_cast<const U4*>(my_win + v * 16);
+          }
+#pragma unroll
+          for (int u = 0; u < kCopyUnroll; ++u) {
+            const uint64_t v = v0 + static_cast<uint64_t>(u) * blockDim.x;
+            if (v >= hi) continue;
+            if (dst_aligned && v * 16 + 16 <= nbytes) {
+              *reinterpret_cast<U4*>(ra.dst + v * 16) = q[u];
+            } else {
+              const char* qb = reinterpret_cast<const char*>(&q[u]);
+              for (uint64_t b = 0; b < 16 && v * 16 + b < nbytes; ++b) ra.dst[v * 16 + b] = qb[b];
+            }
           }
         }
       }
     }
   }
-  ok = BlockBarrier(ctx, channel, block, epoch + 1, 2) && ok;
-  if (ok && ra.dst) CopyOwnedTiles(ra.dst, my_win, nbytes, nvec, kCopyTile, false);
-  SaveEpoch(ctx, channel, block, epoch + 1);
+  SaveEpoch(ctx, channel, block, epoch + nchunks);
 }
 
 // A kernel that waits for a flag nothing will ever set; used to test the
@@ -740,8 +774,18 @@ int tipsk_broadcast(const void* const* srcs, void* const* dsts, uint64_t nbytes,
     }
     CommLaunch l = MakeLaunch(sp, dp, kSignalBytes);
     const int grid = GridFor(len, static_cast<uint64_t>(kCopyTile) * 16, st.blocks);
-    int rc = st.use_multimem ? LaunchComm(BroadcastKernel<true>, grid, s, l, channel, len, root)
-                             : LaunchComm(BroadcastKernel<false>, grid, s, l, channel, len, root);
+    // One chunk unless TIPS_BCAST_CHUNK_BYTES asks for smaller ones.  Measured on 2 GPUs at 64-256 MiB: 8 MiB chunks
+    // 281-346 GB/s, 32 MiB chunks 354-379 GB/s, one chunk 364-401 GB/s: the root's multicast store rate is the
+    // limit, not the copy out of the window, so the extra barriers only cost.  The tests run with small chunks.
+    static const uint64_t chunk_bytes = [] {
+      const char* e = getenv("TIPS_BCAST_CHUNK_BYTES");
+      const uint64_t v = e ? strtoull(e, nullptr, 10) : 0;
+      return v >= 4096 ? v : ~0ull;
+    }();
+    int nchunks = chunk_bytes == ~0ull ? 1 : static_cast<int>(len / chunk_bytes);
+    nchunks = nchunks < 1 ? 1 : (nchunks > 16 ? 16 : nchunks);
+    int rc = st.use_multimem ? LaunchComm(BroadcastKernel<true>, grid, s, l, channel, len, root, nchunks)
+                             : LaunchComm(BroadcastKernel<false>, grid, s, l, channel, len, root, nchunks);
     if (rc) return rc;
   }
   return 0;

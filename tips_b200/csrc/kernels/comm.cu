@@ -343,8 +343,8 @@ AllgathervKernel(CommLaunch args, int channel, GatherSizes sizes) {
 
 // Broadcast: the root writes its data into every rank's window (one multimem store per vector, or one P2P store per
 // peer), then everyone copies from its own window to its output.  The message can be cut into chunks with a barrier
-// after each, so that the other ranks copy chunk c out of their windows while the root stores chunk c+1 (off by
-// default, see tipsk_broadcast).
+// after each, so that the other ranks copy chunk c out of their windows while the root stores chunk c+1; the root
+// fills its own output from the registers it is sending.
 template <bool kMultimem>
 __global__ void __launch_bounds__(kCommThreads)
 BroadcastKernel(CommLaunch args, int channel, uint64_t nbytes, int root, int nchunks) {
@@ -391,15 +391,23 @@ BroadcastKernel(CommLaunch args, int channel, uint64_t nbytes, int root, int nch
             } else {
               for (int r = 0; r < n; ++r) StSys(ctx.peer[r] + ra.win_off + v * 16, q[u]);
             }
+            // the root fills its own output from the registers it is sending, so it has no copy-out pass
+            if (ra.dst != nullptr && ra.dst != ra.src) {
+              if (dst_aligned && v * 16 + 16 <= nbytes) {
+                *reinterpret_cast<U4*>(ra.dst + v * 16) = q[u];
+              } else {
+                const char* qb = reinterpret_cast<const char*>(&q[u]);
+                for (uint64_t b = 0; b < 16 && v * 16 + b < nbytes; ++b) ra.dst[v * 16 + b] = qb[b];
+              }
+            }
           }
         }
       }
     }
     ok = BlockBarrier(ctx, channel, block, epoch + 1 + c, 2) && ok;
-    // copy this chunk out of the own window; the root does it after its last store, so that it never delays a chunk
-    if (ok && ra.dst && (ctx.rank != root || c == nchunks - 1)) {
-      const uint64_t c_first = ctx.rank != root ? first : static_cast<uint64_t>(block);  // the root: all its tiles
-      for (uint64_t t = c_first; t < t_hi; t += grid) {
+    // the other ranks copy this chunk out of their own windows
+    if (ok && ra.dst && ctx.rank != root) {
+      for (uint64_t t = first; t < t_hi; t += grid) {
         const uint64_t lo = t * kCopyTile;
         const uint64_t hi = lo + kCopyTile < nvec ? lo + kCopyTile : nvec;
         for (uint64_t v0 = lo + threadIdx.x; v0 < hi; v0 += static_cast<uint64_t>(blockDim.x) * kCopyUnroll) {
@@ -774,15 +782,15 @@ int tipsk_broadcast(const void* const* srcs, void* const* dsts, uint64_t nbytes,
     }
     CommLaunch l = MakeLaunch(sp, dp, kSignalBytes);
     const int grid = GridFor(len, static_cast<uint64_t>(kCopyTile) * 16, st.blocks);
-    // One chunk unless TIPS_BCAST_CHUNK_BYTES asks for smaller ones.  Measured on 2 GPUs at 64-256 MiB: 8 MiB chunks
-    // 281-346 GB/s, 32 MiB chunks 354-379 GB/s, one chunk 364-401 GB/s: the root's multicast store rate is the
-    // limit, not the copy out of the window, so the extra barriers only cost.  The tests run with small chunks.
+    // 32 MiB chunks (TIPS_BCAST_CHUNK_BYTES overrides; the tests use small ones).  Measured on 2 GPUs at 64-256 MiB:
+    // one chunk 374-411 GB/s, 16 MiB chunks 390-421 GB/s, 32 MiB chunks 410-475 GB/s; smaller chunks lose to the
+    // extra barriers.
     static const uint64_t chunk_bytes = [] {
       const char* e = getenv("TIPS_BCAST_CHUNK_BYTES");
       const uint64_t v = e ? strtoull(e, nullptr, 10) : 0;
-      return v >= 4096 ? v : ~0ull;
+      return v >= 4096 ? v : (32ull << 20);
     }();
-    int nchunks = chunk_bytes == ~0ull ? 1 : static_cast<int>(len / chunk_bytes);
+    int nchunks = static_cast<int>(len / chunk_bytes);
     nchunks = nchunks < 1 ? 1 : (nchunks > 16 ? 16 : nchunks);
     int rc = st.use_multimem ? LaunchComm(BroadcastKernel<true>, grid, s, l, channel, len, root, nchunks)
                              : LaunchComm(BroadcastKernel<false>, grid, s, l, channel, len, root, nchunks);

@@ -211,7 +211,7 @@ PsPushScatterKernel(PsLaunch args, PsMeta meta, int64_t batch, int64_t grad_ld, 
 // no fences; concurrent pulls may see a row half-way through an update and duplicate ids are applied one after the
 // other.  This is the reference's own consistency model: its servers apply pushes as they arrive, shard by shard, with
 // no barrier between workers (tips/core/ps/ps_server.h:248-264).  SGD: w += -lr * g (one vector reduction).  Adagrad:
-// G += g^2 with the old value returned, then w += -lr * g / (sqrt(G_new) + eps).
+// read G, then G += g^2 and w += -lr * g / (sqrt(G + g^2) + eps) as two vector reductions.
 template <typename GradT>
 __global__ void __launch_bounds__(256)
 PsPushDirectKernel(PsLaunch args, PsMeta meta, int64_t batch, int64_t grad_ld, int64_t grad_col0, float grad_scale,
@@ -246,17 +246,26 @@ PsPushDirectKernel(PsLaunch args, PsMeta meta, int64_t batch, int64_t grad_ld, i
     float* st = reinterpret_cast<float*>(pr.slab[owner] + meta.state_off[f]) + lrow * dim;
     const GradT* g = grads + b * grad_ld + grad_col0 + static_cast<int64_t>(f) * dim;
     for (int v = sublane; v < vecs; v += lanes_per_item) {
-      float d[4];
+      float d[4], gv[4];
 #pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        const float gv = ToFloat<GradT>(g[v * 4 + k]) * grad_scale;
-        if (rule == 1) {
-          const float g2  = gv * gv;
-          const float old = atomicAdd_system(st + v * 4 + k, g2);
-          d[k] = -lr * gv / (sqrtf(old + g2) + eps);
-        } else {
-          d[k] = -lr * gv;
+      for (int k = 0; k < 4; ++k) gv[k] = ToFloat<GradT>(g[v * 4 + k]) * grad_scale;
+      if (rule == 1) {
+        // one vector load of the accumulator (it may miss updates that are in flight: the asynchronous model),
+        // then two vector reductions; no returning atomics, which would cost a round trip per element
+        const U4 q = LdSys(reinterpret_cast<const char*>(st + v * 4));
+        const float acc[4] = {__uint_as_float(q.x), __uint_as_float(q.y), __uint_as_float(q.z), __uint_as_float(q.w)};
+        float g2[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          g2[k] = gv[k] * gv[k];
+          d[k]  = -lr * gv[k] / (sqrtf(acc[k] + g2[k]) + eps);
         }
+        asm volatile("red.relaxed.sys.global.add.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(st + v * 4), "f"(g2[0]), "f"(g2[1]),
+                     "f"(g2[2]), "f"(g2[3])
+                     : "memory");
+      } else {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) d[k] = -lr * gv[k];
       }
       asm volatile("red.relaxed.sys.global.add.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(w + v * 4), "f"(d[0]), "f"(d[1]),
                    "f"(d[2]), "f"(d[3])

@@ -38,6 +38,9 @@ def parse_args():
     ap.add_argument("--no-graph", action="store_true", help="run the CTR step eagerly instead of as a CUDA graph")
     ap.add_argument("--ps-async", action="store_true",
                     help="parameter-server pushes applied as they arrive (no fences); default is the exact synchronous update")
+    ap.add_argument("--fused-update", type=int, default=None, choices=[0, 1],
+                    help="1: the optimizer step runs inside the gradient allreduce kernel, state sharded over the "
+                         "ranks (N > 1); default: the fused_update configuration field")
     ap.add_argument("--backend", default=None, help="fused (default) or nccl (library floor)")
     return ap.parse_args()
 
@@ -124,7 +127,8 @@ def main():
             r = workloads.run_resnet50_floor(args.batch, args.steps, args.warmup)
             result["impl"] = "floor (cuDNN BN + torch SGD + NCCL DDP)"
         else:
-            r = workloads.run_resnet50(args.batch, args.steps, args.warmup)
+            r = workloads.run_resnet50(args.batch, args.steps, args.warmup,
+                                       None if args.fused_update is None else bool(args.fused_update))
         launches += r["gpu_launches"]
         result.update({
             "metric": "resnet50_train_images_per_sec", "value": r["value"], "unit": "images/s",
@@ -133,6 +137,8 @@ def main():
             "config": {"model": "ResNet-50 v1.5", "global_batch": args.batch * size, "per_gpu_batch": args.batch,
                        "image": "224x224x3 NHWC", "optimizer": "SGD momentum 0.9 wd 1e-4",
                        "parallelism": f"dp{size}", "fusion_bucket_mb": 64,
+                       "optimizer_step": "inside the gradient allreduce kernel, state sharded"
+                       if r.get("update_in_allreduce") else "separate kernel",
                        "l2": "inputs and activations per step far exceed the 126 MB L2"},
         })
     if args.workload in ("all", "ctr") and args.impl != "floor":
@@ -153,13 +159,16 @@ def main():
             result.update(ps)
             result["vs_baseline"] = None
     if args.workload == "bert":
-        b = workloads.run_bert(32, 512, args.steps, args.warmup)
+        b = workloads.run_bert(32, 512, args.steps, args.warmup,
+                               fused_update=None if args.fused_update is None else bool(args.fused_update))
         launches += b["gpu_launches"]
         result.update({"metric": "bert_large_mlm_train_tokens_per_sec", "value": b["value"], "unit": "tokens/s",
                        "ms_per_step": b["ms_per_step"], "vs_baseline": None, "e2e": b["e2e"],
                        "config": {"model": "BERT-large-shaped encoder (24x1024x16, FFN 4096, vocab 30522)",
                                   "seq_len": 512, "per_gpu_batch": 32, "global_batch": 32 * size,
-                                  "optimizer": "AdamW", "parallelism": f"dp{size}"}})
+                                  "optimizer": "AdamW", "parallelism": f"dp{size}",
+                                  "optimizer_step": "inside the gradient allreduce kernel, state sharded"
+                                  if b.get("update_in_allreduce") else "separate kernel"}})
     result["gpu_launches"] = launches
     if rank == 0:
         result["clocks"] = sampler.stop()

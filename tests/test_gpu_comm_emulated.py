@@ -118,6 +118,82 @@ def test_allgatherv_and_broadcast(comm4):
         assert torch.equal(o, src)
 
 
+def _reference_step(kind, w, state, g, step, hp):
+    """fp32 reference of one optimizer step (the rules of torch.optim.SGD / AdamW)."""
+    if kind == "sgd":
+        lr, mom, damp, wd, nesterov = hp
+        g = g + wd * w
+        if step == 1:
+            state["m"] = g.clone()
+        else:
+            state["m"] = mom * state["m"] + (1 - damp) * g
+        g = g + mom * state["m"] if nesterov else state["m"]
+        return w - lr * g
+    lr, b1, b2, eps, wd, _ = hp
+    state["m"] = b1 * state.get("m", torch.zeros_like(w)) + (1 - b1) * g
+    state["v"] = b2 * state.get("v", torch.zeros_like(w)) + (1 - b2) * g * g
+    mhat = state["m"] / (1 - b1 ** step)
+    denom = (state["v"] / (1 - b2 ** step)).sqrt() + eps
+    return w * (1 - lr * wd) - lr * mhat / denom
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("kind", ["sgd", "adam"])
+@pytest.mark.parametrize("numel", [8 * 1000, 2048 * 4 * 8 * 2 + 4096 + 64])
+def test_allreduce_fused_with_optimizer_step(comm4, dtype, kind, numel):
+    """One launch reduces the gradient bucket, steps the share of the master weights each rank owns and stores the
+    new parameters into every rank's window; three steps against an fp32 reference."""
+    from tips_b200.parallel.sharding import ShardLayout
+    st, lib = comm4
+    dev = st.device
+    n = 4
+    es = torch.empty((), dtype=dtype).element_size()
+    nbytes = numel * es
+    _, goff = st.alloc_symmetric(nbytes)
+    _, poff = st.alloc_symmetric(nbytes)
+    grads = [w[goff:goff + nbytes].view(dtype) for w in st.windows]
+    params = [w[poff:poff + nbytes].view(dtype) for w in st.windows]
+    torch.manual_seed(numel + es)
+    w0 = (torch.randn(numel, device=dev) * 0.5).to(dtype)
+    for p in params:
+        p.copy_(w0)
+    lay = ShardLayout(numel, es, n, int(lib.tipsk_comm_update_subtile()))
+    assert lay.shard_numel * es == int(lib.tipsk_comm_update_shard_vecs(nbytes)) * 16
+    masters = [lay.take(w0.float(), r) for r in range(n)]
+    s0 = [torch.zeros_like(m) for m in masters]
+    s1 = [torch.zeros_like(m) for m in masters]
+    code = 0 if kind == "sgd" else 1
+    _check(lib, lib.tipsk_comm_attach_update(goff, nbytes, DT[dtype], poff, code, _arr([m.data_ptr() for m in masters]),
+                                             _arr([m.data_ptr() for m in s0]), _arr([m.data_ptr() for m in s1])))
+    assert lib.tipsk_comm_update_attached(goff, nbytes) == 1
+    hp = [0.1, 0.9, 0.0, 1e-3, 1.0] if kind == "sgd" else [1e-2, 0.9, 0.999, 1e-8, 0.01, 1.0]
+    ref_w = w0.float().clone()
+    ref_state = {}
+    tol = 1e-5 if dtype == torch.float32 else 2e-2
+    for step in range(1, 4):
+        gs = [(torch.randn(numel, device=dev) * 0.3).to(dtype) for _ in range(n)]
+        for g, src in zip(grads, gs):
+            g.copy_(src)
+        _check(lib, lib.tipsk_comm_set_update_hyper(goff, (ctypes.c_float * len(hp))(*hp), len(hp), step))
+        _check(lib, lib.tipsk_allreduce_update(goff, 0.25, 1, torch.cuda.current_stream().cuda_stream))
+        torch.cuda.synchronize()
+        st.check_status()
+        gsum = sum(g.float() for g in gs) * 0.25
+        ref_w = _reference_step(kind, ref_w, ref_state, gsum, step, hp)
+        got_master = lay.assemble(torch.stack(masters))
+        assert torch.allclose(got_master, ref_w, atol=2e-5, rtol=1e-4), (step, (got_master - ref_w).abs().max())
+        for p in params:
+            assert torch.allclose(p.float(), ref_w, atol=tol, rtol=tol)
+            assert torch.equal(p, params[0])
+    if kind == "sgd":
+        assert torch.allclose(lay.assemble(torch.stack(s0)), ref_state["m"], atol=2e-5, rtol=1e-4)
+    else:
+        assert torch.allclose(lay.assemble(torch.stack(s1)), ref_state["v"], atol=1e-6, rtol=1e-4)
+    assert lib.tipsk_comm_update_launches(goff) == 3
+    lib.tipsk_comm_detach_update(goff)
+    assert lib.tipsk_comm_update_attached(goff, nbytes) == 0
+
+
 def test_bounded_wait_reports_timeout(comm4):
     """A wait on a flag that nothing sets must give up inside the budget and leave a status."""
     st, lib = comm4

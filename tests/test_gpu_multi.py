@@ -26,6 +26,14 @@ def test_collectives_two_gpus(multimem):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs at least 2 GPUs")
+@pytest.mark.parametrize("multimem", ["1", "0"])
+def test_optimizer_step_inside_the_allreduce(multimem):
+    n = min(torch.cuda.device_count(), 4)
+    r = _run("fused_update_worker.py", n, env={"TIPS_DISABLE_MULTIMEM": "0" if multimem == "1" else "1"})
+    assert r.returncode == 0 and "FUSED_UPDATE_OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs at least 2 GPUs")
 def test_parameter_server_two_gpus():
     r = _run("ps_worker.py", 2)
     assert r.returncode == 0 and "MULTI_GPU_PS_OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]

@@ -111,7 +111,7 @@ class _Prefetcher:
         return cur
 
 
-def run_resnet50(batch: int, steps: int, warmup: int):
+def run_resnet50(batch: int, steps: int, warmup: int, fused_update=None):
     from tips_b200.models.resnet50 import resnet50
     from tips_b200.ops.optim import FusedSGD
     dev = torch.device("cuda", torch.cuda.current_device())
@@ -120,8 +120,8 @@ def run_resnet50(batch: int, steps: int, warmup: int):
     model = resnet50(device=dev, library_conv=os.environ.get("TIPS_RESNET_LIBRARY_CONV", "0") == "1")
     model.train()
     opt = FusedSGD(model.parameters(), lr=0.1, momentum=0.9, weight_decay=1e-4)
-    opt = tips.DistributedOptimizer(opt, named_parameters=model.named_parameters())
-    tips.broadcast_parameters(model.state_dict(), root_rank=0)
+    opt = tips.DistributedOptimizer(opt, named_parameters=model.named_parameters(), fused_update=fused_update)
+    tips.broadcast_parameters(model.state_dict(), root_rank=0, optimizer=opt)
     g = torch.Generator().manual_seed(100 + tips.rank())
     nhost = 3
     host = []
@@ -159,9 +159,11 @@ def run_resnet50(batch: int, steps: int, warmup: int):
     last["loss"] = reader.drain()
     e2e = {"value": batch * tips.size() * steps / (ms2 / 1e3), "unit": "images/s", "ms_per_step": ms2 / steps,
            "h2d_bytes_per_step": pre.bytes_per_step, "d2h_bytes_per_step": 4, "last_loss": last.get("loss")}
+    update_in_allreduce = bool(getattr(opt, "_tips_update_in_allreduce", False))
     del pre, model, opt, x_dev, y_dev
     release_cached_memory()
-    return {"value": value, "ms_per_step": ms / steps, "gpu_launches": launches, "e2e": e2e}
+    return {"value": value, "ms_per_step": ms / steps, "gpu_launches": launches, "e2e": e2e,
+            "update_in_allreduce": update_in_allreduce}
 
 
 def run_resnet50_floor(batch: int, steps: int, warmup: int):
@@ -253,15 +255,16 @@ def run_ctr(batch: int, rows: int, steps: int, warmup: int, graph: bool = True, 
     return {"value": value, "ms_per_step": ms / steps, "gpu_launches": launches, "e2e": e2e}
 
 
-def run_bert(batch: int, seq: int, steps: int, warmup: int, layers: int = 24):
+def run_bert(batch: int, seq: int, steps: int, warmup: int, layers: int = 24, fused_update=None):
     """BERT-large-shaped MLM training, data-parallel, AdamW (tokens/s)."""
     from tips_b200.models.bert import bert_large, synthetic_mlm_batch
     from tips_b200.ops.optim import FusedAdamW
     dev = torch.device("cuda", torch.cuda.current_device())
     torch.manual_seed(4321)
     model = bert_large(device=dev, layers=layers, max_seq=seq).train()
-    opt = tips.DistributedOptimizer(FusedAdamW(model.parameters(), lr=1e-4, weight_decay=0.01))
-    tips.broadcast_parameters(model.state_dict(), root_rank=0)
+    opt = tips.DistributedOptimizer(FusedAdamW(model.parameters(), lr=1e-4, weight_decay=0.01),
+                                    fused_update=fused_update)
+    tips.broadcast_parameters(model.state_dict(), root_rank=0, optimizer=opt)
     host = [tuple(t.pin_memory() for t in synthetic_mlm_batch(batch, seq, 30522, seed=31 * tips.rank() + i))
             for i in range(3)]
     resident = [t.to(dev) for t in host[0]]
@@ -291,4 +294,5 @@ def run_bert(batch: int, seq: int, steps: int, warmup: int, layers: int = 24):
     last["loss"] = reader.drain()
     e2e = {"value": batch * seq * tips.size() * steps / (ms2 / 1e3), "unit": "tokens/s", "ms_per_step": ms2 / steps,
            "h2d_bytes_per_step": pre.bytes_per_step, "d2h_bytes_per_step": 4, "last_loss": last.get("loss")}
-    return {"value": value, "ms_per_step": ms / steps, "gpu_launches": launches, "e2e": e2e}
+    return {"value": value, "ms_per_step": ms / steps, "gpu_launches": launches, "e2e": e2e,
+            "update_in_allreduce": bool(getattr(opt, "_tips_update_in_allreduce", False))}

@@ -28,6 +28,7 @@ class Config:
     use_multimem: bool = True                # NVLS multimem instructions when a multicast mapping exists
     symm_window_bytes: int = 256 << 20       # staging window for tensors outside symmetric memory
     static_schedule: bool = True             # freeze the bucket order after the first negotiated step
+    fused_update: bool = False               # fused optimizers step inside the gradient allreduce, state sharded
     # Parameter server
     ps_local_shards: int = 1
     # Observability

@@ -27,10 +27,12 @@
 
 #include <cstdio>
 #include <cstring>
+#include <map>
 #include <mutex>
 #include <vector>
 
 #include "kernels/common.cuh"
+#include "kernels/optim_rules.cuh"
 #include "kernels/tips_kernels.h"
 
 namespace tipsk {
@@ -282,6 +284,132 @@ AllreduceKernel(CommLaunch args, int channel, uint64_t nbytes, int op, float pre
   }
   ok = BlockBarrier(ctx, channel, block, epoch + 1, 2) && ok;
   if (ok && !kOneShot && ra.dst) CopyOwnedTiles(ra.dst, my_win, nbytes, nvec, tile_vecs, false);
+  SaveEpoch(ctx, channel, block, epoch + 1);
+}
+
+// ---------------------------------------------------------------------------
+// Allreduce fused with the optimizer step.  The gradient bucket and the
+// parameter buffer both live in the window.  Every rank owns the same share of
+// the 16-byte vectors as in the two-shot allreduce (sub-tile `rank` of every
+// tile) and keeps the fp32 master weights and the optimizer state of that share
+// only, packed densely: vector j of tile t sits at [t * kUpdSubTile + j].
+//   -- barrier: every rank has packed its gradients --
+//   reduce own share of the gradients (in the switch, or from every peer)
+//   -> scale -> SGD-momentum / Adam on the master share -> cast -> store the new
+//   parameters into EVERY rank's parameter buffer (multicast store, or one store per peer)
+//   -- barrier: every rank's share has arrived, the parameters are complete --
+// The reduced gradient is never written anywhere, the optimizer reads and
+// writes 1/N of its state per rank, and no separate optimizer launch follows.
+constexpr int kUpdSubTile = 2048;  // vectors per rank per tile; also the layout unit of the state shards
+
+struct UpdateArgs {
+  float* master;       // this rank's share of the fp32 weights
+  float* s0;           // momentum buffer / first moment
+  float* s1;           // second moment (Adam)
+  uint64_t param_off;  // byte offset of the parameter buffer inside every rank's window
+};
+struct UpdateLaunch {
+  UpdateArgs r[kMaxRanks];
+  SgdParams sgd;
+  AdamParams adam;
+};
+
+template <int kE>
+__device__ __forceinline__ void LoadState(const float* p, float (&v)[kE]) {
+#pragma unroll
+  for (int i = 0; i < kE; i += 4) {
+    const float4 q = *reinterpret_cast<const float4*>(p + i);
+    v[i] = q.x; v[i + 1] = q.y; v[i + 2] = q.z; v[i + 3] = q.w;
+  }
+}
+template <int kE>
+__device__ __forceinline__ void StoreState(float* p, const float (&v)[kE]) {
+#pragma unroll
+  for (int i = 0; i < kE; i += 4) *reinterpret_cast<float4*>(p + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+}
+
+template <typename T, bool kMultimem, bool kAdam>
+__global__ void __launch_bounds__(kCommThreads)
+AllreduceUpdateKernel(CommLaunch args, UpdateLaunch upd, int channel, uint64_t nbytes, float scale) {
+  const RankArgs& ra   = args.r[blockIdx.y];
+  const UpdateArgs& ua = upd.r[blockIdx.y];
+  const CommCtx& ctx   = ra.ctx;
+  const int n          = ctx.nranks;
+  const int block      = blockIdx.x;
+  constexpr int kE      = 16 / sizeof(T);
+  constexpr int kUnroll = kMultimem ? 4 : 2;  // one reduced vector per load in the switch: more of them in flight
+  constexpr int kSrcs   = kMultimem ? 1 : kMaxRanks;
+  const uint64_t nvec      = nbytes / 16;  // the host side only accepts whole vectors
+  const uint64_t tile_vecs = static_cast<uint64_t>(kUpdSubTile) * n;
+  const uint64_t ntiles    = (nvec + tile_vecs - 1) / tile_vecs;
+  uint32_t epoch = NextEpoch(ctx, channel, block);
+
+  bool ok = BlockBarrier(ctx, channel, block, epoch, 1);
+  if (ok) {
+    for (uint64_t t = block; t < ntiles; t += gridDim.x) {
+      const uint64_t sub_lo = t * tile_vecs + static_cast<uint64_t>(ctx.rank) * kUpdSubTile;
+      for (uint32_t base = threadIdx.x; base < kUpdSubTile; base += kCommThreads * kUnroll) {
+        U4 in[kUnroll][kSrcs];
+        bool live[kUnroll];
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+          const uint64_t vec = sub_lo + base + u * kCommThreads;
+          live[u] = base + u * kCommThreads < kUpdSubTile && vec < nvec;
+          if (!live[u]) continue;
+          const uint64_t off = ra.win_off + vec * 16;
+          if constexpr (kMultimem) {
+            in[u][0] = MultimemLdReduce<T>(ctx.mc + off);
+          } else {
+#pragma unroll
+            for (int r = 0; r < kMaxRanks; ++r)
+              if (r < n) in[u][r] = LdSys(ctx.peer[(ctx.rank + r) % n] + off);
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+          if (!live[u]) continue;
+          const uint32_t j   = base + u * kCommThreads;
+          const uint64_t vec = sub_lo + j;
+          Acc<T> acc;
+          acc.Zero();
+#pragma unroll
+          for (int r = 0; r < kSrcs; ++r)
+            if (r < n) acc.Add(in[u][r]);
+          acc.Scale(scale);
+          const uint64_t at = (t * kUpdSubTile + j) * kE;  // element offset inside the state share
+          float w[kE], m[kE], v[kE];
+          LoadState<kE>(ua.master + at, w);
+          if constexpr (kAdam) {
+            LoadState<kE>(ua.s0 + at, m);
+            LoadState<kE>(ua.s1 + at, v);
+#pragma unroll
+            for (int e = 0; e < kE; ++e) AdamUpdate(w[e], m[e], v[e], acc.a[e], upd.adam);
+            StoreState<kE>(ua.s0 + at, m);
+            StoreState<kE>(ua.s1 + at, v);
+          } else {
+            const bool has_m = upd.sgd.momentum != 0.f;
+            if (has_m && !upd.sgd.first_step) LoadState<kE>(ua.s0 + at, m);
+#pragma unroll
+            for (int e = 0; e < kE; ++e) SgdUpdate(w[e], m[e], acc.a[e], upd.sgd);
+            if (has_m) StoreState<kE>(ua.s0 + at, m);
+          }
+          StoreState<kE>(ua.master + at, w);
+#pragma unroll
+          for (int e = 0; e < kE; ++e) acc.a[e] = w[e];
+          const U4 out       = acc.Pack();
+          const uint64_t off = ua.param_off + vec * 16;
+          if constexpr (kMultimem) {
+            MultimemSt(ctx.mc + off, out);
+          } else {
+#pragma unroll
+            for (int r = 0; r < kMaxRanks; ++r)
+              if (r < n) StSys(ctx.peer[(ctx.rank + r) % n] + off, out);
+          }
+        }
+      }
+    }
+  }
+  BlockBarrier(ctx, channel, block, epoch + 1, 2);
   SaveEpoch(ctx, channel, block, epoch + 1);
 }
 
@@ -558,6 +686,31 @@ int LaunchAllreduce(int dtype, const CommLaunch& l, int channel, uint64_t nbytes
   }
 }
 
+
+// Optimizer updates attached to gradient buckets, keyed by the bucket's window offset.
+struct AttachedUpdate {
+  uint64_t nbytes = 0;
+  int dtype = 0;
+  int kind = 0;  // 0 SGD with momentum, 1 Adam / AdamW
+  UpdateArgs r[kMaxRanks];
+  float h[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  int64_t step = 0;
+  uint64_t launches = 0;
+};
+std::map<int64_t, AttachedUpdate> g_updates;
+std::mutex g_updates_mu;
+
+template <typename T>
+int LaunchUpdateT(const CommLaunch& l, const UpdateLaunch& u, bool adam, bool multimem, int channel, uint64_t nbytes,
+                  float scale, int grid, cudaStream_t s) {
+  if (adam) {
+    if (multimem) return LaunchComm(AllreduceUpdateKernel<T, true, true>, grid, s, l, u, channel, nbytes, scale);
+    return LaunchComm(AllreduceUpdateKernel<T, false, true>, grid, s, l, u, channel, nbytes, scale);
+  }
+  if (multimem) return LaunchComm(AllreduceUpdateKernel<T, true, false>, grid, s, l, u, channel, nbytes, scale);
+  return LaunchComm(AllreduceUpdateKernel<T, false, false>, grid, s, l, u, channel, nbytes, scale);
+}
+
 }  // namespace
 
 extern "C" {
@@ -633,6 +786,10 @@ int tipsk_comm_shutdown(void) {
   for (cudaEvent_t e : st.event_pool) cudaEventDestroy(e);
   st.event_pool.clear();
   st.ready = false;
+  {
+    std::lock_guard<std::mutex> ulock(g_updates_mu);
+    g_updates.clear();
+  }
   return 0;
 }
 
@@ -722,6 +879,123 @@ int tipsk_allreduce(const void* const* srcs, void* const* dsts, int64_t win_off,
     if (rc) return rc;
   }
   return 0;
+}
+
+/* ---- allreduce fused with the optimizer step ----
+ * Number of 16-byte vectors of master weights / state that every rank keeps for a bucket of `nbytes` bytes. */
+int tipsk_comm_update_subtile(void) { return kUpdSubTile; }
+int64_t tipsk_comm_update_shard_vecs(uint64_t nbytes) {
+  CommState& st = g_comm;
+  const uint64_t nvec      = nbytes / 16;
+  const uint64_t tile_vecs = static_cast<uint64_t>(kUpdSubTile) * st.nranks;
+  return static_cast<int64_t>((nvec + tile_vecs - 1) / tile_vecs * kUpdSubTile);
+}
+
+/* Attaches an optimizer update to the gradient bucket at window offset `grad_off`: from now on
+ * tipsk_allreduce_update (and the engine's in-place sum-allreduce of exactly that buffer) reduces the gradients,
+ * updates this rank's share of the fp32 master weights / state and stores the new parameters, in `dtype`, into every
+ * rank's window at `param_off`.  master / s0 / s1 are host arrays with one device pointer per LOCAL rank, each
+ * tipsk_comm_update_shard_vecs(nbytes) * 16 / sizeof(dtype) floats (s1 only for Adam, s0 may be null for plain SGD). */
+int tipsk_comm_attach_update(int64_t grad_off, uint64_t nbytes, int dtype, int64_t param_off, int kind,
+                             void* const* master, void* const* s0, void* const* s1) {
+  CommState& st = g_comm;
+  TIPSK_REQUIRE(st.ready, "comm not initialised");
+  TIPSK_REQUIRE(dtype == kF32 || dtype == kBF16 || dtype == kF16, "update: gradients must be fp32, bf16 or fp16");
+  TIPSK_REQUIRE(nbytes > 0 && nbytes % 16 == 0, "update: the bucket must be a whole number of 16-byte vectors");
+  TIPSK_REQUIRE(kind == 0 || kind == 1, "update: kind is 0 (SGD) or 1 (Adam)");
+  for (int64_t off : {grad_off, param_off}) {
+    TIPSK_REQUIRE(off >= static_cast<int64_t>(kSignalBytes) && off % 16 == 0, "update: bad window offset");
+    TIPSK_REQUIRE(static_cast<uint64_t>(off) + nbytes <= st.window_bytes, "update: buffer exceeds the window");
+  }
+  TIPSK_REQUIRE(grad_off + static_cast<int64_t>(nbytes) <= param_off || param_off + static_cast<int64_t>(nbytes) <= grad_off,
+                "update: gradient and parameter buffers overlap");
+  AttachedUpdate a;
+  a.nbytes = nbytes;
+  a.dtype  = dtype;
+  a.kind   = kind;
+  const int local = st.emulated > 0 ? st.emulated : 1;
+  for (int i = 0; i < local; ++i) {
+    TIPSK_REQUIRE(master && master[i], "update: master weights missing");
+    TIPSK_REQUIRE(kind == 0 || (s0 && s0[i] && s1 && s1[i]), "update: Adam needs both moment buffers");
+    a.r[i].master    = static_cast<float*>(master[i]);
+    a.r[i].s0        = s0 ? static_cast<float*>(s0[i]) : nullptr;
+    a.r[i].s1        = s1 ? static_cast<float*>(s1[i]) : nullptr;
+    a.r[i].param_off = static_cast<uint64_t>(param_off);
+  }
+  std::lock_guard<std::mutex> lock(g_updates_mu);
+  g_updates[grad_off] = a;
+  return 0;
+}
+
+int tipsk_comm_detach_update(int64_t grad_off) {
+  std::lock_guard<std::mutex> lock(g_updates_mu);
+  if (grad_off < 0) g_updates.clear();
+  else g_updates.erase(grad_off);
+  return 0;
+}
+
+int tipsk_comm_update_attached(int64_t grad_off, uint64_t nbytes) {
+  std::lock_guard<std::mutex> lock(g_updates_mu);
+  auto it = g_updates.find(grad_off);
+  return it != g_updates.end() && it->second.nbytes == nbytes ? 1 : 0;
+}
+
+/* Hyper-parameters of the next update of that bucket.  SGD: {lr, momentum, dampening, weight_decay, nesterov};
+ * Adam: {lr, beta1, beta2, eps, weight_decay, decoupled}.  `step` counts from 1 (first step of SGD seeds the
+ * momentum buffer, Adam's bias correction). */
+int tipsk_comm_set_update_hyper(int64_t grad_off, const float* h, int nh, int64_t step) {
+  std::lock_guard<std::mutex> lock(g_updates_mu);
+  auto it = g_updates.find(grad_off);
+  TIPSK_REQUIRE(it != g_updates.end(), "update: no update attached at that offset");
+  TIPSK_REQUIRE(nh >= 1 && nh <= 8 && step >= 1, "update: bad hyper-parameters");
+  for (int i = 0; i < nh; ++i) it->second.h[i] = h[i];
+  it->second.step = step;
+  return 0;
+}
+
+uint64_t tipsk_comm_update_launches(int64_t grad_off) {
+  std::lock_guard<std::mutex> lock(g_updates_mu);
+  auto it = g_updates.find(grad_off);
+  return it == g_updates.end() ? 0 : it->second.launches;
+}
+
+/* One launch: sum-allreduce of the attached gradient bucket times `scale`, optimizer step on the owned share,
+ * new parameters stored to every rank. */
+int tipsk_allreduce_update(int64_t grad_off, float scale, int channel, void* stream) {
+  CommState& st = g_comm;
+  TIPSK_REQUIRE(st.ready, "comm not initialised");
+  TIPSK_REQUIRE(channel >= 0 && channel < kNumChannels, "bad channel");
+  AttachedUpdate a;
+  {
+    std::lock_guard<std::mutex> lock(g_updates_mu);
+    auto it = g_updates.find(grad_off);
+    TIPSK_REQUIRE(it != g_updates.end(), "update: no update attached at that offset");
+    TIPSK_REQUIRE(it->second.step >= 1, "update: hyper-parameters were never set");
+    it->second.launches++;
+    a = it->second;
+  }
+  cudaStream_t s = stream ? static_cast<cudaStream_t>(stream) : st.streams[channel];
+  CommLaunch l   = MakeLaunch(nullptr, nullptr, static_cast<uint64_t>(grad_off));
+  UpdateLaunch u;
+  memset(&u, 0, sizeof(u));
+  for (int i = 0; i < kMaxRanks; ++i) u.r[i] = a.r[i];
+  const float* h = a.h;
+  if (a.kind == 0) {
+    u.sgd = SgdParams{h[0], h[1], h[2], h[3], 1.f, h[4] != 0.f ? 1 : 0, a.step == 1 ? 1 : 0};
+  } else {
+    const float step = static_cast<float>(a.step);
+    u.adam = AdamParams{h[0], h[1], h[2], h[3], h[4], 1.f, 1.f - powf(h[1], step), 1.f - powf(h[2], step),
+                        h[5] != 0.f ? 1 : 0, nullptr};
+  }
+  const uint64_t tile_bytes = static_cast<uint64_t>(kUpdSubTile) * st.nranks * 16;
+  const int grid            = GridFor(a.nbytes, tile_bytes, st.blocks);
+  const bool mm             = st.use_multimem;
+  switch (a.dtype) {
+    case kF32: return LaunchUpdateT<float>(l, u, a.kind == 1, mm, channel, a.nbytes, scale, grid, s);
+    case kBF16: return LaunchUpdateT<__nv_bfloat16>(l, u, a.kind == 1, mm, channel, a.nbytes, scale, grid, s);
+    case kF16: return LaunchUpdateT<__half>(l, u, a.kind == 1, mm, channel, a.nbytes, scale, grid, s);
+    default: return SetError(-2, "update: unsupported dtype");
+  }
 }
 
 /* Allgatherv of per-rank byte counts; staged through the staging area, chunked when a slab is larger. */

@@ -50,7 +50,10 @@ int tipsk_device_execute(const tips_device_op* op, char* err, int err_len) {
     const char* in        = static_cast<const char*>(op->in);
     const bool in_window  = g_window && in >= g_window + tipsk::kSignalBytes && in + nbytes <= g_window + g_window_bytes &&
                            ((in - g_window) % 16) == 0;
-    if (in_window && op->in == op->out) {
+    if (in_window && op->in == op->out && op->reduce_op == 0 && tipsk_comm_update_attached(in - g_window, nbytes)) {
+      // this bucket carries an optimizer update: reduce, update the owned share, store the new parameters
+      rc = tipsk_allreduce_update(in - g_window, static_cast<float>(op->prescale * op->postscale), ch, stream);
+    } else if (in_window && op->in == op->out) {
       rc = tipsk_allreduce(nullptr, nullptr, in - g_window, nbytes, op->dtype, op->reduce_op,
                            static_cast<float>(op->prescale), static_cast<float>(op->postscale), ch, stream);
     } else if (in_window) {

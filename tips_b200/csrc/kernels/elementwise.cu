@@ -10,6 +10,7 @@
 // Here one launch covers a whole bucket: every element is read once and written
 // once, in 16-byte vectors, so the kernels run at HBM speed.
 #include "kernels/common.cuh"
+#include "kernels/optim_rules.cuh"
 #include "kernels/tips_kernels.h"
 
 namespace tipsk {
@@ -56,20 +57,6 @@ __device__ __forceinline__ void Store4(T* p, const float (&in)[4]) {
   *reinterpret_cast<Quad<T>*>(p) = q;
 }
 
-struct SgdParams {
-  float lr, momentum, dampening, wd, grad_scale;
-  int nesterov, first_step;
-};
-
-__device__ __forceinline__ void SgdUpdate(float& p, float& m, float g, const SgdParams& a) {
-  g = g * a.grad_scale + a.wd * p;
-  if (a.momentum != 0.f) {
-    m = a.first_step ? g : a.momentum * m + (1.f - a.dampening) * g;
-    g = a.nesterov ? g + a.momentum * m : m;
-  }
-  p -= a.lr * g;
-}
-
 template <typename G, typename P16>
 __global__ void __launch_bounds__(kThreads)
 SgdFlatKernel(float* __restrict__ p32, P16* __restrict__ p16, const G* __restrict__ g, float* __restrict__ m,
@@ -96,23 +83,6 @@ SgdFlatKernel(float* __restrict__ p32, P16* __restrict__ p16, const G* __restric
     if (a.momentum != 0.f) m[t] = mm;
     if (p16) p16[t] = FromFloat<P16>(p);
   }
-}
-
-struct AdamParams {
-  float lr, beta1, beta2, eps, wd, grad_scale, bias1, bias2;  // bias = 1 - beta^step
-  int decoupled;
-  const int64_t* step_dev;  // when set, the step count is read on the device (CUDA-graph replays)
-};
-
-__device__ __forceinline__ void AdamUpdate(float& p, float& m, float& v, float g, const AdamParams& a) {
-  g *= a.grad_scale;
-  if (!a.decoupled) g += a.wd * p;
-  m = a.beta1 * m + (1.f - a.beta1) * g;
-  v = a.beta2 * v + (1.f - a.beta2) * g * g;
-  const float mhat  = m / a.bias1;
-  const float denom = sqrtf(v / a.bias2) + a.eps;
-  if (a.decoupled) p *= (1.f - a.lr * a.wd);
-  p -= a.lr * mhat / denom;
 }
 
 template <typename G, typename P16>

@@ -128,6 +128,16 @@ int tipsk_allgatherv(const void* const* host_srcs, void* const* host_dsts, const
 int tipsk_broadcast(const void* const* host_srcs, void* const* host_dsts, uint64_t nbytes, int root, int channel,
                     void* stream);
 int tipsk_comm_wait_never(int channel, void* stream);
+/* Allreduce fused with the optimizer step on the share of the parameters each rank owns (see comm.cu). */
+int tipsk_comm_update_subtile(void);
+int64_t tipsk_comm_update_shard_vecs(uint64_t nbytes);
+int tipsk_comm_attach_update(int64_t grad_off, uint64_t nbytes, int dtype, int64_t param_off, int kind,
+                             void* const* host_master, void* const* host_s0, void* const* host_s1);
+int tipsk_comm_detach_update(int64_t grad_off);
+int tipsk_comm_update_attached(int64_t grad_off, uint64_t nbytes);
+int tipsk_comm_set_update_hyper(int64_t grad_off, const float* h, int nh, int64_t step);
+uint64_t tipsk_comm_update_launches(int64_t grad_off);
+int tipsk_allreduce_update(int64_t grad_off, float scale, int channel, void* stream);
 void* tipsk_event_create(void);
 void tipsk_event_recycle(void* ev);
 int tipsk_event_record(void* ev, void* stream);

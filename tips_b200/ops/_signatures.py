@@ -49,6 +49,14 @@ _PROTOS = {
     "tipsk_allgatherv": (I, [PP, PP, POINTER(U), I, P]),
     "tipsk_broadcast": (I, [PP, PP, U, I, I, P]),
     "tipsk_comm_wait_never": (I, [I, P]),
+    "tipsk_comm_update_subtile": (I, []),
+    "tipsk_comm_update_shard_vecs": (L, [U]),
+    "tipsk_comm_attach_update": (I, [L, U, I, L, I, PP, PP, PP]),
+    "tipsk_comm_detach_update": (I, [L]),
+    "tipsk_comm_update_attached": (I, [L, U]),
+    "tipsk_comm_set_update_hyper": (I, [L, POINTER(c_float), I, L]),
+    "tipsk_comm_update_launches": (U, [L]),
+    "tipsk_allreduce_update": (I, [L, F, I, P]),
     "tipsk_event_create": (P, []),
     "tipsk_event_recycle": (None, [P]),
     "tipsk_event_record": (I, [P, P]),

@@ -39,6 +39,90 @@ class _FlatBucketState:
         self.state = {}
         self.steps = 0
         self.grads_packed = False  # set by DistributedOptimizer when the bucket already holds reduced grads
+        self.layout = None         # ShardLayout when the update runs inside the allreduce kernel
+        self.rank = 0
+        self.param_off = -1
+        self._pending_full = {}    # full-size tensors loaded on this rank and not yet shared with the others
+
+    # -- update inside the allreduce: this rank keeps master weights and state of the vectors it owns -------------
+    @property
+    def sharded(self) -> bool:
+        return self.layout is not None
+
+    def shard(self, device_state, state_keys):
+        """Move the parameters into the symmetric window and cut master weights / state down to this rank's share.
+        `state_keys` names the state tensors the optimizer's rule needs; they start at zero."""
+        from ..parallel.sharding import ShardLayout
+        b = self.bucket
+        if b.win_off < 0 or b.grad.dtype != self.flat_param.dtype:
+            raise ValueError("the fused update needs the gradient bucket in the window and in the parameters' dtype")
+        lib = base.K()
+        es = self.flat_param.element_size()
+        nbytes = b.numel * es
+        pbuf, poff = device_state.alloc_symmetric(nbytes, self.flat_param.dtype)
+        pbuf.copy_(self.flat_param)
+        for i, p in enumerate(b.params):
+            p.data = pbuf[b.offsets[i]:b.offsets[i] + p.numel()].view(p.shape)
+        full_master = self.master.float() if self.master is self.flat_param else self.master
+        self.flat_param = pbuf
+        self.param_off = poff
+        self.rank = device_state.rank
+        self.layout = ShardLayout(b.numel, es, device_state.size, int(lib.tipsk_comm_update_subtile()))
+        assert self.layout.shard_numel * es == int(lib.tipsk_comm_update_shard_vecs(nbytes)) * 16
+        self.master = self.layout.take(full_master, self.rank)
+        self.state = {k: torch.zeros_like(self.master) for k in state_keys}
+        return self
+
+    def attach(self, kind: int, s0=None, s1=None):
+        import ctypes
+        b = self.bucket
+
+        def arr(t):
+            return (ctypes.c_void_p * 1)(t.data_ptr()) if t is not None else None
+
+        base.check(base.K().tipsk_comm_attach_update(
+            b.win_off, b.numel * self.flat_param.element_size(), base.code(self.flat_param), self.param_off, kind,
+            arr(self.master), arr(s0), arr(s1)), "attach_update")
+
+    def full(self, shard: torch.Tensor) -> torch.Tensor:
+        """Full-size tensor assembled from every rank's share (a collective: every rank calls it)."""
+        if not self.sharded:
+            return shard
+        from ..parallel import collectives as C
+        gathered = C.allgather(shard.reshape(1, -1), name=None)
+        return self.layout.assemble(gathered)
+
+    def full_master(self) -> torch.Tensor:
+        return self.full(self.master)
+
+    def load_master(self, full: torch.Tensor) -> None:
+        full = full.to(self.master.device, torch.float32).reshape(-1)
+        if self.sharded:
+            self.master.copy_(self.layout.take(full, self.rank))
+            self._pending_full["master"] = full
+        else:
+            self.master.copy_(full)
+        if self.low or self.sharded:
+            self.flat_param.copy_(full)
+
+    def load_state(self, key: str, full: torch.Tensor) -> None:
+        if key == "step_dev":  # rebuilt from `steps` by the optimizer
+            return
+        full = full.to(self.master.device, torch.float32).reshape(-1)
+        if self.sharded:
+            if key not in self.state:
+                raise KeyError(f"the attached update has no state tensor {key!r}")
+            self.state[key].copy_(self.layout.take(full, self.rank))  # in place: the kernel holds this pointer
+            self._pending_full[key] = full
+        else:
+            self.state[key] = full.clone()
+
+    def refresh_master_from_params(self) -> None:
+        """After the parameters were overwritten from outside (a broadcast, a loaded state dict)."""
+        if self.sharded:
+            self.master.copy_(self.layout.take(self.flat_param.float(), self.rank))
+        elif self.low:
+            self.master.copy_(self.flat_param)
 
 
 class _FusedOptimizer(torch.optim.Optimizer):
@@ -88,6 +172,18 @@ class _FusedOptimizer(torch.optim.Optimizer):
                 loss = closure()
         for fs in self.build():
             b = fs.bucket
+            if fs.sharded:
+                # the allreduce kernel of this bucket already applied the update to the share each rank owns
+                if not fs.grads_packed:
+                    raise RuntimeError("this optimizer's update runs inside the gradient allreduce: call step() "
+                                       "through DistributedOptimizer, after backward")
+                if grad_scale != 1.0:
+                    raise ValueError("grad_scale is not supported when the update runs inside the allreduce")
+                fs.grads_packed = False
+                fs.steps += 1
+                for p in b.params:
+                    p.grad = None
+                continue
             if not fs.grads_packed:
                 if all(p.grad is None for p in b.params):
                     continue
@@ -102,9 +198,52 @@ class _FusedOptimizer(torch.optim.Optimizer):
     def _update(self, fs, grad_scale):
         raise NotImplementedError
 
-    # state_dict: flat state is exposed per bucket
+    # -- update inside the allreduce --------------------------------------------
+    _update_kind = -1  # 0 SGD, 1 Adam: which rule the allreduce kernel applies
+
+    def shard_for_fused_update(self, device_state) -> bool:
+        """Run this optimizer's update inside the gradient allreduce (csrc/kernels/comm.cu): parameters move into
+        the symmetric window, every rank keeps 1/N of the master weights and state.  Returns False, and changes
+        nothing, when a bucket does not qualify (no window, gradients in another dtype than the parameters)."""
+        flat = self.build(device_state)
+        if self._update_kind < 0 or device_state is None or device_state.window is None or device_state.emulated:
+            return False
+        if any(fs.sharded for fs in flat):
+            return True
+        if any(fs.bucket.win_off < 0 or fs.bucket.grad.dtype != fs.flat_param.dtype or fs.steps for fs in flat):
+            return False
+        for fs in flat:
+            fs.shard(device_state, self._shard_state_keys(fs))
+            self._attach(fs)
+        return True
+
+    def _shard_state_keys(self, fs):
+        return []
+
+    def _attach(self, fs):
+        raise NotImplementedError
+
+    def _hyper(self, fs):
+        raise NotImplementedError
+
+    def push_update_hyper(self, fs) -> None:
+        """Hand the hyper-parameters of the coming step to the allreduce kernel of that bucket."""
+        import ctypes
+        h = [float(x) for x in self._hyper(fs)]
+        base.check(base.K().tipsk_comm_set_update_hyper(fs.bucket.win_off, (ctypes.c_float * len(h))(*h), len(h),
+                                                        fs.steps + 1), "set_update_hyper")
+
+    def refresh_master_from_params(self) -> None:
+        """Call after overwriting parameters from outside the optimizer (broadcast_parameters, load_state_dict):
+        the fp32 master weights are re-read from the parameters."""
+        for fs in self.build():
+            fs.refresh_master_from_params()
+
+    # state_dict: flat state is exposed per bucket, always as full-size tensors (with a sharded update this is a
+    # collective: every rank has to call it)
     def flat_state(self):
-        return [{"steps": fs.steps, **{k: v for k, v in fs.state.items()}} for fs in self.build()]
+        return [{"steps": fs.steps, **{k: fs.full(v) for k, v in fs.state.items() if k != "step_dev"}}
+                for fs in self.build()]
 
     def load_flat_state(self, states):
         for fs, s in zip(self.build(), states):
@@ -112,7 +251,7 @@ class _FusedOptimizer(torch.optim.Optimizer):
             for k, v in s.items():
                 if k == "steps":
                     continue
-                fs.state[k] = v.to(fs.master.device).clone()
+                fs.load_state(k, v)
 
 
 class FusedSGD(_FusedOptimizer):
@@ -124,6 +263,18 @@ class FusedSGD(_FusedOptimizer):
             raise ValueError("Nesterov momentum requires a momentum and zero dampening")
         defaults = dict(lr=lr, momentum=momentum, dampening=dampening, weight_decay=weight_decay, nesterov=nesterov)
         super().__init__(params, defaults, bucket_bytes, wire_dtype)
+
+    _update_kind = 0
+
+    def _shard_state_keys(self, fs):
+        return ["momentum_buffer"] if float(fs.group["momentum"]) != 0.0 else []
+
+    def _attach(self, fs):
+        fs.attach(0, fs.state.get("momentum_buffer"))
+
+    def _hyper(self, fs):
+        g = fs.group
+        return [g["lr"], g["momentum"], g["dampening"], g["weight_decay"], 1.0 if g["nesterov"] else 0.0]
 
     def _update(self, fs, grad_scale):
         g, b = fs.group, fs.bucket
@@ -161,6 +312,19 @@ class FusedAdam(_FusedOptimizer):
                         decoupled_weight_decay=decoupled_weight_decay)
         super().__init__(params, defaults, bucket_bytes, wire_dtype)
         self.capturable = capturable
+
+    _update_kind = 1
+
+    def _shard_state_keys(self, fs):
+        return ["exp_avg", "exp_avg_sq"]
+
+    def _attach(self, fs):
+        fs.attach(1, fs.state["exp_avg"], fs.state["exp_avg_sq"])
+
+    def _hyper(self, fs):
+        g = fs.group
+        return [g["lr"], g["betas"][0], g["betas"][1], g["eps"], g["weight_decay"],
+                1.0 if g["decoupled_weight_decay"] else 0.0]
 
     def _update(self, fs, grad_scale):
         g, b = fs.group, fs.bucket

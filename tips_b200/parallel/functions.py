@@ -24,8 +24,10 @@ except Exception:  # pragma: no cover
     _pickle = pickle
 
 
-def broadcast_parameters(params, root_rank: int = 0, prefix: str = "tips.bcast") -> None:
-    """Broadcast parameters (a state_dict, a list of (name, tensor) or an iterable of tensors) in place."""
+def broadcast_parameters(params, root_rank: int = 0, prefix: str = "tips.bcast", optimizer=None) -> None:
+    """Broadcast parameters (a state_dict, a list of (name, tensor) or an iterable of tensors) in place.
+    Pass the fused `optimizer` that already owns these parameters, if there is one, so that its fp32 master
+    weights follow the new values."""
     if isinstance(params, dict):
         items = sorted(params.items())
     else:
@@ -40,6 +42,8 @@ def broadcast_parameters(params, root_rank: int = 0, prefix: str = "tips.bcast")
                                           name=f"{prefix}.{name}"))
     for h in handles:
         C.synchronize(h)
+    if optimizer is not None and hasattr(optimizer, "refresh_master_from_params"):
+        optimizer.refresh_master_from_params()
 
 
 broadcast_variables = broadcast_parameters
@@ -97,6 +101,23 @@ def broadcast_optimizer_state(optimizer: torch.optim.Optimizer, root_rank: int =
                                 root_rank, name="tips.bcast_opt.meta")
         for i, (fs, (steps, keys)) in enumerate(zip(flat, meta)):
             fs.steps = steps
+            if fs.sharded:
+                # Every rank holds its own share, so there is nothing to copy unless the root has just loaded
+                # full-size tensors (a checkpoint) that the other ranks have not seen: those travel whole and
+                # every rank cuts its share out.
+                pending = broadcast_object(sorted(fs._pending_full.keys()) if C._rank() == root_rank else None,
+                                           root_rank, name=f"tips.bcast_opt.{i}.pending")
+                for k in pending:
+                    full = fs._pending_full.get(k) if C._rank() == root_rank else None
+                    if full is None:
+                        full = torch.empty(fs.layout.numel, dtype=torch.float32, device=fs.master.device)
+                    C.broadcast_(full, root_rank, name=f"tips.bcast_opt.{i}.{k}")
+                    if k == "master":
+                        fs.load_master(full)
+                    else:
+                        fs.load_state(k, full)
+                fs._pending_full = {}
+                continue
             for k in keys:
                 if k not in fs.state:
                     fs.state[k] = torch.zeros_like(fs.master)

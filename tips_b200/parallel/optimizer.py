@@ -37,7 +37,7 @@ class _DistributedMixin:
     """Behaviour mixed into a dynamic subclass of the user's optimizer class."""
 
     def _tips_setup(self, named_parameters, compression, backward_passes_per_step, op, gradient_predivide_factor,
-                    sparse_as_dense, average_aggregated_gradients, groups):
+                    sparse_as_dense, average_aggregated_gradients, groups, fused_update=None):
         _require_init()
         if op not in (C.Average, C.Sum):
             raise ValueError("op must be Average or Sum")
@@ -83,9 +83,17 @@ class _DistributedMixin:
             wire = "fp16"
         elif compression is Compression.bf16:
             wire = "bf16"
+        self._tips_update_in_allreduce = False
         if self._tips_fused:
             self._wire_dtype = wire
             self._tips_buckets = [fs.bucket for fs in self.build(dev_state)]
+            if fused_update is None:
+                fused_update = get_config().fused_update
+            if fused_update and self._tips_size > 1 and dev_state is not None and get_config().backend == "fused":
+                if op != C.Average and op != C.Sum:
+                    raise ValueError("the update inside the allreduce needs op Average or Sum")
+                self._tips_update_in_allreduce = self.shard_for_fused_update(dev_state)
+                self._tips_fs_of = {id(fs.bucket): fs for fs in self._flat}
         else:
             by_kind = {}
             for p in params:
@@ -165,6 +173,12 @@ class _DistributedMixin:
                 b.grad.mul_(post)
             b.handle = None
             return
+        if self._tips_update_in_allreduce:
+            if saved:
+                raise TipsError("sparse gradients cannot be combined with the update inside the allreduce; use "
+                                "sparse_as_dense=True", 3)
+            # the kernel that reduces this bucket also applies the step: it needs this step's hyper-parameters
+            self.push_update_hyper(self._tips_fs_of[id(b)])
         h = C._Handle()
         h.kind = "allreduce"
         h.output = b.grad
@@ -274,10 +288,16 @@ class _DistributedMixin:
 
 def DistributedOptimizer(optimizer, named_parameters=None, compression=Compression.none,
                          backward_passes_per_step=1, op=C.Average, gradient_predivide_factor=1.0,
-                         sparse_as_dense=False, average_aggregated_gradients=True, groups=None):
-    """Wrap `optimizer` so that `step()` applies gradients combined over all ranks."""
+                         sparse_as_dense=False, average_aggregated_gradients=True, groups=None, fused_update=None):
+    """Wrap `optimizer` so that `step()` applies gradients combined over all ranks.
+
+    ``fused_update`` (default: the ``fused_update`` configuration field) makes a FusedSGD / FusedAdam step run
+    inside the kernel that reduces each gradient bucket: every rank reduces its share of the bucket, updates the
+    fp32 master weights and state of that share (the only copy of them in the job) and stores the new parameters
+    into every rank's parameter buffer in symmetric memory.  The reduced gradients are then never materialised, so
+    code that reads or clips ``p.grad`` between ``synchronize()`` and ``step()`` cannot use it."""
     cls = type(optimizer.__class__.__name__, (_DistributedMixin, optimizer.__class__), {})
     optimizer.__class__ = cls
     optimizer._tips_setup(named_parameters, compression, backward_passes_per_step, op, gradient_predivide_factor,
-                          sparse_as_dense, average_aggregated_gradients, groups)
+                          sparse_as_dense, average_aggregated_gradients, groups, fused_update)
     return optimizer

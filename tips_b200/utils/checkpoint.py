@@ -23,7 +23,7 @@ def _optimizer_state(optimizer):
         return {"fused": True,
                 "flat": [{k: (v.cpu() if isinstance(v, torch.Tensor) else v) for k, v in s.items()}
                          for s in optimizer.flat_state()],
-                "masters": [fs.master.cpu() for fs in optimizer.build()],
+                "masters": [fs.full_master().cpu() for fs in optimizer.build()],
                 "param_groups": [{k: v for k, v in g.items() if k != "params"} for g in optimizer.param_groups]}
     return {"fused": False, "state_dict": optimizer.state_dict()}
 
@@ -35,9 +35,7 @@ def _load_optimizer_state(optimizer, state):
             raise TypeError("the checkpoint holds fused-optimizer state but the optimizer is not a fused one")
         optimizer.load_flat_state(state["flat"])
         for fs, m in zip(optimizer.build(), state["masters"]):
-            fs.master.copy_(m.to(fs.master.device))
-            if fs.low:
-                fs.flat_param.copy_(fs.master)
+            fs.load_master(m)
         for g, src in zip(optimizer.param_groups, state["param_groups"]):
             g.update(src)
     else:
@@ -47,12 +45,15 @@ def _load_optimizer_state(optimizer, state):
 def save_checkpoint(path: str, model: torch.nn.Module, optimizer=None, extra: Optional[dict] = None,
                     rank0_only: bool = True) -> bool:
     """Write a checkpoint. With rank0_only (default) only rank 0 writes; returns True if this rank wrote."""
+    opt_state = None
+    if optimizer is not None and any(getattr(fs, "sharded", False) for fs in getattr(optimizer, "_flat", [])):
+        opt_state = _optimizer_state(optimizer)  # assembling a sharded state is a collective: every rank takes part
     if rank0_only and runtime.is_initialized() and runtime.rank() != 0:
         return False
     payload = {"model": {k: v.detach().cpu() for k, v in model.state_dict().items()}, "extra": dict(extra or {}),
                "optimizer_class": type(optimizer).__name__ if optimizer is not None else None}
     if optimizer is not None:
-        payload["optimizer"] = _optimizer_state(optimizer)
+        payload["optimizer"] = opt_state if opt_state is not None else _optimizer_state(optimizer)
     os.makedirs(os.path.dirname(os.path.abspath(path)) or ".", exist_ok=True)
     tmp = path + ".tmp"
     torch.save(payload, tmp)

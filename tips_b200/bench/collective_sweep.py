@@ -5,6 +5,8 @@ vs NCCL on the same GPUs.  Device-timed with CUDA events on the launching stream
 
 Bus bandwidth uses the usual conventions: allreduce algbw * 2(N-1)/N, allgather and broadcast algbw * (N-1)/N
 with algbw = total bytes / time.  The roofline reference is the measured 770 GB/s peer copy per direction.
+``--ops update`` times the allreduce followed by the Adam kernel on full-size state against the single kernel that
+reduces, updates the share of the state this rank owns and stores the parameters to every rank.
 """
 from __future__ import annotations
 
@@ -67,6 +69,9 @@ def main(argv=None):
     rows = []
     max_bytes = a.max_mb << 20
     sym, sym_off = st.alloc_symmetric(max_bytes)
+    upd_max = min(max_bytes, 256 << 20)
+    if "update" in a.ops:
+        _, par_off = st.alloc_symmetric(upd_max)
     size = a.min_kb << 10
     sizes = []
     while size <= max_bytes:
@@ -112,6 +117,32 @@ def main(argv=None):
                 res["broadcast_gbs"] = nbytes / ms / 1e6
                 ms = _time(lambda: dist.broadcast(x, 0), iters)
                 res["nccl_broadcast_gbs"] = nbytes / ms / 1e6
+            if "update" in a.ops and 16 <= nbytes <= upd_max:
+                # allreduce + Adam as two kernels on full-size state, against the one kernel that reduces this
+                # rank's share, updates 1/n of the state and stores the parameters to every rank
+                shard = int(lib.tipsk_comm_update_shard_vecs(nbytes)) * (16 // es)
+                full = [torch.zeros(numel, device=dev) for _ in range(3)]
+                part = [torch.zeros(shard, device=dev) for _ in range(3)]
+                low = torch.zeros(numel, dtype=dtype, device=dev)
+                hp = (ctypes.c_float * 6)(1e-4, 0.9, 0.999, 1e-8, 0.01, 1.0)
+
+                def two_kernels():
+                    rc = lib.tipsk_allreduce(None, None, sym_off, nbytes, code, 0, 1.0, 1.0 / n, 3, stream)
+                    return rc or lib.tipsk_adam_flat_devstep(
+                        full[0].data_ptr(), low.data_ptr() if es == 2 else None, code if es == 2 else 6,
+                        sym.data_ptr(), code, full[1].data_ptr(), full[2].data_ptr(), numel, 1e-4, 0.9, 0.999, 1e-8,
+                        0.01, 2, None, 1.0, 1, stream)
+
+                res["allreduce_then_adam_ms"] = _time(_checked(lib, two_kernels), iters)
+                arr = [(ctypes.c_void_p * 1)(t.data_ptr()) for t in part]
+                rc = lib.tipsk_comm_attach_update(sym_off, nbytes, code, par_off, 1, arr[0], arr[1], arr[2])
+                rc = rc or lib.tipsk_comm_set_update_hyper(sym_off, hp, 6, 2)
+                if rc:
+                    raise RuntimeError(lib.tipsk_last_error().decode())
+                res["allreduce_adam_fused_ms"] = _time(
+                    _checked(lib, lambda: lib.tipsk_allreduce_update(sym_off, 1.0 / n, 3, stream)), iters)
+                lib.tipsk_comm_detach_update(sym_off)
+                del full, part, low
             st.check_status()
             rows.append(res)
             if rank == 0:

@@ -155,7 +155,7 @@ def run_resnet50(batch: int, steps: int, warmup: int, fused_update=None):
         opt.step()
         reader.push(loss)
 
-    ms2, _ = timed(step_e2e, steps, max(3, warmup // 2))
+    ms2, _ = timed(step_e2e, steps, max(5, warmup))
     last["loss"] = reader.drain()
     e2e = {"value": batch * tips.size() * steps / (ms2 / 1e3), "unit": "images/s", "ms_per_step": ms2 / steps,
            "h2d_bytes_per_step": pre.bytes_per_step, "d2h_bytes_per_step": 4, "last_loss": last.get("loss")}
@@ -203,7 +203,7 @@ def run_resnet50_floor(batch: int, steps: int, warmup: int):
         opt.zero_grad(set_to_none=True)
         reader.push(loss)
 
-    ms2, _ = timed(step_e2e, steps, max(3, warmup // 2))
+    ms2, _ = timed(step_e2e, steps, max(5, warmup))
     last["loss"] = reader.drain()
     e2e = {"value": batch * tips.size() * steps / (ms2 / 1e3), "unit": "images/s", "ms_per_step": ms2 / steps,
            "h2d_bytes_per_step": pre.bytes_per_step, "d2h_bytes_per_step": 4, "last_loss": last.get("loss")}
@@ -247,7 +247,7 @@ def run_ctr(batch: int, rows: int, steps: int, warmup: int, graph: bool = True, 
         ids, dense, labels = pre.get()
         reader.push(trainer.train_step(ids, dense, labels))
 
-    ms2, _ = timed(step_e2e, steps, max(3, warmup // 2))
+    ms2, _ = timed(step_e2e, steps, max(5, warmup))
     last["loss"] = reader.drain()
     trainer.check()
     e2e = {"value": batch * tips.size() * steps / (ms2 / 1e3), "unit": "samples/s", "ms_per_step": ms2 / steps,
@@ -290,7 +290,7 @@ def run_bert(batch: int, seq: int, steps: int, warmup: int, layers: int = 24, fu
         opt.step()
         reader.push(loss)
 
-    ms2, _ = timed(step_e2e, steps, max(3, warmup // 2))
+    ms2, _ = timed(step_e2e, steps, max(5, warmup))
     last["loss"] = reader.drain()
     e2e = {"value": batch * seq * tips.size() * steps / (ms2 / 1e3), "unit": "tokens/s", "ms_per_step": ms2 / steps,
            "h2d_bytes_per_step": pre.bytes_per_step, "d2h_bytes_per_step": 4, "last_loss": last.get("loss")}

@@ -23,8 +23,10 @@ def _dp_matches_single_process(rank, size, fused, passes):
     ref = _make(1234)
     make = (lambda p: FusedSGD(p, lr=0.01, momentum=0.9)) if fused else (lambda p: torch.optim.SGD(p, lr=0.01, momentum=0.9))
     opt = tips.DistributedOptimizer(make(model.parameters()), named_parameters=model.named_parameters(),
-                                    backward_passes_per_step=passes)
+                                    backward_passes_per_step=passes, fused_update=True if fused else None)
     assert type(opt).__name__ == ("FusedSGD" if fused else "SGD")  # same class name as the wrapped optimizer
+    # without a symmetric window (CPU ranks) the step cannot move into the allreduce kernel: separate update
+    assert not opt._tips_update_in_allreduce
     ropt = torch.optim.SGD(ref.parameters(), lr=0.01, momentum=0.9)
     for step in range(3):
         for k in range(passes):

@@ -18,6 +18,7 @@ SHAPES = [
     (8, 56, 56, 64, 64, 3, 1),
     (4, 28, 28, 256, 512, 1, 2),
     (4, 28, 28, 128, 128, 3, 2),
+    (32, 56, 56, 64, 64, 1, 1),   # enough tiles for the weights to stay resident in shared memory
 ]
 
 

@@ -49,6 +49,7 @@ struct ConvParams {
   int taps, cblocks;               // filter taps, 64-channel blocks of the contraction
   int accumulate;                  // 1: add the result to what the output tensor holds (TMA reduce-add store)
   int b_resident;                  // bytes of weights kept in shared memory for the whole kernel (0: streamed per stage)
+  int b_mn;                        // 1: the weight matrix is [contracted channel, tap * produced channel] (MN-major B)
   int tiles_w, tiles_h, tiles_n;   // boxes per output extent
   int tw, th, tn;                  // box extents; tw * th * tn <= 128
   int wo, ho, nb;                  // output extents (for the statistics mask)
@@ -58,7 +59,7 @@ struct ConvParams {
 
 struct ConvMaps {
   CUtensorMap a[4];  // activation phases
-  CUtensorMap b;     // weights [Cout, taps * Cin], K-major
+  CUtensorMap b;     // weights [Cout, taps * Cin], K-major; or [contracted, taps * produced] when b_mn
   CUtensorMap c;     // output
 };
 
@@ -157,8 +158,14 @@ ConvTapsKernel(const __grid_constant__ ConvMaps maps, const __grid_constant__ Co
       if (b_res) {
         MbarExpectTx(b_full, static_cast<uint32_t>(p.b_resident));
         for (int t = 0; t < p.taps; ++t)
-          for (int cb = 0; cb < p.cblocks; ++cb)
-            TmaLoad2D(resident + (t * p.cblocks + cb) * Cfg::kBBytes, &maps.b, p.tap[t].kofs + cb * kBK, 0, b_full);
+          for (int cb = 0; cb < p.cblocks; ++cb) {
+            uint8_t* dst = resident + (t * p.cblocks + cb) * Cfg::kBBytes;
+            if (p.b_mn) {  // BN/64 boxes of [64 contracted rows x 64 produced channels]
+              for (int j = 0; j < BN / 64; ++j) TmaLoad2D(dst + j * 8192, &maps.b, p.tap[t].kofs + j * 64, cb * kBK, b_full);
+            } else {
+              TmaLoad2D(dst, &maps.b, p.tap[t].kofs + cb * kBK, 0, b_full);
+            }
+          }
       }
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
         const int mt = tile / p.n_tiles, nt = tile % p.n_tiles;
@@ -177,15 +184,24 @@ ConvTapsKernel(const __grid_constant__ ConvMaps maps, const __grid_constant__ Co
             uint8_t* a_dst = smem + s * Cfg::kStageBytes;
             MbarExpectTx(&full_bar[s], stage_tx);
             TmaLoad4D(a_dst, &maps.a[tap.map], cb * kBK, w0 + tap.dw, h0 + tap.dh, n0, &full_bar[s]);
-            if (!b_res) TmaLoad2D(a_dst + Cfg::kABytes, &maps.b, tap.kofs + cb * kBK, nt * BN, &full_bar[s]);
+            if (!b_res) {
+              if (p.b_mn) {
+                for (int j = 0; j < BN / 64; ++j)
+                  TmaLoad2D(a_dst + Cfg::kABytes + j * 8192, &maps.b, tap.kofs + nt * BN + j * 64, cb * kBK, &full_bar[s]);
+              } else {
+                TmaLoad2D(a_dst + Cfg::kABytes, &maps.b, tap.kofs + cb * kBK, nt * BN, &full_bar[s]);
+              }
+            }
           }
         }
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(BN >> 3) << 17) |
-                                 (static_cast<uint32_t>(kBM >> 4) << 24);
+      // bit 16: B is MN-major (the weights in the layout the forward pass uses, contracted over their rows)
+      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (p.b_mn ? (1u << 16) : 0u) |
+                             (static_cast<uint32_t>(BN >> 3) << 17) | (static_cast<uint32_t>(kBM >> 4) << 24);
+      const uint64_t b_kstep = p.b_mn ? 128 : 2;  // 16 contraction steps further: +2048 bytes MN-major, +32 K-major
       uint32_t it = 0;
       int local = 0;
       bool ok = true;
@@ -211,9 +227,11 @@ ConvTapsKernel(const __grid_constant__ ConvMaps maps, const __grid_constant__ Co
           TcFenceAfter();
           const uint32_t a_addr = SmemAddr(smem + s * Cfg::kStageBytes);
           const uint64_t adesc  = SmemDescSw128(a_addr);
-          const uint64_t bdesc  = SmemDescSw128(b_res ? SmemAddr(resident) + kt * Cfg::kBBytes : a_addr + Cfg::kABytes);
+          const uint32_t b_addr = b_res ? SmemAddr(resident) + kt * Cfg::kBBytes : a_addr + Cfg::kABytes;
+          const uint64_t bdesc  = p.b_mn ? SmemDescMnSw128(b_addr, 8192) : SmemDescSw128(b_addr);
 #pragma unroll
-          for (int k = 0; k < kBK / 16; ++k) UmmaBf16(tmem_d, adesc + 2 * k, bdesc + 2 * k, idesc, (kt > 0 || k > 0) ? 1u : 0u);
+          for (int k = 0; k < kBK / 16; ++k)
+            UmmaBf16(tmem_d, adesc + 2 * k, bdesc + b_kstep * k, idesc, (kt > 0 || k > 0) ? 1u : 0u);
           UmmaCommit(&empty_bar[s]);
         }
         if (ok) UmmaCommit(&tmem_full[buf]);
@@ -664,7 +682,7 @@ int LaunchWgrad(const WgradMaps& maps, const WgradParams& p, int splits, cudaStr
 // Runs the tap kernel: out[view_out pixel, co] = sum over taps and 64-channel blocks.
 int RunTaps(const View* in_views, int n_views, const ConvTap* taps, int n_taps, int cin, const void* weights,
             int w_rows, int64_t w_cols, const View& out, float* stat_sum, float* stat_sq, cudaStream_t s,
-            int accumulate = 0) {
+            int accumulate = 0, int b_mn = 0) {
   TIPSK_REQUIRE(n_taps >= 1 && n_taps <= kMaxTaps, "conv: 1..9 filter taps are supported");
   TIPSK_REQUIRE(cin % 64 == 0, "conv: the contracted channel count must be a multiple of 64");
   TIPSK_REQUIRE(w_rows % 64 == 0, "conv: the produced channel count must be a multiple of 64");
@@ -684,8 +702,11 @@ int RunTaps(const View* in_views, int n_views, const ConvTap* taps, int n_taps, 
     if (rc) return rc;
   }
   for (int i = n_views; i < 4; ++i) maps.a[i] = maps.a[0];
-  rc = MakeTmap2D(&maps.b, weights, w_rows, w_cols, bn);
+  // K-major: [produced channel, tap * contracted] read in boxes of bn rows; MN-major: [contracted channel,
+  // tap * produced] read in boxes of 64 rows x 64 produced channels
+  rc = b_mn ? MakeTmap2D(&maps.b, weights, cin, w_cols, 64) : MakeTmap2D(&maps.b, weights, w_rows, w_cols, bn);
   if (rc) return rc;
+  p.b_mn = b_mn;
   rc = MapOf(&maps.c, out, box);
   if (rc) return rc;
   p.error = ConvErrorWord();
@@ -870,12 +891,29 @@ int tipsk_conv2d_fwd(const void* x, const void* wgt, void* y, int n, int h, int 
 
 /* dx[n, h, w, cin] = data gradient; wgt_t is the weight permuted to [cin, r, s, cout].  With `accumulate` the
  * gradient is added to what dx already holds (the gradient of another consumer of the same activation). */
+static int DgradImpl(const void* dy, const void* wgt_t, void* dx, int n, int h, int w, int cin, int cout, int r, int s,
+                     int stride, int pad, int accumulate, int ohwi, void* stream);
+
 int tipsk_conv2d_dgrad(const void* dy, const void* wgt_t, void* dx, int n, int h, int w, int cin, int cout, int r,
                        int s, int stride, int pad, int accumulate, void* stream) {
+  return DgradImpl(dy, wgt_t, dx, n, h, w, cin, cout, r, s, stride, pad, accumulate, 0, stream);
+}
+
+/* The same data gradient from the weights as the forward pass takes them, wgt[cout, r, s, cin]: the kernel
+ * contracts over the rows of that matrix (MN-major B operand), so no transposed copy of the weights is made. */
+int tipsk_conv2d_dgrad_ohwi(const void* dy, const void* wgt, void* dx, int n, int h, int w, int cin, int cout, int r,
+                            int s, int stride, int pad, int accumulate, void* stream) {
+  return DgradImpl(dy, wgt, dx, n, h, w, cin, cout, r, s, stride, pad, accumulate, 1, stream);
+}
+
+static int DgradImpl(const void* dy, const void* wgt_t, void* dx, int n, int h, int w, int cin, int cout, int r, int s,
+                     int stride, int pad, int accumulate, int ohwi, void* stream) {
   TIPSK_REQUIRE(tipsk_conv2d_supported(cin, cout, r, s, stride, pad), "conv2d_dgrad: unsupported shape");
   const int ho = (h + 2 * pad - r) / stride + 1, wo = (w + 2 * pad - s) / stride + 1;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const int64_t w_cols = static_cast<int64_t>(r) * s * cout;
+  // columns of the weight matrix and the width of one tap in it
+  const int tap_cols   = ohwi ? cin : cout;
+  const int64_t w_cols = static_cast<int64_t>(r) * s * tap_cols;
   if (stride == 1) {
     ConvTap taps[kMaxTaps];
     int nt = 0;
@@ -883,12 +921,12 @@ int tipsk_conv2d_dgrad(const void* dy, const void* wgt_t, void* dx, int n, int h
       for (int fs = 0; fs < s; ++fs) {
         ConvTap t{};
         t.dh = static_cast<int16_t>(pad - fr); t.dw = static_cast<int16_t>(pad - fs); t.map = 0;
-        t.kofs = (fr * s + fs) * cout;
+        t.kofs = (fr * s + fs) * tap_cols;
         taps[nt++] = t;
       }
     View in  = r == 1 ? FlatView(dy, n, ho, wo, cout) : FullView(dy, n, ho, wo, cout);
     View out = r == 1 ? FlatView(dx, n, h, w, cin) : FullView(dx, n, h, w, cin);
-    return RunTaps(&in, 1, taps, nt, cout, wgt_t, cin, w_cols, out, nullptr, nullptr, st, accumulate);
+    return RunTaps(&in, 1, taps, nt, cout, wgt_t, cin, w_cols, out, nullptr, nullptr, st, accumulate, ohwi);
   }
   // stride 2: the input pixels of parity class (bh, bw) receive the taps with (b + pad - f) even
   const View in = FullView(dy, n, ho, wo, cout);
@@ -906,14 +944,14 @@ int tipsk_conv2d_dgrad(const void* dy, const void* wgt_t, void* dx, int n, int h
         if ((bw + pad - fs) & 1) continue;
         ConvTap t{};
         t.dh = static_cast<int16_t>((bh + pad - fr) / 2); t.dw = static_cast<int16_t>((bw + pad - fs) / 2); t.map = 0;
-        t.kofs = (fr * s + fs) * cout;
+        t.kofs = (fr * s + fs) * tap_cols;
         taps[nt++] = t;
       }
     }
     if (nt == 0) continue;
     const View out = PhaseView(dx, n, h, w, cin, bh, bw);
     if (out.w <= 0 || out.h <= 0) continue;
-    int rc = RunTaps(&in, 1, taps, nt, cout, wgt_t, cin, w_cols, out, nullptr, nullptr, st, accumulate);
+    int rc = RunTaps(&in, 1, taps, nt, cout, wgt_t, cin, w_cols, out, nullptr, nullptr, st, accumulate, ohwi);
     if (rc) return rc;
   }
   return 0;

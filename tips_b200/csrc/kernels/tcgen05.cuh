@@ -138,6 +138,14 @@ using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, voi
                               CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
 inline EncodeFn GetEncodeFn() {
+  // The driver call that encodes a tensor map needs this thread to have a current context.  A thread that has
+  // made no runtime call yet (the autograd engine's worker on its first node) has none: the encode then fails
+  // with CUDA_ERROR_INVALID_CONTEXT.  cudaFree(nullptr) binds the primary context of the current device.
+  static thread_local bool bound = false;
+  if (!bound) {
+    cudaFree(nullptr);
+    bound = true;
+  }
   static EncodeFn fn = nullptr;
   static std::once_flag once;
   std::call_once(once, [] {

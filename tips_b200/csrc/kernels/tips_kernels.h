@@ -182,6 +182,9 @@ int tipsk_conv2d_fwd(const void* x, const void* wgt, void* y, int n, int h, int 
                      int stride, int pad, float* stat_sum, float* stat_sq, void* stream);
 int tipsk_conv2d_dgrad(const void* dy, const void* wgt_t, void* dx, int n, int h, int w, int cin, int cout, int r,
                        int s, int stride, int pad, int accumulate, void* stream);
+/* The same from the forward weight layout wgt[cout, r, s, cin] (no transposed copy of the weights). */
+int tipsk_conv2d_dgrad_ohwi(const void* dy, const void* wgt, void* dx, int n, int h, int w, int cin, int cout, int r,
+                            int s, int stride, int pad, int accumulate, void* stream);
 int tipsk_conv2d_wgrad(const void* x, const void* dy, float* dw, int n, int h, int w, int cin, int cout, int r, int s,
                        int stride, int pad, void* stream);
 int tipsk_conv_status(void);

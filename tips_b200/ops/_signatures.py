@@ -79,6 +79,7 @@ _PROTOS = {
     "tipsk_conv2d_supported": (I, [I, I, I, I, I, I]),
     "tipsk_conv2d_fwd": (I, [P, P, P, I, I, I, I, I, I, I, I, I, P, P, P]),
     "tipsk_conv2d_dgrad": (I, [P, P, P, I, I, I, I, I, I, I, I, I, I, P]),
+    "tipsk_conv2d_dgrad_ohwi": (I, [P, P, P, I, I, I, I, I, I, I, I, I, I, P]),
     "tipsk_conv2d_wgrad": (I, [P, P, P, I, I, I, I, I, I, I, I, I, P]),
     "tipsk_conv_status": (I, []),
     "tipsk_stem_geometry": (I, [I, I, P, P, P, P]),

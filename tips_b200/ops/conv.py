@@ -12,12 +12,18 @@ The reference has no convolution of its own: its evaluated model is a TensorFlow
 from __future__ import annotations
 
 import math
+import os
 
 import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
 from . import base
+
+
+# TIPS_CONV_DGRAD_TRANSPOSED_COPY=1: give the data gradient a transposed copy of the weights (K-major operand)
+# instead of the forward weights themselves; kept for A/B measurements.
+_DGRAD_TRANSPOSED_COPY = os.environ.get("TIPS_CONV_DGRAD_TRANSPOSED_COPY", "0") == "1"
 
 
 def _is_stem(x, weight, stride, padding) -> bool:
@@ -63,16 +69,22 @@ def conv2d_dgrad(dy, weight, x_shape, stride, padding, into=None):
     n, cin, h, w = x_shape
     cout, r, s, _ = weight.shape
     dyc = _nhwc(dy)
-    wt = weight.permute(3, 1, 2, 0).contiguous()  # [C_in, R, S, C_out]
     if into is not None:
         assert tuple(into.shape) == tuple(x_shape) and into.is_contiguous(memory_format=torch.channels_last)
         dx = into
     else:
         dx = torch.empty(x_shape, dtype=dy.dtype, device=dy.device, memory_format=torch.channels_last)
     launches = 1 if stride == 1 else (1 if r == 1 else 4)
-    base.check(base.K().tipsk_conv2d_dgrad(
-        dyc.data_ptr(), wt.data_ptr(), dx.data_ptr(), n, h, w, cin, cout, r, s, stride, padding,
-        1 if into is not None else 0, base.stream()), "conv2d_dgrad")
+    if _DGRAD_TRANSPOSED_COPY:
+        wt = weight.permute(3, 1, 2, 0).contiguous()  # [C_in, R, S, C_out], K-major for the contraction over C_out
+        base.check(base.K().tipsk_conv2d_dgrad(
+            dyc.data_ptr(), wt.data_ptr(), dx.data_ptr(), n, h, w, cin, cout, r, s, stride, padding,
+            1 if into is not None else 0, base.stream()), "conv2d_dgrad")
+    else:
+        # the forward weights as they are: the kernel contracts over their rows (MN-major operand)
+        base.check(base.K().tipsk_conv2d_dgrad_ohwi(
+            dyc.data_ptr(), weight.contiguous().data_ptr(), dx.data_ptr(), n, h, w, cin, cout, r, s, stride, padding,
+            1 if into is not None else 0, base.stream()), "conv2d_dgrad")
     base.count_launches(launches - 1)
     return dx
 

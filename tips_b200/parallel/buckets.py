@@ -32,7 +32,9 @@ class Bucket:
         off = 0
         for p in params:
             self.offsets.append(off)
-            off += (p.numel() + 7) // 8 * 8  # keep every tensor 16-byte aligned for 2-byte wire types
+            # every tensor starts on a 128-byte boundary (2-byte types): parameters are views of the flat buffer, and
+            # a TMA box row of a weight matrix that straddles two 128-byte lines costs an extra sector per row
+            off += (p.numel() + 63) // 64 * 64
         self.numel = max(off, 8)
         self.grad: Optional[torch.Tensor] = None      # flat [numel] wire dtype
         self.win_off: int = -1

@@ -255,3 +255,29 @@ def test_bert_layer_matches_plain_pytorch():
     ga, gb = x.grad.float(), xr.grad
     assert float((ga * gb).sum() / (ga.norm() * gb.norm())) > 0.995
     assert (ga - gb).abs().max() <= 0.1 * max(1.0, float(gb.abs().max()))
+
+
+def test_make_subgraph_replays_our_kernels():
+    """A function made of this package's kernels, captured once and replayed on new inputs."""
+    from tips_b200.ops import norm
+    from tips_b200.utils.misc import executing_eagerly, make_subgraph
+    dev = torch.device("cuda", 0)
+    ln = norm.LayerNorm(1024).to(dev).to(torch.bfloat16)
+    seen = []
+
+    def fn(x):
+        seen.append(executing_eagerly())
+        with torch.no_grad():
+            return ln(x) * 2
+
+    x0 = torch.randn(512, 1024, device=dev).to(torch.bfloat16)
+    g = make_subgraph(fn, x0)
+    assert seen[-1] is False and seen[0] is True  # warm-up ran eagerly, the last call was the capture
+    for seed in (1, 2):
+        torch.manual_seed(seed)
+        x = torch.randn(512, 1024, device=dev).to(torch.bfloat16)
+        out = g(x).clone()
+        with torch.no_grad():
+            ref = ln(x) * 2
+        assert torch.equal(out, ref)
+    assert g.replays == 2

@@ -32,3 +32,23 @@ def test_ownership_matches_the_kernel_rule():
 def test_rejects_partial_vectors():
     with pytest.raises(ValueError):
         ShardLayout(12, 2, 2, 2048)
+
+
+def test_misc_helpers_without_a_gpu():
+    from tips_b200.utils import misc
+    assert misc.executing_eagerly()
+    calls = []
+
+    @misc.cache
+    def f(a, b=1):
+        calls.append((a, b))
+        return a + b
+
+    assert f(1, b=2) == 3 and f(1, b=2) == 3 and len(calls) == 1
+    ps = [torch.nn.Parameter(torch.zeros(1)) for _ in range(3)]
+    assert misc.refs_to_vars(misc.vars_to_refs(ps), ps) == ps
+
+    def g(x):
+        return x * 2
+
+    assert misc.make_subgraph(g, torch.ones(3)) is g  # CPU tensors: the function itself

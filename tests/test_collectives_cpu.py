@@ -113,3 +113,29 @@ def test_fusion_and_global_order():
 
 def test_stall_detector_aborts_the_tensor():
     run_ranks(_stall, 2, env={"TIPS_STALL_ABORT_MS": "1500", "TIPS_STALL_WARN_MS": "500"})
+
+
+def _groups(rank, size):
+    import tips_b200 as tips
+    g = tips.Group([3, 1, 1])           # unsorted, with a duplicate: normalised to [1, 3]
+    h = tips.Group(range(size))
+    assert g.size == 2 and g.world_ranks == [1, 3]
+    assert h.size == size and h.rank == rank
+    if rank in (1, 3):
+        assert g.is_member and g.rank == (0 if rank == 1 else 1)
+        assert g.to_world_rank(g.rank) == rank
+        g.barrier()
+        assert g.allgather_object({"r": rank}) == [{"r": 1}, {"r": 3}]
+        assert g.allreduce(rank) == 4.0
+    else:
+        assert not g.is_member and g.rank == -1
+        with pytest.raises(tips.TipsError):
+            g.barrier()
+    assert h.allreduce(1.0) == float(size)
+    with pytest.raises(tips.TipsError):
+        tips.Group([0, size])           # out of range
+    tips.barrier()
+
+
+def test_rank_subgroups():
+    run_ranks(_groups, 4)

@@ -13,6 +13,7 @@ from .parallel.collectives import (Average, Max, Min, Product, Sum, allgather, a
                                    broadcast_async, broadcast_async_, grouped_allreduce, poll, sparse_allreduce,
                                    synchronize)
 from .parallel.compression import Compression
+from .parallel.group import Group
 from .parallel.optimizer import DistributedOptimizer
 from .parallel.functions import (allgather_object, broadcast_object, broadcast_object_fn, broadcast_optimizer_state,
                                  broadcast_parameters, broadcast_variables, metric_average, allreduce_gradients,

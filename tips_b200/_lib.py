@@ -66,6 +66,13 @@ def core() -> ctypes.CDLL:
     lib.tips_handle_output.restype = c_void_p
     lib.tips_host_allgather.argtypes = [c_void_p, c_int64, c_void_p, c_int64, POINTER(c_int64)]
     lib.tips_host_broadcast.argtypes = [c_void_p, c_int64, c_int]
+    lib.tips_group_new.argtypes = [POINTER(ctypes.c_int32), c_int]
+    lib.tips_group_new.restype = c_int64
+    for fn in (lib.tips_group_size, lib.tips_group_rank):
+        fn.argtypes = [c_int64]
+    lib.tips_group_to_world.argtypes = [c_int64, c_int]
+    lib.tips_group_barrier.argtypes = [c_int64, c_int]
+    lib.tips_group_allgather.argtypes = [c_int64, c_void_p, c_int64, c_void_p, c_int64, POINTER(c_int64), c_int]
     lib.tips_set_fusion_threshold.argtypes = [c_int64]
     lib.tips_set_device_executor.argtypes = [c_void_p]
     lib.tips_take_negotiated_order.argtypes = [c_char_p, c_int]

@@ -130,6 +130,63 @@ int tips_host_allgather(const void* in, int64_t n, void* out, int64_t max_n, int
   });
 }
 
+// ---- sub-groups of ranks (the reference's MpiGroup, tips/core/mpi_group.h:15-96) ----
+int64_t tips_group_new(const int32_t* world_ranks, int n) {
+  int64_t id = -1;
+  int rc = Guard([&] {
+    if (!Context::Global().initialized()) return Fail(kPrecondition, "tips is not initialised");
+    if (n < 1 || !world_ranks) return Fail(kInvalidArgument, "a group needs at least one rank");
+    std::vector<int> ranks(world_ranks, world_ranks + n);
+    for (int r : ranks)
+      if (r < 0 || r >= Context::Global().size()) return Fail(kInvalidArgument, "group rank out of range");
+    id = static_cast<int64_t>(Context::Global().NewGroup(ranks)->id());
+    return 0;
+  });
+  return rc == 0 ? id : rc;
+}
+
+static Group* GroupOf(int64_t id) {
+  if (!Context::Global().initialized() || id < 0) return nullptr;
+  return Context::Global().FindGroup(static_cast<uint64_t>(id));
+}
+
+int tips_group_size(int64_t id) {
+  Group* g = GroupOf(id);
+  return g ? g->size() : -1;
+}
+int tips_group_rank(int64_t id) {  // -1 when this process is not a member
+  Group* g = GroupOf(id);
+  return g ? g->rank() : -1;
+}
+int tips_group_to_world(int64_t id, int group_rank) {
+  Group* g = GroupOf(id);
+  return (g && group_rank >= 0 && group_rank < g->size()) ? g->ToWorldRank(group_rank) : -1;
+}
+int tips_group_barrier(int64_t id, int timeout_ms) {
+  return Guard([&] {
+    Group* g = GroupOf(id);
+    if (!g) return Fail(kInvalidArgument, "unknown group");
+    Status st = g->Barrier(timeout_ms);
+    return st.ok() ? 0 : Fail(st);
+  });
+}
+int tips_group_allgather(int64_t id, const void* in, int64_t n, void* out, int64_t max_n, int64_t* out_sizes,
+                         int timeout_ms) {
+  return Guard([&] {
+    Group* g = GroupOf(id);
+    if (!g) return Fail(kInvalidArgument, "unknown group");
+    std::vector<std::string> all;
+    Status st = g->AllgatherBytes(std::string(static_cast<const char*>(in), n), &all, timeout_ms);
+    if (!st.ok()) return Fail(st);
+    for (size_t r = 0; r < all.size(); ++r) {
+      if (static_cast<int64_t>(all[r].size()) > max_n) return Fail(kInvalidArgument, "allgather output too small");
+      memcpy(static_cast<char*>(out) + r * max_n, all[r].data(), all[r].size());
+      out_sizes[r] = static_cast<int64_t>(all[r].size());
+    }
+    return 0;
+  });
+}
+
 int tips_host_broadcast(void* data, int64_t n, int root) {
   return Guard([&] {
     if (!Context::Global().initialized()) return Fail(kPrecondition, "tips is not initialised");

@@ -260,6 +260,13 @@ Group* Context::NewGroup(const std::vector<int>& world_ranks) {
   return groups_.back().get();
 }
 
+Group* Context::FindGroup(uint64_t id) {
+  if (id == 0) return world_.get();
+  for (auto& g : groups_)
+    if (g->id() == id) return g.get();
+  return nullptr;
+}
+
 Status Context::BroadcastBytes(std::string* inout, int root, int timeout_ms) {
   std::vector<std::string> all;
   Status st = AllgatherBytes(rank_ == root ? *inout : std::string(), &all, timeout_ms);

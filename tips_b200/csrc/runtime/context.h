@@ -99,6 +99,8 @@ class Context {
   // Collective over the world: every rank calls it with the same list, in
   // the same order relative to other NewGroup calls.
   Group* NewGroup(const std::vector<int>& world_ranks);
+  // The group created with that id by NewGroup (0 = the world), or null.
+  Group* FindGroup(uint64_t id);
 
   // Host collectives over the world group.
   Status Barrier(int timeout_ms = -1) { return world_->Barrier(timeout_ms); }

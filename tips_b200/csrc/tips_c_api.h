@@ -41,6 +41,18 @@ int tips_barrier(void);
 int tips_host_allgather(const void* in, int64_t n, void* out, int64_t max_n, int64_t* out_sizes);
 int tips_host_broadcast(void* data, int64_t n, int root);
 
+/* ---- sub-groups of ranks ------------------------------------------------ */
+/* Collective over the world: every rank calls it with the same list, in the same order relative to other
+ * tips_group_new calls.  Returns the group id (> 0), or a negative error.  Id 0 is the world. */
+int64_t tips_group_new(const int32_t* world_ranks, int n);
+int tips_group_size(int64_t id);
+int tips_group_rank(int64_t id);                     /* -1: this process is not a member */
+int tips_group_to_world(int64_t id, int group_rank);
+/* Members only: */
+int tips_group_barrier(int64_t id, int timeout_ms);
+int tips_group_allgather(int64_t id, const void* in, int64_t n, void* out, int64_t max_n, int64_t* out_sizes,
+                         int timeout_ms);
+
 /* ---- engine options ---------------------------------------------------- */
 int tips_set_fusion_threshold(int64_t bytes);
 int tips_set_cycle_time_ms(int ms);

@@ -149,8 +149,17 @@ def test_allreduce_fused_with_optimizer_step(comm4, dtype, kind, numel):
     n = 4
     es = torch.empty((), dtype=dtype).element_size()
     nbytes = numel * es
+    # canary words before, between and after the two buffers: the kernel must not write outside them
+    guards = []
+    _, g0 = st.alloc_symmetric(256)
     _, goff = st.alloc_symmetric(nbytes)
+    _, g1 = st.alloc_symmetric(256)
     _, poff = st.alloc_symmetric(nbytes)
+    _, g2 = st.alloc_symmetric(256)
+    for w in st.windows:
+        for off in (g0, g1, g2):
+            w[off:off + 256].fill_(0xA5)
+            guards.append(w[off:off + 256])
     grads = [w[goff:goff + nbytes].view(dtype) for w in st.windows]
     params = [w[poff:poff + nbytes].view(dtype) for w in st.windows]
     torch.manual_seed(numel + es)
@@ -190,6 +199,7 @@ def test_allreduce_fused_with_optimizer_step(comm4, dtype, kind, numel):
     else:
         assert torch.allclose(lay.assemble(torch.stack(s1)), ref_state["v"], atol=1e-6, rtol=1e-4)
     assert lib.tipsk_comm_update_launches(goff) == 3
+    assert all(bool((g == 0xA5).all()) for g in guards)
     lib.tipsk_comm_detach_update(goff)
     assert lib.tipsk_comm_update_attached(goff, nbytes) == 0
 

@@ -46,6 +46,33 @@ def _conv(cin, cout, k, stride=1, padding=0):
     return Conv2d(cin, cout, k, stride=stride, padding=padding)
 
 
+class _StatsArena:
+    """One zeroed fp32 buffer per forward pass from which every conv + batch-norm pair takes its [2, C] slot for the
+    epilogue statistics: one fill kernel per step instead of one per layer."""
+
+    def __init__(self):
+        self.buf = None
+        self.off = 0
+
+    def begin(self, floats: int, device) -> None:
+        self.buf = torch.zeros(floats, dtype=torch.float32, device=device)
+        self.off = 0
+
+    def end(self) -> None:
+        self.buf = None
+
+    def take(self, channels: int, device) -> torch.Tensor:
+        n = 2 * channels
+        if self.buf is None or self.buf.device != device or self.off + n > self.buf.numel():
+            return torch.zeros(2, channels, dtype=torch.float32, device=device)
+        v = self.buf[self.off:self.off + n].view(2, channels)
+        self.off += n
+        return v
+
+
+_ARENA = _StatsArena()
+
+
 def _conv_bn(conv, bn, x, residual=None, passthrough=False):
     """bn(conv(x)) (+ residual, ReLU); in training the convolution's epilogue hands the batch statistics to the
     normalisation, which then needs no reduction pass of its own.  With `passthrough` the result is a pair
@@ -53,7 +80,7 @@ def _conv_bn(conv, bn, x, residual=None, passthrough=False):
     the convolution's data-gradient kernel."""
     if (isinstance(conv, Conv2d) and isinstance(bn, BatchNorm2d) and bn.training
             and _conv_supported(x, conv.weight, conv.stride, conv.padding)):
-        stats = torch.zeros(2, conv.out_channels, dtype=torch.float32, device=x.device)
+        stats = _ARENA.take(conv.out_channels, x.device)
         if passthrough:
             y, alias = conv2d_passthrough(x, conv.weight, conv.stride, conv.padding, stats)
             return bn(y, residual=residual, stats=stats), alias
@@ -91,6 +118,7 @@ class Bottleneck(nn.Module):
 class ResNet50(nn.Module):
     def __init__(self, num_classes=1000, layers=(3, 4, 6, 3), width=64):
         super().__init__()
+        self._stat_floats = None  # size of the per-forward statistics arena, counted on first use
         self.conv1 = _conv(3, width, 7, stride=2, padding=3)
         self.bn1 = _NORM(width, relu=True)
         self.maxpool = nn.MaxPool2d(3, stride=2, padding=1) if _LIBRARY_CONV else MaxPool3x3S2()
@@ -110,8 +138,15 @@ class ResNet50(nn.Module):
                 nn.init.kaiming_normal_(m.weight, mode="fan_out", nonlinearity="relu")  # Conv2d does the same itself
 
     def forward(self, x):
-        x = self.maxpool(_conv_bn(self.conv1, self.bn1, x))
-        x = self.blocks(x)
+        if self.training and x.is_cuda:
+            if self._stat_floats is None:
+                self._stat_floats = sum(2 * m.num_features for m in self.modules() if isinstance(m, BatchNorm2d))
+            _ARENA.begin(self._stat_floats, x.device)
+        try:
+            x = self.maxpool(_conv_bn(self.conv1, self.bn1, x))
+            x = self.blocks(x)
+        finally:
+            _ARENA.end()
         x = torch.flatten(self.avgpool(x), 1)
         return self.fc(x)
 

@@ -256,12 +256,14 @@ void Context::Finalize() {
 Group* Context::NewGroup(const std::vector<int>& world_ranks) {
   TIPS_CHECK(initialized_);
   for (int r : world_ranks) TIPS_CHECK(r >= 0 && r < size_) << "group rank out of range: " << r;
+  std::lock_guard<std::mutex> lock(groups_mu_);
   groups_.emplace_back(new Group(next_group_id_++, world_ranks, rank_));
   return groups_.back().get();
 }
 
 Group* Context::FindGroup(uint64_t id) {
   if (id == 0) return world_.get();
+  std::lock_guard<std::mutex> lock(groups_mu_);
   for (auto& g : groups_)
     if (g->id() == id) return g.get();
   return nullptr;

@@ -135,6 +135,7 @@ class Context {
   int host_timeout_ms_{300000};
   std::unique_ptr<Group> world_;
   std::vector<std::unique_ptr<Group>> groups_;
+  std::mutex groups_mu_;  // guards groups_ and next_group_id_
   uint64_t next_group_id_{1};
 
   // Leader-side state of the gather service: (group id, seq) -> arrivals.

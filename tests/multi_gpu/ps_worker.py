@@ -26,7 +26,7 @@ def main():
             allsh = tips.allgather(shard.reshape(1, -1)).reshape(n, t.rows_per_shard, dim)
             w = torch.zeros(t.rows_per_shard * n, dim, device=dev)
             for r in range(n):
-                w[r::n] = allsh[r]
+                w[t.global_ids(f, r, device=dev)] = allsh[r]
             out.append(w[:rows].clone())
         return out
     ws = gather_tables()

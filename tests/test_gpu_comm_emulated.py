@@ -222,3 +222,42 @@ def test_bounded_wait_reports_timeout(comm4):
     torch.cuda.synchronize()
     st.check_status()
     assert torch.equal(o[0], torch.full((100,), 4.0, device=st.device))
+
+
+def test_optimizer_step_raises_after_a_device_wait_ran_out(comm4):
+    """A kernel that gave up on a peer must stop the training loop: DistributedOptimizer.step() raises TipsError
+    (code 5) instead of applying gradients that were never combined, and keeps raising until the collectives are
+    reset.  The wait runs out on a flag that nothing sets; no fault is injected on the device."""
+    import os
+    import tips_b200 as tips
+    from tips_b200.ops.optim import FusedSGD
+    from tips_b200.runtime import TipsError
+    st, lib = comm4
+    os.environ.setdefault("RANK", "0")
+    os.environ.setdefault("WORLD_SIZE", "1")
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    tips.init(device=False)
+    try:
+        model = torch.nn.Linear(64, 64).to(st.device)
+        opt = tips.DistributedOptimizer(FusedSGD(model.parameters(), lr=0.1))
+        model(torch.ones(4, 64, device=st.device)).sum().backward()
+        opt.step()                                        # healthy step
+        w0 = model.weight.detach().clone()
+        lib.tipsk_comm_set_budget_ms(200)
+        _check(lib, lib.tipsk_comm_wait_never(3, torch.cuda.current_stream().cuda_stream))
+        torch.cuda.synchronize()
+        model(torch.ones(4, 64, device=st.device)).sum().backward()
+        with pytest.raises(TipsError) as e:
+            opt.step()
+        assert e.value.code == 5 and "timed out" in str(e.value)
+        assert torch.equal(model.weight.detach(), w0)     # the update was not applied
+        with pytest.raises(TipsError):
+            tips.parallel.collectives._check_device_status()
+        _check(lib, lib.tipsk_comm_reset())
+        opt.reset()
+        lib.tipsk_comm_set_budget_ms(2000)
+        model(torch.ones(4, 64, device=st.device)).sum().backward()
+        opt.step()
+        assert not torch.equal(model.weight.detach(), w0)
+    finally:
+        tips.shutdown()

@@ -8,17 +8,8 @@ pytestmark = pytest.mark.gpu
 
 def _dense_tables(table, fields, rows, dim):
     """Reassemble the global [rows, dim] tables (and Adagrad state) from the shards."""
-    n = table.size
-    out, state = [], []
-    for f in range(fields):
-        w = torch.zeros(table.rows_per_shard * n, dim, device=table.device)
-        s = torch.zeros_like(w)
-        for r in range(n):
-            w[r::n] = table.local_shard(f, rank=r)
-            if table.has_state:
-                s[r::n] = table.local_shard(f, rank=r, state=True)
-        out.append(w[:rows].clone())
-        state.append(s[:rows].clone())
+    out = [table.dense_table(f) for f in range(fields)]
+    state = [table.dense_table(f, state=True) if table.has_state else torch.zeros_like(out[f]) for f in range(fields)]
     return out, state
 
 
@@ -96,6 +87,67 @@ def test_pull_push_emulated_ranks():
         assert t1_vals.abs().sum() > 0
     finally:
         device.teardown(st)
+
+
+@pytest.mark.parametrize("ranks", [2, 4, 8])
+def test_push_with_mostly_duplicate_ids_emulated(ranks):
+    """Three synchronous steps on 2, 4 and 8 emulated ranks with ids drawn from 40 hot rows for 70 % of the batch
+    (so most of every batch is duplicates, within a rank and across ranks): the tables equal the dense model, the
+    number of rows sent to owners is the number of distinct ids per rank, not the batch size."""
+    from tips_b200.config import set_config
+    from tips_b200.parallel import device
+    from tips_b200.ps.gpu import ShardedEmbedding
+    set_config(symm_window_bytes=1 << 20, device_wait_budget_ms=2000, comm_blocks=8)
+    st = device.setup(emulate_ranks=ranks)
+    try:
+        dev = st.device
+        fields, rows, dim, batch = 3, 2503, 64, 768
+        t = ShardedEmbedding(fields, rows, dim, optimizer="adagrad", lr=0.05, init_scale=0.1, seed=21,
+                             expected_batch=batch, device=dev)
+        ws, ss = _dense_tables(t, fields, rows, dim)
+        torch.manual_seed(7)
+        distinct = 0
+        for step in range(3):
+            ids = []
+            for r in range(ranks):
+                hot = torch.randint(0, 40, (batch, fields), device=dev)
+                cold = torch.randint(0, rows, (batch, fields), device=dev)
+                ids.append(torch.where(torch.rand(batch, fields, device=dev) < 0.7, hot, cold))
+                distinct += sum(int(ids[-1][:, f].unique().numel()) for f in range(fields))
+            outs = t.pull(ids, dtype=torch.float32)
+            for r in range(ranks):
+                ref = torch.cat([ws[f][ids[r][:, f]] for f in range(fields)], dim=1)
+                assert torch.allclose(outs[r], ref, atol=3e-4, rtol=1e-4)
+            grads = [torch.randn(batch, fields * dim, device=dev).to(torch.bfloat16) for _ in range(ranks)]
+            t.push(ids, grads, grad_scale=1.0 / ranks)
+            _reference_update(ws, ss, ids, [g.float() / ranks for g in grads], "adagrad", 0.05, t.eps, dim)
+        t.check()
+        st.check_status()
+        sent, remote = t.traffic()
+        assert sent == distinct, (sent, distinct)
+        assert 0 < remote < sent
+        assert distinct < 0.6 * 3 * ranks * batch * fields
+        got, got_s = _dense_tables(t, fields, rows, dim)
+        for f in range(fields):
+            assert torch.allclose(got[f], ws[f], atol=3e-4, rtol=1e-4)
+            assert torch.allclose(got_s[f], ss[f], atol=1e-3, rtol=1e-4)
+    finally:
+        device.teardown(st)
+
+
+def test_hot_rows_are_spread_over_the_ranks():
+    """The smallest ids of every field (the most frequent under a Zipf distribution) must not share an owner."""
+    from tips_b200.ops import base
+    import ctypes
+    lib = base.K()
+    for n in (2, 4, 8):
+        counts = [0] * n
+        for f in range(26):
+            for i in range(4):
+                o, l = ctypes.c_int32(), ctypes.c_int64()
+                assert lib.tipsk_ps_place(f, i, n, ctypes.byref(o), ctypes.byref(l)) == 0
+                counts[o.value] += 1
+        assert max(counts) - min(counts) <= 2, counts
 
 
 def test_ctr_trainer_loss_decreases():

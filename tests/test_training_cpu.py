@@ -153,12 +153,69 @@ def _elastic_and_resume(rank, size, tmp):
     assert ub.params["steps"] == 6
     ue = elastic.UpdateEpochStateCallback(state)
     ue.on_train_begin()
-    ue.on_epoch_end(state.epoch)
+    ue.on_epoch_end(0)                                       # first epoch of the restarted loop
     assert state.epoch == 2
 
 
 def test_elastic_state_and_resume(tmp_path):
     run_ranks(_elastic_and_resume, 2, str(tmp_path))
+
+
+def _elastic_retry(rank, size):
+    """A step fails on the host (rank 1's request to the coordinator is dropped, so the tensor stalls on rank 0 and
+    times out on rank 1); elastic.run resets the collectives, rolls back to the last commit and finishes the run
+    with the weights of an undisturbed run, identical on every rank."""
+    import ctypes
+    import tips_b200 as tips
+    from tips_b200 import _lib, elastic
+    tips.set_config(collective_timeout_s=4.0)
+
+    def make():
+        torch.manual_seed(7)
+        m = torch.nn.Linear(6, 3)
+        return m, tips.DistributedOptimizer(torch.optim.SGD(m.parameters(), lr=0.05, momentum=0.9))
+
+    def data(step, r):
+        g = torch.Generator().manual_seed(100 * step + r)
+        return torch.randn(5, 6, generator=g)
+
+    model, opt = make()
+    state = elastic.State(model, opt)
+    failures = {"left": 1, "seen": 0}
+
+    @elastic.run
+    def train(state):
+        for step in range(state.batch, 5):
+            if step == 2 and rank == 1 and failures["left"]:
+                failures["left"] = 0
+                _lib.core().tips_inject_drop_requests(0, 1)
+            state.model(data(step, rank)).pow(2).sum().backward()
+            try:
+                state.optimizer.step()
+            except tips.TipsError:
+                failures["seen"] += 1
+                raise
+            state.optimizer.zero_grad()
+            state.batch = step + 1
+            state.commit()
+
+    train(state)
+    assert failures["seen"] == 1 and state.batch == 5
+    # an undisturbed single-process run over both ranks' data
+    torch.manual_seed(7)
+    ref = torch.nn.Linear(6, 3)
+    ropt = torch.optim.SGD(ref.parameters(), lr=0.05, momentum=0.9)
+    for step in range(5):
+        (sum(ref(data(step, r)).pow(2).sum() for r in range(size)) / size).backward()
+        ropt.step()
+        ropt.zero_grad()
+    assert torch.allclose(model.weight.detach(), ref.weight.detach(), atol=1e-5)
+    ws = tips.allgather_object(model.weight.detach().clone())
+    assert all(torch.equal(w, ws[0]) for w in ws)
+
+
+def test_elastic_run_retries_a_failed_step():
+    run_ranks(_elastic_retry, 2, env={"TIPS_STALL_ABORT_MS": "1500", "TIPS_STALL_WARN_MS": "500"})
 
 
 def _peer_loss(rank, size):

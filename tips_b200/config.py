@@ -29,8 +29,10 @@ class Config:
     symm_window_bytes: int = 256 << 20       # staging window for tensors outside symmetric memory
     static_schedule: bool = True             # freeze the bucket order after the first negotiated step
     fused_update: bool = False               # fused optimizers step inside the gradient allreduce, state sharded
-    # Parameter server
-    ps_local_shards: int = 1
+    device_status_check: str = "step"        # step: every synchronize() reads the kernels' status block (no device
+                                             # wait) and raises if a bounded wait ran out; sync: waits for the
+                                             # collective first, so the failing step itself raises; off
+    collective_timeout_s: float = 0.0        # >0: DistributedOptimizer.synchronize() gives up on a bucket after this long
     # Observability
     log_level: str = "WARNING"
     timeline_path: str = ""

@@ -315,6 +315,13 @@ int tips_thaw_schedule(void) {
   return 0;
 }
 
+int tips_reset_collectives(void) {
+  return Guard([&] {
+    Status st = CollectiveEngine::Global().Reset();
+    return st.ok() ? 0 : Fail(st);
+  });
+}
+
 int tips_timeline_enable(int on) {
   CollectiveEngine::Global().EnableTimeline(on != 0);
   return 0;

@@ -160,6 +160,10 @@ class CollectiveEngine {
   // rank (take it from LastNegotiatedOrder()).
   Status FreezeSchedule(const std::vector<std::string>& names);
   void ThawSchedule();
+  // Fails every collective in flight on this rank with `kAborted`, forgets partial negotiations and frozen
+  // schedules, and returns once the engine thread has done so: the state a failed step leaves behind is gone and
+  // the same tensor names can be submitted again.  Every rank calls it, then the ranks meet on a host barrier.
+  Status Reset();
   bool schedule_frozen() const { return frozen_.load(); }
   // Names of the responses executed since the last call to this function.
   std::vector<std::string> TakeNegotiatedOrder();
@@ -174,7 +178,7 @@ class CollectiveEngine {
   CollectiveEngine() = default;
 
   struct Event {
-    enum Kind { kLocalRequest, kRemoteRequest, kResponse, kFrozenReady, kPeerFailure, kShutdown } kind;
+    enum Kind { kLocalRequest, kRemoteRequest, kResponse, kFrozenReady, kPeerFailure, kReset, kShutdown } kind;
     RequestMessage request;
     RpcMsgHead head;
     ResponseMessage response;
@@ -207,6 +211,9 @@ class CollectiveEngine {
   std::unordered_map<std::string, OpRecord> tensor_table_;
   std::unordered_map<int64_t, std::shared_ptr<HandleState>> handles_;
   std::condition_variable handle_cv_;
+  uint64_t resets_requested_{0};  // guarded by mu_
+  uint64_t resets_done_{0};
+  std::condition_variable reset_cv_;
   int64_t next_handle_{1};
 
   MessageTable message_table_;  // rank 0, background thread only

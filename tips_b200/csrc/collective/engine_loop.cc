@@ -102,6 +102,19 @@ void CollectiveEngine::Loop() {
           message_table_.clear();
           FailAll(Status(kUnavailable, "rank " + std::to_string(ev.peer) + " left the job"));
           break;
+        case Event::kReset:
+          message_table_.clear();
+          ready.clear();
+          FailAll(Status(kAborted, "the collective engine was reset"));
+          ThawSchedule();
+          {
+            std::lock_guard<std::mutex> lock(mu_);
+            negotiated_.clear();
+            order_log_.clear();
+            ++resets_done_;
+          }
+          reset_cv_.notify_all();
+          break;
       }
       if (stop) break;
     }
@@ -196,7 +209,8 @@ void CollectiveEngine::Execute(const ResponseMessage& resp) {
   const int64_t t0 = NowMicros();
   for (auto& r : recs) Trace(r.name, "NEGOTIATE", r.enqueue_us, t0);
   if (resp.response_type == ResponseType::kError) {
-    st = Status(kPrecondition, resp.error_message);
+    // a tensor that the stall detector gave up on is a timeout (a retry may succeed), anything else a mismatch
+    st = Status(resp.error_message.rfind("stalled:", 0) == 0 ? kTimeout : kPrecondition, resp.error_message);
   } else if (resp.response_type == ResponseType::kShutdown) {
     st = Status(kAborted, "coordinator shut down");
   } else if (recs.size() == 1) {
@@ -363,6 +377,22 @@ Status CollectiveEngine::FreezeSchedule(const std::vector<std::string>& names) {
   for (size_t i = 0; i < names.size(); ++i) schedule_index_[names[i]] = {sid, i};
   schedules_.push_back(std::move(sched));
   frozen_ = true;
+  return Status::OK();
+}
+
+Status CollectiveEngine::Reset() {
+  if (!initialized_.load() || shut_down_.load()) return Status(kPrecondition, "the engine is not running");
+  uint64_t ticket;
+  {
+    std::lock_guard<std::mutex> lock(mu_);
+    ticket = ++resets_requested_;
+  }
+  Event ev;
+  ev.kind = Event::kReset;
+  queue_.WriteMove(std::move(ev));
+  std::unique_lock<std::mutex> lock(mu_);
+  if (!reset_cv_.wait_for(lock, std::chrono::seconds(30), [&] { return resets_done_ >= ticket; }))
+    return Status(kTimeout, "the engine thread did not answer the reset");
   return Status::OK();
 }
 

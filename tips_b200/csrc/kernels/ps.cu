@@ -1,6 +1,6 @@
 // Parameter-server data path on the GPU: sharded embedding tables that live in
 // peer-mapped memory, pull fused with the embedding lookup, push fused with a
-// cross-rank scatter-reduce and the server-side optimizer.
+// local segment-reduce, a cross-rank scatter and the server-side optimizer.
 //
 // Reference counterpart: PsClient::Pull / PsServer::PullTask (rows travel as
 // FlatBuffers over a ZeroMQ RPC, tips/core/ps/ps_client.h:78-109,
@@ -9,32 +9,47 @@
 // ps_server.h:232-265, sparse_access_method.h:41-61), and the zero
 // initialisation of a row on first pull (sparse_access_method.h:23-27).
 //
-// Placement: row `id` of a table is owned by rank (id mod N) and stored at
-// local row (id div N) of that rank's shard; pull and push use the same rule.
+// Placement: see ps_placement.h (rotated round-robin, one rule for pull, push,
+// initialisation, dump and load).
 //
 // Pull: one half-warp (or warp) per (sample, field) resolves the owner and
 // loads the row straight from the owner's HBM over NVLink with 16-byte
 // system-scope loads, converts and writes it into the consumer's input matrix at
 // its column offset.  No request message, no staging copy.
 //
-// Push: three launches separated by cross-rank fences.
-//   scatter  every (sample, field) gradient row is added into a slot of the
-//            OWNER's accumulation table (open addressing keyed by (field,row);
-//            the slot is claimed with a 64-bit CAS on peer memory, the gradient
-//            is added with vector float atomics on peer memory); duplicates
-//            inside a batch and across ranks end up summed in one slot
-//   apply    the owner walks its slots, applies SGD or Adagrad to the row with
-//            the summed gradient, and clears the slot
+// Synchronous push, per rank:
+//   scatter   every (sample, field) gradient row is added into a slot of a LOCAL
+//             open-addressing table keyed by (field, id): duplicate ids of the
+//             batch end up summed in one slot (device-scope CAS + vector float
+//             atomics in this GPU's L2); the lane that claims a slot appends it to
+//             a touched list
+//   send      walks the touched list: one summed row per distinct id goes to its
+//             owner's inbox (a region per sender, so plain 16-byte stores over
+//             NVLink, no remote atomics and no round trips); the slot is cleared
+//   fence     cross-rank barrier; the per-sender row counts travel with it
+//   reduce    the owner folds the rows of all inboxes into the same local table
+//             (rows that several ranks touched are summed) and rebuilds the
+//             touched list
+//   apply     the owner walks the touched list, applies SGD or Adagrad to the
+//             row with the gradient summed over every occurrence on every rank,
+//             and clears the slot
 // so the update is exactly the synchronous one: one optimizer step per touched
-// row with the gradient summed over every occurrence on every rank.
+// row.  With one rank the scatter is followed directly by the apply.  A training
+// step needs two fences: the one inside the push and the one in front of the
+// next pull (every owner has applied its updates); the push only fences first
+// when no fenced pull has run since the previous push.
 #include "kernels/comm.cuh"
 #include "kernels/common.cuh"
+#include "kernels/ps_placement.h"
 #include "kernels/tips_kernels.h"
 
 namespace tipsk {
 namespace {
 
-constexpr int kMaxFields = 64;
+constexpr int kMaxFields      = 64;
+constexpr uint32_t kNoSlot    = 0xffffffffu;
+constexpr unsigned kFullMask  = 0xffffffffu;
+constexpr size_t kInboxHeader = 128;  // per-sender row counts, one u32 per rank
 
 struct PsMeta {
   uint64_t field_off[kMaxFields];   // byte offset of the field's shard inside every rank's slab
@@ -44,13 +59,27 @@ struct PsMeta {
   int32_t dim;                      // fp32 elements per row, multiple of 4
 };
 
+// Per-rank control words in device memory; all zero between pushes.
+struct alignas(8) PsCtl {
+  uint32_t ucount;                  // entries of the touched list
+  uint32_t done;                    // blocks of the running list walker that have finished
+  uint32_t send_count[kMaxRanks];   // rows sent to each owner by the running send
+  uint32_t pad[6];
+  unsigned long long sent_total;    // rows sent since the last status call (own rows included)
+  unsigned long long sent_remote;   // of those, rows that crossed NVLink
+  unsigned long long applied;       // rows updated since the last status call
+};
+
 struct PsRank {
   char* slab[kMaxRanks];            // every rank's table slab as mapped here
-  char* acc[kMaxRanks];             // every rank's accumulation table as mapped here
+  char* inbox[kMaxRanks];           // every rank's inbox as mapped here (null with one rank)
+  char* acc;                        // local accumulation table: [slots] u64 keys, [slots][dim] fp32 sums
+  uint32_t* ulist;                  // local touched list, [slots]
+  PsCtl* ctl;
   const int64_t* ids;               // [batch, nfields]
   const void* grads;                // push: [batch, ld] rows of nfields*dim (fp32 or bf16)
   void* out;                        // pull: [batch, ld]
-  int32_t* error;                   // local error word (accumulation table full, bad id)
+  int32_t* error;                   // local error word (table full, bad id, inbox full)
   int32_t rank;
   int32_t nranks;
 };
@@ -67,6 +96,23 @@ __device__ __forceinline__ uint64_t Mix64(uint64_t x) {
   return x;
 }
 
+// Work split of a warp over rows of `dim` floats: `lpi` lanes move one row as 16-byte vectors.
+struct RowLanes {
+  int lpi, ipw, sub, sublane, lane;
+  __device__ __forceinline__ explicit RowLanes(int dim) {
+    const int vecs = dim / 4;
+    lpi = 1;
+    while (lpi < vecs && lpi < 32) lpi <<= 1;
+    ipw     = 32 / lpi;
+    lane    = threadIdx.x & 31;
+    sub     = lane / lpi;
+    sublane = lane % lpi;
+  }
+  __device__ __forceinline__ unsigned group_mask() const {
+    return lpi == 32 ? kFullMask : (((1u << lpi) - 1u) << (sub * lpi));
+  }
+};
+
 // Counter-based uniform in [-scale, scale): depends only on (seed, field, global row, column),
 // so a table has the same contents however it is sharded.
 __global__ void __launch_bounds__(256)
@@ -81,7 +127,7 @@ TableInitKernel(float* shard, int64_t rows_local, int dim, int field, int rank, 
     }
     const int64_t lrow = i / dim;
     const int col      = static_cast<int>(i % dim);
-    const int64_t grow = lrow * nranks + rank;
+    const int64_t grow = PsGlobalId(field, lrow, rank, nranks);
     float v = 0.f;
     if (grow < rows_global) {
       uint64_t h = Mix64(seed ^ (static_cast<uint64_t>(field) << 48) ^ (static_cast<uint64_t>(grow) * 0x9e3779b97f4a7c15ull) ^
@@ -95,37 +141,33 @@ TableInitKernel(float* shard, int64_t rows_local, int dim, int field, int rank, 
 template <typename OutT>
 __global__ void __launch_bounds__(256)
 PsPullKernel(PsLaunch args, PsMeta meta, int64_t batch, int64_t out_ld, int64_t out_col0) {
-  const PsRank& pr   = args.r[blockIdx.y];
-  const int n        = pr.nranks;
-  const int dim      = meta.dim;
-  const int vecs     = dim / 4;
-  int lanes_per_item = 1;
-  while (lanes_per_item < vecs && lanes_per_item < 32) lanes_per_item <<= 1;
-  const int items_per_warp = 32 / lanes_per_item;
-  const int lane     = threadIdx.x & 31;
-  const int sub      = lane / lanes_per_item;
-  const int sublane  = lane % lanes_per_item;
+  const PsRank& pr = args.r[blockIdx.y];
+  const int n      = pr.nranks;
+  const int dim    = meta.dim;
+  const int vecs   = dim / 4;
+  const RowLanes L(dim);
   const int64_t warp_global = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
   const int64_t nwarps      = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
   const int64_t total       = batch * meta.nfields;
   OutT* out = static_cast<OutT*>(pr.out);
-  for (int64_t base = warp_global * items_per_warp; base < total; base += nwarps * items_per_warp) {
-    const int64_t item = base + sub;
+  for (int64_t base = warp_global * L.ipw; base < total; base += nwarps * L.ipw) {
+    const int64_t item = base + L.sub;
     if (item >= total) continue;
     const int f      = static_cast<int>(item % meta.nfields);
     const int64_t b  = item / meta.nfields;
     const int64_t id = pr.ids[item];
     OutT* dst        = out + b * out_ld + out_col0 + static_cast<int64_t>(f) * dim;
-    const int owner  = static_cast<int>(id % n);
-    const int64_t lrow = id / n;
+    int owner;
+    int64_t lrow;
+    PsPlace(f, id < 0 ? 0 : id, n, &owner, &lrow);
     if (id < 0 || lrow >= meta.rows_per_shard[f]) {
-      if (sublane == 0) atomicExch(pr.error, 2);
-      for (int v = sublane; v < vecs; v += lanes_per_item)
+      if (L.sublane == 0) atomicExch(pr.error, 2);
+      for (int v = L.sublane; v < vecs; v += L.lpi)
         for (int k = 0; k < 4; ++k) dst[v * 4 + k] = FromFloat<OutT>(0.f);
       continue;
     }
     const char* row = pr.slab[owner] + meta.field_off[f] + static_cast<uint64_t>(lrow) * dim * 4;
-    for (int v = sublane; v < vecs; v += lanes_per_item) {
+    for (int v = L.sublane; v < vecs; v += L.lpi) {
       U4 q = owner == pr.rank ? *reinterpret_cast<const U4*>(row + v * 16) : LdSys(row + v * 16);
       const float fv[4] = {__uint_as_float(q.x), __uint_as_float(q.y), __uint_as_float(q.z), __uint_as_float(q.w)};
       if (sizeof(OutT) == 4) {
@@ -140,69 +182,269 @@ PsPullKernel(PsLaunch args, PsMeta meta, int64_t batch, int64_t out_ld, int64_t 
   }
 }
 
-// Slot layout of the accumulation table: [slots] u64 keys, then [slots][dim] fp32 sums.
-__device__ __forceinline__ uint64_t SlotKey(int field, int64_t lrow) {
-  return ((static_cast<uint64_t>(field) << 44) | static_cast<uint64_t>(lrow)) + 1;  // 0 = empty
+// Key of a table slot: field and global row id; 0 = empty.
+__device__ __forceinline__ uint64_t SlotKey(int field, int64_t id) {
+  return ((static_cast<uint64_t>(field) << 44) | static_cast<uint64_t>(id)) + 1;
+}
+__device__ __forceinline__ int KeyField(uint64_t key) { return static_cast<int>((key - 1) >> 44); }
+__device__ __forceinline__ int64_t KeyId(uint64_t key) { return static_cast<int64_t>((key - 1) & ((1ull << 44) - 1)); }
+
+// Finds or claims the slot of `key` in the local table; *claimed tells whether this call created it.
+__device__ __forceinline__ uint32_t ClaimSlot(unsigned long long* keys, uint64_t slots, uint64_t key, bool* claimed) {
+  uint64_t h = Mix64(key) & (slots - 1);
+  for (uint32_t probe = 0; probe < 4096 && probe < slots; ++probe) {
+    const unsigned long long prev = atomicCAS(keys + h, 0ull, static_cast<unsigned long long>(key));
+    if (prev == 0ull) {
+      *claimed = true;
+      return static_cast<uint32_t>(h);
+    }
+    if (prev == key) return static_cast<uint32_t>(h);
+    h = (h + 1) & (slots - 1);
+  }
+  return kNoSlot;
 }
 
-template <typename GradT>
+// Appends the slots claimed by the lanes of this warp to the touched list: one atomic per warp.
+// Every lane of the warp calls it.
+__device__ __forceinline__ void AppendClaims(const PsRank& pr, bool claimed, uint32_t slot, int lane) {
+  const unsigned m = __ballot_sync(kFullMask, claimed);
+  if (m == 0) return;
+  const int leader = __ffs(m) - 1;
+  uint32_t first   = 0;
+  if (lane == leader) first = atomicAdd(&pr.ctl->ucount, static_cast<uint32_t>(__popc(m)));
+  first = __shfl_sync(kFullMask, first, leader);
+  if (claimed) pr.ulist[first + __popc(m & ((1u << lane) - 1u))] = slot;
+}
+
+__device__ __forceinline__ void RedAdd4(float* addr, float a, float b, float c, float d) {
+  asm volatile("red.relaxed.gpu.global.add.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d)
+               : "memory");
+}
+
+template <typename GradT, bool kVec>
+__device__ __forceinline__ void LoadGrad4(const GradT* g, float* out) {
+  if (kVec) {
+    if (sizeof(GradT) == 4) {
+      const float4 q = *reinterpret_cast<const float4*>(g);
+      out[0] = q.x; out[1] = q.y; out[2] = q.z; out[3] = q.w;
+    } else {
+      uint2 q = *reinterpret_cast<const uint2*>(g);
+      const GradT* h = reinterpret_cast<const GradT*>(&q);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) out[k] = ToFloat<GradT>(h[k]);
+    }
+  } else {
+#pragma unroll
+    for (int k = 0; k < 4; ++k) out[k] = ToFloat<GradT>(g[k]);
+  }
+}
+
+// Local segment-reduce of the batch: phase 1 resolves one item per lane (32 probes in flight per
+// warp), phase 2 adds the gradient rows with `lpi` lanes per row.
+template <typename GradT, bool kVec>
 __global__ void __launch_bounds__(256)
-PsPushScatterKernel(PsLaunch args, PsMeta meta, int64_t batch, int64_t grad_ld, int64_t grad_col0, uint64_t slots,
-                    float grad_scale) {
-  const PsRank& pr   = args.r[blockIdx.y];
-  const int n        = pr.nranks;
-  const int dim      = meta.dim;
-  const int vecs     = dim / 4;
-  int lanes_per_item = 1;
-  while (lanes_per_item < vecs && lanes_per_item < 32) lanes_per_item <<= 1;
-  const int items_per_warp = 32 / lanes_per_item;
-  const int lane     = threadIdx.x & 31;
-  const int sub      = lane / lanes_per_item;
-  const int sublane  = lane % lanes_per_item;
-  const unsigned group_mask = lanes_per_item == 32 ? 0xffffffffu : (((1u << lanes_per_item) - 1u) << (sub * lanes_per_item));
+PsScatterKernel(PsLaunch args, PsMeta meta, int64_t batch, int64_t grad_ld, int64_t grad_col0, uint64_t slots,
+                float grad_scale) {
+  const PsRank& pr = args.r[blockIdx.y];
+  const int n      = pr.nranks;
+  const int dim    = meta.dim;
+  const int vecs   = dim / 4;
+  const RowLanes L(dim);
   const int64_t warp_global = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
   const int64_t nwarps      = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
   const int64_t total       = batch * meta.nfields;
-  const GradT* grads = static_cast<const GradT*>(pr.grads);
-  for (int64_t base = warp_global * items_per_warp; base < total; base += nwarps * items_per_warp) {
-    const int64_t item = base + sub;
-    if (item >= total) continue;
-    const int f      = static_cast<int>(item % meta.nfields);
-    const int64_t b  = item / meta.nfields;
-    const int64_t id = pr.ids[item];
-    const int owner  = static_cast<int>(id % n);
-    const int64_t lrow = id / n;
-    if (id < 0 || lrow >= meta.rows_per_shard[f]) {
-      if (sublane == 0) atomicExch(pr.error, 2);
-      continue;
-    }
-    // claim / find the slot in the owner's table (one lane probes, the group follows)
-    uint64_t slot = ~0ull;
-    if (sublane == 0) {
-      const uint64_t key = SlotKey(f, lrow);
-      unsigned long long* keys = reinterpret_cast<unsigned long long*>(pr.acc[owner]);
-      uint64_t h = Mix64(key) & (slots - 1);
-      for (uint64_t probe = 0; probe < slots && probe < 4096; ++probe) {
-        unsigned long long prev = atomicCAS_system(keys + h, 0ull, static_cast<unsigned long long>(key));
-        if (prev == 0ull || prev == key) {
-          slot = h;
-          break;
-        }
-        h = (h + 1) & (slots - 1);
+  const GradT* grads        = static_cast<const GradT*>(pr.grads);
+  unsigned long long* keys  = reinterpret_cast<unsigned long long*>(pr.acc);
+  float* sums_base          = reinterpret_cast<float*>(pr.acc + slots * 8);
+  for (int64_t base = warp_global * 32; base < total; base += nwarps * 32) {
+    const int64_t mine = base + L.lane;
+    uint32_t slot = kNoSlot;
+    bool claimed  = false;
+    if (mine < total) {
+      const int f      = static_cast<int>(mine % meta.nfields);
+      const int64_t id = pr.ids[mine];
+      if (id < 0 || id / n >= meta.rows_per_shard[f]) {
+        atomicExch(pr.error, 2);
+      } else {
+        slot = ClaimSlot(keys, slots, SlotKey(f, id), &claimed);
+        if (slot == kNoSlot) atomicExch(pr.error, 1);  // table full: the host raises after the step
       }
-      if (slot == ~0ull) atomicExch(pr.error, 1);  // table full: the host raises after the step
     }
-    slot = __shfl_sync(group_mask, slot, sub * lanes_per_item);
-    if (slot == ~0ull) continue;
-    float* sums = reinterpret_cast<float*>(pr.acc[owner] + slots * 8) + slot * dim;
-    const GradT* g = grads + b * grad_ld + grad_col0 + static_cast<int64_t>(f) * dim;
-    for (int v = sublane; v < vecs; v += lanes_per_item) {
-      float gv[4];
-#pragma unroll
-      for (int k = 0; k < 4; ++k) gv[k] = ToFloat<GradT>(g[v * 4 + k]) * grad_scale;
-      asm volatile("red.relaxed.sys.global.add.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(sums + v * 4), "f"(gv[0]), "f"(gv[1]),
-                   "f"(gv[2]), "f"(gv[3])
+    AppendClaims(pr, claimed, slot, L.lane);
+    for (int j = 0; j < 32; j += L.ipw) {
+      const int src      = j + L.sub;
+      const uint32_t s   = __shfl_sync(kFullMask, slot, src);
+      const int64_t item = base + src;
+      if (item >= total || s == kNoSlot) continue;
+      const int f     = static_cast<int>(item % meta.nfields);
+      const int64_t b = item / meta.nfields;
+      float* sums     = sums_base + static_cast<uint64_t>(s) * dim;
+      const GradT* g  = grads + b * grad_ld + grad_col0 + static_cast<int64_t>(f) * dim;
+      for (int v = L.sublane; v < vecs; v += L.lpi) {
+        float gv[4];
+        LoadGrad4<GradT, kVec>(g + v * 4, gv);
+        RedAdd4(sums + v * 4, gv[0] * grad_scale, gv[1] * grad_scale, gv[2] * grad_scale, gv[3] * grad_scale);
+      }
+    }
+  }
+}
+
+// Byte offsets inside an inbox: header, then per sender `cap` keys, then per sender `cap` rows.
+__device__ __forceinline__ unsigned long long* InboxKeys(char* inbox, int sender, uint64_t cap) {
+  return reinterpret_cast<unsigned long long*>(inbox + kInboxHeader) + static_cast<uint64_t>(sender) * cap;
+}
+__device__ __forceinline__ float* InboxRows(char* inbox, int nranks, int sender, uint64_t cap, int dim) {
+  return reinterpret_cast<float*>(inbox + kInboxHeader + static_cast<uint64_t>(nranks) * cap * 8) +
+         static_cast<uint64_t>(sender) * cap * dim;
+}
+
+// Last-block detection for the list walkers: returns true in exactly one block, after every other
+// block of this rank's grid row has finished its share.
+__device__ __forceinline__ bool LastBlockDone(PsCtl* ctl) {
+  __shared__ int s_last;
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) s_last = atomicAdd(&ctl->done, 1u) == gridDim.x - 1 ? 1 : 0;
+  __syncthreads();
+  return s_last != 0;
+}
+
+// One summed row per distinct id goes to its owner's inbox; the local slot is cleared.
+__global__ void __launch_bounds__(256)
+PsSendKernel(PsLaunch args, PsMeta meta, uint64_t slots, uint64_t cap) {
+  const PsRank& pr = args.r[blockIdx.y];
+  const int n      = pr.nranks;
+  const int dim    = meta.dim;
+  const int vecs   = dim / 4;
+  const RowLanes L(dim);
+  const int64_t warp_global = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int64_t nwarps      = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
+  unsigned long long* keys  = reinterpret_cast<unsigned long long*>(pr.acc);
+  float* sums_base          = reinterpret_cast<float*>(pr.acc + slots * 8);
+  const int64_t total       = *reinterpret_cast<volatile uint32_t*>(&pr.ctl->ucount);
+  for (int64_t base = warp_global * 32; base < total; base += nwarps * 32) {
+    const int64_t mine = base + L.lane;
+    uint32_t slot = kNoSlot, pos = 0;
+    int owner     = -1;
+    unsigned long long key = 0;
+    if (mine < total) {
+      slot = pr.ulist[mine];
+      key  = keys[slot];
+      int64_t lrow;
+      PsPlace(KeyField(key), KeyId(key), n, &owner, &lrow);
+    }
+    // one atomic per (warp, owner): lanes with the same owner take consecutive positions
+    const unsigned peers = __match_any_sync(kFullMask, owner);
+    if (owner >= 0) {
+      const int leader = __ffs(peers) - 1;
+      uint32_t first   = 0;
+      if (L.lane == leader) first = atomicAdd(&pr.ctl->send_count[owner], static_cast<uint32_t>(__popc(peers)));
+      first = __shfl_sync(peers, first, leader);
+      pos   = first + __popc(peers & ((1u << L.lane) - 1u));
+      if (pos < cap) {
+        asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(InboxKeys(pr.inbox[owner], pr.rank, cap) + pos), "l"(key)
+                     : "memory");
+      } else {
+        atomicExch(pr.error, 3);  // inbox full: the row is dropped, the host raises after the step
+      }
+      keys[slot] = 0;
+    }
+    for (int j = 0; j < 32; j += L.ipw) {
+      const int src    = j + L.sub;
+      const uint32_t s = __shfl_sync(kFullMask, slot, src);
+      const int o      = __shfl_sync(kFullMask, owner, src);
+      const uint32_t p = __shfl_sync(kFullMask, pos, src);
+      if (s == kNoSlot) continue;
+      float* sums = sums_base + static_cast<uint64_t>(s) * dim;
+      float* dst  = p < cap ? InboxRows(pr.inbox[o], n, pr.rank, cap, dim) + static_cast<uint64_t>(p) * dim : nullptr;
+      for (int v = L.sublane; v < vecs; v += L.lpi) {
+        const U4 q = *reinterpret_cast<const U4*>(sums + v * 4);
+        if (dst) StSys(dst + v * 4, q);
+        *reinterpret_cast<float4*>(sums + v * 4) = make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+    }
+  }
+  if (LastBlockDone(pr.ctl)) {
+    if (threadIdx.x < n) {
+      const int o       = threadIdx.x;
+      uint32_t c        = atomicExch(&pr.ctl->send_count[o], 0u);
+      if (c > cap) c = static_cast<uint32_t>(cap);
+      // the count is published by the fence that follows (system-scope release after this kernel)
+      asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(reinterpret_cast<uint32_t*>(pr.inbox[o]) + pr.rank), "r"(c)
                    : "memory");
+      atomicAdd(&pr.ctl->sent_total, static_cast<unsigned long long>(c));
+      if (o != pr.rank) atomicAdd(&pr.ctl->sent_remote, static_cast<unsigned long long>(c));
+    }
+    if (threadIdx.x == 0) {
+      pr.ctl->ucount = 0;
+      pr.ctl->done   = 0;
+    }
+    __threadfence_system();
+  }
+}
+
+// The owner folds the rows that arrived in its inboxes into its local table.
+__global__ void __launch_bounds__(256)
+PsOwnerReduceKernel(PsLaunch args, PsMeta meta, uint64_t slots, uint64_t cap) {
+  const PsRank& pr = args.r[blockIdx.y];
+  const int n      = pr.nranks;
+  const int dim    = meta.dim;
+  const int vecs   = dim / 4;
+  const RowLanes L(dim);
+  const int64_t warp_global = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int64_t nwarps      = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
+  unsigned long long* keys  = reinterpret_cast<unsigned long long*>(pr.acc);
+  float* sums_base          = reinterpret_cast<float*>(pr.acc + slots * 8);
+  char* inbox               = pr.inbox[pr.rank];
+  // exclusive prefix of the per-sender counts (written by the senders, published by the fence)
+  uint32_t start[kMaxRanks + 1];
+  start[0] = 0;
+#pragma unroll
+  for (int s = 0; s < kMaxRanks; ++s) {
+    uint32_t c = 0;
+    if (s < n) {
+      asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(c) : "l"(reinterpret_cast<uint32_t*>(inbox) + s) : "memory");
+      if (c > cap) c = static_cast<uint32_t>(cap);
+    }
+    start[s + 1] = start[s] + c;
+  }
+  const int64_t total = start[kMaxRanks];
+  for (int64_t base = warp_global * 32; base < total; base += nwarps * 32) {
+    const int64_t mine = base + L.lane;
+    uint32_t slot = kNoSlot;
+    uint64_t cell = 0;  // sender * cap + position: where the entry sits in the inbox
+    bool claimed  = false;
+    if (mine < total) {
+      int s           = 0;
+      uint32_t sstart = 0;
+#pragma unroll
+      for (int k = 1; k < kMaxRanks; ++k)
+        if (mine >= start[k]) {
+          s      = k;
+          sstart = start[k];
+        }
+      cell = static_cast<uint64_t>(s) * cap + (mine - sstart);
+      unsigned long long key;
+      asm volatile("ld.relaxed.sys.global.u64 %0, [%1];"
+                   : "=l"(key)
+                   : "l"(reinterpret_cast<unsigned long long*>(inbox + kInboxHeader) + cell)
+                   : "memory");
+      slot = ClaimSlot(keys, slots, key, &claimed);
+      if (slot == kNoSlot) atomicExch(pr.error, 1);
+    }
+    AppendClaims(pr, claimed, slot, L.lane);
+    const float* rows = reinterpret_cast<const float*>(inbox + kInboxHeader + static_cast<uint64_t>(n) * cap * 8);
+    for (int j = 0; j < 32; j += L.ipw) {
+      const int src    = j + L.sub;
+      const uint32_t s = __shfl_sync(kFullMask, slot, src);
+      const uint64_t c = __shfl_sync(kFullMask, cell, src);
+      if (s == kNoSlot) continue;
+      float* sums      = sums_base + static_cast<uint64_t>(s) * dim;
+      const float* row = rows + c * dim;
+      for (int v = L.sublane; v < vecs; v += L.lpi) {
+        const U4 q = LdSys(row + v * 4);
+        RedAdd4(sums + v * 4, __uint_as_float(q.x), __uint_as_float(q.y), __uint_as_float(q.z), __uint_as_float(q.w));
+      }
     }
   }
 }
@@ -216,36 +458,32 @@ template <typename GradT>
 __global__ void __launch_bounds__(256)
 PsPushDirectKernel(PsLaunch args, PsMeta meta, int64_t batch, int64_t grad_ld, int64_t grad_col0, float grad_scale,
                    int rule, float lr, float eps) {
-  const PsRank& pr   = args.r[blockIdx.y];
-  const int n        = pr.nranks;
-  const int dim      = meta.dim;
-  const int vecs     = dim / 4;
-  int lanes_per_item = 1;
-  while (lanes_per_item < vecs && lanes_per_item < 32) lanes_per_item <<= 1;
-  const int items_per_warp = 32 / lanes_per_item;
-  const int lane     = threadIdx.x & 31;
-  const int sub      = lane / lanes_per_item;
-  const int sublane  = lane % lanes_per_item;
+  const PsRank& pr = args.r[blockIdx.y];
+  const int n      = pr.nranks;
+  const int dim    = meta.dim;
+  const int vecs   = dim / 4;
+  const RowLanes L(dim);
   const int64_t warp_global = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
   const int64_t nwarps      = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
   const int64_t total       = batch * meta.nfields;
   const GradT* grads = static_cast<const GradT*>(pr.grads);
-  for (int64_t base = warp_global * items_per_warp; base < total; base += nwarps * items_per_warp) {
-    const int64_t item = base + sub;
+  for (int64_t base = warp_global * L.ipw; base < total; base += nwarps * L.ipw) {
+    const int64_t item = base + L.sub;
     if (item >= total) continue;
     const int f      = static_cast<int>(item % meta.nfields);
     const int64_t b  = item / meta.nfields;
     const int64_t id = pr.ids[item];
-    const int owner  = static_cast<int>(id % n);
-    const int64_t lrow = id / n;
+    int owner;
+    int64_t lrow;
+    PsPlace(f, id < 0 ? 0 : id, n, &owner, &lrow);
     if (id < 0 || lrow >= meta.rows_per_shard[f]) {
-      if (sublane == 0) atomicExch(pr.error, 2);
+      if (L.sublane == 0) atomicExch(pr.error, 2);
       continue;
     }
     float* w  = reinterpret_cast<float*>(pr.slab[owner] + meta.field_off[f]) + lrow * dim;
     float* st = reinterpret_cast<float*>(pr.slab[owner] + meta.state_off[f]) + lrow * dim;
     const GradT* g = grads + b * grad_ld + grad_col0 + static_cast<int64_t>(f) * dim;
-    for (int v = sublane; v < vecs; v += lanes_per_item) {
+    for (int v = L.sublane; v < vecs; v += L.lpi) {
       float d[4], gv[4];
 #pragma unroll
       for (int k = 0; k < 4; ++k) gv[k] = ToFloat<GradT>(g[v * 4 + k]) * grad_scale;
@@ -276,33 +514,33 @@ PsPushDirectKernel(PsLaunch args, PsMeta meta, int64_t batch, int64_t grad_ld, i
 
 // rule: 0 = SGD (w -= lr*g), 1 = Adagrad (G += g*g; w -= lr*g/(sqrt(G)+eps)),
 //       2 = the reference's literal rule (w = lr*g, sparse_access_method.h:51-56)
+// Walks the touched list only: the cost follows the number of distinct rows, not the table size.
 __global__ void __launch_bounds__(256)
-PsPushApplyKernel(PsLaunch args, PsMeta meta, uint64_t slots, int rule, float lr, float eps, unsigned long long* touched) {
+PsPushApplyKernel(PsLaunch args, PsMeta meta, uint64_t slots, int rule, float lr, float eps) {
   const PsRank& pr = args.r[blockIdx.y];
+  const int n      = pr.nranks;
   const int dim    = meta.dim;
   const int vecs   = dim / 4;
-  int lanes_per_item = 1;
-  while (lanes_per_item < vecs && lanes_per_item < 32) lanes_per_item <<= 1;
-  const int items_per_warp = 32 / lanes_per_item;
-  const int lane    = threadIdx.x & 31;
-  const int sub     = lane / lanes_per_item;
-  const int sublane = lane % lanes_per_item;
+  const RowLanes L(dim);
   const int64_t warp_global = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
   const int64_t nwarps      = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
-  unsigned long long* keys  = reinterpret_cast<unsigned long long*>(pr.acc[pr.rank]);
-  float* sums_base          = reinterpret_cast<float*>(pr.acc[pr.rank] + slots * 8);
+  unsigned long long* keys  = reinterpret_cast<unsigned long long*>(pr.acc);
+  float* sums_base          = reinterpret_cast<float*>(pr.acc + slots * 8);
   char* slab                = pr.slab[pr.rank];
-  for (uint64_t base = warp_global * items_per_warp; base < slots; base += nwarps * items_per_warp) {
-    const uint64_t slot = base + sub;
-    if (slot >= slots) continue;
-    const uint64_t key = keys[slot];
-    if (key == 0) continue;
-    const int f        = static_cast<int>((key - 1) >> 44);
-    const int64_t lrow = static_cast<int64_t>((key - 1) & ((1ull << 44) - 1));
-    float* w  = reinterpret_cast<float*>(slab + meta.field_off[f]) + lrow * dim;
-    float* st = reinterpret_cast<float*>(slab + meta.state_off[f]) + lrow * dim;
-    float* sums = sums_base + slot * dim;
-    for (int v = sublane; v < vecs; v += lanes_per_item) {
+  const int64_t total       = *reinterpret_cast<volatile uint32_t*>(&pr.ctl->ucount);
+  for (int64_t base = warp_global * L.ipw; base < total; base += nwarps * L.ipw) {
+    const int64_t e = base + L.sub;
+    if (e >= total) continue;
+    const uint32_t slot = pr.ulist[e];
+    const uint64_t key  = keys[slot];
+    const int f         = KeyField(key);
+    int owner;
+    int64_t lrow;
+    PsPlace(f, KeyId(key), n, &owner, &lrow);
+    float* w    = reinterpret_cast<float*>(slab + meta.field_off[f]) + lrow * dim;
+    float* st   = reinterpret_cast<float*>(slab + meta.state_off[f]) + lrow * dim;
+    float* sums = sums_base + static_cast<uint64_t>(slot) * dim;
+    for (int v = L.sublane; v < vecs; v += L.lpi) {
       float4 g  = *reinterpret_cast<float4*>(sums + v * 4);
       float4 wv = *reinterpret_cast<float4*>(w + v * 4);
       if (rule == 1) {
@@ -321,10 +559,14 @@ PsPushApplyKernel(PsLaunch args, PsMeta meta, uint64_t slots, int rule, float lr
       *reinterpret_cast<float4*>(w + v * 4)    = wv;
       *reinterpret_cast<float4*>(sums + v * 4) = make_float4(0.f, 0.f, 0.f, 0.f);
     }
-    __syncwarp(lanes_per_item == 32 ? 0xffffffffu : (((1u << lanes_per_item) - 1u) << (sub * lanes_per_item)));
-    if (sublane == 0) {
-      keys[slot] = 0;
-      if (touched) atomicAdd(touched, 1ull);
+    __syncwarp(L.group_mask());
+    if (L.sublane == 0) keys[slot] = 0;
+  }
+  if (LastBlockDone(pr.ctl)) {
+    if (threadIdx.x == 0) {
+      atomicAdd(&pr.ctl->applied, static_cast<unsigned long long>(total));
+      pr.ctl->ucount = 0;
+      pr.ctl->done   = 0;
     }
   }
 }
@@ -353,10 +595,18 @@ struct PsState {
   bool ready = false;
   PsMeta meta;
   char* slab[kMaxRanks];
-  char* acc[kMaxRanks];
+  char* inbox[kMaxRanks];
+  char* acc[kMaxRanks];        // per local rank (one entry unless the ranks are emulated on one GPU)
+  uint32_t* ulist[kMaxRanks];
+  PsCtl* ctl[kMaxRanks];
+  int nlocal = 0;
   uint64_t slots = 0;
+  uint64_t inbox_cap = 0;
   int32_t* error_dev = nullptr;
-  unsigned long long* touched_dev = nullptr;
+  bool lead_fence = true;      // the next push must fence first (no fenced pull since the previous push)
+  bool timing = false;
+  cudaEvent_t ev[6] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+  int ev_used = 0;
 };
 PsState g_ps;
 
@@ -367,12 +617,16 @@ int MakePsLaunch(PsLaunch* l, const int64_t* const* ids, const void* const* grad
   if (rc) return rc;
   memset(l, 0, sizeof(*l));
   const int local = emulated ? nranks : 1;
+  if (local != g_ps.nlocal) return SetError(-2, "ps: configured for another number of local ranks");
   for (int i = 0; i < local; ++i) {
     PsRank& r = l->r[i];
     for (int p = 0; p < nranks; ++p) {
-      r.slab[p] = g_ps.slab[p];
-      r.acc[p]  = g_ps.acc[p];
+      r.slab[p]  = g_ps.slab[p];
+      r.inbox[p] = g_ps.inbox[p];
     }
+    r.acc    = g_ps.acc[i];
+    r.ulist  = g_ps.ulist[i];
+    r.ctl    = g_ps.ctl[i];
     r.ids    = ids ? ids[i] : nullptr;
     r.grads  = grads ? grads[i] : nullptr;
     r.out    = outs ? outs[i] : nullptr;
@@ -395,6 +649,11 @@ int LanesPerItem(int dim) {
   int l = 1;
   while (l < dim / 4 && l < 32) l <<= 1;
   return l;
+}
+
+void Mark(cudaStream_t s) {
+  PsState& st = g_ps;
+  if (st.timing && st.ev_used < 6) cudaEventRecord(st.ev[st.ev_used++], s);
 }
 
 }  // namespace
@@ -436,15 +695,40 @@ int tipsk_table_init(float* shard, int64_t rows_local, int dim, int field, int r
   return 0;
 }
 
-/* Registers the table slabs and accumulation tables (one pointer per rank, as mapped in this
- * process) and the per-field layout.  `slots` must be a power of two; an accumulation table is
- * slots*8 + slots*dim*4 bytes and must be zero before the first push. */
-int tipsk_ps_configure(void* const* slabs, void* const* accs, int nranks, const uint64_t* field_off,
-                       const uint64_t* state_off, const int64_t* rows_per_shard, int nfields, int dim, uint64_t slots) {
+/* Placement rule of the tables as the kernels compute it (ps_placement.h), for host code and tests. */
+int tipsk_ps_place(int field, int64_t id, int nranks, int32_t* owner, int64_t* local_row) {
+  TIPSK_REQUIRE(nranks >= 1 && id >= 0, "ps place: bad arguments");
+  int o;
+  int64_t l;
+  PsPlace(field, id, nranks, &o, &l);
+  *owner     = o;
+  *local_row = l;
+  return 0;
+}
+
+/* Bytes of the per-rank buffers of the push path for a given geometry. */
+uint64_t tipsk_ps_acc_bytes(uint64_t slots, int dim) { return slots * 8 + slots * static_cast<uint64_t>(dim) * 4; }
+uint64_t tipsk_ps_inbox_bytes(int nranks, uint64_t inbox_cap, int dim) {
+  return kInboxHeader + static_cast<uint64_t>(nranks) * inbox_cap * (8 + static_cast<uint64_t>(dim) * 4);
+}
+uint64_t tipsk_ps_ctl_bytes() { return sizeof(PsCtl); }
+
+/* Registers the buffers of the data path and the per-field layout.
+ *   slabs, inboxes   one pointer per rank, as mapped in this process (inboxes may be null with one rank)
+ *   accs, ulists, ctls   one pointer per LOCAL rank (one, or `nranks` when the ranks are emulated on one GPU):
+ *                    accumulation table (tipsk_ps_acc_bytes), touched list (slots u32), control words
+ *                    (tipsk_ps_ctl_bytes); all three must be zero before the first push
+ *   slots            power of two; inbox_cap: rows one sender may send to one owner in a push, even. */
+int tipsk_ps_configure(void* const* slabs, void* const* inboxes, void* const* accs, void* const* ulists,
+                       void* const* ctls, int nranks, int nlocal, const uint64_t* field_off, const uint64_t* state_off,
+                       const int64_t* rows_per_shard, int nfields, int dim, uint64_t slots, uint64_t inbox_cap) {
   TIPSK_REQUIRE(nfields >= 1 && nfields <= kMaxFields, "ps: 1..64 fields are supported");
   TIPSK_REQUIRE(dim >= 4 && dim % 4 == 0, "ps: the row dimension must be a multiple of 4");
-  TIPSK_REQUIRE(slots >= 2 && (slots & (slots - 1)) == 0, "ps: slots must be a power of two");
+  TIPSK_REQUIRE(slots >= 2 && (slots & (slots - 1)) == 0 && slots <= (1ull << 31), "ps: slots must be a power of two");
   TIPSK_REQUIRE(nranks >= 1 && nranks <= kMaxRanks, "ps: 1..8 ranks");
+  TIPSK_REQUIRE(nlocal == 1 || nlocal == nranks, "ps: one local rank, or all of them (emulation)");
+  TIPSK_REQUIRE(nranks == 1 || !accs || (inboxes && inbox_cap >= 2 && inbox_cap % 2 == 0),
+                "ps: several ranks need inboxes with an even capacity");
   PsState& st = g_ps;
   memset(&st.meta, 0, sizeof(st.meta));
   for (int f = 0; f < nfields; ++f) {
@@ -455,31 +739,83 @@ int tipsk_ps_configure(void* const* slabs, void* const* accs, int nranks, const 
   st.meta.nfields = nfields;
   st.meta.dim     = dim;
   for (int r = 0; r < kMaxRanks; ++r) {
-    st.slab[r] = r < nranks ? static_cast<char*>(slabs[r]) : nullptr;
-    st.acc[r]  = r < nranks && accs ? static_cast<char*>(accs[r]) : nullptr;
+    st.slab[r]  = r < nranks ? static_cast<char*>(slabs[r]) : nullptr;
+    st.inbox[r] = r < nranks && inboxes ? static_cast<char*>(inboxes[r]) : nullptr;
+    st.acc[r]   = r < nlocal && accs ? static_cast<char*>(accs[r]) : nullptr;
+    st.ulist[r] = r < nlocal && ulists ? static_cast<uint32_t*>(ulists[r]) : nullptr;
+    st.ctl[r]   = r < nlocal && ctls ? static_cast<PsCtl*>(ctls[r]) : nullptr;
   }
-  st.slots = slots;
+  st.nlocal     = nlocal;
+  st.slots      = slots;
+  st.inbox_cap  = inbox_cap;
+  st.lead_fence = true;
   if (!st.error_dev) {
     TIPSK_CUDA(cudaMalloc(reinterpret_cast<void**>(&st.error_dev), sizeof(int32_t)));
-    TIPSK_CUDA(cudaMalloc(reinterpret_cast<void**>(&st.touched_dev), sizeof(unsigned long long)));
+    TIPSK_CUDA(cudaMemset(st.error_dev, 0, sizeof(int32_t)));
   }
-  TIPSK_CUDA(cudaMemset(st.error_dev, 0, sizeof(int32_t)));
-  TIPSK_CUDA(cudaMemset(st.touched_dev, 0, sizeof(unsigned long long)));
   st.ready = true;
   return 0;
 }
 
-/* Reads and clears the PS error word (0 ok, 1 accumulation table full, 2 id out of range) and the
+/* Reads and clears the PS error word (0 ok, 1 accumulation table full, 2 id out of range, 3 inbox full) and the
  * count of rows updated since the last call.  Synchronises the device. */
 int tipsk_ps_status(int32_t* error, uint64_t* touched) {
   PsState& st = g_ps;
   TIPSK_REQUIRE(st.ready, "ps not configured");
   TIPSK_CUDA(cudaMemcpy(error, st.error_dev, sizeof(int32_t), cudaMemcpyDeviceToHost));
-  unsigned long long t = 0;
-  TIPSK_CUDA(cudaMemcpy(&t, st.touched_dev, sizeof(t), cudaMemcpyDeviceToHost));
-  *touched = t;
   TIPSK_CUDA(cudaMemset(st.error_dev, 0, sizeof(int32_t)));
-  TIPSK_CUDA(cudaMemset(st.touched_dev, 0, sizeof(unsigned long long)));
+  uint64_t t = 0;
+  for (int i = 0; i < st.nlocal; ++i) {
+    if (!st.ctl[i]) continue;
+    PsCtl c;
+    TIPSK_CUDA(cudaMemcpy(&c, st.ctl[i], sizeof(c), cudaMemcpyDeviceToHost));
+    t += c.applied;
+    TIPSK_CUDA(cudaMemset(&st.ctl[i]->applied, 0, sizeof(unsigned long long)));
+  }
+  *touched = t;
+  return 0;
+}
+
+/* Traffic counters of the synchronous push since the last call: out[0] rows sent to owners (after the local
+ * reduction of duplicates; rows this rank owns itself included), out[1] those that crossed NVLink.  Summed over the
+ * local ranks.  Synchronises the device. */
+int tipsk_ps_traffic(uint64_t* out) {
+  PsState& st = g_ps;
+  TIPSK_REQUIRE(st.ready, "ps not configured");
+  out[0] = out[1] = 0;
+  for (int i = 0; i < st.nlocal; ++i) {
+    if (!st.ctl[i]) continue;
+    PsCtl c;
+    TIPSK_CUDA(cudaMemcpy(&c, st.ctl[i], sizeof(c), cudaMemcpyDeviceToHost));
+    out[0] += c.sent_total;
+    out[1] += c.sent_remote;
+    TIPSK_CUDA(cudaMemset(&st.ctl[i]->sent_total, 0, 2 * sizeof(unsigned long long)));
+  }
+  return 0;
+}
+
+/* Per-phase device timing of the next synchronous pushes (eager launches only, not under stream capture):
+ * events are recorded around scatter / send / fence / reduce / apply.  tipsk_ps_phase_ms synchronises and
+ * returns the five durations of the last push in milliseconds (0 for phases that did not run). */
+int tipsk_ps_phase_timing(int enable) {
+  PsState& st = g_ps;
+  if (enable && !st.ev[0])
+    for (auto& e : st.ev) TIPSK_CUDA(cudaEventCreate(&e));
+  st.timing  = enable != 0;
+  st.ev_used = 0;
+  return 0;
+}
+int tipsk_ps_phase_ms(float* out5) {
+  PsState& st = g_ps;
+  for (int i = 0; i < 5; ++i) out5[i] = 0.f;
+  if (!st.timing || st.ev_used < 2) return 0;
+  TIPSK_CUDA(cudaEventSynchronize(st.ev[st.ev_used - 1]));
+  if (st.ev_used == 3) {  // one rank: scatter, apply
+    TIPSK_CUDA(cudaEventElapsedTime(&out5[0], st.ev[0], st.ev[1]));
+    TIPSK_CUDA(cudaEventElapsedTime(&out5[4], st.ev[1], st.ev[2]));
+  } else if (st.ev_used == 6) {
+    for (int i = 0; i < 5; ++i) TIPSK_CUDA(cudaEventElapsedTime(&out5[i], st.ev[i], st.ev[i + 1]));
+  }
   return 0;
 }
 
@@ -491,9 +827,11 @@ int tipsk_ps_pull(const int64_t* const* ids, void* const* outs, int64_t batch, i
   PsState& st = g_ps;
   TIPSK_REQUIRE(st.ready, "ps not configured");
   if (batch <= 0) return 0;
+  TIPSK_REQUIRE(out_ld % 4 == 0 && out_col0 % 4 == 0, "ps pull: the output pitch and column offset must be multiples of 4");
   if (fence) {
     int rc = tipsk_comm_fence(2, stream);
     if (rc) return rc;
+    st.lead_fence = false;
   }
   PsLaunch l;
   int local = MakePsLaunch(&l, ids, nullptr, outs);
@@ -516,28 +854,57 @@ int tipsk_ps_push(const int64_t* const* ids, const void* const* grads, int64_t b
                   int64_t grad_col0, int grad_dtype, float grad_scale, int rule, float lr, float eps, void* stream) {
   PsState& st = g_ps;
   TIPSK_REQUIRE(st.ready, "ps not configured");
-  TIPSK_REQUIRE(st.acc[0] != nullptr, "ps push: no accumulation tables configured");
+  TIPSK_REQUIRE(st.acc[0] != nullptr && st.ulist[0] != nullptr && st.ctl[0] != nullptr,
+                "ps push: no accumulation tables configured");
+  TIPSK_REQUIRE(grad_dtype == kF32 || grad_dtype == kBF16, "ps push: gradients must be fp32 or bf16");
   if (batch <= 0) return 0;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  int rc = tipsk_comm_fence(2, stream);  // every rank finished reading rows (its pull) and clearing slots
-  if (rc) return rc;
   PsLaunch l;
   int local = MakePsLaunch(&l, ids, grads, nullptr);
   if (local < 0) return local;
+  const int nranks = l.r[0].nranks;
+  TIPSK_REQUIRE(nranks == 1 || st.inbox[0] != nullptr, "ps push: no inboxes configured");
+  if (nranks > 1 && st.lead_fence) {
+    // every rank has finished reading its inbox and applying the previous push
+    int rc = tipsk_comm_fence(2, stream);
+    if (rc) return rc;
+  }
+  st.lead_fence = true;
+  st.ev_used    = 0;
   const int lpi = LanesPerItem(st.meta.dim);
   dim3 grid(PsGrid(batch * st.meta.nfields, lpi), local);
-  if (grad_dtype == kF32)
-    PsPushScatterKernel<float><<<grid, 256, 0, s>>>(l, st.meta, batch, grad_ld, grad_col0, st.slots, grad_scale);
-  else if (grad_dtype == kBF16)
-    PsPushScatterKernel<__nv_bfloat16><<<grid, 256, 0, s>>>(l, st.meta, batch, grad_ld, grad_col0, st.slots, grad_scale);
-  else
-    return SetError(-2, "ps push: gradients must be fp32 or bf16");
+  bool vec = grad_ld % 4 == 0 && grad_col0 % 4 == 0;
+  for (int i = 0; i < local; ++i) vec = vec && (reinterpret_cast<uintptr_t>(grads[i]) % 16 == 0);
+  Mark(s);
+  if (grad_dtype == kF32) {
+    if (vec)
+      PsScatterKernel<float, true><<<grid, 256, 0, s>>>(l, st.meta, batch, grad_ld, grad_col0, st.slots, grad_scale);
+    else
+      PsScatterKernel<float, false><<<grid, 256, 0, s>>>(l, st.meta, batch, grad_ld, grad_col0, st.slots, grad_scale);
+  } else {
+    if (vec)
+      PsScatterKernel<__nv_bfloat16, true><<<grid, 256, 0, s>>>(l, st.meta, batch, grad_ld, grad_col0, st.slots,
+                                                               grad_scale);
+    else
+      PsScatterKernel<__nv_bfloat16, false><<<grid, 256, 0, s>>>(l, st.meta, batch, grad_ld, grad_col0, st.slots,
+                                                                grad_scale);
+  }
   TIPSK_LAUNCH_CHECK();
-  rc = tipsk_comm_fence(2, stream);  // every rank's scatter has landed
-  if (rc) return rc;
-  dim3 agrid(PsGrid(static_cast<int64_t>(st.slots), lpi), local);
-  PsPushApplyKernel<<<agrid, 256, 0, s>>>(l, st.meta, st.slots, rule, lr, eps, st.touched_dev);
+  Mark(s);
+  if (nranks > 1) {
+    PsSendKernel<<<grid, 256, 0, s>>>(l, st.meta, st.slots, st.inbox_cap);
+    TIPSK_LAUNCH_CHECK();
+    Mark(s);
+    int rc = tipsk_comm_fence(2, stream);  // every rank's rows and counts have landed
+    if (rc) return rc;
+    Mark(s);
+    PsOwnerReduceKernel<<<grid, 256, 0, s>>>(l, st.meta, st.slots, st.inbox_cap);
+    TIPSK_LAUNCH_CHECK();
+    Mark(s);
+  }
+  PsPushApplyKernel<<<grid, 256, 0, s>>>(l, st.meta, st.slots, rule, lr, eps);
   TIPSK_LAUNCH_CHECK();
+  Mark(s);
   return 0;
 }
 

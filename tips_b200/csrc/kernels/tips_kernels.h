@@ -150,9 +150,18 @@ void* tipsk_device_executor_ptr(void);
 int tipsk_comm_fence(int channel, void* stream);
 int tipsk_table_init(float* shard, int64_t rows_local, int dim, int field, int rank, int nranks, int64_t rows_global,
                      uint64_t seed, float scale, void* stream);
-int tipsk_ps_configure(void* const* host_slabs, void* const* host_accs, int nranks, const uint64_t* host_field_off,
-                       const uint64_t* host_state_off, const int64_t* host_rows_per_shard, int nfields, int dim,
-                       uint64_t slots);
+/* Placement of row `id` of `field` under `nranks` ranks (ps_placement.h). */
+int tipsk_ps_place(int field, int64_t id, int nranks, int32_t* host_owner, int64_t* host_local_row);
+uint64_t tipsk_ps_acc_bytes(uint64_t slots, int dim);
+uint64_t tipsk_ps_inbox_bytes(int nranks, uint64_t inbox_cap, int dim);
+uint64_t tipsk_ps_ctl_bytes(void);
+int tipsk_ps_configure(void* const* host_slabs, void* const* host_inboxes, void* const* host_accs,
+                       void* const* host_ulists, void* const* host_ctls, int nranks, int nlocal,
+                       const uint64_t* host_field_off, const uint64_t* host_state_off,
+                       const int64_t* host_rows_per_shard, int nfields, int dim, uint64_t slots, uint64_t inbox_cap);
+int tipsk_ps_traffic(uint64_t* host_out2);
+int tipsk_ps_phase_timing(int enable);
+int tipsk_ps_phase_ms(float* host_out5);
 int tipsk_ps_status(int32_t* host_error, uint64_t* host_touched);
 int tipsk_ps_pull(const int64_t* const* host_ids, void* const* host_outs, int64_t batch, int64_t out_ld,
                   int64_t out_col0, int out_dtype, int fence, void* stream);

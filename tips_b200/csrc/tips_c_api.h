@@ -100,6 +100,9 @@ int tips_set_device_executor(void* fn);
 int tips_take_negotiated_order(char* out, int out_len);
 int tips_freeze_schedule(const char* names_newline_separated);
 int tips_thaw_schedule(void);
+/* Fails every collective in flight on this rank (status 4), forgets partial negotiations and frozen schedules;
+ * every rank calls it after a failed step, then the ranks meet on tips_barrier() before the next collective. */
+int tips_reset_collectives(void);
 
 /* ---- observability ----------------------------------------------------- */
 int tips_timeline_enable(int on);

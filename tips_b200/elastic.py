@@ -92,6 +92,11 @@ def run(train_fn: Callable[[State], object], max_retries: int = 3):
                 attempts += 1
                 if attempts > max_retries or e.code not in (5, 6):  # timeout, unavailable
                     raise
+                # the failed step left handles, counters, a frozen schedule and device flags behind: clear them on
+                # every rank (the ranks meet on a barrier inside), then roll back and adopt rank 0's state
+                runtime.reset_collectives()
+                if state.optimizer is not None and hasattr(state.optimizer, "reset"):
+                    state.optimizer.reset()
                 state.restore()
                 state.on_reset()
                 state.sync()
@@ -151,4 +156,5 @@ class UpdateEpochStateCallback(Callback):
         self.initial_epoch = self.state.epoch
 
     def on_epoch_end(self, epoch, logs=None):
-        self.state.epoch = self.initial_epoch + epoch + 1 if epoch < self.initial_epoch else epoch + 1
+        # `epoch` counts from 0 in every (re)started loop, as in the reference (tips/_keras/elastic.py:80-86)
+        self.state.epoch = self.initial_epoch + epoch + 1

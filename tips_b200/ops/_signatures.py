@@ -66,7 +66,14 @@ _PROTOS = {
     "tipsk_device_executor_ptr": (P, []),
     "tipsk_comm_fence": (I, [I, P]),
     "tipsk_table_init": (I, [P, L, I, I, I, I, L, U, F, P]),
-    "tipsk_ps_configure": (I, [PP, PP, I, POINTER(U), POINTER(U), POINTER(L), I, I, U]),
+    "tipsk_ps_place": (I, [I, L, I, POINTER(c_int32), POINTER(L)]),
+    "tipsk_ps_acc_bytes": (U, [U, I]),
+    "tipsk_ps_inbox_bytes": (U, [I, U, I]),
+    "tipsk_ps_ctl_bytes": (U, []),
+    "tipsk_ps_configure": (I, [PP, PP, PP, PP, PP, I, I, POINTER(U), POINTER(U), POINTER(L), I, I, U, U]),
+    "tipsk_ps_traffic": (I, [POINTER(U)]),
+    "tipsk_ps_phase_timing": (I, [I]),
+    "tipsk_ps_phase_ms": (I, [POINTER(F)]),
     "tipsk_ps_status": (I, [POINTER(c_int32), POINTER(U)]),
     "tipsk_ps_pull": (I, [PP, PP, L, L, L, I, I, P]),
     "tipsk_ps_push": (I, [PP, PP, L, L, L, I, F, I, F, F, P]),

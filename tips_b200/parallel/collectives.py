@@ -45,7 +45,7 @@ _handles_lock = threading.Lock()
 
 
 class _Handle:
-    __slots__ = ("id", "keep", "output", "post", "done_event", "alloc_cb", "gathered", "kind", "name")
+    __slots__ = ("id", "keep", "output", "post", "done_event", "ready_event", "alloc_cb", "gathered", "kind", "name")
 
     def __init__(self):
         self.id = 0
@@ -53,6 +53,7 @@ class _Handle:
         self.output = None
         self.post = None
         self.done_event = None
+        self.ready_event = None
         self.alloc_cb = None
         self.gathered = None
         self.kind = ""
@@ -105,10 +106,12 @@ def _enqueue(h: _Handle, kind: int, name: str, tensor_in, tensor_out, shape, dty
         op.ready_event = ready
         op.done_event = done
         h.done_event = done
+        h.ready_event = ready
     if alloc is not None:
         op.alloc = alloc
     hid = lib.tips_enqueue(ctypes.byref(op))
     if hid < 0:
+        _recycle_events(h)
         raise TipsError(f"{name}: {_lib.last_error()}", int(-hid))
     h.id = hid
     h.name = name
@@ -120,6 +123,38 @@ def _enqueue(h: _Handle, kind: int, name: str, tensor_in, tensor_out, shape, dty
 def poll(handle: _Handle) -> bool:
     """True once the collective behind `handle` has completed (or failed)."""
     return _lib.core().tips_poll(handle.id) != 1
+
+
+def _recycle_events(handle: _Handle) -> None:
+    """Return the CUDA events of a finished (or failed) device collective to the pool.  Safe once the engine has
+    answered the handle: its executor has issued the stream wait on `ready` and recorded `done` by then."""
+    if handle.done_event is None and handle.ready_event is None:
+        return
+    from . import device as _device
+    st = _device._state
+    for ev in (handle.ready_event, handle.done_event):
+        if ev is not None and st is not None:
+            st.recycle_event(ev)
+    handle.ready_event = handle.done_event = None
+
+
+def _check_device_status(wait: bool = False) -> None:
+    """Raise TipsError(code 5) if a kernel of the GPU data plane gave up on a bounded wait (a lost or late peer).
+
+    The status block lives in mapped host memory, so reading it costs nothing and does not wait for the device;
+    `wait` (or ``device_status_check="sync"``) first waits for the current stream, which makes the failing step
+    itself raise instead of a later one.  The status stays set until ``tips_b200.reset_collectives()``."""
+    from ..config import get_config
+    mode = get_config().device_status_check
+    if mode == "off":
+        return
+    from . import device as _device
+    st = _device._state
+    if st is None or st.window is None:
+        return
+    if wait or mode == "sync":
+        torch.cuda.current_stream().synchronize()
+    st.check_status(clear=False)
 
 
 def synchronize(handle: _Handle, timeout_s: float | None = None):
@@ -135,6 +170,8 @@ def synchronize(handle: _Handle, timeout_s: float | None = None):
             lib.tips_release(handle.id)
             with _handles_lock:
                 _handles.pop(handle.id, None)
+            handle.id = 0
+            _recycle_events(handle)
             raise TipsError(f"{handle.name}: {buf.value.decode()}", rc)
         if handle.kind == "allgather" and handle.gathered is not None:
             handle.output = handle.gathered[0]
@@ -144,8 +181,8 @@ def synchronize(handle: _Handle, timeout_s: float | None = None):
         if handle.done_event is not None:
             from . import device as _device
             _device.stream_wait_event(torch.cuda.current_stream().cuda_stream, handle.done_event)
-            _device.state().recycle_event(handle.done_event)
-            handle.done_event = None
+            _recycle_events(handle)
+            _check_device_status()
         handle.id = 0
     out = handle.output
     if handle.post is not None:
@@ -154,6 +191,20 @@ def synchronize(handle: _Handle, timeout_s: float | None = None):
         handle.output = out
     handle.keep = []
     return out
+
+
+def abandon(handle: _Handle) -> None:
+    """Forget a collective that will never be waited for (after a failed step): releases the engine handle if the
+    engine has answered it, and returns its events."""
+    lib = _lib.core()
+    if handle.id:
+        if lib.tips_poll(handle.id) != 1:
+            lib.tips_release(handle.id)
+            _recycle_events(handle)
+        with _handles_lock:
+            _handles.pop(handle.id, None)
+        handle.id = 0
+    handle.keep = []
 
 
 # ------------------------------------------------------------------ allreduce

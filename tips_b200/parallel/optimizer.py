@@ -195,10 +195,15 @@ class _DistributedMixin:
                     # no gradient at all on this rank: still take part with zeros so that ranks stay in step
                     pass
                 self._tips_launch(b)
+        timeout = get_config().collective_timeout_s
         for b in self._tips_buckets:
             if b.handle is not None:
-                C.synchronize(b.handle)
+                C.synchronize(b.handle, timeout if timeout > 0 else None)
                 b.handle = None
+        # a kernel that gave up on a peer skipped its reduction (and, with the update inside the allreduce, its
+        # update): stop here, before the optimizer applies gradients that were never combined
+        if any(b.grad.is_cuda for b in self._tips_buckets):
+            C._check_device_status()
         for p in self._tips_sparse:
             p.grad = C.sparse_allreduce(p.grad, name=f"tips.sparse.{id(p)}", op=self._tips_op)
         self._tips_sparse = []
@@ -276,6 +281,29 @@ class _DistributedMixin:
         if not self._tips_fused:
             # reduced gradients were consumed; drop the views so that the next backward
             # writes fresh gradients instead of accumulating into the bucket
+            for p in self._tips_params:
+                p.grad = None
+
+    def reset(self):
+        """Forget the step in progress after a failure: drop the handles of the buckets in flight, clear the
+        per-step counters and the frozen bucket order, so that the next backward pass starts a clean step that is
+        negotiated again.  Call it on every rank after ``tips_b200.reset_collectives()`` (``elastic.run`` does)."""
+        for b in self._tips_buckets:
+            if b.handle is not None:
+                C.abandon(b.handle)
+                b.handle = None
+            b.ready_count = 0
+            b.launched = False
+        for k in self._tips_pass_count:
+            self._tips_pass_count[k] = 0
+        self._tips_sparse = []
+        self._tips_synchronized = False
+        self._tips_should_sync = True
+        self._tips_frozen = False
+        if self._tips_fused:
+            for fs in self._flat:
+                fs.grads_packed = False
+        else:
             for p in self._tips_params:
                 p.grad = None
 

@@ -3,10 +3,12 @@
 The reference's parameter server keeps rows in host hash maps on server ranks and
 moves them through an RPC (tips/core/ps/sparse_table.h:38-185, ps_server.h:147-265,
 ps_client.h:78-130).  Here every rank is a server and a worker at once: a table's
-row ``id`` lives on rank ``id % N`` at local row ``id // N`` of a slab in
-peer-mapped device memory, ``pull`` is a lookup kernel that reads rows straight
-from the owner's HBM over NVLink, and ``push`` scatters gradients into the owner's
-accumulation table and applies the server-side optimizer there (csrc/kernels/ps.cu).
+row ``id`` lives at local row ``id // N`` of a slab in peer-mapped device memory on
+the rank given by a rotated round-robin rule (``place``; csrc/kernels/ps_placement.h),
+``pull`` is a lookup kernel that reads rows straight from the owner's HBM over NVLink,
+and ``push`` sums the duplicate ids of the batch locally, stores one row per distinct
+id into the owner's inbox, and the owner applies the server-side optimizer once per
+touched row (csrc/kernels/ps.cu).
 
 Rows exist from the start (a dense slab initialised to zero or to a seeded uniform),
 which is what the reference's lazy zero-initialisation on first pull amounts to
@@ -75,9 +77,14 @@ class ShardedEmbedding:
             while slots < 2 * expected_batch * num_fields:
                 slots *= 2
         self.slots = slots
-        acc_bytes = slots * 8 + slots * dim * 4
-        self.slabs, self.accs = self._allocate(slab_bytes, acc_bytes, st)
+        # rows one sender may send to one owner in a push: the worst case (every distinct row of a batch has the
+        # same owner), so a skewed batch can never overflow an inbox
+        self.inbox_cap = (expected_batch * num_fields + 1) // 2 * 2
         lib = base.K()
+        self._alloc_bytes = (slab_bytes, int(lib.tipsk_ps_acc_bytes(slots, dim)),
+                             int(lib.tipsk_ps_inbox_bytes(n, self.inbox_cap, dim)) if n > 1 else 0,
+                             int(lib.tipsk_ps_ctl_bytes()))
+        self._allocate(st)
         local = range(n) if self.emulated else [self.rank]
         for r in local:
             slab = self.slabs[r] if self.emulated else self.slabs[0]
@@ -92,31 +99,33 @@ class ShardedEmbedding:
         self._configure()
 
     # ------------------------------------------------------------------ set-up
-    def _allocate(self, slab_bytes, acc_bytes, st):
+    def _allocate(self, st):
+        """Table slab and inbox in peer-mapped memory; accumulation table, touched list and control words local."""
         n = self.size
-        if self.emulated:
-            slabs = [torch.empty(slab_bytes, dtype=torch.uint8, device=self.device) for _ in range(n)]
-            accs = [torch.zeros(acc_bytes, dtype=torch.uint8, device=self.device) for _ in range(n)]
-            self._slab_ptrs = [t.data_ptr() for t in slabs]
-            self._acc_ptrs = [t.data_ptr() for t in accs]
-            return slabs, accs
-        if n == 1:
-            slab = torch.empty(slab_bytes, dtype=torch.uint8, device=self.device)
-            acc = torch.zeros(acc_bytes, dtype=torch.uint8, device=self.device)
-            self._slab_ptrs, self._acc_ptrs = [slab.data_ptr()], [acc.data_ptr()]
-            return [slab], [acc]
+        slab_bytes, acc_bytes, inbox_bytes, ctl_bytes = self._alloc_bytes
+        nlocal = n if self.emulated else 1
+        dev = self.device
+        self.accs = [torch.zeros(acc_bytes, dtype=torch.uint8, device=dev) for _ in range(nlocal)]
+        self.ulists = [torch.zeros(self.slots, dtype=torch.int32, device=dev) for _ in range(nlocal)]
+        self.ctls = [torch.zeros(ctl_bytes, dtype=torch.uint8, device=dev) for _ in range(nlocal)]
+        if self.emulated or n == 1:
+            self.slabs = [torch.empty(slab_bytes, dtype=torch.uint8, device=dev) for _ in range(nlocal)]
+            self.inboxes = [torch.zeros(max(inbox_bytes, 16), dtype=torch.uint8, device=dev) for _ in range(nlocal)]
+            self._slab_ptrs = [t.data_ptr() for t in self.slabs]
+            self._inbox_ptrs = [t.data_ptr() for t in self.inboxes]
+            return
         import torch.distributed as dist
         import torch.distributed._symmetric_memory as symm_mem
         group = dist.group.WORLD
-        slab = symm_mem.empty(slab_bytes, dtype=torch.uint8, device=self.device)
+        slab = symm_mem.empty(slab_bytes, dtype=torch.uint8, device=dev)
         h1 = symm_mem.rendezvous(slab, group.group_name)
-        acc = symm_mem.empty(acc_bytes, dtype=torch.uint8, device=self.device)
-        h2 = symm_mem.rendezvous(acc, group.group_name)
-        acc.zero_()
+        inbox = symm_mem.empty(inbox_bytes, dtype=torch.uint8, device=dev)
+        h2 = symm_mem.rendezvous(inbox, group.group_name)
+        inbox.zero_()
         self._handles = (h1, h2)
+        self.slabs, self.inboxes = [slab], [inbox]
         self._slab_ptrs = [int(p) for p in h1.buffer_ptrs]
-        self._acc_ptrs = [int(p) for p in h2.buffer_ptrs]
-        return [slab], [acc]
+        self._inbox_ptrs = [int(p) for p in h2.buffer_ptrs]
 
     def _sync_ranks(self):
         if self.size > 1 and not self.emulated:
@@ -128,10 +137,12 @@ class ShardedEmbedding:
         global _active
         lib = base.K()
         n = self.size
-        base.check(lib.tipsk_ps_configure(base.ptr_array(self._slab_ptrs), base.ptr_array(self._acc_ptrs), n,
+        base.check(lib.tipsk_ps_configure(base.ptr_array(self._slab_ptrs), base.ptr_array(self._inbox_ptrs),
+                                          base.ptr_array(self.accs), base.ptr_array(self.ulists),
+                                          base.ptr_array(self.ctls), n, len(self.accs),
                                           base.u64_array(self.field_off), base.u64_array(self.state_off),
                                           base.i64_array([self.rows_per_shard] * self.num_fields), self.num_fields,
-                                          self.dim, self.slots), "ps_configure")
+                                          self.dim, self.slots, self.inbox_cap), "ps_configure")
         _active = self
 
     def _activate(self):
@@ -179,7 +190,16 @@ class ShardedEmbedding:
             raise RuntimeError("parameter-server push: accumulation table full; raise `slots`")
         if err.value == 2:
             raise RuntimeError("parameter-server: an id was negative or beyond the table")
+        if err.value == 3:
+            raise RuntimeError("parameter-server push: an owner's inbox is full; raise `expected_batch`")
         return int(touched.value)
+
+    def traffic(self):
+        """(rows sent to owners, rows that crossed NVLink) by synchronous pushes since the last call. Synchronises."""
+        self._activate()
+        out = (ctypes.c_uint64 * 2)()
+        base.check(base.K().tipsk_ps_traffic(out), "ps_traffic")
+        return int(out[0]), int(out[1])
 
     # ------------------------------------------------------------------ host views / checkpoint
     def local_shard(self, field: int, rank: Optional[int] = None, state: bool = False) -> torch.Tensor:
@@ -189,8 +209,30 @@ class ShardedEmbedding:
         nbytes = self.rows_per_shard * self.dim * 4
         return slab[off:off + nbytes].view(torch.float32).view(self.rows_per_shard, self.dim)
 
-    def owner_of(self, ids: torch.Tensor):
-        return ids % self.size, ids // self.size
+    def place(self, ids: torch.Tensor, field: int, world: Optional[int] = None):
+        """(owner rank, local row) of the rows `ids` of `field`: the rule of csrc/kernels/ps_placement.h."""
+        n = self.size if world is None else world
+        lrow = ids // n
+        rot = ((((lrow & 0xFFFFFFFF) * 0x9E3779B1) & 0xFFFFFFFF) >> 16) + field
+        return (ids % n + rot) % n, lrow
+
+    def global_ids(self, field: int, rank: int, world: Optional[int] = None, rows_per_shard: Optional[int] = None,
+                   device=None) -> torch.Tensor:
+        """Global row id held at every local row of `rank`'s shard of `field` (ids >= rows are padding)."""
+        n = self.size if world is None else world
+        lrow = torch.arange(self.rows_per_shard if rows_per_shard is None else rows_per_shard, dtype=torch.int64,
+                            device=device)
+        rot = ((((lrow & 0xFFFFFFFF) * 0x9E3779B1) & 0xFFFFFFFF) >> 16) + field
+        return lrow * n + (rank + n - rot % n) % n
+
+    def dense_table(self, field: int, state: bool = False) -> torch.Tensor:
+        """The whole [rows, dim] table of `field` (or its Adagrad state) assembled from the shards this process
+        can see: all of them when the ranks are emulated or there is one rank (tests, small tables)."""
+        assert self.emulated or self.size == 1
+        out = torch.zeros(self.rows_per_shard * self.size, self.dim, device=self.device)
+        for r in range(self.size):
+            out[self.global_ids(field, r, device=self.device)] = self.local_shard(field, r, state=state)
+        return out[:self.rows].clone()
 
     # ------------------------------------------------------------------ dumps
     # The reference can only dump a sparse table as text, one line per key ("<key>\tVec:\t<e> <e> ... \n",
@@ -209,7 +251,7 @@ class ShardedEmbedding:
         paths = []
         for r in self._ranks_here():
             path = f"{prefix}.rank{r}.bin"
-            header = {"format": "tips_b200.ps.v1", "rank": r, "world": self.size, "fields": self.num_fields,
+            header = {"format": "tips_b200.ps.v2", "rank": r, "world": self.size, "fields": self.num_fields,
                       "rows": self.rows, "rows_per_shard": self.rows_per_shard, "dim": self.dim,
                       "state": bool(self.has_state)}
             with open(path, "wb") as f:
@@ -227,7 +269,7 @@ class ShardedEmbedding:
 
     def load(self, prefix: str) -> None:
         """Read every `<prefix>.rank*.bin` written by `save` (by any number of ranks) and keep the rows this
-        process owns under the current sharding: id -> (rank id % N, local row id // N)."""
+        process owns under the current sharding (`place`)."""
         import glob
         import json
         import numpy as np
@@ -250,15 +292,16 @@ class ShardedEmbedding:
                             buf = np.frombuffer(f.read(cnt * self.dim * 4), dtype=np.float32).reshape(cnt, self.dim)
                             if state and not self.has_state:
                                 continue
-                            ids = (torch.arange(lo, lo + cnt, dtype=torch.int64) * old_n + old_r)
+                            ids = self.global_ids(fld, old_r, world=old_n, rows_per_shard=old_rows)[lo:lo + cnt]
                             valid = ids < self.rows
+                            owner, lrow = self.place(ids, fld)
                             for r in self._ranks_here():
-                                mine = valid & (ids % self.size == r)
+                                mine = valid & (owner == r)
                                 if not bool(mine.any()):
                                     continue
                                 rows = torch.from_numpy(buf.copy())[mine].to(self.device)
                                 dst = self.local_shard(fld, r, state=state)
-                                dst[(ids[mine] // self.size).to(self.device)] = rows
+                                dst[lrow[mine].to(self.device)] = rows
         if seen_world is None:
             raise ValueError("empty dump")
         torch.cuda.synchronize()
@@ -270,11 +313,11 @@ class ShardedEmbedding:
         with open(path, "w") as f:
             for r in self._ranks_here():
                 shard = self.local_shard(field, r).cpu()
+                keys = self.global_ids(field, r).tolist()
                 for lrow in range(self.rows_per_shard):
-                    key = lrow * self.size + r
-                    if key >= self.rows:
-                        break
-                    f.write(f"{key}\tVec:\t" + "".join(f"{float(v):g} " for v in shard[lrow]) + "\n")
+                    if keys[lrow] >= self.rows:
+                        continue
+                    f.write(f"{keys[lrow]}\tVec:\t" + "".join(f"{float(v):g} " for v in shard[lrow]) + "\n")
 
 
 class _LookupFn(torch.autograd.Function):

@@ -131,6 +131,22 @@ def barrier() -> None:
     _check(_lib.core().tips_barrier(), "barrier")
 
 
+def reset_collectives() -> None:
+    """Bring the collective machinery back to a clean state after a failed step, on every rank: collectives still
+    in flight fail with status 4, partial negotiations and the frozen bucket order are forgotten, the flags, epochs
+    and error state of the GPU data plane are cleared, and the ranks meet on a host barrier before any of them
+    issues the next collective.  Raises if a rank does not arrive (the job cannot continue with the same ranks)."""
+    _require_init()
+    lib = _lib.core()
+    _check(-abs(lib.tips_reset_collectives()), "reset_collectives")
+    if _device_state is not None and _device_state.window is not None:
+        k = _lib.kernels()
+        if k.tipsk_comm_reset() != 0:
+            raise TipsError("tipsk_comm_reset: " + k.tipsk_last_error().decode(), 7)
+    if lib.tips_size() > 1:
+        barrier()
+
+
 def device_state():
     return _device_state
 

@@ -103,6 +103,27 @@ def test_stem_convolution(n, h, w):
     assert (conv.weight.grad.float() - wr.grad).abs().max() <= 2e-2 * sw
 
 
+def test_stem_takes_an_fp32_nchw_image():
+    """The stem fed an fp32 NCHW batch (layout change and cast inside its padding copy) gives the same output and
+    weight gradient as the stem fed the bf16 channels-last copy of that batch."""
+    from tips_b200.ops.conv import Conv2d
+    dev = torch.device("cuda", 0)
+    torch.manual_seed(5)
+    conv = Conv2d(3, 64, 7, stride=2, padding=3).to(dev).to(torch.bfloat16)
+    raw = torch.randn(3, 3, 62, 94, device=dev)
+    x = raw.to(torch.bfloat16).contiguous(memory_format=torch.channels_last)
+    y0 = conv(x)
+    dy = (torch.randn_like(y0.float()) * 0.1).to(torch.bfloat16)
+    y0.backward(dy)
+    g0 = conv.weight.grad.clone()
+    conv.weight.grad = None
+    y1 = conv(raw)
+    y1.backward(dy)
+    assert _status() == 0
+    assert y1.dtype == torch.bfloat16 and torch.equal(y0, y1)
+    assert torch.equal(g0, conv.weight.grad)
+
+
 def test_conv_module_falls_back_for_other_filters():
     from tips_b200.ops.conv import Conv2d
     dev = torch.device("cuda", 0)

@@ -42,9 +42,13 @@ def test_pull_push_single_rank(rule, dim):
     assert torch.equal(out, ref)
     out16 = t.pull(ids, dtype=torch.bfloat16)
     assert torch.equal(out16, ref.to(torch.bfloat16))
+    assert torch.equal(t.pull(ids, dtype=torch.float32, index=True), ref)      # distinct rows fetched once
+    assert torch.equal(t.pull(ids, dtype=torch.bfloat16, index=True), ref.to(torch.bfloat16))
     for step in range(2):
         grads = torch.randn(batch, fields * dim, device=dev)
-        t.push(ids, grads, grad_scale=0.5)
+        if step == 1:
+            t.pull(ids, dtype=torch.float32, index=True)
+        t.push(ids, grads, grad_scale=0.5, reuse_index=step == 1)
         _reference_update(ws, ss, [ids], [grads * 0.5], rule, 0.1, t.eps, dim)
     assert t.check() > 0
     got, got_s = _dense_tables(t, fields, rows, dim)
@@ -89,8 +93,9 @@ def test_pull_push_emulated_ranks():
         device.teardown(st)
 
 
+@pytest.mark.parametrize("indexed", [False, True])
 @pytest.mark.parametrize("ranks", [2, 4, 8])
-def test_push_with_mostly_duplicate_ids_emulated(ranks):
+def test_push_with_mostly_duplicate_ids_emulated(ranks, indexed):
     """Three synchronous steps on 2, 4 and 8 emulated ranks with ids drawn from 40 hot rows for 70 % of the batch
     (so most of every batch is duplicates, within a rank and across ranks): the tables equal the dense model, the
     number of rows sent to owners is the number of distinct ids per rank, not the batch size."""
@@ -106,27 +111,34 @@ def test_push_with_mostly_duplicate_ids_emulated(ranks):
                              expected_batch=batch, device=dev)
         ws, ss = _dense_tables(t, fields, rows, dim)
         torch.manual_seed(7)
-        distinct = 0
+        total_distinct = 0
         for step in range(3):
-            ids = []
+            ids, distinct = [], 0
             for r in range(ranks):
                 hot = torch.randint(0, 40, (batch, fields), device=dev)
                 cold = torch.randint(0, rows, (batch, fields), device=dev)
                 ids.append(torch.where(torch.rand(batch, fields, device=dev) < 0.7, hot, cold))
                 distinct += sum(int(ids[-1][:, f].unique().numel()) for f in range(fields))
-            outs = t.pull(ids, dtype=torch.float32)
+            total_distinct += distinct
+            outs = t.pull(ids, dtype=torch.float32, index=indexed)
             for r in range(ranks):
                 ref = torch.cat([ws[f][ids[r][:, f]] for f in range(fields)], dim=1)
                 assert torch.allclose(outs[r], ref, atol=3e-4, rtol=1e-4)
+            pulls = 1
+            if indexed and step == 1:
+                t.pull(ids, dtype=torch.bfloat16, index=True)   # an index that nothing consumes is dropped
+                outs = t.pull(ids, dtype=torch.float32, index=True)
+                pulls = 3
             grads = [torch.randn(batch, fields * dim, device=dev).to(torch.bfloat16) for _ in range(ranks)]
-            t.push(ids, grads, grad_scale=1.0 / ranks)
+            t.push(ids, grads, grad_scale=1.0 / ranks, reuse_index=indexed)
             _reference_update(ws, ss, ids, [g.float() / ranks for g in grads], "adagrad", 0.05, t.eps, dim)
+            sent, remote, fetched = t.traffic()
+            assert sent == distinct, (sent, distinct)
+            assert 0 < remote < sent
+            assert fetched == (pulls * remote if indexed else 0)
         t.check()
         st.check_status()
-        sent, remote = t.traffic()
-        assert sent == distinct, (sent, distinct)
-        assert 0 < remote < sent
-        assert distinct < 0.6 * 3 * ranks * batch * fields
+        assert total_distinct < 0.6 * 3 * ranks * batch * fields
         got, got_s = _dense_tables(t, fields, rows, dim)
         for f in range(fields):
             assert torch.allclose(got[f], ws[f], atol=3e-4, rtol=1e-4)

@@ -114,3 +114,67 @@ def _dump(rank, size, folder, servers, binary, phase):
 def test_dump_and_reload_under_another_sharding(tmp_path, binary):
     run_ranks(_dump, 3, str(tmp_path), [0, 1, 2], binary, "write")
     run_ranks(_dump, 3, str(tmp_path), [1, 2], binary, "read")
+
+
+def _dense_table(rank, size, servers, rule, tmp):
+    """Dense table over `servers`: assign, pull by range, pushes from every rank, rule numerics, dump and reload
+    under another sharding."""
+    import tips_b200 as tips
+    from tips_b200.ps.host import HostDenseTable, Route
+    n, lr, eps = 1003, 0.1, 1e-8
+    table = HostDenseTable("d_" + rule, n, route=Route(servers=servers), optimizer=rule, lr=lr, eps=eps, local_shards=2)
+    init = np.linspace(-1.0, 1.0, n).astype(np.float32)
+    if rank == 0:
+        table.assign(init)
+    tips.barrier()
+    assert np.array_equal(table.pull(), init)
+    assert np.array_equal(table.pull(100, 777), init[100:777])   # a range that crosses several shards
+    cnt, total = table.local_count_and_sum()
+    counts = tips.allgather_object(cnt)
+    assert sum(counts) == n
+    assert all((c > 0) == (r in servers) for r, c in enumerate(counts))
+    assert abs(sum(tips.allgather_object(total)) - float(init.astype(np.float64).sum())) < 1e-3
+    tips.barrier()
+    # every rank pushes its own gradient for a different range, one after the other (order of updates is defined)
+    w = init.astype(np.float64).copy()
+    acc = np.zeros(n)
+    rng = np.random.default_rng(3)
+    for step in range(2):
+        for r in range(size):
+            lo, hi = 50 * r, n - 31 * r
+            g = rng.standard_normal(hi - lo).astype(np.float32)
+            if rank == r:
+                table.push(g, begin=lo)
+            tips.barrier()
+            g64 = g.astype(np.float64)
+            if rule == "sgd":
+                w[lo:hi] -= lr * g64
+            elif rule == "adagrad":
+                acc[lo:hi] += g64 * g64
+                w[lo:hi] -= lr * g64 / (np.sqrt(acc[lo:hi]) + eps)
+            else:
+                w[lo:hi] = lr * g64
+    got = table.pull()
+    assert np.allclose(got, w, atol=2e-5), np.abs(got - w).max()
+    with pytest.raises(ValueError):
+        table.pull(5, n + 1)
+    # dump: every server writes its shards; reload into a table sharded over ONE server
+    path = os.path.join(tmp, f"dense_{rule}.rank{rank}.bin")
+    if rank in servers:
+        table.save(path)
+    tips.barrier()
+    single = HostDenseTable("d2_" + rule, n, route=Route(servers=[size - 1]), optimizer=rule, lr=lr)
+    for r in servers:
+        single.load(os.path.join(tmp, f"dense_{rule}.rank{r}.bin"))
+    tips.barrier()
+    assert np.allclose(single.pull(), got)
+    c = table.counters()
+    assert (c["elements_pulled"] > 0) == (rank in servers)
+    single.close()
+    table.close()
+
+
+@pytest.mark.parametrize("servers,rule", [([0], "sgd"), ([0, 1], "adagrad"), ([0, 1, 2], "sgd"),
+                                          ([1, 2], "literal_reference")])
+def test_dense_table(tmp_path, servers, rule):
+    run_ranks(_dense_table, 3, servers, rule, str(tmp_path))

@@ -5,8 +5,8 @@ push, with the rows and bytes that cross NVLink against the rows of the batch.
     python -m tips_b200.bench.ps_phases [--rows 10000000] [--iters 20]                      (one GPU)
     python -m torch.distributed.run --nproc-per-node N -m tips_b200.bench.ps_phases ...    (N GPUs)
 
-Each phase is timed with CUDA events recorded on the launching stream between the kernels of an eager push
-(tipsk_ps_phase_timing); the figures are the max over ranks of the per-rank mean over `iters` steps after 5
+Each phase is timed with CUDA events recorded on the launching stream between the kernels of an eager pull and
+push (tipsk_ps_phase_timing); the figures are the max over ranks of the per-rank mean over `iters` steps after 5
 warm-up steps.  Every step uses a fresh batch of ids, so the rows touched differ from step to step.
 """
 from __future__ import annotations
@@ -23,6 +23,7 @@ from tips_b200.ops import base
 from tips_b200.ps.gpu import ShardedEmbedding
 
 PHASES = ("scatter", "send", "fence", "reduce", "apply")
+PULL_PHASES = ("index", "pull fence", "fetch", "expand")
 
 
 def _max_over_ranks(values):
@@ -46,6 +47,7 @@ def main(argv=None):
     ap.add_argument("--fields", type=int, default=26)
     ap.add_argument("--dim", type=int, default=64)
     ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--plain", action="store_true", help="plain pull and push (no index shared between them)")
     ap.add_argument("--out", default="")
     a = ap.parse_args(argv)
     tips.init()
@@ -62,44 +64,53 @@ def main(argv=None):
     distinct = sum(int(b[:, f].unique().numel()) for b in batches[warm:] for f in range(a.fields))
     base.check(lib.tipsk_ps_phase_timing(1), "phase_timing")
     acc = [0.0] * 5
+    pacc = [0.0] * 4
     pull_ms = 0.0
     step_ms = 0.0
     e = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
     ms5 = (ctypes.c_float * 5)()
+    ms4 = (ctypes.c_float * 4)()
     for i, ids in enumerate(batches):
         if i == warm:
             table.check()
             table.traffic()
         e[0].record()
-        table.pull(ids, out=out)
+        table.pull(ids, out=out, index=not a.plain)
         e[1].record()
-        table.push(ids, grads, grad_scale=1.0 / n)
+        table.push(ids, grads, grad_scale=1.0 / n, reuse_index=not a.plain)
         e[2].record()
         torch.cuda.synchronize()
         if i >= warm:
             base.check(lib.tipsk_ps_phase_ms(ms5), "phase_ms")
             for k in range(5):
                 acc[k] += ms5[k]
+            base.check(lib.tipsk_ps_pull_phase_ms(ms4), "pull_phase_ms")
+            for k in range(4):
+                pacc[k] += ms4[k]
             pull_ms += e[0].elapsed_time(e[1])
             step_ms += e[0].elapsed_time(e[2])
     base.check(lib.tipsk_ps_phase_timing(0), "phase_timing")
     applied = table.check()
-    sent, remote = table.traffic()
+    sent, remote, fetched = table.traffic()
     it = a.iters
-    per = _max_over_ranks([1e3 * v / it for v in acc] + [1e3 * pull_ms / it, 1e3 * step_ms / it])
-    tot = _sum_over_ranks([sent, remote, applied, distinct])
+    per = _max_over_ranks([1e3 * v / it for v in acc] + [1e3 * pull_ms / it, 1e3 * step_ms / it] +
+                          [1e3 * v / it for v in pacc])
+    tot = _sum_over_ranks([sent, remote, applied, distinct, fetched])
     if rank == 0:
         row_bytes = a.dim * 4 + 8
         items = a.batch * a.fields
         res = {"n_gpus": n, "rows_per_table": a.rows, "batch_per_gpu": a.batch, "fields": a.fields, "dim": a.dim,
-               "iters": it, "us": {**{p: round(per[k], 1) for k, p in enumerate(PHASES)},
-                                   "pull (with its fence)": round(per[5], 1), "pull + push": round(per[6], 1)},
+               "iters": it, "indexed": not a.plain,
+               "us": {**{p: round(per[7 + k], 1) for k, p in enumerate(PULL_PHASES) if not a.plain},
+                      "pull (with its fence)": round(per[5], 1),
+                      **{p: round(per[k], 1) for k, p in enumerate(PHASES)}, "pull + push": round(per[6], 1)},
                "per_step_per_gpu": {
                    "items (sample, field)": items,
                    "distinct ids in the batch": round(tot[3] / it / n),
-                   "rows sent to owners": round(tot[0] / it / n),
-                   "rows over NVLink": round(tot[1] / it / n),
+                   "rows pulled over NVLink": round(tot[4] / it / n) if not a.plain else round(items * (n - 1) / n),
+                   "rows pushed over NVLink": round(tot[1] / it / n),
                    "rows applied by the owner": round(tot[2] / it / n),
+                   "NVLink bytes (pull)": round((tot[4] / it / n if not a.plain else items * (n - 1) / n) * a.dim * 4),
                    "NVLink bytes (push)": round(tot[1] / it / n * row_bytes),
                    "bytes if every item were sent": round(items * row_bytes * (n - 1) / n)}}
         line = json.dumps(res)

@@ -27,8 +27,9 @@ def _launch_count() -> int:
     return n
 
 
-def timed(step_fn, steps: int, warmup: int):
-    """Run `warmup` untimed and `steps` timed calls of step_fn between CUDA events; max over ranks."""
+def timed(step_fn, steps: int, warmup: int, inner: int = 1):
+    """Run `warmup` untimed and `steps * inner` timed calls of step_fn between CUDA events; max over ranks.
+    Returns (milliseconds for the whole timed region, launcher calls made inside it)."""
     for _ in range(warmup):
         step_fn()
     torch.cuda.synchronize()
@@ -37,7 +38,7 @@ def timed(step_fn, steps: int, warmup: int):
     l0 = _launch_count()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    for _ in range(steps):
+    for _ in range(steps * inner):
         step_fn()
     e1.record()
     torch.cuda.synchronize()
@@ -45,6 +46,21 @@ def timed(step_fn, steps: int, warmup: int):
     tips.barrier()
     ms = _max_over_ranks(e0.elapsed_time(e1))
     return ms, l1 - l0
+
+
+def inner_repeats(step_fn, steps: int, target_ms: float = 1200.0, probe: int = 20) -> int:
+    """How many times a short step must be repeated per counted step so that the timed region lasts about
+    `target_ms`; measured on `probe` calls, the same value on every rank."""
+    torch.cuda.synchronize()
+    tips.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(probe):
+        step_fn()
+    e1.record()
+    torch.cuda.synchronize()
+    per_step = max(_max_over_ranks(e0.elapsed_time(e1)) / probe, 1e-3)
+    return max(1, int(round(target_ms / (per_step * max(steps, 1)) + 0.5)))
 
 
 class _LossReader:
@@ -111,6 +127,17 @@ class _Prefetcher:
         return cur
 
 
+def _image_batches(batch: int, count: int):
+    """`count` pinned host batches of the named input: fp32 N(0,1) images in NCHW layout, labels uniform over 1000."""
+    g = torch.Generator().manual_seed(100 + tips.rank())
+    host = []
+    for _ in range(count):
+        x = torch.randn(batch, 3, 224, 224, generator=g)
+        y = torch.randint(0, 1000, (batch,), generator=g)
+        host.append((x.pin_memory(), y.pin_memory()))
+    return host
+
+
 def run_resnet50(batch: int, steps: int, warmup: int, fused_update=None):
     from tips_b200.models.resnet50 import resnet50
     from tips_b200.ops.optim import FusedSGD
@@ -122,13 +149,8 @@ def run_resnet50(batch: int, steps: int, warmup: int, fused_update=None):
     opt = FusedSGD(model.parameters(), lr=0.1, momentum=0.9, weight_decay=1e-4)
     opt = tips.DistributedOptimizer(opt, named_parameters=model.named_parameters(), fused_update=fused_update)
     tips.broadcast_parameters(model.state_dict(), root_rank=0, optimizer=opt)
-    g = torch.Generator().manual_seed(100 + tips.rank())
-    nhost = 3
-    host = []
-    for _ in range(nhost):
-        x = torch.randn(batch, 3, 224, 224, generator=g).to(torch.bfloat16).contiguous(memory_format=torch.channels_last)
-        y = torch.randint(0, 1000, (batch,), generator=g)
-        host.append((x.pin_memory(), y.pin_memory()))
+    host = _image_batches(batch, 3)
+    # inputs stay fp32 NCHW on the device as well: the stem's padding copy changes the layout and casts to bf16
     x_dev = host[0][0].to(dev, non_blocking=True)
     y_dev = host[0][1].to(dev, non_blocking=True)
 
@@ -177,14 +199,14 @@ def run_resnet50_floor(batch: int, steps: int, warmup: int):
         model = torch.nn.parallel.DistributedDataParallel(model, device_ids=[dev.index], bucket_cap_mb=64,
                                                           gradient_as_bucket_view=True)
     opt = torch.optim.SGD(model.parameters(), lr=0.1, momentum=0.9, weight_decay=1e-4)
-    g = torch.Generator().manual_seed(100 + tips.rank())
-    x = torch.randn(batch, 3, 224, 224, generator=g).to(torch.bfloat16).contiguous(memory_format=torch.channels_last)
-    y = torch.randint(0, 1000, (batch,), generator=g)
-    host = [(x.pin_memory(), y.pin_memory())] * 3
-    x_dev, y_dev = x.to(dev), y.to(dev)
+    host = _image_batches(batch, 3)
+    x_dev, y_dev = host[0][0].to(dev), host[0][1].to(dev)
+
+    def prep(x):  # the same fp32 NCHW input as the product arm; layout change and cast by library kernels
+        return x.to(torch.bfloat16).contiguous(memory_format=torch.channels_last)
 
     def step_resident():
-        loss = torch.nn.functional.cross_entropy(model(x_dev).float(), y_dev)
+        loss = torch.nn.functional.cross_entropy(model(prep(x_dev)).float(), y_dev)
         loss.backward()
         opt.step()
         opt.zero_grad(set_to_none=True)
@@ -197,7 +219,7 @@ def run_resnet50_floor(batch: int, steps: int, warmup: int):
 
     def step_e2e():
         xb, yb = pre.get()
-        loss = torch.nn.functional.cross_entropy(model(xb).float(), yb)
+        loss = torch.nn.functional.cross_entropy(model(prep(xb)).float(), yb)
         loss.backward()
         opt.step()
         opt.zero_grad(set_to_none=True)
@@ -207,7 +229,10 @@ def run_resnet50_floor(batch: int, steps: int, warmup: int):
     last["loss"] = reader.drain()
     e2e = {"value": batch * tips.size() * steps / (ms2 / 1e3), "unit": "images/s", "ms_per_step": ms2 / steps,
            "h2d_bytes_per_step": pre.bytes_per_step, "d2h_bytes_per_step": 4, "last_loss": last.get("loss")}
-    return {"value": batch * tips.size() * steps / (ms / 1e3), "ms_per_step": ms / steps, "gpu_launches": 0, "e2e": e2e}
+    out = {"value": batch * tips.size() * steps / (ms / 1e3), "ms_per_step": ms / steps, "gpu_launches": 0, "e2e": e2e}
+    del pre, model, opt, x_dev, y_dev
+    release_cached_memory()
+    return out
 
 
 def release_cached_memory():
@@ -228,17 +253,31 @@ def run_ctr(batch: int, rows: int, steps: int, warmup: int, graph: bool = True, 
         raise MemoryError(f"CTR tables need {need >> 30} GiB on this GPU, {free >> 30} GiB are free")
     trainer = CtrTrainer(num_fields=26, rows_per_table=rows, dim=64, dense_features=13, hidden=(512, 256),
                          device=dev, expected_batch=batch, graph=graph, sync_ps=sync_ps)
-    nhost = 3
-    host = [tuple(t.pin_memory() for t in synthetic_ctr_batch(batch, 26, rows, 13, seed=7 * tips.rank() + i))
+    nhost = 8
+    host = [tuple(t.pin_memory() for t in synthetic_ctr_batch(batch, 26, rows, 13, seed=7 * tips.rank() + 1000 * i))
             for i in range(nhost)]
-    resident = [t.to(dev) for t in host[0]]
+    # eight different batches in rotation: the ids, hence the rows of the 133 GB of tables that a step touches, change
+    # from step to step
+    resident = [[t.to(dev) for t in b] for b in host]
+    cursor = {"i": 0}
 
     def step_resident():
-        return trainer.train_step(*resident)
+        b = resident[cursor["i"] % nhost]
+        cursor["i"] += 1
+        return trainer.train_step(*b)
 
-    ms, launches = timed(step_resident, steps, warmup)
+    # kernels per step: launcher calls of one eager step (the captured graph replays exactly those)
+    l0 = _launch_count()
+    step_resident()
+    per_step_launches = _launch_count() - l0
+    for _ in range(max(warmup, 4)):
+        step_resident()
+    inner = inner_repeats(step_resident, steps)
+    ms, launches = timed(step_resident, steps, 2, inner)
+    if graph:
+        launches = per_step_launches * steps * inner
     trainer.check()
-    value = batch * tips.size() * steps / (ms / 1e3)
+    value = batch * tips.size() * steps * inner / (ms / 1e3)
     pre = _Prefetcher(host)
     last = {}
     reader = _LossReader()
@@ -247,12 +286,127 @@ def run_ctr(batch: int, rows: int, steps: int, warmup: int, graph: bool = True, 
         ids, dense, labels = pre.get()
         reader.push(trainer.train_step(ids, dense, labels))
 
-    ms2, _ = timed(step_e2e, steps, max(5, warmup))
+    for _ in range(max(5, warmup)):
+        step_e2e()
+    inner2 = inner_repeats(step_e2e, steps)
+    ms2, _ = timed(step_e2e, steps, 2, inner2)
     last["loss"] = reader.drain()
     trainer.check()
-    e2e = {"value": batch * tips.size() * steps / (ms2 / 1e3), "unit": "samples/s", "ms_per_step": ms2 / steps,
+    e2e = {"value": batch * tips.size() * steps * inner2 / (ms2 / 1e3), "unit": "samples/s",
+           "ms_per_step": ms2 / (steps * inner2), "timed_region_ms": ms2, "repeats_per_step": inner2,
            "h2d_bytes_per_step": pre.bytes_per_step, "d2h_bytes_per_step": 4, "last_loss": last.get("loss")}
-    return {"value": value, "ms_per_step": ms / steps, "gpu_launches": launches, "e2e": e2e}
+    out = {"value": value, "ms_per_step": ms / (steps * inner), "timed_region_ms": ms, "repeats_per_step": inner,
+           "gpu_launches": launches, "e2e": e2e}
+    trainer.close()
+    del pre, trainer, resident
+    release_cached_memory()
+    return out
+
+
+class _FloorCtr:
+    """Library floor of the parameter-server workload: the same tables, sharded over the ranks by `id % N`, looked
+    up with torch's embedding kernel, exchanged with NCCL all-to-all, updated by torch's sparse Adagrad; the MLP is
+    torch Linear layers (cuBLAS) under DistributedDataParallel with torch Adam."""
+
+    def __init__(self, fields, rows, dim, dense, hidden, dev):
+        import torch.distributed as dist
+        self.world, self.rank = tips.size(), tips.rank()
+        self.fields, self.dim, self.dense, self.dev = fields, dim, dense, dev
+        self.rps = (rows + self.world - 1) // self.world
+        self.table = torch.empty(fields * self.rps, dim, device=dev).uniform_(-0.05, 0.05).requires_grad_()
+        self.topt = torch.optim.Adagrad([self.table], lr=0.05)
+        dims = [fields * dim + dense] + list(hidden)
+        layers = []
+        for i in range(len(hidden)):
+            layers += [torch.nn.Linear(dims[i], dims[i + 1]), torch.nn.ReLU()]
+        layers.append(torch.nn.Linear(dims[-1], 1))
+        torch.manual_seed(17)
+        self.mlp = torch.nn.Sequential(*layers).to(dev).to(torch.bfloat16)
+        if self.world > 1:
+            self.mlp = torch.nn.parallel.DistributedDataParallel(self.mlp, device_ids=[dev.index])
+        self.mopt = torch.optim.Adam(self.mlp.parameters(), lr=1e-3)
+        self.dist = dist
+        self.field_base = (torch.arange(fields, device=dev) * self.rps).view(1, fields)
+
+    def lookup(self, ids):
+        n = self.world
+        key = (ids // n + self.field_base).view(-1)
+        if n == 1:
+            return torch.nn.functional.embedding(key, self.table, sparse=True)
+        import torch.distributed.nn.functional as dfn
+        owner = (ids % n).view(-1)
+        order = torch.argsort(owner, stable=True)
+        send = torch.bincount(owner, minlength=n)
+        recv = torch.empty_like(send)
+        self.dist.all_to_all_single(recv, send)
+        send_l, recv_l = send.tolist(), recv.tolist()
+        keys_in = torch.empty(sum(recv_l), dtype=key.dtype, device=self.dev)
+        self.dist.all_to_all_single(keys_in, key[order], recv_l, send_l)
+        rows_out = torch.nn.functional.embedding(keys_in, self.table, sparse=True)
+        back = torch.empty(key.numel(), self.dim, device=self.dev)
+        back = dfn.all_to_all_single(back, rows_out, send_l, recv_l)
+        emb = torch.empty_like(back)
+        return emb.index_copy(0, order, back)  # the gradient flows back through the all-to-all
+
+    def step(self, ids, dense, labels):
+        emb = self.lookup(ids).view(ids.shape[0], self.fields * self.dim)
+        if self.world > 1:
+            emb.register_hook(lambda g: g / self.world)
+        x = torch.cat([emb.to(torch.bfloat16), dense], dim=1)
+        logit = self.mlp(x).view(-1).float()
+        loss = torch.nn.functional.binary_cross_entropy_with_logits(logit, labels)
+        loss.backward()
+        self.topt.step()
+        self.mopt.step()
+        self.topt.zero_grad(set_to_none=True)
+        self.mopt.zero_grad(set_to_none=True)
+        return loss.detach()
+
+
+def run_ctr_floor(batch: int, rows: int, steps: int, warmup: int):
+    from tips_b200.models.ctr import synthetic_ctr_batch
+    dev = torch.device("cuda", torch.cuda.current_device())
+    release_cached_memory()
+    need = 26 * ((rows + tips.size() - 1) // tips.size()) * 64 * 4 * 2 + (8 << 30)
+    free, _ = torch.cuda.mem_get_info()
+    if need > free:
+        raise MemoryError(f"CTR floor tables need {need >> 30} GiB on this GPU, {free >> 30} GiB are free")
+    model = _FloorCtr(26, rows, 64, 13, (512, 256), dev)
+    nhost = 8
+    host = [tuple(t.pin_memory() for t in synthetic_ctr_batch(batch, 26, rows, 13, seed=7 * tips.rank() + 1000 * i))
+            for i in range(nhost)]
+    resident = [[t.to(dev) for t in b] for b in host]
+    cursor = {"i": 0}
+
+    def step_resident():
+        b = resident[cursor["i"] % nhost]
+        cursor["i"] += 1
+        return model.step(*b)
+
+    for _ in range(max(warmup, 4)):
+        step_resident()
+    inner = inner_repeats(step_resident, steps, probe=10)
+    ms, _ = timed(step_resident, steps, 2, inner)
+    pre = _Prefetcher(host)
+    reader = _LossReader()
+
+    def step_e2e():
+        ids, dense, labels = pre.get()
+        reader.push(model.step(ids, dense, labels))
+
+    for _ in range(5):
+        step_e2e()
+    inner2 = inner_repeats(step_e2e, steps, probe=10)
+    ms2, _ = timed(step_e2e, steps, 2, inner2)
+    loss = reader.drain()
+    e2e = {"value": batch * tips.size() * steps * inner2 / (ms2 / 1e3), "unit": "samples/s",
+           "ms_per_step": ms2 / (steps * inner2), "timed_region_ms": ms2, "repeats_per_step": inner2,
+           "h2d_bytes_per_step": pre.bytes_per_step, "d2h_bytes_per_step": 4, "last_loss": loss}
+    out = {"value": batch * tips.size() * steps * inner / (ms / 1e3), "ms_per_step": ms / (steps * inner),
+           "timed_region_ms": ms, "repeats_per_step": inner, "gpu_launches": 0, "e2e": e2e}
+    del pre, model, resident
+    release_cached_memory()
+    return out
 
 
 def run_bert(batch: int, seq: int, steps: int, warmup: int, layers: int = 24, fused_update=None):

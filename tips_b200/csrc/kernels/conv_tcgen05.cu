@@ -832,6 +832,31 @@ StemPadKernel(const __nv_bfloat16* __restrict__ x, uint4* __restrict__ xp, int n
   }
 }
 
+// Same for an fp32 image in NCHW layout, as an input pipeline delivers it: the layout change and the cast to
+// bf16 happen inside the copy that the stem needs anyway.
+__global__ void __launch_bounds__(256)
+StemPadNchwKernel(const float* __restrict__ x, uint4* __restrict__ xp, int n, int h, int w, int hp, int wp) {
+  const int64_t total = static_cast<int64_t>(n) * hp * wp;
+  const int64_t plane = static_cast<int64_t>(h) * w;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int pw = static_cast<int>(i % wp);
+    const int ph = static_cast<int>((i / wp) % hp);
+    const int in = static_cast<int>(i / (static_cast<int64_t>(wp) * hp));
+    const int ih = ph - 3, iw = pw - 3;
+    alignas(16) __nv_bfloat16 v[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] = __float2bfloat16_rn(0.f);
+    if (ih >= 0 && ih < h && iw >= 0 && iw < w) {
+      const float* src = x + static_cast<int64_t>(in) * 3 * plane + static_cast<int64_t>(ih) * w + iw;
+      v[0] = __float2bfloat16_rn(src[0]);
+      v[1] = __float2bfloat16_rn(src[plane]);
+      v[2] = __float2bfloat16_rn(src[2 * plane]);
+    }
+    xp[i] = *reinterpret_cast<const uint4*>(v);
+  }
+}
+
 // The two row-parity views of the padded stem input (windows of 8 pixels = 64 elements every 2 pixels) and the
 // seven filter-row taps.
 void StemViewsAndTaps(const void* xp, int n, int hp, int wp, int ho, int wo, View* views, ConvTap* taps) {
@@ -999,6 +1024,18 @@ int tipsk_stem_pad(const void* x, void* xp, int n, int h, int w, void* stream) {
   StemPadKernel<<<static_cast<int>(std::min<int64_t>((total + 255) / 256, NumSMs() * 16)), 256, 0,
                   static_cast<cudaStream_t>(stream)>>>(static_cast<const __nv_bfloat16*>(x),
                                                        static_cast<uint4*>(xp), n, h, w, hp, wp);
+  TIPSK_LAUNCH_CHECK();
+  return 0;
+}
+
+/* x: [n, 3, h, w] fp32 (NCHW, contiguous) -> xp: the padded 8-channel bf16 buffer of the stem. */
+int tipsk_stem_pad_nchw_f32(const void* x, void* xp, int n, int h, int w, void* stream) {
+  int hp, wp, ho, wo;
+  tipsk_stem_geometry(h, w, &hp, &wp, &ho, &wo);
+  const int64_t total = static_cast<int64_t>(n) * hp * wp;
+  StemPadNchwKernel<<<static_cast<int>(std::min<int64_t>((total + 255) / 256, NumSMs() * 16)), 256, 0,
+                      static_cast<cudaStream_t>(stream)>>>(static_cast<const float*>(x), static_cast<uint4*>(xp), n, h,
+                                                           w, hp, wp);
   TIPSK_LAUNCH_CHECK();
   return 0;
 }

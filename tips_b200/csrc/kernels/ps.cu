@@ -17,22 +17,35 @@
 // system-scope loads, converts and writes it into the consumer's input matrix at
 // its column offset.  No request message, no staging copy.
 //
+// Indexed pull (the training path, tipsk_ps_pull with `index`): the (field, id)
+// pairs of the batch are first resolved into slots of a LOCAL open-addressing
+// table (device-scope CAS in this GPU's L2), which yields the list of distinct
+// rows and a slot per item; every distinct row is then fetched ONCE from its
+// owner into a row cache and the items are expanded from the cache.  Under a
+// Zipf distribution about half of a batch is duplicates, so half of the NVLink
+// traffic of the pull disappears, and the index is reused by the push of the
+// same step.
+//
 // Synchronous push, per rank:
-//   scatter   every (sample, field) gradient row is added into a slot of a LOCAL
-//             open-addressing table keyed by (field, id): duplicate ids of the
-//             batch end up summed in one slot (device-scope CAS + vector float
-//             atomics in this GPU's L2); the lane that claims a slot appends it to
-//             a touched list
-//   send      walks the touched list: one summed row per distinct id goes to its
-//             owner's inbox (a region per sender, so plain 16-byte stores over
-//             NVLink, no remote atomics and no round trips); the slot is cleared
+//   scatter   every (sample, field) gradient row is added into its slot of the
+//             local table (vector float atomics in this GPU's L2): duplicate ids
+//             of the batch end up summed in one slot.  With the index of the
+//             pull the slot is known; otherwise the slot is found or claimed
+//             here and appended to the list of distinct rows
+//   send      walks the list of distinct rows: a row this rank owns stays in
+//             the table and moves to the apply list; every other row goes to
+//             its owner's inbox (a region per sender, so plain 16-byte stores
+//             over NVLink, no remote atomics and no round trips), its sums are
+//             zeroed and its key stays in place until the apply pass, so that
+//             the probe chains of the table stay whole
 //   fence     cross-rank barrier; the per-sender row counts travel with it
-//   reduce    the owner folds the rows of all inboxes into the same local table
-//             (rows that several ranks touched are summed) and rebuilds the
-//             touched list
-//   apply     the owner walks the touched list, applies SGD or Adagrad to the
+//   reduce    the owner folds the rows of its inboxes into the same table
+//             (rows that several ranks touched are summed) and extends the
+//             apply list
+//   apply     the owner walks the apply list, applies SGD or Adagrad to the
 //             row with the gradient summed over every occurrence on every rank,
-//             and clears the slot
+//             and clears the slot; the keys of the rows that were sent away are
+//             emptied in the same pass
 // so the update is exactly the synchronous one: one optimizer step per touched
 // row.  With one rank the scatter is followed directly by the apply.  A training
 // step needs two fences: the one inside the push and the one in front of the
@@ -59,23 +72,27 @@ struct PsMeta {
   int32_t dim;                      // fp32 elements per row, multiple of 4
 };
 
-// Per-rank control words in device memory; all zero between pushes.
+// Per-rank control words in device memory; all zero between steps.
 struct alignas(8) PsCtl {
-  uint32_t ucount;                  // entries of the touched list
+  uint32_t ucount;                  // entries of the list of distinct rows of the batch
+  uint32_t acount;                  // entries of the apply list (several ranks)
   uint32_t done;                    // blocks of the running list walker that have finished
   uint32_t send_count[kMaxRanks];   // rows sent to each owner by the running send
-  uint32_t pad[6];
-  unsigned long long sent_total;    // rows sent since the last status call (own rows included)
+  uint32_t pad[5];
+  unsigned long long sent_total;    // distinct rows of the batches since the last status call (own rows included)
   unsigned long long sent_remote;   // of those, rows that crossed NVLink
   unsigned long long applied;       // rows updated since the last status call
+  unsigned long long fetched_remote;  // rows that the indexed pull read over NVLink
 };
 
 struct PsRank {
   char* slab[kMaxRanks];            // every rank's table slab as mapped here
   char* inbox[kMaxRanks];           // every rank's inbox as mapped here (null with one rank)
-  char* acc;                        // local accumulation table: [slots] u64 keys, [slots][dim] fp32 sums
-  uint32_t* ulist;                  // local touched list, [slots]
+  char* acc;                        // local table: [slots] u64 keys, [slots][dim] fp32 sums
+  uint32_t* ulist;                  // [2][slots]: list of distinct rows of the batch, then the apply list
   PsCtl* ctl;
+  uint32_t* item_slot;              // [capacity] slot of every (sample, field) item of the indexed batch
+  char* cache;                      // [slots][dim] rows fetched by the indexed pull, in the output dtype
   const int64_t* ids;               // [batch, nfields]
   const void* grads;                // push: [batch, ld] rows of nfields*dim (fp32 or bf16)
   void* out;                        // pull: [batch, ld]
@@ -204,21 +221,30 @@ __device__ __forceinline__ uint32_t ClaimSlot(unsigned long long* keys, uint64_t
   return kNoSlot;
 }
 
-// Appends the slots claimed by the lanes of this warp to the touched list: one atomic per warp.
+// Appends the slots flagged by the lanes of this warp to a list: one atomic per warp.
 // Every lane of the warp calls it.
-__device__ __forceinline__ void AppendClaims(const PsRank& pr, bool claimed, uint32_t slot, int lane) {
-  const unsigned m = __ballot_sync(kFullMask, claimed);
+__device__ __forceinline__ void AppendSlots(uint32_t* list, uint32_t* count, bool flagged, uint32_t slot, int lane) {
+  const unsigned m = __ballot_sync(kFullMask, flagged);
   if (m == 0) return;
   const int leader = __ffs(m) - 1;
   uint32_t first   = 0;
-  if (lane == leader) first = atomicAdd(&pr.ctl->ucount, static_cast<uint32_t>(__popc(m)));
+  if (lane == leader) first = atomicAdd(count, static_cast<uint32_t>(__popc(m)));
   first = __shfl_sync(kFullMask, first, leader);
-  if (claimed) pr.ulist[first + __popc(m & ((1u << lane) - 1u))] = slot;
+  if (flagged) list[first + __popc(m & ((1u << lane) - 1u))] = slot;
 }
 
+// No "memory" clobber: nothing in these kernels reads the sums back, so the loads of the next rows may be
+// scheduled ahead of the reduction.
 __device__ __forceinline__ void RedAdd4(float* addr, float a, float b, float c, float d) {
-  asm volatile("red.relaxed.gpu.global.add.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d)
-               : "memory");
+  asm volatile("red.relaxed.gpu.global.add.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d));
+}
+
+// System-scope 16-byte load of data that no one writes while the kernel runs (rows between two fences, inbox
+// entries after the fence): not volatile and without a "memory" clobber, so several of them can be in flight.
+__device__ __forceinline__ U4 LdSysFree(const void* addr) {
+  U4 v;
+  asm("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(addr));
+  return v;
 }
 
 template <typename GradT, bool kVec>
@@ -239,9 +265,140 @@ __device__ __forceinline__ void LoadGrad4(const GradT* g, float* out) {
   }
 }
 
-// Local segment-reduce of the batch: phase 1 resolves one item per lane (32 probes in flight per
-// warp), phase 2 adds the gradient rows with `lpi` lanes per row.
-template <typename GradT, bool kVec>
+constexpr int kRowsInFlight = 4;  // rows that a lane group loads before it stores the first one
+
+// Resolves every (sample, field) item of the batch into a slot of the local table: the distinct rows land in
+// the list, item_slot[item] holds the slot (kNoSlot for a bad id or a full table).
+__global__ void __launch_bounds__(256)
+PsIndexKernel(PsLaunch args, PsMeta meta, int64_t batch, uint64_t slots) {
+  const PsRank& pr = args.r[blockIdx.y];
+  const int n      = pr.nranks;
+  const int lane   = threadIdx.x & 31;
+  const int64_t warp_global = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int64_t nwarps      = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
+  const int64_t total       = batch * meta.nfields;
+  unsigned long long* keys  = reinterpret_cast<unsigned long long*>(pr.acc);
+  for (int64_t base = warp_global * 32; base < total; base += nwarps * 32) {
+    const int64_t mine = base + lane;
+    uint32_t slot = kNoSlot;
+    bool claimed  = false;
+    if (mine < total) {
+      const int f      = static_cast<int>(mine % meta.nfields);
+      const int64_t id = pr.ids[mine];
+      if (id < 0 || id / n >= meta.rows_per_shard[f]) {
+        atomicExch(pr.error, 2);
+      } else {
+        slot = ClaimSlot(keys, slots, SlotKey(f, id), &claimed);
+        if (slot == kNoSlot) atomicExch(pr.error, 1);
+      }
+      pr.item_slot[mine] = slot;
+    }
+    AppendSlots(pr.ulist, &pr.ctl->ucount, claimed, slot, lane);
+  }
+}
+
+// Fetches every distinct row of the indexed batch once, from its owner's HBM, into the row cache (converted to
+// the output dtype).
+template <typename OutT>
+__global__ void __launch_bounds__(256)
+PsFetchKernel(PsLaunch args, PsMeta meta, uint64_t slots) {
+  const PsRank& pr = args.r[blockIdx.y];
+  const int n      = pr.nranks;
+  const int dim    = meta.dim;
+  const int vecs   = dim / 4;
+  const RowLanes L(dim);
+  const int64_t warp_global = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int64_t nwarps      = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
+  unsigned long long* keys  = reinterpret_cast<unsigned long long*>(pr.acc);
+  OutT* cache               = reinterpret_cast<OutT*>(pr.cache);
+  const int64_t total       = *reinterpret_cast<volatile uint32_t*>(&pr.ctl->ucount);
+  for (int64_t base = warp_global * 32; base < total; base += nwarps * 32) {
+    const int64_t mine = base + L.lane;
+    uint32_t slot   = kNoSlot;
+    const char* row = nullptr;
+    bool remote     = false;
+    if (mine < total) {
+      slot = pr.ulist[mine];
+      const unsigned long long key = keys[slot];
+      const int f = KeyField(key);
+      int owner;
+      int64_t lrow;
+      PsPlace(f, KeyId(key), n, &owner, &lrow);
+      row    = pr.slab[owner] + meta.field_off[f] + static_cast<uint64_t>(lrow) * dim * 4;
+      remote = owner != pr.rank;
+    }
+    const unsigned rm = __ballot_sync(kFullMask, remote);
+    if (rm && L.lane == 0) atomicAdd(&pr.ctl->fetched_remote, static_cast<unsigned long long>(__popc(rm)));
+    for (int vb = 0; vb < vecs; vb += L.lpi) {  // uniform over the warp: the shuffles below need every lane
+      const int v       = vb + L.sublane;
+      const bool active = v < vecs;
+      for (int j0 = 0; j0 < 32; j0 += kRowsInFlight * L.ipw) {
+        U4 q[kRowsInFlight];
+        uint32_t sl[kRowsInFlight];
+#pragma unroll
+        for (int u = 0; u < kRowsInFlight; ++u) {
+          const int src = j0 + u * L.ipw + L.sub;
+          sl[u]         = kNoSlot;
+          if (j0 + u * L.ipw >= 32) continue;  // uniform over the warp
+          sl[u] = __shfl_sync(kFullMask, slot, src);
+          const char* r = reinterpret_cast<const char*>(__shfl_sync(kFullMask, reinterpret_cast<unsigned long long>(row), src));
+          if (!active) sl[u] = kNoSlot;
+          if (sl[u] != kNoSlot) q[u] = LdSysFree(r + v * 16);
+        }
+#pragma unroll
+        for (int u = 0; u < kRowsInFlight; ++u) {
+          if (sl[u] == kNoSlot) continue;
+          OutT* dst = cache + static_cast<uint64_t>(sl[u]) * dim + v * 4;
+          if (sizeof(OutT) == 4) {
+            *reinterpret_cast<U4*>(dst) = q[u];
+          } else {
+            OutT o[4] = {FromFloat<OutT>(__uint_as_float(q[u].x)), FromFloat<OutT>(__uint_as_float(q[u].y)),
+                         FromFloat<OutT>(__uint_as_float(q[u].z)), FromFloat<OutT>(__uint_as_float(q[u].w))};
+            *reinterpret_cast<uint2*>(dst) = *reinterpret_cast<uint2*>(o);
+          }
+        }
+      }
+    }
+  }
+}
+
+// Copies every item's row from the cache into the consumer's input matrix.
+template <typename OutT>
+__global__ void __launch_bounds__(256)
+PsExpandKernel(PsLaunch args, PsMeta meta, int64_t batch, int64_t out_ld, int64_t out_col0) {
+  const PsRank& pr = args.r[blockIdx.y];
+  const int dim    = meta.dim;
+  const int vecs   = dim / 4;
+  const RowLanes L(dim);
+  const int64_t warp_global = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int64_t nwarps      = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
+  const int64_t total       = batch * meta.nfields;
+  const OutT* cache         = reinterpret_cast<const OutT*>(pr.cache);
+  OutT* out                 = static_cast<OutT*>(pr.out);
+  using V = typename std::conditional<sizeof(OutT) == 4, U4, uint2>::type;  // four elements
+  for (int64_t base = warp_global * L.ipw; base < total; base += nwarps * L.ipw) {
+    const int64_t item = base + L.sub;
+    if (item >= total) continue;
+    const int f       = static_cast<int>(item % meta.nfields);
+    const int64_t b   = item / meta.nfields;
+    const uint32_t sl = pr.item_slot[item];
+    OutT* dst         = out + b * out_ld + out_col0 + static_cast<int64_t>(f) * dim;
+    for (int v = L.sublane; v < vecs; v += L.lpi) {
+      V q{};
+      if (sl != kNoSlot) q = *reinterpret_cast<const V*>(cache + static_cast<uint64_t>(sl) * dim + v * 4);
+      *reinterpret_cast<V*>(dst + v * 4) = q;
+    }
+  }
+}
+
+// Forgets an index that no push consumed: empties the slots of the list.
+__global__ void __launch_bounds__(256)
+PsClearIndexKernel(PsLaunch args, uint64_t slots);
+
+// Local segment-reduce of the batch.  kIndexed: the slot of every item comes from the index of the pull.
+// Otherwise phase 1 resolves one item per lane (32 probes in flight per warp) and extends the list of distinct
+// rows; phase 2 adds the gradient rows with `lpi` lanes per row.
+template <typename GradT, bool kVec, bool kIndexed>
 __global__ void __launch_bounds__(256)
 PsScatterKernel(PsLaunch args, PsMeta meta, int64_t batch, int64_t grad_ld, int64_t grad_col0, uint64_t slots,
                 float grad_scale) {
@@ -259,18 +416,22 @@ PsScatterKernel(PsLaunch args, PsMeta meta, int64_t batch, int64_t grad_ld, int6
   for (int64_t base = warp_global * 32; base < total; base += nwarps * 32) {
     const int64_t mine = base + L.lane;
     uint32_t slot = kNoSlot;
-    bool claimed  = false;
-    if (mine < total) {
-      const int f      = static_cast<int>(mine % meta.nfields);
-      const int64_t id = pr.ids[mine];
-      if (id < 0 || id / n >= meta.rows_per_shard[f]) {
-        atomicExch(pr.error, 2);
-      } else {
-        slot = ClaimSlot(keys, slots, SlotKey(f, id), &claimed);
-        if (slot == kNoSlot) atomicExch(pr.error, 1);  // table full: the host raises after the step
+    if (kIndexed) {
+      if (mine < total) slot = pr.item_slot[mine];
+    } else {
+      bool claimed = false;
+      if (mine < total) {
+        const int f      = static_cast<int>(mine % meta.nfields);
+        const int64_t id = pr.ids[mine];
+        if (id < 0 || id / n >= meta.rows_per_shard[f]) {
+          atomicExch(pr.error, 2);
+        } else {
+          slot = ClaimSlot(keys, slots, SlotKey(f, id), &claimed);
+          if (slot == kNoSlot) atomicExch(pr.error, 1);  // table full: the host raises after the step
+        }
       }
+      AppendSlots(pr.ulist, &pr.ctl->ucount, claimed, slot, L.lane);
     }
-    AppendClaims(pr, claimed, slot, L.lane);
     for (int j = 0; j < 32; j += L.ipw) {
       const int src      = j + L.sub;
       const uint32_t s   = __shfl_sync(kFullMask, slot, src);
@@ -309,7 +470,23 @@ __device__ __forceinline__ bool LastBlockDone(PsCtl* ctl) {
   return s_last != 0;
 }
 
-// One summed row per distinct id goes to its owner's inbox; the local slot is cleared.
+__global__ void __launch_bounds__(256)
+PsClearIndexKernel(PsLaunch args, uint64_t slots) {
+  const PsRank& pr = args.r[blockIdx.y];
+  unsigned long long* keys = reinterpret_cast<unsigned long long*>(pr.acc);
+  const int64_t total      = *reinterpret_cast<volatile uint32_t*>(&pr.ctl->ucount);
+  const int64_t stride     = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride)
+    keys[pr.ulist[i]] = 0;
+  if (LastBlockDone(pr.ctl) && threadIdx.x == 0) {
+    pr.ctl->ucount = 0;
+    pr.ctl->done   = 0;
+  }
+  (void)slots;
+}
+
+// Walks the list of distinct rows of the batch: a row this rank owns stays in the table and joins the apply
+// list; every other row goes to its owner's inbox and its slot is cleared.
 __global__ void __launch_bounds__(256)
 PsSendKernel(PsLaunch args, PsMeta meta, uint64_t slots, uint64_t cap) {
   const PsRank& pr = args.r[blockIdx.y];
@@ -321,6 +498,7 @@ PsSendKernel(PsLaunch args, PsMeta meta, uint64_t slots, uint64_t cap) {
   const int64_t nwarps      = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
   unsigned long long* keys  = reinterpret_cast<unsigned long long*>(pr.acc);
   float* sums_base          = reinterpret_cast<float*>(pr.acc + slots * 8);
+  uint32_t* apply_list      = pr.ulist + slots;
   const int64_t total       = *reinterpret_cast<volatile uint32_t*>(&pr.ctl->ucount);
   for (int64_t base = warp_global * 32; base < total; base += nwarps * 32) {
     const int64_t mine = base + L.lane;
@@ -333,8 +511,15 @@ PsSendKernel(PsLaunch args, PsMeta meta, uint64_t slots, uint64_t cap) {
       int64_t lrow;
       PsPlace(KeyField(key), KeyId(key), n, &owner, &lrow);
     }
+    const bool own = owner == pr.rank;
+    AppendSlots(apply_list, &pr.ctl->acount, own, slot, L.lane);
+    if (own) {
+      owner = -1;      // nothing to send
+      slot  = kNoSlot;
+    }
     // one atomic per (warp, owner): lanes with the same owner take consecutive positions
     const unsigned peers = __match_any_sync(kFullMask, owner);
+    float* dst = nullptr;
     if (owner >= 0) {
       const int leader = __ffs(peers) - 1;
       uint32_t first   = 0;
@@ -344,46 +529,65 @@ PsSendKernel(PsLaunch args, PsMeta meta, uint64_t slots, uint64_t cap) {
       if (pos < cap) {
         asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(InboxKeys(pr.inbox[owner], pr.rank, cap) + pos), "l"(key)
                      : "memory");
+        dst = InboxRows(pr.inbox[owner], n, pr.rank, cap, dim) + static_cast<uint64_t>(pos) * dim;
       } else {
         atomicExch(pr.error, 3);  // inbox full: the row is dropped, the host raises after the step
       }
-      keys[slot] = 0;
+      // The key stays in its slot until the apply pass: emptying it here would cut the probe chains of the
+      // rows that remain, and the reduce pass would then claim a second slot for a key that is already present.
     }
-    for (int j = 0; j < 32; j += L.ipw) {
-      const int src    = j + L.sub;
-      const uint32_t s = __shfl_sync(kFullMask, slot, src);
-      const int o      = __shfl_sync(kFullMask, owner, src);
-      const uint32_t p = __shfl_sync(kFullMask, pos, src);
-      if (s == kNoSlot) continue;
-      float* sums = sums_base + static_cast<uint64_t>(s) * dim;
-      float* dst  = p < cap ? InboxRows(pr.inbox[o], n, pr.rank, cap, dim) + static_cast<uint64_t>(p) * dim : nullptr;
-      for (int v = L.sublane; v < vecs; v += L.lpi) {
-        const U4 q = *reinterpret_cast<const U4*>(sums + v * 4);
-        if (dst) StSys(dst + v * 4, q);
-        *reinterpret_cast<float4*>(sums + v * 4) = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int vb = 0; vb < vecs; vb += L.lpi) {  // uniform over the warp: the shuffles below need every lane
+      const int v       = vb + L.sublane;
+      const bool active = v < vecs;
+      for (int j0 = 0; j0 < 32; j0 += kRowsInFlight * L.ipw) {
+        U4 q[kRowsInFlight];
+        float* sm[kRowsInFlight];
+        float* ds[kRowsInFlight];
+#pragma unroll
+        for (int u = 0; u < kRowsInFlight; ++u) {
+          const int src = j0 + u * L.ipw + L.sub;
+          sm[u]         = nullptr;
+          ds[u]         = nullptr;
+          if (j0 + u * L.ipw >= 32) continue;  // uniform over the warp
+          const uint32_t sl = __shfl_sync(kFullMask, slot, src);
+          ds[u] = reinterpret_cast<float*>(__shfl_sync(kFullMask, reinterpret_cast<unsigned long long>(dst), src));
+          if (sl == kNoSlot || !active) continue;
+          sm[u] = sums_base + static_cast<uint64_t>(sl) * dim + v * 4;
+          q[u]  = *reinterpret_cast<const U4*>(sm[u]);
+        }
+#pragma unroll
+        for (int u = 0; u < kRowsInFlight; ++u) {
+          if (!sm[u]) continue;
+          if (ds[u]) StSys(ds[u] + v * 4, q[u]);
+          *reinterpret_cast<float4*>(sm[u]) = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
       }
     }
   }
   if (LastBlockDone(pr.ctl)) {
-    if (threadIdx.x < n) {
-      const int o       = threadIdx.x;
-      uint32_t c        = atomicExch(&pr.ctl->send_count[o], 0u);
+    __shared__ unsigned long long s_remote;
+    if (threadIdx.x == 0) s_remote = 0;
+    __syncthreads();
+    if (threadIdx.x < n && threadIdx.x != pr.rank) {
+      const int o = threadIdx.x;
+      uint32_t c  = atomicExch(&pr.ctl->send_count[o], 0u);
       if (c > cap) c = static_cast<uint32_t>(cap);
       // the count is published by the fence that follows (system-scope release after this kernel)
       asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(reinterpret_cast<uint32_t*>(pr.inbox[o]) + pr.rank), "r"(c)
                    : "memory");
-      atomicAdd(&pr.ctl->sent_total, static_cast<unsigned long long>(c));
-      if (o != pr.rank) atomicAdd(&pr.ctl->sent_remote, static_cast<unsigned long long>(c));
+      atomicAdd(&s_remote, static_cast<unsigned long long>(c));
     }
+    __syncthreads();
     if (threadIdx.x == 0) {
-      pr.ctl->ucount = 0;
-      pr.ctl->done   = 0;
+      pr.ctl->sent_total += static_cast<unsigned long long>(total);
+      pr.ctl->sent_remote += s_remote;
+      pr.ctl->done = 0;  // ucount stays: the apply pass empties the slots of the rows that were sent
     }
     __threadfence_system();
   }
 }
 
-// The owner folds the rows that arrived in its inboxes into its local table.
+// The owner folds the rows that arrived in its inboxes into its local table and extends the apply list.
 __global__ void __launch_bounds__(256)
 PsOwnerReduceKernel(PsLaunch args, PsMeta meta, uint64_t slots, uint64_t cap) {
   const PsRank& pr = args.r[blockIdx.y];
@@ -395,6 +599,7 @@ PsOwnerReduceKernel(PsLaunch args, PsMeta meta, uint64_t slots, uint64_t cap) {
   const int64_t nwarps      = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
   unsigned long long* keys  = reinterpret_cast<unsigned long long*>(pr.acc);
   float* sums_base          = reinterpret_cast<float*>(pr.acc + slots * 8);
+  uint32_t* apply_list      = pr.ulist + slots;
   char* inbox               = pr.inbox[pr.rank];
   // exclusive prefix of the per-sender counts (written by the senders, published by the fence)
   uint32_t start[kMaxRanks + 1];
@@ -402,18 +607,19 @@ PsOwnerReduceKernel(PsLaunch args, PsMeta meta, uint64_t slots, uint64_t cap) {
 #pragma unroll
   for (int s = 0; s < kMaxRanks; ++s) {
     uint32_t c = 0;
-    if (s < n) {
+    if (s < n && s != pr.rank) {
       asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(c) : "l"(reinterpret_cast<uint32_t*>(inbox) + s) : "memory");
       if (c > cap) c = static_cast<uint32_t>(cap);
     }
     start[s + 1] = start[s] + c;
   }
   const int64_t total = start[kMaxRanks];
+  const float* rows   = reinterpret_cast<const float*>(inbox + kInboxHeader + static_cast<uint64_t>(n) * cap * 8);
   for (int64_t base = warp_global * 32; base < total; base += nwarps * 32) {
     const int64_t mine = base + L.lane;
-    uint32_t slot = kNoSlot;
-    uint64_t cell = 0;  // sender * cap + position: where the entry sits in the inbox
-    bool claimed  = false;
+    uint32_t slot    = kNoSlot;
+    const float* row = nullptr;
+    bool claimed     = false;
     if (mine < total) {
       int s           = 0;
       uint32_t sstart = 0;
@@ -423,7 +629,7 @@ PsOwnerReduceKernel(PsLaunch args, PsMeta meta, uint64_t slots, uint64_t cap) {
           s      = k;
           sstart = start[k];
         }
-      cell = static_cast<uint64_t>(s) * cap + (mine - sstart);
+      const uint64_t cell = static_cast<uint64_t>(s) * cap + (mine - sstart);  // where the entry sits in the inbox
       unsigned long long key;
       asm volatile("ld.relaxed.sys.global.u64 %0, [%1];"
                    : "=l"(key)
@@ -431,19 +637,33 @@ PsOwnerReduceKernel(PsLaunch args, PsMeta meta, uint64_t slots, uint64_t cap) {
                    : "memory");
       slot = ClaimSlot(keys, slots, key, &claimed);
       if (slot == kNoSlot) atomicExch(pr.error, 1);
+      row = rows + cell * dim;
     }
-    AppendClaims(pr, claimed, slot, L.lane);
-    const float* rows = reinterpret_cast<const float*>(inbox + kInboxHeader + static_cast<uint64_t>(n) * cap * 8);
-    for (int j = 0; j < 32; j += L.ipw) {
-      const int src    = j + L.sub;
-      const uint32_t s = __shfl_sync(kFullMask, slot, src);
-      const uint64_t c = __shfl_sync(kFullMask, cell, src);
-      if (s == kNoSlot) continue;
-      float* sums      = sums_base + static_cast<uint64_t>(s) * dim;
-      const float* row = rows + c * dim;
-      for (int v = L.sublane; v < vecs; v += L.lpi) {
-        const U4 q = LdSys(row + v * 4);
-        RedAdd4(sums + v * 4, __uint_as_float(q.x), __uint_as_float(q.y), __uint_as_float(q.z), __uint_as_float(q.w));
+    AppendSlots(apply_list, &pr.ctl->acount, claimed, slot, L.lane);
+    for (int vb = 0; vb < vecs; vb += L.lpi) {  // uniform over the warp: the shuffles below need every lane
+      const int v       = vb + L.sublane;
+      const bool active = v < vecs;
+      for (int j0 = 0; j0 < 32; j0 += kRowsInFlight * L.ipw) {
+        U4 q[kRowsInFlight];
+        float* sm[kRowsInFlight];
+#pragma unroll
+        for (int u = 0; u < kRowsInFlight; ++u) {
+          const int src = j0 + u * L.ipw + L.sub;
+          sm[u]         = nullptr;
+          if (j0 + u * L.ipw >= 32) continue;  // uniform over the warp
+          const uint32_t sl = __shfl_sync(kFullMask, slot, src);
+          const float* r =
+              reinterpret_cast<const float*>(__shfl_sync(kFullMask, reinterpret_cast<unsigned long long>(row), src));
+          if (sl == kNoSlot || !active) continue;
+          sm[u] = sums_base + static_cast<uint64_t>(sl) * dim + v * 4;
+          q[u]  = LdSysFree(r + v * 4);
+        }
+#pragma unroll
+        for (int u = 0; u < kRowsInFlight; ++u) {
+          if (!sm[u]) continue;
+          RedAdd4(sm[u], __uint_as_float(q[u].x), __uint_as_float(q[u].y), __uint_as_float(q[u].z),
+                  __uint_as_float(q[u].w));
+        }
       }
     }
   }
@@ -527,11 +747,14 @@ PsPushApplyKernel(PsLaunch args, PsMeta meta, uint64_t slots, int rule, float lr
   unsigned long long* keys  = reinterpret_cast<unsigned long long*>(pr.acc);
   float* sums_base          = reinterpret_cast<float*>(pr.acc + slots * 8);
   char* slab                = pr.slab[pr.rank];
-  const int64_t total       = *reinterpret_cast<volatile uint32_t*>(&pr.ctl->ucount);
+  // several ranks: the apply list that send and reduce built; one rank: the list of distinct rows of the batch
+  const uint32_t* list      = n > 1 ? pr.ulist + slots : pr.ulist;
+  uint32_t* count           = n > 1 ? &pr.ctl->acount : &pr.ctl->ucount;
+  const int64_t total       = *reinterpret_cast<volatile uint32_t*>(count);
   for (int64_t base = warp_global * L.ipw; base < total; base += nwarps * L.ipw) {
     const int64_t e = base + L.sub;
     if (e >= total) continue;
-    const uint32_t slot = pr.ulist[e];
+    const uint32_t slot = list[e];
     const uint64_t key  = keys[slot];
     const int f         = KeyField(key);
     int owner;
@@ -562,10 +785,26 @@ PsPushApplyKernel(PsLaunch args, PsMeta meta, uint64_t slots, int rule, float lr
     __syncwarp(L.group_mask());
     if (L.sublane == 0) keys[slot] = 0;
   }
+  if (n > 1) {
+    // rows of this rank's batch that other ranks own were sent away: their sums are zero, empty their keys
+    const int64_t batch_rows = *reinterpret_cast<volatile uint32_t*>(&pr.ctl->ucount);
+    const int64_t stride     = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < batch_rows; i += stride) {
+      const uint32_t slot = pr.ulist[i];
+      const uint64_t key  = *reinterpret_cast<volatile unsigned long long*>(keys + slot);
+      if (key == 0) continue;  // a row of this rank, already applied and emptied by the loop above
+      int owner;
+      int64_t lrow;
+      PsPlace(KeyField(key), KeyId(key), n, &owner, &lrow);
+      if (owner != pr.rank) keys[slot] = 0;
+    }
+  }
   if (LastBlockDone(pr.ctl)) {
     if (threadIdx.x == 0) {
-      atomicAdd(&pr.ctl->applied, static_cast<unsigned long long>(total));
+      pr.ctl->applied += static_cast<unsigned long long>(total);
+      if (n == 1) pr.ctl->sent_total += static_cast<unsigned long long>(total);
       pr.ctl->ucount = 0;
+      pr.ctl->acount = 0;
       pr.ctl->done   = 0;
     }
   }
@@ -599,14 +838,20 @@ struct PsState {
   char* acc[kMaxRanks];        // per local rank (one entry unless the ranks are emulated on one GPU)
   uint32_t* ulist[kMaxRanks];
   PsCtl* ctl[kMaxRanks];
+  uint32_t* item_slot[kMaxRanks];
+  char* cache[kMaxRanks];
   int nlocal = 0;
   uint64_t slots = 0;
   uint64_t inbox_cap = 0;
+  uint64_t item_cap = 0;       // items (sample, field) that item_slot can hold
   int32_t* error_dev = nullptr;
   bool lead_fence = true;      // the next push must fence first (no fenced pull since the previous push)
+  int64_t index_items = -1;    // >= 0: the table holds the index of a pulled batch of that many items
   bool timing = false;
   cudaEvent_t ev[6] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
   int ev_used = 0;
+  cudaEvent_t pull_ev[5] = {nullptr, nullptr, nullptr, nullptr, nullptr};
+  int pull_ev_used = 0;
 };
 PsState g_ps;
 
@@ -627,6 +872,8 @@ int MakePsLaunch(PsLaunch* l, const int64_t* const* ids, const void* const* grad
     r.acc    = g_ps.acc[i];
     r.ulist  = g_ps.ulist[i];
     r.ctl    = g_ps.ctl[i];
+    r.item_slot = g_ps.item_slot[i];
+    r.cache  = g_ps.cache[i];
     r.ids    = ids ? ids[i] : nullptr;
     r.grads  = grads ? grads[i] : nullptr;
     r.out    = outs ? outs[i] : nullptr;
@@ -654,6 +901,40 @@ int LanesPerItem(int dim) {
 void Mark(cudaStream_t s) {
   PsState& st = g_ps;
   if (st.timing && st.ev_used < 6) cudaEventRecord(st.ev[st.ev_used++], s);
+}
+void MarkPull(cudaStream_t s) {
+  PsState& st = g_ps;
+  if (st.timing && st.pull_ev_used < 5) cudaEventRecord(st.pull_ev[st.pull_ev_used++], s);
+}
+
+// Drops an index that no push consumed, so that the table is empty again.
+int DropIndex(PsLaunch& l, int local, cudaStream_t s) {
+  PsState& st = g_ps;
+  if (st.index_items < 0) return 0;
+  dim3 grid(PsGrid(st.index_items, 1), local);
+  PsClearIndexKernel<<<grid, 256, 0, s>>>(l, st.slots);
+  TIPSK_LAUNCH_CHECK();
+  st.index_items = -1;
+  return 0;
+}
+
+template <typename GradT>
+int LaunchScatter(const PsLaunch& l, dim3 grid, cudaStream_t s, bool vec, bool indexed, int64_t batch,
+                         int64_t grad_ld, int64_t grad_col0, float grad_scale) {
+  PsState& st = g_ps;
+  if (indexed) {
+    if (vec)
+      PsScatterKernel<GradT, true, true><<<grid, 256, 0, s>>>(l, st.meta, batch, grad_ld, grad_col0, st.slots, grad_scale);
+    else
+      PsScatterKernel<GradT, false, true><<<grid, 256, 0, s>>>(l, st.meta, batch, grad_ld, grad_col0, st.slots, grad_scale);
+  } else {
+    if (vec)
+      PsScatterKernel<GradT, true, false><<<grid, 256, 0, s>>>(l, st.meta, batch, grad_ld, grad_col0, st.slots, grad_scale);
+    else
+      PsScatterKernel<GradT, false, false><<<grid, 256, 0, s>>>(l, st.meta, batch, grad_ld, grad_col0, st.slots, grad_scale);
+  }
+  TIPSK_LAUNCH_CHECK();
+  return 0;
 }
 
 }  // namespace
@@ -715,13 +996,16 @@ uint64_t tipsk_ps_ctl_bytes() { return sizeof(PsCtl); }
 
 /* Registers the buffers of the data path and the per-field layout.
  *   slabs, inboxes   one pointer per rank, as mapped in this process (inboxes may be null with one rank)
- *   accs, ulists, ctls   one pointer per LOCAL rank (one, or `nranks` when the ranks are emulated on one GPU):
- *                    accumulation table (tipsk_ps_acc_bytes), touched list (slots u32), control words
- *                    (tipsk_ps_ctl_bytes); all three must be zero before the first push
+ *   accs, ulists, ctls, item_slots, caches   one pointer per LOCAL rank (one, or `nranks` when the ranks are
+ *                    emulated on one GPU): accumulation table (tipsk_ps_acc_bytes), the two lists (2 * slots u32),
+ *                    control words (tipsk_ps_ctl_bytes), slot per item (item_cap u32), row cache of the indexed
+ *                    pull (slots * dim * 4 bytes); the first three must be zero before the first call; item_slots
+ *                    and caches may be null (no indexed pull)
  *   slots            power of two; inbox_cap: rows one sender may send to one owner in a push, even. */
 int tipsk_ps_configure(void* const* slabs, void* const* inboxes, void* const* accs, void* const* ulists,
-                       void* const* ctls, int nranks, int nlocal, const uint64_t* field_off, const uint64_t* state_off,
-                       const int64_t* rows_per_shard, int nfields, int dim, uint64_t slots, uint64_t inbox_cap) {
+                       void* const* ctls, void* const* item_slots, void* const* caches, int nranks, int nlocal,
+                       const uint64_t* field_off, const uint64_t* state_off, const int64_t* rows_per_shard, int nfields,
+                       int dim, uint64_t slots, uint64_t inbox_cap, uint64_t item_cap) {
   TIPSK_REQUIRE(nfields >= 1 && nfields <= kMaxFields, "ps: 1..64 fields are supported");
   TIPSK_REQUIRE(dim >= 4 && dim % 4 == 0, "ps: the row dimension must be a multiple of 4");
   TIPSK_REQUIRE(slots >= 2 && (slots & (slots - 1)) == 0 && slots <= (1ull << 31), "ps: slots must be a power of two");
@@ -739,16 +1023,20 @@ int tipsk_ps_configure(void* const* slabs, void* const* inboxes, void* const* ac
   st.meta.nfields = nfields;
   st.meta.dim     = dim;
   for (int r = 0; r < kMaxRanks; ++r) {
-    st.slab[r]  = r < nranks ? static_cast<char*>(slabs[r]) : nullptr;
-    st.inbox[r] = r < nranks && inboxes ? static_cast<char*>(inboxes[r]) : nullptr;
-    st.acc[r]   = r < nlocal && accs ? static_cast<char*>(accs[r]) : nullptr;
-    st.ulist[r] = r < nlocal && ulists ? static_cast<uint32_t*>(ulists[r]) : nullptr;
-    st.ctl[r]   = r < nlocal && ctls ? static_cast<PsCtl*>(ctls[r]) : nullptr;
+    st.slab[r]      = r < nranks ? static_cast<char*>(slabs[r]) : nullptr;
+    st.inbox[r]     = r < nranks && inboxes ? static_cast<char*>(inboxes[r]) : nullptr;
+    st.acc[r]       = r < nlocal && accs ? static_cast<char*>(accs[r]) : nullptr;
+    st.ulist[r]     = r < nlocal && ulists ? static_cast<uint32_t*>(ulists[r]) : nullptr;
+    st.ctl[r]       = r < nlocal && ctls ? static_cast<PsCtl*>(ctls[r]) : nullptr;
+    st.item_slot[r] = r < nlocal && item_slots ? static_cast<uint32_t*>(item_slots[r]) : nullptr;
+    st.cache[r]     = r < nlocal && caches ? static_cast<char*>(caches[r]) : nullptr;
   }
-  st.nlocal     = nlocal;
-  st.slots      = slots;
-  st.inbox_cap  = inbox_cap;
-  st.lead_fence = true;
+  st.nlocal      = nlocal;
+  st.slots       = slots;
+  st.inbox_cap   = inbox_cap;
+  st.item_cap    = item_cap;
+  st.lead_fence  = true;
+  st.index_items = -1;
   if (!st.error_dev) {
     TIPSK_CUDA(cudaMalloc(reinterpret_cast<void**>(&st.error_dev), sizeof(int32_t)));
     TIPSK_CUDA(cudaMemset(st.error_dev, 0, sizeof(int32_t)));
@@ -776,20 +1064,22 @@ int tipsk_ps_status(int32_t* error, uint64_t* touched) {
   return 0;
 }
 
-/* Traffic counters of the synchronous push since the last call: out[0] rows sent to owners (after the local
- * reduction of duplicates; rows this rank owns itself included), out[1] those that crossed NVLink.  Summed over the
- * local ranks.  Synchronises the device. */
+/* Traffic counters since the last call: out[0] distinct rows of the pushed batches (after the local reduction of
+ * duplicates; rows this rank owns itself included), out[1] those that crossed NVLink to their owner, out[2] rows
+ * that indexed pulls read over NVLink.  Summed over the local ranks.  Synchronises the device. */
 int tipsk_ps_traffic(uint64_t* out) {
   PsState& st = g_ps;
   TIPSK_REQUIRE(st.ready, "ps not configured");
-  out[0] = out[1] = 0;
+  out[0] = out[1] = out[2] = 0;
   for (int i = 0; i < st.nlocal; ++i) {
     if (!st.ctl[i]) continue;
     PsCtl c;
     TIPSK_CUDA(cudaMemcpy(&c, st.ctl[i], sizeof(c), cudaMemcpyDeviceToHost));
     out[0] += c.sent_total;
     out[1] += c.sent_remote;
+    out[2] += c.fetched_remote;
     TIPSK_CUDA(cudaMemset(&st.ctl[i]->sent_total, 0, 2 * sizeof(unsigned long long)));
+    TIPSK_CUDA(cudaMemset(&st.ctl[i]->fetched_remote, 0, sizeof(unsigned long long)));
   }
   return 0;
 }
@@ -799,10 +1089,22 @@ int tipsk_ps_traffic(uint64_t* out) {
  * returns the five durations of the last push in milliseconds (0 for phases that did not run). */
 int tipsk_ps_phase_timing(int enable) {
   PsState& st = g_ps;
-  if (enable && !st.ev[0])
+  if (enable && !st.ev[0]) {
     for (auto& e : st.ev) TIPSK_CUDA(cudaEventCreate(&e));
-  st.timing  = enable != 0;
-  st.ev_used = 0;
+    for (auto& e : st.pull_ev) TIPSK_CUDA(cudaEventCreate(&e));
+  }
+  st.timing       = enable != 0;
+  st.ev_used      = 0;
+  st.pull_ev_used = 0;
+  return 0;
+}
+/* The durations of the last indexed pull: index, fence, fetch, expand (milliseconds). */
+int tipsk_ps_pull_phase_ms(float* out4) {
+  PsState& st = g_ps;
+  for (int i = 0; i < 4; ++i) out4[i] = 0.f;
+  if (!st.timing || st.pull_ev_used != 5) return 0;
+  TIPSK_CUDA(cudaEventSynchronize(st.pull_ev[4]));
+  for (int i = 0; i < 4; ++i) TIPSK_CUDA(cudaEventElapsedTime(&out4[i], st.pull_ev[i], st.pull_ev[i + 1]));
   return 0;
 }
 int tipsk_ps_phase_ms(float* out5) {
@@ -821,37 +1123,70 @@ int tipsk_ps_phase_ms(float* out5) {
 
 /* ids: [batch, nfields] int64 (one pointer per local rank); out: [batch, out_ld] of out_dtype (fp32/bf16),
  * field f lands at columns out_col0 + f*dim.  `fence` non-zero puts a cross-rank fence first, so that
- * rows updated by the previous push on any rank are visible. */
+ * rows updated by the previous push on any rank are visible.  `index` non-zero: the batch is first resolved into
+ * its distinct rows, each of which is fetched once; the index stays in place for a following
+ * tipsk_ps_push(..., reuse_index = 1) of the SAME ids (it is dropped by any other pull or push). */
 int tipsk_ps_pull(const int64_t* const* ids, void* const* outs, int64_t batch, int64_t out_ld, int64_t out_col0,
-                  int out_dtype, int fence, void* stream) {
+                  int out_dtype, int fence, int index, void* stream) {
   PsState& st = g_ps;
   TIPSK_REQUIRE(st.ready, "ps not configured");
   if (batch <= 0) return 0;
   TIPSK_REQUIRE(out_ld % 4 == 0 && out_col0 % 4 == 0, "ps pull: the output pitch and column offset must be multiples of 4");
+  TIPSK_REQUIRE(out_dtype == kF32 || out_dtype == kBF16, "ps pull: output must be fp32 or bf16");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  PsLaunch l;
+  int local = MakePsLaunch(&l, ids, nullptr, outs);
+  if (local < 0) return local;
+  const int64_t items = batch * st.meta.nfields;
+  const int lpi       = LanesPerItem(st.meta.dim);
+  dim3 grid(PsGrid(items, lpi), local);
+  if (index) {
+    TIPSK_REQUIRE(st.acc[0] && st.ulist[0] && st.ctl[0] && st.item_slot[0] && st.cache[0],
+                  "ps pull: the indexed pull needs the accumulation table, lists, item slots and row cache");
+    TIPSK_REQUIRE(static_cast<uint64_t>(items) <= st.item_cap, "ps pull: the batch exceeds the configured item capacity");
+    int rc = DropIndex(l, local, s);
+    if (rc) return rc;
+    st.pull_ev_used = 0;
+    MarkPull(s);
+    PsIndexKernel<<<dim3(PsGrid(items, 1), local), 256, 0, s>>>(l, st.meta, batch, st.slots);
+    TIPSK_LAUNCH_CHECK();
+    st.index_items = items;
+    MarkPull(s);
+  }
   if (fence) {
     int rc = tipsk_comm_fence(2, stream);
     if (rc) return rc;
     st.lead_fence = false;
   }
-  PsLaunch l;
-  int local = MakePsLaunch(&l, ids, nullptr, outs);
-  if (local < 0) return local;
-  const int lpi = LanesPerItem(st.meta.dim);
-  dim3 grid(PsGrid(batch * st.meta.nfields, lpi), local);
-  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (!index) {
+    if (out_dtype == kF32)
+      PsPullKernel<float><<<grid, 256, 0, s>>>(l, st.meta, batch, out_ld, out_col0);
+    else
+      PsPullKernel<__nv_bfloat16><<<grid, 256, 0, s>>>(l, st.meta, batch, out_ld, out_col0);
+    TIPSK_LAUNCH_CHECK();
+    return 0;
+  }
+  MarkPull(s);
   if (out_dtype == kF32)
-    PsPullKernel<float><<<grid, 256, 0, s>>>(l, st.meta, batch, out_ld, out_col0);
-  else if (out_dtype == kBF16)
-    PsPullKernel<__nv_bfloat16><<<grid, 256, 0, s>>>(l, st.meta, batch, out_ld, out_col0);
+    PsFetchKernel<float><<<grid, 256, 0, s>>>(l, st.meta, st.slots);
   else
-    return SetError(-2, "ps pull: output must be fp32 or bf16");
+    PsFetchKernel<__nv_bfloat16><<<grid, 256, 0, s>>>(l, st.meta, st.slots);
   TIPSK_LAUNCH_CHECK();
+  MarkPull(s);
+  if (out_dtype == kF32)
+    PsExpandKernel<float><<<grid, 256, 0, s>>>(l, st.meta, batch, out_ld, out_col0);
+  else
+    PsExpandKernel<__nv_bfloat16><<<grid, 256, 0, s>>>(l, st.meta, batch, out_ld, out_col0);
+  TIPSK_LAUNCH_CHECK();
+  MarkPull(s);
   return 0;
 }
 
-/* grads: [batch, grad_ld] of grad_dtype, field f at columns grad_col0 + f*dim. */
+/* grads: [batch, grad_ld] of grad_dtype, field f at columns grad_col0 + f*dim.  `reuse_index` non-zero: `ids` are
+ * the ids of the last tipsk_ps_pull(..., index = 1), whose index gives every item's slot. */
 int tipsk_ps_push(const int64_t* const* ids, const void* const* grads, int64_t batch, int64_t grad_ld,
-                  int64_t grad_col0, int grad_dtype, float grad_scale, int rule, float lr, float eps, void* stream) {
+                  int64_t grad_col0, int grad_dtype, float grad_scale, int rule, float lr, float eps, int reuse_index,
+                  void* stream) {
   PsState& st = g_ps;
   TIPSK_REQUIRE(st.ready, "ps not configured");
   TIPSK_REQUIRE(st.acc[0] != nullptr && st.ulist[0] != nullptr && st.ctl[0] != nullptr,
@@ -862,40 +1197,38 @@ int tipsk_ps_push(const int64_t* const* ids, const void* const* grads, int64_t b
   PsLaunch l;
   int local = MakePsLaunch(&l, ids, grads, nullptr);
   if (local < 0) return local;
-  const int nranks = l.r[0].nranks;
+  const int nranks    = l.r[0].nranks;
+  const int64_t items = batch * st.meta.nfields;
   TIPSK_REQUIRE(nranks == 1 || st.inbox[0] != nullptr, "ps push: no inboxes configured");
+  TIPSK_REQUIRE(!reuse_index || st.index_items == items,
+                "ps push: reuse_index needs the index of a pull of the same batch right before");
+  if (!reuse_index) {
+    int rc = DropIndex(l, local, s);
+    if (rc) return rc;
+  }
   if (nranks > 1 && st.lead_fence) {
     // every rank has finished reading its inbox and applying the previous push
     int rc = tipsk_comm_fence(2, stream);
     if (rc) return rc;
   }
-  st.lead_fence = true;
-  st.ev_used    = 0;
-  const int lpi = LanesPerItem(st.meta.dim);
-  dim3 grid(PsGrid(batch * st.meta.nfields, lpi), local);
+  st.lead_fence  = true;
+  st.index_items = -1;  // the push consumes the index: send and apply empty the table
+  st.ev_used     = 0;
+  const int lpi  = LanesPerItem(st.meta.dim);
+  dim3 grid(PsGrid(items, lpi), local);
   bool vec = grad_ld % 4 == 0 && grad_col0 % 4 == 0;
   for (int i = 0; i < local; ++i) vec = vec && (reinterpret_cast<uintptr_t>(grads[i]) % 16 == 0);
   Mark(s);
-  if (grad_dtype == kF32) {
-    if (vec)
-      PsScatterKernel<float, true><<<grid, 256, 0, s>>>(l, st.meta, batch, grad_ld, grad_col0, st.slots, grad_scale);
-    else
-      PsScatterKernel<float, false><<<grid, 256, 0, s>>>(l, st.meta, batch, grad_ld, grad_col0, st.slots, grad_scale);
-  } else {
-    if (vec)
-      PsScatterKernel<__nv_bfloat16, true><<<grid, 256, 0, s>>>(l, st.meta, batch, grad_ld, grad_col0, st.slots,
-                                                               grad_scale);
-    else
-      PsScatterKernel<__nv_bfloat16, false><<<grid, 256, 0, s>>>(l, st.meta, batch, grad_ld, grad_col0, st.slots,
-                                                                grad_scale);
-  }
-  TIPSK_LAUNCH_CHECK();
+  int rc = grad_dtype == kF32
+               ? LaunchScatter<float>(l, grid, s, vec, reuse_index != 0, batch, grad_ld, grad_col0, grad_scale)
+               : LaunchScatter<__nv_bfloat16>(l, grid, s, vec, reuse_index != 0, batch, grad_ld, grad_col0, grad_scale);
+  if (rc) return rc;
   Mark(s);
   if (nranks > 1) {
     PsSendKernel<<<grid, 256, 0, s>>>(l, st.meta, st.slots, st.inbox_cap);
     TIPSK_LAUNCH_CHECK();
     Mark(s);
-    int rc = tipsk_comm_fence(2, stream);  // every rank's rows and counts have landed
+    rc = tipsk_comm_fence(2, stream);  // every rank's rows and counts have landed
     if (rc) return rc;
     Mark(s);
     PsOwnerReduceKernel<<<grid, 256, 0, s>>>(l, st.meta, st.slots, st.inbox_cap);

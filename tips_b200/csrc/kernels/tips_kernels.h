@@ -156,17 +156,20 @@ uint64_t tipsk_ps_acc_bytes(uint64_t slots, int dim);
 uint64_t tipsk_ps_inbox_bytes(int nranks, uint64_t inbox_cap, int dim);
 uint64_t tipsk_ps_ctl_bytes(void);
 int tipsk_ps_configure(void* const* host_slabs, void* const* host_inboxes, void* const* host_accs,
-                       void* const* host_ulists, void* const* host_ctls, int nranks, int nlocal,
-                       const uint64_t* host_field_off, const uint64_t* host_state_off,
-                       const int64_t* host_rows_per_shard, int nfields, int dim, uint64_t slots, uint64_t inbox_cap);
-int tipsk_ps_traffic(uint64_t* host_out2);
+                       void* const* host_ulists, void* const* host_ctls, void* const* host_item_slots,
+                       void* const* host_caches, int nranks, int nlocal, const uint64_t* host_field_off,
+                       const uint64_t* host_state_off, const int64_t* host_rows_per_shard, int nfields, int dim,
+                       uint64_t slots, uint64_t inbox_cap, uint64_t item_cap);
+int tipsk_ps_traffic(uint64_t* host_out3);
 int tipsk_ps_phase_timing(int enable);
 int tipsk_ps_phase_ms(float* host_out5);
+int tipsk_ps_pull_phase_ms(float* host_out4);
 int tipsk_ps_status(int32_t* host_error, uint64_t* host_touched);
 int tipsk_ps_pull(const int64_t* const* host_ids, void* const* host_outs, int64_t batch, int64_t out_ld,
-                  int64_t out_col0, int out_dtype, int fence, void* stream);
+                  int64_t out_col0, int out_dtype, int fence, int index, void* stream);
 int tipsk_ps_push(const int64_t* const* host_ids, const void* const* host_grads, int64_t batch, int64_t grad_ld,
-                  int64_t grad_col0, int grad_dtype, float grad_scale, int rule, float lr, float eps, void* stream);
+                  int64_t grad_col0, int grad_dtype, float grad_scale, int rule, float lr, float eps, int reuse_index,
+                  void* stream);
 /* Asynchronous push: gradients applied straight to the owner's rows with atomics, no fences (SGD / Adagrad). */
 int tipsk_ps_push_async(const int64_t* const* host_ids, const void* const* host_grads, int64_t batch, int64_t grad_ld,
                   int64_t grad_col0, int grad_dtype, float grad_scale, int rule, float lr, float eps, void* stream);
@@ -201,6 +204,8 @@ int tipsk_conv_status(void);
  * weights [cout, 7, 8, 8] with the eighth horizontal tap and channels 3..7 zero. */
 int tipsk_stem_geometry(int h, int w, int* hp, int* wp, int* ho, int* wo);
 int tipsk_stem_pad(const void* x, void* xp, int n, int h, int w, void* stream);
+/* The same from an fp32 NCHW image: layout change and cast to bf16 inside the padding copy. */
+int tipsk_stem_pad_nchw_f32(const void* x, void* xp, int n, int h, int w, void* stream);
 int tipsk_stem_conv_fwd(const void* xp, const void* wgt_p, void* y, int n, int h, int w, int cout, float* stat_sum,
                         float* stat_sq, void* stream);
 int tipsk_stem_conv_wgrad(const void* xp, const void* dy, float* dw, int n, int h, int w, int cout, void* stream);

@@ -17,7 +17,9 @@
 //   local shard = (hash(key) div n_servers) mod local_shards
 #pragma once
 
+#include <condition_variable>
 #include <functional>
+#include <mutex>
 #include <map>
 #include <memory>
 #include <string>
@@ -169,12 +171,36 @@ class DenseTable : public Table {
     if (!is_server() || g % num_servers() != server_index()) return nullptr;
     return &data_[g / num_servers()][index - boundaries_[g]];
   }
-  // Applies f(index, value&) to every local element, shards in parallel on the shard threads.
+  // Applies f(index, value&) to every local element.  While the table's service runs, every local shard is
+  // visited on its own shard thread (in parallel with the others, serialised with the pushes to that shard) and
+  // the call returns when all are done; otherwise the shards are visited one after the other on the caller.
   void ForEach(const std::function<void(size_t, T&)>& f) {
-    for (int l = 0; l < local_shard_num(); ++l) {
+    auto visit = [this, &f](int l) {
       int g = ToGlobalShard(server_index(), l);
       for (size_t i = 0; i < data_[l].size(); ++i) f(boundaries_[g] + i, data_[l][i]);
+    };
+    if (!is_server()) return;
+    if (!running()) {
+      for (int l = 0; l < local_shard_num(); ++l) visit(l);
+      return;
     }
+    std::mutex mu;
+    std::condition_variable cv;
+    int pending = local_shard_num();
+    for (int l = 0; l < local_shard_num(); ++l) {
+      bool ok = Submit(l, [&, l] {
+        visit(l);
+        std::lock_guard<std::mutex> lock(mu);
+        if (--pending == 0) cv.notify_all();
+      });
+      if (!ok) {
+        visit(l);
+        std::lock_guard<std::mutex> lock(mu);
+        --pending;
+      }
+    }
+    std::unique_lock<std::mutex> lock(mu);
+    cv.wait(lock, [&] { return pending == 0; });
   }
   Status Save(const std::string& path) const;
   Status Load(const std::string& path);

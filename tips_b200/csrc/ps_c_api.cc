@@ -11,6 +11,7 @@
 #include <memory>
 #include <mutex>
 
+#include "ps/dense_server.h"
 #include "ps/ps_server.h"
 #include "runtime/context.h"
 
@@ -25,8 +26,15 @@ struct PsBundle {
   std::unique_ptr<PsClient> client;
 };
 
+struct DenseBundle {
+  std::unique_ptr<DenseTable<float>> table;
+  std::unique_ptr<DensePsServer> server;
+  std::unique_ptr<DensePsClient> client;
+};
+
 std::mutex g_mu;
 std::map<int64_t, std::unique_ptr<PsBundle>> g_tables;
+std::map<int64_t, std::unique_ptr<DenseBundle>> g_dense;
 int64_t g_next = 1;
 thread_local std::string tl_ps_error;
 
@@ -39,6 +47,12 @@ PsBundle* Get(int64_t id) {
   std::lock_guard<std::mutex> lock(g_mu);
   auto it = g_tables.find(id);
   return it == g_tables.end() ? nullptr : it->second.get();
+}
+
+DenseBundle* GetDense(int64_t id) {
+  std::lock_guard<std::mutex> lock(g_mu);
+  auto it = g_dense.find(id);
+  return it == g_dense.end() ? nullptr : it->second.get();
 }
 
 }  // namespace
@@ -167,6 +181,115 @@ int tips_ps_server_counters(int64_t id, uint64_t* rows_pulled, uint64_t* rows_pu
   if (!b) return Fail(kInvalidArgument, "unknown ps table");
   *rows_pulled = b->server->rows_pulled();
   *rows_pushed = b->server->rows_pushed();
+  return 0;
+}
+
+/* ---- dense tables: `size` fp32 elements range-partitioned over the servers' shards ----
+ * rule: 0 SGD (w -= lr*g), 1 Adagrad, 2 the reference's literal rule (w = lr*g).  Creation is collective like the
+ * sparse tables': every rank creates the same table, then the ranks synchronise before the first pull. */
+int64_t tips_ps_dense_create(const char* name, const int* servers, int nservers, int local_shards, int64_t size,
+                             int rule, double lr, double eps) {
+  try {
+    Context& ctx = Context::Global();
+    if (!ctx.initialized()) return Fail(kPrecondition, "tips is not initialised");
+    if (size < 0 || rule < 0 || rule > 2) return Fail(kInvalidArgument, "bad size or update rule");
+    std::vector<int> sv(servers, servers + nservers);
+    for (int s : sv)
+      if (s < 0 || s >= ctx.size()) return Fail(kInvalidArgument, "server rank out of range");
+    auto b   = std::make_unique<DenseBundle>();
+    b->table = std::make_unique<DenseTable<float>>(sv, ctx.rank(), local_shards);
+    b->table->Resize(static_cast<size_t>(size));
+    b->server = std::make_unique<DensePsServer>(name, b->table.get(), static_cast<DenseRule>(rule), lr, eps);
+    b->server->Start();
+    b->client = std::make_unique<DensePsClient>(name, b->table.get(), ctx.rank());
+    std::lock_guard<std::mutex> lock(g_mu);
+    int64_t id  = g_next++;
+    g_dense[id] = std::move(b);
+    return id;
+  } catch (const std::exception& e) {
+    return Fail(kInternal, e.what());
+  }
+}
+
+int tips_ps_dense_destroy(int64_t id) {
+  std::unique_ptr<DenseBundle> b;
+  {
+    std::lock_guard<std::mutex> lock(g_mu);
+    auto it = g_dense.find(id);
+    if (it == g_dense.end()) return 0;
+    b = std::move(it->second);
+    g_dense.erase(it);
+  }
+  b->server->Stop();
+  return 0;
+}
+
+/* out receives the elements [begin, end). */
+int tips_ps_dense_pull(int64_t id, int64_t begin, int64_t end, float* out, int timeout_ms) {
+  try {
+    DenseBundle* b = GetDense(id);
+    if (!b) return Fail(kInvalidArgument, "unknown dense ps table");
+    auto fut = b->client->Pull(static_cast<uint64_t>(begin), static_cast<uint64_t>(end), out);
+    if (!fut->Wait(timeout_ms)) return Fail(kTimeout, "dense pull timed out");
+    if (!fut->status.ok()) return Fail(fut->status.code(), fut->status.message());
+    return 0;
+  } catch (const std::exception& e) {
+    return Fail(kInternal, e.what());
+  }
+}
+
+/* op 0: `values` is the gradient of [begin, end), the owning shards apply the table's rule; op 1: assignment. */
+int tips_ps_dense_push(int64_t id, int64_t begin, int64_t end, const float* values, int op, int timeout_ms) {
+  try {
+    DenseBundle* b = GetDense(id);
+    if (!b) return Fail(kInvalidArgument, "unknown dense ps table");
+    auto fut = b->client->Push(static_cast<uint64_t>(begin), static_cast<uint64_t>(end), values,
+                               static_cast<DensePushOp>(op));
+    if (!fut->Wait(timeout_ms)) return Fail(kTimeout, "dense push timed out");
+    if (!fut->status.ok()) return Fail(fut->status.code(), fut->status.message());
+    if (fut->missing_rows) return Fail(kPrecondition, "dense push: a server rejected a range");
+    return 0;
+  } catch (const std::exception& e) {
+    return Fail(kInternal, e.what());
+  }
+}
+
+/* Elements stored on this rank, and the sum of them (computed on the shard threads in parallel). */
+int tips_ps_dense_local(int64_t id, int64_t* count, double* sum) {
+  DenseBundle* b = GetDense(id);
+  if (!b) return Fail(kInvalidArgument, "unknown dense ps table");
+  std::mutex mu;
+  int64_t n = 0;
+  double s  = 0;
+  b->table->ForEach([&](size_t, float& v) {
+    std::lock_guard<std::mutex> lock(mu);
+    ++n;
+    s += v;
+  });
+  *count = n;
+  *sum   = s;
+  return 0;
+}
+
+int tips_ps_dense_save(int64_t id, const char* path) {
+  DenseBundle* b = GetDense(id);
+  if (!b) return Fail(kInvalidArgument, "unknown dense ps table");
+  Status st = b->table->Save(path);
+  return st.ok() ? 0 : Fail(st.code(), st.message());
+}
+
+int tips_ps_dense_load(int64_t id, const char* path) {
+  DenseBundle* b = GetDense(id);
+  if (!b) return Fail(kInvalidArgument, "unknown dense ps table");
+  Status st = b->table->Load(path);
+  return st.ok() ? 0 : Fail(st.code(), st.message());
+}
+
+int tips_ps_dense_counters(int64_t id, uint64_t* pulled, uint64_t* pushed) {
+  DenseBundle* b = GetDense(id);
+  if (!b) return Fail(kInvalidArgument, "unknown dense ps table");
+  *pulled = b->server->elements_pulled();
+  *pushed = b->server->elements_pushed();
   return 0;
 }
 

@@ -81,7 +81,7 @@ class CtrTrainer:
             opt = FusedAdam(self.mlp.parameters(), lr=mlp_lr, weight_decay=0.0)
             self.opt = tips.DistributedOptimizer(opt) if tips.is_initialized() else opt
         if tips.is_initialized() and tips.size() > 1:
-            tips.broadcast_parameters(self.mlp.state_dict(), root_rank=0)
+            tips.broadcast_parameters(self.mlp.state_dict(), root_rank=0, optimizer=None if self.graph else self.opt)
             if self.graph:  # the flat master copies follow the broadcast parameters
                 for fs in self.opt.build():
                     if fs.low:
@@ -136,6 +136,12 @@ class CtrTrainer:
             self._g = g
         self._g.replay()
         return self._loss_static
+
+    def close(self):
+        """Release the tables and the captured graph."""
+        self._g = None
+        self._loss_static = None
+        self.tables.close()
 
     def check(self):
         from ..ops.linear import gemm_status

@@ -70,13 +70,14 @@ _PROTOS = {
     "tipsk_ps_acc_bytes": (U, [U, I]),
     "tipsk_ps_inbox_bytes": (U, [I, U, I]),
     "tipsk_ps_ctl_bytes": (U, []),
-    "tipsk_ps_configure": (I, [PP, PP, PP, PP, PP, I, I, POINTER(U), POINTER(U), POINTER(L), I, I, U, U]),
+    "tipsk_ps_configure": (I, [PP, PP, PP, PP, PP, PP, PP, I, I, POINTER(U), POINTER(U), POINTER(L), I, I, U, U, U]),
     "tipsk_ps_traffic": (I, [POINTER(U)]),
     "tipsk_ps_phase_timing": (I, [I]),
     "tipsk_ps_phase_ms": (I, [POINTER(F)]),
+    "tipsk_ps_pull_phase_ms": (I, [POINTER(F)]),
     "tipsk_ps_status": (I, [POINTER(c_int32), POINTER(U)]),
-    "tipsk_ps_pull": (I, [PP, PP, L, L, L, I, I, P]),
-    "tipsk_ps_push": (I, [PP, PP, L, L, L, I, F, I, F, F, P]),
+    "tipsk_ps_pull": (I, [PP, PP, L, L, L, I, I, I, P]),
+    "tipsk_ps_push": (I, [PP, PP, L, L, L, I, F, I, F, F, I, P]),
     "tipsk_ps_push_async": (I, [PP, PP, L, L, L, I, F, I, F, F, P]),
     "tipsk_gemm_bf16": (I, [P, P, P, P, P, I, I, I, I, I, I, I, P]),
     "tipsk_copy4d": (I, [P, P, L, L, L, L, P, P, P]),
@@ -91,6 +92,7 @@ _PROTOS = {
     "tipsk_conv_status": (I, []),
     "tipsk_stem_geometry": (I, [I, I, P, P, P, P]),
     "tipsk_stem_pad": (I, [P, P, I, I, I, P]),
+    "tipsk_stem_pad_nchw_f32": (I, [P, P, I, I, I, P]),
     "tipsk_stem_conv_fwd": (I, [P, P, P, I, I, I, I, P, P, P]),
     "tipsk_stem_conv_wgrad": (I, [P, P, P, I, I, I, I, P]),
     "tipsk_maxpool3x3s2_fwd": (I, [P, P, P, I, I, I, I, I, P]),

@@ -33,7 +33,15 @@ def _is_stem(x, weight, stride, padding) -> bool:
             and not x.requires_grad)
 
 
+def _is_raw_image(x, weight, stride, padding) -> bool:
+    """An fp32 NCHW image batch handed straight to the stem: the padding copy changes layout and casts."""
+    return (x.dtype == torch.float32 and x.dim() == 4 and x.is_contiguous() and weight.dtype == torch.bfloat16
+            and _is_stem(x, weight, stride, padding))
+
+
 def supported(x: torch.Tensor, weight: torch.Tensor, stride: int, padding: int) -> bool:
+    if x.is_cuda and _is_raw_image(x, weight, stride, padding):
+        return True
     if not (x.is_cuda and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and x.dim() == 4):
         return False
     if _is_stem(x, weight, stride, padding):
@@ -155,16 +163,21 @@ class _StemFn(torch.autograd.Function):
     def forward(ctx, x, weight, stats):
         import ctypes
         lib = base.K()
-        xc = _nhwc(x)
+        raw = x.dtype == torch.float32
+        xc = x if raw else _nhwc(x)
         n, _, h, w = xc.shape
         cout = weight.shape[0]
         g = [ctypes.c_int() for _ in range(4)]
         lib.tipsk_stem_geometry(h, w, *[ctypes.byref(v) for v in g])
         hp, wp, ho, wo = (v.value for v in g)
-        xp = torch.empty((n, hp, wp, 8), dtype=x.dtype, device=x.device)
-        base.check(lib.tipsk_stem_pad(xc.data_ptr(), xp.data_ptr(), n, h, w, base.stream()), "stem_pad")
+        xp = torch.empty((n, hp, wp, 8), dtype=weight.dtype, device=x.device)
+        if raw:
+            base.check(lib.tipsk_stem_pad_nchw_f32(xc.data_ptr(), xp.data_ptr(), n, h, w, base.stream()),
+                       "stem_pad_nchw")
+        else:
+            base.check(lib.tipsk_stem_pad(xc.data_ptr(), xp.data_ptr(), n, h, w, base.stream()), "stem_pad")
         wpad = F.pad(weight, (0, 5, 0, 1)).contiguous()  # [C_out, 7, 8, 8]
-        y = torch.empty((n, cout, ho, wo), dtype=x.dtype, device=x.device, memory_format=torch.channels_last)
+        y = torch.empty((n, cout, ho, wo), dtype=weight.dtype, device=x.device, memory_format=torch.channels_last)
         base.check(lib.tipsk_stem_conv_fwd(
             xp.data_ptr(), wpad.data_ptr(), y.data_ptr(), n, h, w, cout,
             stats.data_ptr() if stats is not None else None,

@@ -14,12 +14,40 @@ server-side SGD rule lives in the parameter server
 """
 from __future__ import annotations
 
+import weakref
 from typing import List
 
 import torch
 
 from ..parallel.buckets import Bucket, build_buckets
 from . import base
+
+
+# Every flat parameter buffer alive in this process: code that overwrites parameters from outside an optimizer
+# (a broadcast, a loaded state dict) finds the fused optimizer state that owns them here and refreshes its fp32
+# master copy, which would otherwise be written back over the new values by the next step.
+_flat_registry = weakref.WeakSet()
+
+
+def refresh_masters_of(tensors) -> int:
+    """Re-read the fp32 master weights of every fused optimizer that owns one of `tensors` (parameters that were
+    just overwritten in place).  Returns the number of flat buffers refreshed."""
+    states = list(_flat_registry)
+    if not states:
+        return 0
+    spans = [(fs, fs.flat_param.data_ptr(), fs.flat_param.data_ptr() + fs.flat_param.numel() * fs.flat_param.element_size())
+             for fs in states]
+    hit = []
+    for t in tensors:
+        if not isinstance(t, torch.Tensor) or t.numel() == 0:
+            continue
+        ptr = t.data_ptr()
+        for fs, lo, hi in spans:
+            if lo <= ptr < hi and fs not in hit:
+                hit.append(fs)
+    for fs in hit:
+        fs.refresh_master_from_params()
+    return len(hit)
 
 
 class _FlatBucketState:
@@ -43,6 +71,7 @@ class _FlatBucketState:
         self.rank = 0
         self.param_off = -1
         self._pending_full = {}    # full-size tensors loaded on this rank and not yet shared with the others
+        _flat_registry.add(self)
 
     # -- update inside the allreduce: this rank keeps master weights and state of the vectors it owns -------------
     @property

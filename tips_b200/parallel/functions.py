@@ -26,8 +26,8 @@ except Exception:  # pragma: no cover
 
 def broadcast_parameters(params, root_rank: int = 0, prefix: str = "tips.bcast", optimizer=None) -> None:
     """Broadcast parameters (a state_dict, a list of (name, tensor) or an iterable of tensors) in place.
-    Pass the fused `optimizer` that already owns these parameters, if there is one, so that its fp32 master
-    weights follow the new values."""
+    A fused optimizer that already owns these parameters is found through its flat buffers and its fp32 master
+    weights follow the new values (`optimizer` may still be passed; it is refreshed as a whole)."""
     if isinstance(params, dict):
         items = sorted(params.items())
     else:
@@ -44,6 +44,9 @@ def broadcast_parameters(params, root_rank: int = 0, prefix: str = "tips.bcast",
         C.synchronize(h)
     if optimizer is not None and hasattr(optimizer, "refresh_master_from_params"):
         optimizer.refresh_master_from_params()
+    else:
+        from ..ops.optim import refresh_masters_of
+        refresh_masters_of(t for _, t in items)
 
 
 broadcast_variables = broadcast_parameters

@@ -80,6 +80,7 @@ class ShardedEmbedding:
         # rows one sender may send to one owner in a push: the worst case (every distinct row of a batch has the
         # same owner), so a skewed batch can never overflow an inbox
         self.inbox_cap = (expected_batch * num_fields + 1) // 2 * 2
+        self.item_cap = expected_batch * num_fields   # items (sample, field) of a batch that an indexed pull can hold
         lib = base.K()
         self._alloc_bytes = (slab_bytes, int(lib.tipsk_ps_acc_bytes(slots, dim)),
                              int(lib.tipsk_ps_inbox_bytes(n, self.inbox_cap, dim)) if n > 1 else 0,
@@ -106,8 +107,10 @@ class ShardedEmbedding:
         nlocal = n if self.emulated else 1
         dev = self.device
         self.accs = [torch.zeros(acc_bytes, dtype=torch.uint8, device=dev) for _ in range(nlocal)]
-        self.ulists = [torch.zeros(self.slots, dtype=torch.int32, device=dev) for _ in range(nlocal)]
+        self.ulists = [torch.zeros(2 * self.slots, dtype=torch.int32, device=dev) for _ in range(nlocal)]
         self.ctls = [torch.zeros(ctl_bytes, dtype=torch.uint8, device=dev) for _ in range(nlocal)]
+        self.item_slots = [torch.zeros(self.item_cap, dtype=torch.int32, device=dev) for _ in range(nlocal)]
+        self.caches = [torch.empty(self.slots * self.dim * 4, dtype=torch.uint8, device=dev) for _ in range(nlocal)]
         if self.emulated or n == 1:
             self.slabs = [torch.empty(slab_bytes, dtype=torch.uint8, device=dev) for _ in range(nlocal)]
             self.inboxes = [torch.zeros(max(inbox_bytes, 16), dtype=torch.uint8, device=dev) for _ in range(nlocal)]
@@ -139,15 +142,29 @@ class ShardedEmbedding:
         n = self.size
         base.check(lib.tipsk_ps_configure(base.ptr_array(self._slab_ptrs), base.ptr_array(self._inbox_ptrs),
                                           base.ptr_array(self.accs), base.ptr_array(self.ulists),
-                                          base.ptr_array(self.ctls), n, len(self.accs),
+                                          base.ptr_array(self.ctls), base.ptr_array(self.item_slots),
+                                          base.ptr_array(self.caches), n, len(self.accs),
                                           base.u64_array(self.field_off), base.u64_array(self.state_off),
                                           base.i64_array([self.rows_per_shard] * self.num_fields), self.num_fields,
-                                          self.dim, self.slots, self.inbox_cap), "ps_configure")
+                                          self.dim, self.slots, self.inbox_cap, self.item_cap), "ps_configure")
         _active = self
 
     def _activate(self):
+        if self.slabs is None:
+            raise RuntimeError("this table was closed")
         if _active is not self:
             self._configure()
+
+    def close(self):
+        """Release the device memory of the tables (the kernel library keeps no pointer to it afterwards)."""
+        global _active
+        if _active is self:
+            _active = None
+        torch.cuda.synchronize()
+        self._sync_ranks()
+        self.slabs = self.inboxes = self.accs = self.ulists = self.ctls = self.item_slots = self.caches = None
+        self._handles = None
+        self._slab_ptrs = self._inbox_ptrs = []
 
     # ------------------------------------------------------------------ data path
     def _per_rank(self, tensors):
@@ -157,27 +174,41 @@ class ShardedEmbedding:
             return base.ptr_array(list(tensors)), tensors[0]
         return base.ptr_array([tensors]), tensors
 
-    def pull(self, ids, out=None, out_col0: int = 0, dtype=torch.bfloat16, fence: bool = True):
-        """Gather rows: ids [B, F] int64 -> out[:, out_col0 + f*dim : ...] (a new [B, F*dim] tensor if out is None)."""
+    def pull(self, ids, out=None, out_col0: int = 0, dtype=torch.bfloat16, fence: bool = True, index: bool = False):
+        """Gather rows: ids [B, F] int64 -> out[:, out_col0 + f*dim : ...] (a new [B, F*dim] tensor if out is None).
+
+        `index=True` resolves the batch into its distinct rows first and fetches each of them once (about half of a
+        Zipf batch is duplicates); the index stays in place for a following ``push(ids, ..., reuse_index=True)`` of
+        the same, unmodified ids, which then skips the hashing.  Any other pull or push drops it."""
         self._activate()
         ids_arr, ids0 = self._per_rank(ids)
         b = ids0.shape[0]
+        if index and b * self.num_fields > self.item_cap:
+            index = False  # a batch larger than announced: plain pull
         if out is None:
             mk = lambda: torch.empty(b, self.num_fields * self.dim, dtype=dtype, device=self.device)
             out = [mk() for _ in range(self.size)] if self.emulated else mk()
         out_arr, out0 = self._per_rank(out)
         base.check(base.K().tipsk_ps_pull(ids_arr, out_arr, b, out0.stride(0), out_col0, base.code(out0),
-                                          int(fence and self.sync), base.stream()), "ps_pull")
+                                          int(fence and self.sync), int(index and self.sync), base.stream()),
+                   "ps_pull")
+        self._indexed = bool(index and self.sync)
         return out
 
-    def push(self, ids, grads, grad_col0: int = 0, grad_scale: float = 1.0, lr: Optional[float] = None):
+    def push(self, ids, grads, grad_col0: int = 0, grad_scale: float = 1.0, lr: Optional[float] = None,
+             reuse_index: bool = False):
         """Scatter-reduce the row gradients to their owners and apply the optimizer there."""
         self._activate()
         ids_arr, ids0 = self._per_rank(ids)
         g_arr, g0 = self._per_rank(grads)
-        fn = base.K().tipsk_ps_push if self.sync else base.K().tipsk_ps_push_async
-        base.check(fn(ids_arr, g_arr, ids0.shape[0], g0.stride(0), grad_col0, base.code(g0), float(grad_scale),
-                      self.rule, float(self.lr if lr is None else lr), float(self.eps), base.stream()), "ps_push")
+        args = (ids_arr, g_arr, ids0.shape[0], g0.stride(0), grad_col0, base.code(g0), float(grad_scale), self.rule,
+                float(self.lr if lr is None else lr), float(self.eps))
+        if self.sync:
+            reuse = bool(reuse_index and getattr(self, "_indexed", False))
+            base.check(base.K().tipsk_ps_push(*args, int(reuse), base.stream()), "ps_push")
+            self._indexed = False
+        else:
+            base.check(base.K().tipsk_ps_push_async(*args, base.stream()), "ps_push")
         base.count_launches(1)
 
     def check(self):
@@ -195,11 +226,12 @@ class ShardedEmbedding:
         return int(touched.value)
 
     def traffic(self):
-        """(rows sent to owners, rows that crossed NVLink) by synchronous pushes since the last call. Synchronises."""
+        """(distinct rows of the pushed batches, those that crossed NVLink to their owner, rows that indexed pulls
+        read over NVLink) since the last call.  Synchronises."""
         self._activate()
-        out = (ctypes.c_uint64 * 2)()
+        out = (ctypes.c_uint64 * 3)()
         base.check(base.K().tipsk_ps_traffic(out), "ps_traffic")
-        return int(out[0]), int(out[1])
+        return int(out[0]), int(out[1]), int(out[2])
 
     # ------------------------------------------------------------------ host views / checkpoint
     def local_shard(self, field: int, rank: Optional[int] = None, state: bool = False) -> torch.Tensor:
@@ -325,15 +357,20 @@ class _LookupFn(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, table, ids, anchor, out, col0, grad_scale):
-        table.pull(ids, out=out, out_col0=col0)
+        # the backward pass pushes the gradients of these very ids: with several ranks the batch is resolved into its
+        # distinct rows once, for the pull (each row crosses NVLink once) and for the push (no second hashing);
+        # with one rank the plain lookup is as fast and needs no extra pass
+        table.pull(ids, out=out, out_col0=col0, index=table.size > 1)
         ctx.table, ctx.ids, ctx.col0, ctx.grad_scale = table, ids, col0, grad_scale
+        ctx.ids_version = ids._version
         ctx.mark_dirty(out)
         return out
 
     @staticmethod
     def backward(ctx, dout):
         g = dout if dout.stride(1) == 1 else dout.contiguous()
-        ctx.table.push(ctx.ids, g, grad_col0=ctx.col0, grad_scale=ctx.grad_scale)
+        ctx.table.push(ctx.ids, g, grad_col0=ctx.col0, grad_scale=ctx.grad_scale,
+                       reuse_index=ctx.ids._version == ctx.ids_version)
         return None, None, None, None, None, None
 
 

@@ -39,6 +39,15 @@ def _lib_ps():
         lib.tips_ps_table_save.argtypes = [c_int64, c_char_p, c_int]
         lib.tips_ps_table_load.argtypes = [c_int64, c_char_p, c_int, c_int]
         lib.tips_ps_server_counters.argtypes = [c_int64, POINTER(c_uint64), POINTER(c_uint64)]
+        lib.tips_ps_dense_create.restype = c_int64
+        lib.tips_ps_dense_create.argtypes = [c_char_p, POINTER(c_int), c_int, c_int, c_int64, c_int, c_double, c_double]
+        lib.tips_ps_dense_destroy.argtypes = [c_int64]
+        lib.tips_ps_dense_pull.argtypes = [c_int64, c_int64, c_int64, c_void_p, c_int]
+        lib.tips_ps_dense_push.argtypes = [c_int64, c_int64, c_int64, c_void_p, c_int, c_int]
+        lib.tips_ps_dense_local.argtypes = [c_int64, POINTER(c_int64), POINTER(c_double)]
+        lib.tips_ps_dense_save.argtypes = [c_int64, c_char_p]
+        lib.tips_ps_dense_load.argtypes = [c_int64, c_char_p]
+        lib.tips_ps_dense_counters.argtypes = [c_int64, POINTER(c_uint64), POINTER(c_uint64)]
         _declared = True
     return lib
 
@@ -128,4 +137,87 @@ class HostSparseTable:
         if self._id > 0:
             barrier()
             _lib_ps().tips_ps_table_destroy(self._id)
+            self._id = -1
+
+
+class HostDenseTable:
+    """A dense fp32 vector of `size` elements, range-partitioned over the server ranks' shards; pulled and pushed
+    by index range, the update rule applied by the owning shard's thread (csrc/ps/dense_server.h).
+
+    The reference declares this table (range partition, Lookup, ForEach, Load/Save and a pull access method,
+    tips/core/ps/dense_table.h:49-131, dense_access_method.h:10-25) but neither builds nor serves it."""
+
+    def __init__(self, name: str, size: int, route: Optional[Route] = None, optimizer: str = "sgd", lr: float = 0.01,
+                 eps: float = 1e-8, local_shards: int = 1, timeout_s: float = 60.0):
+        _require_init()
+        if optimizer not in _RULES:
+            raise ValueError(f"optimizer must be one of {sorted(_RULES)}")
+        self.route = route or Route()
+        self.name, self.size = name, int(size)
+        self.timeout_ms = int(timeout_s * 1000)
+        lib = _lib_ps()
+        servers = (c_int * len(self.route.servers))(*self.route.servers)
+        self._id = lib.tips_ps_dense_create(name.encode(), servers, len(self.route.servers), local_shards, self.size,
+                                            _RULES[optimizer], lr, eps)
+        if self._id < 0:
+            raise TipsError("dense ps table create: " + lib.tips_ps_last_error().decode(), int(-self._id))
+        barrier()
+
+    def _range(self, begin, end):
+        end = self.size if end is None else end
+        if not 0 <= begin <= end <= self.size:
+            raise ValueError(f"range [{begin}, {end}) is outside the table of {self.size} elements")
+        return begin, end
+
+    def pull(self, begin: int = 0, end: Optional[int] = None) -> np.ndarray:
+        lib = _lib_ps()
+        begin, end = self._range(begin, end)
+        out = np.empty(end - begin, dtype=np.float32)
+        rc = lib.tips_ps_dense_pull(self._id, begin, end, out.ctypes.data, self.timeout_ms)
+        if rc < 0:
+            raise TipsError("dense pull: " + lib.tips_ps_last_error().decode(), -rc)
+        return out
+
+    def _push(self, values, begin, op):
+        lib = _lib_ps()
+        v = np.ascontiguousarray(np.asarray(values, dtype=np.float32).reshape(-1))
+        begin, end = self._range(begin, begin + v.size)
+        rc = lib.tips_ps_dense_push(self._id, begin, end, v.ctypes.data, op, self.timeout_ms)
+        if rc < 0:
+            raise TipsError("dense push: " + lib.tips_ps_last_error().decode(), -rc)
+
+    def push(self, grads, begin: int = 0) -> None:
+        """Send the gradient of elements [begin, begin + len(grads)); the owning shards apply the update rule."""
+        self._push(grads, begin, 0)
+
+    def assign(self, values, begin: int = 0) -> None:
+        """Overwrite elements [begin, begin + len(values)) (initial values, checkpoint restore)."""
+        self._push(values, begin, 1)
+
+    def local_count_and_sum(self):
+        """(number of elements stored on this rank, their sum), computed shard-parallel on the server threads."""
+        n, s = c_int64(0), c_double(0)
+        _lib_ps().tips_ps_dense_local(self._id, ctypes.byref(n), ctypes.byref(s))
+        return int(n.value), float(s.value)
+
+    def save(self, path: str) -> None:
+        lib = _lib_ps()
+        if lib.tips_ps_dense_save(self._id, path.encode()) != 0:
+            raise TipsError("dense save: " + lib.tips_ps_last_error().decode())
+
+    def load(self, path: str) -> None:
+        """Read a dump written by any rank under any sharding; elements this rank owns now are kept."""
+        lib = _lib_ps()
+        if lib.tips_ps_dense_load(self._id, path.encode()) != 0:
+            raise TipsError("dense load: " + lib.tips_ps_last_error().decode())
+
+    def counters(self):
+        a, b = c_uint64(0), c_uint64(0)
+        _lib_ps().tips_ps_dense_counters(self._id, ctypes.byref(a), ctypes.byref(b))
+        return {"elements_pulled": a.value, "elements_pushed": b.value}
+
+    def close(self):
+        if self._id > 0:
+            barrier()
+            _lib_ps().tips_ps_dense_destroy(self._id)
             self._id = -1

@@ -64,6 +64,9 @@ def save_checkpoint(path: str, model: torch.nn.Module, optimizer=None, extra: Op
 def load_checkpoint(path: str, model: torch.nn.Module, optimizer=None, map_location="cpu") -> dict:
     payload = torch.load(path, map_location=map_location, weights_only=False)
     model.load_state_dict(payload["model"])
+    # a fused optimizer that owns these parameters keeps fp32 master copies: they follow the loaded values
+    from ..ops.optim import refresh_masters_of
+    refresh_masters_of(model.state_dict().values())
     if optimizer is not None and "optimizer" in payload:
         _load_optimizer_state(optimizer, payload["optimizer"])
     return payload.get("extra", {})

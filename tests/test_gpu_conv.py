@@ -121,7 +121,8 @@ def test_stem_takes_an_fp32_nchw_image():
     y1.backward(dy)
     assert _status() == 0
     assert y1.dtype == torch.bfloat16 and torch.equal(y0, y1)
-    assert torch.equal(g0, conv.weight.grad)
+    # the weight gradient is summed over pixel ranges with fp32 atomics, so its last bits depend on arrival order
+    assert torch.allclose(g0.float(), conv.weight.grad.float(), rtol=2e-2, atol=2e-2 * float(g0.float().abs().max()))
 
 
 def test_conv_module_falls_back_for_other_filters():

@@ -28,14 +28,14 @@ PULL_PHASES = ("index", "pull fence", "fetch", "expand")
 
 def _max_over_ranks(values):
     t = torch.tensor(values, dtype=torch.float64)
-    if tips.size() > 1:
+    if tips.is_initialized() and tips.size() > 1:
         t = tips.allreduce(t, op=tips.Max, name=None)
     return [float(v) for v in t]
 
 
 def _sum_over_ranks(values):
     t = torch.tensor(values, dtype=torch.float64)
-    if tips.size() > 1:
+    if tips.is_initialized() and tips.size() > 1:
         t = tips.allreduce(t, op=tips.Sum, name=None)
     return [float(v) for v in t]
 
@@ -48,20 +48,37 @@ def main(argv=None):
     ap.add_argument("--dim", type=int, default=64)
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--plain", action="store_true", help="plain pull and push (no index shared between them)")
+    ap.add_argument("--emulate", type=int, default=0,
+                    help="run that many ranks on ONE GPU (one launch covers all of them): the kernels without NVLink")
     ap.add_argument("--out", default="")
     a = ap.parse_args(argv)
-    tips.init()
-    rank, n = tips.rank(), tips.size()
+    em = a.emulate if a.emulate > 1 else 0
+    if em:
+        from tips_b200.config import set_config
+        from tips_b200.parallel import device as _device
+        set_config(symm_window_bytes=1 << 20, comm_blocks=8)
+        _device.setup(emulate_ranks=em)
+        rank, n = 0, em
+    else:
+        tips.init()
+        rank, n = tips.rank(), tips.size()
     dev = torch.device("cuda", torch.cuda.current_device())
     table = ShardedEmbedding(a.fields, a.rows, a.dim, optimizer="adagrad", lr=0.05, init_scale=0.05, seed=0,
                              expected_batch=a.batch, device=dev)
     lib = base.K()
     warm = 5
-    batches = [synthetic_ctr_batch(a.batch, a.fields, a.rows, 13, seed=1000 * rank + i)[0].to(dev)
-               for i in range(a.iters + warm)]
-    grads = torch.randn(a.batch, a.fields * a.dim, device=dev).to(torch.bfloat16)
-    out = torch.empty(a.batch, a.fields * a.dim, dtype=torch.bfloat16, device=dev)
-    distinct = sum(int(b[:, f].unique().numel()) for b in batches[warm:] for f in range(a.fields))
+
+    def ids_of(i):
+        mk = lambda r: synthetic_ctr_batch(a.batch, a.fields, a.rows, 13, seed=1000 * r + i)[0].to(dev)
+        return [mk(r) for r in range(em)] if em else mk(rank)
+
+    batches = [ids_of(i) for i in range(a.iters + warm)]
+    mk_g = lambda: torch.randn(a.batch, a.fields * a.dim, device=dev).to(torch.bfloat16)
+    mk_o = lambda: torch.empty(a.batch, a.fields * a.dim, dtype=torch.bfloat16, device=dev)
+    grads = [mk_g() for _ in range(em)] if em else mk_g()
+    out = [mk_o() for _ in range(em)] if em else mk_o()
+    distinct = sum(int(t[:, f].unique().numel()) for b in batches[warm:] for t in (b if em else [b])
+                   for f in range(a.fields))
     base.check(lib.tipsk_ps_phase_timing(1), "phase_timing")
     acc = [0.0] * 5
     pacc = [0.0] * 4
@@ -99,7 +116,7 @@ def main(argv=None):
     if rank == 0:
         row_bytes = a.dim * 4 + 8
         items = a.batch * a.fields
-        res = {"n_gpus": n, "rows_per_table": a.rows, "batch_per_gpu": a.batch, "fields": a.fields, "dim": a.dim,
+        res = {"n_gpus": 1 if em else n, "emulated_ranks": em, "rows_per_table": a.rows, "batch_per_gpu": a.batch, "fields": a.fields, "dim": a.dim,
                "iters": it, "indexed": not a.plain,
                "us": {**{p: round(per[7 + k], 1) for k, p in enumerate(PULL_PHASES) if not a.plain},
                       "pull (with its fence)": round(per[5], 1),
@@ -118,7 +135,8 @@ def main(argv=None):
         if a.out:
             with open(a.out, "a") as f:
                 f.write(line + "\n")
-    tips.shutdown()
+    if not em:
+        tips.shutdown()
 
 
 if __name__ == "__main__":

@@ -265,7 +265,7 @@ __device__ __forceinline__ void LoadGrad4(const GradT* g, float* out) {
   }
 }
 
-constexpr int kRowsInFlight = 4;  // rows that a lane group loads before it stores the first one
+constexpr int kRowsInFlight = 8;  // rows that a lane group loads before it stores the first one
 
 // Resolves every (sample, field) item of the batch into a slot of the local table: the distinct rows land in
 // the list, item_slot[item] holds the slot (kNoSlot for a bad id or a full table).
@@ -297,26 +297,59 @@ PsIndexKernel(PsLaunch args, PsMeta meta, int64_t batch, uint64_t slots) {
   }
 }
 
+constexpr int kChunk = 256;  // list entries that a block resolves together (one per thread)
+
+// Moves the rows that a block has resolved into shared memory (s_slot: table slot or kNoSlot, s_ptr: the other
+// end of the copy): `lpi` lanes per row, kRowsInFlight rows loaded by a lane group before the first is consumed.
+// load(ptr, slot, v) returns the 16 bytes of vector v of a row, store(ptr, slot, v, q) consumes them.
+template <typename Load, typename Store>
+__device__ __forceinline__ void MoveRows(const uint32_t* s_slot, char* const* s_ptr, int dim, Load load, Store store) {
+  const int vecs = dim / 4;
+  int lpi = 1;
+  while (lpi < vecs && lpi < 32) lpi <<= 1;
+  const int groups  = kChunk / lpi;
+  const int g       = threadIdx.x / lpi;
+  const int sublane = threadIdx.x % lpi;
+  for (int v = sublane; v < vecs; v += lpi) {
+    for (int r0 = g; r0 < kChunk; r0 += groups * kRowsInFlight) {
+      U4 q[kRowsInFlight];
+      uint32_t sl[kRowsInFlight];
+      char* ptr[kRowsInFlight];
+#pragma unroll
+      for (int u = 0; u < kRowsInFlight; ++u) {
+        const int r = r0 + u * groups;
+        sl[u]       = r < kChunk ? s_slot[r] : kNoSlot;
+        if (sl[u] == kNoSlot) continue;
+        ptr[u] = s_ptr[r];
+        q[u]   = load(ptr[u], sl[u], v);
+      }
+#pragma unroll
+      for (int u = 0; u < kRowsInFlight; ++u)
+        if (sl[u] != kNoSlot) store(ptr[u], sl[u], v, q[u]);
+    }
+  }
+}
+
 // Fetches every distinct row of the indexed batch once, from its owner's HBM, into the row cache (converted to
-// the output dtype).
+// the output dtype).  A block resolves 256 list entries at a time (slot -> key -> owner and address, one entry
+// per thread, so the dependent loads of all of them overlap), then moves their rows.
 template <typename OutT>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(kChunk)
 PsFetchKernel(PsLaunch args, PsMeta meta, uint64_t slots) {
+  __shared__ uint32_t s_slot[kChunk];
+  __shared__ char* s_ptr[kChunk];
   const PsRank& pr = args.r[blockIdx.y];
   const int n      = pr.nranks;
   const int dim    = meta.dim;
-  const int vecs   = dim / 4;
-  const RowLanes L(dim);
-  const int64_t warp_global = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
-  const int64_t nwarps      = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
-  unsigned long long* keys  = reinterpret_cast<unsigned long long*>(pr.acc);
-  OutT* cache               = reinterpret_cast<OutT*>(pr.cache);
-  const int64_t total       = *reinterpret_cast<volatile uint32_t*>(&pr.ctl->ucount);
-  for (int64_t base = warp_global * 32; base < total; base += nwarps * 32) {
-    const int64_t mine = base + L.lane;
-    uint32_t slot   = kNoSlot;
-    const char* row = nullptr;
-    bool remote     = false;
+  unsigned long long* keys = reinterpret_cast<unsigned long long*>(pr.acc);
+  OutT* cache              = reinterpret_cast<OutT*>(pr.cache);
+  const int64_t total      = *reinterpret_cast<volatile uint32_t*>(&pr.ctl->ucount);
+  const int64_t nchunks    = (total + kChunk - 1) / kChunk;
+  for (int64_t chunk = blockIdx.x; chunk < nchunks; chunk += gridDim.x) {
+    const int64_t mine = chunk * kChunk + threadIdx.x;
+    uint32_t slot = kNoSlot;
+    char* row     = nullptr;
+    int remote    = 0;
     if (mine < total) {
       slot = pr.ulist[mine];
       const unsigned long long key = keys[slot];
@@ -327,38 +360,23 @@ PsFetchKernel(PsLaunch args, PsMeta meta, uint64_t slots) {
       row    = pr.slab[owner] + meta.field_off[f] + static_cast<uint64_t>(lrow) * dim * 4;
       remote = owner != pr.rank;
     }
-    const unsigned rm = __ballot_sync(kFullMask, remote);
-    if (rm && L.lane == 0) atomicAdd(&pr.ctl->fetched_remote, static_cast<unsigned long long>(__popc(rm)));
-    for (int vb = 0; vb < vecs; vb += L.lpi) {  // uniform over the warp: the shuffles below need every lane
-      const int v       = vb + L.sublane;
-      const bool active = v < vecs;
-      for (int j0 = 0; j0 < 32; j0 += kRowsInFlight * L.ipw) {
-        U4 q[kRowsInFlight];
-        uint32_t sl[kRowsInFlight];
-#pragma unroll
-        for (int u = 0; u < kRowsInFlight; ++u) {
-          const int src = j0 + u * L.ipw + L.sub;
-          sl[u]         = kNoSlot;
-          if (j0 + u * L.ipw >= 32) continue;  // uniform over the warp
-          sl[u] = __shfl_sync(kFullMask, slot, src);
-          const char* r = reinterpret_cast<const char*>(__shfl_sync(kFullMask, reinterpret_cast<unsigned long long>(row), src));
-          if (!active) sl[u] = kNoSlot;
-          if (sl[u] != kNoSlot) q[u] = LdSysFree(r + v * 16);
-        }
-#pragma unroll
-        for (int u = 0; u < kRowsInFlight; ++u) {
-          if (sl[u] == kNoSlot) continue;
-          OutT* dst = cache + static_cast<uint64_t>(sl[u]) * dim + v * 4;
+    s_slot[threadIdx.x] = slot;
+    s_ptr[threadIdx.x]  = row;
+    const int nremote   = __syncthreads_count(remote);
+    if (threadIdx.x == 0 && nremote) atomicAdd(&pr.ctl->fetched_remote, static_cast<unsigned long long>(nremote));
+    MoveRows(
+        s_slot, s_ptr, dim, [](char* p, uint32_t, int v) { return LdSysFree(p + v * 16); },
+        [&](char*, uint32_t sl, int v, const U4& q) {
+          OutT* dst = cache + static_cast<uint64_t>(sl) * dim + v * 4;
           if (sizeof(OutT) == 4) {
-            *reinterpret_cast<U4*>(dst) = q[u];
+            *reinterpret_cast<U4*>(dst) = q;
           } else {
-            OutT o[4] = {FromFloat<OutT>(__uint_as_float(q[u].x)), FromFloat<OutT>(__uint_as_float(q[u].y)),
-                         FromFloat<OutT>(__uint_as_float(q[u].z)), FromFloat<OutT>(__uint_as_float(q[u].w))};
+            OutT o[4] = {FromFloat<OutT>(__uint_as_float(q.x)), FromFloat<OutT>(__uint_as_float(q.y)),
+                         FromFloat<OutT>(__uint_as_float(q.z)), FromFloat<OutT>(__uint_as_float(q.w))};
             *reinterpret_cast<uint2*>(dst) = *reinterpret_cast<uint2*>(o);
           }
-        }
-      }
-    }
+        });
+    __syncthreads();
   }
 }
 
@@ -485,24 +503,43 @@ PsClearIndexKernel(PsLaunch args, uint64_t slots) {
   (void)slots;
 }
 
+// Positions for the entries of a block in per-destination lists: every thread names a destination (or -1),
+// gets its position inside the block with a shared-memory atomic, one thread per destination reserves the block's
+// range with ONE global atomic, and the thread's final position comes back.  All threads of the block call it.
+__device__ __forceinline__ uint32_t ReservePositions(int dest, int ndest, uint32_t* const* counters, uint32_t* s_cnt,
+                                                     uint32_t* s_base) {
+  if (threadIdx.x < ndest) s_cnt[threadIdx.x] = 0;
+  __syncthreads();
+  uint32_t local = 0;
+  if (dest >= 0) local = atomicAdd(&s_cnt[dest], 1u);
+  __syncthreads();
+  if (threadIdx.x < ndest) s_base[threadIdx.x] = s_cnt[threadIdx.x] ? atomicAdd(counters[threadIdx.x], s_cnt[threadIdx.x]) : 0;
+  __syncthreads();
+  return dest >= 0 ? s_base[dest] + local : 0;
+}
+
 // Walks the list of distinct rows of the batch: a row this rank owns stays in the table and joins the apply
-// list; every other row goes to its owner's inbox and its slot is cleared.
-__global__ void __launch_bounds__(256)
+// list; every other row goes to its owner's inbox, its sums are zeroed and its key stays until the apply pass.
+__global__ void __launch_bounds__(kChunk)
 PsSendKernel(PsLaunch args, PsMeta meta, uint64_t slots, uint64_t cap) {
+  __shared__ uint32_t s_slot[kChunk];
+  __shared__ char* s_ptr[kChunk];
+  __shared__ uint32_t s_cnt[kMaxRanks + 1], s_base[kMaxRanks + 1];
+  __shared__ uint32_t* s_counter[kMaxRanks + 1];
   const PsRank& pr = args.r[blockIdx.y];
   const int n      = pr.nranks;
   const int dim    = meta.dim;
-  const int vecs   = dim / 4;
-  const RowLanes L(dim);
-  const int64_t warp_global = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
-  const int64_t nwarps      = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
-  unsigned long long* keys  = reinterpret_cast<unsigned long long*>(pr.acc);
-  float* sums_base          = reinterpret_cast<float*>(pr.acc + slots * 8);
-  uint32_t* apply_list      = pr.ulist + slots;
-  const int64_t total       = *reinterpret_cast<volatile uint32_t*>(&pr.ctl->ucount);
-  for (int64_t base = warp_global * 32; base < total; base += nwarps * 32) {
-    const int64_t mine = base + L.lane;
-    uint32_t slot = kNoSlot, pos = 0;
+  unsigned long long* keys = reinterpret_cast<unsigned long long*>(pr.acc);
+  float* sums_base         = reinterpret_cast<float*>(pr.acc + slots * 8);
+  uint32_t* apply_list     = pr.ulist + slots;
+  const int64_t total      = *reinterpret_cast<volatile uint32_t*>(&pr.ctl->ucount);
+  const int64_t nchunks    = (total + kChunk - 1) / kChunk;
+  // destination d < n: the inbox of rank d; destination n: this rank's apply list
+  if (threadIdx.x <= n) s_counter[threadIdx.x] = threadIdx.x < n ? &pr.ctl->send_count[threadIdx.x] : &pr.ctl->acount;
+  __syncthreads();
+  for (int64_t chunk = blockIdx.x; chunk < nchunks; chunk += gridDim.x) {
+    const int64_t mine = chunk * kChunk + threadIdx.x;
+    uint32_t slot = kNoSlot;
     int owner     = -1;
     unsigned long long key = 0;
     if (mine < total) {
@@ -511,58 +548,36 @@ PsSendKernel(PsLaunch args, PsMeta meta, uint64_t slots, uint64_t cap) {
       int64_t lrow;
       PsPlace(KeyField(key), KeyId(key), n, &owner, &lrow);
     }
-    const bool own = owner == pr.rank;
-    AppendSlots(apply_list, &pr.ctl->acount, own, slot, L.lane);
+    const bool own     = owner == pr.rank;
+    const uint32_t pos = ReservePositions(own ? n : owner, n + 1, s_counter, s_cnt, s_base);
+    char* dst = nullptr;
     if (own) {
-      owner = -1;      // nothing to send
-      slot  = kNoSlot;
-    }
-    // one atomic per (warp, owner): lanes with the same owner take consecutive positions
-    const unsigned peers = __match_any_sync(kFullMask, owner);
-    float* dst = nullptr;
-    if (owner >= 0) {
-      const int leader = __ffs(peers) - 1;
-      uint32_t first   = 0;
-      if (L.lane == leader) first = atomicAdd(&pr.ctl->send_count[owner], static_cast<uint32_t>(__popc(peers)));
-      first = __shfl_sync(peers, first, leader);
-      pos   = first + __popc(peers & ((1u << L.lane) - 1u));
+      apply_list[pos] = slot;
+      slot            = kNoSlot;  // nothing to send
+    } else if (owner >= 0) {
       if (pos < cap) {
         asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(InboxKeys(pr.inbox[owner], pr.rank, cap) + pos), "l"(key)
                      : "memory");
-        dst = InboxRows(pr.inbox[owner], n, pr.rank, cap, dim) + static_cast<uint64_t>(pos) * dim;
+        dst = reinterpret_cast<char*>(InboxRows(pr.inbox[owner], n, pr.rank, cap, dim) + static_cast<uint64_t>(pos) * dim);
       } else {
         atomicExch(pr.error, 3);  // inbox full: the row is dropped, the host raises after the step
       }
       // The key stays in its slot until the apply pass: emptying it here would cut the probe chains of the
       // rows that remain, and the reduce pass would then claim a second slot for a key that is already present.
     }
-    for (int vb = 0; vb < vecs; vb += L.lpi) {  // uniform over the warp: the shuffles below need every lane
-      const int v       = vb + L.sublane;
-      const bool active = v < vecs;
-      for (int j0 = 0; j0 < 32; j0 += kRowsInFlight * L.ipw) {
-        U4 q[kRowsInFlight];
-        float* sm[kRowsInFlight];
-        float* ds[kRowsInFlight];
-#pragma unroll
-        for (int u = 0; u < kRowsInFlight; ++u) {
-          const int src = j0 + u * L.ipw + L.sub;
-          sm[u]         = nullptr;
-          ds[u]         = nullptr;
-          if (j0 + u * L.ipw >= 32) continue;  // uniform over the warp
-          const uint32_t sl = __shfl_sync(kFullMask, slot, src);
-          ds[u] = reinterpret_cast<float*>(__shfl_sync(kFullMask, reinterpret_cast<unsigned long long>(dst), src));
-          if (sl == kNoSlot || !active) continue;
-          sm[u] = sums_base + static_cast<uint64_t>(sl) * dim + v * 4;
-          q[u]  = *reinterpret_cast<const U4*>(sm[u]);
-        }
-#pragma unroll
-        for (int u = 0; u < kRowsInFlight; ++u) {
-          if (!sm[u]) continue;
-          if (ds[u]) StSys(ds[u] + v * 4, q[u]);
-          *reinterpret_cast<float4*>(sm[u]) = make_float4(0.f, 0.f, 0.f, 0.f);
-        }
-      }
-    }
+    s_slot[threadIdx.x] = slot;
+    s_ptr[threadIdx.x]  = dst;
+    __syncthreads();
+    MoveRows(
+        s_slot, s_ptr, dim,
+        [&](char*, uint32_t sl, int v) {
+          return *reinterpret_cast<const U4*>(sums_base + static_cast<uint64_t>(sl) * dim + v * 4);
+        },
+        [&](char* d, uint32_t sl, int v, const U4& q) {
+          if (d) StSys(d + v * 16, q);
+          *reinterpret_cast<float4*>(sums_base + static_cast<uint64_t>(sl) * dim + v * 4) = make_float4(0.f, 0.f, 0.f, 0.f);
+        });
+    __syncthreads();
   }
   if (LastBlockDone(pr.ctl)) {
     __shared__ unsigned long long s_remote;
@@ -588,19 +603,19 @@ PsSendKernel(PsLaunch args, PsMeta meta, uint64_t slots, uint64_t cap) {
 }
 
 // The owner folds the rows that arrived in its inboxes into its local table and extends the apply list.
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(kChunk)
 PsOwnerReduceKernel(PsLaunch args, PsMeta meta, uint64_t slots, uint64_t cap) {
+  __shared__ uint32_t s_slot[kChunk];
+  __shared__ char* s_ptr[kChunk];
+  __shared__ uint32_t s_cnt[1], s_base[1];
+  __shared__ uint32_t* s_counter[1];
   const PsRank& pr = args.r[blockIdx.y];
   const int n      = pr.nranks;
   const int dim    = meta.dim;
-  const int vecs   = dim / 4;
-  const RowLanes L(dim);
-  const int64_t warp_global = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
-  const int64_t nwarps      = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
-  unsigned long long* keys  = reinterpret_cast<unsigned long long*>(pr.acc);
-  float* sums_base          = reinterpret_cast<float*>(pr.acc + slots * 8);
-  uint32_t* apply_list      = pr.ulist + slots;
-  char* inbox               = pr.inbox[pr.rank];
+  unsigned long long* keys = reinterpret_cast<unsigned long long*>(pr.acc);
+  float* sums_base         = reinterpret_cast<float*>(pr.acc + slots * 8);
+  uint32_t* apply_list     = pr.ulist + slots;
+  char* inbox              = pr.inbox[pr.rank];
   // exclusive prefix of the per-sender counts (written by the senders, published by the fence)
   uint32_t start[kMaxRanks + 1];
   start[0] = 0;
@@ -613,13 +628,16 @@ PsOwnerReduceKernel(PsLaunch args, PsMeta meta, uint64_t slots, uint64_t cap) {
     }
     start[s + 1] = start[s] + c;
   }
-  const int64_t total = start[kMaxRanks];
-  const float* rows   = reinterpret_cast<const float*>(inbox + kInboxHeader + static_cast<uint64_t>(n) * cap * 8);
-  for (int64_t base = warp_global * 32; base < total; base += nwarps * 32) {
-    const int64_t mine = base + L.lane;
-    uint32_t slot    = kNoSlot;
-    const float* row = nullptr;
-    bool claimed     = false;
+  const int64_t total   = start[kMaxRanks];
+  const int64_t nchunks = (total + kChunk - 1) / kChunk;
+  char* rows            = inbox + kInboxHeader + static_cast<uint64_t>(n) * cap * 8;
+  if (threadIdx.x == 0) s_counter[0] = &pr.ctl->acount;
+  __syncthreads();
+  for (int64_t chunk = blockIdx.x; chunk < nchunks; chunk += gridDim.x) {
+    const int64_t mine = chunk * kChunk + threadIdx.x;
+    uint32_t slot = kNoSlot;
+    char* row     = nullptr;
+    bool claimed  = false;
     if (mine < total) {
       int s           = 0;
       uint32_t sstart = 0;
@@ -637,35 +655,20 @@ PsOwnerReduceKernel(PsLaunch args, PsMeta meta, uint64_t slots, uint64_t cap) {
                    : "memory");
       slot = ClaimSlot(keys, slots, key, &claimed);
       if (slot == kNoSlot) atomicExch(pr.error, 1);
-      row = rows + cell * dim;
+      row = rows + cell * dim * 4;
     }
-    AppendSlots(apply_list, &pr.ctl->acount, claimed, slot, L.lane);
-    for (int vb = 0; vb < vecs; vb += L.lpi) {  // uniform over the warp: the shuffles below need every lane
-      const int v       = vb + L.sublane;
-      const bool active = v < vecs;
-      for (int j0 = 0; j0 < 32; j0 += kRowsInFlight * L.ipw) {
-        U4 q[kRowsInFlight];
-        float* sm[kRowsInFlight];
-#pragma unroll
-        for (int u = 0; u < kRowsInFlight; ++u) {
-          const int src = j0 + u * L.ipw + L.sub;
-          sm[u]         = nullptr;
-          if (j0 + u * L.ipw >= 32) continue;  // uniform over the warp
-          const uint32_t sl = __shfl_sync(kFullMask, slot, src);
-          const float* r =
-              reinterpret_cast<const float*>(__shfl_sync(kFullMask, reinterpret_cast<unsigned long long>(row), src));
-          if (sl == kNoSlot || !active) continue;
-          sm[u] = sums_base + static_cast<uint64_t>(sl) * dim + v * 4;
-          q[u]  = LdSysFree(r + v * 4);
-        }
-#pragma unroll
-        for (int u = 0; u < kRowsInFlight; ++u) {
-          if (!sm[u]) continue;
-          RedAdd4(sm[u], __uint_as_float(q[u].x), __uint_as_float(q[u].y), __uint_as_float(q[u].z),
-                  __uint_as_float(q[u].w));
-        }
-      }
-    }
+    const uint32_t pos = ReservePositions(claimed ? 0 : -1, 1, s_counter, s_cnt, s_base);
+    if (claimed) apply_list[pos] = slot;
+    s_slot[threadIdx.x] = slot;
+    s_ptr[threadIdx.x]  = row;
+    __syncthreads();
+    MoveRows(
+        s_slot, s_ptr, dim, [](char* p, uint32_t, int v) { return LdSysFree(p + v * 16); },
+        [&](char*, uint32_t sl, int v, const U4& q) {
+          RedAdd4(sums_base + static_cast<uint64_t>(sl) * dim + v * 4, __uint_as_float(q.x), __uint_as_float(q.y),
+                  __uint_as_float(q.z), __uint_as_float(q.w));
+        });
+    __syncthreads();
   }
 }
 
@@ -888,6 +891,15 @@ int PsGrid(int64_t items, int lanes_per_item) {
   int64_t warps  = (items * lanes_per_item + 31) / 32;
   int64_t blocks = (warps + 7) / 8;
   int64_t cap    = static_cast<int64_t>(NumSMs()) * 8;
+  if (blocks < 1) blocks = 1;
+  return static_cast<int>(blocks < cap ? blocks : cap);
+}
+
+// Grid of the list walkers (fetch, send, reduce): one block per 256 list entries, at most 3 blocks per SM (what
+// their register count lets an SM hold, so the grid is one wave and blocks loop over further chunks).
+int ListGrid(int64_t max_entries) {
+  int64_t blocks = (max_entries + 255) / 256;
+  int64_t cap    = static_cast<int64_t>(NumSMs()) * 3;
   if (blocks < 1) blocks = 1;
   return static_cast<int>(blocks < cap ? blocks : cap);
 }
@@ -1167,10 +1179,11 @@ int tipsk_ps_pull(const int64_t* const* ids, void* const* outs, int64_t batch, i
     return 0;
   }
   MarkPull(s);
+  dim3 lgrid(ListGrid(items), local);
   if (out_dtype == kF32)
-    PsFetchKernel<float><<<grid, 256, 0, s>>>(l, st.meta, st.slots);
+    PsFetchKernel<float><<<lgrid, 256, 0, s>>>(l, st.meta, st.slots);
   else
-    PsFetchKernel<__nv_bfloat16><<<grid, 256, 0, s>>>(l, st.meta, st.slots);
+    PsFetchKernel<__nv_bfloat16><<<lgrid, 256, 0, s>>>(l, st.meta, st.slots);
   TIPSK_LAUNCH_CHECK();
   MarkPull(s);
   if (out_dtype == kF32)
@@ -1225,13 +1238,14 @@ int tipsk_ps_push(const int64_t* const* ids, const void* const* grads, int64_t b
   if (rc) return rc;
   Mark(s);
   if (nranks > 1) {
-    PsSendKernel<<<grid, 256, 0, s>>>(l, st.meta, st.slots, st.inbox_cap);
+    dim3 lgrid(ListGrid(items), local);
+    PsSendKernel<<<lgrid, 256, 0, s>>>(l, st.meta, st.slots, st.inbox_cap);
     TIPSK_LAUNCH_CHECK();
     Mark(s);
     rc = tipsk_comm_fence(2, stream);  // every rank's rows and counts have landed
     if (rc) return rc;
     Mark(s);
-    PsOwnerReduceKernel<<<grid, 256, 0, s>>>(l, st.meta, st.slots, st.inbox_cap);
+    PsOwnerReduceKernel<<<lgrid, 256, 0, s>>>(l, st.meta, st.slots, st.inbox_cap);
     TIPSK_LAUNCH_CHECK();
     Mark(s);
   }

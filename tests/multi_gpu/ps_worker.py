@@ -54,8 +54,10 @@ def main():
     t.pull(ids, dtype=torch.float32)
     torch.cuda.synchronize()
     got = gather_tables()
+    # the hottest rows sum hundreds of fp32 gradient rows per step in arrival order (more with more ranks), and
+    # Adagrad divides by the root of the accumulated squares: the last bits of those sums show after three steps
     for f in range(fields):
-        assert torch.allclose(got[f], ws[f], atol=3e-4, rtol=1e-4), (f, (got[f] - ws[f]).abs().max())
+        assert torch.allclose(got[f], ws[f], atol=1e-3, rtol=1e-4), (f, (got[f] - ws[f]).abs().max())
     tips.barrier()
     if rank == 0:
         print("MULTI_GPU_PS_OK")

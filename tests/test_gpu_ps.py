@@ -93,16 +93,28 @@ def test_pull_push_emulated_ranks():
         device.teardown(st)
 
 
+@pytest.mark.parametrize("wire", ["fp32", "grad"])
 @pytest.mark.parametrize("indexed", [False, True])
 @pytest.mark.parametrize("ranks", [2, 4, 8])
-def test_push_with_mostly_duplicate_ids_emulated(ranks, indexed):
+def test_push_with_mostly_duplicate_ids_emulated(ranks, indexed, wire):
     """Three synchronous steps on 2, 4 and 8 emulated ranks with ids drawn from 40 hot rows for 70 % of the batch
     (so most of every batch is duplicates, within a rank and across ranks): the tables equal the dense model, the
     number of rows sent to owners is the number of distinct ids per rank, not the batch size."""
     from tips_b200.config import set_config
     from tips_b200.parallel import device
     from tips_b200.ps.gpu import ShardedEmbedding
-    set_config(symm_window_bytes=1 << 20, device_wait_budget_ms=2000, comm_blocks=8)
+    # wire "grad": the bf16 gradients of this test make every rank's per-row sum cross as bf16 (one rounding)
+    set_config(symm_window_bytes=1 << 20, device_wait_budget_ms=2000, comm_blocks=8, ps_wire_dtype=wire)
+
+    def close(a, b, atol=3e-4, rtol=1e-4):
+        if wire == "fp32":
+            return torch.allclose(a, b, atol=atol, rtol=rtol)
+        # bf16 on the wire: a row's gradient is exact to 2^-9 of each rank's partial sum, and where the partial sums
+        # of the ranks nearly cancel Adagrad turns that into a visible step (lr * g / |g| on a first update), so
+        # the comparison is statistical: nearly all elements agree closely and the mean error is small
+        d = (a - b).abs()
+        return float((d > 4e-3).float().mean()) < 0.02 and float(d.mean()) < 5e-4
+
     st = device.setup(emulate_ranks=ranks)
     try:
         dev = st.device
@@ -123,7 +135,7 @@ def test_push_with_mostly_duplicate_ids_emulated(ranks, indexed):
             outs = t.pull(ids, dtype=torch.float32, index=indexed)
             for r in range(ranks):
                 ref = torch.cat([ws[f][ids[r][:, f]] for f in range(fields)], dim=1)
-                assert torch.allclose(outs[r], ref, atol=3e-4, rtol=1e-4)
+                assert close(outs[r], ref)
             pulls = 1
             if indexed and step == 1:
                 t.pull(ids, dtype=torch.bfloat16, index=True)   # an index that nothing consumes is dropped
@@ -141,9 +153,10 @@ def test_push_with_mostly_duplicate_ids_emulated(ranks, indexed):
         assert total_distinct < 0.6 * 3 * ranks * batch * fields
         got, got_s = _dense_tables(t, fields, rows, dim)
         for f in range(fields):
-            assert torch.allclose(got[f], ws[f], atol=3e-4, rtol=1e-4)
-            assert torch.allclose(got_s[f], ss[f], atol=1e-3, rtol=1e-4)
+            assert close(got[f], ws[f])
+            assert close(got_s[f], ss[f], atol=1e-3) if wire == "fp32" else torch.allclose(got_s[f], ss[f], atol=0.5, rtol=5e-2)
     finally:
+        set_config(ps_wire_dtype="grad")
         device.teardown(st)
 
 

@@ -33,6 +33,10 @@ class Config:
                                              # wait) and raises if a bounded wait ran out; sync: waits for the
                                              # collective first, so the failing step itself raises; off
     collective_timeout_s: float = 0.0        # >0: DistributedOptimizer.synchronize() gives up on a bucket after this long
+    # Parameter server
+    ps_wire_dtype: str = "grad"              # grad: rows of a push cross NVLink in the dtype of the pushed gradients
+                                             # (a rank's per-row sum is rounded to bf16 once when they are bf16);
+                                             # fp32: always fp32
     # Observability
     log_level: str = "WARNING"
     timeline_path: str = ""

@@ -520,8 +520,9 @@ __device__ __forceinline__ uint32_t ReservePositions(int dest, int ndest, uint32
 
 // Walks the list of distinct rows of the batch: a row this rank owns stays in the table and joins the apply
 // list; every other row goes to its owner's inbox, its sums are zeroed and its key stays until the apply pass.
+// wire_bf16: the summed rows cross NVLink as bf16 (half the bytes); the inbox keeps its fp32 row pitch.
 __global__ void __launch_bounds__(kChunk)
-PsSendKernel(PsLaunch args, PsMeta meta, uint64_t slots, uint64_t cap) {
+PsSendKernel(PsLaunch args, PsMeta meta, uint64_t slots, uint64_t cap, int wire_bf16) {
   __shared__ uint32_t s_slot[kChunk];
   __shared__ char* s_ptr[kChunk];
   __shared__ uint32_t s_cnt[kMaxRanks + 1], s_base[kMaxRanks + 1];
@@ -574,7 +575,17 @@ PsSendKernel(PsLaunch args, PsMeta meta, uint64_t slots, uint64_t cap) {
           return *reinterpret_cast<const U4*>(sums_base + static_cast<uint64_t>(sl) * dim + v * 4);
         },
         [&](char* d, uint32_t sl, int v, const U4& q) {
-          if (d) StSys(d + v * 16, q);
+          if (d) {
+            if (wire_bf16) {
+              const __nv_bfloat162 lo = __floats2bfloat162_rn(__uint_as_float(q.x), __uint_as_float(q.y));
+              const __nv_bfloat162 hi = __floats2bfloat162_rn(__uint_as_float(q.z), __uint_as_float(q.w));
+              asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1,%2};" ::"l"(d + v * 8),
+                           "r"(*reinterpret_cast<const uint32_t*>(&lo)), "r"(*reinterpret_cast<const uint32_t*>(&hi))
+                           : "memory");
+            } else {
+              StSys(d + v * 16, q);
+            }
+          }
           *reinterpret_cast<float4*>(sums_base + static_cast<uint64_t>(sl) * dim + v * 4) = make_float4(0.f, 0.f, 0.f, 0.f);
         });
     __syncthreads();
@@ -604,7 +615,7 @@ PsSendKernel(PsLaunch args, PsMeta meta, uint64_t slots, uint64_t cap) {
 
 // The owner folds the rows that arrived in its inboxes into its local table and extends the apply list.
 __global__ void __launch_bounds__(kChunk)
-PsOwnerReduceKernel(PsLaunch args, PsMeta meta, uint64_t slots, uint64_t cap) {
+PsOwnerReduceKernel(PsLaunch args, PsMeta meta, uint64_t slots, uint64_t cap, int wire_bf16) {
   __shared__ uint32_t s_slot[kChunk];
   __shared__ char* s_ptr[kChunk];
   __shared__ uint32_t s_cnt[1], s_base[1];
@@ -663,7 +674,15 @@ PsOwnerReduceKernel(PsLaunch args, PsMeta meta, uint64_t slots, uint64_t cap) {
     s_ptr[threadIdx.x]  = row;
     __syncthreads();
     MoveRows(
-        s_slot, s_ptr, dim, [](char* p, uint32_t, int v) { return LdSysFree(p + v * 16); },
+        s_slot, s_ptr, dim,
+        [&](char* p, uint32_t, int v) {
+          if (!wire_bf16) return LdSysFree(p + v * 16);
+          uint32_t a, b;
+          asm("ld.relaxed.sys.global.v2.u32 {%0,%1}, [%2];" : "=r"(a), "=r"(b) : "l"(p + v * 8));
+          U4 q;  // bf16 -> fp32: the 16 bits become the high half of the word
+          q.x = a << 16; q.y = a & 0xffff0000u; q.z = b << 16; q.w = b & 0xffff0000u;
+          return q;
+        },
         [&](char*, uint32_t sl, int v, const U4& q) {
           RedAdd4(sums_base + static_cast<uint64_t>(sl) * dim + v * 4, __uint_as_float(q.x), __uint_as_float(q.y),
                   __uint_as_float(q.z), __uint_as_float(q.w));
@@ -849,6 +868,7 @@ struct PsState {
   uint64_t item_cap = 0;       // items (sample, field) that item_slot can hold
   int32_t* error_dev = nullptr;
   bool lead_fence = true;      // the next push must fence first (no fenced pull since the previous push)
+  bool wire_follows_grads = true;  // bf16 gradients: the rows cross NVLink as bf16
   int64_t index_items = -1;    // >= 0: the table holds the index of a pulled batch of that many items
   bool timing = false;
   cudaEvent_t ev[6] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
@@ -1096,6 +1116,14 @@ int tipsk_ps_traffic(uint64_t* out) {
   return 0;
 }
 
+/* follow non-zero (the default): when the pushed gradients are bf16, each rank's per-row sum of its duplicates is
+ * rounded to bf16 once and crosses NVLink in half the bytes; zero: rows always travel as fp32.  The same value on
+ * every rank. */
+int tipsk_ps_wire_follows_grads(int follow) {
+  g_ps.wire_follows_grads = follow != 0;
+  return 0;
+}
+
 /* Per-phase device timing of the next synchronous pushes (eager launches only, not under stream capture):
  * events are recorded around scatter / send / fence / reduce / apply.  tipsk_ps_phase_ms synchronises and
  * returns the five durations of the last push in milliseconds (0 for phases that did not run). */
@@ -1239,13 +1267,14 @@ int tipsk_ps_push(const int64_t* const* ids, const void* const* grads, int64_t b
   Mark(s);
   if (nranks > 1) {
     dim3 lgrid(ListGrid(items), local);
-    PsSendKernel<<<lgrid, 256, 0, s>>>(l, st.meta, st.slots, st.inbox_cap);
+    const int wire_bf16 = st.wire_follows_grads && grad_dtype == kBF16 ? 1 : 0;
+    PsSendKernel<<<lgrid, 256, 0, s>>>(l, st.meta, st.slots, st.inbox_cap, wire_bf16);
     TIPSK_LAUNCH_CHECK();
     Mark(s);
     rc = tipsk_comm_fence(2, stream);  // every rank's rows and counts have landed
     if (rc) return rc;
     Mark(s);
-    PsOwnerReduceKernel<<<lgrid, 256, 0, s>>>(l, st.meta, st.slots, st.inbox_cap);
+    PsOwnerReduceKernel<<<lgrid, 256, 0, s>>>(l, st.meta, st.slots, st.inbox_cap, wire_bf16);
     TIPSK_LAUNCH_CHECK();
     Mark(s);
   }

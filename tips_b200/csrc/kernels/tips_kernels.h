@@ -161,6 +161,7 @@ int tipsk_ps_configure(void* const* host_slabs, void* const* host_inboxes, void*
                        const uint64_t* host_state_off, const int64_t* host_rows_per_shard, int nfields, int dim,
                        uint64_t slots, uint64_t inbox_cap, uint64_t item_cap);
 int tipsk_ps_traffic(uint64_t* host_out3);
+int tipsk_ps_wire_follows_grads(int follow);
 int tipsk_ps_phase_timing(int enable);
 int tipsk_ps_phase_ms(float* host_out5);
 int tipsk_ps_pull_phase_ms(float* host_out4);

@@ -55,7 +55,8 @@ class CtrTrainer:
     """
 
     def __init__(self, num_fields=26, rows_per_table=10_000_000, dim=64, dense_features=13, hidden=(512, 256),
-                 table_lr=0.05, mlp_lr=1e-3, device=None, expected_batch=8192, seed=0, graph=False, sync_ps=True):
+                 table_lr=0.05, mlp_lr=1e-3, device=None, expected_batch=8192, seed=0, graph=False, sync_ps=True,
+                 overlap_push=True):
         self.device = device or torch.device("cuda", torch.cuda.current_device())
         self.fields, self.dim, self.dense = num_fields, dim, dense_features
         self.emb_cols = num_fields * dim
@@ -64,6 +65,8 @@ class CtrTrainer:
         self.tables = ShardedEmbedding(num_fields, rows_per_table, dim, optimizer="adagrad", lr=table_lr,
                                        init_scale=0.05, seed=seed, expected_batch=expected_batch, device=self.device,
                                        sync=sync_ps)
+        # the push of the embedding gradients runs beside the allreduce and the update of the MLP
+        self.tables.push_stream = torch.cuda.Stream(device=self.device) if overlap_push else None
         torch.manual_seed(seed + 17)
         self.mlp = CtrMLP(self.in_features, hidden).to(self.device).to(torch.bfloat16)
         self.world = tips.size() if tips.is_initialized() else 1
@@ -116,6 +119,7 @@ class CtrTrainer:
         if self.graph:
             self._allreduce_inline()
         self.opt.step()
+        self.tables.join_push()
         return loss.detach()
 
     def train_step(self, ids, dense, labels):

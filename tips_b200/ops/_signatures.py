@@ -72,6 +72,7 @@ _PROTOS = {
     "tipsk_ps_ctl_bytes": (U, []),
     "tipsk_ps_configure": (I, [PP, PP, PP, PP, PP, PP, PP, I, I, POINTER(U), POINTER(U), POINTER(L), I, I, U, U, U]),
     "tipsk_ps_traffic": (I, [POINTER(U)]),
+    "tipsk_ps_wire_follows_grads": (I, [I]),
     "tipsk_ps_phase_timing": (I, [I]),
     "tipsk_ps_phase_ms": (I, [POINTER(F)]),
     "tipsk_ps_pull_phase_ms": (I, [POINTER(F)]),

@@ -61,6 +61,8 @@ class ShardedEmbedding:
         self.num_fields, self.rows, self.dim = num_fields, rows_per_table, dim
         self.rule, self.lr, self.eps = _RULES[optimizer], lr, eps
         self.sync = bool(sync)
+        self.push_stream = None    # set by a trainer: embedding_lookup's backward then pushes on that stream
+        self.push_inflight = None
         if not self.sync and self.rule not in (0, 1):
             raise ValueError("asynchronous pushes support the sgd and adagrad rules")
         self.rank, self.size, self.emulated, st = _world()
@@ -147,6 +149,8 @@ class ShardedEmbedding:
                                           base.u64_array(self.field_off), base.u64_array(self.state_off),
                                           base.i64_array([self.rows_per_shard] * self.num_fields), self.num_fields,
                                           self.dim, self.slots, self.inbox_cap, self.item_cap), "ps_configure")
+        from ..config import get_config
+        lib.tipsk_ps_wire_follows_grads(0 if get_config().ps_wire_dtype == "fp32" else 1)
         _active = self
 
     def _activate(self):
@@ -210,6 +214,12 @@ class ShardedEmbedding:
         else:
             base.check(base.K().tipsk_ps_push_async(*args, base.stream()), "ps_push")
         base.count_launches(1)
+
+    def join_push(self):
+        """Make the current stream wait for a push that embedding_lookup's backward put on `push_stream`."""
+        if self.push_stream is not None and self.push_inflight is not None:
+            torch.cuda.current_stream().wait_stream(self.push_stream)
+            self.push_inflight = None
 
     def check(self):
         """Raise if a push overflowed the accumulation table or an id was out of range. Synchronises."""
@@ -369,8 +379,18 @@ class _LookupFn(torch.autograd.Function):
     @staticmethod
     def backward(ctx, dout):
         g = dout if dout.stride(1) == 1 else dout.contiguous()
-        ctx.table.push(ctx.ids, g, grad_col0=ctx.col0, grad_scale=ctx.grad_scale,
-                       reuse_index=ctx.ids._version == ctx.ids_version)
+        table = ctx.table
+        reuse = ctx.ids._version == ctx.ids_version
+        side = getattr(table, "push_stream", None)
+        if side is None:
+            table.push(ctx.ids, g, grad_col0=ctx.col0, grad_scale=ctx.grad_scale, reuse_index=reuse)
+        else:
+            # the push runs beside what follows on this stream (gradient allreduce and update of the dense part);
+            # the owner of `push_stream` joins it before the next pull and keeps `g` alive until then
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                table.push(ctx.ids, g, grad_col0=ctx.col0, grad_scale=ctx.grad_scale, reuse_index=reuse)
+            table.push_inflight = g
         return None, None, None, None, None, None
 
 

@@ -179,6 +179,31 @@ def test_losses():
     assert torch.allclose(logits.grad.float(), lg.grad, atol=2e-3)
 
 
+@pytest.mark.parametrize("dtype,rows,k", [(torch.bfloat16, 8192, 256), (torch.bfloat16, 777, 520),
+                                          (torch.float32, 1000, 36)])
+def test_one_unit_output_layer_fused_with_bce(dtype, rows, k):
+    """linear1_sigmoid_bce_loss against torch in fp32: loss, dx, dw, db; the input is a column slice of a wider
+    matrix (a row pitch larger than k) and the upstream gradient is not 1."""
+    from tips_b200.ops.pointwise import linear1_sigmoid_bce_loss
+    torch.manual_seed(rows)
+    dev = _dev()
+    wide = torch.randn(rows, k + 8, device=dev).to(dtype)
+    x = wide[:, :k].detach().requires_grad_()
+    w = (torch.randn(1, k, device=dev) * 0.1).to(dtype).requires_grad_()
+    b = torch.randn(1, device=dev).to(dtype).requires_grad_()
+    t = (torch.rand(rows, device=dev) < 0.25).float()
+    loss = linear1_sigmoid_bce_loss(x, w, b, t)
+    (loss * 3.0).backward()
+    xr, wr, br = (v.detach().float().requires_grad_() for v in (x, w, b))
+    ref = torch.nn.functional.binary_cross_entropy_with_logits(torch.nn.functional.linear(xr, wr, br).view(-1), t)
+    (ref * 3.0).backward()
+    low = dtype != torch.float32
+    assert torch.allclose(loss, ref, atol=1e-4 if low else 1e-5, rtol=1e-4)
+    assert torch.allclose(x.grad.float(), xr.grad, atol=1e-6 if not low else 2e-6, rtol=1e-2 if low else 1e-4)
+    assert torch.allclose(w.grad.float(), wr.grad, atol=2e-3 if low else 1e-5, rtol=1e-2 if low else 1e-4)
+    assert torch.allclose(b.grad.float(), br.grad, atol=2e-3 if low else 1e-5, rtol=1e-2 if low else 1e-4)
+
+
 @pytest.mark.parametrize("n,c,h,w", [(2, 64, 16, 16), (3, 8, 7, 9), (1, 16, 1, 5), (4, 64, 112, 112)])
 def test_maxpool_3x3_s2(n, c, h, w):
     from tips_b200.ops.pool import max_pool_3x3_s2

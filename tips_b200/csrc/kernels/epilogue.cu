@@ -77,26 +77,38 @@ BiasActBwdKernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __r
 #pragma unroll
       for (int k = 0; k < N; ++k) bv[k] = 0.f;
     }
-    for (int64_t r = static_cast<int64_t>(blockIdx.y) * 8 + threadIdx.y; r < rows;
-         r += static_cast<int64_t>(gridDim.y) * 8) {
-      const int64_t off = r * cols + static_cast<int64_t>(vc) * N;
-      Vec16<T> d = LoadVec(dy + off), o;
-      if (act != 0) {
-        Vec16<T> q = LoadVec(x + off);
+    const int64_t step = static_cast<int64_t>(gridDim.y) * 8;
+    for (int64_t r = static_cast<int64_t>(blockIdx.y) * 8 + threadIdx.y; r < rows; r += 2 * step) {
+      // two rows in flight per thread
+      const int64_t off[2] = {r * cols + static_cast<int64_t>(vc) * N, (r + step) * cols + static_cast<int64_t>(vc) * N};
+      const bool have[2]   = {true, r + step < rows};
+      Vec16<T> d[2], q[2];
 #pragma unroll
-        for (int k = 0; k < N; ++k) {
-          const float g = ToFloat<T>(d.v[k]) * ActGrad(ToFloat<T>(q.v[k]) + bv[k], act);
-          acc[k] += g;
-          o.v[k] = FromFloat<T>(g);
+      for (int u = 0; u < 2; ++u)
+        if (have[u]) {
+          d[u] = LoadVec(dy + off[u]);
+          if (act != 0) q[u] = LoadVec(x + off[u]);
         }
-      } else {
 #pragma unroll
-        for (int k = 0; k < N; ++k) {
-          acc[k] += ToFloat<T>(d.v[k]);
-          o.v[k] = d.v[k];
+      for (int u = 0; u < 2; ++u) {
+        if (!have[u]) continue;
+        Vec16<T> o;
+        if (act != 0) {
+#pragma unroll
+          for (int k = 0; k < N; ++k) {
+            const float g = ToFloat<T>(d[u].v[k]) * ActGrad(ToFloat<T>(q[u].v[k]) + bv[k], act);
+            acc[k] += g;
+            o.v[k] = FromFloat<T>(g);
+          }
+        } else {
+#pragma unroll
+          for (int k = 0; k < N; ++k) {
+            acc[k] += ToFloat<T>(d[u].v[k]);
+            o.v[k] = d[u].v[k];
+          }
         }
+        if (dx) StoreVec(dx + off[u], o);
       }
-      if (dx) StoreVec(dx + off, o);
     }
   }
   if (!dbias) return;
@@ -134,6 +146,97 @@ SigmoidBceKernel(const T* __restrict__ z, const float* __restrict__ t, float* __
 #pragma unroll
     for (int o = 4; o > 0; o >>= 1) v += __shfl_xor_sync(0xffu, v, o);
     if (threadIdx.x == 0) atomicAdd(loss_sum, v);
+  }
+}
+
+// Output layer with one unit fused with its loss: z_i = x_i . w + b, loss = sum_i BCE(z_i, t_i), and
+// dz_i = (sigmoid(z_i) - t_i) * scale kept for the backward pass.  A GEMM with one output column wastes a
+// 128-wide tensor-core tile on it; this is a streaming dot product per row (one warp per row, 16-byte loads).
+template <typename T>
+__global__ void __launch_bounds__(256)
+DotSigmoidBceFwdKernel(const T* __restrict__ x, const T* __restrict__ w, const T* __restrict__ bias,
+                       const float* __restrict__ t, float* __restrict__ loss_sum, float* __restrict__ dz,
+                       float* __restrict__ logits, int64_t rows, int k, int64_t ldx, float scale) {
+  constexpr int N = 16 / sizeof(T);
+  __shared__ float warp_sums[8];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const float b  = bias ? ToFloat<T>(bias[0]) : 0.f;
+  float local    = 0.f;
+  for (int64_t r = static_cast<int64_t>(blockIdx.x) * 8 + warp; r < rows; r += static_cast<int64_t>(gridDim.x) * 8) {
+    const T* row = x + r * ldx;
+    float acc    = 0.f;
+    for (int c = lane * N; c < k; c += 32 * N) {
+      const Vec16<T> xv = LoadVec(row + c), wv = LoadVec(w + c);
+#pragma unroll
+      for (int j = 0; j < N; ++j) acc += ToFloat<T>(xv.v[j]) * ToFloat<T>(wv.v[j]);
+    }
+    acc = WarpSum(acc);
+    if (lane == 0) {
+      const float z = acc + b, ti = t[r];
+      local += fmaxf(z, 0.f) - z * ti + log1pf(__expf(-fabsf(z)));
+      dz[r] = (1.f / (1.f + __expf(-z)) - ti) * scale;
+      if (logits) logits[r] = z;
+    }
+  }
+  if (lane == 0) warp_sums[warp] = local;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float v = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v += warp_sums[j];
+    atomicAdd(loss_sum, v * scale);
+  }
+}
+
+// Backward of the same layer: g_i = dz_i * dloss; dx_i = g_i * w; dw = sum_i g_i * x_i; db = sum_i g_i.
+// A block owns a run of rows and 32 * N columns per pass; its warps keep the dw partial sums of their rows in
+// registers, the block adds them up in shared memory and issues one atomic per column.
+template <typename T>
+__global__ void __launch_bounds__(256)
+DotSigmoidBceBwdKernel(const T* __restrict__ x, const T* __restrict__ w, const float* __restrict__ dz,
+                       const float* __restrict__ dloss, T* __restrict__ dx, float* __restrict__ dw,
+                       float* __restrict__ db, int64_t rows, int k, int64_t ldx, int64_t rows_per_block) {
+  constexpr int N = 16 / sizeof(T);
+  __shared__ float red[8][32 * N + 1];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const float up = dloss ? *dloss : 1.f;
+  const int64_t r0 = static_cast<int64_t>(blockIdx.x) * rows_per_block;
+  const int64_t r1 = r0 + rows_per_block < rows ? r0 + rows_per_block : rows;
+  for (int c0 = 0; c0 < k; c0 += 32 * N) {
+    const int c       = c0 + lane * N;
+    const bool active = c < k;
+    Vec16<T> wv;
+    if (active) wv = LoadVec(w + c);
+    float acc[N];
+#pragma unroll
+    for (int j = 0; j < N; ++j) acc[j] = 0.f;
+    float gsum = 0.f;
+    for (int64_t r = r0 + warp; r < r1; r += 8) {
+      const float g = dz[r] * up;
+      gsum += g;
+      if (active) {
+        const Vec16<T> xv = LoadVec(x + r * ldx + c);
+        Vec16<T> o;
+#pragma unroll
+        for (int j = 0; j < N; ++j) {
+          acc[j] += g * ToFloat<T>(xv.v[j]);
+          o.v[j] = FromFloat<T>(g * ToFloat<T>(wv.v[j]));
+        }
+        StoreVec(dx + r * k + c, o);
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < N; ++j) red[warp][lane * N + j] = acc[j];
+    __syncthreads();
+    for (int col = threadIdx.x; col < 32 * N; col += blockDim.x) {
+      if (c0 + col >= k) continue;
+      float v = 0.f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v += red[j][col];
+      atomicAdd(dw + c0 + col, v);
+    }
+    if (c0 == 0 && db && lane == 0) atomicAdd(db, gsum);
+    __syncthreads();
   }
 }
 
@@ -222,7 +325,7 @@ int tipsk_bias_act_bwd(const void* dy, const void* x, const void* bias, void* dx
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (dbias) TIPSK_CUDA(cudaMemsetAsync(dbias, 0, sizeof(float) * cols, s));
   const int col_tiles = CeilDiv(cols / n, 32);
-  int parts = CeilDiv(NumSMs() * 4, col_tiles);
+  int parts = CeilDiv(NumSMs() * 2, col_tiles);  // every partition ends in one atomic per column
   int maxp  = CeilDiv(rows, 8 * 4);
   if (parts > maxp) parts = maxp;
   if (parts < 1) parts = 1;
@@ -244,6 +347,50 @@ int tipsk_sigmoid_bce(const void* logits, const float* targets, float* loss_sum,
   EPI_DISPATCH(dtype, {
     SigmoidBceKernel<T><<<grid, 256, 0, s>>>(static_cast<const T*>(logits), targets, loss_sum, static_cast<T*>(dlogits),
                                              n, grad_scale);
+  });
+  TIPSK_LAUNCH_CHECK();
+  return 0;
+}
+
+/* One-unit output layer fused with its loss.  x: [rows, k] with pitch ldx, w: [k], bias: [1] or null, targets:
+ * [rows] fp32.  loss_sum (fp32 scalar, zeroed here) receives scale * sum of the per-row binary cross-entropies,
+ * dz [rows] fp32 the gradient of that sum with respect to the logits, logits (optional, [rows] fp32) the logits. */
+int tipsk_dot_sigmoid_bce_fwd(const void* x, const void* w, const void* bias, const float* targets, float* loss_sum,
+                              float* dz, float* logits, int64_t rows, int k, int64_t ldx, float scale, int dtype,
+                              void* stream) {
+  if (rows <= 0) return 0;
+  const int n = 16 / (int)DTypeSize(dtype);
+  TIPSK_REQUIRE(k % n == 0 && ldx % n == 0, "dot_sigmoid_bce: k and the row pitch must be multiples of 16 bytes");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  TIPSK_CUDA(cudaMemsetAsync(loss_sum, 0, sizeof(float), s));
+  int grid = CeilDiv(rows, 8);
+  if (grid > NumSMs() * 8) grid = NumSMs() * 8;
+  EPI_DISPATCH(dtype, {
+    DotSigmoidBceFwdKernel<T><<<grid, 256, 0, s>>>(static_cast<const T*>(x), static_cast<const T*>(w),
+                                                   static_cast<const T*>(bias), targets, loss_sum, dz, logits, rows, k,
+                                                   ldx, scale);
+  });
+  TIPSK_LAUNCH_CHECK();
+  return 0;
+}
+
+/* dx: [rows, k] (contiguous) = dz * dloss * w; dw: [k] fp32 and db: [1] fp32 (may be null), both zeroed here;
+ * dloss: device scalar (null = 1). */
+int tipsk_dot_sigmoid_bce_bwd(const void* x, const void* w, const float* dz, const float* dloss, void* dx, float* dw,
+                              float* db, int64_t rows, int k, int64_t ldx, int dtype, void* stream) {
+  if (rows <= 0) return 0;
+  const int n = 16 / (int)DTypeSize(dtype);
+  TIPSK_REQUIRE(k % n == 0 && ldx % n == 0, "dot_sigmoid_bce: k and the row pitch must be multiples of 16 bytes");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  TIPSK_CUDA(cudaMemsetAsync(dw, 0, sizeof(float) * k, s));
+  if (db) TIPSK_CUDA(cudaMemsetAsync(db, 0, sizeof(float), s));
+  int blocks = NumSMs() * 2;
+  int64_t rpb = (rows + blocks - 1) / blocks;
+  rpb         = (rpb + 7) / 8 * 8;
+  blocks      = CeilDiv(rows, rpb);
+  EPI_DISPATCH(dtype, {
+    DotSigmoidBceBwdKernel<T><<<blocks, 256, 0, s>>>(static_cast<const T*>(x), static_cast<const T*>(w), dz, dloss,
+                                                     static_cast<T*>(dx), dw, db, rows, k, ldx, rpb);
   });
   TIPSK_LAUNCH_CHECK();
   return 0;

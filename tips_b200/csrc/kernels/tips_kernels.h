@@ -96,6 +96,12 @@ int tipsk_bias_act_fwd(const void* x, const void* bias, void* y, int64_t rows, i
 int tipsk_bias_act_bwd(const void* dy, const void* x, const void* bias, void* dx, float* dbias, int64_t rows, int cols,
                        int act, int dtype, void* stream);
 /* Binary cross entropy with logits: loss_sum (fp32 scalar, accumulated) and dlogits = (sigmoid(z) - t) * scale. */
+/* One-unit output layer fused with the sigmoid cross-entropy loss (forward keeps dz for the backward pass). */
+int tipsk_dot_sigmoid_bce_fwd(const void* x, const void* w, const void* bias, const float* targets, float* loss_sum,
+                              float* dz, float* logits, int64_t rows, int k, int64_t ldx, float scale, int dtype,
+                              void* stream);
+int tipsk_dot_sigmoid_bce_bwd(const void* x, const void* w, const float* dz, const float* dloss, void* dx, float* dw,
+                              float* db, int64_t rows, int k, int64_t ldx, int dtype, void* stream);
 int tipsk_sigmoid_bce(const void* logits, const float* targets, float* loss_sum, void* dlogits, int64_t n,
                       float grad_scale, int dtype, void* stream);
 /* Softmax cross entropy over [rows, cols] with int64 labels (ignore_index skipped):

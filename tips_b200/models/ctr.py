@@ -15,7 +15,7 @@ import torch.nn as nn
 import tips_b200 as tips
 from ..ops.linear import Linear
 from ..ops.optim import FusedAdam
-from ..ops.pointwise import sigmoid_bce_loss
+from ..ops.pointwise import linear1_sigmoid_bce_loss, sigmoid_bce_loss
 from ..ps.gpu import ShardedEmbedding, embedding_lookup
 
 
@@ -38,10 +38,17 @@ class CtrMLP(nn.Module):
         self.layers = nn.ModuleList([Linear(dims[i], dims[i + 1], act="relu") for i in range(len(hidden))])
         self.out = Linear(dims[-1], 1)
 
-    def forward(self, x):
+    def hidden(self, x):
         for layer in self.layers:
             x = layer(x)
-        return self.out(x)
+        return x
+
+    def forward(self, x):
+        return self.out(self.hidden(x))
+
+    def loss(self, x, labels):
+        """Mean binary cross-entropy; the one-unit output layer and the loss run as one streaming op."""
+        return linear1_sigmoid_bce_loss(self.hidden(x), self.out.weight, self.out.bias, labels)
 
 
 class CtrTrainer:
@@ -95,11 +102,14 @@ class CtrTrainer:
             self._x = torch.zeros(batch, self.in_features, dtype=torch.bfloat16, device=self.device)
         return self._x
 
-    def forward(self, ids, dense):
+    def _features(self, ids, dense):
         x = self._input_buffer(ids.shape[0]).detach()
         x[:, self.emb_cols:self.emb_cols + self.dense] = dense
-        x = embedding_lookup(self.tables, ids, x, col0=0, grad_scale=1.0 / self.world)
-        return self.mlp(x).view(-1)
+        return embedding_lookup(self.tables, ids, x, col0=0, grad_scale=1.0 / self.world)
+
+    def forward(self, ids, dense):
+        """Click logits [B]."""
+        return self.mlp(self._features(ids, dense)).view(-1)
 
     def _allreduce_inline(self):
         """Graph mode: pack every bucket and average it over the ranks in place, on the current stream."""
@@ -114,7 +124,7 @@ class CtrTrainer:
             fs.grads_packed = True
 
     def _step_impl(self, ids, dense, labels):
-        loss = sigmoid_bce_loss(self.forward(ids, dense), labels)
+        loss = self.mlp.loss(self._features(ids, dense), labels)
         loss.backward()
         if self.graph:
             self._allreduce_inline()

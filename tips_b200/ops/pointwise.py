@@ -81,6 +81,56 @@ def sigmoid_bce_loss(logits, targets, reduction="mean"):
     return F.binary_cross_entropy_with_logits(logits.float(), targets.float(), reduction=reduction)
 
 
+class _DotSigmoidBceFn(torch.autograd.Function):
+    """loss = reduction(BCE(x @ w + b, targets)) for a layer with ONE output unit, in two streaming kernels
+    (forward keeps d loss / d logit; backward produces dx, dw, db in one pass over x)."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias, targets, scale):
+        x2 = x if x.stride(-1) == 1 else x.contiguous()
+        rows, k = x2.shape
+        w = weight.reshape(-1).contiguous()
+        t = targets.to(torch.float32).contiguous()
+        loss = torch.empty((), dtype=torch.float32, device=x.device)
+        dz = torch.empty(rows, dtype=torch.float32, device=x.device)
+        base.check(base.K().tipsk_dot_sigmoid_bce_fwd(x2.data_ptr(), w.data_ptr(), base.ptr(bias), t.data_ptr(),
+                                                      loss.data_ptr(), dz.data_ptr(), None, rows, k, x2.stride(0),
+                                                      scale, base.code(x2), base.stream()), "dot_sigmoid_bce_fwd")
+        ctx.save_for_backward(x2, w, dz)
+        ctx.meta = (weight.shape, weight.dtype, None if bias is None else bias.dtype)
+        return loss
+
+    @staticmethod
+    def backward(ctx, dloss):
+        x2, w, dz = ctx.saved_tensors
+        wshape, wdtype, bdtype = ctx.meta
+        rows, k = x2.shape
+        dx = torch.empty(rows, k, dtype=x2.dtype, device=x2.device)
+        dw = torch.empty(k, dtype=torch.float32, device=x2.device)
+        db = torch.empty(1, dtype=torch.float32, device=x2.device) if bdtype is not None else None
+        up = dloss.to(torch.float32).contiguous()
+        base.check(base.K().tipsk_dot_sigmoid_bce_bwd(x2.data_ptr(), w.data_ptr(), dz.data_ptr(), up.data_ptr(),
+                                                      dx.data_ptr(), dw.data_ptr(), base.ptr(db), rows, k,
+                                                      x2.stride(0), base.code(x2), base.stream()),
+                   "dot_sigmoid_bce_bwd")
+        return dx, dw.view(wshape).to(wdtype), (None if db is None else db.to(bdtype)), None, None
+
+
+def linear1_sigmoid_bce_loss(x, weight, bias, targets, reduction="mean"):
+    """Binary cross-entropy of ``sigmoid(x @ weight.T + bias)`` for a ``[1, K]`` weight: the one-unit output layer
+    of a click model and its loss as one op.  Same value and gradients as
+    ``sigmoid_bce_loss(linear(x, weight, bias).view(-1), targets)``."""
+    assert weight.shape[0] == 1 and x.dim() == 2
+    scale = 1.0 / x.shape[0] if reduction == "mean" else 1.0
+    es = x.element_size()
+    if (x.is_cuda and x.dtype == weight.dtype and x.dtype in (torch.bfloat16, torch.float16, torch.float32)
+            and (x.shape[1] * es) % 16 == 0 and (x.stride(0) * es) % 16 == 0 and x.data_ptr() % 16 == 0
+            and (bias is None or bias.dtype == x.dtype)):
+        return _DotSigmoidBceFn.apply(x, weight, bias, targets, scale)
+    z = F.linear(x.float(), weight.float(), None if bias is None else bias.float()).view(-1)
+    return F.binary_cross_entropy_with_logits(z, targets.float(), reduction=reduction)
+
+
 class _SoftmaxXentFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, logits, labels, ignore_index):

@@ -71,7 +71,10 @@ def test_noalloc_matches_regular_entry_point_twice():
 
 def test_noalloc_rejects_oversized_problem():
     """A shape whose partial sums do not fit the built-in array is refused before anything is launched.
-    The buffers are real and correctly sized, so even a library that failed to refuse would stay in bounds."""
+    The size check on the host is the only guard: x and y below have the right size, but the scratch is the fixed
+    786432-float array and this shape needs 1204224 floats, so kernels launched for it would write past the
+    array.  tests/test_no_alloc_limit_cpu.py checks on a machine without a GPU that the refusal comes before any
+    CUDA call."""
     lib = _load()
     dev = torch.device("cuda", 0)
     c, m = 200704, 256     # 784 column tiles -> 2 partial rows + 1 -> 1204224 scratch floats > 786432

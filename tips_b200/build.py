@@ -127,16 +127,19 @@ def build_all(force=False):
     return build_core(force=force), build_kernels(force=force)
 
 
-def build_native_tests():
-    """Compile csrc/tests/*.cc into executables under build/ (linked against libtips_core.so)."""
-    core = build_core()
+def build_native_tests(sanitize=None):
+    """Compile csrc/tests/*.cc into executables under build/, linked against libtips_core.so or, with
+    `sanitize` ("thread" / "address"), against that sanitizer build of the library (executables get the suffix)."""
+    core = build_core(sanitize=sanitize)
     OBJ.mkdir(exist_ok=True)
     outs = []
+    libname = "tips_core" + (f"_{sanitize}" if sanitize else "")
+    extra = [f"-fsanitize={sanitize}", "-fno-omit-frame-pointer"] if sanitize else []
     for src in sorted((CSRC / "tests").glob("*.cc")):
-        exe = OBJ / src.stem
+        exe = OBJ / (src.stem + (f"_{sanitize}" if sanitize else ""))
         if (not exe.exists() or exe.stat().st_mtime < max(src.stat().st_mtime, core.stat().st_mtime)):
-            cmd = [CXX, "-std=c++17", "-O1", "-g1", "-pthread", f"-I{CSRC}", str(src), f"-L{LIB}", "-ltips_core",
-                   f"-Wl,-rpath,{LIB}", "-o", str(exe)]
+            cmd = [CXX, "-std=c++17", "-O1", "-g1", "-pthread", *extra, f"-I{CSRC}", str(src), f"-L{LIB}",
+                   f"-l{libname}", f"-Wl,-rpath,{LIB}", "-o", str(exe)]
             r = subprocess.run(cmd, capture_output=True, text=True)
             if r.returncode != 0:
                 raise RuntimeError(f"compile failed: {' '.join(cmd)}\n{r.stderr}")

@@ -6,6 +6,7 @@
 #include "tips_c_api.h"
 
 #include <cstring>
+#include <chrono>
 #include <sstream>
 
 #include "collective/coordinator.h"
@@ -356,6 +357,65 @@ int tips_counters(uint64_t* out, int n) {
 int tips_set_log_level(int min_level, int verbose) {
   LogConfig::MinLevel()     = min_level;
   LogConfig::VerboseLevel() = verbose;
+  return 0;
+}
+
+/* Cost of the control-plane messages, the counterpart of the reference's serializer timing test
+ * (tips/core/message/flatbuffers_test.cc:12-66, 1000 x build / read of a message): `iters` round trips of a
+ * request (name of 24 characters, 4 dimensions) and of a response (8 fused tensor names) through the wire format.
+ * out = {request encode, request decode, response encode, response decode} in nanoseconds per message. */
+int tips_bench_messages(int iters, double* out4) {
+  using namespace tips::collective;
+  if (iters < 1) iters = 1;
+  RequestMessage req;
+  req.request_rank = 3;
+  req.tensor_name  = "tips.opt0.bucket.17.grad";
+  req.tensor_shape = {256, 3, 224, 224};
+  ResponseMessage resp;
+  resp.response_type = ResponseType::kAllreduce;
+  for (int i = 0; i < 8; ++i) resp.tensor_names.push_back("tips.opt0.bucket." + std::to_string(i));
+  resp.tensor_sizes = {1, 2, 3, 4, 5, 6, 7, 8};
+  auto now = [] { return std::chrono::steady_clock::now(); };
+  auto ns  = [&](std::chrono::steady_clock::time_point a) {
+    return std::chrono::duration<double, std::nano>(now() - a).count() / iters;
+  };
+  volatile int64_t sink = 0;
+  NaiveBuffer rbuf, pbuf;
+  auto t = now();
+  for (int i = 0; i < iters; ++i) {
+    NaiveBuffer b;
+    req.request_rank = i;
+    req.Serialize(&b);
+    sink += static_cast<int64_t>(b.size());
+    if (i == 0) rbuf = b;
+  }
+  out4[0] = ns(t);
+  t       = now();
+  for (int i = 0; i < iters; ++i) {
+    NaiveBuffer b(rbuf.data(), rbuf.size());
+    RequestMessage m;
+    m.Deserialize(&b);
+    sink += m.NumElements();
+  }
+  out4[1] = ns(t);
+  t       = now();
+  for (int i = 0; i < iters; ++i) {
+    NaiveBuffer b;
+    resp.root_rank = i;
+    resp.Serialize(&b);
+    sink += static_cast<int64_t>(b.size());
+    if (i == 0) pbuf = b;
+  }
+  out4[2] = ns(t);
+  t       = now();
+  for (int i = 0; i < iters; ++i) {
+    NaiveBuffer b(pbuf.data(), pbuf.size());
+    ResponseMessage m;
+    m.Deserialize(&b);
+    sink += static_cast<int64_t>(m.tensor_names.size());
+  }
+  out4[3] = ns(t);
+  (void)sink;
   return 0;
 }
 

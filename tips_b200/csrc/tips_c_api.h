@@ -112,6 +112,9 @@ int tips_counters(uint64_t* out, int n);
 const char* tips_counter_names(void);
 int tips_set_log_level(int min_level, int verbose);
 
+/* Nanoseconds per message for request encode / decode and response encode / decode (see c_api.cc). */
+int tips_bench_messages(int iters, double* out4);
+
 /* ---- fault injection (tests) ------------------------------------------- */
 int tips_inject_drop_requests(int dst_rank, int n);
 

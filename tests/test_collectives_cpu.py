@@ -139,3 +139,39 @@ def _groups(rank, size):
 
 def test_rank_subgroups():
     run_ranks(_groups, 4)
+
+
+def _grouped_broadcast(rank, size):
+    """A state dict of 40 tensors of three dtypes travels as ONE negotiated collective, in place, from a root other
+    than 0; so does a stock optimizer's state."""
+    import tips_b200 as tips
+    torch.manual_seed(rank)
+    sd = {}
+    for i in range(12):
+        sd[f"w{i}"] = torch.randn(7 + i, 3)
+        sd[f"b{i}"] = torch.randn(5 + i).to(torch.bfloat16)
+        sd[f"n{i}"] = torch.full((1,), rank * 100 + i, dtype=torch.int64)
+    sd["odd"] = torch.randn(6, 4).t()            # not contiguous
+    want = tips.allgather_object({k: v.clone() for k, v in sd.items()})[size - 1]
+    before = tips.metrics()["ops_enqueued"]
+    tips.broadcast_parameters(sd, root_rank=size - 1)
+    assert tips.metrics()["ops_enqueued"] - before == 1
+    for k, v in sd.items():
+        assert torch.equal(v, want[k]), k
+    model = torch.nn.Linear(6, 3)
+    opt = torch.optim.Adam(model.parameters(), lr=0.1 * (rank + 1))
+    model(torch.ones(2, 6) * (rank + 1)).sum().backward()
+    opt.step()
+    tips.broadcast_optimizer_state(opt, root_rank=0)
+    st = tips.allgather_object({k: {n: (v.clone() if isinstance(v, torch.Tensor) else v) for n, v in s.items()}
+                                for k, s in opt.state_dict()["state"].items()})
+    for other in st[1:]:
+        for k in st[0]:
+            for n in st[0][k]:
+                a, b = st[0][k][n], other[k][n]
+                assert torch.equal(a, b) if isinstance(a, torch.Tensor) else a == b
+    assert opt.param_groups[0]["lr"] == 0.1
+
+
+def test_parameters_are_broadcast_as_one_collective():
+    run_ranks(_grouped_broadcast, 3)

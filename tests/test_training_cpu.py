@@ -139,6 +139,17 @@ def _elastic_and_resume(rank, size, tmp):
         model.weight.add_(rank + 1.0)                        # diverge, then resume from the file
     extra = resume(path, model, opt)
     assert extra["epoch"] == 5 and torch.allclose(model.weight.detach(), ref)
+    # restart: a fresh, unwrapped optimizer comes back wrapped, with the saved state, on every rank
+    model2 = torch.nn.Linear(8, 4)
+    opt2, extra2 = tips.load_model(path, model2, FusedAdam(model2.parameters(), lr=0.5))
+    assert type(opt2).__name__ == "FusedAdam" and hasattr(opt2, "synchronize") and extra2["epoch"] == 5
+    assert torch.allclose(model2.weight.detach(), ref) and opt2.param_groups[0]["lr"] == 0.01
+    model2(torch.ones(2, 8) * (rank + 1)).sum().backward()
+    opt2.step()
+    w2 = tips.allgather_object(model2.weight.detach().clone())
+    assert all(torch.equal(w, w2[0]) for w in w2)
+    with pytest.raises(TypeError):          # another optimizer class than the one that wrote the file: every rank
+        tips.load_model(path, model2, torch.optim.SGD(model2.parameters(), lr=0.1))
     commits = elastic.CommitStateCallback(state, batches_per_commit=2)
     n0 = state.commits
     for b in range(4):

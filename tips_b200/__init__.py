@@ -7,7 +7,7 @@ place of TensorFlow ones.
 """
 from .config import Config, get_config, set_config
 from .runtime import (TipsError, barrier, init, initialized, is_initialized, local_rank, local_size, metrics, rank,
-                      shutdown, size)
+                      reset_collectives, shutdown, size)
 from .parallel.collectives import (Average, Max, Min, Product, Sum, allgather, allgather_async, allreduce,
                                    allreduce_, allreduce_async, allreduce_async_, broadcast, broadcast_,
                                    broadcast_async, broadcast_async_, grouped_allreduce, poll, sparse_allreduce,
@@ -22,4 +22,4 @@ from .parallel.functions import (allgather_object, broadcast_object, broadcast_o
 
 __version__ = "0.1.0"
 from . import callbacks, elastic
-from .utils.checkpoint import load_checkpoint, resume, save_checkpoint
+from .utils.checkpoint import load_checkpoint, load_model, resume, save_checkpoint

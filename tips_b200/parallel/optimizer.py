@@ -28,6 +28,7 @@ from ..runtime import TipsError, _require_init
 from . import collectives as C
 from .buckets import build_buckets
 from .compression import Compression
+from ..utils.trace import nvtx_range
 
 
 _optimizer_counter = 0
@@ -162,7 +163,8 @@ class _DistributedMixin:
             for p in b.params:
                 if id(p) in saved:
                     p.grad = None
-        b.pack(scale=pre)
+        with nvtx_range(f"tips.pack {b.name}"):
+            b.pack(scale=pre)
         if saved:
             for p in b.params:
                 if id(p) in saved:
@@ -183,8 +185,9 @@ class _DistributedMixin:
         h.kind = "allreduce"
         h.output = b.grad
         h.keep = [b.grad]
-        b.handle = C._enqueue(h, 0, b.name, b.grad, b.grad, (b.numel,), b.grad.dtype, reduce_op=0, prescale=1.0,
-                              postscale=post)
+        with nvtx_range(f"tips.enqueue {b.name}"):
+            b.handle = C._enqueue(h, 0, b.name, b.grad, b.grad, (b.numel,), b.grad.dtype, reduce_op=0, prescale=1.0,
+                                  postscale=post)
 
     # ------------------------------------------------------------- public API
     def synchronize(self):
@@ -198,7 +201,8 @@ class _DistributedMixin:
         timeout = get_config().collective_timeout_s
         for b in self._tips_buckets:
             if b.handle is not None:
-                C.synchronize(b.handle, timeout if timeout > 0 else None)
+                with nvtx_range(f"tips.wait {b.name}"):
+                    C.synchronize(b.handle, timeout if timeout > 0 else None)
                 b.handle = None
         # a kernel that gave up on a peer skipped its reduction (and, with the update inside the allreduce, its
         # update): stop here, before the optimizer applies gradients that were never combined

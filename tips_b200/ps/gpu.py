@@ -25,6 +25,7 @@ import torch
 
 from .. import _lib
 from ..ops import base
+from ..utils.trace import nvtx_range
 
 _RULES = {"sgd": 0, "adagrad": 1, "literal_reference": 2}
 _active = None
@@ -193,9 +194,10 @@ class ShardedEmbedding:
             mk = lambda: torch.empty(b, self.num_fields * self.dim, dtype=dtype, device=self.device)
             out = [mk() for _ in range(self.size)] if self.emulated else mk()
         out_arr, out0 = self._per_rank(out)
-        base.check(base.K().tipsk_ps_pull(ids_arr, out_arr, b, out0.stride(0), out_col0, base.code(out0),
-                                          int(fence and self.sync), int(index and self.sync), base.stream()),
-                   "ps_pull")
+        with nvtx_range("tips.ps.pull"):
+            base.check(base.K().tipsk_ps_pull(ids_arr, out_arr, b, out0.stride(0), out_col0, base.code(out0),
+                                              int(fence and self.sync), int(index and self.sync), base.stream()),
+                       "ps_pull")
         self._indexed = bool(index and self.sync)
         return out
 
@@ -207,12 +209,13 @@ class ShardedEmbedding:
         g_arr, g0 = self._per_rank(grads)
         args = (ids_arr, g_arr, ids0.shape[0], g0.stride(0), grad_col0, base.code(g0), float(grad_scale), self.rule,
                 float(self.lr if lr is None else lr), float(self.eps))
-        if self.sync:
-            reuse = bool(reuse_index and getattr(self, "_indexed", False))
-            base.check(base.K().tipsk_ps_push(*args, int(reuse), base.stream()), "ps_push")
-            self._indexed = False
-        else:
-            base.check(base.K().tipsk_ps_push_async(*args, base.stream()), "ps_push")
+        with nvtx_range("tips.ps.push"):
+            if self.sync:
+                reuse = bool(reuse_index and getattr(self, "_indexed", False))
+                base.check(base.K().tipsk_ps_push(*args, int(reuse), base.stream()), "ps_push")
+                self._indexed = False
+            else:
+                base.check(base.K().tipsk_ps_push_async(*args, base.stream()), "ps_push")
         base.count_launches(1)
 
     def join_push(self):

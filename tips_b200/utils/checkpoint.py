@@ -83,3 +83,29 @@ def resume(path: str, model: torch.nn.Module, optimizer=None, root_rank: int = 0
             F.broadcast_optimizer_state(optimizer, root_rank)
         extra = F.broadcast_object(extra, root_rank, name="tips.resume.extra")
     return extra or {}
+
+
+def load_model(path: str, model: torch.nn.Module, optimizer=None, root_rank: int = 0, **distributed_kwargs):
+    """Resume a training job from a checkpoint and hand back an optimizer that is ready for distributed training.
+
+    The reference's ``load_model`` loads a saved Keras model and re-wraps whatever stock optimizer class the file
+    names in its DistributedOptimizer, so the caller never wraps by hand after a restart
+    (tips/_keras/__init__.py:215-231).  Here the optimizer object is built by the caller (a torch checkpoint holds
+    state, not objects); it may be a plain or fused torch optimizer or one that is wrapped already.  If it is not
+    wrapped yet and the runtime is initialised it is wrapped with ``DistributedOptimizer(**distributed_kwargs)``
+    first; then the checkpoint is loaded on `root_rank` and broadcast (``resume``).  The optimizer class recorded in
+    the file must match.  Returns ``(optimizer, extra)``."""
+    from ..parallel.optimizer import DistributedOptimizer, _DistributedMixin
+    if optimizer is not None:
+        # every rank learns the class the file names, so that a mismatch raises everywhere and not only on the root
+        saved = None
+        if not runtime.is_initialized() or runtime.rank() == root_rank:
+            saved = torch.load(path, map_location="cpu", weights_only=False).get("optimizer_class")
+        if runtime.is_initialized() and runtime.size() > 1:
+            saved = F.broadcast_object(saved, root_rank, name="tips.load_model.class")
+        if saved is not None and saved != type(optimizer).__name__:
+            raise TypeError(f"the checkpoint was written with a {saved} optimizer, got {type(optimizer).__name__}")
+        if runtime.is_initialized() and not isinstance(optimizer, _DistributedMixin):
+            optimizer = DistributedOptimizer(optimizer, **distributed_kwargs)
+    extra = resume(path, model, optimizer, root_rank)
+    return optimizer, extra

@@ -39,6 +39,12 @@ def test_parameter_server_two_gpus():
     assert r.returncode == 0 and "MULTI_GPU_PS_OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
 
 
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs at least 2 GPUs")
+def test_dense_parameter_server_table():
+    r = _run("dense_worker.py", min(torch.cuda.device_count(), 4))
+    assert r.returncode == 0 and "MULTI_GPU_DENSE_OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
+
+
 @pytest.mark.skipif(torch.cuda.device_count() < 4, reason="needs at least 4 GPUs")
 def test_collectives_and_ps_all_gpus():
     n = torch.cuda.device_count()

@@ -261,3 +261,91 @@ def test_async_push_emulated_ranks(rule):
             assert torch.allclose(outs[r], torch.cat([got[f][ids[r][:, f]] for f in range(fields)], dim=1))
     finally:
         device.teardown(st)
+
+
+@pytest.mark.parametrize("rule,dtype", [("sgd", torch.float32), ("sgd", torch.bfloat16), ("adam", torch.bfloat16)])
+def test_dense_table_single_rank(rule, dtype):
+    """ShardedDense on one rank against torch's optimizer on an fp32 copy: assign, three pushes, pull, state
+    round trip."""
+    from tips_b200.ps.gpu import ShardedDense
+    dev = torch.device("cuda", 0)
+    torch.manual_seed(4)
+    n = 10_000
+    kw = dict(lr=0.05, momentum=0.9) if rule == "sgd" else dict(lr=0.01, weight_decay=0.0)
+    t = ShardedDense(n, dtype=dtype, optimizer=rule, device=dev, **kw)
+    init = torch.randn(n, device=dev)
+    t.assign(init)
+    ref = init.clone().to(dtype).float().requires_grad_()
+    ropt = torch.optim.SGD([ref], **kw) if rule == "sgd" else torch.optim.Adam([ref], **kw)
+    for step in range(3):
+        g = torch.randn(n, device=dev).to(dtype)
+        t.push(g)
+        ref.grad = g.float()
+        ropt.step()
+    tol = 1e-5 if dtype == torch.float32 else 2e-2
+    assert torch.allclose(t.pull().float(), ref.detach(), atol=tol, rtol=tol)
+    assert t.pull(10, 20).shape == (10,)
+    saved = t.state()
+    t2 = ShardedDense(n, dtype=dtype, optimizer=rule, device=dev, **kw)
+    t2.load_state(saved)
+    g = torch.randn(n, device=dev).to(dtype)
+    t.push(g)
+    t2.push(g)
+    assert torch.equal(t.pull(), t2.pull())
+
+
+@pytest.mark.parametrize("ranks,rule", [(1, "sgd"), (4, "sgd"), (4, "adagrad")])
+def test_hashed_table_creates_rows_on_first_pull(ranks, rule):
+    """Arbitrary 64-bit keys (negative, huge, duplicates): unknown keys pull zeros and exist afterwards, a push to
+    a key that was never pulled is counted as missing, updates match a dictionary model; 1 rank and 4 emulated."""
+    from tips_b200.config import set_config
+    from tips_b200.parallel import device
+    from tips_b200.ps.gpu import HashedEmbedding
+    st = None
+    if ranks > 1:
+        set_config(symm_window_bytes=1 << 20, device_wait_budget_ms=2000, comm_blocks=8)
+        st = device.setup(emulate_ranks=ranks)
+    try:
+        dev = st.device if st else torch.device("cuda", 0)
+        dim, lr = 16, 0.1
+        t = HashedEmbedding(dim, capacity_per_rank=4096, optimizer=rule, lr=lr, device=dev)
+        g = torch.Generator().manual_seed(3)
+        pool = torch.randint(-2**62, 2**62, (600,), generator=g)
+        pool[:3] = torch.tensor([0, -5, 2**62 + 12345])
+        wrap = (lambda x: [x.to(dev)] * 1 if False else x.to(dev))
+        per_rank = [pool[torch.randint(0, 600, (512,), generator=g)] for _ in range(max(ranks, 1))]
+        arg = [k.to(dev) for k in per_rank] if ranks > 1 else per_rank[0].to(dev)
+        first = t.pull(arg)
+        for o in (first if ranks > 1 else [first]):
+            assert float(o.abs().sum()) == 0.0                      # created as zeros
+        seen = set(int(v) for k in per_rank for v in k)
+        total = sum(t.local_size(r) for r in range(ranks)) if ranks > 1 else t.local_size()
+        assert total == len(seen)
+        model, acc = {}, {}
+        for step in range(2):
+            grads = [torch.randn(512, dim, generator=g) for _ in per_rank]
+            garg = [x.to(dev) for x in grads] if ranks > 1 else grads[0].to(dev)
+            t.push(arg, garg)
+            torch.cuda.synchronize()
+            if rule == "sgd":
+                for k, gr in zip(per_rank, grads):
+                    for i in range(512):
+                        model[int(k[i])] = model.get(int(k[i]), torch.zeros(dim)) - lr * gr[i]
+        assert t.check() == 0
+        if rule == "sgd":
+            got = t.pull(arg)
+            for k, o in zip(per_rank, got if ranks > 1 else [got]):
+                want = torch.stack([model[int(v)] for v in k])
+                assert torch.allclose(o.cpu(), want, atol=1e-4, rtol=1e-4)
+        else:
+            got = t.pull(arg)
+            assert all(float(o.abs().sum()) > 0 for o in (got if ranks > 1 else [got]))
+        never = torch.tensor([7_000_000_001], dtype=torch.int64)
+        nk = [never.to(dev)] * ranks if ranks > 1 else never.to(dev)
+        ng = [torch.ones(1, dim, device=dev)] * ranks if ranks > 1 else torch.ones(1, dim, device=dev)
+        t.push(nk, ng)
+        torch.cuda.synchronize()
+        assert t.check() == max(ranks, 1)
+    finally:
+        if st is not None:
+            device.teardown(st)

@@ -832,6 +832,163 @@ PsPushApplyKernel(PsLaunch args, PsMeta meta, uint64_t slots, int rule, float lr
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Tables keyed by arbitrary 64-bit ids: rows are created on first pull, as in the reference's sparse table
+// (PullAccessAgent creates and zero-initialises a missing row, tips/core/ps/access_method.h:90-99,
+// sparse_access_method.h:23-27; any hashable key, sparse_table.h:164-165).  Every rank owns an open-addressing
+// table in peer-mapped memory: [cap] keys (stored as key + 1, 0 = empty), [cap][dim] fp32 rows that start at
+// zero, and the Adagrad accumulators.  The owner of a key is a hash of it; a pull finds the slot or claims an
+// empty one with a system-scope CAS on the owner's memory (bounded probes; a full table raises an error word),
+// then reads the row.  A push finds the slot (a key that was never pulled is counted as missing, like the host
+// server does) and applies SGD or Adagrad to the owner's row with vector atomics as the gradients arrive: the
+// reference's consistency model, servers apply pushes in arrival order (ps_server.h:248-264).
+struct HashTables {
+  unsigned long long* keys[kMaxRanks];
+  float* rows[kMaxRanks];
+  float* state[kMaxRanks];
+  uint64_t cap;   // slots per rank, power of two
+  int32_t dim;
+  int32_t nranks;
+};
+struct HashIO {
+  const int64_t* ids[kMaxRanks];   // per local rank: [count] keys
+  const void* grads[kMaxRanks];    // push: [count, ld]
+  void* out[kMaxRanks];            // pull: [count, ld]
+  int32_t* error;                  // 1 table full, 2 key not representable
+  unsigned long long* missing;     // push: rows that were never pulled
+};
+
+constexpr uint32_t kHashMaxProbes = 4096;
+
+__device__ __forceinline__ int HashOwner(uint64_t key, int n) { return static_cast<int>(Mix64(key ^ 0x9e3779b97f4a7c15ull) % n); }
+
+// Slot of `key` in the owner's table; insert = claim an empty slot when the key is absent.
+__device__ __forceinline__ uint32_t HashFind(unsigned long long* keys, uint64_t cap, uint64_t key, bool insert) {
+  const unsigned long long stored = key + 1;
+  uint64_t h = Mix64(key) & (cap - 1);
+  for (uint32_t probe = 0; probe < kHashMaxProbes && probe < cap; ++probe) {
+    unsigned long long cur;
+    asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(cur) : "l"(keys + h) : "memory");
+    if (cur == stored) return static_cast<uint32_t>(h);
+    if (cur == 0ull) {
+      if (!insert) return kNoSlot;
+      cur = atomicCAS_system(keys + h, 0ull, stored);
+      if (cur == 0ull || cur == stored) return static_cast<uint32_t>(h);
+    }
+    h = (h + 1) & (cap - 1);
+  }
+  return kNoSlot - 1;  // probes exhausted: the table is (nearly) full
+}
+
+template <typename OutT>
+__global__ void __launch_bounds__(256)
+HashPullKernel(HashTables t, HashIO io, int64_t count, int64_t out_ld) {
+  const int dim  = t.dim;
+  const int vecs = dim / 4;
+  const RowLanes L(dim);
+  const int64_t warp_global = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int64_t nwarps      = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
+  const int64_t* ids        = io.ids[blockIdx.y];
+  OutT* out                 = static_cast<OutT*>(io.out[blockIdx.y]);
+  for (int64_t base = warp_global * 32; base < count; base += nwarps * 32) {
+    const int64_t mine = base + L.lane;
+    uint32_t slot = kNoSlot;
+    int owner     = 0;
+    if (mine < count) {
+      const uint64_t key = static_cast<uint64_t>(ids[mine]);
+      if (key == ~0ull) {
+        atomicExch(io.error, 2);
+      } else {
+        owner = HashOwner(key, t.nranks);
+        slot  = HashFind(t.keys[owner], t.cap, key, true);
+        if (slot == kNoSlot - 1) {
+          atomicExch(io.error, 1);
+          slot = kNoSlot;
+        }
+      }
+    }
+    for (int j = 0; j < 32; j += L.ipw) {
+      const int src      = j + L.sub;
+      const uint32_t s   = __shfl_sync(kFullMask, slot, src);
+      const int o        = __shfl_sync(kFullMask, owner, src);
+      const int64_t item = base + src;
+      if (item >= count) continue;
+      OutT* dst = out + item * out_ld;
+      for (int v = L.sublane; v < vecs; v += L.lpi) {
+        U4 q{0, 0, 0, 0};
+        if (s != kNoSlot) q = LdSys(t.rows[o] + static_cast<uint64_t>(s) * dim + v * 4);
+        if (sizeof(OutT) == 4) {
+          *reinterpret_cast<U4*>(dst + v * 4) = q;
+        } else {
+          OutT w[4] = {FromFloat<OutT>(__uint_as_float(q.x)), FromFloat<OutT>(__uint_as_float(q.y)),
+                       FromFloat<OutT>(__uint_as_float(q.z)), FromFloat<OutT>(__uint_as_float(q.w))};
+          *reinterpret_cast<uint2*>(dst + v * 4) = *reinterpret_cast<uint2*>(w);
+        }
+      }
+    }
+  }
+}
+
+template <typename GradT>
+__global__ void __launch_bounds__(256)
+HashPushKernel(HashTables t, HashIO io, int64_t count, int64_t grad_ld, float grad_scale, int rule, float lr, float eps) {
+  const int dim  = t.dim;
+  const int vecs = dim / 4;
+  const RowLanes L(dim);
+  const int64_t warp_global = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int64_t nwarps      = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
+  const int64_t* ids        = io.ids[blockIdx.y];
+  const GradT* grads        = static_cast<const GradT*>(io.grads[blockIdx.y]);
+  for (int64_t base = warp_global * 32; base < count; base += nwarps * 32) {
+    const int64_t mine = base + L.lane;
+    uint32_t slot = kNoSlot;
+    int owner     = 0;
+    if (mine < count) {
+      const uint64_t key = static_cast<uint64_t>(ids[mine]);
+      owner = HashOwner(key, t.nranks);
+      slot  = key == ~0ull ? kNoSlot : HashFind(t.keys[owner], t.cap, key, false);
+      if (slot >= kNoSlot - 1) {
+        slot = kNoSlot;
+        atomicAdd(io.missing, 1ull);
+      }
+    }
+    for (int j = 0; j < 32; j += L.ipw) {
+      const int src      = j + L.sub;
+      const uint32_t s   = __shfl_sync(kFullMask, slot, src);
+      const int o        = __shfl_sync(kFullMask, owner, src);
+      const int64_t item = base + src;
+      if (item >= count || s == kNoSlot) continue;
+      float* w       = t.rows[o] + static_cast<uint64_t>(s) * dim;
+      float* st      = t.state[o] ? t.state[o] + static_cast<uint64_t>(s) * dim : nullptr;
+      const GradT* g = grads + item * grad_ld;
+      for (int v = L.sublane; v < vecs; v += L.lpi) {
+        float d[4], gv[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) gv[k] = ToFloat<GradT>(g[v * 4 + k]) * grad_scale;
+        if (rule == 1 && st) {
+          const U4 q = LdSys(st + v * 4);
+          const float acc[4] = {__uint_as_float(q.x), __uint_as_float(q.y), __uint_as_float(q.z), __uint_as_float(q.w)};
+          float g2[4];
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            g2[k] = gv[k] * gv[k];
+            d[k]  = -lr * gv[k] / (sqrtf(acc[k] + g2[k]) + eps);
+          }
+          asm volatile("red.relaxed.sys.global.add.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(st + v * 4), "f"(g2[0]), "f"(g2[1]),
+                       "f"(g2[2]), "f"(g2[3])
+                       : "memory");
+        } else {
+#pragma unroll
+          for (int k = 0; k < 4; ++k) d[k] = -lr * gv[k];
+        }
+        asm volatile("red.relaxed.sys.global.add.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(w + v * 4), "f"(d[0]), "f"(d[1]),
+                     "f"(d[2]), "f"(d[3])
+                     : "memory");
+      }
+    }
+  }
+}
+
 // One-block cross-rank barrier: when it completes on this rank, every rank has reached the
 // same point of its stream, i.e. finished all the work it enqueued before its own fence.
 __global__ void FenceKernel(CommCtx c0, CommCtx c1, CommCtx c2, CommCtx c3, CommCtx c4, CommCtx c5, CommCtx c6, CommCtx c7,
@@ -1305,6 +1462,78 @@ int tipsk_ps_push_async(const int64_t* const* ids, const void* const* grads, int
                                                           eps);
   else
     return SetError(-2, "ps push: gradients must be fp32 or bf16");
+  TIPSK_LAUNCH_CHECK();
+  return 0;
+}
+
+/* ---- tables keyed by arbitrary 64-bit ids (rows created on first pull) ----
+ * keys / rows / states: one pointer per rank as mapped here ([cap] u64, [cap][dim] fp32, [cap][dim] fp32 or null);
+ * all zero at creation.  ids / outs / grads: one pointer per LOCAL rank (nlocal = 1, or nranks when emulated).
+ * error: device int32 (1 table full, 2 key 2^64-1), missing: device u64 counter of pushed rows never pulled. */
+int tipsk_hash_pull(void* const* keys, void* const* rows, int nranks, uint64_t cap, int dim, const int64_t* const* ids,
+                    void* const* outs, int nlocal, int64_t count, int64_t out_ld, int out_dtype, int32_t* error,
+                    void* stream) {
+  TIPSK_REQUIRE(nranks >= 1 && nranks <= kMaxRanks && (nlocal == 1 || nlocal == nranks), "hash pull: bad rank counts");
+  TIPSK_REQUIRE(cap >= 2 && (cap & (cap - 1)) == 0 && cap <= (1ull << 31), "hash pull: cap must be a power of two");
+  TIPSK_REQUIRE(dim >= 4 && dim % 4 == 0 && out_ld % 4 == 0, "hash pull: dim and the output pitch must be multiples of 4");
+  TIPSK_REQUIRE(out_dtype == kF32 || out_dtype == kBF16, "hash pull: output must be fp32 or bf16");
+  if (count <= 0) return 0;
+  HashTables t;
+  HashIO io;
+  memset(&t, 0, sizeof(t));
+  memset(&io, 0, sizeof(io));
+  for (int r = 0; r < nranks; ++r) {
+    t.keys[r] = static_cast<unsigned long long*>(keys[r]);
+    t.rows[r] = static_cast<float*>(rows[r]);
+  }
+  t.cap = cap; t.dim = dim; t.nranks = nranks;
+  for (int i = 0; i < nlocal; ++i) {
+    io.ids[i] = ids[i];
+    io.out[i] = outs[i];
+  }
+  io.error = error;
+  dim3 grid(PsGrid(count, LanesPerItem(dim)), nlocal);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (out_dtype == kF32)
+    HashPullKernel<float><<<grid, 256, 0, s>>>(t, io, count, out_ld);
+  else
+    HashPullKernel<__nv_bfloat16><<<grid, 256, 0, s>>>(t, io, count, out_ld);
+  TIPSK_LAUNCH_CHECK();
+  return 0;
+}
+
+int tipsk_hash_push(void* const* keys, void* const* rows, void* const* states, int nranks, uint64_t cap, int dim,
+                    const int64_t* const* ids, const void* const* grads, int nlocal, int64_t count, int64_t grad_ld,
+                    int grad_dtype, float grad_scale, int rule, float lr, float eps, int32_t* error,
+                    unsigned long long* missing, void* stream) {
+  TIPSK_REQUIRE(nranks >= 1 && nranks <= kMaxRanks && (nlocal == 1 || nlocal == nranks), "hash push: bad rank counts");
+  TIPSK_REQUIRE(cap >= 2 && (cap & (cap - 1)) == 0 && cap <= (1ull << 31), "hash push: cap must be a power of two");
+  TIPSK_REQUIRE(dim >= 4 && dim % 4 == 0, "hash push: dim must be a multiple of 4");
+  TIPSK_REQUIRE(grad_dtype == kF32 || grad_dtype == kBF16, "hash push: gradients must be fp32 or bf16");
+  TIPSK_REQUIRE(rule == 0 || (rule == 1 && states), "hash push: SGD, or Adagrad with accumulators");
+  if (count <= 0) return 0;
+  HashTables t;
+  HashIO io;
+  memset(&t, 0, sizeof(t));
+  memset(&io, 0, sizeof(io));
+  for (int r = 0; r < nranks; ++r) {
+    t.keys[r]  = static_cast<unsigned long long*>(keys[r]);
+    t.rows[r]  = static_cast<float*>(rows[r]);
+    t.state[r] = states ? static_cast<float*>(states[r]) : nullptr;
+  }
+  t.cap = cap; t.dim = dim; t.nranks = nranks;
+  for (int i = 0; i < nlocal; ++i) {
+    io.ids[i]   = ids[i];
+    io.grads[i] = grads[i];
+  }
+  io.error   = error;
+  io.missing = missing;
+  dim3 grid(PsGrid(count, LanesPerItem(dim)), nlocal);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (grad_dtype == kF32)
+    HashPushKernel<float><<<grid, 256, 0, s>>>(t, io, count, grad_ld, grad_scale, rule, lr, eps);
+  else
+    HashPushKernel<__nv_bfloat16><<<grid, 256, 0, s>>>(t, io, count, grad_ld, grad_scale, rule, lr, eps);
   TIPSK_LAUNCH_CHECK();
   return 0;
 }

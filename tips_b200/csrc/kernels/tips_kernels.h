@@ -177,6 +177,14 @@ int tipsk_ps_pull(const int64_t* const* host_ids, void* const* host_outs, int64_
 int tipsk_ps_push(const int64_t* const* host_ids, const void* const* host_grads, int64_t batch, int64_t grad_ld,
                   int64_t grad_col0, int grad_dtype, float grad_scale, int rule, float lr, float eps, int reuse_index,
                   void* stream);
+/* Tables keyed by arbitrary 64-bit ids, rows created (zero) on first pull; see ps.cu. */
+int tipsk_hash_pull(void* const* host_keys, void* const* host_rows, int nranks, uint64_t cap, int dim,
+                    const int64_t* const* host_ids, void* const* host_outs, int nlocal, int64_t count, int64_t out_ld,
+                    int out_dtype, int32_t* error_dev, void* stream);
+int tipsk_hash_push(void* const* host_keys, void* const* host_rows, void* const* host_states, int nranks, uint64_t cap,
+                    int dim, const int64_t* const* host_ids, const void* const* host_grads, int nlocal, int64_t count,
+                    int64_t grad_ld, int grad_dtype, float grad_scale, int rule, float lr, float eps, int32_t* error_dev,
+                    unsigned long long* missing_dev, void* stream);
 /* Asynchronous push: gradients applied straight to the owner's rows with atomics, no fences (SGD / Adagrad). */
 int tipsk_ps_push_async(const int64_t* const* host_ids, const void* const* host_grads, int64_t batch, int64_t grad_ld,
                   int64_t grad_col0, int grad_dtype, float grad_scale, int rule, float lr, float eps, void* stream);

@@ -81,6 +81,8 @@ _PROTOS = {
     "tipsk_ps_status": (I, [POINTER(c_int32), POINTER(U)]),
     "tipsk_ps_pull": (I, [PP, PP, L, L, L, I, I, I, P]),
     "tipsk_ps_push": (I, [PP, PP, L, L, L, I, F, I, F, F, I, P]),
+    "tipsk_hash_pull": (I, [PP, PP, I, U, I, PP, PP, I, L, L, I, P, P]),
+    "tipsk_hash_push": (I, [PP, PP, PP, I, U, I, PP, PP, I, L, L, I, F, I, F, F, P, P, P]),
     "tipsk_ps_push_async": (I, [PP, PP, L, L, L, I, F, I, F, F, P]),
     "tipsk_gemm_bf16": (I, [P, P, P, P, P, I, I, I, I, I, I, I, P]),
     "tipsk_copy4d": (I, [P, P, L, L, L, L, P, P, P]),

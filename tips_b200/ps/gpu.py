@@ -402,3 +402,182 @@ def embedding_lookup(table: ShardedEmbedding, ids: torch.Tensor, out: torch.Tens
     """Differentiable pull into `out` (a [B, ld] buffer); the backward pass pushes the gradient."""
     anchor = torch.zeros((), device=out.device, requires_grad=True)
     return _LookupFn.apply(table, ids, anchor, out, col0, grad_scale)
+
+
+class ShardedDense:
+    """A dense parameter-server table on the GPUs: a vector of `size` elements whose fp32 master copy and optimizer
+    state are sharded over the ranks (every rank serves 1/N of the vector), updated by the server-side rule when
+    gradients are pushed, with the current values readable on every rank.
+
+    The reference declares a range-partitioned dense table with a pull access method
+    (tips/core/ps/dense_table.h:49-131, dense_access_method.h:10-25) and stops there; the host version of this
+    table is ``tips_b200.ps.host.HostDenseTable``.  On the GPUs a push is ONE kernel (csrc/kernels/comm.cu,
+    ``AllreduceUpdateKernel``): every rank reduces the share of the pushed gradients that it serves straight out
+    of the peers' memory (NVLS ``multimem.ld_reduce`` or peer loads), applies SGD-momentum or Adam(W) to its share
+    of the master weights, and stores the new values into every rank's copy, so a pull is a local read.  With one
+    rank the same rule runs as the plain fused optimizer kernel.
+
+    ``push`` is a collective: every rank calls it with its own gradient, in the same order."""
+
+    def __init__(self, size: int, dtype=torch.bfloat16, optimizer: str = "sgd", lr: float = 0.01, momentum: float = 0.0,
+                 betas=(0.9, 0.999), eps: float = 1e-8, weight_decay: float = 0.0, device=None, average: bool = True):
+        from .. import runtime
+        from ..ops.optim import FusedAdam, FusedSGD
+        if optimizer not in ("sgd", "adam", "adamw"):
+            raise ValueError("optimizer must be sgd, adam or adamw")
+        st = runtime.device_state() if runtime.is_initialized() else None
+        self.world = runtime.size() if runtime.is_initialized() else 1
+        self.device = device or (st.device if st is not None else torch.device("cuda", torch.cuda.current_device()))
+        self.size, self.average = int(size), bool(average)
+        self.param = torch.nn.Parameter(torch.zeros(self.size, dtype=dtype, device=self.device))
+        if optimizer == "sgd":
+            self.opt = FusedSGD([self.param], lr=lr, momentum=momentum, weight_decay=weight_decay,
+                                bucket_bytes=1 << 62)
+        else:
+            from ..ops.optim import FusedAdamW
+            cls = FusedAdamW if optimizer == "adamw" else FusedAdam
+            self.opt = cls([self.param], lr=lr, betas=betas, eps=eps, weight_decay=weight_decay, bucket_bytes=1 << 62)
+        use_window = st is not None and st.window is not None and self.world > 1
+        self._fs = self.opt.build(st if use_window else None)[0]
+        self.sharded = bool(use_window and self.opt.shard_for_fused_update(st))
+        if self.world > 1 and not self.sharded:
+            raise RuntimeError("a dense table over several ranks needs the symmetric window of the GPU data plane")
+
+    def pull(self, begin: int = 0, end: Optional[int] = None) -> torch.Tensor:
+        """Current values of elements [begin, end): this rank's copy, which the last push brought up to date."""
+        return self.param.detach()[begin:self.size if end is None else end]
+
+    def assign(self, values: torch.Tensor) -> None:
+        """Overwrite the whole vector (initial values, a restored checkpoint); every rank passes the same values."""
+        with torch.no_grad():
+            self.param.copy_(values.to(self.param.dtype).reshape(-1))
+        self._fs.refresh_master_from_params()
+
+    def push(self, grad: torch.Tensor, lr: Optional[float] = None) -> None:
+        """Hand in this rank's gradient of the whole vector; the gradients of all ranks are summed (averaged with
+        ``average=True``) and every rank's shard is updated by the table's rule."""
+        if lr is not None:
+            self.opt.param_groups[0]["lr"] = lr
+        fs, b = self._fs, self._fs.bucket
+        self.param.grad = grad.reshape(-1)
+        b.pack()
+        fs.grads_packed = True
+        post = 1.0 / self.world if self.average else 1.0
+        if self.sharded:
+            self.opt.push_update_hyper(fs)
+            base.check(base.K().tipsk_allreduce_update(b.win_off, post, 3, base.comm_stream()), "dense_push")
+        elif post != 1.0:
+            b.grad.mul_(post)
+        self.opt.step()
+
+    def state(self) -> dict:
+        """Full-size master weights and optimizer state (a collective when the table is sharded)."""
+        fs = self._fs
+        return {"master": fs.full_master().cpu(), "steps": fs.steps,
+                "state": {k: fs.full(v).cpu() for k, v in fs.state.items() if k != "step_dev"}}
+
+    def load_state(self, saved: dict) -> None:
+        """Inverse of `state`, under any number of ranks: every rank cuts its own share out."""
+        fs = self._fs
+        fs.steps = int(saved["steps"])
+        fs.load_master(saved["master"].to(self.device))
+        for k, v in saved["state"].items():
+            fs.load_state(k, v.to(self.device))
+
+
+class HashedEmbedding:
+    """A sparse table keyed by ARBITRARY 64-bit ids whose rows come into existence (as zeros) the first time they
+    are pulled: the reference's sparse-table semantics (tips/core/ps/access_method.h:90-99,
+    sparse_access_method.h:23-27, sparse_table.h:164-165) on the GPUs.
+
+    Every rank owns an open-addressing table of `capacity_per_rank` slots in peer-mapped memory; the owner of a key
+    is a hash of it.  ``pull`` finds or claims the slot on the owner (system-scope CAS over NVLink, bounded probing)
+    and reads the row; ``push`` applies SGD or Adagrad to the owner's row with vector atomics as gradients arrive,
+    the reference's consistency model (servers apply pushes in arrival order, ps_server.h:248-264), and reports how
+    many pushed rows had never been pulled.  ``ShardedEmbedding`` is the table for dense id ranges with the exact
+    synchronous update; the host tables in ``tips_b200.ps.host`` serve the same keys from CPU memory."""
+
+    def __init__(self, dim: int, capacity_per_rank: int, optimizer: str = "sgd", lr: float = 0.01, eps: float = 1e-8,
+                 device=None):
+        if optimizer not in ("sgd", "adagrad"):
+            raise ValueError("optimizer must be sgd or adagrad")
+        if dim % 4:
+            raise ValueError("dim must be a multiple of 4")
+        self.rank, self.size, self.emulated, st = _world()
+        self.device = device or (st.device if st is not None else torch.device("cuda", torch.cuda.current_device()))
+        self.dim, self.lr, self.eps = dim, lr, eps
+        self.rule = 1 if optimizer == "adagrad" else 0
+        cap = 2
+        while cap < capacity_per_rank:
+            cap *= 2
+        self.cap = cap
+        sizes = [cap * 8, cap * dim * 4, cap * dim * 4 if self.rule == 1 else 0]
+        nlocal = self.size if self.emulated else 1
+        if self.emulated or self.size == 1:
+            bufs = [[torch.zeros(max(sz, 16), dtype=torch.uint8, device=self.device) for _ in range(nlocal)] for sz in sizes]
+            ptrs = [[t.data_ptr() for t in group] for group in bufs]
+        else:
+            import torch.distributed as dist
+            import torch.distributed._symmetric_memory as symm_mem
+            bufs, ptrs, self._handles = [], [], []
+            for sz in sizes:
+                t = symm_mem.empty(max(sz, 16), dtype=torch.uint8, device=self.device)
+                h = symm_mem.rendezvous(t, dist.group.WORLD.group_name)
+                t.zero_()
+                bufs.append([t])
+                ptrs.append([int(p) for p in h.buffer_ptrs])
+                self._handles.append(h)
+        self._bufs = bufs
+        self._keys, self._rows = ptrs[0], ptrs[1]
+        self._state = ptrs[2] if self.rule == 1 else None
+        self._error = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self._missing = torch.zeros(1, dtype=torch.int64, device=self.device)
+        torch.cuda.synchronize()
+        if self.size > 1 and not self.emulated:
+            from .. import runtime
+            runtime.barrier()
+
+    def _per_rank(self, tensors):
+        if self.emulated:
+            assert isinstance(tensors, (list, tuple)) and len(tensors) == self.size
+            return base.ptr_array(list(tensors)), tensors[0], len(tensors)
+        return base.ptr_array([tensors]), tensors, 1
+
+    def pull(self, keys, dtype=torch.float32, fence: bool = False):
+        """keys [B] int64 (any bit pattern except -1) -> [B, dim]; unknown keys become zero rows on their owner."""
+        k_arr, k0, nlocal = self._per_rank(keys)
+        mk = lambda: torch.empty(k0.numel(), self.dim, dtype=dtype, device=self.device)
+        out = [mk() for _ in range(self.size)] if self.emulated else mk()
+        o_arr, o0, _ = self._per_rank(out)
+        if fence:
+            base.check(base.K().tipsk_comm_fence(2, base.stream()), "fence")
+        base.check(base.K().tipsk_hash_pull(base.ptr_array(self._keys), base.ptr_array(self._rows), self.size, self.cap,
+                                            self.dim, k_arr, o_arr, nlocal, k0.numel(), o0.stride(0), base.code(o0),
+                                            self._error.data_ptr(), base.stream()), "hash_pull")
+        return out
+
+    def push(self, keys, grads, grad_scale: float = 1.0, lr: Optional[float] = None) -> None:
+        k_arr, k0, nlocal = self._per_rank(keys)
+        g_arr, g0, _ = self._per_rank(grads)
+        base.check(base.K().tipsk_hash_push(base.ptr_array(self._keys), base.ptr_array(self._rows),
+                                            base.ptr_array(self._state) if self._state else None, self.size, self.cap,
+                                            self.dim, k_arr, g_arr, nlocal, k0.numel(), g0.stride(0), base.code(g0),
+                                            float(grad_scale), self.rule, float(self.lr if lr is None else lr),
+                                            float(self.eps), self._error.data_ptr(), self._missing.data_ptr(),
+                                            base.stream()), "hash_push")
+
+    def check(self) -> int:
+        """Raise if a table filled up; returns (and clears) the number of pushed rows that had never been pulled."""
+        err, missing = int(self._error.item()), int(self._missing.item())
+        self._error.zero_()
+        self._missing.zero_()
+        if err == 1:
+            raise RuntimeError("hashed table: an owner's table is full; raise capacity_per_rank")
+        if err == 2:
+            raise RuntimeError("hashed table: the key 2**64 - 1 cannot be stored")
+        return missing
+
+    def local_size(self, rank: Optional[int] = None) -> int:
+        """Rows that exist on this rank (emulated: on `rank`)."""
+        keys = self._bufs[0][rank if self.emulated else 0]
+        return int((keys.view(torch.int64) != 0).sum().item())

@@ -16,6 +16,8 @@ import os
 class Config:
     # Collective engine
     fusion_threshold_bytes: int = 64 << 20   # size of one gradient bucket / host fusion buffer
+    fusion_slice_bytes: int = 8 << 20        # a bucket is reduced in slices of about this size as backward
+                                             # completes them (0: the whole bucket at once)
     cycle_time_ms: int = 0                   # extra batching delay of the coordinator loop
     stall_warn_s: float = 60.0               # warn when a tensor waits this long for some ranks
     stall_abort_s: float = 0.0               # >0: fail the tensor instead of waiting forever

@@ -59,9 +59,26 @@ class Bucket:
         return self.grad[self.offsets[i]:self.offsets[i] + p.numel()].view(p.shape)
 
     # -- pack / unpack ------------------------------------------------------------
-    def pack(self, scale: float = 1.0, accumulate: bool = False):
-        """Gather the parameters' .grad tensors into the flat buffer (one launch on CUDA)."""
+    def slices(self, slice_bytes: int):
+        """Cut the bucket into runs of consecutive parameters of about `slice_bytes`: [(first, last + 1, element
+        offset, elements)].  Parameters sit in the buffer in the order backward produces their gradients, so a
+        slice is complete, and can be reduced, while backward is still working on the later ones."""
+        es = torch.empty((), dtype=self.wire_dtype).element_size()
+        out, first, start = [], 0, 0
+        for i in range(len(self.params)):
+            end = self.offsets[i + 1] if i + 1 < len(self.params) else self.numel
+            last = i + 1 == len(self.params)
+            if (end - start) * es >= slice_bytes or last:
+                out.append((first, i + 1, start, end - start))
+                first, start = i + 1, end
+        return out
+
+    def pack(self, scale: float = 1.0, accumulate: bool = False, only=None):
+        """Gather the parameters' .grad tensors into the flat buffer (one launch on CUDA); `only` = (first, last)
+        restricts it to that run of parameters."""
         grads = [p.grad for p in self.params]
+        if only is not None:
+            grads = [g if only[0] <= i < only[1] else None for i, g in enumerate(grads)]
         if self.device.type == "cuda":
             from ..ops import base
             present = [(i, g) for i, g in enumerate(grads) if g is not None]

@@ -113,11 +113,24 @@ class _DistributedMixin:
         for i, b in enumerate(self._tips_buckets):
             b.index = i
             b.name = f"{prefix}.bucket.{i}"
-        self._tips_bucket_of = {}
+        # A bucket is reduced in slices: runs of consecutive parameters of about fusion_slice_bytes that are handed
+        # to the engine as soon as backward has produced their gradients, so that only the last slice of the last
+        # bucket is left when backward ends.  One slice = the whole bucket when slicing does not apply.
+        self._tips_slice_of = {}
+        slice_bytes = int(get_config().fusion_slice_bytes)
         for b in self._tips_buckets:
             b.pending = len(b.params)
-            for p in b.params:
-                self._tips_bucket_of[id(p)] = b
+            es = b.grad.element_size()
+            sliced = (slice_bytes > 0 and self._tips_size > 1 and not self._tips_update_in_allreduce
+                      and b.numel * es >= 2 * slice_bytes)
+            b.slice_list = b.slices(slice_bytes) if sliced else [(0, len(b.params), 0, b.numel)]
+            b.slice_ready = [0] * len(b.slice_list)
+            b.slice_launched = [False] * len(b.slice_list)
+            b.handles = [None] * len(b.slice_list)
+            b.slice_names = [b.name if len(b.slice_list) == 1 else f"{b.name}.s{k}" for k in range(len(b.slice_list))]
+            for k, (i0, i1, _, _) in enumerate(b.slice_list):
+                for p in b.params[i0:i1]:
+                    self._tips_slice_of[id(p)] = (b, k)
         for p in params:
             self._tips_hooks.append(p.register_post_accumulate_grad_hook(self._tips_make_hook()))
         import ctypes
@@ -138,14 +151,16 @@ class _DistributedMixin:
                     p.grad = p.grad.to_dense()
                 else:
                     self._tips_sparse.append(p)
-            b = self._tips_bucket_of[pid]
+            b, k = self._tips_slice_of[pid]
             b.ready_count += 1
-            if b.ready_count == len(b.params):
-                self._tips_launch(b)
+            b.slice_ready[k] += 1
+            i0, i1, _, _ = b.slice_list[k]
+            if b.slice_ready[k] == i1 - i0:
+                self._tips_launch(b, k)
         return hook
 
-    def _tips_launch(self, b):
-        """Pack the bucket and hand it to the collective engine."""
+    def _tips_launch(self, b, k):
+        """Pack slice `k` of the bucket and hand it to the collective engine."""
         n = self._tips_size
         pre = 1.0
         post = 1.0
@@ -154,26 +169,30 @@ class _DistributedMixin:
             post = self._tips_predivide / n
         if self._tips_avg_aggregated and self._tips_passes > 1:
             pre /= self._tips_passes
-        dense = [p for p in b.params if not (p.grad is not None and p.grad.is_sparse)]
-        if any(p.grad is None for p in dense) or len(dense) != len(b.params):
-            b.grad.zero_()
+        i0, i1, off, count = b.slice_list[k]
+        params = b.params[i0:i1]
+        part = b.grad[off:off + count]
+        dense = [p for p in params if not (p.grad is not None and p.grad.is_sparse)]
+        if any(p.grad is None for p in dense) or len(dense) != len(params):
+            part.zero_()
         saved = None
-        if len(dense) != len(b.params):  # sparse gradients travel separately
-            saved = {id(p): p.grad for p in b.params if p.grad is not None and p.grad.is_sparse}
-            for p in b.params:
+        if len(dense) != len(params):  # sparse gradients travel separately
+            saved = {id(p): p.grad for p in params if p.grad is not None and p.grad.is_sparse}
+            for p in params:
                 if id(p) in saved:
                     p.grad = None
-        with nvtx_range(f"tips.pack {b.name}"):
-            b.pack(scale=pre)
+        with nvtx_range(f"tips.pack {b.slice_names[k]}"):
+            b.pack(scale=pre, only=(i0, i1))
         if saved:
-            for p in b.params:
+            for p in params:
                 if id(p) in saved:
                     p.grad = saved[id(p)]
+        b.slice_launched[k] = True
         b.launched = True
         if n == 1:
             if post != 1.0:
-                b.grad.mul_(post)
-            b.handle = None
+                part.mul_(post)
+            b.handles[k] = None
             return
         if self._tips_update_in_allreduce:
             if saved:
@@ -183,27 +202,28 @@ class _DistributedMixin:
             self.push_update_hyper(self._tips_fs_of[id(b)])
         h = C._Handle()
         h.kind = "allreduce"
-        h.output = b.grad
-        h.keep = [b.grad]
-        with nvtx_range(f"tips.enqueue {b.name}"):
-            b.handle = C._enqueue(h, 0, b.name, b.grad, b.grad, (b.numel,), b.grad.dtype, reduce_op=0, prescale=1.0,
-                                  postscale=post)
+        h.output = part
+        h.keep = [part]
+        with nvtx_range(f"tips.enqueue {b.slice_names[k]}"):
+            b.handles[k] = C._enqueue(h, 0, b.slice_names[k], part, part, (count,), part.dtype, reduce_op=0,
+                                      prescale=1.0, postscale=post)
 
     # ------------------------------------------------------------- public API
     def synchronize(self):
         """Wait for every gradient allreduce of this step and make the reduced gradients visible."""
         for b in self._tips_buckets:
-            if not getattr(b, "launched", False):
-                if b.ready_count == 0 and all(p.grad is None for p in b.params):
-                    # no gradient at all on this rank: still take part with zeros so that ranks stay in step
-                    pass
-                self._tips_launch(b)
+            for k in range(len(b.slice_list)):
+                if not b.slice_launched[k]:
+                    # no (or not every) gradient of the slice on this rank: still take part, with zeros for the
+                    # missing ones, so that the ranks stay in step
+                    self._tips_launch(b, k)
         timeout = get_config().collective_timeout_s
         for b in self._tips_buckets:
-            if b.handle is not None:
-                with nvtx_range(f"tips.wait {b.name}"):
-                    C.synchronize(b.handle, timeout if timeout > 0 else None)
-                b.handle = None
+            for k, h in enumerate(b.handles):
+                if h is not None:
+                    with nvtx_range(f"tips.wait {b.slice_names[k]}"):
+                        C.synchronize(h, timeout if timeout > 0 else None)
+                    b.handles[k] = None
         # a kernel that gave up on a peer skipped its reduction (and, with the update inside the allreduce, its
         # update): stop here, before the optimizer applies gradients that were never combined
         if any(b.grad.is_cuda for b in self._tips_buckets):
@@ -238,7 +258,7 @@ class _DistributedMixin:
         if n <= 0:
             return
         names = buf.value.decode().split("\n")
-        mine = {b.name for b in self._tips_buckets}
+        mine = {name for b in self._tips_buckets for name in b.slice_names}
         order = [x for x in names if x in mine]
         if len(order) != len(mine):
             return
@@ -280,6 +300,8 @@ class _DistributedMixin:
         for b in self._tips_buckets:
             b.ready_count = 0
             b.launched = False
+            b.slice_ready = [0] * len(b.slice_list)
+            b.slice_launched = [False] * len(b.slice_list)
         for k in self._tips_pass_count:
             self._tips_pass_count[k] = 0
         if not self._tips_fused:
@@ -293,11 +315,14 @@ class _DistributedMixin:
         per-step counters and the frozen bucket order, so that the next backward pass starts a clean step that is
         negotiated again.  Call it on every rank after ``tips_b200.reset_collectives()`` (``elastic.run`` does)."""
         for b in self._tips_buckets:
-            if b.handle is not None:
-                C.abandon(b.handle)
-                b.handle = None
+            for k, h in enumerate(b.handles):
+                if h is not None:
+                    C.abandon(h)
+                    b.handles[k] = None
             b.ready_count = 0
             b.launched = False
+            b.slice_ready = [0] * len(b.slice_list)
+            b.slice_launched = [False] * len(b.slice_list)
         for k in self._tips_pass_count:
             self._tips_pass_count[k] = 0
         self._tips_sparse = []
@@ -312,7 +337,7 @@ class _DistributedMixin:
                 p.grad = None
 
     def zero_grad(self, set_to_none: bool = True):
-        if any(getattr(b, "launched", False) and b.handle is not None for b in self._tips_buckets):
+        if any(h is not None for b in self._tips_buckets for h in b.handles):
             raise TipsError("zero_grad() called while gradient allreduces are in flight; call step() or "
                             "synchronize() first", 3)
         return super().zero_grad(set_to_none)

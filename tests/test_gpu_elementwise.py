@@ -306,3 +306,20 @@ def test_make_subgraph_replays_our_kernels():
             ref = ln(x) * 2
         assert torch.equal(out, ref)
     assert g.replays == 2
+
+
+@pytest.mark.parametrize("dtype,shape", [(torch.bfloat16, (5, 2048, 7, 7)), (torch.float32, (3, 12, 4, 9))])
+def test_global_average_pool(dtype, shape):
+    from tips_b200.ops.pool import global_avg_pool
+    torch.manual_seed(1)
+    dev = _dev()
+    x = torch.randn(shape, device=dev).to(dtype).contiguous(memory_format=torch.channels_last).requires_grad_()
+    y = global_avg_pool(x)
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    xr = x.detach().float().requires_grad_()
+    yr = xr.mean(dim=(2, 3))
+    yr.backward(dy.float())
+    tol = 1e-5 if dtype == torch.float32 else 2e-2
+    assert y.shape == yr.shape and torch.allclose(y.float(), yr, atol=tol, rtol=tol)
+    assert torch.allclose(x.grad.float(), xr.grad, atol=tol, rtol=tol)

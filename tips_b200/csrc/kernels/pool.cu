@@ -7,6 +7,8 @@
 // input activation is not read again.
 //
 // The reference has no pooling (model math is TensorFlow's); this serves the ResNet-50 benchmark model.
+#include <algorithm>
+
 #include "kernels/common.cuh"
 #include "kernels/tips_kernels.h"
 
@@ -109,6 +111,54 @@ int GridFor(int64_t total) {
   return static_cast<int>(blocks < cap ? blocks : cap);
 }
 
+// Global average pooling of an NHWC activation: y[n, c] = mean over the hw pixels; one thread per (image, 8
+// channels), 16-byte loads down the pixel axis.  Backward spreads dy / hw over the pixels.
+template <typename T>
+__global__ void __launch_bounds__(256)
+GlobalAvgPoolFwdKernel(const T* __restrict__ x, T* __restrict__ y, int n, int hw, int c) {
+  constexpr int V = 16 / sizeof(T);
+  const int cv = c / V;
+  const int64_t total = static_cast<int64_t>(n) * cv;
+  const float inv = 1.f / static_cast<float>(hw);
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int cg = static_cast<int>(i % cv);
+    const int in = static_cast<int>(i / cv);
+    float acc[V];
+#pragma unroll
+    for (int j = 0; j < V; ++j) acc[j] = 0.f;
+    const T* base = x + static_cast<int64_t>(in) * hw * c + cg * V;
+    for (int p = 0; p < hw; ++p) {
+      const Vec16<T> v = LoadVec(base + static_cast<int64_t>(p) * c);
+#pragma unroll
+      for (int j = 0; j < V; ++j) acc[j] += ToFloat(v.v[j]);
+    }
+    Vec16<T> o;
+#pragma unroll
+    for (int j = 0; j < V; ++j) o.v[j] = FromFloat<T>(acc[j] * inv);
+    StoreVec(y + static_cast<int64_t>(in) * c + cg * V, o);
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+GlobalAvgPoolBwdKernel(const T* __restrict__ dy, T* __restrict__ dx, int n, int hw, int c) {
+  constexpr int V = 16 / sizeof(T);
+  const int cv = c / V;
+  const int64_t total = static_cast<int64_t>(n) * hw * cv;
+  const float inv = 1.f / static_cast<float>(hw);
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int cg = static_cast<int>(i % cv);
+    const int in = static_cast<int>(i / (static_cast<int64_t>(cv) * hw));
+    const Vec16<T> g = LoadVec(dy + static_cast<int64_t>(in) * c + cg * V);
+    Vec16<T> o;
+#pragma unroll
+    for (int j = 0; j < V; ++j) o.v[j] = FromFloat<T>(ToFloat(g.v[j]) * inv);
+    StoreVec(dx + i * V, o);
+  }
+}
+
 }  // namespace
 }  // namespace tipsk
 
@@ -152,6 +202,45 @@ int tipsk_maxpool3x3s2_bwd(const void* dy, const void* idx, void* dx, int n, int
     MaxPoolBwdKernel<__half><<<GridFor(total), 256, 0, s>>>(static_cast<const __half*>(dy),
                                                             static_cast<const uint8_t*>(idx), static_cast<__half*>(dx),
                                                             n, h, w, c, ho, wo);
+  TIPSK_LAUNCH_CHECK();
+  return 0;
+}
+
+/* Global average pooling on NHWC: x [n, hw, c] -> y [n, c]; c a multiple of 8 (16-bit types) / 4 (fp32). */
+int tipsk_global_avgpool_fwd(const void* x, void* y, int n, int hw, int c, int dtype, void* stream) {
+  if (n <= 0 || hw <= 0 || c <= 0) return 0;
+  const int v = 16 / static_cast<int>(DTypeSize(dtype));
+  TIPSK_REQUIRE(dtype == kBF16 || dtype == kF16 || dtype == kF32, "avgpool: bf16, fp16 or fp32");
+  TIPSK_REQUIRE(c % v == 0, "avgpool: the channel count must be a multiple of 16 bytes");
+  const int64_t total = static_cast<int64_t>(n) * (c / v);
+  const int grid = static_cast<int>(std::min<int64_t>((total + 255) / 256, NumSMs() * 8));
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (dtype == kBF16)
+    GlobalAvgPoolFwdKernel<__nv_bfloat16><<<grid, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(x),
+                                                               static_cast<__nv_bfloat16*>(y), n, hw, c);
+  else if (dtype == kF16)
+    GlobalAvgPoolFwdKernel<__half><<<grid, 256, 0, s>>>(static_cast<const __half*>(x), static_cast<__half*>(y), n, hw, c);
+  else
+    GlobalAvgPoolFwdKernel<float><<<grid, 256, 0, s>>>(static_cast<const float*>(x), static_cast<float*>(y), n, hw, c);
+  TIPSK_LAUNCH_CHECK();
+  return 0;
+}
+
+int tipsk_global_avgpool_bwd(const void* dy, void* dx, int n, int hw, int c, int dtype, void* stream) {
+  if (n <= 0 || hw <= 0 || c <= 0) return 0;
+  const int v = 16 / static_cast<int>(DTypeSize(dtype));
+  TIPSK_REQUIRE(dtype == kBF16 || dtype == kF16 || dtype == kF32, "avgpool: bf16, fp16 or fp32");
+  TIPSK_REQUIRE(c % v == 0, "avgpool: the channel count must be a multiple of 16 bytes");
+  const int64_t total = static_cast<int64_t>(n) * hw * (c / v);
+  const int grid = static_cast<int>(std::min<int64_t>((total + 255) / 256, NumSMs() * 8));
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (dtype == kBF16)
+    GlobalAvgPoolBwdKernel<__nv_bfloat16><<<grid, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(dy),
+                                                               static_cast<__nv_bfloat16*>(dx), n, hw, c);
+  else if (dtype == kF16)
+    GlobalAvgPoolBwdKernel<__half><<<grid, 256, 0, s>>>(static_cast<const __half*>(dy), static_cast<__half*>(dx), n, hw, c);
+  else
+    GlobalAvgPoolBwdKernel<float><<<grid, 256, 0, s>>>(static_cast<const float*>(dy), static_cast<float*>(dx), n, hw, c);
   TIPSK_LAUNCH_CHECK();
   return 0;
 }

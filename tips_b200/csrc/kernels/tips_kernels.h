@@ -199,6 +199,9 @@ int tipsk_gemm_bf16_nn(const void* a, const void* b, void* c, int m, int n, int 
 int tipsk_gemm_status(void);
 
 /* ---- 3x3 / stride 2 / pad 1 max pooling on NHWC (pool.cu); idx holds the argmax position 0..8 per output ---- */
+/* Global average pooling on NHWC (x [n, hw, c] -> y [n, c]) and its backward (pool.cu). */
+int tipsk_global_avgpool_fwd(const void* x, void* y, int n, int hw, int c, int dtype, void* stream);
+int tipsk_global_avgpool_bwd(const void* dy, void* dx, int n, int hw, int c, int dtype, void* stream);
 int tipsk_maxpool3x3s2_fwd(const void* x, void* y, void* idx, int n, int h, int w, int c, int dtype, void* stream);
 int tipsk_maxpool3x3s2_bwd(const void* dy, const void* idx, void* dx, int n, int h, int w, int c, int dtype,
                            void* stream);

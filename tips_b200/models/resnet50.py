@@ -15,7 +15,8 @@ import torch.nn as nn
 
 from ..ops.conv import Conv2d, conv2d_passthrough, supported as _conv_supported
 from ..ops.norm import BatchNorm2d
-from ..ops.pool import MaxPool3x3S2
+from ..ops.linear import Linear
+from ..ops.pool import MaxPool3x3S2, global_avg_pool
 from ..ops.pointwise import softmax_cross_entropy
 
 
@@ -131,8 +132,9 @@ class ResNet50(nn.Module):
                 blocks.append(Bottleneck(cin, w, stride, downsample=(i == 0)))
                 cin = w * Bottleneck.expansion
         self.blocks = nn.Sequential(*blocks)
-        self.avgpool = nn.AdaptiveAvgPool2d(1)
-        self.fc = nn.Linear(cin, num_classes)
+        # library arm: torch pooling and nn.Linear (cuBLAS); otherwise the pooling kernel and the tcgen05 GEMM
+        self.avgpool = nn.AdaptiveAvgPool2d(1) if _LIBRARY_CONV else None
+        self.fc = nn.Linear(cin, num_classes) if _LIBRARY_CONV else Linear(cin, num_classes)
         for m in self.modules():
             if isinstance(m, nn.Conv2d):
                 nn.init.kaiming_normal_(m.weight, mode="fan_out", nonlinearity="relu")  # Conv2d does the same itself
@@ -147,7 +149,7 @@ class ResNet50(nn.Module):
             x = self.blocks(x)
         finally:
             _ARENA.end()
-        x = torch.flatten(self.avgpool(x), 1)
+        x = torch.flatten(self.avgpool(x), 1) if self.avgpool is not None else global_avg_pool(x)
         return self.fc(x)
 
     def loss(self, images, labels):

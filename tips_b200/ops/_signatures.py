@@ -100,6 +100,8 @@ _PROTOS = {
     "tipsk_stem_pad_nchw_f32": (I, [P, P, I, I, I, P]),
     "tipsk_stem_conv_fwd": (I, [P, P, P, I, I, I, I, P, P, P]),
     "tipsk_stem_conv_wgrad": (I, [P, P, P, I, I, I, I, P]),
+    "tipsk_global_avgpool_fwd": (I, [P, P, I, I, I, I, P]),
+    "tipsk_global_avgpool_bwd": (I, [P, P, I, I, I, I, P]),
     "tipsk_maxpool3x3s2_fwd": (I, [P, P, P, I, I, I, I, I, P]),
     "tipsk_maxpool3x3s2_bwd": (I, [P, P, P, I, I, I, I, I, P]),
 }

@@ -48,3 +48,32 @@ def max_pool_3x3_s2(x: torch.Tensor) -> torch.Tensor:
 class MaxPool3x3S2(nn.Module):
     def forward(self, x):
         return max_pool_3x3_s2(x)
+
+
+class _GlobalAvgPoolFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x):
+        xc = x.contiguous(memory_format=torch.channels_last)
+        n, c, h, w = xc.shape
+        y = torch.empty((n, c), dtype=x.dtype, device=x.device)
+        base.check(base.K().tipsk_global_avgpool_fwd(xc.data_ptr(), y.data_ptr(), n, h * w, c, base.code(xc),
+                                                     base.stream()), "avgpool_fwd")
+        ctx.x_shape = (n, c, h, w)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        n, c, h, w = ctx.x_shape
+        dyc = dy.contiguous()
+        dx = torch.empty(ctx.x_shape, dtype=dy.dtype, device=dy.device, memory_format=torch.channels_last)
+        base.check(base.K().tipsk_global_avgpool_bwd(dyc.data_ptr(), dx.data_ptr(), n, h * w, c, base.code(dyc),
+                                                     base.stream()), "avgpool_bwd")
+        return dx
+
+
+def global_avg_pool(x: torch.Tensor) -> torch.Tensor:
+    """[N, C, H, W] (channels-last) -> [N, C]: the mean over the pixels (the pooling in front of a classifier)."""
+    es = x.element_size()
+    if x.is_cuda and x.dim() == 4 and x.dtype in (torch.bfloat16, torch.float16, torch.float32) and (x.shape[1] * es) % 16 == 0:
+        return _GlobalAvgPoolFn.apply(x)
+    return x.float().mean(dim=(2, 3)).to(x.dtype)

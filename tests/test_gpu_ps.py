@@ -349,3 +349,48 @@ def test_hashed_table_creates_rows_on_first_pull(ranks, rule):
     finally:
         if st is not None:
             device.teardown(st)
+
+
+def test_server_subgroup_emulated(tmp_path):
+    """Four ranks, of which ranks 1 and 3 hold the tables (servers) and all four pull and push (workers): rows live
+    on the two servers only, the update equals the dense model, and the dump reloads into a one-rank table."""
+    from tips_b200.config import set_config
+    from tips_b200.parallel import device
+    from tips_b200.ps.gpu import ShardedEmbedding
+    set_config(symm_window_bytes=1 << 20, device_wait_budget_ms=2000, comm_blocks=8, ps_wire_dtype="fp32")
+    st = device.setup(emulate_ranks=4)
+    try:
+        dev = st.device
+        fields, rows, dim, batch = 2, 1777, 32, 512
+        t = ShardedEmbedding(fields, rows, dim, optimizer="adagrad", lr=0.05, init_scale=0.1, seed=2,
+                             expected_batch=batch, device=dev, servers=[3, 1])
+        assert t.servers == [1, 3] and t.rows_per_shard == (rows + 1) // 2
+        ws, ss = _dense_tables(t, fields, rows, dim)
+        torch.manual_seed(11)
+        for step in range(2):
+            ids = [(torch.rand(batch, fields, device=dev) ** 2 * rows).long().clamp_(0, rows - 1) for _ in range(4)]
+            outs = t.pull(ids, dtype=torch.float32, index=step == 1)
+            for r in range(4):
+                ref = torch.cat([ws[f][ids[r][:, f]] for f in range(fields)], dim=1)
+                assert torch.allclose(outs[r], ref, atol=3e-4, rtol=1e-4)
+            grads = [torch.randn(batch, fields * dim, device=dev) for _ in range(4)]
+            t.push(ids, grads, grad_scale=0.25, reuse_index=step == 1)
+            _reference_update(ws, ss, ids, [g * 0.25 for g in grads], "adagrad", 0.05, t.eps, dim)
+        t.check()
+        st.check_status()
+        sent, remote, _ = t.traffic()
+        assert 0 < remote < sent              # the servers' own rows never left them, the workers' all did
+        got, got_s = _dense_tables(t, fields, rows, dim)
+        for f in range(fields):
+            assert torch.allclose(got[f], ws[f], atol=3e-4, rtol=1e-4)
+            assert torch.allclose(got_s[f], ss[f], atol=1e-3, rtol=1e-4)
+        assert len(t.save(str(tmp_path / "sub"))) == 2
+    finally:
+        set_config(ps_wire_dtype="grad")
+        device.teardown(st)
+    single = ShardedEmbedding(fields, rows, dim, optimizer="adagrad", lr=0.05, device=torch.device("cuda", 0),
+                              expected_batch=batch)
+    single.load(str(tmp_path / "sub"))
+    again, _ = _dense_tables(single, fields, rows, dim)
+    for f in range(fields):
+        assert torch.equal(again[f], got[f])

@@ -75,6 +75,36 @@ def _slices_are_used(rank, size):
     assert tips.metrics()["ops_enqueued"] - before == len(b.slice_list)
 
 
+def _explicit_groups(rank, size):
+    """`groups` as the reference defines it: an integer cuts the parameters into that many allreduce groups, a list of
+    parameter lists fuses each inner list and leaves the other parameters alone; training is unchanged."""
+    import tips_b200 as tips
+    from tips_b200.models.mnist_cnn import synthetic_batch
+    model = _make(5)
+    names = dict(model.named_parameters())
+    opt = tips.DistributedOptimizer(torch.optim.SGD(model.parameters(), lr=0.01),
+                                    groups=[[names["conv1.weight"], names["conv1.bias"]], [names["fc2.weight"]]])
+    sizes = sorted(len(b.params) for b in opt._tips_buckets)
+    assert sizes == [1] * (len(names) - 2) + [2]
+    x, y = synthetic_batch(8, rank)
+    torch.nn.functional.cross_entropy(model(x), y).backward()
+    opt.step()
+    w = tips.allgather_object(model.fc2.weight.detach().sum().item())
+    model2 = _make(5)
+    opt2 = tips.DistributedOptimizer(torch.optim.SGD(model2.parameters(), lr=0.01), groups=3)
+    assert 3 <= len(opt2._tips_buckets) <= 4
+    torch.nn.functional.cross_entropy(model2(x), y).backward()
+    opt2.step()
+    assert torch.allclose(model2.fc2.weight, model.fc2.weight, atol=1e-7)
+    with pytest.raises(ValueError):
+        tips.DistributedOptimizer(torch.optim.SGD(model.parameters(), lr=0.01), groups=[[torch.nn.Parameter(torch.ones(1))]])
+    assert all(abs(v - w[0]) < 1e-6 for v in w)
+
+
+def test_explicit_allreduce_groups():
+    run_ranks(_explicit_groups, 2)
+
+
 def test_slice_bookkeeping():
     run_ranks(_slices_are_used, 2, env={"TIPS_FUSION_SLICE_BYTES": "65536"})
 

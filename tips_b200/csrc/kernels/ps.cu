@@ -86,8 +86,8 @@ struct alignas(8) PsCtl {
 };
 
 struct PsRank {
-  char* slab[kMaxRanks];            // every rank's table slab as mapped here
-  char* inbox[kMaxRanks];           // every rank's inbox as mapped here (null with one rank)
+  char* slab[kMaxRanks];            // every server's table slab as mapped here
+  char* inbox[kMaxRanks];           // every server's inbox as mapped here (null with one rank)
   char* acc;                        // local table: [slots] u64 keys, [slots][dim] fp32 sums
   uint32_t* ulist;                  // [2][slots]: list of distinct rows of the batch, then the apply list
   PsCtl* ctl;
@@ -98,7 +98,9 @@ struct PsRank {
   void* out;                        // pull: [batch, ld]
   int32_t* error;                   // local error word (table full, bad id, inbox full)
   int32_t rank;
-  int32_t nranks;
+  int32_t nranks;                   // ranks of the job: every one of them may pull and push (a worker)
+  int32_t nservers;                 // ranks that hold shards; slab[] and inbox[] are in server order
+  int32_t my_server;                // this rank's index among the servers, or -1 for a pure worker
 };
 struct PsLaunch {
   PsRank r[kMaxRanks];
@@ -159,7 +161,7 @@ template <typename OutT>
 __global__ void __launch_bounds__(256)
 PsPullKernel(PsLaunch args, PsMeta meta, int64_t batch, int64_t out_ld, int64_t out_col0) {
   const PsRank& pr = args.r[blockIdx.y];
-  const int n      = pr.nranks;
+  const int n      = pr.nservers;
   const int dim    = meta.dim;
   const int vecs   = dim / 4;
   const RowLanes L(dim);
@@ -185,7 +187,7 @@ PsPullKernel(PsLaunch args, PsMeta meta, int64_t batch, int64_t out_ld, int64_t 
     }
     const char* row = pr.slab[owner] + meta.field_off[f] + static_cast<uint64_t>(lrow) * dim * 4;
     for (int v = L.sublane; v < vecs; v += L.lpi) {
-      U4 q = owner == pr.rank ? *reinterpret_cast<const U4*>(row + v * 16) : LdSys(row + v * 16);
+      U4 q = owner == pr.my_server ? *reinterpret_cast<const U4*>(row + v * 16) : LdSys(row + v * 16);
       const float fv[4] = {__uint_as_float(q.x), __uint_as_float(q.y), __uint_as_float(q.z), __uint_as_float(q.w)};
       if (sizeof(OutT) == 4) {
         *reinterpret_cast<U4*>(dst + v * 4) = q;
@@ -272,7 +274,7 @@ constexpr int kRowsInFlight = 8;  // rows that a lane group loads before it stor
 __global__ void __launch_bounds__(256)
 PsIndexKernel(PsLaunch args, PsMeta meta, int64_t batch, uint64_t slots) {
   const PsRank& pr = args.r[blockIdx.y];
-  const int n      = pr.nranks;
+  const int n      = pr.nservers;  // placement is among the servers
   const int lane   = threadIdx.x & 31;
   const int64_t warp_global = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
   const int64_t nwarps      = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
@@ -339,7 +341,7 @@ PsFetchKernel(PsLaunch args, PsMeta meta, uint64_t slots) {
   __shared__ uint32_t s_slot[kChunk];
   __shared__ char* s_ptr[kChunk];
   const PsRank& pr = args.r[blockIdx.y];
-  const int n      = pr.nranks;
+  const int n      = pr.nservers;  // placement is among the servers
   const int dim    = meta.dim;
   unsigned long long* keys = reinterpret_cast<unsigned long long*>(pr.acc);
   OutT* cache              = reinterpret_cast<OutT*>(pr.cache);
@@ -358,7 +360,7 @@ PsFetchKernel(PsLaunch args, PsMeta meta, uint64_t slots) {
       int64_t lrow;
       PsPlace(f, KeyId(key), n, &owner, &lrow);
       row    = pr.slab[owner] + meta.field_off[f] + static_cast<uint64_t>(lrow) * dim * 4;
-      remote = owner != pr.rank;
+      remote = owner != pr.my_server;
     }
     s_slot[threadIdx.x] = slot;
     s_ptr[threadIdx.x]  = row;
@@ -421,7 +423,7 @@ __global__ void __launch_bounds__(256)
 PsScatterKernel(PsLaunch args, PsMeta meta, int64_t batch, int64_t grad_ld, int64_t grad_col0, uint64_t slots,
                 float grad_scale) {
   const PsRank& pr = args.r[blockIdx.y];
-  const int n      = pr.nranks;
+  const int n      = pr.nservers;  // placement is among the servers
   const int dim    = meta.dim;
   const int vecs   = dim / 4;
   const RowLanes L(dim);
@@ -528,15 +530,16 @@ PsSendKernel(PsLaunch args, PsMeta meta, uint64_t slots, uint64_t cap, int wire_
   __shared__ uint32_t s_cnt[kMaxRanks + 1], s_base[kMaxRanks + 1];
   __shared__ uint32_t* s_counter[kMaxRanks + 1];
   const PsRank& pr = args.r[blockIdx.y];
-  const int n      = pr.nranks;
+  const int n      = pr.nranks;    // senders: every rank of the job
+  const int ns     = pr.nservers;  // destinations: the ranks that hold shards
   const int dim    = meta.dim;
   unsigned long long* keys = reinterpret_cast<unsigned long long*>(pr.acc);
   float* sums_base         = reinterpret_cast<float*>(pr.acc + slots * 8);
   uint32_t* apply_list     = pr.ulist + slots;
   const int64_t total      = *reinterpret_cast<volatile uint32_t*>(&pr.ctl->ucount);
   const int64_t nchunks    = (total + kChunk - 1) / kChunk;
-  // destination d < n: the inbox of rank d; destination n: this rank's apply list
-  if (threadIdx.x <= n) s_counter[threadIdx.x] = threadIdx.x < n ? &pr.ctl->send_count[threadIdx.x] : &pr.ctl->acount;
+  // destination d < ns: the inbox of server d; destination ns: this rank's apply list
+  if (threadIdx.x <= ns) s_counter[threadIdx.x] = threadIdx.x < ns ? &pr.ctl->send_count[threadIdx.x] : &pr.ctl->acount;
   __syncthreads();
   for (int64_t chunk = blockIdx.x; chunk < nchunks; chunk += gridDim.x) {
     const int64_t mine = chunk * kChunk + threadIdx.x;
@@ -547,10 +550,10 @@ PsSendKernel(PsLaunch args, PsMeta meta, uint64_t slots, uint64_t cap, int wire_
       slot = pr.ulist[mine];
       key  = keys[slot];
       int64_t lrow;
-      PsPlace(KeyField(key), KeyId(key), n, &owner, &lrow);
+      PsPlace(KeyField(key), KeyId(key), ns, &owner, &lrow);
     }
-    const bool own     = owner == pr.rank;
-    const uint32_t pos = ReservePositions(own ? n : owner, n + 1, s_counter, s_cnt, s_base);
+    const bool own     = owner >= 0 && owner == pr.my_server;
+    const uint32_t pos = ReservePositions(own ? ns : owner, ns + 1, s_counter, s_cnt, s_base);
     char* dst = nullptr;
     if (own) {
       apply_list[pos] = slot;
@@ -594,7 +597,7 @@ PsSendKernel(PsLaunch args, PsMeta meta, uint64_t slots, uint64_t cap, int wire_
     __shared__ unsigned long long s_remote;
     if (threadIdx.x == 0) s_remote = 0;
     __syncthreads();
-    if (threadIdx.x < n && threadIdx.x != pr.rank) {
+    if (threadIdx.x < ns && threadIdx.x != pr.my_server) {
       const int o = threadIdx.x;
       uint32_t c  = atomicExch(&pr.ctl->send_count[o], 0u);
       if (c > cap) c = static_cast<uint32_t>(cap);
@@ -626,14 +629,14 @@ PsOwnerReduceKernel(PsLaunch args, PsMeta meta, uint64_t slots, uint64_t cap, in
   unsigned long long* keys = reinterpret_cast<unsigned long long*>(pr.acc);
   float* sums_base         = reinterpret_cast<float*>(pr.acc + slots * 8);
   uint32_t* apply_list     = pr.ulist + slots;
-  char* inbox              = pr.inbox[pr.rank];
+  char* inbox              = pr.inbox[pr.my_server < 0 ? 0 : pr.my_server];
   // exclusive prefix of the per-sender counts (written by the senders, published by the fence)
   uint32_t start[kMaxRanks + 1];
   start[0] = 0;
 #pragma unroll
   for (int s = 0; s < kMaxRanks; ++s) {
     uint32_t c = 0;
-    if (s < n && s != pr.rank) {
+    if (pr.my_server >= 0 && s < n && s != pr.rank) {
       asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(c) : "l"(reinterpret_cast<uint32_t*>(inbox) + s) : "memory");
       if (c > cap) c = static_cast<uint32_t>(cap);
     }
@@ -701,7 +704,7 @@ __global__ void __launch_bounds__(256)
 PsPushDirectKernel(PsLaunch args, PsMeta meta, int64_t batch, int64_t grad_ld, int64_t grad_col0, float grad_scale,
                    int rule, float lr, float eps) {
   const PsRank& pr = args.r[blockIdx.y];
-  const int n      = pr.nranks;
+  const int n      = pr.nservers;  // placement is among the servers
   const int dim    = meta.dim;
   const int vecs   = dim / 4;
   const RowLanes L(dim);
@@ -761,6 +764,7 @@ __global__ void __launch_bounds__(256)
 PsPushApplyKernel(PsLaunch args, PsMeta meta, uint64_t slots, int rule, float lr, float eps) {
   const PsRank& pr = args.r[blockIdx.y];
   const int n      = pr.nranks;
+  const int ns     = pr.nservers;
   const int dim    = meta.dim;
   const int vecs   = dim / 4;
   const RowLanes L(dim);
@@ -768,7 +772,7 @@ PsPushApplyKernel(PsLaunch args, PsMeta meta, uint64_t slots, int rule, float lr
   const int64_t nwarps      = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
   unsigned long long* keys  = reinterpret_cast<unsigned long long*>(pr.acc);
   float* sums_base          = reinterpret_cast<float*>(pr.acc + slots * 8);
-  char* slab                = pr.slab[pr.rank];
+  char* slab                = pr.slab[pr.my_server < 0 ? 0 : pr.my_server];
   // several ranks: the apply list that send and reduce built; one rank: the list of distinct rows of the batch
   const uint32_t* list      = n > 1 ? pr.ulist + slots : pr.ulist;
   uint32_t* count           = n > 1 ? &pr.ctl->acount : &pr.ctl->ucount;
@@ -781,7 +785,7 @@ PsPushApplyKernel(PsLaunch args, PsMeta meta, uint64_t slots, int rule, float lr
     const int f         = KeyField(key);
     int owner;
     int64_t lrow;
-    PsPlace(f, KeyId(key), n, &owner, &lrow);
+    PsPlace(f, KeyId(key), ns, &owner, &lrow);
     float* w    = reinterpret_cast<float*>(slab + meta.field_off[f]) + lrow * dim;
     float* st   = reinterpret_cast<float*>(slab + meta.state_off[f]) + lrow * dim;
     float* sums = sums_base + static_cast<uint64_t>(slot) * dim;
@@ -817,8 +821,8 @@ PsPushApplyKernel(PsLaunch args, PsMeta meta, uint64_t slots, int rule, float lr
       if (key == 0) continue;  // a row of this rank, already applied and emptied by the loop above
       int owner;
       int64_t lrow;
-      PsPlace(KeyField(key), KeyId(key), n, &owner, &lrow);
-      if (owner != pr.rank) keys[slot] = 0;
+      PsPlace(KeyField(key), KeyId(key), ns, &owner, &lrow);
+      if (owner != pr.my_server) keys[slot] = 0;
     }
   }
   if (LastBlockDone(pr.ctl)) {
@@ -1020,6 +1024,8 @@ struct PsState {
   uint32_t* item_slot[kMaxRanks];
   char* cache[kMaxRanks];
   int nlocal = 0;
+  int nservers = 0;
+  int server_rank[kMaxRanks];  // world rank of server j
   uint64_t slots = 0;
   uint64_t inbox_cap = 0;
   uint64_t item_cap = 0;       // items (sample, field) that item_slot can hold
@@ -1045,7 +1051,7 @@ int MakePsLaunch(PsLaunch* l, const int64_t* const* ids, const void* const* grad
   if (local != g_ps.nlocal) return SetError(-2, "ps: configured for another number of local ranks");
   for (int i = 0; i < local; ++i) {
     PsRank& r = l->r[i];
-    for (int p = 0; p < nranks; ++p) {
+    for (int p = 0; p < g_ps.nservers; ++p) {
       r.slab[p]  = g_ps.slab[p];
       r.inbox[p] = g_ps.inbox[p];
     }
@@ -1058,8 +1064,12 @@ int MakePsLaunch(PsLaunch* l, const int64_t* const* ids, const void* const* grad
     r.grads  = grads ? grads[i] : nullptr;
     r.out    = outs ? outs[i] : nullptr;
     r.error  = g_ps.error_dev;
-    r.rank   = emulated ? i : rank;
-    r.nranks = nranks;
+    r.rank      = emulated ? i : rank;
+    r.nranks    = nranks;
+    r.nservers  = g_ps.nservers;
+    r.my_server = -1;
+    for (int j = 0; j < g_ps.nservers; ++j)
+      if (g_ps.server_rank[j] == r.rank) r.my_server = j;
   }
   return local;
 }
@@ -1184,7 +1194,10 @@ uint64_t tipsk_ps_inbox_bytes(int nranks, uint64_t inbox_cap, int dim) {
 uint64_t tipsk_ps_ctl_bytes() { return sizeof(PsCtl); }
 
 /* Registers the buffers of the data path and the per-field layout.
- *   slabs, inboxes   one pointer per rank, as mapped in this process (inboxes may be null with one rank)
+ *   servers          world ranks that hold shards, ascending (null: every rank); rows are placed among them, every
+ *                    rank of the job may pull and push
+ *   slabs, inboxes   one pointer per SERVER, in the order of `servers`, as mapped in this process (inboxes may be
+ *                    null with one rank)
  *   accs, ulists, ctls, item_slots, caches   one pointer per LOCAL rank (one, or `nranks` when the ranks are
  *                    emulated on one GPU): accumulation table (tipsk_ps_acc_bytes), the two lists (2 * slots u32),
  *                    control words (tipsk_ps_ctl_bytes), slot per item (item_cap u32), row cache of the indexed
@@ -1193,8 +1206,14 @@ uint64_t tipsk_ps_ctl_bytes() { return sizeof(PsCtl); }
  *   slots            power of two; inbox_cap: rows one sender may send to one owner in a push, even. */
 int tipsk_ps_configure(void* const* slabs, void* const* inboxes, void* const* accs, void* const* ulists,
                        void* const* ctls, void* const* item_slots, void* const* caches, int nranks, int nlocal,
-                       const uint64_t* field_off, const uint64_t* state_off, const int64_t* rows_per_shard, int nfields,
-                       int dim, uint64_t slots, uint64_t inbox_cap, uint64_t item_cap) {
+                       const int32_t* servers, int nservers, const uint64_t* field_off, const uint64_t* state_off,
+                       const int64_t* rows_per_shard, int nfields, int dim, uint64_t slots, uint64_t inbox_cap,
+                       uint64_t item_cap) {
+  if (!servers) nservers = nranks;
+  TIPSK_REQUIRE(nservers >= 1 && nservers <= nranks && nranks <= kMaxRanks, "ps: between one server and all ranks");
+  for (int j = 0; servers && j < nservers; ++j)
+    TIPSK_REQUIRE(servers[j] >= 0 && servers[j] < nranks && (j == 0 || servers[j] > servers[j - 1]),
+                  "ps: server ranks must be ascending ranks of the job");
   TIPSK_REQUIRE(nfields >= 1 && nfields <= kMaxFields, "ps: 1..64 fields are supported");
   TIPSK_REQUIRE(dim >= 4 && dim % 4 == 0, "ps: the row dimension must be a multiple of 4");
   TIPSK_REQUIRE(slots >= 2 && (slots & (slots - 1)) == 0 && slots <= (1ull << 31), "ps: slots must be a power of two");
@@ -1211,9 +1230,11 @@ int tipsk_ps_configure(void* const* slabs, void* const* inboxes, void* const* ac
   }
   st.meta.nfields = nfields;
   st.meta.dim     = dim;
+  st.nservers = nservers;
+  for (int j = 0; j < kMaxRanks; ++j) st.server_rank[j] = j < nservers ? (servers ? servers[j] : j) : -1;
   for (int r = 0; r < kMaxRanks; ++r) {
-    st.slab[r]      = r < nranks ? static_cast<char*>(slabs[r]) : nullptr;
-    st.inbox[r]     = r < nranks && inboxes ? static_cast<char*>(inboxes[r]) : nullptr;
+    st.slab[r]      = r < nservers ? static_cast<char*>(slabs[r]) : nullptr;
+    st.inbox[r]     = r < nservers && inboxes ? static_cast<char*>(inboxes[r]) : nullptr;
     st.acc[r]       = r < nlocal && accs ? static_cast<char*>(accs[r]) : nullptr;
     st.ulist[r]     = r < nlocal && ulists ? static_cast<uint32_t*>(ulists[r]) : nullptr;
     st.ctl[r]       = r < nlocal && ctls ? static_cast<PsCtl*>(ctls[r]) : nullptr;

@@ -85,7 +85,27 @@ class _DistributedMixin:
         elif compression is Compression.bf16:
             wire = "bf16"
         self._tips_update_in_allreduce = False
+        # `groups` (tips/tensorflow/__init__.py:394-404): explicit grouping of the gradient allreduces.  An integer is
+        # the number of groups the parameters are cut into; a list of parameter lists puts every inner list into one
+        # group and leaves every other parameter in a group of its own.  A group is a fusion bucket here.
+        if groups is not None and not isinstance(groups, int):
+            groups = [list(g) for g in groups]
+            known = {id(p) for p in params}
+            flat_ids = [id(p) for g in groups for p in g]
+            if len(set(flat_ids)) != len(flat_ids) or not set(flat_ids) <= known:
+                raise ValueError("groups must hold parameters of this optimizer, each at most once")
+        if isinstance(groups, int) and groups < 0:
+            raise ValueError("groups must be a non-negative integer or a list of parameter lists")
+        total_bytes = sum(p.numel() * p.element_size() for p in params)
+        group_threshold = None
+        if isinstance(groups, int) and groups > 0:
+            group_threshold = max(1, -(-total_bytes // groups))
         if self._tips_fused:
+            if groups is not None and not isinstance(groups, int):
+                raise ValueError("explicit parameter lists in `groups` need a stock torch optimizer; a fused "
+                                 "optimizer takes an integer number of groups")
+            if group_threshold is not None and not self._built:
+                self._bucket_bytes = group_threshold
             self._wire_dtype = wire
             self._tips_buckets = [fs.bucket for fs in self.build(dev_state)]
             if fused_update is None:
@@ -96,15 +116,27 @@ class _DistributedMixin:
                 self._tips_update_in_allreduce = self.shard_for_fused_update(dev_state)
                 self._tips_fs_of = {id(fs.bucket): fs for fs in self._flat}
         else:
-            by_kind = {}
-            for p in params:
-                by_kind.setdefault((p.dtype, p.device), []).append(p)
             self._tips_buckets = []
-            for plist in by_kind.values():
-                for b in build_buckets(plist, None, wire, dev_state):
-                    b.index = len(self._tips_buckets)
-                    b.name = f"tips.bucket.{b.index}"
-                    self._tips_buckets.append(b)
+
+            def add(plist, threshold):
+                by_kind = {}
+                for p in plist:
+                    by_kind.setdefault((p.dtype, p.device), []).append(p)
+                for same in by_kind.values():
+                    for b in build_buckets(same, threshold, wire, dev_state):
+                        b.index = len(self._tips_buckets)
+                        b.name = f"tips.bucket.{b.index}"
+                        self._tips_buckets.append(b)
+
+            if groups is not None and not isinstance(groups, int):
+                grouped = {id(p) for g in groups for p in g}
+                for g in groups:
+                    add([p for p in g if p.requires_grad], 1 << 62)   # one bucket per list (per dtype and device)
+                for p in params:
+                    if id(p) not in grouped:
+                        add([p], 1 << 62)
+            else:
+                add(params, group_threshold)
         # Bucket names are the negotiation keys: unique per optimizer instance, identical across ranks as
         # long as every rank creates its optimizers in the same order.
         global _optimizer_counter

@@ -51,8 +51,13 @@ class ShardedEmbedding:
 
     def __init__(self, num_fields: int, rows_per_table: int, dim: int, optimizer: str = "adagrad", lr: float = 0.01,
                  eps: float = 1e-8, init_scale: float = 0.0, seed: int = 0, slots: Optional[int] = None,
-                 expected_batch: int = 8192, device=None, sync: bool = True):
-        """`sync=True`: a push is the exact synchronous update (gradients of all ranks summed per row, then the
+                 expected_batch: int = 8192, device=None, sync: bool = True, servers=None):
+        """`servers`: the ranks that hold shards (default: every rank).  Every rank of the job may pull and push (a
+        worker); only the listed ranks serve rows: the reference's split into PS_SERVER and PS_WORKER node sets, where
+        a rank may be either or both (tips/core/ps/route.h:22-134).  On this transport every rank still maps a
+        window of the slab's size, because the peer-mapped allocation is symmetric; only the servers' windows hold rows.
+
+        `sync=True`: a push is the exact synchronous update (gradients of all ranks summed per row, then the
         optimizer applied once), with cross-rank fences around it.  `sync=False`: the reference's consistency model:
         pushes are applied to the owner's rows as they arrive (atomics, no fences), pulls may read rows mid-update."""
         if optimizer not in _RULES:
@@ -68,7 +73,11 @@ class ShardedEmbedding:
             raise ValueError("asynchronous pushes support the sgd and adagrad rules")
         self.rank, self.size, self.emulated, st = _world()
         self.device = device or (st.device if st is not None else torch.device("cuda", torch.cuda.current_device()))
-        n = self.size
+        self.servers = sorted(set(range(self.size) if servers is None else servers))
+        if not self.servers or self.servers[0] < 0 or self.servers[-1] >= self.size:
+            raise ValueError("servers must be ranks of the job")
+        self.nservers = len(self.servers)
+        n = self.nservers   # rows are placed among the servers
         self.rows_per_shard = (rows_per_table + n - 1) // n
         field_bytes = self.rows_per_shard * dim * 4
         self.has_state = self.rule == 1
@@ -86,16 +95,18 @@ class ShardedEmbedding:
         self.item_cap = expected_batch * num_fields   # items (sample, field) of a batch that an indexed pull can hold
         lib = base.K()
         self._alloc_bytes = (slab_bytes, int(lib.tipsk_ps_acc_bytes(slots, dim)),
-                             int(lib.tipsk_ps_inbox_bytes(n, self.inbox_cap, dim)) if n > 1 else 0,
+                             int(lib.tipsk_ps_inbox_bytes(self.size, self.inbox_cap, dim)) if self.size > 1 else 0,
                              int(lib.tipsk_ps_ctl_bytes()))
         self._allocate(st)
-        local = range(n) if self.emulated else [self.rank]
+        local = range(self.size) if self.emulated else [self.rank]
         for r in local:
+            if r not in self.servers:
+                continue
             slab = self.slabs[r] if self.emulated else self.slabs[0]
             for f in range(num_fields):
                 w = slab[self.field_off[f]:self.field_off[f] + field_bytes].view(torch.float32)
-                base.check(lib.tipsk_table_init(w.data_ptr(), self.rows_per_shard, dim, f, r, n, rows_per_table,
-                                                seed, float(init_scale), base.stream()), "table_init")
+                base.check(lib.tipsk_table_init(w.data_ptr(), self.rows_per_shard, dim, f, self.servers.index(r), n,
+                                                rows_per_table, seed, float(init_scale), base.stream()), "table_init")
             if self.has_state:
                 slab[num_fields * field_bytes:].zero_()
         torch.cuda.synchronize()
@@ -143,10 +154,12 @@ class ShardedEmbedding:
         global _active
         lib = base.K()
         n = self.size
-        base.check(lib.tipsk_ps_configure(base.ptr_array(self._slab_ptrs), base.ptr_array(self._inbox_ptrs),
+        srv = (ctypes.c_int32 * self.nservers)(*self.servers)
+        base.check(lib.tipsk_ps_configure(base.ptr_array([self._slab_ptrs[r] for r in self.servers]),
+                                          base.ptr_array([self._inbox_ptrs[r] for r in self.servers]),
                                           base.ptr_array(self.accs), base.ptr_array(self.ulists),
                                           base.ptr_array(self.ctls), base.ptr_array(self.item_slots),
-                                          base.ptr_array(self.caches), n, len(self.accs),
+                                          base.ptr_array(self.caches), n, len(self.accs), srv, self.nservers,
                                           base.u64_array(self.field_off), base.u64_array(self.state_off),
                                           base.i64_array([self.rows_per_shard] * self.num_fields), self.num_fields,
                                           self.dim, self.slots, self.inbox_cap, self.item_cap), "ps_configure")
@@ -255,16 +268,18 @@ class ShardedEmbedding:
         return slab[off:off + nbytes].view(torch.float32).view(self.rows_per_shard, self.dim)
 
     def place(self, ids: torch.Tensor, field: int, world: Optional[int] = None):
-        """(owner rank, local row) of the rows `ids` of `field`: the rule of csrc/kernels/ps_placement.h."""
-        n = self.size if world is None else world
+        """(index of the owning server, local row) of the rows `ids` of `field`: the rule of
+        csrc/kernels/ps_placement.h among `world` servers (default: this table's)."""
+        n = self.nservers if world is None else world
         lrow = ids // n
         rot = ((((lrow & 0xFFFFFFFF) * 0x9E3779B1) & 0xFFFFFFFF) >> 16) + field
         return (ids % n + rot) % n, lrow
 
     def global_ids(self, field: int, rank: int, world: Optional[int] = None, rows_per_shard: Optional[int] = None,
                    device=None) -> torch.Tensor:
-        """Global row id held at every local row of `rank`'s shard of `field` (ids >= rows are padding)."""
-        n = self.size if world is None else world
+        """Global row id held at every local row of the shard of `field` on server number `rank` (ids >= rows are
+        padding)."""
+        n = self.nservers if world is None else world
         lrow = torch.arange(self.rows_per_shard if rows_per_shard is None else rows_per_shard, dtype=torch.int64,
                             device=device)
         rot = ((((lrow & 0xFFFFFFFF) * 0x9E3779B1) & 0xFFFFFFFF) >> 16) + field
@@ -274,9 +289,9 @@ class ShardedEmbedding:
         """The whole [rows, dim] table of `field` (or its Adagrad state) assembled from the shards this process
         can see: all of them when the ranks are emulated or there is one rank (tests, small tables)."""
         assert self.emulated or self.size == 1
-        out = torch.zeros(self.rows_per_shard * self.size, self.dim, device=self.device)
-        for r in range(self.size):
-            out[self.global_ids(field, r, device=self.device)] = self.local_shard(field, r, state=state)
+        out = torch.zeros(self.rows_per_shard * self.nservers, self.dim, device=self.device)
+        for j, r in enumerate(self.servers):
+            out[self.global_ids(field, j, device=self.device)] = self.local_shard(field, r, state=state)
         return out[:self.rows].clone()
 
     # ------------------------------------------------------------------ dumps
@@ -286,7 +301,9 @@ class ShardedEmbedding:
     # be read back under a different number of ranks, and small tables can also be written in that text format.
 
     def _ranks_here(self):
-        return range(self.size) if self.emulated else [self.rank]
+        """World ranks whose shards this process holds (servers only)."""
+        here = range(self.size) if self.emulated else [self.rank]
+        return [r for r in here if r in self.servers]
 
     def save(self, prefix: str) -> list:
         """Write `<prefix>.rank<r>.bin` for the shard(s) held by this process; returns the paths."""
@@ -296,7 +313,8 @@ class ShardedEmbedding:
         paths = []
         for r in self._ranks_here():
             path = f"{prefix}.rank{r}.bin"
-            header = {"format": "tips_b200.ps.v2", "rank": r, "world": self.size, "fields": self.num_fields,
+            header = {"format": "tips_b200.ps.v2", "rank": self.servers.index(r), "world": self.nservers,
+                      "fields": self.num_fields,
                       "rows": self.rows, "rows_per_shard": self.rows_per_shard, "dim": self.dim,
                       "state": bool(self.has_state)}
             with open(path, "wb") as f:
@@ -341,7 +359,7 @@ class ShardedEmbedding:
                             valid = ids < self.rows
                             owner, lrow = self.place(ids, fld)
                             for r in self._ranks_here():
-                                mine = valid & (owner == r)
+                                mine = valid & (owner == self.servers.index(r))
                                 if not bool(mine.any()):
                                     continue
                                 rows = torch.from_numpy(buf.copy())[mine].to(self.device)
@@ -358,7 +376,7 @@ class ShardedEmbedding:
         with open(path, "w") as f:
             for r in self._ranks_here():
                 shard = self.local_shard(field, r).cpu()
-                keys = self.global_ids(field, r).tolist()
+                keys = self.global_ids(field, self.servers.index(r)).tolist()
                 for lrow in range(self.rows_per_shard):
                     if keys[lrow] >= self.rows:
                         continue

@@ -152,6 +152,13 @@ def test_push_with_mostly_duplicate_ids_emulated(ranks, indexed, wire):
         st.check_status()
         assert total_distinct < 0.6 * 3 * ranks * batch * fields
         got, got_s = _dense_tables(t, fields, rows, dim)
+        # bf16 pulls read the owners' bf16 copy of the rows, which the apply pass keeps current
+        assert t.shadow_base > 0
+        outs16 = t.pull(ids, dtype=torch.bfloat16, index=True)
+        for r in range(ranks):
+            want16 = torch.cat([got[f][ids[r][:, f]] for f in range(fields)], dim=1).to(torch.bfloat16)
+            assert torch.equal(outs16[r], want16)
+        t.pull(ids, dtype=torch.float32)   # a plain pull drops the unused index
         for f in range(fields):
             assert close(got[f], ws[f])
             assert close(got_s[f], ss[f], atol=1e-3) if wire == "fp32" else torch.allclose(got_s[f], ss[f], atol=0.5, rtol=5e-2)

@@ -39,6 +39,8 @@ class Config:
     ps_wire_dtype: str = "grad"              # grad: rows of a push cross NVLink in the dtype of the pushed gradients
                                              # (a rank's per-row sum is rounded to bf16 once when they are bf16);
                                              # fp32: always fp32
+    ps_bf16_shadow: bool = True              # tables over several ranks keep a bf16 copy of their rows that bf16
+                                             # pulls read (half the bytes over NVLink, a quarter more table memory)
     # Observability
     log_level: str = "WARNING"
     timeline_path: str = ""

@@ -70,7 +70,14 @@ struct PsMeta {
   int64_t rows_per_shard[kMaxFields];
   int32_t nfields;
   int32_t dim;                      // fp32 elements per row, multiple of 4
+  // Optional bf16 copy of the rows that the owner keeps current (0: none): field f starts at
+  // shadow_base + f * rows_per_shard[f] * dim * 2.  Pulls into bf16 read it, which halves their bytes on NVLink.
+  uint64_t shadow_base;
 };
+
+__host__ __device__ __forceinline__ uint64_t ShadowOffset(const PsMeta& m, int f, int64_t lrow) {
+  return m.shadow_base + (static_cast<uint64_t>(f) * m.rows_per_shard[f] + static_cast<uint64_t>(lrow)) * m.dim * 2;
+}
 
 // Per-rank control words in device memory; all zero between steps.
 struct alignas(8) PsCtl {
@@ -345,6 +352,7 @@ PsFetchKernel(PsLaunch args, PsMeta meta, uint64_t slots) {
   const int dim    = meta.dim;
   unsigned long long* keys = reinterpret_cast<unsigned long long*>(pr.acc);
   OutT* cache              = reinterpret_cast<OutT*>(pr.cache);
+  const bool shadow        = sizeof(OutT) == 2 && meta.shadow_base != 0;
   const int64_t total      = *reinterpret_cast<volatile uint32_t*>(&pr.ctl->ucount);
   const int64_t nchunks    = (total + kChunk - 1) / kChunk;
   for (int64_t chunk = blockIdx.x; chunk < nchunks; chunk += gridDim.x) {
@@ -359,7 +367,8 @@ PsFetchKernel(PsLaunch args, PsMeta meta, uint64_t slots) {
       int owner;
       int64_t lrow;
       PsPlace(f, KeyId(key), n, &owner, &lrow);
-      row    = pr.slab[owner] + meta.field_off[f] + static_cast<uint64_t>(lrow) * dim * 4;
+      row    = shadow ? pr.slab[owner] + ShadowOffset(meta, f, lrow)
+                      : pr.slab[owner] + meta.field_off[f] + static_cast<uint64_t>(lrow) * dim * 4;
       remote = owner != pr.my_server;
     }
     s_slot[threadIdx.x] = slot;
@@ -367,11 +376,19 @@ PsFetchKernel(PsLaunch args, PsMeta meta, uint64_t slots) {
     const int nremote   = __syncthreads_count(remote);
     if (threadIdx.x == 0 && nremote) atomicAdd(&pr.ctl->fetched_remote, static_cast<unsigned long long>(nremote));
     MoveRows(
-        s_slot, s_ptr, dim, [](char* p, uint32_t, int v) { return LdSysFree(p + v * 16); },
+        s_slot, s_ptr, dim,
+        [&](char* p, uint32_t, int v) {
+          if (!shadow) return LdSysFree(p + v * 16);
+          U4 q{0, 0, 0, 0};  // four bf16 values of the owner's bf16 copy: 8 bytes per lane
+          asm("ld.relaxed.sys.global.v2.u32 {%0,%1}, [%2];" : "=r"(q.x), "=r"(q.y) : "l"(p + v * 8));
+          return q;
+        },
         [&](char*, uint32_t sl, int v, const U4& q) {
           OutT* dst = cache + static_cast<uint64_t>(sl) * dim + v * 4;
           if (sizeof(OutT) == 4) {
             *reinterpret_cast<U4*>(dst) = q;
+          } else if (shadow) {
+            *reinterpret_cast<uint2*>(dst) = make_uint2(q.x, q.y);
           } else {
             OutT o[4] = {FromFloat<OutT>(__uint_as_float(q.x)), FromFloat<OutT>(__uint_as_float(q.y)),
                          FromFloat<OutT>(__uint_as_float(q.z)), FromFloat<OutT>(__uint_as_float(q.w))};
@@ -807,6 +824,11 @@ PsPushApplyKernel(PsLaunch args, PsMeta meta, uint64_t slots, int rule, float lr
       }
       *reinterpret_cast<float4*>(w + v * 4)    = wv;
       *reinterpret_cast<float4*>(sums + v * 4) = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (meta.shadow_base) {
+        const __nv_bfloat162 lo = __floats2bfloat162_rn(wv.x, wv.y), hi = __floats2bfloat162_rn(wv.z, wv.w);
+        *reinterpret_cast<uint2*>(slab + ShadowOffset(meta, f, lrow) + v * 8) =
+            make_uint2(*reinterpret_cast<const uint32_t*>(&lo), *reinterpret_cast<const uint32_t*>(&hi));
+      }
     }
     __syncwarp(L.group_mask());
     if (L.sublane == 0) keys[slot] = 0;
@@ -1203,12 +1225,14 @@ uint64_t tipsk_ps_ctl_bytes() { return sizeof(PsCtl); }
  *                    control words (tipsk_ps_ctl_bytes), slot per item (item_cap u32), row cache of the indexed
  *                    pull (slots * dim * 4 bytes); the first three must be zero before the first call; item_slots
  *                    and caches may be null (no indexed pull)
- *   slots            power of two; inbox_cap: rows one sender may send to one owner in a push, even. */
+ *   slots            power of two; inbox_cap: rows one sender may send to one owner in a push, even
+ *   shadow_base      byte offset inside every slab of a bf16 copy of the rows (fields in order, rows_per_shard * dim
+ *                    bf16 each) that the apply pass keeps current and bf16 pulls read; 0: none. */
 int tipsk_ps_configure(void* const* slabs, void* const* inboxes, void* const* accs, void* const* ulists,
                        void* const* ctls, void* const* item_slots, void* const* caches, int nranks, int nlocal,
                        const int32_t* servers, int nservers, const uint64_t* field_off, const uint64_t* state_off,
                        const int64_t* rows_per_shard, int nfields, int dim, uint64_t slots, uint64_t inbox_cap,
-                       uint64_t item_cap) {
+                       uint64_t item_cap, uint64_t shadow_base) {
   if (!servers) nservers = nranks;
   TIPSK_REQUIRE(nservers >= 1 && nservers <= nranks && nranks <= kMaxRanks, "ps: between one server and all ranks");
   for (int j = 0; servers && j < nservers; ++j)
@@ -1228,8 +1252,9 @@ int tipsk_ps_configure(void* const* slabs, void* const* inboxes, void* const* ac
     st.meta.state_off[f]      = state_off ? state_off[f] : 0;
     st.meta.rows_per_shard[f] = rows_per_shard[f];
   }
-  st.meta.nfields = nfields;
-  st.meta.dim     = dim;
+  st.meta.nfields     = nfields;
+  st.meta.dim         = dim;
+  st.meta.shadow_base = shadow_base;
   st.nservers = nservers;
   for (int j = 0; j < kMaxRanks; ++j) st.server_rank[j] = j < nservers ? (servers ? servers[j] : j) : -1;
   for (int r = 0; r < kMaxRanks; ++r) {

@@ -166,7 +166,7 @@ int tipsk_ps_configure(void* const* host_slabs, void* const* host_inboxes, void*
                        void* const* host_caches, int nranks, int nlocal, const int32_t* host_servers, int nservers,
                        const uint64_t* host_field_off, const uint64_t* host_state_off,
                        const int64_t* host_rows_per_shard, int nfields, int dim, uint64_t slots, uint64_t inbox_cap,
-                       uint64_t item_cap);
+                       uint64_t item_cap, uint64_t shadow_base);
 int tipsk_ps_traffic(uint64_t* host_out3);
 int tipsk_ps_wire_follows_grads(int follow);
 int tipsk_ps_phase_timing(int enable);

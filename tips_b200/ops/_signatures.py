@@ -73,7 +73,7 @@ _PROTOS = {
     "tipsk_ps_inbox_bytes": (U, [I, U, I]),
     "tipsk_ps_ctl_bytes": (U, []),
     "tipsk_ps_configure": (I, [PP, PP, PP, PP, PP, PP, PP, I, I, POINTER(c_int32), I, POINTER(U), POINTER(U), POINTER(L),
-                               I, I, U, U, U]),
+                               I, I, U, U, U, U]),
     "tipsk_ps_traffic": (I, [POINTER(U)]),
     "tipsk_ps_wire_follows_grads": (I, [I]),
     "tipsk_ps_phase_timing": (I, [I]),

@@ -84,6 +84,12 @@ class ShardedEmbedding:
         self.field_off = [f * field_bytes for f in range(num_fields)]
         self.state_off = [(num_fields + f) * field_bytes if self.has_state else 0 for f in range(num_fields)]
         slab_bytes = field_bytes * num_fields * (2 if self.has_state else 1)
+        # bf16 copy of the rows, kept current by the owner's apply pass and read by bf16 pulls: only where rows
+        # cross NVLink (several ranks) and only with synchronous pushes (asynchronous ones update rows in place)
+        from ..config import get_config
+        self.shadow_base = slab_bytes if (self.size > 1 and self.sync and get_config().ps_bf16_shadow) else 0
+        if self.shadow_base:
+            slab_bytes += (field_bytes // 2) * num_fields
         if slots is None:
             slots = 1
             while slots < 2 * expected_batch * num_fields:
@@ -108,7 +114,8 @@ class ShardedEmbedding:
                 base.check(lib.tipsk_table_init(w.data_ptr(), self.rows_per_shard, dim, f, self.servers.index(r), n,
                                                 rows_per_table, seed, float(init_scale), base.stream()), "table_init")
             if self.has_state:
-                slab[num_fields * field_bytes:].zero_()
+                slab[num_fields * field_bytes:2 * num_fields * field_bytes].zero_()
+        self.refresh_shadow()
         torch.cuda.synchronize()
         self._sync_ranks()
         self._configure()
@@ -162,7 +169,8 @@ class ShardedEmbedding:
                                           base.ptr_array(self.caches), n, len(self.accs), srv, self.nservers,
                                           base.u64_array(self.field_off), base.u64_array(self.state_off),
                                           base.i64_array([self.rows_per_shard] * self.num_fields), self.num_fields,
-                                          self.dim, self.slots, self.inbox_cap, self.item_cap), "ps_configure")
+                                          self.dim, self.slots, self.inbox_cap, self.item_cap, self.shadow_base),
+                   "ps_configure")
         from ..config import get_config
         lib.tipsk_ps_wire_follows_grads(0 if get_config().ps_wire_dtype == "fp32" else 1)
         _active = self
@@ -267,6 +275,18 @@ class ShardedEmbedding:
         nbytes = self.rows_per_shard * self.dim * 4
         return slab[off:off + nbytes].view(torch.float32).view(self.rows_per_shard, self.dim)
 
+    def refresh_shadow(self) -> None:
+        """Rebuild the bf16 copy of the rows from the fp32 rows (after rows were written from outside the push
+        path: initialisation, a loaded dump, a direct edit of `local_shard`)."""
+        if not self.shadow_base:
+            return
+        half = self.rows_per_shard * self.dim * 2
+        for r in self._ranks_here():
+            slab = self.slabs[r if self.emulated else 0]
+            for f in range(self.num_fields):
+                dst = slab[self.shadow_base + f * half:self.shadow_base + (f + 1) * half].view(torch.bfloat16)
+                dst.copy_(self.local_shard(f, r).reshape(-1))
+
     def place(self, ids: torch.Tensor, field: int, world: Optional[int] = None):
         """(index of the owning server, local row) of the rows `ids` of `field`: the rule of
         csrc/kernels/ps_placement.h among `world` servers (default: this table's)."""
@@ -367,6 +387,7 @@ class ShardedEmbedding:
                                 dst[lrow[mine].to(self.device)] = rows
         if seen_world is None:
             raise ValueError("empty dump")
+        self.refresh_shadow()
         torch.cuda.synchronize()
         self._sync_ranks()
 

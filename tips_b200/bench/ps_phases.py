@@ -114,7 +114,11 @@ def main(argv=None):
                           [1e3 * v / it for v in pacc])
     tot = _sum_over_ranks([sent, remote, applied, distinct, fetched])
     if rank == 0:
-        row_bytes = a.dim * 4 + 8
+        # bytes per row on the wire: pushed rows travel in the gradients' dtype (bf16 here) unless the wire is set
+        # to fp32, plus the 8-byte key; pulled rows are read from the owner's bf16 copy when there is one
+        from tips_b200.config import get_config
+        row_bytes = a.dim * (4 if get_config().ps_wire_dtype == "fp32" else 2) + 8
+        pull_row_bytes = a.dim * (2 if (table.shadow_base and not a.plain) else 4)
         items = a.batch * a.fields
         res = {"n_gpus": 1 if em else n, "emulated_ranks": em, "rows_per_table": a.rows, "batch_per_gpu": a.batch, "fields": a.fields, "dim": a.dim,
                "iters": it, "indexed": not a.plain,
@@ -127,9 +131,9 @@ def main(argv=None):
                    "rows pulled over NVLink": round(tot[4] / it / n) if not a.plain else round(items * (n - 1) / n),
                    "rows pushed over NVLink": round(tot[1] / it / n),
                    "rows applied by the owner": round(tot[2] / it / n),
-                   "NVLink bytes (pull)": round((tot[4] / it / n if not a.plain else items * (n - 1) / n) * a.dim * 4),
+                   "NVLink bytes (pull)": round((tot[4] / it / n if not a.plain else items * (n - 1) / n) * pull_row_bytes),
                    "NVLink bytes (push)": round(tot[1] / it / n * row_bytes),
-                   "bytes if every item were sent": round(items * row_bytes * (n - 1) / n)}}
+                   "bytes if every item were sent as fp32": round(items * (a.dim * 4 + 8) * (n - 1) / n)}}
         line = json.dumps(res)
         print(line)
         if a.out:

@@ -131,8 +131,9 @@ def main():
             r = workloads.run_resnet50_floor(args.batch, args.steps, args.warmup)
             result["impl"] = "floor (cuDNN BN + torch SGD + NCCL DDP)"
         else:
-            r = workloads.run_resnet50(args.batch, args.steps, args.warmup,
-                                       None if args.fused_update is None else bool(args.fused_update))
+            # several ranks: the SGD step runs inside the kernel that reduces the gradient bucket unless told otherwise
+            fused = (size > 1) if args.fused_update is None else bool(args.fused_update)
+            r = workloads.run_resnet50(args.batch, args.steps, args.warmup, fused)
         launches += r["gpu_launches"]
         result.update({
             "metric": "resnet50_train_images_per_sec", "value": r["value"], "unit": "images/s",

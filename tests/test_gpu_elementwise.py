@@ -323,3 +323,28 @@ def test_global_average_pool(dtype, shape):
     tol = 1e-5 if dtype == torch.float32 else 2e-2
     assert y.shape == yr.shape and torch.allclose(y.float(), yr, atol=tol, rtol=tol)
     assert torch.allclose(x.grad.float(), xr.grad, atol=tol, rtol=tol)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_embedding_sum(dtype):
+    """embed_sum against torch indexing in fp32: values, and the gradients of the token table (duplicate ids),
+    the position table (longer than the sequence) and the type row."""
+    from tips_b200.ops.pointwise import embed_sum
+    torch.manual_seed(2)
+    dev = _dev()
+    vocab, seq, hidden, batch = 300, 24, 64, 5
+    tok = torch.randn(vocab, hidden, device=dev).to(dtype).requires_grad_()
+    pos = torch.randn(seq + 8, hidden, device=dev).to(dtype).requires_grad_()
+    typ = torch.randn(2, hidden, device=dev).to(dtype).requires_grad_()
+    ids = torch.randint(0, 40, (batch, seq), device=dev)          # many duplicates
+    x = embed_sum(ids, tok, pos, typ[0])
+    dx = torch.randn_like(x)
+    x.backward(dx)
+    tr, pr, yr = (t.detach().float().requires_grad_() for t in (tok, pos, typ))
+    xr = tr[ids] + pr[:seq][None] + yr[0]
+    xr.backward(dx.float())
+    tol = 1e-5 if dtype == torch.float32 else 6e-2
+    assert torch.allclose(x.float(), xr, atol=tol, rtol=tol)
+    assert torch.allclose(tok.grad.float(), tr.grad, atol=tol * 4, rtol=tol)
+    assert torch.allclose(pos.grad.float(), pr.grad, atol=tol, rtol=tol)
+    assert torch.allclose(typ.grad.float(), yr.grad, atol=tol * 8, rtol=tol)

@@ -240,6 +240,106 @@ DotSigmoidBceBwdKernel(const T* __restrict__ x, const T* __restrict__ w, const f
   }
 }
 
+// Input embedding of a transformer encoder: x[t, :] = tok[ids[t], :] + pos[t mod seq, :] + typ[:], one warp per
+// token, 16-byte vectors.  Backward: the token-table gradient is a scatter-add of the rows of dx (packed bf16x2 /
+// fp32 atomics into a zeroed table-sized buffer; a token id repeats a few times per batch at most), the position
+// gradient sums dx over the batch in fp32 (one thread per (position, 8 columns), no atomics), the type gradient
+// is the column sum of the position gradient.
+template <typename T>
+__global__ void __launch_bounds__(256)
+EmbedSumFwdKernel(const int64_t* __restrict__ ids, const T* __restrict__ tok, const T* __restrict__ pos,
+                  const T* __restrict__ typ, T* __restrict__ x, int64_t tokens, int seq, int hidden, int64_t vocab) {
+  constexpr int N = 16 / sizeof(T);
+  const int lane = threadIdx.x & 31;
+  const int64_t warp  = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int64_t nwarp = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
+  for (int64_t t = warp; t < tokens; t += nwarp) {
+    int64_t id = ids[t];
+    if (id < 0 || id >= vocab) id = 0;
+    const T* a = tok + id * hidden;
+    const T* b = pos + static_cast<int64_t>(t % seq) * hidden;
+    for (int c = lane * N; c < hidden; c += 32 * N) {
+      const Vec16<T> va = LoadVec(a + c), vb = LoadVec(b + c), vc = LoadVec(typ + c);
+      Vec16<T> o;
+#pragma unroll
+      for (int j = 0; j < N; ++j) o.v[j] = FromFloat<T>(ToFloat<T>(va.v[j]) + ToFloat<T>(vb.v[j]) + ToFloat<T>(vc.v[j]));
+      StoreVec(x + t * hidden + c, o);
+    }
+  }
+}
+
+template <typename T>
+__device__ __forceinline__ void AtomicAddPair(T* addr, T a, T b);
+template <>
+__device__ __forceinline__ void AtomicAddPair<float>(float* addr, float a, float b) {
+  atomicAdd(addr, a);
+  atomicAdd(addr + 1, b);
+}
+template <>
+__device__ __forceinline__ void AtomicAddPair<__nv_bfloat16>(__nv_bfloat16* addr, __nv_bfloat16 a, __nv_bfloat16 b) {
+  atomicAdd(reinterpret_cast<__nv_bfloat162*>(addr), __halves2bfloat162(a, b));
+}
+template <>
+__device__ __forceinline__ void AtomicAddPair<__half>(__half* addr, __half a, __half b) {
+  atomicAdd(reinterpret_cast<__half2*>(addr), __halves2half2(a, b));
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+EmbedTokBwdKernel(const int64_t* __restrict__ ids, const T* __restrict__ dx, T* __restrict__ dtok, int64_t tokens,
+                  int hidden, int64_t vocab) {
+  constexpr int N = 16 / sizeof(T);
+  const int lane = threadIdx.x & 31;
+  const int64_t warp  = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int64_t nwarp = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
+  for (int64_t t = warp; t < tokens; t += nwarp) {
+    const int64_t id = ids[t];
+    if (id < 0 || id >= vocab) continue;
+    T* row = dtok + id * hidden;
+    for (int c = lane * N; c < hidden; c += 32 * N) {
+      const Vec16<T> g = LoadVec(dx + t * hidden + c);
+#pragma unroll
+      for (int j = 0; j < N; j += 2) AtomicAddPair<T>(row + c + j, g.v[j], g.v[j + 1]);
+    }
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+EmbedPosBwdKernel(const T* __restrict__ dx, T* __restrict__ dpos, int64_t batch, int seq, int hidden) {
+  constexpr int N = 16 / sizeof(T);
+  const int cv = hidden / N;
+  const int64_t total = static_cast<int64_t>(seq) * cv;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int c = static_cast<int>(i % cv) * N;
+    const int s = static_cast<int>(i / cv);
+    float acc[N];
+#pragma unroll
+    for (int j = 0; j < N; ++j) acc[j] = 0.f;
+    for (int64_t b = 0; b < batch; ++b) {
+      const Vec16<T> g = LoadVec(dx + (b * seq + s) * hidden + c);
+#pragma unroll
+      for (int j = 0; j < N; ++j) acc[j] += ToFloat<T>(g.v[j]);
+    }
+    Vec16<T> o;
+#pragma unroll
+    for (int j = 0; j < N; ++j) o.v[j] = FromFloat<T>(acc[j]);
+    StoreVec(dpos + static_cast<int64_t>(s) * hidden + c, o);
+  }
+}
+
+// dtyp[c] = sum over the positions of dpos[s, c] (fp32 accumulation), one thread per column.
+template <typename T>
+__global__ void __launch_bounds__(256)
+EmbedTypBwdKernel(const T* __restrict__ dpos, T* __restrict__ dtyp, int seq, int hidden) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= hidden) return;
+  float acc = 0.f;
+  for (int s = 0; s < seq; ++s) acc += ToFloat<T>(dpos[static_cast<int64_t>(s) * hidden + c]);
+  dtyp[c] = FromFloat<T>(acc);
+}
+
 __device__ __forceinline__ float BlockReduce(float v, bool is_max, float* scratch) {
   v = is_max ? WarpMax(v) : WarpSum(v);
   __syncthreads();
@@ -325,8 +425,10 @@ int tipsk_bias_act_bwd(const void* dy, const void* x, const void* bias, void* dx
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (dbias) TIPSK_CUDA(cudaMemsetAsync(dbias, 0, sizeof(float) * cols, s));
   const int col_tiles = CeilDiv(cols / n, 32);
-  int parts = CeilDiv(NumSMs() * 2, col_tiles);  // every partition ends in one atomic per column
-  int maxp  = CeilDiv(rows, 8 * 4);
+  // about four blocks per SM, but at least 8 row iterations per thread: every partition ends in one atomic per
+  // column, and a short tensor cut into hundreds of partitions spends its time in those
+  int parts = CeilDiv(NumSMs() * 4, col_tiles);
+  int maxp  = CeilDiv(rows, 8 * 8);
   if (parts > maxp) parts = maxp;
   if (parts < 1) parts = 1;
   dim3 grid(col_tiles, parts), block(32, 8);
@@ -391,6 +493,45 @@ int tipsk_dot_sigmoid_bce_bwd(const void* x, const void* w, const float* dz, con
   EPI_DISPATCH(dtype, {
     DotSigmoidBceBwdKernel<T><<<blocks, 256, 0, s>>>(static_cast<const T*>(x), static_cast<const T*>(w), dz, dloss,
                                                      static_cast<T*>(dx), dw, db, rows, k, ldx, rpb);
+  });
+  TIPSK_LAUNCH_CHECK();
+  return 0;
+}
+
+/* x[t] = tok[ids[t]] + pos[t mod seq] + typ for t < tokens (ids laid out [batch, seq]); hidden a multiple of 16
+ * bytes; ids outside [0, vocab) read row 0 and get no gradient. */
+int tipsk_embed_sum_fwd(const int64_t* ids, const void* tok, const void* pos, const void* typ, void* x, int64_t tokens,
+                        int seq, int hidden, int64_t vocab, int dtype, void* stream) {
+  if (tokens <= 0) return 0;
+  TIPSK_REQUIRE(hidden % (16 / (int)DTypeSize(dtype)) == 0 && seq >= 1, "embed: hidden must be a multiple of 16 bytes");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  int grid = CeilDiv(tokens, 8);
+  if (grid > NumSMs() * 8) grid = NumSMs() * 8;
+  EPI_DISPATCH(dtype, {
+    EmbedSumFwdKernel<T><<<grid, 256, 0, s>>>(ids, static_cast<const T*>(tok), static_cast<const T*>(pos),
+                                              static_cast<const T*>(typ), static_cast<T*>(x), tokens, seq, hidden, vocab);
+  });
+  TIPSK_LAUNCH_CHECK();
+  return 0;
+}
+
+/* dtok [vocab, hidden] (zeroed here), dpos [seq, hidden], dtyp [hidden]; tokens = batch * seq. */
+int tipsk_embed_sum_bwd(const int64_t* ids, const void* dx, void* dtok, void* dpos, void* dtyp, int64_t tokens, int seq,
+                        int hidden, int64_t vocab, int dtype, void* stream) {
+  if (tokens <= 0) return 0;
+  const int n = 16 / (int)DTypeSize(dtype);
+  TIPSK_REQUIRE(hidden % n == 0 && seq >= 1 && tokens % seq == 0, "embed: hidden must be a multiple of 16 bytes");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  TIPSK_CUDA(cudaMemsetAsync(dtok, 0, static_cast<size_t>(vocab) * hidden * DTypeSize(dtype), s));
+  int grid = CeilDiv(tokens, 8);
+  if (grid > NumSMs() * 8) grid = NumSMs() * 8;
+  const int64_t pos_items = static_cast<int64_t>(seq) * (hidden / n);
+  int pgrid = CeilDiv(pos_items, 256);
+  if (pgrid > NumSMs() * 8) pgrid = NumSMs() * 8;
+  EPI_DISPATCH(dtype, {
+    EmbedTokBwdKernel<T><<<grid, 256, 0, s>>>(ids, static_cast<const T*>(dx), static_cast<T*>(dtok), tokens, hidden, vocab);
+    EmbedPosBwdKernel<T><<<pgrid, 256, 0, s>>>(static_cast<const T*>(dx), static_cast<T*>(dpos), tokens / seq, seq, hidden);
+    EmbedTypBwdKernel<T><<<CeilDiv(hidden, 256), 256, 0, s>>>(static_cast<const T*>(dpos), static_cast<T*>(dtyp), seq, hidden);
   });
   TIPSK_LAUNCH_CHECK();
   return 0;

@@ -102,6 +102,11 @@ int tipsk_dot_sigmoid_bce_fwd(const void* x, const void* w, const void* bias, co
                               void* stream);
 int tipsk_dot_sigmoid_bce_bwd(const void* x, const void* w, const float* dz, const float* dloss, void* dx, float* dw,
                               float* db, int64_t rows, int k, int64_t ldx, int dtype, void* stream);
+/* Encoder input embedding: token row + position row + type row, and its backward (epilogue.cu). */
+int tipsk_embed_sum_fwd(const int64_t* ids, const void* tok, const void* pos, const void* typ, void* x, int64_t tokens,
+                        int seq, int hidden, int64_t vocab, int dtype, void* stream);
+int tipsk_embed_sum_bwd(const int64_t* ids, const void* dx, void* dtok, void* dpos, void* dtyp, int64_t tokens, int seq,
+                        int hidden, int64_t vocab, int dtype, void* stream);
 int tipsk_sigmoid_bce(const void* logits, const float* targets, float* loss_sum, void* dlogits, int64_t n,
                       float grad_scale, int dtype, void* stream);
 /* Softmax cross entropy over [rows, cols] with int64 labels (ignore_index skipped):

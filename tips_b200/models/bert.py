@@ -4,7 +4,7 @@ FFN 4096, vocab 30522, sequence 512 by default).
 The reference does not contain the model (it trains TensorFlow models through its collective mode);
 this is the second data-parallel benchmark workload.  Linear layers run on the tcgen05 GEMM with bias and
 GELU fused into the epilogue, layer norms and the softmax cross-entropy are the fused kernels of this
-package, the attention core is the library scaled-dot-product attention.
+package (the input embedding as well), the attention core is the library scaled-dot-product attention.
 """
 from __future__ import annotations
 
@@ -14,7 +14,12 @@ import torch.nn as nn
 from ..ops.attention import packed_attention
 from ..ops.linear import Linear
 from ..ops.norm import LayerNorm
-from ..ops.pointwise import softmax_cross_entropy
+from ..ops.pointwise import embed_sum, softmax_cross_entropy
+
+
+import os
+
+_TORCH_EMBED = os.environ.get("TIPS_BERT_TORCH_EMBED", "0") == "1"
 
 
 class BertLayer(nn.Module):
@@ -59,9 +64,11 @@ class BertMLM(nn.Module):
                 nn.init.normal_(m.weight, std=0.02)
 
     def encode(self, ids):
-        b, s = ids.shape
-        pos = torch.arange(s, device=ids.device)
-        x = self.tok(ids) + self.pos(pos)[None] + self.typ.weight[0]
+        if _TORCH_EMBED:  # TIPS_BERT_TORCH_EMBED=1: torch's embedding kernels, kept for A/B measurements
+            pos = torch.arange(ids.shape[1], device=ids.device)
+            x = self.tok(ids) + self.pos(pos)[None] + self.typ.weight[0]
+        else:
+            x = embed_sum(ids, self.tok.weight, self.pos.weight, self.typ.weight[0])
         x = self.ln_emb(x)
         for layer in self.layers:
             x = layer(x)

@@ -34,6 +34,8 @@ _PROTOS = {
     "tipsk_bias_act_fwd": (I, [P, P, P, L, I, I, I, P]),
     "tipsk_bias_act_bwd": (I, [P, P, P, P, P, L, I, I, I, P]),
     "tipsk_sigmoid_bce": (I, [P, P, P, P, L, F, I, P]),
+    "tipsk_embed_sum_fwd": (I, [P, P, P, P, P, L, I, I, L, I, P]),
+    "tipsk_embed_sum_bwd": (I, [P, P, P, P, P, L, I, I, L, I, P]),
     "tipsk_dot_sigmoid_bce_fwd": (I, [P, P, P, P, P, P, P, L, I, L, F, I, P]),
     "tipsk_dot_sigmoid_bce_bwd": (I, [P, P, P, P, P, P, P, L, I, L, I, P]),
     "tipsk_softmax_xent": (I, [P, P, P, P, P, L, I, L, F, I, P]),

@@ -131,6 +131,49 @@ def linear1_sigmoid_bce_loss(x, weight, bias, targets, reduction="mean"):
     return F.binary_cross_entropy_with_logits(z, targets.float(), reduction=reduction)
 
 
+class _EmbedSumFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, ids, tok, pos, typ):
+        b, seq = ids.shape
+        hidden = tok.shape[1]
+        idc = ids.contiguous()
+        x = torch.empty(b, seq, hidden, dtype=tok.dtype, device=tok.device)
+        base.check(base.K().tipsk_embed_sum_fwd(idc.data_ptr(), tok.data_ptr(), pos.data_ptr(), typ.data_ptr(),
+                                                x.data_ptr(), b * seq, seq, hidden, tok.shape[0], base.code(tok),
+                                                base.stream()), "embed_sum_fwd")
+        ctx.save_for_backward(idc)
+        ctx.shapes = (tuple(tok.shape), tuple(pos.shape), tuple(typ.shape), tok.dtype)
+        return x
+
+    @staticmethod
+    def backward(ctx, dx):
+        (idc,) = ctx.saved_tensors
+        tshape, pshape, yshape, dtype = ctx.shapes
+        b, seq = idc.shape
+        g = dx.contiguous()
+        dtok = torch.empty(tshape, dtype=dtype, device=g.device)
+        dpos = torch.zeros(pshape, dtype=dtype, device=g.device) if pshape[0] != seq else torch.empty(pshape, dtype=dtype, device=g.device)
+        dtyp = torch.empty(yshape, dtype=dtype, device=g.device)
+        base.check(base.K().tipsk_embed_sum_bwd(idc.data_ptr(), g.data_ptr(), dtok.data_ptr(), dpos.data_ptr(),
+                                                dtyp.data_ptr(), b * seq, seq, tshape[1], tshape[0], base.code(g),
+                                                base.stream()), "embed_sum_bwd")
+        return None, dtok, dpos, dtyp
+
+
+def embed_sum(ids, tok_weight, pos_weight, type_row):
+    """``tok_weight[ids] + pos_weight[:seq] + type_row`` for ids [B, S]: the input embedding of a transformer
+    encoder as one gather kernel (and three small kernels in backward); `pos_weight` has at least S rows."""
+    hidden = tok_weight.shape[1]
+    es = tok_weight.element_size()
+    if (ids.is_cuda and tok_weight.is_cuda and tok_weight.dtype == pos_weight.dtype == type_row.dtype
+            and tok_weight.dtype in (torch.bfloat16, torch.float16, torch.float32) and (hidden * es) % 16 == 0
+            and tok_weight.is_contiguous() and pos_weight.is_contiguous() and type_row.is_contiguous()
+            and pos_weight.shape[0] >= ids.shape[1]):
+        return _EmbedSumFn.apply(ids, tok_weight, pos_weight, type_row)
+    seq = ids.shape[1]
+    return tok_weight[ids] + pos_weight[:seq][None] + type_row
+
+
 class _SoftmaxXentFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, logits, labels, ignore_index):

@@ -1,5 +1,5 @@
-"""Host parameter server with arbitrary 64-bit keys (the reference's PsServer / PsClient path):
-ranks 0..servers-1 serve shards, every rank pulls and pushes.
+"""Host parameter server (the reference's PsServer / PsClient path): a sparse table with arbitrary 64-bit keys
+and a dense table addressed by index range; ranks 0..servers-1 serve shards, every rank pulls and pushes.
 
     python -m torch.distributed.run --nproc-per-node 3 examples/host_ps.py
 """
@@ -10,7 +10,7 @@ import numpy as np
 
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 import tips_b200 as tips  # noqa: E402
-from tips_b200.ps.host import HostSparseTable, Route  # noqa: E402
+from tips_b200.ps.host import HostDenseTable, HostSparseTable, Route  # noqa: E402
 
 
 def main():
@@ -26,6 +26,17 @@ def main():
         tips.barrier()
     print(f"rank {tips.rank()}: local rows {table.local_size()} counters {table.counters()}")
     table.close()
+    # a dense vector of 10 000 weights: rank 0 sets it, every rank pushes a gradient for its own range
+    dense = HostDenseTable("dense_demo", 10_000, route=Route(servers=servers), optimizer="sgd", lr=0.5)
+    if tips.rank() == 0:
+        dense.assign(np.ones(10_000, dtype=np.float32))
+    tips.barrier()
+    lo = 1000 * tips.rank()
+    dense.push(np.full(500, 0.2, dtype=np.float32), begin=lo)
+    tips.barrier()
+    w = dense.pull(lo, lo + 502)
+    print(f"rank {tips.rank()}: dense[{lo}:{lo + 3}] = {w[:3]}, dense[{lo + 500}] = {w[500]}  {dense.counters()}")
+    dense.close()
     tips.shutdown()
 
 

@@ -70,6 +70,34 @@ def main():
     st.check_status()
     for (k, a), (_, b) in zip(model.state_dict().items(), ref.state_dict().items()):
         assert torch.allclose(a, b, atol=2e-5, rtol=1e-4), (k, (a - b).abs().max())
+    # sub-groups: even and odd ranks run their own device collectives at the same time, then all ranks as a group
+    even, odd = tips.Group(range(0, size, 2)), tips.Group(range(1, size, 2))
+    everyone = tips.Group(range(size))
+    mine = even if rank % 2 == 0 else odd
+    peers = mine.world_ranks
+    assert mine._device is not None and (odd if rank % 2 == 0 else even).rank == -1
+    for n, dtype in [(3, torch.float32), (100003, torch.bfloat16), (12_000_001, torch.float32)]:
+        t = torch.full((n,), float(rank + 1), device=dev, dtype=dtype)
+        mine.allreduce_(t)
+        assert (t == float(sum(p + 1 for p in peers))).all(), (n, dtype)
+        t = torch.full((n,), float(rank + 1), device=dev, dtype=dtype)
+        everyone.allreduce_(t, op="Max")
+        assert (t == float(size)).all()
+    t = torch.full((1000,), float(rank), device=dev)
+    mine.allreduce_(t, op="Average")
+    assert torch.allclose(t, torch.full_like(t, sum(peers) / len(peers)))
+    g = mine.allgather(torch.full((mine.rank + 2, 5), float(rank), device=dev))
+    assert g.shape[0] == sum(i + 2 for i in range(len(peers)))
+    off = 0
+    for i, p in enumerate(peers):
+        assert (g[off:off + i + 2] == p).all()
+        off += i + 2
+    for root in range(len(peers)):
+        b = torch.full((70001,), float(rank), device=dev, dtype=torch.bfloat16)
+        mine.broadcast_(b, root=root)
+        assert (b == peers[root]).all()
+    torch.cuda.synchronize()
+    st.check_status()
     m = tips.metrics()
     if rank == 0:
         assert m["frozen_executions"] > 0, m

@@ -127,6 +127,15 @@ def _groups(rank, size):
         g.barrier()
         assert g.allgather_object({"r": rank}) == [{"r": 1}, {"r": 3}]
         assert g.allreduce(rank) == 4.0
+        # tensor collectives among the members (CPU tensors travel over the control plane)
+        t = torch.full((3, 2), float(rank))
+        assert torch.equal(g.allreduce_(t.clone()), torch.full((3, 2), 4.0))
+        assert torch.equal(g.allreduce_(t.clone(), op="Average"), torch.full((3, 2), 2.0))
+        assert torch.equal(g.allreduce_(t.clone().to(torch.int64), op="Max"), torch.full((3, 2), 3, dtype=torch.int64))
+        got = g.allgather(torch.full((g.rank + 1, 2), float(rank)))
+        assert got.shape == (3, 2) and got[:, 0].tolist() == [1.0, 3.0, 3.0]
+        b = torch.full((4,), float(rank))
+        assert torch.equal(g.broadcast_(b, root=1), torch.full((4,), 3.0))
     else:
         assert not g.is_member and g.rank == -1
         with pytest.raises(tips.TipsError):

@@ -261,3 +261,60 @@ def test_optimizer_step_raises_after_a_device_wait_ran_out(comm4):
         assert not torch.equal(model.weight.detach(), w0)
     finally:
         tips.shutdown()
+
+
+def test_subgroup_collectives(comm4):
+    """Two disjoint groups of two ranks and the four ranks together, interleaved: every group has flags, epochs
+    and a staging area of its own, so neither disturbs the others; sizes above the group's staging area are
+    chunked."""
+    from tips_b200.parallel.device import DeviceGroup
+    st, lib = comm4
+    dev = st.device
+    ga = DeviceGroup([1, 3], stage_bytes=1 << 20)
+    gb = DeviceGroup([2, 0], stage_bytes=1 << 20)
+    assert ga.members == [1, 3] and gb.members == [0, 2] and ga.area_off != gb.area_off
+    torch.manual_seed(5)
+    for n, dtype in [(7, torch.float32), (70001, torch.float32), (700001, torch.bfloat16), (4096, torch.int64)]:
+        def rand():
+            if dtype.is_floating_point:
+                return torch.randn(n, device=dev).to(dtype)
+            return torch.randint(-50, 50, (n,), device=dev, dtype=dtype)
+        xa, xb, xw = [rand() for _ in range(2)], [rand() for _ in range(2)], [rand() for _ in range(4)]
+        ra, rb = xa[0].double() + xa[1].double(), xb[0].double() + xb[1].double()
+        rw = sum(x.double() for x in xw)
+        ow = [torch.empty_like(x) for x in xw]
+        ga.allreduce_(xa)
+        _check(lib, lib.tipsk_allreduce(_arr([x.data_ptr() for x in xw]), _arr([o.data_ptr() for o in ow]), -1,
+                                        n * xw[0].element_size(), DT[dtype], 0, 1.0, 1.0, 0,
+                                        torch.cuda.current_stream().cuda_stream))
+        gb.allreduce_(xb, postscale=0.5)
+        torch.cuda.synchronize()
+        st.check_status()
+        tol = 1e-5 if dtype != torch.bfloat16 else 3e-2
+        for got, want in [(xa, ra), (xb, rb * 0.5), (ow, rw)]:
+            for t in got:
+                assert torch.allclose(t.double(), want.to(dtype).double() if not dtype.is_floating_point else want,
+                                      atol=tol, rtol=tol)
+    # max over a group
+    xs = [torch.randn(3000, device=dev) for _ in range(2)]
+    want = torch.maximum(xs[0], xs[1])
+    ga.allreduce_(xs, op_code=1)
+    torch.cuda.synchronize()
+    assert torch.equal(xs[0], want) and torch.equal(xs[1], want)
+    # allgatherv with different first dimensions, one of them above the staging area
+    parts = [torch.randn(5, 33, device=dev), torch.randn(9000, 33, device=dev)]
+    outs = gb.allgatherv(parts, [5, 9000])
+    torch.cuda.synchronize()
+    st.check_status()
+    for o in outs:
+        assert torch.equal(o, torch.cat(parts, 0))
+    # broadcast from group rank 1 (the job's rank 3)
+    bs = [torch.full((300001,), float(i), device=dev) for i in range(2)]
+    ga.broadcast_(bs, root=1)
+    torch.cuda.synchronize()
+    st.check_status()
+    assert float(bs[0].min()) == 1.0 and float(bs[0].max()) == 1.0 and float(bs[1].min()) == 1.0
+    with pytest.raises(ValueError):
+        DeviceGroup([0, 4])
+    ga.close()
+    gb.close()

@@ -13,7 +13,7 @@ class _Geometry:
     """The fields of a ShardedEmbedding that the placement helpers read, without a device."""
 
     def __init__(self, n, rows):
-        self.size, self.rows = n, rows
+        self.size, self.nservers, self.rows = n, n, rows
         self.rows_per_shard = (rows + n - 1) // n
 
     place = ShardedEmbedding.place

@@ -31,6 +31,7 @@ class Config:
     comm_blocks: int = 64                    # grid of the communication kernels (SM budget)
     use_multimem: bool = True                # NVLS multimem instructions when a multicast mapping exists
     symm_window_bytes: int = 256 << 20       # staging window for tensors outside symmetric memory
+    group_stage_bytes: int = 32 << 20        # staging area of every sub-group of ranks with device collectives
     static_schedule: bool = True             # freeze the bucket order after the first negotiated step
     fused_update: bool = False               # fused optimizers step inside the gradient allreduce, state sharded
     device_status_check: str = "step"        # step: every synchronize() reads the kernels' status block (no device

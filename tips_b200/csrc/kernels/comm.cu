@@ -606,11 +606,38 @@ int GridFor(uint64_t nbytes, uint64_t tile_bytes, int max_blocks) {
   return static_cast<int>(tiles < static_cast<uint64_t>(max_blocks) ? tiles : max_blocks);
 }
 
-template <typename K, typename... A>
-int LaunchComm(K kernel, int grid_x, cudaStream_t stream, A... a) {
+// Who takes part in a launch: all ranks of the job, or a sub-group of them with its own flags, epochs and staging
+// area.  `ctx` has one entry per grid row: one (this process) or, with the ranks emulated on one GPU, one per member.
+struct CommView {
+  int nranks = 1;              // participants
+  int nlocal = 1;              // grid rows launched here
+  bool cooperative = false;    // the rows wait on one another inside one launch (emulation)
+  bool multimem = false;
+  uint64_t stage_off = kSignalBytes;
+  uint64_t stage_bytes = 0;
+  CommCtx ctx[kMaxRanks];
+  int member_rank[kMaxRanks];  // world rank of participant r (identity for the world view)
+};
+
+CommView WorldView() {
   CommState& st = g_comm;
-  dim3 grid(grid_x, st.emulated > 0 ? st.emulated : 1), block(kCommThreads);
-  if (st.emulated > 0) {
+  CommView v;
+  v.nranks      = st.nranks;
+  v.nlocal      = st.emulated > 0 ? st.emulated : 1;
+  v.cooperative = st.emulated > 0;
+  v.multimem    = st.use_multimem;
+  v.stage_off   = kSignalBytes;
+  v.stage_bytes = st.staging_bytes;
+  for (int i = 0; i < v.nlocal; ++i) v.ctx[i] = st.ctx[st.emulated > 0 ? i : st.rank];
+  for (int r = 0; r < kMaxRanks; ++r) v.member_rank[r] = r;
+  return v;
+}
+
+template <typename K, typename... A>
+int LaunchComm(const CommView& view, K kernel, int grid_x, cudaStream_t stream, A... a) {
+  CommState& st = g_comm;
+  dim3 grid(grid_x, view.nlocal), block(kCommThreads);
+  if (view.cooperative) {
     void* params[] = {(void*)&a...};
     TIPSK_CUDA(cudaLaunchCooperativeKernel((const void*)kernel, grid, block, params, 0, stream));
   } else {
@@ -647,15 +674,12 @@ using namespace tipsk;
 
 namespace {
 
-// Builds the per-rank launch arguments. In emulation `srcs`/`dsts` hold one
-// pointer per rank; otherwise only entry 0 is used.
-CommLaunch MakeLaunch(const void* const* srcs, void* const* dsts, uint64_t win_off) {
+// Builds the per-row launch arguments: `srcs` / `dsts` hold one pointer per grid row of the view.
+CommLaunch MakeLaunch(const CommView& view, const void* const* srcs, void* const* dsts, uint64_t win_off) {
   CommLaunch l;
   memset(&l, 0, sizeof(l));
-  CommState& st = g_comm;
-  int n = st.emulated > 0 ? st.emulated : 1;
-  for (int i = 0; i < n; ++i) {
-    l.r[i].ctx     = st.ctx[st.emulated > 0 ? i : st.rank];
+  for (int i = 0; i < view.nlocal; ++i) {
+    l.r[i].ctx     = view.ctx[i];
     l.r[i].src     = static_cast<const char*>(srcs ? srcs[i] : nullptr);
     l.r[i].dst     = static_cast<char*>(dsts ? dsts[i] : nullptr);
     l.r[i].win_off = win_off;
@@ -664,25 +688,25 @@ CommLaunch MakeLaunch(const void* const* srcs, void* const* dsts, uint64_t win_o
 }
 
 template <typename T>
-int LaunchAllreduceT(const CommLaunch& l, int channel, uint64_t nbytes, int op, float pre, float post, bool one_shot,
-                     bool multimem, int grid, cudaStream_t s) {
+int LaunchAllreduceT(const CommView& vw, const CommLaunch& l, int channel, uint64_t nbytes, int op, float pre, float post,
+                     bool one_shot, bool multimem, int grid, cudaStream_t s) {
   if (one_shot) {
-    if (multimem) return LaunchComm(AllreduceKernel<T, true, true>, grid, s, l, channel, nbytes, op, pre, post);
-    return LaunchComm(AllreduceKernel<T, false, true>, grid, s, l, channel, nbytes, op, pre, post);
+    if (multimem) return LaunchComm(vw, AllreduceKernel<T, true, true>, grid, s, l, channel, nbytes, op, pre, post);
+    return LaunchComm(vw, AllreduceKernel<T, false, true>, grid, s, l, channel, nbytes, op, pre, post);
   }
-  if (multimem) return LaunchComm(AllreduceKernel<T, true, false>, grid, s, l, channel, nbytes, op, pre, post);
-  return LaunchComm(AllreduceKernel<T, false, false>, grid, s, l, channel, nbytes, op, pre, post);
+  if (multimem) return LaunchComm(vw, AllreduceKernel<T, true, false>, grid, s, l, channel, nbytes, op, pre, post);
+  return LaunchComm(vw, AllreduceKernel<T, false, false>, grid, s, l, channel, nbytes, op, pre, post);
 }
 
-int LaunchAllreduce(int dtype, const CommLaunch& l, int channel, uint64_t nbytes, int op, float pre, float post,
-                    bool one_shot, bool multimem, int grid, cudaStream_t s) {
+int LaunchAllreduce(const CommView& vw, int dtype, const CommLaunch& l, int channel, uint64_t nbytes, int op, float pre,
+                    float post, bool one_shot, bool multimem, int grid, cudaStream_t s) {
   switch (dtype) {
-    case kF32: return LaunchAllreduceT<float>(l, channel, nbytes, op, pre, post, one_shot, multimem, grid, s);
-    case kBF16: return LaunchAllreduceT<__nv_bfloat16>(l, channel, nbytes, op, pre, post, one_shot, multimem, grid, s);
-    case kF16: return LaunchAllreduceT<__half>(l, channel, nbytes, op, pre, post, one_shot, multimem, grid, s);
-    case kI32: return LaunchAllreduceT<int32_t>(l, channel, nbytes, op, pre, post, one_shot, false, grid, s);
-    case kI64: return LaunchAllreduceT<int64_t>(l, channel, nbytes, op, pre, post, one_shot, false, grid, s);
-    case kF64: return LaunchAllreduceT<double>(l, channel, nbytes, op, pre, post, one_shot, false, grid, s);
+    case kF32: return LaunchAllreduceT<float>(vw, l, channel, nbytes, op, pre, post, one_shot, multimem, grid, s);
+    case kBF16: return LaunchAllreduceT<__nv_bfloat16>(vw, l, channel, nbytes, op, pre, post, one_shot, multimem, grid, s);
+    case kF16: return LaunchAllreduceT<__half>(vw, l, channel, nbytes, op, pre, post, one_shot, multimem, grid, s);
+    case kI32: return LaunchAllreduceT<int32_t>(vw, l, channel, nbytes, op, pre, post, one_shot, false, grid, s);
+    case kI64: return LaunchAllreduceT<int64_t>(vw, l, channel, nbytes, op, pre, post, one_shot, false, grid, s);
+    case kF64: return LaunchAllreduceT<double>(vw, l, channel, nbytes, op, pre, post, one_shot, false, grid, s);
     default: return SetError(-2, "allreduce: unsupported dtype on the device path");
   }
 }
@@ -704,12 +728,161 @@ std::mutex g_updates_mu;
 template <typename T>
 int LaunchUpdateT(const CommLaunch& l, const UpdateLaunch& u, bool adam, bool multimem, int channel, uint64_t nbytes,
                   float scale, int grid, cudaStream_t s) {
+  const CommView vw = WorldView();
   if (adam) {
-    if (multimem) return LaunchComm(AllreduceUpdateKernel<T, true, true>, grid, s, l, u, channel, nbytes, scale);
-    return LaunchComm(AllreduceUpdateKernel<T, false, true>, grid, s, l, u, channel, nbytes, scale);
+    if (multimem) return LaunchComm(vw, AllreduceUpdateKernel<T, true, true>, grid, s, l, u, channel, nbytes, scale);
+    return LaunchComm(vw, AllreduceUpdateKernel<T, false, true>, grid, s, l, u, channel, nbytes, scale);
   }
-  if (multimem) return LaunchComm(AllreduceUpdateKernel<T, true, false>, grid, s, l, u, channel, nbytes, scale);
-  return LaunchComm(AllreduceUpdateKernel<T, false, false>, grid, s, l, u, channel, nbytes, scale);
+  if (multimem) return LaunchComm(vw, AllreduceUpdateKernel<T, true, false>, grid, s, l, u, channel, nbytes, scale);
+  return LaunchComm(vw, AllreduceUpdateKernel<T, false, false>, grid, s, l, u, channel, nbytes, scale);
+}
+
+// The three collectives on a view (all ranks, or a sub-group): see the comments of the extern "C" entry points.
+int AllreduceOn(const CommView& vw, const void* const* srcs, void* const* dsts, int64_t win_off, uint64_t nbytes,
+                int dtype, int op, float prescale, float postscale, int channel, cudaStream_t s) {
+  CommState& st = g_comm;
+  if (nbytes == 0) return 0;
+  const bool mm  = vw.multimem && op == 0;
+  const uint64_t tile_bytes = static_cast<uint64_t>(SubTileOf(mm)) * vw.nranks * 16;
+  if (!srcs) {
+    TIPSK_REQUIRE(win_off >= static_cast<int64_t>(kSignalBytes) && win_off % 16 == 0, "allreduce: bad window offset");
+    TIPSK_REQUIRE(static_cast<uint64_t>(win_off) + ((nbytes + 15) & ~15ull) <= st.window_bytes,
+                  "allreduce: buffer exceeds the window");
+    const bool one_shot = dsts != nullptr && nbytes <= st.one_shot_bytes;
+    CommLaunch l = MakeLaunch(vw, nullptr, dsts, static_cast<uint64_t>(win_off));
+    return LaunchAllreduce(vw, dtype, l, channel, nbytes, op, prescale, postscale, one_shot, mm,
+                           GridFor(nbytes, tile_bytes, st.blocks), s);
+  }
+  TIPSK_REQUIRE(dsts != nullptr, "allreduce: staged mode needs an output");
+  const uint64_t chunk = vw.stage_bytes;
+  TIPSK_REQUIRE(chunk >= 4096, "allreduce: no staging area configured");
+  for (uint64_t done = 0; done < nbytes; done += chunk) {
+    const uint64_t len = nbytes - done < chunk ? nbytes - done : chunk;
+    const void* sp[kMaxRanks];
+    void* dp[kMaxRanks];
+    for (int i = 0; i < vw.nlocal; ++i) {
+      sp[i] = static_cast<const char*>(srcs[i]) + done;
+      dp[i] = static_cast<char*>(dsts[i]) + done;
+    }
+    CommLaunch l = MakeLaunch(vw, sp, dp, vw.stage_off);
+    const bool one_shot = len <= st.one_shot_bytes;
+    int rc = LaunchAllreduce(vw, dtype, l, channel, len, op, prescale, postscale, one_shot, mm,
+                             GridFor(len, tile_bytes, st.blocks), s);
+    if (rc) return rc;
+  }
+  return 0;
+}
+
+int AllgathervOn(const CommView& vw, const void* const* srcs, void* const* dsts, const uint64_t* bytes_per_rank,
+                 int channel, cudaStream_t s) {
+  CommState& st = g_comm;
+  const int n = vw.nranks;
+  uint64_t displ[kMaxRanks], largest = 0;
+  uint64_t acc = 0;
+  for (int r = 0; r < n; ++r) {
+    displ[r] = acc;
+    acc += bytes_per_rank[r];
+    if (bytes_per_rank[r] > largest) largest = bytes_per_rank[r];
+  }
+  const uint64_t chunk = vw.stage_bytes;
+  TIPSK_REQUIRE(chunk >= 4096, "allgatherv: no staging area configured");
+  for (uint64_t done = 0; done < largest; done += chunk) {
+    GatherSizes gs;
+    memset(&gs, 0, sizeof(gs));
+    for (int r = 0; r < n; ++r) {
+      uint64_t left = bytes_per_rank[r] > done ? bytes_per_rank[r] - done : 0;
+      gs.bytes[r]   = left < chunk ? left : chunk;
+      gs.displ[r]   = displ[r] + done;
+    }
+    const void* sp[kMaxRanks];
+    for (int i = 0; i < vw.nlocal; ++i) {
+      const int r = vw.ctx[i].rank;  // this row's rank among the participants
+      sp[i] = static_cast<const char*>(srcs[i]) + (bytes_per_rank[r] > done ? done : 0);
+    }
+    CommLaunch l = MakeLaunch(vw, sp, dsts, vw.stage_off);
+    uint64_t biggest = 0;
+    for (int r = 0; r < n; ++r) if (gs.bytes[r] > biggest) biggest = gs.bytes[r];
+    int rc = LaunchComm(vw, AllgathervKernel, GridFor(biggest, static_cast<uint64_t>(kCopyTile) * 16, st.blocks), s, l,
+                        channel, gs);
+    if (rc) return rc;
+  }
+  return 0;
+}
+
+int BroadcastOn(const CommView& vw, const void* const* srcs, void* const* dsts, uint64_t nbytes, int root, int channel,
+                cudaStream_t s) {
+  CommState& st = g_comm;
+  TIPSK_REQUIRE(root >= 0 && root < vw.nranks, "broadcast: bad root");
+  const uint64_t chunk = vw.stage_bytes;
+  TIPSK_REQUIRE(chunk >= 4096, "broadcast: no staging area configured");
+  for (uint64_t done = 0; done < nbytes; done += chunk) {
+    const uint64_t len = nbytes - done < chunk ? nbytes - done : chunk;
+    const void* sp[kMaxRanks];
+    void* dp[kMaxRanks];
+    for (int i = 0; i < vw.nlocal; ++i) {
+      sp[i] = srcs[i] ? static_cast<const char*>(srcs[i]) + done : nullptr;
+      dp[i] = static_cast<char*>(dsts[i]) + done;
+    }
+    CommLaunch l = MakeLaunch(vw, sp, dp, vw.stage_off);
+    const int grid = GridFor(len, static_cast<uint64_t>(kCopyTile) * 16, st.blocks);
+    // 32 MiB chunks (TIPS_BCAST_CHUNK_BYTES overrides; the tests use small ones).  Measured on 2 GPUs at 64-256 MiB:
+    // one chunk 374-411 GB/s, 16 MiB chunks 390-421 GB/s, 32 MiB chunks 410-475 GB/s; smaller chunks lose to the
+    // extra barriers.
+    static const uint64_t chunk_bytes = [] {
+      const char* e = getenv("TIPS_BCAST_CHUNK_BYTES");
+      const uint64_t v = e ? strtoull(e, nullptr, 10) : 0;
+      return v >= 4096 ? v : (32ull << 20);
+    }();
+    int nchunks = static_cast<int>(len / chunk_bytes);
+    nchunks = nchunks < 1 ? 1 : (nchunks > 16 ? 16 : nchunks);
+    int rc = vw.multimem ? LaunchComm(vw, BroadcastKernel<true>, grid, s, l, channel, len, root, nchunks)
+                         : LaunchComm(vw, BroadcastKernel<false>, grid, s, l, channel, len, root, nchunks);
+    if (rc) return rc;
+  }
+  return 0;
+}
+
+// Sub-groups of ranks with device collectives of their own.
+struct DeviceGroup {
+  int n = 0;
+  int members[kMaxRanks];        // world ranks, ascending
+  uint64_t area_off = 0;         // window offset of the group's area: [kFlagBytes flags | staging]
+  uint64_t stage_bytes = 0;
+  uint32_t* epochs[kMaxRanks];   // per local row
+};
+std::map<int64_t, DeviceGroup> g_groups;
+std::mutex g_groups_mu;
+
+// View of a group for this process; fails when no local rank is a member.
+int GroupView(int64_t id, CommView* out) {
+  CommState& st = g_comm;
+  std::lock_guard<std::mutex> lock(g_groups_mu);
+  auto it = g_groups.find(id);
+  TIPSK_REQUIRE(it != g_groups.end(), "comm group: unknown group");
+  const DeviceGroup& g = it->second;
+  CommView v;
+  v.nranks      = g.n;
+  v.cooperative = st.emulated > 0;
+  v.multimem    = false;  // the multicast mapping spans all ranks: a sub-group uses peer loads and stores
+  v.stage_off   = g.area_off + kFlagBytes;
+  v.stage_bytes = g.stage_bytes;
+  v.nlocal      = 0;
+  for (int r = 0; r < g.n; ++r) v.member_rank[r] = g.members[r];
+  for (int r = 0; r < g.n; ++r) {
+    const int world = g.members[r];
+    if (st.emulated == 0 && world != st.rank) continue;
+    CommCtx c = st.ctx[world];
+    for (int q = 0; q < kMaxRanks; ++q) c.peer[q] = q < g.n ? st.ctx[world].peer[g.members[q]] : nullptr;
+    c.mc       = nullptr;
+    c.rank     = r;
+    c.nranks   = g.n;
+    c.flag_off = g.area_off;
+    c.epochs   = g.epochs[v.nlocal];
+    v.ctx[v.nlocal++] = c;
+  }
+  TIPSK_REQUIRE(v.nlocal > 0, "comm group: this process is not a member");
+  *out = v;
+  return 0;
 }
 
 }  // namespace
@@ -791,6 +964,13 @@ int tipsk_comm_shutdown(void) {
     std::lock_guard<std::mutex> ulock(g_updates_mu);
     g_updates.clear();
   }
+  {
+    std::lock_guard<std::mutex> glock(g_groups_mu);
+    for (auto& kv : g_groups)
+      for (uint32_t* e : kv.second.epochs)
+        if (e) cudaFree(e);
+    g_groups.clear();
+  }
   return 0;
 }
 
@@ -833,6 +1013,19 @@ int tipsk_comm_reset(void) {
     TIPSK_CUDA(cudaMemset(c.epochs, 0, sizeof(uint32_t) * kNumChannels * kMaxCommBlocks));
     TIPSK_CUDA(cudaMemset(c.failed, 0, sizeof(int32_t)));
   }
+  {  // sub-groups: the flag areas of the local members and their epoch counters
+    std::lock_guard<std::mutex> lock(g_groups_mu);
+    for (auto& kv : g_groups) {
+      DeviceGroup& g = kv.second;
+      int row = 0;
+      for (int r = 0; r < g.n; ++r) {
+        const int world = g.members[r];
+        if (st.emulated == 0 && world != st.rank) continue;
+        TIPSK_CUDA(cudaMemset(st.ctx[world].peer[world] + g.area_off, 0, kFlagBytes));
+        TIPSK_CUDA(cudaMemset(g.epochs[row++], 0, sizeof(uint32_t) * kNumChannels * kMaxCommBlocks));
+      }
+    }
+  }
   memset(st.status_host, 0, sizeof(CommStatus) * kMaxRanks);
   TIPSK_CUDA(cudaDeviceSynchronize());
   return 0;
@@ -848,38 +1041,8 @@ int tipsk_allreduce(const void* const* srcs, void* const* dsts, int64_t win_off,
   CommState& st = g_comm;
   TIPSK_REQUIRE(st.ready, "comm not initialised");
   TIPSK_REQUIRE(channel >= 0 && channel < kNumChannels, "bad channel");
-  if (nbytes == 0) return 0;
   cudaStream_t s = stream ? static_cast<cudaStream_t>(stream) : st.streams[channel];
-  const bool mm  = st.use_multimem && op == 0;
-  const uint64_t tile_bytes = static_cast<uint64_t>(SubTileOf(mm)) * st.nranks * 16;
-  if (!srcs) {
-    TIPSK_REQUIRE(win_off >= static_cast<int64_t>(kSignalBytes) && win_off % 16 == 0, "allreduce: bad window offset");
-    TIPSK_REQUIRE(static_cast<uint64_t>(win_off) + ((nbytes + 15) & ~15ull) <= st.window_bytes,
-                  "allreduce: buffer exceeds the window");
-    const bool one_shot = dsts != nullptr && nbytes <= st.one_shot_bytes;
-    CommLaunch l = MakeLaunch(nullptr, dsts, static_cast<uint64_t>(win_off));
-    return LaunchAllreduce(dtype, l, channel, nbytes, op, prescale, postscale, one_shot, mm,
-                           GridFor(nbytes, tile_bytes, st.blocks), s);
-  }
-  TIPSK_REQUIRE(dsts != nullptr, "allreduce: staged mode needs an output");
-  const uint64_t chunk = st.staging_bytes;
-  TIPSK_REQUIRE(chunk >= 4096, "allreduce: no staging area configured");
-  const int local = st.emulated > 0 ? st.emulated : 1;
-  for (uint64_t done = 0; done < nbytes; done += chunk) {
-    const uint64_t len = nbytes - done < chunk ? nbytes - done : chunk;
-    const void* sp[kMaxRanks];
-    void* dp[kMaxRanks];
-    for (int i = 0; i < local; ++i) {
-      sp[i] = static_cast<const char*>(srcs[i]) + done;
-      dp[i] = static_cast<char*>(dsts[i]) + done;
-    }
-    CommLaunch l = MakeLaunch(sp, dp, kSignalBytes);
-    const bool one_shot = len <= st.one_shot_bytes;
-    int rc = LaunchAllreduce(dtype, l, channel, len, op, prescale, postscale, one_shot, mm,
-                             GridFor(len, tile_bytes, st.blocks), s);
-    if (rc) return rc;
-  }
-  return 0;
+  return AllreduceOn(WorldView(), srcs, dsts, win_off, nbytes, dtype, op, prescale, postscale, channel, s);
 }
 
 /* ---- allreduce fused with the optimizer step ----
@@ -976,7 +1139,7 @@ int tipsk_allreduce_update(int64_t grad_off, float scale, int channel, void* str
     a = it->second;
   }
   cudaStream_t s = stream ? static_cast<cudaStream_t>(stream) : st.streams[channel];
-  CommLaunch l   = MakeLaunch(nullptr, nullptr, static_cast<uint64_t>(grad_off));
+  CommLaunch l   = MakeLaunch(WorldView(), nullptr, nullptr, static_cast<uint64_t>(grad_off));
   UpdateLaunch u;
   memset(&u, 0, sizeof(u));
   for (int i = 0; i < kMaxRanks; ++i) u.r[i] = a.r[i];
@@ -1017,74 +1180,87 @@ int tipsk_allgatherv(const void* const* srcs, void* const* dsts, const uint64_t*
   CommState& st = g_comm;
   TIPSK_REQUIRE(st.ready, "comm not initialised");
   cudaStream_t s = stream ? static_cast<cudaStream_t>(stream) : st.streams[channel];
-  const int n     = st.nranks;
-  const int local = st.emulated > 0 ? st.emulated : 1;
-  uint64_t displ[kMaxRanks], largest = 0;
-  uint64_t acc = 0;
-  for (int r = 0; r < n; ++r) {
-    displ[r] = acc;
-    acc += bytes_per_rank[r];
-    if (bytes_per_rank[r] > largest) largest = bytes_per_rank[r];
-  }
-  const uint64_t chunk = st.staging_bytes;
-  TIPSK_REQUIRE(chunk >= 4096, "allgatherv: no staging area configured");
-  for (uint64_t done = 0; done < largest; done += chunk) {
-    GatherSizes gs;
-    memset(&gs, 0, sizeof(gs));
-    for (int r = 0; r < n; ++r) {
-      uint64_t left = bytes_per_rank[r] > done ? bytes_per_rank[r] - done : 0;
-      gs.bytes[r]   = left < chunk ? left : chunk;
-      gs.displ[r]   = displ[r] + done;
-    }
-    const void* sp[kMaxRanks];
-    for (int i = 0; i < local; ++i) {
-      int r = st.emulated > 0 ? i : st.rank;
-      sp[i] = static_cast<const char*>(srcs[i]) + (bytes_per_rank[r] > done ? done : 0);
-    }
-    CommLaunch l = MakeLaunch(sp, dsts, kSignalBytes);
-    uint64_t biggest = 0;
-    for (int r = 0; r < n; ++r) if (gs.bytes[r] > biggest) biggest = gs.bytes[r];
-    int rc = LaunchComm(AllgathervKernel, GridFor(biggest, static_cast<uint64_t>(kCopyTile) * 16, st.blocks), s, l,
-                        channel, gs);
-    if (rc) return rc;
-  }
-  return 0;
+  return AllgathervOn(WorldView(), srcs, dsts, bytes_per_rank, channel, s);
 }
 
 int tipsk_broadcast(const void* const* srcs, void* const* dsts, uint64_t nbytes, int root, int channel, void* stream) {
   CommState& st = g_comm;
   TIPSK_REQUIRE(st.ready, "comm not initialised");
-  TIPSK_REQUIRE(root >= 0 && root < st.nranks, "broadcast: bad root");
   cudaStream_t s = stream ? static_cast<cudaStream_t>(stream) : st.streams[channel];
-  const uint64_t chunk = st.staging_bytes;
-  TIPSK_REQUIRE(chunk >= 4096, "broadcast: no staging area configured");
-  const int local = st.emulated > 0 ? st.emulated : 1;
-  for (uint64_t done = 0; done < nbytes; done += chunk) {
-    const uint64_t len = nbytes - done < chunk ? nbytes - done : chunk;
-    const void* sp[kMaxRanks];
-    void* dp[kMaxRanks];
-    for (int i = 0; i < local; ++i) {
-      sp[i] = srcs[i] ? static_cast<const char*>(srcs[i]) + done : nullptr;
-      dp[i] = static_cast<char*>(dsts[i]) + done;
-    }
-    CommLaunch l = MakeLaunch(sp, dp, kSignalBytes);
-    const int grid = GridFor(len, static_cast<uint64_t>(kCopyTile) * 16, st.blocks);
-    // 32 MiB chunks (TIPS_BCAST_CHUNK_BYTES overrides; the tests use small ones).  Measured on 2 GPUs at 64-256 MiB:
-    // one chunk 374-411 GB/s, 16 MiB chunks 390-421 GB/s, 32 MiB chunks 410-475 GB/s; smaller chunks lose to the
-    // extra barriers.
-    static const uint64_t chunk_bytes = [] {
-      const char* e = getenv("TIPS_BCAST_CHUNK_BYTES");
-      const uint64_t v = e ? strtoull(e, nullptr, 10) : 0;
-      return v >= 4096 ? v : (32ull << 20);
-    }();
-    int nchunks = static_cast<int>(len / chunk_bytes);
-    nchunks = nchunks < 1 ? 1 : (nchunks > 16 ? 16 : nchunks);
-    int rc = st.use_multimem ? LaunchComm(BroadcastKernel<true>, grid, s, l, channel, len, root, nchunks)
-                             : LaunchComm(BroadcastKernel<false>, grid, s, l, channel, len, root, nchunks);
-    if (rc) return rc;
+  return BroadcastOn(WorldView(), srcs, dsts, nbytes, root, channel, s);
+}
+
+/* ---- device collectives of a sub-group of ranks ----
+ * `members`: ascending world ranks.  `area_off`: offset of kFlagBytes + stage_bytes zeroed bytes inside EVERY rank's
+ * window, the same offset everywhere (flags first, then the group's staging area), reserved for this group alone.
+ * Called by every member (with the ranks emulated on one GPU: once).  The collectives below are launched by the
+ * members only, in the same order on every member, on the stream they are given; srcs / dsts hold one pointer per
+ * local member (one; with emulation one per member, in member order).  Ranks inside a group are group ranks. */
+int tipsk_comm_group_create(int64_t id, const int32_t* members, int n, uint64_t area_off, uint64_t stage_bytes) {
+  CommState& st = g_comm;
+  TIPSK_REQUIRE(st.ready, "comm not initialised");
+  TIPSK_REQUIRE(n >= 1 && n <= st.nranks, "comm group: bad size");
+  TIPSK_REQUIRE(area_off >= kSignalBytes && area_off % 256 == 0 && area_off + kFlagBytes + stage_bytes <= st.window_bytes,
+                "comm group: the area does not fit the window");
+  TIPSK_REQUIRE(stage_bytes >= 4096 && stage_bytes % 4096 == 0, "comm group: the staging area must be a multiple of 4096");
+  DeviceGroup g;
+  g.n = n;
+  for (int i = 0; i < n; ++i) {
+    TIPSK_REQUIRE(members[i] >= 0 && members[i] < st.nranks && (i == 0 || members[i] > members[i - 1]),
+                  "comm group: members must be ascending ranks of the job");
+    g.members[i] = members[i];
   }
+  g.area_off    = area_off;
+  g.stage_bytes = stage_bytes;
+  const int rows = st.emulated > 0 ? n : 1;
+  for (int i = 0; i < kMaxRanks; ++i) g.epochs[i] = nullptr;
+  for (int i = 0; i < rows; ++i) {
+    TIPSK_CUDA(cudaMalloc(reinterpret_cast<void**>(&g.epochs[i]), sizeof(uint32_t) * kNumChannels * kMaxCommBlocks));
+    TIPSK_CUDA(cudaMemset(g.epochs[i], 0, sizeof(uint32_t) * kNumChannels * kMaxCommBlocks));
+  }
+  std::lock_guard<std::mutex> lock(g_groups_mu);
+  g_groups[id] = g;
   return 0;
 }
+
+int tipsk_comm_group_destroy(int64_t id) {
+  std::lock_guard<std::mutex> lock(g_groups_mu);
+  auto it = g_groups.find(id);
+  if (it == g_groups.end()) return 0;
+  for (uint32_t* e : it->second.epochs)
+    if (e) cudaFree(e);
+  g_groups.erase(it);
+  return 0;
+}
+
+int tipsk_group_allreduce(int64_t id, const void* const* srcs, void* const* dsts, uint64_t nbytes, int dtype, int op,
+                          float prescale, float postscale, void* stream) {
+  CommView vw;
+  int rc = GroupView(id, &vw);
+  if (rc) return rc;
+  TIPSK_REQUIRE(srcs && dsts && stream, "group allreduce: needs inputs, outputs and a stream");
+  return AllreduceOn(vw, srcs, dsts, -1, nbytes, dtype, op, prescale, postscale, 0, static_cast<cudaStream_t>(stream));
+}
+
+int tipsk_group_allgatherv(int64_t id, const void* const* srcs, void* const* dsts, const uint64_t* bytes_per_member,
+                           void* stream) {
+  CommView vw;
+  int rc = GroupView(id, &vw);
+  if (rc) return rc;
+  TIPSK_REQUIRE(srcs && dsts && stream, "group allgatherv: needs inputs, outputs and a stream");
+  return AllgathervOn(vw, srcs, dsts, bytes_per_member, 0, static_cast<cudaStream_t>(stream));
+}
+
+int tipsk_group_broadcast(int64_t id, const void* const* srcs, void* const* dsts, uint64_t nbytes, int root,
+                          void* stream) {
+  CommView vw;
+  int rc = GroupView(id, &vw);
+  if (rc) return rc;
+  TIPSK_REQUIRE(srcs && dsts && stream, "group broadcast: needs inputs, outputs and a stream");
+  return BroadcastOn(vw, srcs, dsts, nbytes, root, 0, static_cast<cudaStream_t>(stream));
+}
+
+uint64_t tipsk_comm_flag_bytes(void) { return kFlagBytes; }
 
 /* Launches a kernel that waits (bounded) for a flag that is never set; afterwards
  * tipsk_comm_status reports a timeout. */

@@ -49,6 +49,10 @@ struct CommCtx {
   uint64_t budget_ns;
   int32_t rank;
   int32_t nranks;
+  // Byte offset of this context's flag area inside every member's window: 0 = the area at the start of the
+  // window (the collectives of all ranks); a sub-group of ranks has an area of its own further up, so that its
+  // barriers and epochs are independent of everyone else's.
+  uint64_t flag_off;
 };
 
 __device__ __forceinline__ uint64_t GlobalTimerNs() {
@@ -145,8 +149,8 @@ __device__ __forceinline__ bool BlockBarrier(const CommCtx& ctx, int channel, in
   __syncthreads();
   if (threadIdx.x < ctx.nranks) {
     const int peer = threadIdx.x;
-    StReleaseSys(FlagAddr(ctx.peer[peer], channel, block, ctx.rank), epoch);
-    const uint32_t* mine = FlagAddr(ctx.peer[ctx.rank], channel, block, peer);
+    StReleaseSys(FlagAddr(ctx.peer[peer] + ctx.flag_off, channel, block, ctx.rank), epoch);
+    const uint32_t* mine = FlagAddr(ctx.peer[ctx.rank] + ctx.flag_off, channel, block, peer);
     // device memory, not the host-visible block: a PCIe read per barrier would serialise the blocks
     const bool already_failed = *reinterpret_cast<volatile int32_t*>(ctx.failed) != 0;
     if (already_failed) {

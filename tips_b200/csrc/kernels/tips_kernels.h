@@ -139,6 +139,17 @@ int tipsk_allgatherv(const void* const* host_srcs, void* const* host_dsts, const
 int tipsk_broadcast(const void* const* host_srcs, void* const* host_dsts, uint64_t nbytes, int root, int channel,
                     void* stream);
 int tipsk_comm_wait_never(int channel, void* stream);
+/* Device collectives of a sub-group of ranks (see comm.cu): the group owns kFlagBytes + stage_bytes bytes at `area_off`
+ * of every rank's window. */
+int tipsk_comm_group_create(int64_t id, const int32_t* members, int n, uint64_t area_off, uint64_t stage_bytes);
+int tipsk_comm_group_destroy(int64_t id);
+int tipsk_group_allreduce(int64_t id, const void* const* host_srcs, void* const* host_dsts, uint64_t nbytes, int dtype,
+                          int op, float prescale, float postscale, void* stream);
+int tipsk_group_allgatherv(int64_t id, const void* const* host_srcs, void* const* host_dsts,
+                           const uint64_t* bytes_per_member, void* stream);
+int tipsk_group_broadcast(int64_t id, const void* const* host_srcs, void* const* host_dsts, uint64_t nbytes, int root,
+                          void* stream);
+uint64_t tipsk_comm_flag_bytes(void);
 /* Allreduce fused with the optimizer step on the share of the parameters each rank owns (see comm.cu). */
 int tipsk_comm_update_subtile(void);
 int64_t tipsk_comm_update_shard_vecs(uint64_t nbytes);

@@ -222,6 +222,116 @@ def teardown(st: DeviceState) -> None:
         _state = None
 
 
+# ------------------------------------------------------------------ sub-groups
+
+
+class DeviceGroup:
+    """Device collectives (allreduce, allgatherv, broadcast) among a subset of the ranks, run by the same kernels
+    as the collectives of all ranks over peer loads and stores.
+
+    A group owns a slice of every rank's window: barrier flags plus a staging area, at the same offset everywhere,
+    so its barriers and epochs are independent of the other groups' and of the job-wide collectives, and two
+    disjoint groups run at the same time.  EVERY rank of the job constructs the group, in the same order relative
+    to other symmetric allocations (the reservation must land at the same offset on all ranks); only members may
+    call the collectives, in the same order on every member.  The calls are queued on the current CUDA stream.
+
+    The reference has one communicator for the whole job (tips/core/mpi_context.h:20-53: the global communicator
+    and a per-node one); sub-groups are what its parameter-server mode builds on top, with workers and servers as
+    separate rank sets (tips/core/ps/route.h:58-114).
+
+    With the ranks emulated on one GPU the tensor arguments are lists with one tensor per member, in member order.
+    """
+
+    _standalone_ids = 1 << 40
+
+    def __init__(self, members, group_id: int | None = None, stage_bytes: int | None = None):
+        st = state()
+        lib = _lib.kernels()
+        self.members = sorted(int(m) for m in members)
+        if len(set(self.members)) != len(self.members) or not self.members or self.members[0] < 0 \
+                or self.members[-1] >= st.size:
+            raise ValueError(f"bad group members {members} for a job of {st.size} ranks")
+        if st.window is None:
+            raise RuntimeError("device groups need more than one rank")
+        if group_id is None:
+            DeviceGroup._standalone_ids += 1
+            group_id = DeviceGroup._standalone_ids
+        self.id = int(group_id)
+        self.stage_bytes = int(stage_bytes if stage_bytes is not None else get_config().group_stage_bytes) // 4096 * 4096
+        # the window is zeroed when it is created and symmetric allocations are never handed out twice,
+        # so the flags of the new area start at zero on every rank
+        _, self.area_off = st.alloc_symmetric(int(lib.tipsk_comm_flag_bytes()) + self.stage_bytes)
+        arr = (ctypes.c_int32 * len(self.members))(*self.members)
+        if lib.tipsk_comm_group_create(self.id, arr, len(self.members), self.area_off, self.stage_bytes):
+            raise RuntimeError("device group: " + lib.tipsk_last_error().decode())
+        self._st = st
+
+    @property
+    def size(self) -> int:
+        return len(self.members)
+
+    @property
+    def rank(self) -> int:
+        """Group rank of this process (-1: not a member); 0 when the ranks are emulated."""
+        if self._st.emulated:
+            return 0
+        return self.members.index(self._st.rank) if self._st.rank in self.members else -1
+
+    def _rows(self, x):
+        rows = list(x) if isinstance(x, (list, tuple)) else [x]
+        want = self.size if self._st.emulated else 1
+        if len(rows) != want:
+            raise ValueError(f"expected {want} tensor(s), got {len(rows)}")
+        if self.rank < 0:
+            raise RuntimeError("this rank is not a member of the group")
+        for t in rows:
+            if not (t.is_cuda and t.is_contiguous()):
+                raise ValueError("device group collectives take contiguous CUDA tensors")
+        return rows
+
+    def _check(self, rc, what):
+        if rc:
+            raise RuntimeError(f"group {what}: " + _lib.kernels().tipsk_last_error().decode())
+
+    def allreduce_(self, tensors, op_code: int = 0, prescale: float = 1.0, postscale: float = 1.0):
+        """In-place reduction over the members (op_code: 0 sum, 1 max, 2 min, 3 product)."""
+        from ..ops import base
+        rows = self._rows(tensors)
+        nbytes = rows[0].numel() * rows[0].element_size()
+        ptrs = _ptr_array([t.data_ptr() for t in rows])
+        self._check(_lib.kernels().tipsk_group_allreduce(self.id, ptrs, ptrs, nbytes, base.code(rows[0]), op_code,
+                                                        prescale, postscale, base.comm_stream()), "allreduce")
+        return tensors
+
+    def allgatherv(self, tensors, first_dims):
+        """Concatenation along dim 0 of every member's tensor; `first_dims` lists every member's dim 0."""
+        from ..ops import base
+        rows = self._rows(tensors)
+        inner = rows[0].shape[1:]
+        row_bytes = rows[0].element_size()
+        for d in inner:
+            row_bytes *= d
+        sizes = (ctypes.c_uint64 * self.size)(*[int(d) * row_bytes for d in first_dims])
+        outs = [torch.empty((int(sum(first_dims)),) + tuple(inner), dtype=t.dtype, device=t.device) for t in rows]
+        self._check(_lib.kernels().tipsk_group_allgatherv(self.id, _ptr_array([t.data_ptr() for t in rows]),
+                                                         _ptr_array([o.data_ptr() for o in outs]), sizes,
+                                                         base.comm_stream()), "allgatherv")
+        return outs if isinstance(tensors, (list, tuple)) else outs[0]
+
+    def broadcast_(self, tensors, root: int = 0):
+        """In-place broadcast from group rank `root`."""
+        from ..ops import base
+        rows = self._rows(tensors)
+        nbytes = rows[0].numel() * rows[0].element_size()
+        ptrs = _ptr_array([t.data_ptr() for t in rows])
+        self._check(_lib.kernels().tipsk_group_broadcast(self.id, ptrs, ptrs, nbytes, int(root), base.comm_stream()),
+                    "broadcast")
+        return tensors
+
+    def close(self):
+        _lib.kernels().tipsk_comm_group_destroy(self.id)
+
+
 # ------------------------------------------------------------------ NCCL floor
 
 

@@ -45,6 +45,23 @@ def main():
         b = tips.broadcast(torch.full((70001,), float(rank), device=dev, dtype=torch.bfloat16), root_rank=root)
         assert (b == root).all()
     st.check_status()
+    # large messages: the gather above the pushing kernel's limit, the broadcast as scatter + allgather (forced for
+    # two ranks too), an odd byte count, every root
+    lib = tips._lib.kernels()
+    assert lib.tipsk_comm_set_option(b"bcast_scatter_min_ranks", 2) == 0
+    g = tips.allgather(torch.full(((rank + 1) * 3_000_001,), float(rank), device=dev))
+    off = 0
+    for r in range(size):
+        part = g[off:off + (r + 1) * 3_000_001]
+        assert float(part.min()) == r and float(part.max()) == r
+        off += (r + 1) * 3_000_001
+    for root in range(size):
+        torch.manual_seed(root)
+        want = torch.randn(9_000_001).to(torch.bfloat16)
+        b = tips.broadcast(want.to(dev) if rank == root else torch.zeros(9_000_001, device=dev, dtype=torch.bfloat16),
+                           root_rank=root)
+        assert torch.equal(b.cpu(), want), root
+    st.check_status()
 
     # DistributedOptimizer against a single-process reference on the concatenated batch
     from tips_b200.ops.optim import FusedSGD

@@ -118,6 +118,71 @@ def test_allgatherv_and_broadcast(comm4):
         assert torch.equal(o, src)
 
 
+@pytest.mark.parametrize("push", [True, False])
+def test_allgatherv_pushed_and_pulled(comm4, push):
+    """The same ragged gather through the pushing kernel (small slabs) and through the pulling one; the byte counts
+    are odd on purpose and one output is misaligned."""
+    st, lib = comm4
+    dev = st.device
+    _check(lib, lib.tipsk_comm_set_option(b"allgather_push_bytes", (32 << 20) if push else 0))
+    try:
+        for sizes in ([3, 0, 70001, 1], [65536 * 3 + 5, 17, 16, 250001], [0, 0, 9, 0]):
+            xs = [torch.randint(0, 255, (s,), dtype=torch.uint8, device=dev) for s in sizes]
+            total = sum(sizes)
+            raw = [torch.full((total + 64,), 0xEE, dtype=torch.uint8, device=dev) for _ in range(4)]
+            outs = [r[3 * (i % 2):3 * (i % 2) + total] for i, r in enumerate(raw)]   # ranks 1, 3: odd address
+            nbytes = (ctypes.c_uint64 * 4)(*sizes)
+            _check(lib, lib.tipsk_allgatherv(_arr([x.data_ptr() if x.numel() else 0 for x in xs]),
+                                             _arr([o.data_ptr() for o in outs]), nbytes, 0,
+                                             torch.cuda.current_stream().cuda_stream))
+            torch.cuda.synchronize()
+            st.check_status()
+            ref = torch.cat(xs)
+            for i, (o, r) in enumerate(zip(outs, raw)):
+                assert torch.equal(o, ref), (sizes, i)
+                assert bool((r[3 * (i % 2) + total:] == 0xEE).all()) and bool((r[:3 * (i % 2)] == 0xEE).all())
+    finally:
+        _check(lib, lib.tipsk_comm_set_option(b"allgather_push_bytes", 32 << 20))
+
+
+@pytest.mark.parametrize("chunk", [65536, 1 << 20, 8 << 20])
+def test_broadcast_scatter_then_allgather(comm4, chunk):
+    """Large broadcasts: the root scatters tiles to their owners, the owners forward them, in a pipeline over
+    chunks.  Every root, byte counts that end inside a vector, a misaligned input and output, and a message larger
+    than the staging area (several launches)."""
+    st, lib = comm4
+    dev = st.device
+    _check(lib, lib.tipsk_comm_set_option(b"bcast_scatter_bytes", 1 << 20))
+    _check(lib, lib.tipsk_comm_set_option(b"bcast_scatter_chunk_bytes", chunk))
+    try:
+        for nbytes, root, shift in [(1 << 20, 0, 0), ((3 << 20) + 7, 1, 0), ((2 << 20) + 4097, 3, 5),
+                                    ((19 << 20) + 13, 2, 0)]:
+            src = torch.randint(0, 255, (nbytes + 16,), dtype=torch.uint8, device=dev)[shift:shift + nbytes]
+            raw = [torch.full((nbytes + 64,), 0xEE, dtype=torch.uint8, device=dev) for _ in range(4)]
+            outs = [r[shift:shift + nbytes] for r in raw]
+            srcs = [torch.zeros(16, dtype=torch.uint8, device=dev) for _ in range(4)]
+            srcs[root] = src
+            _check(lib, lib.tipsk_broadcast(_arr([s.data_ptr() for s in srcs]), _arr([o.data_ptr() for o in outs]),
+                                            nbytes, root, 0, torch.cuda.current_stream().cuda_stream))
+            torch.cuda.synchronize()
+            st.check_status()
+            for i, (o, r) in enumerate(zip(outs, raw)):
+                assert torch.equal(o, src), (nbytes, root, i)
+                assert bool((r[shift + nbytes:] == 0xEE).all()) and bool((r[:shift] == 0xEE).all())
+        # in place on the root (input and output are the same buffer)
+        buf = [torch.randint(0, 255, (3 << 20,), dtype=torch.uint8, device=dev) for _ in range(4)]
+        want = buf[1].clone()
+        ptrs = _arr([b.data_ptr() for b in buf])
+        _check(lib, lib.tipsk_broadcast(ptrs, ptrs, 3 << 20, 1, 0, torch.cuda.current_stream().cuda_stream))
+        torch.cuda.synchronize()
+        st.check_status()
+        for b in buf:
+            assert torch.equal(b, want)
+    finally:
+        _check(lib, lib.tipsk_comm_set_option(b"bcast_scatter_bytes", 2 << 20))
+        _check(lib, lib.tipsk_comm_set_option(b"bcast_scatter_chunk_bytes", 8 << 20))
+
+
 def _reference_step(kind, w, state, g, step, hp):
     """fp32 reference of one optimizer step (the rules of torch.optim.SGD / AdamW)."""
     if kind == "sgd":

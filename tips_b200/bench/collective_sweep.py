@@ -31,6 +31,12 @@ def _checked(lib, call):
     return run
 
 
+def _opt(lib, name, value):
+    """Kernel selection of the library; every rank sets the same value between two timed runs."""
+    if lib.tipsk_comm_set_option(name.encode(), int(value)):
+        raise RuntimeError(lib.tipsk_last_error().decode())
+
+
 def _time(fn, iters, warmup=3):
     for _ in range(warmup):
         fn()
@@ -53,6 +59,8 @@ def main(argv=None):
     ap.add_argument("--min-kb", type=int, default=1)
     ap.add_argument("--dtypes", default="fp32,bf16")
     ap.add_argument("--ops", default="allreduce,allgather,broadcast")
+    ap.add_argument("--scatter-chunks-mb", default="", help="also time the scatter broadcast with these pipeline "
+                    "chunk sizes, e.g. 2,4,16")
     ap.add_argument("--out", default="")
     a = ap.parse_args(argv)
     tips.init()
@@ -106,6 +114,12 @@ def main(argv=None):
                 ms = _time(_checked(lib, lambda: lib.tipsk_allgatherv(srcs, dsts, per, 3, stream)), iters)
                 res["allgather_ms"] = ms
                 res["allgather_busbw"] = nbytes * n / ms / 1e6 * (n - 1) / n
+                if nbytes * n <= (32 << 20):
+                    # the same gather through the pulling kernel, which larger slabs use
+                    _opt(lib, "allgather_push_bytes", 0)
+                    ms = _time(_checked(lib, lambda: lib.tipsk_allgatherv(srcs, dsts, per, 3, stream)), iters)
+                    _opt(lib, "allgather_push_bytes", 32 << 20)
+                    res["allgather_pull_busbw"] = nbytes * n / ms / 1e6 * (n - 1) / n
                 ms = _time(lambda: dist.all_gather_into_tensor(out, x), iters)
                 res["nccl_allgather_busbw"] = nbytes * n / ms / 1e6 * (n - 1) / n
                 del out
@@ -115,6 +129,17 @@ def main(argv=None):
                 ms = _time(_checked(lib, lambda: lib.tipsk_broadcast(srcs, dsts, nbytes, 0, 3, stream)), iters)
                 res["broadcast_ms"] = ms
                 res["broadcast_gbs"] = nbytes / ms / 1e6
+                if nbytes >= (2 << 20) and n >= 3:
+                    # the same message stored to everybody by the root alone (what smaller messages use)
+                    _opt(lib, "bcast_scatter_bytes", 0)
+                    ms = _time(_checked(lib, lambda: lib.tipsk_broadcast(srcs, dsts, nbytes, 0, 3, stream)), iters)
+                    _opt(lib, "bcast_scatter_bytes", 2 << 20)
+                    res["broadcast_direct_gbs"] = nbytes / ms / 1e6
+                    for mb in [int(c) for c in a.scatter_chunks_mb.split(",") if c]:
+                        _opt(lib, "bcast_scatter_chunk_bytes", mb << 20)
+                        ms = _time(_checked(lib, lambda: lib.tipsk_broadcast(srcs, dsts, nbytes, 0, 3, stream)), iters)
+                        res[f"broadcast_gbs_chunk{mb}mb"] = nbytes / ms / 1e6
+                    _opt(lib, "bcast_scatter_chunk_bytes", 8 << 20)
                 ms = _time(lambda: dist.broadcast(x, 0), iters)
                 res["nccl_broadcast_gbs"] = nbytes / ms / 1e6
             if "update" in a.ops and 16 <= nbytes <= upd_max:

@@ -470,6 +470,231 @@ AllgathervKernel(CommLaunch args, int channel, GatherSizes sizes) {
   SaveEpoch(ctx, channel, block, epoch + 1);
 }
 
+// One 16-byte vector of a byte buffer that may be unaligned and may end inside the vector (the rest reads as zero).
+__device__ __forceinline__ U4 LoadVecBytes(const char* base, uint64_t v, uint64_t nbytes, bool aligned) {
+  if (aligned && v * 16 + 16 <= nbytes) return *reinterpret_cast<const U4*>(base + v * 16);
+  U4 q;
+  char* qb = reinterpret_cast<char*>(&q);
+  for (uint64_t b = 0; b < 16; ++b) qb[b] = v * 16 + b < nbytes ? base[v * 16 + b] : 0;
+  return q;
+}
+__device__ __forceinline__ void StoreVecBytes(char* base, uint64_t v, uint64_t nbytes, bool aligned, const U4& q) {
+  if (aligned && v * 16 + 16 <= nbytes) {
+    *reinterpret_cast<U4*>(base + v * 16) = q;
+    return;
+  }
+  const char* qb = reinterpret_cast<const char*>(&q);
+  for (uint64_t b = 0; b < 16 && v * 16 + b < nbytes; ++b) base[v * 16 + b] = qb[b];
+}
+
+// Allgatherv for small slabs, by pushing: every rank stores its slab straight from its input into every rank's
+// window (one multimem store per vector, or one store per peer), one barrier, and everyone copies the gathered
+// slabs from its own window to its output.  Against the pulling kernel above it saves the copy of the input into
+// the window and, above all, the chain of peer loads that a block walks rank after rank: with slabs of a few
+// hundred KB that chain, not the bytes, is the time.  Tiles are small so that a 64 KB slab already spreads over
+// several blocks.  Tile t of every slab belongs to block t % grid on every rank, for the stores and for the copy.
+constexpr int kPushTile = kCommThreads * 2;  // vectors (16 KB)
+
+template <bool kMultimem>
+__global__ void __launch_bounds__(kCommThreads)
+AllgatherPushKernel(CommLaunch args, int channel, GatherSizes sizes) {
+  const RankArgs& ra = args.r[blockIdx.y];
+  const CommCtx& ctx = ra.ctx;
+  const int n        = ctx.nranks;
+  const int block    = blockIdx.x;
+  char* my_win       = ctx.peer[ctx.rank] + ra.win_off;
+  uint32_t epoch     = NextEpoch(ctx, channel, block);
+  uint64_t wdispl[kMaxRanks];  // where rank r's slab starts inside the staging area (16-byte aligned)
+  {
+    uint64_t at = 0;
+#pragma unroll
+    for (int r = 0; r < kMaxRanks; ++r) {
+      wdispl[r] = at;
+      if (r < n) at += (sizes.bytes[r] + 15) & ~15ull;
+    }
+  }
+  {
+    const uint64_t bytes  = sizes.bytes[ctx.rank];
+    const uint64_t nvec   = (bytes + 15) / 16;
+    const uint64_t ntiles = (nvec + kPushTile - 1) / kPushTile;
+    const bool aligned    = (reinterpret_cast<uintptr_t>(ra.src) & 15) == 0;
+    const uint64_t base   = ra.win_off + wdispl[ctx.rank];
+    for (uint64_t t = block; t < ntiles; t += gridDim.x) {
+      const uint64_t lo = t * kPushTile;
+      const uint64_t hi = lo + kPushTile < nvec ? lo + kPushTile : nvec;
+      U4 q[2];
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        const uint64_t v = lo + threadIdx.x + static_cast<uint64_t>(u) * blockDim.x;
+        if (v < hi) q[u] = LoadVecBytes(ra.src, v, bytes, aligned);
+      }
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        const uint64_t v = lo + threadIdx.x + static_cast<uint64_t>(u) * blockDim.x;
+        if (v >= hi) continue;
+        if (kMultimem) {
+          MultimemSt(ctx.mc + base + v * 16, q[u]);
+        } else {
+#pragma unroll
+          for (int r = 0; r < kMaxRanks; ++r)
+            if (r < n) StSys(ctx.peer[(ctx.rank + r) % n] + base + v * 16, q[u]);
+        }
+      }
+    }
+  }
+  const bool ok = BlockBarrier(ctx, channel, block, epoch, 1);
+  if (ok && ra.dst) {
+    for (int r = 0; r < n; ++r) {
+      const uint64_t bytes  = sizes.bytes[r];
+      const uint64_t nvec   = (bytes + 15) / 16;
+      const uint64_t ntiles = (nvec + kPushTile - 1) / kPushTile;
+      const char* from      = my_win + wdispl[r];
+      char* to              = ra.dst + sizes.displ[r];
+      const bool aligned    = (reinterpret_cast<uintptr_t>(to) & 15) == 0;
+      for (uint64_t t = block; t < ntiles; t += gridDim.x) {
+        const uint64_t lo = t * kPushTile;
+        const uint64_t hi = lo + kPushTile < nvec ? lo + kPushTile : nvec;
+        U4 q[2];
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          const uint64_t v = lo + threadIdx.x + static_cast<uint64_t>(u) * blockDim.x;
+          if (v < hi) q[u] = *reinterpret_cast<const U4*>(from + v * 16);
+        }
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          const uint64_t v = lo + threadIdx.x + static_cast<uint64_t>(u) * blockDim.x;
+          if (v < hi) StoreVecBytes(to, v, bytes, aligned, q[u]);
+        }
+      }
+    }
+  }
+  BlockBarrier(ctx, channel, block, epoch + 1, 2);  // nobody overwrites a window that is still being copied out
+  SaveEpoch(ctx, channel, block, epoch + 1);
+}
+
+// Broadcast of a large message as scatter + allgather.  One root that stores everything to everybody is bound by
+// what a single source can feed into the switch; here the root sends every tile to ONE rank, its owner (tiles
+// rotate over the ranks), and the owner passes it on to the others (one multimem store, or a store per peer), so
+// that all ranks feed the switch.  The message is cut into chunks and the three steps run as a pipeline with one
+// barrier per step:
+//   step i:  root      scatters chunk i                                  (S)
+//            the rest  forward their tiles of chunk i-1 to everybody      (G)  and write them to their output,
+//                      copy the other tiles of chunk i-2 from their own window to their output  (C)
+// The root writes its output from the registers it sends; tiles the root owns itself go to everybody at once.
+template <bool kMultimem>
+__global__ void __launch_bounds__(kCommThreads)
+BroadcastScatterKernel(CommLaunch args, int channel, uint64_t nbytes, int root, int nchunks) {
+  const RankArgs& ra = args.r[blockIdx.y];
+  const CommCtx& ctx = ra.ctx;
+  const int n        = ctx.nranks;
+  const int block    = blockIdx.x;
+  const int grid     = gridDim.x;
+  const int me       = ctx.rank;
+  char* my_win       = ctx.peer[me] + ra.win_off;
+  uint32_t epoch     = NextEpoch(ctx, channel, block);
+  const uint64_t nvec   = (nbytes + 15) / 16;
+  const uint64_t ntiles = (nvec + kCopyTile - 1) / kCopyTile;
+  const bool src_aligned = me == root && (reinterpret_cast<uintptr_t>(ra.src) & 15) == 0;
+  const bool dst_aligned = ra.dst != nullptr && (reinterpret_cast<uintptr_t>(ra.dst) & 15) == 0;
+  const bool write_dst   = ra.dst != nullptr && !(me == root && ra.dst == ra.src);
+  // Tiles of chunk c that belong to this block: t = first(c), first(c) + grid, ...; tile t is owned by rank (t / grid) % n.
+  auto chunk_lo = [&](int c) { return ntiles * static_cast<uint64_t>(c) / nchunks; };
+  auto first_of = [&](uint64_t t_lo) { return t_lo + (static_cast<uint64_t>(block) + grid - t_lo % grid) % grid; };
+
+  bool ok = BlockBarrier(ctx, channel, block, epoch, 1);  // the windows are free
+  for (int it = 0; it < nchunks + 2; ++it) {
+    if (ok && me == root && it < nchunks) {
+      const uint64_t t_lo = chunk_lo(it), t_hi = chunk_lo(it + 1);
+      for (uint64_t t = first_of(t_lo); t < t_hi; t += grid) {
+        const int owner   = static_cast<int>((t / grid) % n);
+        const uint64_t lo = t * kCopyTile;
+        const uint64_t hi = lo + kCopyTile < nvec ? lo + kCopyTile : nvec;
+        for (uint64_t v0 = lo + threadIdx.x; v0 < hi; v0 += static_cast<uint64_t>(blockDim.x) * kCopyUnroll) {
+          U4 q[kCopyUnroll];
+#pragma unroll
+          for (int u = 0; u < kCopyUnroll; ++u) {
+            const uint64_t v = v0 + static_cast<uint64_t>(u) * blockDim.x;
+            if (v < hi) q[u] = LoadVecBytes(ra.src, v, nbytes, src_aligned);
+          }
+#pragma unroll
+          for (int u = 0; u < kCopyUnroll; ++u) {
+            const uint64_t v = v0 + static_cast<uint64_t>(u) * blockDim.x;
+            if (v >= hi) continue;
+            const uint64_t off = ra.win_off + v * 16;
+            if (owner != root) {
+              StSys(ctx.peer[owner] + off, q[u]);
+            } else if (kMultimem) {
+              MultimemSt(ctx.mc + off, q[u]);
+            } else {
+#pragma unroll
+              for (int r = 1; r < kMaxRanks; ++r)
+                if (r < n) StSys(ctx.peer[(me + r) % n] + off, q[u]);
+            }
+            if (write_dst) StoreVecBytes(ra.dst, v, nbytes, dst_aligned, q[u]);
+          }
+        }
+      }
+    }
+    if (ok && me != root) {
+      if (it >= 1 && it <= nchunks) {  // forward my tiles of chunk it-1
+        const uint64_t t_lo = chunk_lo(it - 1), t_hi = chunk_lo(it);
+        for (uint64_t t = first_of(t_lo); t < t_hi; t += grid) {
+          if (static_cast<int>((t / grid) % n) != me) continue;
+          const uint64_t lo = t * kCopyTile;
+          const uint64_t hi = lo + kCopyTile < nvec ? lo + kCopyTile : nvec;
+          for (uint64_t v0 = lo + threadIdx.x; v0 < hi; v0 += static_cast<uint64_t>(blockDim.x) * kCopyUnroll) {
+            U4 q[kCopyUnroll];
+#pragma unroll
+            for (int u = 0; u < kCopyUnroll; ++u) {
+              const uint64_t v = v0 + static_cast<uint64_t>(u) * blockDim.x;
+              if (v < hi) q[u] = *reinterpret_cast<const U4*>(my_win + v * 16);
+            }
+#pragma unroll
+            for (int u = 0; u < kCopyUnroll; ++u) {
+              const uint64_t v = v0 + static_cast<uint64_t>(u) * blockDim.x;
+              if (v >= hi) continue;
+              const uint64_t off = ra.win_off + v * 16;
+              if (kMultimem) {
+                MultimemSt(ctx.mc + off, q[u]);  // also lands in the root's window and in mine: same bytes, unread
+              } else {
+#pragma unroll
+                for (int r = 1; r < kMaxRanks; ++r) {
+                  const int to = (me + r) % n;
+                  if (r < n && to != root) StSys(ctx.peer[to] + off, q[u]);
+                }
+              }
+              if (write_dst) StoreVecBytes(ra.dst, v, nbytes, dst_aligned, q[u]);
+            }
+          }
+        }
+      }
+      if (it >= 2 && write_dst) {  // the others' tiles of chunk it-2 have arrived in my window
+        const uint64_t t_lo = chunk_lo(it - 2), t_hi = chunk_lo(it - 1);
+        for (uint64_t t = first_of(t_lo); t < t_hi; t += grid) {
+          if (static_cast<int>((t / grid) % n) == me) continue;
+          const uint64_t lo = t * kCopyTile;
+          const uint64_t hi = lo + kCopyTile < nvec ? lo + kCopyTile : nvec;
+          for (uint64_t v0 = lo + threadIdx.x; v0 < hi; v0 += static_cast<uint64_t>(blockDim.x) * kCopyUnroll) {
+            U4 q[kCopyUnroll];
+#pragma unroll
+            for (int u = 0; u < kCopyUnroll; ++u) {
+              const uint64_t v = v0 + static_cast<uint64_t>(u) * blockDim.x;
+              if (v < hi) q[u] = *reinterpret_cast<const U4*>(my_win + v * 16);
+            }
+#pragma unroll
+            for (int u = 0; u < kCopyUnroll; ++u) {
+              const uint64_t v = v0 + static_cast<uint64_t>(u) * blockDim.x;
+              if (v < hi) StoreVecBytes(ra.dst, v, nbytes, dst_aligned, q[u]);
+            }
+          }
+        }
+      }
+    }
+    ok = BlockBarrier(ctx, channel, block, epoch + 1 + it, 2) && ok;
+  }
+  SaveEpoch(ctx, channel, block, epoch + 2 + nchunks);
+}
+
 // Broadcast: the root writes its data into every rank's window (one multimem store per vector, or one P2P store per
 // peer), then everyone copies from its own window to its output.  The message can be cut into chunks with a barrier
 // after each, so that the other ranks copy chunk c out of their windows while the root stores chunk c+1; the root
@@ -593,6 +818,11 @@ struct CommState {
   CommStatus* status_host = nullptr;
   int blocks = 32;
   size_t one_shot_bytes = 512 << 10;
+  // kernel selection (tipsk_comm_set_option; the environment gives the initial values)
+  uint64_t allgather_push_bytes = 32ull << 20;   // gathered size up to which the pushing allgather runs (0: never)
+  uint64_t bcast_scatter_bytes  = 2ull << 20;    // message size from which broadcast runs as scatter + allgather (0: never)
+  uint64_t bcast_scatter_chunk  = 8ull << 20;    // its pipeline chunk
+  int bcast_scatter_min_ranks   = 3;
   bool use_multimem = false;
   std::vector<cudaEvent_t> event_pool;
   std::mutex mu;
@@ -786,6 +1016,22 @@ int AllgathervOn(const CommView& vw, const void* const* srcs, void* const* dsts,
   }
   const uint64_t chunk = vw.stage_bytes;
   TIPSK_REQUIRE(chunk >= 4096, "allgatherv: no staging area configured");
+  // Small gathers are pushed (see AllgatherPushKernel): everything has to fit the staging area at once.
+  const uint64_t push_limit = st.allgather_push_bytes;
+  uint64_t padded = 0;
+  for (int r = 0; r < n; ++r) padded += (bytes_per_rank[r] + 15) & ~15ull;
+  if (padded > 0 && padded <= push_limit && padded <= chunk) {
+    GatherSizes gs;
+    memset(&gs, 0, sizeof(gs));
+    for (int r = 0; r < n; ++r) {
+      gs.bytes[r] = bytes_per_rank[r];
+      gs.displ[r] = displ[r];
+    }
+    CommLaunch l = MakeLaunch(vw, srcs, dsts, vw.stage_off);
+    const int grid = GridFor(largest, static_cast<uint64_t>(kPushTile) * 16, st.blocks);
+    return vw.multimem ? LaunchComm(vw, AllgatherPushKernel<true>, grid, s, l, channel, gs)
+                       : LaunchComm(vw, AllgatherPushKernel<false>, grid, s, l, channel, gs);
+  }
   for (uint64_t done = 0; done < largest; done += chunk) {
     GatherSizes gs;
     memset(&gs, 0, sizeof(gs));
@@ -833,6 +1079,16 @@ int BroadcastOn(const CommView& vw, const void* const* srcs, void* const* dsts, 
       const uint64_t v = e ? strtoull(e, nullptr, 10) : 0;
       return v >= 4096 ? v : (32ull << 20);
     }();
+    // Large messages go as scatter + allgather (see BroadcastScatterKernel), with three or more ranks by default.
+    const uint64_t scatter_min = st.bcast_scatter_bytes, scatter_chunk = st.bcast_scatter_chunk;
+    if (scatter_min > 0 && len >= scatter_min && vw.nranks >= st.bcast_scatter_min_ranks) {
+      int nc = static_cast<int>(len / scatter_chunk);
+      nc     = nc < 1 ? 1 : (nc > 64 ? 64 : nc);
+      int rc = vw.multimem ? LaunchComm(vw, BroadcastScatterKernel<true>, grid, s, l, channel, len, root, nc)
+                           : LaunchComm(vw, BroadcastScatterKernel<false>, grid, s, l, channel, len, root, nc);
+      if (rc) return rc;
+      continue;
+    }
     int nchunks = static_cast<int>(len / chunk_bytes);
     nchunks = nchunks < 1 ? 1 : (nchunks > 16 ? 16 : nchunks);
     int rc = vw.multimem ? LaunchComm(vw, BroadcastKernel<true>, grid, s, l, channel, len, root, nchunks)
@@ -911,6 +1167,17 @@ int tipsk_comm_init(int rank, int nranks, void* const* peer_windows, void* multi
     if (st.blocks > cap) st.blocks = cap;
   }
   st.one_shot_bytes = one_shot_bytes;
+  {
+    auto env_u64 = [](const char* name, uint64_t dflt) {
+      const char* e = getenv(name);
+      return e ? strtoull(e, nullptr, 10) : dflt;
+    };
+    st.allgather_push_bytes    = env_u64("TIPS_ALLGATHER_PUSH_BYTES", 32ull << 20);
+    st.bcast_scatter_bytes     = env_u64("TIPS_BCAST_SCATTER_BYTES", 2ull << 20);
+    st.bcast_scatter_chunk     = env_u64("TIPS_BCAST_SCATTER_CHUNK_BYTES", 8ull << 20);
+    st.bcast_scatter_min_ranks = static_cast<int>(env_u64("TIPS_BCAST_SCATTER_MIN_RANKS", 3));
+    if (st.bcast_scatter_chunk < 65536) st.bcast_scatter_chunk = 65536;
+  }
   st.use_multimem  = use_multimem && multicast_window != nullptr && !emulated;
   if (!st.status_host) {
     TIPSK_CUDA(cudaHostAlloc(reinterpret_cast<void**>(&st.status_host), sizeof(CommStatus) * kMaxRanks,
@@ -971,6 +1238,22 @@ int tipsk_comm_shutdown(void) {
         if (e) cudaFree(e);
     g_groups.clear();
   }
+  return 0;
+}
+
+/* Kernel selection at run time (every rank sets the same values, between collectives):
+ *   allgather_push_bytes       gathered size up to which allgatherv pushes instead of pulling (0: never)
+ *   bcast_scatter_bytes        message size from which broadcast runs as scatter + allgather (0: never)
+ *   bcast_scatter_chunk_bytes  pipeline chunk of that kernel (>= 64 KiB)
+ *   bcast_scatter_min_ranks    fewest ranks for which it is used (>= 2) */
+int tipsk_comm_set_option(const char* name, uint64_t value) {
+  CommState& st = g_comm;
+  const std::string key = name ? name : "";
+  if (key == "allgather_push_bytes") st.allgather_push_bytes = value;
+  else if (key == "bcast_scatter_bytes") st.bcast_scatter_bytes = value;
+  else if (key == "bcast_scatter_chunk_bytes") st.bcast_scatter_chunk = value < 65536 ? 65536 : value;
+  else if (key == "bcast_scatter_min_ranks") st.bcast_scatter_min_ranks = value < 2 ? 2 : static_cast<int>(value);
+  else return SetError(-2, "comm option: unknown name");
   return 0;
 }
 

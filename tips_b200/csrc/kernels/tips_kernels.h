@@ -150,6 +150,7 @@ int tipsk_group_allgatherv(int64_t id, const void* const* host_srcs, void* const
 int tipsk_group_broadcast(int64_t id, const void* const* host_srcs, void* const* host_dsts, uint64_t nbytes, int root,
                           void* stream);
 uint64_t tipsk_comm_flag_bytes(void);
+int tipsk_comm_set_option(const char* name, uint64_t value);
 /* Allreduce fused with the optimizer step on the share of the parameters each rank owns (see comm.cu). */
 int tipsk_comm_update_subtile(void);
 int64_t tipsk_comm_update_shard_vecs(uint64_t nbytes);

@@ -49,6 +49,8 @@ def main():
     # two ranks too), an odd byte count, every root
     lib = tips._lib.kernels()
     assert lib.tipsk_comm_set_option(b"bcast_scatter_min_ranks", 2) == 0
+    assert lib.tipsk_comm_set_option(b"bcast_scatter_bytes", 1 << 20) == 0
+    assert lib.tipsk_comm_set_option(b"bcast_scatter_chunk_bytes", 4 << 20) == 0
     g = tips.allgather(torch.full(((rank + 1) * 3_000_001,), float(rank), device=dev))
     off = 0
     for r in range(size):

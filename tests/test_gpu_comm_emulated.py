@@ -142,7 +142,7 @@ def test_allgatherv_pushed_and_pulled(comm4, push):
                 assert torch.equal(o, ref), (sizes, i)
                 assert bool((r[3 * (i % 2) + total:] == 0xEE).all()) and bool((r[:3 * (i % 2)] == 0xEE).all())
     finally:
-        _check(lib, lib.tipsk_comm_set_option(b"allgather_push_bytes", 32 << 20))
+        _check(lib, lib.tipsk_comm_set_option(b"allgather_push_bytes", 2 << 20))
 
 
 @pytest.mark.parametrize("chunk", [65536, 1 << 20, 8 << 20])
@@ -153,6 +153,7 @@ def test_broadcast_scatter_then_allgather(comm4, chunk):
     st, lib = comm4
     dev = st.device
     _check(lib, lib.tipsk_comm_set_option(b"bcast_scatter_bytes", 1 << 20))
+    _check(lib, lib.tipsk_comm_set_option(b"bcast_scatter_min_ranks", 2))
     _check(lib, lib.tipsk_comm_set_option(b"bcast_scatter_chunk_bytes", chunk))
     try:
         for nbytes, root, shift in [(1 << 20, 0, 0), ((3 << 20) + 7, 1, 0), ((2 << 20) + 4097, 3, 5),
@@ -179,8 +180,9 @@ def test_broadcast_scatter_then_allgather(comm4, chunk):
         for b in buf:
             assert torch.equal(b, want)
     finally:
-        _check(lib, lib.tipsk_comm_set_option(b"bcast_scatter_bytes", 2 << 20))
-        _check(lib, lib.tipsk_comm_set_option(b"bcast_scatter_chunk_bytes", 8 << 20))
+        _check(lib, lib.tipsk_comm_set_option(b"bcast_scatter_bytes", 128 << 20))
+        _check(lib, lib.tipsk_comm_set_option(b"bcast_scatter_min_ranks", 8))
+        _check(lib, lib.tipsk_comm_set_option(b"bcast_scatter_chunk_bytes", 32 << 20))
 
 
 def _reference_step(kind, w, state, g, step, hp):

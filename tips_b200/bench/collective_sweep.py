@@ -59,8 +59,9 @@ def main(argv=None):
     ap.add_argument("--min-kb", type=int, default=1)
     ap.add_argument("--dtypes", default="fp32,bf16")
     ap.add_argument("--ops", default="allreduce,allgather,broadcast")
-    ap.add_argument("--scatter-chunks-mb", default="", help="also time the scatter broadcast with these pipeline "
+    ap.add_argument("--scatter-chunks-mb", default="32", help="also time the scatter broadcast with these pipeline "
                     "chunk sizes, e.g. 2,4,16")
+    ap.add_argument("--verify", type=int, default=1, help="compare the alternative kernels' results with NCCL's")
     ap.add_argument("--out", default="")
     a = ap.parse_args(argv)
     tips.init()
@@ -114,12 +115,20 @@ def main(argv=None):
                 ms = _time(_checked(lib, lambda: lib.tipsk_allgatherv(srcs, dsts, per, 3, stream)), iters)
                 res["allgather_ms"] = ms
                 res["allgather_busbw"] = nbytes * n / ms / 1e6 * (n - 1) / n
-                if nbytes * n <= (32 << 20):
-                    # the same gather through the pulling kernel, which larger slabs use
+                if nbytes * n <= (64 << 20):
+                    # the same gather through each of the two kernels (slabs of up to 2 MiB are pushed by default)
                     _opt(lib, "allgather_push_bytes", 0)
                     ms = _time(_checked(lib, lambda: lib.tipsk_allgatherv(srcs, dsts, per, 3, stream)), iters)
-                    _opt(lib, "allgather_push_bytes", 32 << 20)
                     res["allgather_pull_busbw"] = nbytes * n / ms / 1e6 * (n - 1) / n
+                    _opt(lib, "allgather_push_bytes", 256 << 20)
+                    ms = _time(_checked(lib, lambda: lib.tipsk_allgatherv(srcs, dsts, per, 3, stream)), iters)
+                    res["allgather_push_busbw"] = nbytes * n / ms / 1e6 * (n - 1) / n
+                    if a.verify:
+                        want = torch.empty_like(out)
+                        dist.all_gather_into_tensor(want, x)
+                        if not torch.equal(out, want):
+                            raise RuntimeError(f"pushed allgather of {nbytes} bytes per rank is wrong")
+                    _opt(lib, "allgather_push_bytes", 2 << 20)
                 ms = _time(lambda: dist.all_gather_into_tensor(out, x), iters)
                 res["nccl_allgather_busbw"] = nbytes * n / ms / 1e6 * (n - 1) / n
                 del out
@@ -129,19 +138,28 @@ def main(argv=None):
                 ms = _time(_checked(lib, lambda: lib.tipsk_broadcast(srcs, dsts, nbytes, 0, 3, stream)), iters)
                 res["broadcast_ms"] = ms
                 res["broadcast_gbs"] = nbytes / ms / 1e6
+                ms = _time(lambda: dist.broadcast(x, 0), iters)
+                res["nccl_broadcast_gbs"] = nbytes / ms / 1e6
                 if nbytes >= (2 << 20) and n >= 3:
-                    # the same message stored to everybody by the root alone (what smaller messages use)
+                    # the same message stored to everybody by the root alone, and as scatter + allgather with
+                    # several pipeline chunk sizes (by default: with 8 ranks, from 128 MiB on, 32 MiB chunks)
                     _opt(lib, "bcast_scatter_bytes", 0)
                     ms = _time(_checked(lib, lambda: lib.tipsk_broadcast(srcs, dsts, nbytes, 0, 3, stream)), iters)
-                    _opt(lib, "bcast_scatter_bytes", 2 << 20)
                     res["broadcast_direct_gbs"] = nbytes / ms / 1e6
+                    _opt(lib, "bcast_scatter_bytes", 2 << 20)
+                    _opt(lib, "bcast_scatter_min_ranks", 3)
                     for mb in [int(c) for c in a.scatter_chunks_mb.split(",") if c]:
                         _opt(lib, "bcast_scatter_chunk_bytes", mb << 20)
                         ms = _time(_checked(lib, lambda: lib.tipsk_broadcast(srcs, dsts, nbytes, 0, 3, stream)), iters)
-                        res[f"broadcast_gbs_chunk{mb}mb"] = nbytes / ms / 1e6
-                    _opt(lib, "bcast_scatter_chunk_bytes", 8 << 20)
-                ms = _time(lambda: dist.broadcast(x, 0), iters)
-                res["nccl_broadcast_gbs"] = nbytes / ms / 1e6
+                        res[f"broadcast_scatter_gbs_chunk{mb}mb"] = nbytes / ms / 1e6
+                        if a.verify:
+                            want = x.clone()
+                            dist.broadcast(want, 0)
+                            if not torch.equal(y, want):
+                                raise RuntimeError(f"scatter broadcast of {nbytes} bytes (chunk {mb} MiB) is wrong")
+                    _opt(lib, "bcast_scatter_chunk_bytes", 32 << 20)
+                    _opt(lib, "bcast_scatter_bytes", 128 << 20)
+                    _opt(lib, "bcast_scatter_min_ranks", 8)
             if "update" in a.ops and 16 <= nbytes <= upd_max:
                 # allreduce + Adam as two kernels on full-size state, against the one kernel that reduces this
                 # rank's share, updates 1/n of the state and stores the parameters to every rank

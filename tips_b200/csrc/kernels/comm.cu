@@ -493,7 +493,8 @@ __device__ __forceinline__ void StoreVecBytes(char* base, uint64_t v, uint64_t n
 // the window and, above all, the chain of peer loads that a block walks rank after rank: with slabs of a few
 // hundred KB that chain, not the bytes, is the time.  Tiles are small so that a 64 KB slab already spreads over
 // several blocks.  Tile t of every slab belongs to block t % grid on every rank, for the stores and for the copy.
-constexpr int kPushTile = kCommThreads * 2;  // vectors (16 KB)
+constexpr int kPushUnroll = 1;
+constexpr int kPushTile   = kCommThreads * kPushUnroll;  // vectors (8 KB)
 
 template <bool kMultimem>
 __global__ void __launch_bounds__(kCommThreads)
@@ -522,14 +523,14 @@ AllgatherPushKernel(CommLaunch args, int channel, GatherSizes sizes) {
     for (uint64_t t = block; t < ntiles; t += gridDim.x) {
       const uint64_t lo = t * kPushTile;
       const uint64_t hi = lo + kPushTile < nvec ? lo + kPushTile : nvec;
-      U4 q[2];
+      U4 q[kPushUnroll];
 #pragma unroll
-      for (int u = 0; u < 2; ++u) {
+      for (int u = 0; u < kPushUnroll; ++u) {
         const uint64_t v = lo + threadIdx.x + static_cast<uint64_t>(u) * blockDim.x;
         if (v < hi) q[u] = LoadVecBytes(ra.src, v, bytes, aligned);
       }
 #pragma unroll
-      for (int u = 0; u < 2; ++u) {
+      for (int u = 0; u < kPushUnroll; ++u) {
         const uint64_t v = lo + threadIdx.x + static_cast<uint64_t>(u) * blockDim.x;
         if (v >= hi) continue;
         if (kMultimem) {
@@ -554,14 +555,14 @@ AllgatherPushKernel(CommLaunch args, int channel, GatherSizes sizes) {
       for (uint64_t t = block; t < ntiles; t += gridDim.x) {
         const uint64_t lo = t * kPushTile;
         const uint64_t hi = lo + kPushTile < nvec ? lo + kPushTile : nvec;
-        U4 q[2];
+        U4 q[kPushUnroll];
 #pragma unroll
-        for (int u = 0; u < 2; ++u) {
+        for (int u = 0; u < kPushUnroll; ++u) {
           const uint64_t v = lo + threadIdx.x + static_cast<uint64_t>(u) * blockDim.x;
           if (v < hi) q[u] = *reinterpret_cast<const U4*>(from + v * 16);
         }
 #pragma unroll
-        for (int u = 0; u < 2; ++u) {
+        for (int u = 0; u < kPushUnroll; ++u) {
           const uint64_t v = lo + threadIdx.x + static_cast<uint64_t>(u) * blockDim.x;
           if (v < hi) StoreVecBytes(to, v, bytes, aligned, q[u]);
         }
@@ -580,7 +581,13 @@ AllgatherPushKernel(CommLaunch args, int channel, GatherSizes sizes) {
 //   step i:  root      scatters chunk i                                  (S)
 //            the rest  forward their tiles of chunk i-1 to everybody      (G)  and write them to their output,
 //                      copy the other tiles of chunk i-2 from their own window to their output  (C)
+// G waits on the links and C on local memory, so half of the block's threads do one and half the other.
 // The root writes its output from the registers it sends; tiles the root owns itself go to everybody at once.
+// A barrier drains the block's stores and waits for the slowest rank, and a block moves nothing meanwhile; blocks
+// only meet the same block of the other ranks, so the blocks run in four lanes whose chunk boundaries are a
+// quarter of a chunk apart: while one lane waits the other three keep the links busy.
+constexpr int kBcastLanes = 4;
+
 template <bool kMultimem>
 __global__ void __launch_bounds__(kCommThreads)
 BroadcastScatterKernel(CommLaunch args, int channel, uint64_t nbytes, int root, int nchunks) {
@@ -597,102 +604,106 @@ BroadcastScatterKernel(CommLaunch args, int channel, uint64_t nbytes, int root, 
   const bool src_aligned = me == root && (reinterpret_cast<uintptr_t>(ra.src) & 15) == 0;
   const bool dst_aligned = ra.dst != nullptr && (reinterpret_cast<uintptr_t>(ra.dst) & 15) == 0;
   const bool write_dst   = ra.dst != nullptr && !(me == root && ra.dst == ra.src);
-  // Tiles of chunk c that belong to this block: t = first(c), first(c) + grid, ...; tile t is owned by rank (t / grid) % n.
-  auto chunk_lo = [&](int c) { return ntiles * static_cast<uint64_t>(c) / nchunks; };
+  // Chunks of this block's lane: [lo(c), lo(c+1)) in tiles; the first chunk of lanes 1..3 is shorter.
+  const int lane           = block % kBcastLanes;
+  const uint64_t per_chunk = (ntiles + nchunks - 1) / nchunks;
+  const uint64_t shift     = per_chunk * lane / kBcastLanes;
+  const int my_chunks      = static_cast<int>((ntiles + shift + per_chunk - 1) / per_chunk);
+  auto chunk_lo = [&](int c) {
+    if (c <= 0) return static_cast<uint64_t>(0);
+    const uint64_t at = per_chunk * c - shift;
+    return at < ntiles ? at : ntiles;
+  };
+  // Tiles of [t_lo, t_hi) that belong to this block are first, first + grid, ...; tile t is owned by rank (t / grid) % n.
   auto first_of = [&](uint64_t t_lo) { return t_lo + (static_cast<uint64_t>(block) + grid - t_lo % grid) % grid; };
 
-  bool ok = BlockBarrier(ctx, channel, block, epoch, 1);  // the windows are free
-  for (int it = 0; it < nchunks + 2; ++it) {
-    if (ok && me == root && it < nchunks) {
-      const uint64_t t_lo = chunk_lo(it), t_hi = chunk_lo(it + 1);
-      for (uint64_t t = first_of(t_lo); t < t_hi; t += grid) {
-        const int owner   = static_cast<int>((t / grid) % n);
-        const uint64_t lo = t * kCopyTile;
-        const uint64_t hi = lo + kCopyTile < nvec ? lo + kCopyTile : nvec;
-        for (uint64_t v0 = lo + threadIdx.x; v0 < hi; v0 += static_cast<uint64_t>(blockDim.x) * kCopyUnroll) {
-          U4 q[kCopyUnroll];
+  // S: the root reads a tile of its input and sends it to the tile's owner.
+  auto scatter = [&](uint64_t t_lo, uint64_t t_hi) {
+    for (uint64_t t = first_of(t_lo); t < t_hi; t += grid) {
+      const int owner   = static_cast<int>((t / grid) % n);
+      const uint64_t lo = t * kCopyTile;
+      const uint64_t hi = lo + kCopyTile < nvec ? lo + kCopyTile : nvec;
+      for (uint64_t v0 = lo + threadIdx.x; v0 < hi; v0 += static_cast<uint64_t>(blockDim.x) * kCopyUnroll) {
+        U4 q[kCopyUnroll];
 #pragma unroll
-          for (int u = 0; u < kCopyUnroll; ++u) {
-            const uint64_t v = v0 + static_cast<uint64_t>(u) * blockDim.x;
-            if (v < hi) q[u] = LoadVecBytes(ra.src, v, nbytes, src_aligned);
+        for (int u = 0; u < kCopyUnroll; ++u) {
+          const uint64_t v = v0 + static_cast<uint64_t>(u) * blockDim.x;
+          if (v < hi) q[u] = LoadVecBytes(ra.src, v, nbytes, src_aligned);
+        }
+#pragma unroll
+        for (int u = 0; u < kCopyUnroll; ++u) {
+          const uint64_t v = v0 + static_cast<uint64_t>(u) * blockDim.x;
+          if (v >= hi) continue;
+          const uint64_t off = ra.win_off + v * 16;
+          if (owner != root) {
+            StSys(ctx.peer[owner] + off, q[u]);
+          } else if (kMultimem) {
+            MultimemSt(ctx.mc + off, q[u]);
+          } else {
+#pragma unroll
+            for (int r = 1; r < kMaxRanks; ++r)
+              if (r < n) StSys(ctx.peer[(me + r) % n] + off, q[u]);
           }
-#pragma unroll
-          for (int u = 0; u < kCopyUnroll; ++u) {
-            const uint64_t v = v0 + static_cast<uint64_t>(u) * blockDim.x;
-            if (v >= hi) continue;
-            const uint64_t off = ra.win_off + v * 16;
-            if (owner != root) {
-              StSys(ctx.peer[owner] + off, q[u]);
-            } else if (kMultimem) {
-              MultimemSt(ctx.mc + off, q[u]);
-            } else {
-#pragma unroll
-              for (int r = 1; r < kMaxRanks; ++r)
-                if (r < n) StSys(ctx.peer[(me + r) % n] + off, q[u]);
-            }
-            if (write_dst) StoreVecBytes(ra.dst, v, nbytes, dst_aligned, q[u]);
-          }
+          if (write_dst) StoreVecBytes(ra.dst, v, nbytes, dst_aligned, q[u]);
         }
       }
     }
-    if (ok && me != root) {
-      if (it >= 1 && it <= nchunks) {  // forward my tiles of chunk it-1
-        const uint64_t t_lo = chunk_lo(it - 1), t_hi = chunk_lo(it);
-        for (uint64_t t = first_of(t_lo); t < t_hi; t += grid) {
-          if (static_cast<int>((t / grid) % n) != me) continue;
-          const uint64_t lo = t * kCopyTile;
-          const uint64_t hi = lo + kCopyTile < nvec ? lo + kCopyTile : nvec;
-          for (uint64_t v0 = lo + threadIdx.x; v0 < hi; v0 += static_cast<uint64_t>(blockDim.x) * kCopyUnroll) {
-            U4 q[kCopyUnroll];
+  };
+  // G (forward = true): my tiles go from my window to everybody and to my output.
+  // C (forward = false): the others' tiles go from my window to my output.  `tid` of `nthr` threads take part.
+  auto drain = [&](uint64_t t_lo, uint64_t t_hi, bool forward, int tid, int nthr) {
+    for (uint64_t t = first_of(t_lo); t < t_hi; t += grid) {
+      if ((static_cast<int>((t / grid) % n) == me) != forward) continue;
+      const uint64_t lo = t * kCopyTile;
+      const uint64_t hi = lo + kCopyTile < nvec ? lo + kCopyTile : nvec;
+      for (uint64_t v0 = lo + tid; v0 < hi; v0 += static_cast<uint64_t>(nthr) * kCopyUnroll) {
+        U4 q[kCopyUnroll];
 #pragma unroll
-            for (int u = 0; u < kCopyUnroll; ++u) {
-              const uint64_t v = v0 + static_cast<uint64_t>(u) * blockDim.x;
-              if (v < hi) q[u] = *reinterpret_cast<const U4*>(my_win + v * 16);
-            }
+        for (int u = 0; u < kCopyUnroll; ++u) {
+          const uint64_t v = v0 + static_cast<uint64_t>(u) * nthr;
+          if (v < hi) q[u] = *reinterpret_cast<const U4*>(my_win + v * 16);
+        }
 #pragma unroll
-            for (int u = 0; u < kCopyUnroll; ++u) {
-              const uint64_t v = v0 + static_cast<uint64_t>(u) * blockDim.x;
-              if (v >= hi) continue;
-              const uint64_t off = ra.win_off + v * 16;
-              if (kMultimem) {
-                MultimemSt(ctx.mc + off, q[u]);  // also lands in the root's window and in mine: same bytes, unread
-              } else {
+        for (int u = 0; u < kCopyUnroll; ++u) {
+          const uint64_t v = v0 + static_cast<uint64_t>(u) * nthr;
+          if (v >= hi) continue;
+          if (forward) {
+            const uint64_t off = ra.win_off + v * 16;
+            if (kMultimem) {
+              MultimemSt(ctx.mc + off, q[u]);  // also lands in the root's window and in mine: same bytes, unread
+            } else {
 #pragma unroll
-                for (int r = 1; r < kMaxRanks; ++r) {
-                  const int to = (me + r) % n;
-                  if (r < n && to != root) StSys(ctx.peer[to] + off, q[u]);
-                }
+              for (int r = 1; r < kMaxRanks; ++r) {
+                const int to = (me + r) % n;
+                if (r < n && to != root) StSys(ctx.peer[to] + off, q[u]);
               }
-              if (write_dst) StoreVecBytes(ra.dst, v, nbytes, dst_aligned, q[u]);
             }
           }
+          if (write_dst) StoreVecBytes(ra.dst, v, nbytes, dst_aligned, q[u]);
         }
       }
-      if (it >= 2 && write_dst) {  // the others' tiles of chunk it-2 have arrived in my window
-        const uint64_t t_lo = chunk_lo(it - 2), t_hi = chunk_lo(it - 1);
-        for (uint64_t t = first_of(t_lo); t < t_hi; t += grid) {
-          if (static_cast<int>((t / grid) % n) == me) continue;
-          const uint64_t lo = t * kCopyTile;
-          const uint64_t hi = lo + kCopyTile < nvec ? lo + kCopyTile : nvec;
-          for (uint64_t v0 = lo + threadIdx.x; v0 < hi; v0 += static_cast<uint64_t>(blockDim.x) * kCopyUnroll) {
-            U4 q[kCopyUnroll];
-#pragma unroll
-            for (int u = 0; u < kCopyUnroll; ++u) {
-              const uint64_t v = v0 + static_cast<uint64_t>(u) * blockDim.x;
-              if (v < hi) q[u] = *reinterpret_cast<const U4*>(my_win + v * 16);
-            }
-#pragma unroll
-            for (int u = 0; u < kCopyUnroll; ++u) {
-              const uint64_t v = v0 + static_cast<uint64_t>(u) * blockDim.x;
-              if (v < hi) StoreVecBytes(ra.dst, v, nbytes, dst_aligned, q[u]);
-            }
-          }
-        }
+    }
+  };
+
+  bool ok = BlockBarrier(ctx, channel, block, epoch, 1);  // the windows are free
+  for (int it = 0; it < my_chunks + 2; ++it) {
+    if (ok && me == root && it < my_chunks) scatter(chunk_lo(it), chunk_lo(it + 1));
+    if (ok && me != root) {
+      const bool has_g = it >= 1 && it <= my_chunks;
+      const bool has_c = it >= 2 && write_dst;
+      const int half   = blockDim.x / 2;
+      if (has_g && has_c) {
+        if (static_cast<int>(threadIdx.x) < half) drain(chunk_lo(it - 1), chunk_lo(it), true, threadIdx.x, half);
+        else drain(chunk_lo(it - 2), chunk_lo(it - 1), false, threadIdx.x - half, blockDim.x - half);
+      } else if (has_g) {
+        drain(chunk_lo(it - 1), chunk_lo(it), true, threadIdx.x, blockDim.x);
+      } else if (has_c) {
+        drain(chunk_lo(it - 2), chunk_lo(it - 1), false, threadIdx.x, blockDim.x);
       }
     }
     ok = BlockBarrier(ctx, channel, block, epoch + 1 + it, 2) && ok;
   }
-  SaveEpoch(ctx, channel, block, epoch + 2 + nchunks);
+  SaveEpoch(ctx, channel, block, epoch + 2 + my_chunks);
 }
 
 // Broadcast: the root writes its data into every rank's window (one multimem store per vector, or one P2P store per
@@ -819,10 +830,10 @@ struct CommState {
   int blocks = 32;
   size_t one_shot_bytes = 512 << 10;
   // kernel selection (tipsk_comm_set_option; the environment gives the initial values)
-  uint64_t allgather_push_bytes = 32ull << 20;   // gathered size up to which the pushing allgather runs (0: never)
-  uint64_t bcast_scatter_bytes  = 2ull << 20;    // message size from which broadcast runs as scatter + allgather (0: never)
-  uint64_t bcast_scatter_chunk  = 8ull << 20;    // its pipeline chunk
-  int bcast_scatter_min_ranks   = 3;
+  uint64_t allgather_push_bytes = 2ull << 20;    // largest slab up to which the pushing allgather runs (0: never)
+  uint64_t bcast_scatter_bytes  = 128ull << 20;   // message size from which broadcast runs as scatter + allgather (0: never)
+  uint64_t bcast_scatter_chunk  = 32ull << 20;   // its pipeline chunk
+  int bcast_scatter_min_ranks   = 8;
   bool use_multimem = false;
   std::vector<cudaEvent_t> event_pool;
   std::mutex mu;
@@ -1020,7 +1031,7 @@ int AllgathervOn(const CommView& vw, const void* const* srcs, void* const* dsts,
   const uint64_t push_limit = st.allgather_push_bytes;
   uint64_t padded = 0;
   for (int r = 0; r < n; ++r) padded += (bytes_per_rank[r] + 15) & ~15ull;
-  if (padded > 0 && padded <= push_limit && padded <= chunk) {
+  if (padded > 0 && largest <= push_limit && padded <= chunk) {
     GatherSizes gs;
     memset(&gs, 0, sizeof(gs));
     for (int r = 0; r < n; ++r) {
@@ -1079,7 +1090,8 @@ int BroadcastOn(const CommView& vw, const void* const* srcs, void* const* dsts, 
       const uint64_t v = e ? strtoull(e, nullptr, 10) : 0;
       return v >= 4096 ? v : (32ull << 20);
     }();
-    // Large messages go as scatter + allgather (see BroadcastScatterKernel), with three or more ranks by default.
+    // Large messages go as scatter + allgather (see BroadcastScatterKernel).  Measured: with 8 ranks it passes the
+    // root-stores-everything kernel from 128 MiB on (400 against 350 GB/s at 1 GiB); with 4 ranks it stays behind.
     const uint64_t scatter_min = st.bcast_scatter_bytes, scatter_chunk = st.bcast_scatter_chunk;
     if (scatter_min > 0 && len >= scatter_min && vw.nranks >= st.bcast_scatter_min_ranks) {
       int nc = static_cast<int>(len / scatter_chunk);
@@ -1172,10 +1184,10 @@ int tipsk_comm_init(int rank, int nranks, void* const* peer_windows, void* multi
       const char* e = getenv(name);
       return e ? strtoull(e, nullptr, 10) : dflt;
     };
-    st.allgather_push_bytes    = env_u64("TIPS_ALLGATHER_PUSH_BYTES", 32ull << 20);
-    st.bcast_scatter_bytes     = env_u64("TIPS_BCAST_SCATTER_BYTES", 2ull << 20);
-    st.bcast_scatter_chunk     = env_u64("TIPS_BCAST_SCATTER_CHUNK_BYTES", 8ull << 20);
-    st.bcast_scatter_min_ranks = static_cast<int>(env_u64("TIPS_BCAST_SCATTER_MIN_RANKS", 3));
+    st.allgather_push_bytes    = env_u64("TIPS_ALLGATHER_PUSH_BYTES", 2ull << 20);
+    st.bcast_scatter_bytes     = env_u64("TIPS_BCAST_SCATTER_BYTES", 128ull << 20);
+    st.bcast_scatter_chunk     = env_u64("TIPS_BCAST_SCATTER_CHUNK_BYTES", 32ull << 20);
+    st.bcast_scatter_min_ranks = static_cast<int>(env_u64("TIPS_BCAST_SCATTER_MIN_RANKS", 8));
     if (st.bcast_scatter_chunk < 65536) st.bcast_scatter_chunk = 65536;
   }
   st.use_multimem  = use_multimem && multicast_window != nullptr && !emulated;
@@ -1242,7 +1254,7 @@ int tipsk_comm_shutdown(void) {
 }
 
 /* Kernel selection at run time (every rank sets the same values, between collectives):
- *   allgather_push_bytes       gathered size up to which allgatherv pushes instead of pulling (0: never)
+ *   allgather_push_bytes       largest per-rank slab up to which allgatherv pushes instead of pulling (0: never)
  *   bcast_scatter_bytes        message size from which broadcast runs as scatter + allgather (0: never)
  *   bcast_scatter_chunk_bytes  pipeline chunk of that kernel (>= 64 KiB)
  *   bcast_scatter_min_ranks    fewest ranks for which it is used (>= 2) */

@@ -90,7 +90,7 @@ def bench_bn(out):
         flush = nbytes * 4 < (256 << 20)
         ms = time_ms(lambda: bn(x, residual=r), flush=flush)
         ms_lib = time_ms(lambda: torch.relu(ref(x) + r), flush=flush)
-        gbs = nbytes * 4 / ms / 1e6  # read x twice (stats + apply), read residual, write y
+        gbs = nbytes * (4 + 1 / 16) / ms / 1e6  # read x twice (stats + apply), read residual, write y and the sign bits
         out.append({"kernel": "bn_fwd_train+residual+relu", "shape": [n, c, h, w], "ms": ms, "gbs": gbs,
                     "frac_of_" + pk["source"] + "_copy": gbs / pk["hbm_gbs"], "library_ms": ms_lib,
                     "speedup_vs_library": ms_lib / ms})
@@ -99,7 +99,7 @@ def bench_bn(out):
         y = bn(xg, residual=r.clone().requires_grad_())
         dy = torch.randn_like(y)
         ms = time_ms(lambda: torch.autograd.grad(y, xg, dy, retain_graph=True), flush=flush)
-        gbs = nbytes * 8 / ms / 1e6  # (dy, x, y) twice + dx + dres
+        gbs = nbytes * (6 + 2 / 16) / ms / 1e6  # (dy, x, sign bits) twice (reduce + apply), write dx and dres
         out.append({"kernel": "bn_bwd+relu_mask+dresidual", "shape": [n, c, h, w], "ms": ms, "gbs": gbs,
                     "frac_of_" + pk["source"] + "_copy": gbs / pk["hbm_gbs"]})
         print(out[-1], flush=True)

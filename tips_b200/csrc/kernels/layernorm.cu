@@ -19,11 +19,11 @@ struct VecOf {
 };
 
 // VPL = 16-byte vectors per lane; handles cols <= 32 * VPL * kN, cols % kN == 0.
-template <typename T, int VPL>
+template <typename T, int VPL, bool kResidual>
 __global__ void __launch_bounds__(kWarpsPerBlock * 32)
 LnFwdKernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* __restrict__ beta, T* __restrict__ y,
             float* __restrict__ mean_out, float* __restrict__ rstd_out, int64_t rows, int cols, float eps,
-            const T* __restrict__ residual = nullptr, T* __restrict__ sum_out = nullptr) {
+            const T* __restrict__ residual, T* __restrict__ sum_out) {
   // With `residual` the row normalised is x + residual (rounded to T, as a separate add kernel would leave it),
   // and that sum is also written to `sum_out` for the backward pass.
   constexpr int N = VecOf<T>::kN;
@@ -40,7 +40,7 @@ LnFwdKernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* __res
       const int vi = lane + k * 32;
       if (vi < nvec) {
         Vec16<T> q = LoadVec(xr + vi * N);
-        if (residual != nullptr) {
+        if constexpr (kResidual) {
           const Vec16<T> rr = LoadVec(residual + r * cols + vi * N);
 #pragma unroll
           for (int i = 0; i < N; ++i) q.v[i] = FromFloat<T>(ToFloat<T>(q.v[i]) + ToFloat<T>(rr.v[i]));
@@ -301,9 +301,9 @@ int tipsk_ln_fwd(const void* x, const void* gamma, const void* beta, void* y, fl
   TIPSK_REQUIRE(cols > 0 && cols % (16 / (int)DTypeSize(dtype)) == 0, "layer norm: cols must be a multiple of 16 bytes");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   LN_DISPATCH(dtype, cols, {
-    LnFwdKernel<T, VPL><<<LnGrid(rows), kWarpsPerBlock * 32, 0, s>>>(
+    LnFwdKernel<T, VPL, false><<<LnGrid(rows), kWarpsPerBlock * 32, 0, s>>>(
         static_cast<const T*>(x), static_cast<const T*>(gamma), static_cast<const T*>(beta), static_cast<T*>(y), mean,
-        rstd, rows, cols, eps);
+        rstd, rows, cols, eps, nullptr, nullptr);
   });
   TIPSK_LAUNCH_CHECK();
   return 0;
@@ -318,7 +318,7 @@ int tipsk_ln_fwd_residual(const void* x, const void* residual, const void* gamma
   TIPSK_REQUIRE(residual != nullptr && sum_out != nullptr, "layer norm: residual and sum_out are required");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   LN_DISPATCH(dtype, cols, {
-    LnFwdKernel<T, VPL><<<LnGrid(rows), kWarpsPerBlock * 32, 0, s>>>(
+    LnFwdKernel<T, VPL, true><<<LnGrid(rows), kWarpsPerBlock * 32, 0, s>>>(
         static_cast<const T*>(x), static_cast<const T*>(gamma), static_cast<const T*>(beta), static_cast<T*>(y), mean,
         rstd, rows, cols, eps, static_cast<const T*>(residual), static_cast<T*>(sum_out));
   });

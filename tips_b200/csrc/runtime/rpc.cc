@@ -22,6 +22,10 @@ uint32_t Fnv1a(const std::string& s) {
 RpcService::RpcService(std::string name, RpcRequestHandler handler)
     : name_(std::move(name)), hash_(Fnv1a(name_)), handler_(std::move(handler)) {}
 
+namespace {
+thread_local bool t_on_listener_thread = false;
+}  // namespace
+
 RpcServer& RpcServer::Global() {
   static RpcServer* server = new RpcServer;
   return *server;
@@ -61,6 +65,12 @@ void RpcServer::Initialize(int rank, int size, std::vector<int> peer_fds, int nu
   if (num_listen_threads > size) num_listen_threads = size;
   num_listen_threads_ = num_listen_threads;
   initialized_ = true;
+  {
+    std::lock_guard<std::mutex> lock(out_mu_);
+    out_queue_.clear();
+    sender_stop_ = false;
+  }
+  sender_ = std::thread([this] { SenderLoop(); });
   for (int t = 0; t < num_listen_threads; ++t) listeners_.emplace_back([this, t] { ListenLoop(t); });
 }
 
@@ -104,11 +114,38 @@ Status RpcServer::SendFrame(int dst_rank, const RpcMsgHead& head, const void* pa
   memcpy(frame.data(), &len, sizeof(len));
   memcpy(frame.data() + sizeof(len), &head, sizeof(head));
   if (size) memcpy(frame.data() + sizeof(len) + sizeof(head), payload, size);
+  if (t_on_listener_thread) {  // never block a listener in send(): the sender thread takes it from here
+    {
+      std::lock_guard<std::mutex> lock(out_mu_);
+      out_queue_.emplace_back(dst_rank, std::move(frame));
+    }
+    out_cv_.notify_one();
+    sent_count_++;
+    return Status::OK();
+  }
   std::lock_guard<std::mutex> lock(*send_mus_[dst_rank]);
   if (!net::SendAll(send_fds_[dst_rank], frame.data(), frame.size()))
     return Status(kUnavailable, "send to rank " + std::to_string(dst_rank) + " failed");
   sent_count_++;
   return Status::OK();
+}
+
+void RpcServer::SenderLoop() {
+  for (;;) {
+    std::pair<int, std::vector<uint8_t>> item;
+    {
+      std::unique_lock<std::mutex> lock(out_mu_);
+      out_cv_.wait(lock, [&] { return sender_stop_ || !out_queue_.empty(); });
+      if (out_queue_.empty()) return;  // stop requested and everything handed over has been sent
+      item = std::move(out_queue_.front());
+      out_queue_.pop_front();
+    }
+    const int dst = item.first;
+    if (peer_dead_[dst].load()) continue;
+    std::lock_guard<std::mutex> lock(*send_mus_[dst]);
+    if (!net::SendAll(send_fds_[dst], item.second.data(), item.second.size()) && !stopping_.load() && !quiescing_.load())
+      TIPS_LOG(ERROR) << "send to rank " << dst << " failed";
+  }
 }
 
 Status RpcServer::SendRequest(int dst_rank, const std::string& service_name, const void* payload, size_t size,
@@ -226,6 +263,7 @@ void RpcServer::OnPeerClosed(int peer) {
 }
 
 void RpcServer::ListenLoop(int thread_index) {
+  t_on_listener_thread = true;
   std::vector<int> my_peers;
   const int total_threads = num_listen_threads_;
   for (int r = 0; r < size_; ++r)
@@ -268,6 +306,12 @@ void RpcServer::Finalize() {
   for (auto& t : listeners_)
     if (t.joinable()) t.join();
   listeners_.clear();
+  {
+    std::lock_guard<std::mutex> lock(out_mu_);
+    sender_stop_ = true;
+  }
+  out_cv_.notify_all();
+  if (sender_.joinable()) sender_.join();  // sends what the listeners had handed over, then ends
   std::vector<RpcResponseCallback> failed;
   {
     std::lock_guard<std::mutex> lock(pending_mu_);

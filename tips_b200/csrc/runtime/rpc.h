@@ -17,6 +17,8 @@
 #pragma once
 
 #include <atomic>
+#include <condition_variable>
+#include <deque>
 #include <functional>
 #include <memory>
 #include <mutex>
@@ -128,6 +130,7 @@ class RpcServer {
  private:
   RpcServer() = default;
   void ListenLoop(int thread_index);
+  void SenderLoop();
   bool ReadFrame(int fd, std::vector<uint8_t>* frame);
   Status SendFrame(int dst_rank, const RpcMsgHead& head, const void* payload, size_t size);
   void Dispatch(RpcMessage&& msg);
@@ -145,6 +148,14 @@ class RpcServer {
   std::unique_ptr<std::atomic<bool>[]> peer_dead_;
   int wake_pipe_[2]{-1, -1};
   std::vector<std::thread> listeners_;
+  // Frames produced on a listener thread (responses written by request handlers, requests sent from callbacks) are
+  // handed to this thread: a listener that blocked in send() would stop draining its sockets, and two ranks whose
+  // listeners send each other more than the socket buffers hold, or one rank answering itself, would never finish.
+  std::thread sender_;
+  std::mutex out_mu_;
+  std::condition_variable out_cv_;
+  std::deque<std::pair<int, std::vector<uint8_t>>> out_queue_;
+  bool sender_stop_{false};
 
   std::mutex services_mu_;
   std::unordered_map<uint32_t, std::unique_ptr<RpcService>> services_;

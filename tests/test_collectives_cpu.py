@@ -191,3 +191,23 @@ def _grouped_broadcast(rank, size):
 
 def test_parameters_are_broadcast_as_one_collective():
     run_ranks(_grouped_broadcast, 3)
+
+
+def _shutdown_with_work_in_flight(rank, size):
+    """Shutdown does not wait for collectives nobody synchronised, nor for a tensor that only one rank submitted."""
+    import time
+    import tips_b200 as tips
+    t = torch.ones(1000)
+    handles = [tips.allreduce_async(t * i, name=f"inflight.{i}") for i in range(20)]
+    if rank == 0:
+        handles.append(tips.allreduce_async(t, name="only.rank0"))       # never matched by the other ranks
+    t0 = time.time()
+    tips.shutdown()
+    assert time.time() - t0 < 30
+    assert not tips.is_initialized()
+    assert len(handles) >= 20
+
+
+def test_shutdown_with_work_in_flight():
+    run_ranks(_shutdown_with_work_in_flight, 3)
+

@@ -302,3 +302,37 @@ def _peer_loss(rank, size):
 
 def test_rank_loss_is_an_error_not_a_hang():
     run_ranks(_peer_loss, 3, env={"TIPS_STALL_ABORT_MS": "3000", "TIPS_HOST_TIMEOUT_MS": "5000"})
+
+
+def _fit_with_lr_schedule(rank, size):
+    """The reference's Keras integration test: fit for 10 steps with Adam, an exponential learning-rate decay, the
+    distributed optimizer and the initial broadcast (tips/tensorflow/test_tensorflow2_keras.py:28-52); here the decay
+    is a stock torch scheduler driving the wrapped optimizer, and the replicas must end identical."""
+    import tips_b200 as tips
+    from tips_b200 import callbacks as cb
+    from tips_b200.trainer import fit
+    torch.manual_seed(rank)
+    model = torch.nn.Sequential(torch.nn.Linear(8, 16), torch.nn.ReLU(), torch.nn.Linear(16, 4))
+    opt = tips.DistributedOptimizer(torch.optim.Adam(model.parameters(), lr=0.01 * size))
+    sched = torch.optim.lr_scheduler.ExponentialLR(opt, gamma=0.9)
+
+    def batches(epoch, step):
+        g = torch.Generator().manual_seed(100 * epoch + step * size + rank)
+        return torch.randn(8, 8, generator=g), torch.randint(0, 4, (8,), generator=g)
+
+    class StepSchedule(cb.Callback):
+        def on_epoch_end(self, epoch, logs=None):
+            sched.step()
+
+    history = fit(model, opt, torch.nn.functional.cross_entropy, batches, 2, 5,
+                  [cb.BroadcastGlobalVariablesCallback(0), cb.MetricAverageCallback(), StepSchedule()], verbose=0)
+    assert len(history) == 2 and abs(opt.param_groups[0]["lr"] - 0.01 * size * 0.81) < 1e-9
+    weights = tips.allgather_object(model[0].weight.detach().clone())
+    assert all(torch.equal(weights[0], w) for w in weights)
+    losses = tips.allgather_object(history[-1]["loss"])
+    assert all(abs(losses[0] - v) < 1e-9 for v in losses)        # averaged metric: the same number everywhere
+
+
+def test_fit_with_a_torch_lr_scheduler():
+    run_ranks(_fit_with_lr_schedule, 2)
+

@@ -1,6 +1,6 @@
 """A hand-written training loop, the counterpart of the reference's examples/tensorflow_mnist.py (a custom
 `train_step` around a DistributedGradientTape): the gradients of an ordinary backward pass are averaged over the
-ranks with `allreduce_gradients`, a stock optimizer applies them, metrics are averaged with `metric_average`.
+ranks by a `DistributedGradientTape`, a stock optimizer applies them, metrics are averaged with `metric_average`.
 Synthetic data (28x28x1 uniform, labels 0..9).
 
     python -m torch.distributed.run --nproc-per-node 2 examples/pytorch_mnist_custom_loop.py --steps 200
@@ -34,11 +34,12 @@ def main():
     compression = getattr(tips.Compression, a.compression)
 
     def train_step(images, labels):
-        logits = model(images)
-        loss = torch.nn.functional.cross_entropy(logits, labels)
-        optimizer.zero_grad()
-        loss.backward()
-        tips.allreduce_gradients(model.parameters(), compression=compression)   # what the tape does to its gradients
+        with tips.DistributedGradientTape(compression=compression) as tape:
+            logits = model(images)
+            loss = torch.nn.functional.cross_entropy(logits, labels)
+        params = list(model.parameters())
+        for p, g in zip(params, tape.gradient(loss, params)):      # gradients averaged over the ranks
+            p.grad = g
         optimizer.step()
         return loss.detach(), (logits.argmax(1) == labels).float().mean()
 

@@ -336,3 +336,62 @@ def _fit_with_lr_schedule(rank, size):
 def test_fit_with_a_torch_lr_scheduler():
     run_ranks(_fit_with_lr_schedule, 2)
 
+
+
+def _gradient_tape(rank, size):
+    """tape.gradient returns the ranks' gradients averaged (or summed), whatever the grouping, the wire format or
+    the kind of gradient; a parameter the loss does not touch gives None."""
+    import tips_b200 as tips
+    torch.manual_seed(0)
+    emb = torch.nn.Embedding(20, 4, sparse=True)
+    lin = torch.nn.Linear(4, 3)
+    unused = torch.nn.Parameter(torch.zeros(2))
+    hook = tips.BroadcastGlobalVariablesHook(0, torch.nn.ModuleList([emb, lin]))
+    hook.begin()
+    hook()                                                    # second call: nothing happens
+    params = [emb.weight, lin.weight, lin.bias, unused]
+
+    def loss_of(r):
+        ids = torch.tensor([r, r + 1, 7, 7])
+        return (lin(emb(ids)) * (r + 1.0)).pow(2).sum()
+
+    def local(r):
+        g = torch.autograd.grad(loss_of(r), params, allow_unused=True)
+        return [None if x is None else (x.to_dense() if x.is_sparse else x) for x in g]
+
+    every = [local(r) for r in range(size)]
+    mean = [None if every[0][i] is None else sum(e[i] for e in every) / size for i in range(len(params))]
+    total = [None if m is None else m * size for m in mean]
+
+    def check(got, want, tol=1e-6):
+        assert got[3] is None
+        for g, w in zip(got[:3], want[:3]):
+            g = g.to_dense() if g.is_sparse else g
+            assert torch.allclose(g, w, atol=tol, rtol=tol), (g - w).abs().max()
+
+    with tips.DistributedGradientTape() as tape:
+        loss = loss_of(rank)
+    got = tape.gradient(loss, params)
+    assert got[0].is_sparse                                   # travelled as two allgathers
+    check(got, mean)
+    for kwargs in ({"sparse_as_dense": True, "groups": 2}, {"sparse_as_dense": True, "groups": [[lin.weight, lin.bias]]},
+                   {"sparse_as_dense": True, "op": tips.Sum}, {"sparse_as_dense": True, "gradient_predivide_factor": 2.0},
+                   {"sparse_as_dense": True, "groups": 1, "compression": tips.Compression.fp16}):
+        with tips.DistributedGradientTape(name="tape." + "_".join(sorted(kwargs)), **kwargs) as tape:
+            loss = loss_of(rank)
+        got = tape.gradient(loss, params)
+        assert not got[0].is_sparse
+        check(got, total if kwargs.get("op") == tips.Sum else mean, 5e-2 if "compression" in kwargs else 1e-5)
+    with tips.DistributedGradientTape(persistent=True, sparse_as_dense=True) as tape:
+        loss = loss_of(rank)
+    check(tape.gradient(loss, params), mean)
+    check(tape.gradient(loss, params), mean)                  # the graph was kept
+    with pytest.raises(ValueError):
+        tips.DistributedGradientTape(op=tips.Sum, gradient_predivide_factor=2.0)
+    with pytest.raises(ValueError):
+        tips.DistributedGradientTape(groups=0)
+    assert int(tips.local_size_op()) == tips.local_size() and int(tips.local_rank_op()) == tips.local_rank()
+
+
+def test_distributed_gradient_tape():
+    run_ranks(_gradient_tape, 3)

@@ -18,7 +18,8 @@ from .parallel.optimizer import DistributedOptimizer
 from .parallel.functions import (allgather_object, broadcast_object, broadcast_object_fn, broadcast_optimizer_state,
                                  broadcast_parameters, broadcast_variables, metric_average, allreduce_gradients,
                                  allreduce_value, allgather_value, broadcast_value, broadcast_global_variables,
-                                 rank_op, size_op)
+                                 rank_op, size_op, local_rank_op, local_size_op)
+from .parallel.tape import BroadcastGlobalVariablesHook, DistributedGradientTape
 
 __version__ = "0.1.0"
 from . import callbacks, elastic

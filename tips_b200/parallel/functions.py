@@ -210,6 +210,18 @@ def rank_op() -> torch.Tensor:
     return torch.tensor(C._rank(), dtype=torch.int32)
 
 
+def local_size_op() -> torch.Tensor:
+    """Number of ranks on this node as an int32 tensor."""
+    from .. import runtime
+    return torch.tensor(runtime.local_size(), dtype=torch.int32)
+
+
+def local_rank_op() -> torch.Tensor:
+    """Rank within this node as an int32 tensor."""
+    from .. import runtime
+    return torch.tensor(runtime.local_rank(), dtype=torch.int32)
+
+
 def _as_tensor(value):
     if isinstance(value, torch.Tensor):
         return value

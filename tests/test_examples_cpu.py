@@ -3,8 +3,6 @@ import os
 import subprocess
 import sys
 
-import pytest
-
 from mp_util import free_port
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))

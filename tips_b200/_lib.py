@@ -10,7 +10,6 @@ instead of falling back to another implementation.
 from __future__ import annotations
 
 import ctypes
-import os
 from ctypes import (CFUNCTYPE, POINTER, Structure, c_char_p, c_double, c_int, c_int32, c_int64, c_uint64,
                     c_void_p)
 from pathlib import Path

@@ -6,7 +6,8 @@
 The reference times only its serializer (tips/core/message/flatbuffers_test.cc:12-66, FlatBuffers against its
 NaiveBuffer, 1000 x build / read, numbers logged and never recorded); the negotiated round trip has no
 counterpart there.  This is also the timed row of the MNIST-sized configuration: a step of that model issues one
-bucket per step, so its communication cost is one of these round trips plus the bytes.
+bucket per step, so its communication cost is one of these round trips plus the bytes; the same step is timed a
+second time the way the reference runs it (one negotiated allreduce per gradient tensor, every step).
 """
 from __future__ import annotations
 
@@ -67,11 +68,34 @@ def _rank_main(rank, size, port, iters, out):
         opt.step()
         opt.zero_grad()
     step = (time.perf_counter() - t0) / steps
+    # The same step the way the reference runs it (tips/tensorflow/__init__.py:230-300 and
+    # tips/core/collective/coordinator.cc:243-353): one allreduce per gradient tensor, each negotiated through
+    # rank 0 in every step, nothing fused and no order frozen.
+    from tips_b200 import _lib
+    _lib.core().tips_set_fusion_threshold(0)
+    tips.barrier()
+    plain = torch.optim.SGD(model.parameters(), lr=0.01)
+
+    def reference_step():
+        plain.zero_grad()
+        torch.nn.functional.cross_entropy(model(xb), yb).backward()
+        tips.allreduce_gradients(model.parameters(), name="ref.grads")
+        plain.step()
+
+    for _ in range(3):
+        reference_step()
+    tips.barrier()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        reference_step()
+    ref_step = (time.perf_counter() - t0) / steps
     if rank == 0:
         out.put({"ranks": size, "negotiated_allreduce_us": round(one * 1e6, 1),
                  "allreduce_4MB_ms": round(bw * 1e3, 2), "allreduce_4MB_GBs_per_rank": round(4.194304e-3 / bw, 2),
                  "mnist_cnn_step_ms": round(step * 1e3, 1),
-                 "mnist_cnn_images_per_s": round(64 * size / step, 1)})
+                 "mnist_cnn_images_per_s": round(64 * size / step, 1),
+                 "mnist_cnn_step_ms_per_tensor_negotiated": round(ref_step * 1e3, 1),
+                 "mnist_cnn_images_per_s_per_tensor_negotiated": round(64 * size / ref_step, 1)})
     tips.shutdown()
 
 

@@ -20,7 +20,6 @@ or any loop that calls the ``on_*`` hooks):
 from __future__ import annotations
 
 import math
-import os
 from typing import Callable, Optional, Union
 
 import torch

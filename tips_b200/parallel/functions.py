@@ -12,7 +12,7 @@ from __future__ import annotations
 
 import io
 import pickle
-from typing import Any, Iterable
+from typing import Any
 
 import torch
 

@@ -18,12 +18,10 @@ host tables in tips_b200.ps.host.
 from __future__ import annotations
 
 import ctypes
-import os
 from typing import Optional
 
 import torch
 
-from .. import _lib
 from ..ops import base
 from ..utils.trace import nvtx_range
 

@@ -10,7 +10,7 @@ from __future__ import annotations
 
 import ctypes
 from ctypes import POINTER, c_char_p, c_double, c_int, c_int64, c_uint64, c_void_p
-from typing import Iterable, Optional, Sequence
+from typing import Optional, Sequence
 
 import numpy as np
 

@@ -2,7 +2,7 @@
 reference's example (examples/tensorflow2_keras_mnist.py:93-98)."""
 from __future__ import annotations
 
-from typing import Callable, Iterable, List, Optional
+from typing import Callable, List, Optional
 
 import torch
 

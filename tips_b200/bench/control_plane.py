@@ -74,12 +74,14 @@ def _rank_main(rank, size, port, iters, out):
     from tips_b200 import _lib
     _lib.core().tips_set_fusion_threshold(0)
     tips.barrier()
-    plain = torch.optim.SGD(model.parameters(), lr=0.01)
+    torch.manual_seed(0)
+    model_ref = MnistCNN()   # a model of its own: the first one carries the distributed optimizer's gradient hooks
+    plain = torch.optim.SGD(model_ref.parameters(), lr=0.01)
 
     def reference_step():
         plain.zero_grad()
-        torch.nn.functional.cross_entropy(model(xb), yb).backward()
-        tips.allreduce_gradients(model.parameters(), name="ref.grads")
+        torch.nn.functional.cross_entropy(model_ref(xb), yb).backward()
+        tips.allreduce_gradients(model_ref.parameters(), name="ref.grads")
         plain.step()
 
     for _ in range(3):

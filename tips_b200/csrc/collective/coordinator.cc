@@ -12,6 +12,7 @@ namespace collective {
 namespace {
 
 const char kCoordinatorService[] = "collective_coordinator";
+const char kEngineStopService[]  = "collective_stop";
 
 int64_t NumElements(const std::vector<int64_t>& shape) {
   int64_t n = 1;
@@ -180,6 +181,13 @@ void CollectiveEngine::Initialize(const EngineOptions& opts) {
     ev.head = m.head();
     NaiveBuffer rb(m.payload(), m.payload_size());
     ev.request.Deserialize(&rb);
+    queue_.WriteMove(std::move(ev));
+  });
+  // Rank 0 ends a job's negotiation with this message, sent after its last response on the same connection
+  // (see Loop): a rank stops executing responses exactly where rank 0 stopped sending them.
+  RpcServer::Global().AddService(kEngineStopService, [this](RpcMessage&&) {
+    Event ev;
+    ev.kind = Event::kStopMarker;
     queue_.WriteMove(std::move(ev));
   });
   RpcServer::Global().SetPeerFailureHook([this](int peer) {

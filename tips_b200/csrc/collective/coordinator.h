@@ -178,7 +178,7 @@ class CollectiveEngine {
   CollectiveEngine() = default;
 
   struct Event {
-    enum Kind { kLocalRequest, kRemoteRequest, kResponse, kFrozenReady, kPeerFailure, kReset, kShutdown } kind;
+    enum Kind { kLocalRequest, kRemoteRequest, kResponse, kFrozenReady, kPeerFailure, kReset, kShutdown, kStopMarker } kind;
     RequestMessage request;
     RpcMsgHead head;
     ResponseMessage response;

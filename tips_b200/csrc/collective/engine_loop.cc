@@ -16,6 +16,7 @@ namespace collective {
 namespace {
 
 const char kCoordinatorService[] = "collective_coordinator";
+const char kEngineStopService[]  = "collective_stop";
 
 int64_t NumElements(const std::vector<int64_t>& shape) {
   int64_t n = 1;
@@ -43,11 +44,19 @@ void ScaleHost(void* data, int64_t n, Datatype dtype, double f) {
 }  // namespace
 
 void CollectiveEngine::Loop() {
+  // Shutdown with collectives in flight: every rank has to execute the same responses, or a rank that stopped
+  // early leaves the others inside a collective it never joins.  So rank 0 decides where the job ends: on its own
+  // shutdown it stops answering and tells every rank so, after its last response on the same connection; the other
+  // ranks keep executing what arrives until that message (or a lost peer, or `kStopWaitMs`).
+  constexpr int64_t kStopWaitMs = 10000;
+  bool stopping         = false;
+  int64_t stop_deadline = 0;
   std::vector<std::string> ready;
   while (true) {
     Event first;
-    int got = queue_.ReadFor(&first, 500);
+    int got = queue_.ReadFor(&first, stopping ? 50 : 500);
     if (got < 0) break;
+    if (stopping && NowMicros() > stop_deadline) break;
     if (got == 0) {
       if (rank_ == 0) CheckStalls();
       continue;
@@ -62,7 +71,20 @@ void CollectiveEngine::Loop() {
     bool stop = false;
     for (Event& ev : batch) {
       switch (ev.kind) {
-        case Event::kShutdown: stop = true; break;
+        case Event::kShutdown:
+          if (rank_ == 0 || size_ == 1) {
+            for (int r = 1; r < size_; ++r)
+              RpcServer::Global().SendRequest(r, kEngineStopService, nullptr, 0, [](const Status&, RpcMessage&&) {});
+            stop = true;
+          } else if (!stopping) {
+            stopping      = true;
+            stop_deadline = NowMicros() + kStopWaitMs * 1000;
+          }
+          break;
+        case Event::kStopMarker:
+          // rank 0 has sent its last response: nothing that arrives later is executed anywhere
+          stop = true;
+          break;
         case Event::kLocalRequest:
           counters_.negotiation_requests++;
           if (rank_ == 0) {
@@ -101,6 +123,7 @@ void CollectiveEngine::Loop() {
           TIPS_LOG(ERROR) << "rank " << ev.peer << " left the job; failing the collectives in flight";
           message_table_.clear();
           FailAll(Status(kUnavailable, "rank " + std::to_string(ev.peer) + " left the job"));
+          if (stopping) stop = true;
           break;
         case Event::kReset:
           message_table_.clear();

@@ -61,25 +61,45 @@ class AdagradPushAccess : public PushAccessMethod {
  public:
   AdagradPushAccess(double lr, double eps = 1e-8) : lr_(lr), eps_(eps) {}
   void ApplyPushValue(uint64_t key, AnyVec* row, const AnyVec& grad) override {
+    // The accumulators live in striped maps: a key is only ever touched by the thread of its shard, so a
+    // stripe's lock is held for the lookup alone and shard threads rarely meet on one.
+    Stripe& stripe = stripes_[(key * 0x9E3779B97F4A7C15ull) >> (64 - kStripeBits)];
     AnyVec* state;
     {
-      std::lock_guard<std::mutex> lock(mu_);
-      AnyVec& s = state_[key];
+      std::lock_guard<std::mutex> lock(stripe.mu);
+      AnyVec& s = stripe.state[key];
       if (s.size() != row->size()) s.Resize(Datatype::kFp64, row->size());
       state = &s;
     }
-    for (size_t i = 0; i < row->size(); ++i) {
+    const size_t n = row->size();
+    double* acc    = reinterpret_cast<double*>(state->buffer());
+    if (row->dtype() == Datatype::kFp32 && grad.dtype() == Datatype::kFp32 && grad.size() >= n) {
+      float* w       = reinterpret_cast<float*>(row->buffer());
+      const float* g = reinterpret_cast<const float*>(grad.buffer());
+      for (size_t i = 0; i < n; ++i) {
+        const double gi = g[i];
+        const double si = acc[i] + gi * gi;
+        acc[i]          = si;
+        w[i]            = static_cast<float>(static_cast<double>(w[i]) - lr_ * gi / (std::sqrt(si) + eps_));
+      }
+      return;
+    }
+    for (size_t i = 0; i < n; ++i) {
       const double g = grad.GetAsDouble(i);
-      const double s = state->GetAsDouble(i) + g * g;
-      state->SetFromDouble(i, s);
+      const double s = acc[i] + g * g;
+      acc[i]         = s;
       row->SetFromDouble(i, row->GetAsDouble(i) - lr_ * g / (std::sqrt(s) + eps_));
     }
   }
 
  private:
+  static constexpr int kStripeBits = 6;
+  struct Stripe {
+    std::mutex mu;
+    std::unordered_map<uint64_t, AnyVec> state;
+  };
   double lr_, eps_;
-  std::mutex mu_;
-  std::unordered_map<uint64_t, AnyVec> state_;
+  Stripe stripes_[1 << kStripeBits];
 };
 
 // param = lr * grad, exactly what the reference's SGD access method computes.

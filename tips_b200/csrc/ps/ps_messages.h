@@ -9,6 +9,7 @@
 // uses the runtime's own Datatype codes.  Encoded with NaiveBuffer.
 #pragma once
 
+#include <cstring>
 #include <string>
 #include <vector>
 
@@ -85,12 +86,47 @@ struct PushResponse {
   void Deserialize(NaiveBuffer* b) { *b >> meta.client_id >> meta.message_id; }
 };
 
+// Uniform requests (every row of one dtype and one length, which is what an embedding table sends) travel packed:
+// the keys as one array and the rows as one block, instead of one KeyItem with its own byte vector per row.
+//   packed pull request   meta, dtype, length, keys[u64]
+//   packed pull response  meta, n, bad, then n * length elements (request order; `bad` = rows that exist on the
+//                         server with another dtype or length: their slots are zero)
+//   packed push request   meta, dtype, length, keys[u64], then keys.size() * length elements
+//   packed push response  PushResponse followed by the number of rows that did not exist
+struct PackedHeader {
+  MessageMeta meta;
+  Datatype dtype{Datatype::kFp32};
+  uint32_t length{0};
+  std::vector<uint64_t> keys;
+  void Serialize(NaiveBuffer* b) const {
+    *b << meta.client_id << meta.message_id << static_cast<int32_t>(dtype) << length << keys;
+  }
+  void Deserialize(NaiveBuffer* b) {
+    int32_t dt = 0;
+    *b >> meta.client_id >> meta.message_id >> dt >> length >> keys;
+    dtype = static_cast<Datatype>(dt);
+  }
+  size_t row_bytes() const { return DatatypeNumBytes(dtype) * length; }
+  // Bytes this header takes at the start of a message of `size` bytes (0: the message is too short), so that a
+  // reader can parse the header alone and leave the row block where it is.
+  static size_t EncodedSize(const void* message, size_t size) {
+    constexpr size_t fixed = sizeof(int32_t) + sizeof(uint64_t) + sizeof(int32_t) + sizeof(uint32_t);
+    if (size < fixed + sizeof(uint64_t)) return 0;
+    uint64_t n = 0;
+    memcpy(&n, static_cast<const char*>(message) + fixed, sizeof(n));
+    const size_t total = fixed + sizeof(uint64_t) + n * sizeof(uint64_t);
+    return n <= size && total <= size ? total : 0;
+  }
+};
+
 inline Datatype ToDatatype(int32_t message_dtype) { return static_cast<Datatype>(message_dtype); }
 inline int32_t ToMessageDataType(Datatype t) { return static_cast<int32_t>(t); }
 
 // Names of the RPC services (reference: tips/core/rpc_service_names.h:8-9).
 constexpr const char* kPullServiceName = "pull_service";
 constexpr const char* kPushServiceName = "push_service";
+constexpr const char* kPackedPullServiceName = "pull_packed_service";
+constexpr const char* kPackedPushServiceName = "push_packed_service";
 
 }  // namespace ps
 }  // namespace tips

@@ -7,6 +7,8 @@
 //             request order) and sends it
 //   PsClient  tips/core/ps/ps_client.h:78-176  bucket records by owning server, one request
 //             per server, asynchronous completion
+// Beside the per-row messages of the reference there is a packed form for uniform rows (PullPacked / PushPacked),
+// which the C API uses: no per-row allocation on either side, rows copied once between the message and the table.
 // Differences: the completion fires ONCE per call, after every contacted server answered
 // (the reference calls `done` once per server, ps_client.h:93-107,124-128); a push to a row
 // that was never pulled is reported in the response instead of CHECK-failing the server
@@ -46,6 +48,8 @@ class PsServer {
  private:
   void PullTask(RpcMessage&& msg);
   void PushTask(RpcMessage&& msg);
+  void PackedPullTask(RpcMessage&& msg);
+  void PackedPushTask(RpcMessage&& msg);
 
   std::string name_;
   SparseTable* table_;
@@ -65,6 +69,7 @@ struct PsFuture {
   // pull: value of every requested key, in request order
   std::vector<KeyItem> values;
   uint64_t missing_rows{0};  // push: rows that did not exist on the server
+  uint64_t bad_rows{0};      // packed pull: rows that exist with another dtype or length
   bool Wait(int timeout_ms);
 };
 
@@ -80,6 +85,11 @@ class PsClient {
   // Asynchronous: the future completes once, when every server has answered.
   std::shared_ptr<PsFuture> Pull(const std::vector<PullRecord>& records, std::function<void()> done = nullptr);
   std::shared_ptr<PsFuture> Push(const std::vector<KeyItem>& records, std::function<void()> done = nullptr);
+  // Uniform rows, packed on the wire (see ps_messages.h).  `out` / `values` hold n rows of `length` elements in key
+  // order and must stay alive until the future completes; pulled rows are written straight into `out`.
+  std::shared_ptr<PsFuture> PullPacked(const uint64_t* keys, size_t n, Datatype dtype, uint32_t length, void* out);
+  std::shared_ptr<PsFuture> PushPacked(const uint64_t* keys, size_t n, Datatype dtype, uint32_t length,
+                                       const void* values);
 
  private:
   std::string name_;

@@ -111,18 +111,12 @@ int tips_ps_pull(int64_t id, const uint64_t* keys, int64_t n, int dtype, int len
   try {
     PsBundle* b = Get(id);
     if (!b) return Fail(kInvalidArgument, "unknown ps table");
-    std::vector<PsClient::PullRecord> recs(n);
-    for (int64_t i = 0; i < n; ++i) recs[i] = {keys[i], static_cast<Datatype>(dtype), static_cast<uint32_t>(length)};
-    auto fut = b->client->Pull(recs);
+    auto fut = b->client->PullPacked(keys, static_cast<size_t>(n), static_cast<Datatype>(dtype),
+                                     static_cast<uint32_t>(length), out);
     if (!fut->Wait(timeout_ms)) return Fail(kTimeout, "ps pull timed out");
     if (!fut->status.ok()) return Fail(fut->status.code(), fut->status.message());
-    const size_t row_bytes = DatatypeNumBytes(static_cast<Datatype>(dtype)) * length;
-    for (int64_t i = 0; i < n; ++i) {
-      const KeyItem& it = fut->values[i];
-      if (it.value.size() != row_bytes)
-        return Fail(kPrecondition, "row " + std::to_string(keys[i]) + " has a different length or dtype on the server");
-      memcpy(static_cast<char*>(out) + i * row_bytes, it.value.data(), row_bytes);
-    }
+    if (fut->bad_rows)
+      return Fail(kPrecondition, std::to_string(fut->bad_rows) + " row(s) have a different length or dtype on the server");
     return 0;
   } catch (const std::exception& e) {
     return Fail(kInternal, e.what());
@@ -135,15 +129,8 @@ int64_t tips_ps_push(int64_t id, const uint64_t* keys, int64_t n, int dtype, int
   try {
     PsBundle* b = Get(id);
     if (!b) return Fail(kInvalidArgument, "unknown ps table");
-    const size_t row_bytes = DatatypeNumBytes(static_cast<Datatype>(dtype)) * length;
-    std::vector<KeyItem> recs(n);
-    for (int64_t i = 0; i < n; ++i) {
-      recs[i].key   = keys[i];
-      recs[i].dtype = static_cast<Datatype>(dtype);
-      const uint8_t* p = static_cast<const uint8_t*>(values) + i * row_bytes;
-      recs[i].value.assign(p, p + row_bytes);
-    }
-    auto fut = b->client->Push(recs);
+    auto fut = b->client->PushPacked(keys, static_cast<size_t>(n), static_cast<Datatype>(dtype),
+                                     static_cast<uint32_t>(length), values);
     if (!fut->Wait(timeout_ms)) return Fail(kTimeout, "ps push timed out");
     if (!fut->status.ok()) return Fail(fut->status.code(), fut->status.message());
     return static_cast<int64_t>(fut->missing_rows);

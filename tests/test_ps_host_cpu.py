@@ -178,3 +178,38 @@ def _dense_table(rank, size, servers, rule, tmp):
                                           ([1, 2], "literal_reference")])
 def test_dense_table(tmp_path, servers, rule):
     run_ranks(_dense_table, 3, servers, rule, str(tmp_path))
+
+
+def _large_crossing_traffic(rank, size):
+    """Both ranks serve and both pull and push tens of MB at the same time: requests and responses far above a socket
+    buffer cross in both directions (and each server also answers itself), which must neither stall nor mix rows up.
+    Also the packed wire form: a row that exists with another length is refused, an unknown row is counted."""
+    import tips_b200 as tips
+    from tips_b200.ps.host import HostSparseTable, Route
+    dim, n = 64, 60_000
+    table = HostSparseTable("big", dim=dim, route=Route(), optimizer="sgd", lr=1.0, local_shards=2, timeout_s=120.0)
+    keys = (np.arange(n, dtype=np.uint64) * np.uint64(2654435761) + np.uint64(rank)) % np.uint64(1 << 40)
+    keys = np.unique(keys)
+    assert np.all(table.pull(keys) == 0)                      # creates the rows, about half of them on the other rank
+    grads = -(keys % np.uint64(1000)).astype(np.float32)[:, None] * np.ones((1, dim), dtype=np.float32)
+    for _ in range(2):
+        assert table.push(keys, grads) == 0                   # w -= 1.0 * g, twice
+    got = table.pull(keys)
+    want = 2.0 * (keys % np.uint64(1000)).astype(np.float32)
+    assert np.array_equal(got[:, 0], want) and np.array_equal(got[:, dim - 1], want)
+    tips.barrier()
+    never_pulled = np.array([(1 << 41) + rank, (1 << 41) + 7 + rank], dtype=np.uint64)
+    assert table.push(never_pulled, np.ones((2, dim), dtype=np.float32)) == 2
+    other = HostSparseTable("big2", dim=8, route=Route(), optimizer="sgd", lr=1.0)
+    k = np.array([5 + rank], dtype=np.uint64)
+    other.pull(k)
+    other.dim = 16                                            # ask for the same row with another length
+    with pytest.raises(tips.TipsError, match="different length or dtype"):
+        other.pull(k)
+    other.dim = 8
+    other.close()
+    table.close()
+
+
+def test_large_crossing_traffic():
+    run_ranks(_large_crossing_traffic, 2)

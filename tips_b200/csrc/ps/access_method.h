@@ -118,13 +118,9 @@ class PullAccessAgent {
   PullAccessAgent(SparseTable* table, std::shared_ptr<PullAccessMethod> method)
       : table_(table), method_(std::move(method)) {}
   void GetPullValue(uint64_t key, Datatype dtype, size_t length, AnyVec* out) {
-    AnyVec* row = table_->Find(key);
-    if (!row) {
-      AnyVec fresh;
-      method_->InitParam(key, dtype, length, &fresh);
-      table_->Assign(key, fresh);
-      row = table_->Find(key);
-    }
+    bool created = false;
+    AnyVec* row  = table_->FindOrCreate(key, &created);  // a new row is initialised where it is stored
+    if (created) method_->InitParam(key, dtype, length, row);
     method_->GetPullValue(key, *row, out);
   }
   PullAccessMethod* method() { return method_.get(); }

@@ -114,6 +114,21 @@ void SparseTableShard::Assign(uint64_t key, const AnyVec& value) {
   rows_[key].CopyFrom(value);
 }
 
+AnyVec* SparseTableShard::FindOrCreate(uint64_t key, bool* created) {
+  {
+    RWLockReadGuard guard(lock_);
+    auto it = rows_.find(key);
+    if (it != rows_.end()) {
+      *created = false;
+      return &it->second;
+    }
+  }
+  RWLockWriteGuard guard(lock_);
+  auto ins = rows_.emplace(key, AnyVec());
+  *created = ins.second;
+  return &ins.first->second;
+}
+
 size_t SparseTableShard::size() const {
   RWLockReadGuard guard(lock_);
   return rows_.size();
@@ -139,6 +154,10 @@ SparseTable::SparseTable(std::vector<int> servers, int my_world_rank, int local_
 AnyVec* SparseTable::Find(uint64_t key) { return local_shard(ToLocalShard(key)).Find(key); }
 
 void SparseTable::Assign(uint64_t key, const AnyVec& value) { local_shard(ToLocalShard(key)).Assign(key, value); }
+
+AnyVec* SparseTable::FindOrCreate(uint64_t key, bool* created) {
+  return local_shard(ToLocalShard(key)).FindOrCreate(key, created);
+}
 
 size_t SparseTable::size() const {
   size_t n = 0;

@@ -97,6 +97,8 @@ class SparseTableShard {
   AnyVec* Find(uint64_t key);
   bool Find(uint64_t key, AnyVec* shadow);   // shadow copy of the row
   void Assign(uint64_t key, const AnyVec& value);  // deep copy
+  // The stored row, made empty first if the key is new (`created`); the caller fills a new row in place.
+  AnyVec* FindOrCreate(uint64_t key, bool* created);
   size_t size() const;
   void Dump(std::ostream& os) const;          // "<key>\t<Vec text>\n" per row
   template <typename F>
@@ -119,6 +121,7 @@ class SparseTable : public Table {
   // Local lookups (the key must belong to this server).
   AnyVec* Find(uint64_t key);
   void Assign(uint64_t key, const AnyVec& value);
+  AnyVec* FindOrCreate(uint64_t key, bool* created);
   size_t size() const;
 
   // Text dump of the local shards, one "<key>\tVec:\t<e> <e> ... \n" line per row

@@ -110,7 +110,7 @@ Status RpcServer::SendFrame(int dst_rank, const RpcMsgHead& head, const void* pa
   if (dst_rank < 0 || dst_rank >= size_) return Status(kInvalidArgument, "bad destination rank");
   if (peer_dead_[dst_rank].load()) return Status(kUnavailable, "peer " + std::to_string(dst_rank) + " is gone");
   uint64_t len = sizeof(RpcMsgHead) + size;
-  std::vector<uint8_t> frame(sizeof(uint64_t) + len);
+  FrameBytes frame(sizeof(uint64_t) + len);
   memcpy(frame.data(), &len, sizeof(len));
   memcpy(frame.data() + sizeof(len), &head, sizeof(head));
   if (size) memcpy(frame.data() + sizeof(len) + sizeof(head), payload, size);
@@ -132,7 +132,7 @@ Status RpcServer::SendFrame(int dst_rank, const RpcMsgHead& head, const void* pa
 
 void RpcServer::SenderLoop() {
   for (;;) {
-    std::pair<int, std::vector<uint8_t>> item;
+    std::pair<int, FrameBytes> item;
     {
       std::unique_lock<std::mutex> lock(out_mu_);
       out_cv_.wait(lock, [&] { return sender_stop_ || !out_queue_.empty(); });
@@ -187,7 +187,7 @@ Status RpcServer::SendResponse(const RpcMsgHead& request_head, const void* paylo
   return SendFrame(head.dst_rank, head, payload, size);
 }
 
-bool RpcServer::ReadFrame(int fd, std::vector<uint8_t>* frame) {
+bool RpcServer::ReadFrame(int fd, FrameBytes* frame) {
   uint64_t len = 0;
   if (!net::RecvAll(fd, &len, sizeof(len))) return false;
   if (len < sizeof(RpcMsgHead) || len > (1ull << 34)) return false;
@@ -285,7 +285,7 @@ void RpcServer::ListenLoop(int thread_index) {
       short ev = pfds[k].revents;
       ++k;
       if (!(ev & (POLLIN | POLLHUP | POLLERR))) continue;
-      std::vector<uint8_t> frame;
+      FrameBytes frame;
       if (!ReadFrame(recv_fds_[r], &frame)) {
         OnPeerClosed(r);
         if (stopping_.load()) break;

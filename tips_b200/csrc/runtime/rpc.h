@@ -44,10 +44,32 @@ struct RpcMsgHead {
 
 // One received or to-be-sent frame: [RpcMsgHead | payload]. Move-only owner of
 // its bytes (the counterpart of the reference's ZmqMessage).
+// Byte buffer whose resize() leaves new bytes uninitialised: frames of tens of MB are filled by recv() or memcpy
+// right away, and zeroing them first costs as much as the copy.
+template <typename T>
+struct UninitAllocator : std::allocator<T> {
+  template <typename U>
+  struct rebind {
+    using other = UninitAllocator<U>;
+  };
+  UninitAllocator() = default;
+  template <typename U>
+  UninitAllocator(const UninitAllocator<U>&) {}
+  template <typename U>
+  void construct(U* p) noexcept {
+    ::new (static_cast<void*>(p)) U;  // default-initialisation: nothing for bytes
+  }
+  template <typename U, typename... A>
+  void construct(U* p, A&&... a) {
+    ::new (static_cast<void*>(p)) U(std::forward<A>(a)...);
+  }
+};
+using FrameBytes = std::vector<uint8_t, UninitAllocator<uint8_t>>;
+
 class RpcMessage {
  public:
   RpcMessage() = default;
-  explicit RpcMessage(std::vector<uint8_t>&& frame) : frame_(std::move(frame)) {}
+  explicit RpcMessage(FrameBytes&& frame) : frame_(std::move(frame)) {}
   RpcMessage(RpcMessage&&) = default;
   RpcMessage& operator=(RpcMessage&&) = default;
   RpcMessage(const RpcMessage&) = delete;
@@ -61,7 +83,7 @@ class RpcMessage {
   size_t size() const { return frame_.size(); }
 
  private:
-  std::vector<uint8_t> frame_;
+  FrameBytes frame_;
 };
 
 // Runs on a listener thread when a request for the service arrives. The
@@ -131,7 +153,7 @@ class RpcServer {
   RpcServer() = default;
   void ListenLoop(int thread_index);
   void SenderLoop();
-  bool ReadFrame(int fd, std::vector<uint8_t>* frame);
+  bool ReadFrame(int fd, FrameBytes* frame);
   Status SendFrame(int dst_rank, const RpcMsgHead& head, const void* payload, size_t size);
   void Dispatch(RpcMessage&& msg);
   void OnPeerClosed(int peer);
@@ -154,7 +176,7 @@ class RpcServer {
   std::thread sender_;
   std::mutex out_mu_;
   std::condition_variable out_cv_;
-  std::deque<std::pair<int, std::vector<uint8_t>>> out_queue_;
+  std::deque<std::pair<int, FrameBytes>> out_queue_;
   bool sender_stop_{false};
 
   std::mutex services_mu_;

@@ -38,6 +38,21 @@ def _values(rank, size):
     sp = torch.sparse_coo_tensor(torch.tensor([[rank, size]]), torch.tensor([1.0, 2.0]), (size + 1,))
     dense = tips.sparse_allreduce(sp, op=tips.Sum).to_dense()
     assert dense[size] == 2.0 * size and dense[0] == 1.0
+    # rows of values whose bytes are a multiple of 8 travel with their indices as ONE allgather; a rank may have none
+    rows = torch.tensor([rank, 7, 7]) if rank != 1 else torch.zeros(0, dtype=torch.int64)
+    vals = torch.full((rows.numel(), 4), float(rank + 1))
+    sp = torch.sparse_coo_tensor(rows.unsqueeze(0), vals, (10, 4))
+    before = tips.metrics()["ops_enqueued"]
+    got = tips.sparse_allreduce(sp, op=tips.Average).to_dense()
+    assert tips.metrics()["ops_enqueued"] - before == 1
+    want = torch.zeros(10, 4)
+    for r in range(size):
+        if r != 1:
+            want[r] += r + 1
+            want[7] += 2 * (r + 1)
+    assert torch.allclose(got, want / size)
+    two_d = torch.sparse_coo_tensor(torch.tensor([[rank], [2]]), torch.tensor([1.5], dtype=torch.float64), (size, 3))
+    assert torch.equal(tips.sparse_allreduce(two_d, op=tips.Sum).to_dense()[:, 2], torch.full((size,), 1.5, dtype=torch.float64))
     objs = tips.allgather_object({"rank": rank, "s": "x" * rank})
     assert [o["rank"] for o in objs] == list(range(size))
     assert tips.broadcast_object(("cfg", rank), root_rank=size - 1) == ("cfg", size - 1)

@@ -289,8 +289,26 @@ def sparse_allreduce(tensor: torch.Tensor, name=None, op=Average):
     _require_init()
     t = tensor.coalesce()
     base = _auto_name("sparse_allreduce", name)
-    values = allgather(t.values(), name=base + ".values")
-    indices = allgather(t.indices().t().contiguous(), name=base + ".indices").t()
+    values = t.values()
+    sparse_dim, nnz = t.indices().shape
+    indices = t.indices().t().reshape(-1).reshape(nnz, sparse_dim)   # [nnz, sparse_dim] int64, unit inner stride
+    inner = values.shape[1:]
+    vbytes = values.element_size()
+    for d in inner:
+        vbytes *= d
+    if vbytes % 8 == 0 or nnz == 0:
+        # One collective instead of two: a row of the gathered matrix is [the entry's indices | its values] as bytes
+        # (one negotiation through the coordinator per step instead of two; the reference gathers values and indices
+        # separately, tips/tensorflow/__init__.py:61-76).
+        packed = torch.cat([indices.view(torch.uint8).reshape(nnz, sparse_dim * 8),
+                            values.reshape(-1).view(torch.uint8).reshape(nnz, vbytes)], dim=1)
+        gathered = allgather(packed, name=base + ".entries")
+        total = gathered.shape[0]
+        indices = gathered[:, :sparse_dim * 8].reshape(-1).view(torch.int64).reshape(total, sparse_dim).t()
+        values = gathered[:, sparse_dim * 8:].reshape(-1).view(values.dtype).reshape((total,) + tuple(inner))
+    else:  # value rows that are not a multiple of 8 bytes would leave the int64 indices misaligned
+        values = allgather(values, name=base + ".values")
+        indices = allgather(indices, name=base + ".indices").t()
     if op == Average:
         values = values / _size()
     return torch.sparse_coo_tensor(indices, values, t.shape).coalesce()

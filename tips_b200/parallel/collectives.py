@@ -45,7 +45,8 @@ _handles_lock = threading.Lock()
 
 
 class _Handle:
-    __slots__ = ("id", "keep", "output", "post", "done_event", "ready_event", "alloc_cb", "gathered", "kind", "name")
+    __slots__ = ("id", "keep", "output", "post", "done_event", "ready_event", "alloc_cb", "gathered", "kind", "name",
+                 "first_dims")
 
     def __init__(self):
         self.id = 0
@@ -58,6 +59,7 @@ class _Handle:
         self.gathered = None
         self.kind = ""
         self.name = ""
+        self.first_dims = None   # allgather: dimension 0 of every rank, known once the collective was negotiated
 
 
 def _auto_name(kind: str, name: Optional[str]) -> str:
@@ -335,7 +337,8 @@ def allgather_async(tensor: torch.Tensor, name=None) -> _Handle:
     trailing = tuple(src.shape[1:])
 
     def _alloc(handle, nbytes, first_dims, n, user):
-        total = sum(first_dims[i] for i in range(n))
+        h.first_dims = [int(first_dims[i]) for i in range(n)]   # every rank's dimension 0, in rank order
+        total = sum(h.first_dims)
         out = torch.empty((total,) + trailing, dtype=src.dtype, device=src.device)
         gathered.append(out)
         return out.data_ptr() if out.numel() else 0

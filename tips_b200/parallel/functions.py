@@ -83,18 +83,16 @@ def broadcast_object(obj: Any = None, root_rank: int = 0, name: str | None = Non
     name = name or "tips.bcast_object"
     if C._size() == 1:
         return obj
+    # One collective: an allgather to which only the root contributes bytes.  The negotiation carries every
+    # rank's length, so the other ranks need not learn the size first (the reference broadcasts the size and then
+    # the payload, tips/tensorflow/functions.py:49-124).
     if C._rank() == root_rank:
         buf = io.BytesIO()
         _pickle.dump(obj, buf)
         payload = torch.frombuffer(bytearray(buf.getvalue()), dtype=torch.uint8)
-        size = torch.tensor([payload.numel()], dtype=torch.int64)
     else:
-        payload = None
-        size = torch.zeros(1, dtype=torch.int64)
-    size = C.broadcast(size, root_rank, name=name + ".size")
-    if payload is None:
-        payload = torch.empty(int(size.item()), dtype=torch.uint8)
-    payload = C.broadcast(payload, root_rank, name=name + ".data")
+        payload = torch.empty(0, dtype=torch.uint8)
+    payload = C.allgather(payload, name=name + ".data")
     return pickle.loads(payload.numpy().tobytes())
 
 
@@ -112,10 +110,15 @@ def allgather_object(obj: Any, name: str | None = None) -> list:
     payload = torch.frombuffer(bytearray(buf.getvalue()), dtype=torch.uint8)
     if C._size() == 1:
         return [pickle.loads(payload.numpy().tobytes())]
-    sizes = C.allgather(torch.tensor([payload.numel()], dtype=torch.int64), name=name + ".size")
-    gathered = C.allgather(payload, name=name + ".data")
+    # one collective: the allgather negotiates every rank's length anyway and the handle keeps them
+    # (the reference gathers the sizes first and the payloads second, tips/tensorflow/functions.py:127-168)
+    h = C.allgather_async(payload, name=name + ".data")
+    gathered = C.synchronize(h)
+    sizes = getattr(h, "first_dims", None)
+    if sizes is None:
+        sizes = C.allgather(torch.tensor([payload.numel()], dtype=torch.int64), name=name + ".size").tolist()
     out, off = [], 0
-    for s in sizes.tolist():
+    for s in sizes:
         out.append(pickle.loads(gathered[off:off + s].numpy().tobytes()))
         off += s
     return out

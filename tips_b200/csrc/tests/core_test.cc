@@ -3,6 +3,7 @@
 // with value assertions throughout.  Plain executable: exit code 0 = all passed.
 #include <atomic>
 #include <cstdio>
+#include <cstring>
 #include <numeric>
 #include <thread>
 
@@ -290,6 +291,48 @@ static void TestPsPieces() {
   PullRequest req2;
   req2.Deserialize(&r);
   EXPECT(req2.meta.message_id == 9 && req2.lengths == req.lengths);
+  // packed form of a uniform request: the header can be measured and parsed without touching the row block
+  PackedHeader ph;
+  ph.meta   = {5, 77};
+  ph.dtype  = Datatype::kFp32;
+  ph.length = 4;
+  ph.keys   = {10, 11, 12};
+  NaiveBuffer pb;
+  ph.Serialize(&pb);
+  const size_t header_bytes = pb.size();
+  const float block[12]     = {1, 2, 3, 4, 5, 6, 7, 8, 9, 10, 11, 12};
+  pb.WriteRaw(block, sizeof(block));
+  EXPECT(PackedHeader::EncodedSize(pb.data(), pb.size()) == header_bytes);
+  EXPECT(PackedHeader::EncodedSize(pb.data(), 10) == 0);                 // shorter than the fixed fields
+  EXPECT(PackedHeader::EncodedSize(pb.data(), header_bytes - 1) == 0);  // key array cut short
+  NaiveBuffer hb(pb.data(), header_bytes);
+  PackedHeader ph2;
+  ph2.Deserialize(&hb);
+  EXPECT(ph2.meta.client_id == 5 && ph2.meta.message_id == 77 && ph2.keys == ph.keys && ph2.row_bytes() == 16);
+  EXPECT(memcmp(pb.data() + header_bytes + 2 * ph2.row_bytes(), block + 8, 16) == 0);
+  // find-or-create leaves an empty row for the caller to fill; Adagrad's typed path equals the generic one
+  bool created = false;
+  AnyVec* fresh = table.FindOrCreate(4242, &created);
+  EXPECT(created && fresh != nullptr && fresh->size() == 0);
+  EXPECT(table.FindOrCreate(4242, &created) == fresh && !created);
+  {
+    SparseTable t32({0}, 0, 1), t64({0}, 0, 1);
+    PullAccessAgent p32(&t32, std::make_shared<SparseTablePullAccess>()), p64(&t64, std::make_shared<SparseTablePullAccess>());
+    PushAccessAgent a32(&t32, std::make_shared<AdagradPushAccess>(0.05, 1e-8)), a64(&t64, std::make_shared<AdagradPushAccess>(0.05, 1e-8));
+    AnyVec tmp;
+    p32.GetPullValue(1, Datatype::kFp32, 3, &tmp);
+    p64.GetPullValue(1, Datatype::kFp64, 3, &tmp);
+    for (int step = 0; step < 3; ++step) {
+      AnyVec g32(Datatype::kFp32, 3), g64(Datatype::kFp64, 3);
+      for (int i = 0; i < 3; ++i) {
+        g32.ToVec<float>()[i]  = 0.25f * (i + 1) * (step + 1);
+        g64.ToVec<double>()[i] = 0.25 * (i + 1) * (step + 1);
+      }
+      EXPECT(a32.ApplyPushValue(1, g32) && a64.ApplyPushValue(1, g64));
+    }
+    for (int i = 0; i < 3; ++i)
+      EXPECT(std::fabs(t32.Find(1)->ToVec<float>()[i] - t64.Find(1)->ToVec<double>()[i]) < 1e-6);
+  }
   WorkerParamCache cache;
   cache.SetParam(1, grad);
   cache.AccumulateGrad(1, grad);

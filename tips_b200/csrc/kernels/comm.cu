@@ -1514,6 +1514,10 @@ int tipsk_comm_group_create(int64_t id, const int32_t* members, int n, uint64_t 
     TIPSK_CUDA(cudaMemset(g.epochs[i], 0, sizeof(uint32_t) * kNumChannels * kMaxCommBlocks));
   }
   std::lock_guard<std::mutex> lock(g_groups_mu);
+  auto old = g_groups.find(id);
+  if (old != g_groups.end())  // the id is being reused: release the previous group's counters
+    for (uint32_t* e : old->second.epochs)
+      if (e) cudaFree(e);
   g_groups[id] = g;
   return 0;
 }

@@ -71,3 +71,26 @@ def _timeline(rank, size, folder):
 
 def test_timeline_and_counters(tmp_path):
     run_ranks(_timeline, 2, str(tmp_path), env={"TIPS_TIMELINE_PATH": os.path.join(str(tmp_path), "timeline.json")})
+
+
+def _prometheus(rank, size):
+    import urllib.request
+    import tips_b200 as tips
+    from tips_b200.utils import metrics_export
+    from mp_util import free_port
+    tips.allreduce(torch.ones(8), op=tips.Sum, name="m.0")
+    tips.allgather(torch.ones(rank + 1), name="m.1")
+    text = metrics_export.render()
+    assert f'tips_ops_completed{{rank="{rank}"}} 2.0' in text and "tips_allreduce_bytes" in text
+    if rank == 0:
+        port = metrics_export.start_metrics_server(free_port(), addr="127.0.0.1", per_rank_port=False)
+        tips.allreduce(torch.ones(8), op=tips.Sum, name="m.2")
+        body = urllib.request.urlopen(f"http://127.0.0.1:{port}/metrics", timeout=10).read().decode()
+        assert 'tips_ops_completed{rank="0"} 3.0' in body      # read at scrape time
+    else:
+        tips.allreduce(torch.ones(8), op=tips.Sum, name="m.2")
+    tips.barrier()
+
+
+def test_prometheus_endpoint():
+    run_ranks(_prometheus, 2)

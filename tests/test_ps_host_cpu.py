@@ -213,3 +213,39 @@ def _large_crossing_traffic(rank, size):
 
 def test_large_crossing_traffic():
     run_ranks(_large_crossing_traffic, 2)
+
+
+def _async_calls(rank, size):
+    """Pulls and pushes that return at once: the next batch's rows travel while this batch is used; results equal
+    the blocking calls'; a cancelled pull never writes into its buffer later."""
+    import tips_b200 as tips
+    from tips_b200.ps.host import HostSparseTable, Route
+    table = HostSparseTable("async", dim=16, route=Route(), optimizer="sgd", lr=0.5, local_shards=2)
+    batches = [np.arange(2000, dtype=np.uint64) * np.uint64(7919) + np.uint64(1000 * b + rank) for b in range(4)]
+    for b in batches:
+        table.pull(b)                                          # create every row
+    tips.barrier()
+    nxt = table.pull_async(batches[0])
+    pushes = []
+    for i, keys in enumerate(batches):
+        rows = nxt.wait()
+        assert rows.shape == (2000, 16) and np.all(rows == 0)
+        if i + 1 < len(batches):
+            nxt = table.pull_async(batches[i + 1])             # overlaps with the "compute" below
+        pushes.append(table.push_async(keys, np.full((2000, 16), float(i + 1), dtype=np.float32)))
+    assert all(p.wait() == 0 for p in pushes)
+    assert pushes[0].done() and pushes[0].wait() == 0          # waiting twice is harmless
+    for i, keys in enumerate(batches):
+        assert np.all(table.pull(keys) == -0.5 * (i + 1))
+    missing = table.push_async(np.array([1 << 50], dtype=np.uint64), np.ones((1, 16), dtype=np.float32))
+    assert missing.wait() == 1
+    call = table.pull_async(batches[1])
+    call.cancel()                                              # the answer may still arrive; nobody reads it
+    call.cancel()
+    assert call.done()
+    tips.barrier()
+    table.close()
+
+
+def test_asynchronous_pull_and_push():
+    run_ranks(_async_calls, 2)

@@ -62,14 +62,28 @@ def _rank_main(rank, size, port, a, out):
     step(batches[0])                     # warm-up: creates rows, opens the connections
     tips.barrier()
     t0 = time.perf_counter()
-    for s in range(a.steps):
-        step(batches[1 + s])
+    if a.overlap:
+        # the pull of the next batch and the push of this one are in flight together (asynchronous calls)
+        nxt = table.pull_async(batches[1])
+        pending = None
+        for s in range(a.steps):
+            keys = batches[1 + s]
+            rows = nxt.wait()
+            if s + 1 < a.steps:
+                nxt = table.pull_async(batches[2 + s])
+            if pending is not None:
+                pending.wait()
+            pending = table.push_async(keys, rows * 0.01 + 0.001)
+        pending.wait()
+    else:
+        for s in range(a.steps):
+            step(batches[1 + s])
     tips.barrier()
     dt = (time.perf_counter() - t0) / a.steps
     worst = max(tips.allgather_object(dt))
     if rank == 0:
         distinct = float(np.mean([b.size for b in batches[1:]]))
-        out.put({"ranks": size, "batch_per_rank": a.batch, "fields": a.fields, "dim": a.dim,
+        out.put({"ranks": size, "overlap": bool(a.overlap), "batch_per_rank": a.batch, "fields": a.fields, "dim": a.dim,
                  "distinct_keys_per_step_per_rank": round(distinct), "ms_per_step": round(worst * 1e3, 1),
                  "samples_per_s": round(a.batch * size / worst, 1),
                  "rows_per_s_per_rank": round(2 * distinct / worst, 1)})
@@ -86,6 +100,7 @@ def main(argv=None):
     ap.add_argument("--rows", type=int, default=10_000_000)
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--shards", type=int, default=4, help="shard threads per server")
+    ap.add_argument("--overlap", action="store_true", help="asynchronous calls: next pull and this push in flight together")
     a = ap.parse_args(argv)
     res = []
     ctx = mp.get_context("spawn")

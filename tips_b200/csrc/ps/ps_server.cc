@@ -275,6 +275,11 @@ bool PsFuture::Wait(int timeout_ms) {
   return cv.wait_for(lock, std::chrono::milliseconds(timeout_ms), [&] { return pending == 0; });
 }
 
+void PsFuture::Cancel() {
+  std::lock_guard<std::mutex> lock(mu);
+  cancelled = true;
+}
+
 PsClient::PsClient(std::string name, SparseTable* table, int client_id)
     : name_(std::move(name)), table_(table), client_id_(client_id) {}
 
@@ -414,17 +419,19 @@ std::shared_ptr<PsFuture> PsClient::PullPacked(const uint64_t* keys, size_t n, D
           NaiveBuffer rb(m.payload(), at);
           rb >> client >> message >> count >> bad;
         }
-        if (m.payload_size() < at || count != pos->size() || at + count * row_bytes > m.payload_size()) {
+        if (m.payload_size() < at || count != pos->size() || at + count * row_bytes > m.payload_size())
           result = Status(kInternal, "packed pull response does not match the request");
-        } else {
-          const char* rows = reinterpret_cast<const char*>(m.payload()) + at;
-          for (size_t k = 0; k < pos->size(); ++k)
-            memcpy(static_cast<char*>(out) + (*pos)[k] * row_bytes, rows + k * row_bytes, row_bytes);
-        }
       }
       bool last;
       {
+        // the rows are copied under the future's lock: a caller that gives up (Cancel) takes the same lock, so its
+        // output buffer is never written after it has been told that the call is over
         std::lock_guard<std::mutex> lock(fut->mu);
+        if (result.ok() && !fut->cancelled) {
+          const char* rows = reinterpret_cast<const char*>(m.payload()) + sizeof(int32_t) + 3 * sizeof(uint64_t);
+          for (size_t k = 0; k < pos->size(); ++k)
+            memcpy(static_cast<char*>(out) + (*pos)[k] * row_bytes, rows + k * row_bytes, row_bytes);
+        }
         if (!result.ok()) fut->status = result;
         fut->bad_rows += bad;
         last = --fut->pending == 0;

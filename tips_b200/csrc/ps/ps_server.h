@@ -70,6 +70,8 @@ struct PsFuture {
   std::vector<KeyItem> values;
   uint64_t missing_rows{0};  // push: rows that did not exist on the server
   uint64_t bad_rows{0};      // packed pull: rows that exist with another dtype or length
+  bool cancelled{false};     // packed pull: the caller gave up; late responses must not touch its output buffer
+  void Cancel();
   bool Wait(int timeout_ms);
 };
 

@@ -33,6 +33,13 @@ struct DenseBundle {
 };
 
 std::mutex g_mu;
+// Calls in flight that were started with the *_async entry points, by handle.
+struct AsyncCall {
+  std::shared_ptr<PsFuture> future;
+  bool is_pull{false};
+};
+std::map<int64_t, AsyncCall> g_calls;
+int64_t g_next_call = 1;
 std::map<int64_t, std::unique_ptr<PsBundle>> g_tables;
 std::map<int64_t, std::unique_ptr<DenseBundle>> g_dense;
 int64_t g_next = 1;
@@ -113,7 +120,10 @@ int tips_ps_pull(int64_t id, const uint64_t* keys, int64_t n, int dtype, int len
     if (!b) return Fail(kInvalidArgument, "unknown ps table");
     auto fut = b->client->PullPacked(keys, static_cast<size_t>(n), static_cast<Datatype>(dtype),
                                      static_cast<uint32_t>(length), out);
-    if (!fut->Wait(timeout_ms)) return Fail(kTimeout, "ps pull timed out");
+    if (!fut->Wait(timeout_ms)) {
+      fut->Cancel();  // a late answer must not write into `out` any more
+      return Fail(kTimeout, "ps pull timed out");
+    }
     if (!fut->status.ok()) return Fail(fut->status.code(), fut->status.message());
     if (fut->bad_rows)
       return Fail(kPrecondition, std::to_string(fut->bad_rows) + " row(s) have a different length or dtype on the server");
@@ -137,6 +147,86 @@ int64_t tips_ps_push(int64_t id, const uint64_t* keys, int64_t n, int dtype, int
   } catch (const std::exception& e) {
     return Fail(kInternal, e.what());
   }
+}
+
+/* Asynchronous forms: the call returns a handle (> 0) at once; tips_ps_wait collects the result.  A pull writes into
+ * `out` when the servers answer, so `out` must stay valid until tips_ps_wait returned; `keys` and the pushed `values`
+ * are copied into the requests before the call returns. */
+int64_t tips_ps_pull_async(int64_t id, const uint64_t* keys, int64_t n, int dtype, int length, void* out) {
+  try {
+    PsBundle* b = Get(id);
+    if (!b) return Fail(kInvalidArgument, "unknown ps table");
+    AsyncCall call;
+    call.is_pull = true;
+    call.future  = b->client->PullPacked(keys, static_cast<size_t>(n), static_cast<Datatype>(dtype),
+                                         static_cast<uint32_t>(length), out);
+    std::lock_guard<std::mutex> lock(g_mu);
+    const int64_t h = g_next_call++;
+    g_calls[h]      = std::move(call);
+    return h;
+  } catch (const std::exception& e) {
+    return Fail(kInternal, e.what());
+  }
+}
+
+int64_t tips_ps_push_async(int64_t id, const uint64_t* keys, int64_t n, int dtype, int length, const void* values) {
+  try {
+    PsBundle* b = Get(id);
+    if (!b) return Fail(kInvalidArgument, "unknown ps table");
+    AsyncCall call;
+    call.future = b->client->PushPacked(keys, static_cast<size_t>(n), static_cast<Datatype>(dtype),
+                                        static_cast<uint32_t>(length), values);
+    std::lock_guard<std::mutex> lock(g_mu);
+    const int64_t h = g_next_call++;
+    g_calls[h]      = std::move(call);
+    return h;
+  } catch (const std::exception& e) {
+    return Fail(kInternal, e.what());
+  }
+}
+
+/* Waits for an asynchronous call.  Returns -kTimeout while it is still running after `timeout_ms` (the handle stays
+ * valid; timeout_ms = 0 polls); otherwise the handle is released and the result is 0 for a pull, the number of rows
+ * that did not exist for a push, or a negative status. */
+int64_t tips_ps_wait(int64_t handle, int timeout_ms) {
+  try {
+    AsyncCall call;
+    {
+      std::lock_guard<std::mutex> lock(g_mu);
+      auto it = g_calls.find(handle);
+      if (it == g_calls.end()) return Fail(kInvalidArgument, "unknown ps call handle");
+      call = it->second;
+    }
+    if (!call.future->Wait(timeout_ms)) return Fail(kTimeout, "ps call still running");
+    {
+      std::lock_guard<std::mutex> lock(g_mu);
+      g_calls.erase(handle);
+    }
+    if (!call.future->status.ok()) return Fail(call.future->status.code(), call.future->status.message());
+    if (call.is_pull) {
+      if (call.future->bad_rows)
+        return Fail(kPrecondition,
+                    std::to_string(call.future->bad_rows) + " row(s) have a different length or dtype on the server");
+      return 0;
+    }
+    return static_cast<int64_t>(call.future->missing_rows);
+  } catch (const std::exception& e) {
+    return Fail(kInternal, e.what());
+  }
+}
+
+/* Gives up on an asynchronous call: its output buffer is not written after this returns. */
+int tips_ps_cancel(int64_t handle) {
+  AsyncCall call;
+  {
+    std::lock_guard<std::mutex> lock(g_mu);
+    auto it = g_calls.find(handle);
+    if (it == g_calls.end()) return 0;
+    call = it->second;
+    g_calls.erase(it);
+  }
+  call.future->Cancel();
+  return 0;
 }
 
 int64_t tips_ps_table_size(int64_t id) {

@@ -33,6 +33,13 @@ def _lib_ps():
         lib.tips_ps_pull.argtypes = [c_int64, POINTER(c_uint64), c_int64, c_int, c_int, c_void_p, c_int]
         lib.tips_ps_push.restype = c_int64
         lib.tips_ps_push.argtypes = [c_int64, POINTER(c_uint64), c_int64, c_int, c_int, c_void_p, c_int]
+        lib.tips_ps_pull_async.restype = c_int64
+        lib.tips_ps_pull_async.argtypes = [c_int64, POINTER(c_uint64), c_int64, c_int, c_int, c_void_p]
+        lib.tips_ps_push_async.restype = c_int64
+        lib.tips_ps_push_async.argtypes = [c_int64, POINTER(c_uint64), c_int64, c_int, c_int, c_void_p]
+        lib.tips_ps_wait.restype = c_int64
+        lib.tips_ps_wait.argtypes = [c_int64, c_int]
+        lib.tips_ps_cancel.argtypes = [c_int64]
         lib.tips_ps_table_size.restype = c_int64
         lib.tips_ps_table_size.argtypes = [c_int64]
         lib.tips_ps_table_server_of.argtypes = [c_int64, c_uint64]
@@ -63,6 +70,54 @@ class Route:
         me = _lib.core().tips_rank()
         self.is_server = me in self.servers
         self.is_worker = me in self.workers
+
+
+class PsCall:
+    """A pull or push in flight (``HostSparseTable.pull_async`` / ``push_async``).  ``wait()`` returns the pulled rows
+    or, for a push, the number of rows that did not exist; ``done()`` polls.  The reference's client is asynchronous
+    in the same way, with a completion callback per request (tips/core/ps/ps_client.h:78-176)."""
+
+    def __init__(self, handle: int, out, default_timeout_ms: int):
+        self._handle = handle
+        self._out = out               # pull: the array the answers are written into; kept alive until the call ends
+        self._timeout_ms = default_timeout_ms
+        self._result = None
+
+    def _finish(self, rc: int):
+        self._handle = 0
+        if rc < 0:
+            raise TipsError("ps call: " + _lib_ps().tips_ps_last_error().decode(), int(-rc))
+        self._result = self._out if self._out is not None else int(rc)
+        return self._result
+
+    def done(self) -> bool:
+        if not self._handle:
+            return True
+        rc = _lib_ps().tips_ps_wait(self._handle, 0)
+        if rc == -5:                  # still running
+            return False
+        self._finish(rc)
+        return True
+
+    def wait(self, timeout_s: Optional[float] = None):
+        if not self._handle:
+            return self._result
+        ms = self._timeout_ms if timeout_s is None else int(timeout_s * 1000)
+        rc = _lib_ps().tips_ps_wait(self._handle, ms)
+        if rc == -5:
+            raise TipsError("ps call timed out (it is still running; wait again or cancel())", 5)
+        return self._finish(rc)
+
+    def cancel(self) -> None:
+        if self._handle:
+            _lib_ps().tips_ps_cancel(self._handle)
+            self._handle = 0
+
+    def __del__(self):
+        try:
+            self.cancel()
+        except Exception:
+            pass
 
 
 class HostSparseTable:
@@ -108,6 +163,28 @@ class HostSparseTable:
         if rc < 0:
             raise TipsError("ps push: " + lib.tips_ps_last_error().decode(), int(-rc))
         return int(rc)
+
+    def pull_async(self, keys) -> PsCall:
+        """Start a pull and return at once; ``.wait()`` gives the [n, dim] rows.  Lets the rows of the next batch
+        travel while the current one is being computed."""
+        lib = _lib_ps()
+        k, kp = self._keys(keys)
+        out = np.empty((k.size, self.dim), dtype=self.dtype)
+        h = lib.tips_ps_pull_async(self._id, kp, k.size, _NP2CODE[self.dtype], self.dim, out.ctypes.data)
+        if h <= 0:
+            raise TipsError("ps pull: " + lib.tips_ps_last_error().decode(), int(-h))
+        return PsCall(h, out, self.timeout_ms)
+
+    def push_async(self, keys, grads) -> PsCall:
+        """Start a push and return at once (the gradients are copied into the requests before this returns);
+        ``.wait()`` gives the number of rows that did not exist on their server."""
+        lib = _lib_ps()
+        k, kp = self._keys(keys)
+        g = np.ascontiguousarray(np.asarray(grads, dtype=self.dtype).reshape(k.size, self.dim))
+        h = lib.tips_ps_push_async(self._id, kp, k.size, _NP2CODE[self.dtype], self.dim, g.ctypes.data)
+        if h <= 0:
+            raise TipsError("ps push: " + lib.tips_ps_last_error().decode(), int(-h))
+        return PsCall(h, None, self.timeout_ms)
 
     def local_size(self) -> int:
         return int(_lib_ps().tips_ps_table_size(self._id))

@@ -24,6 +24,15 @@ def main():
         grads = rows * 0.1 + 1.0
         table.push(keys, grads)
         tips.barrier()
+    # asynchronous calls: the rows of the next batch travel while this batch's gradients are pushed
+    batches = [rng.integers(0, 1000, size=64).astype(np.uint64) for _ in range(3)]
+    nxt = table.pull_async(batches[0])
+    for i, keys in enumerate(batches):
+        rows = nxt.wait()
+        if i + 1 < len(batches):
+            nxt = table.pull_async(batches[i + 1])
+        table.push_async(keys, rows * 0.1 + 1.0).wait()
+    tips.barrier()
     print(f"rank {tips.rank()}: local rows {table.local_size()} counters {table.counters()}")
     table.close()
     # a dense vector of 10 000 weights: rank 0 sets it, every rank pushes a gradient for its own range

@@ -42,3 +42,9 @@ def test_elastic_example_retries_the_failed_step():
 def test_host_parameter_server_example():
     out = _run("host_ps.py")
     assert out.strip()
+
+
+def test_parameter_server_mode_on_cpu_ranks():
+    out = _run("host_ps_ctr.py", "--steps", "6", "--batch", "64", "--rows", "5000")
+    assert "step 5 loss" in out and "rank 1: serves" in out
+

@@ -249,3 +249,53 @@ def _async_calls(rank, size):
 
 def test_asynchronous_pull_and_push():
     run_ranks(_async_calls, 2)
+
+
+def _host_embedding_layer(rank, size):
+    """The host table as a layer: two data-parallel steps of a tiny model against a dense single-process model that
+    sees the concatenated batch (SGD on the table, averaged over the ranks; duplicate ids inside a batch)."""
+    import torch
+    import tips_b200 as tips
+    from tips_b200.ps.host import HostEmbedding
+    fields, dim, rows, batch, lr = 3, 4, 50, 6, 0.5
+    layer = HostEmbedding("emb", fields, dim, optimizer="sgd", lr=lr)
+    torch.manual_seed(0)
+    head = torch.nn.Linear(fields * dim, 1)
+    dense = torch.nn.Embedding(fields * rows, dim)             # the oracle: one dense matrix, row = field * rows + id
+    torch.nn.init.zeros_(dense.weight)                         # rows of the server table start at zero too
+    ref_head = torch.nn.Linear(fields * dim, 1)
+    ref_head.load_state_dict(head.state_dict())
+    opt = tips.DistributedOptimizer(torch.optim.SGD(head.parameters(), lr=0.1))
+    ref_opt = torch.optim.SGD([{"params": ref_head.parameters(), "lr": 0.1}, {"params": [dense.weight], "lr": lr}])
+    for step in range(2):
+        g = torch.Generator().manual_seed(10 + step)
+        ids_all = torch.randint(0, rows, (size * batch, fields), generator=g)
+        ids_all[1] = ids_all[0]                                # duplicates inside one rank's batch
+        y_all = torch.rand(size * batch, 1, generator=g)
+        ids, y = ids_all[rank * batch:(rank + 1) * batch], y_all[rank * batch:(rank + 1) * batch]
+        if step == 1:
+            layer.prefetch(ids)
+        out = head(layer(ids) + 1.0)
+        loss = torch.nn.functional.mse_loss(out, y)
+        loss.backward()
+        opt.step()
+        opt.zero_grad()
+        assert layer.wait() == 0
+        tips.barrier()                                         # every rank's push has been applied
+        flat = (ids_all + torch.arange(fields) * rows).reshape(-1)
+        ref_out = ref_head(dense(flat).reshape(size * batch, fields * dim) + 1.0)
+        ref_loss = torch.nn.functional.mse_loss(ref_out, y_all)
+        ref_opt.zero_grad()
+        ref_loss.backward()
+        ref_opt.step()
+        probe = ids_all[:4]
+        got = layer(probe).detach()
+        want = dense((probe + torch.arange(fields) * rows).reshape(-1)).reshape(4, fields * dim).detach()
+        assert torch.allclose(got, want, atol=1e-5), (step, (got - want).abs().max())
+        assert torch.allclose(head.weight, ref_head.weight, atol=1e-5)
+        tips.barrier()
+    layer.close()
+
+
+def test_host_embedding_layer_matches_dense_model():
+    run_ranks(_host_embedding_layer, 2)

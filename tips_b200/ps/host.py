@@ -298,3 +298,101 @@ class HostDenseTable:
             barrier()
             _lib_ps().tips_ps_dense_destroy(self._id)
             self._id = -1
+
+
+# --------------------------------------------------------------------------------------------------------------
+# The sparse table as a layer of a torch model on CPU ranks: pull in forward, push in backward.
+
+def field_keys(ids, num_fields: int):
+    """64-bit table keys of a [batch, num_fields] matrix of per-field ids: the field number in the top 24 bits."""
+    import torch
+    if ids.dim() != 2 or ids.shape[1] != num_fields:
+        raise ValueError(f"ids must be [batch, {num_fields}]")
+    return (torch.arange(num_fields, dtype=torch.int64).unsqueeze(0) << 40) | ids.to(torch.int64)
+
+
+class _HostLookupFn:
+    """Built lazily so that importing this module does not import torch."""
+    fn = None
+
+    @classmethod
+    def get(cls):
+        if cls.fn is not None:
+            return cls.fn
+        import torch
+
+        class Fn(torch.autograd.Function):
+            @staticmethod
+            def forward(ctx, table, ids, anchor, grad_scale, prefetched):
+                keys = field_keys(ids, table.num_fields).reshape(-1)
+                unique, inverse = torch.unique(keys, return_inverse=True)
+                k = unique.numpy().astype(np.uint64)
+                rows = prefetched.wait() if prefetched is not None else table.table.pull(k)
+                ctx.table, ctx.k, ctx.inverse, ctx.scale = table, k, inverse, grad_scale
+                ctx.shape = (ids.shape[0], table.num_fields * table.dim)
+                return torch.from_numpy(rows)[inverse].reshape(ctx.shape)
+
+            @staticmethod
+            def backward(ctx, grad):
+                t = ctx.table
+                g = grad.reshape(-1, t.dim).to(torch.float32)
+                summed = torch.zeros(ctx.k.size, t.dim, dtype=torch.float32)
+                summed.index_add_(0, ctx.inverse, g)              # one gradient row per distinct key
+                if ctx.scale != 1.0:
+                    summed *= ctx.scale
+                call = t.table.push_async(ctx.k, summed.numpy())   # travels while the rest of backward runs
+                t._pending.append(call)
+                return None, None, None, None, None
+
+        cls.fn = Fn
+        return Fn
+
+
+class HostEmbedding:
+    """`num_fields` embedding tables of width `dim` served by the host parameter server, used as a layer:
+    ``layer(ids)`` pulls the rows of a [batch, num_fields] id matrix (every distinct key once) and returns
+    [batch, num_fields * dim]; the backward pass sums the gradient rows per distinct key and pushes them, and the
+    servers apply the update rule (SGD / Adagrad).  Rows are created on first pull, any 63-bit id is valid.
+    ``wait()`` after ``loss.backward()`` (or before the next pull of the same keys) makes sure the pushes have been
+    applied; ``prefetch(ids)`` starts the pull of a later batch (it reads the rows as they are when the request
+    arrives, i.e. possibly before the pushes of the step in between: the reference's asynchronous consistency).
+
+    This is the reference's parameter-server mode (tips/core/ps/ps_client.h pull / push around a training step,
+    with the server-side rule of tips/core/ps/sparse_access_method.h) bound to a framework, which the reference never
+    did; the GPU counterpart is ``tips_b200.ps.gpu.ShardedEmbedding`` / ``embedding_lookup``."""
+
+    def __init__(self, name: str, num_fields: int, dim: int, route: Optional[Route] = None, optimizer: str = "adagrad",
+                 lr: float = 0.05, eps: float = 1e-8, local_shards: int = 2, average_over_ranks: bool = True):
+        self.num_fields, self.dim = int(num_fields), int(dim)
+        self.table = HostSparseTable(name, dim, route, optimizer, lr, eps, np.float32, local_shards)
+        # every rank pushes its own gradient: with data-parallel averaging each contributes 1 / size of the step
+        self.grad_scale = 1.0 / _lib.core().tips_size() if average_over_ranks else 1.0
+        self._pending = []
+        self._prefetched = {}
+
+    def prefetch(self, ids) -> None:
+        import torch
+        keys = torch.unique(field_keys(ids, self.num_fields).reshape(-1)).numpy().astype(np.uint64)
+        self._prefetched[ids.data_ptr()] = (ids, self.table.pull_async(keys))
+
+    def __call__(self, ids):
+        import torch
+        self.wait()                                            # rows pushed by the last step are in before we read
+        hit = self._prefetched.pop(ids.data_ptr(), None)
+        anchor = torch.zeros((), requires_grad=True)           # makes the output part of the graph
+        return _HostLookupFn.get().apply(self, ids, anchor, self.grad_scale, hit[1] if hit else None)
+
+    def wait(self) -> int:
+        """Wait for the pushes in flight; returns how many pushed rows did not exist (0 in normal use)."""
+        missing = 0
+        while self._pending:
+            missing += self._pending.pop().wait()
+        return missing
+
+    def close(self) -> None:
+        self.wait()
+        for _, call in self._prefetched.values():
+            call.cancel()
+        self._prefetched.clear()
+        self.table.close()
+

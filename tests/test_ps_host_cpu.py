@@ -275,7 +275,9 @@ def _host_embedding_layer(rank, size):
         ids, y = ids_all[rank * batch:(rank + 1) * batch], y_all[rank * batch:(rank + 1) * batch]
         if step == 1:
             layer.prefetch(ids)
-        out = head(layer(ids) + 1.0)
+        x = layer(ids)
+        tips.barrier()          # synchronous step for the comparison: every rank has pulled before any rank pushes
+        out = head(x + 1.0)
         loss = torch.nn.functional.mse_loss(out, y)
         loss.backward()
         opt.step()

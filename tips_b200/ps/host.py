@@ -353,6 +353,8 @@ class HostEmbedding:
     ``layer(ids)`` pulls the rows of a [batch, num_fields] id matrix (every distinct key once) and returns
     [batch, num_fields * dim]; the backward pass sums the gradient rows per distinct key and pushes them, and the
     servers apply the update rule (SGD / Adagrad).  Rows are created on first pull, any 63-bit id is valid.
+    Ranks are not synchronised with one another: a pull sees whatever pushes have reached the servers by then (the
+    reference's consistency model); put a barrier between the forward and the backward pass for a synchronous step.
     ``wait()`` after ``loss.backward()`` (or before the next pull of the same keys) makes sure the pushes have been
     applied; ``prefetch(ids)`` starts the pull of a later batch (it reads the rows as they are when the request
     arrives, i.e. possibly before the pushes of the step in between: the reference's asynchronous consistency).

@@ -251,14 +251,14 @@ def test_asynchronous_pull_and_push():
     run_ranks(_async_calls, 2)
 
 
-def _host_embedding_layer(rank, size):
+def _host_embedding_layer(rank, size, sync=False):
     """The host table as a layer: two data-parallel steps of a tiny model against a dense single-process model that
     sees the concatenated batch (SGD on the table, averaged over the ranks; duplicate ids inside a batch)."""
     import torch
     import tips_b200 as tips
     from tips_b200.ps.host import HostEmbedding
     fields, dim, rows, batch, lr = 3, 4, 50, 6, 0.5
-    layer = HostEmbedding("emb", fields, dim, optimizer="sgd", lr=lr)
+    layer = HostEmbedding("emb", fields, dim, optimizer="sgd", lr=lr, sync=sync)
     torch.manual_seed(0)
     head = torch.nn.Linear(fields * dim, 1)
     dense = torch.nn.Embedding(fields * rows, dim)             # the oracle: one dense matrix, row = field * rows + id
@@ -276,14 +276,16 @@ def _host_embedding_layer(rank, size):
         if step == 1:
             layer.prefetch(ids)
         x = layer(ids)
-        tips.barrier()          # synchronous step for the comparison: every rank has pulled before any rank pushes
+        if not sync:
+            tips.barrier()      # synchronous step for the comparison: every rank has pulled before any rank pushes
         out = head(x + 1.0)
         loss = torch.nn.functional.mse_loss(out, y)
         loss.backward()
         opt.step()
         opt.zero_grad()
         assert layer.wait() == 0
-        tips.barrier()                                         # every rank's push has been applied
+        if not sync:
+            tips.barrier()                                     # every rank's push has been applied
         flat = (ids_all + torch.arange(fields) * rows).reshape(-1)
         ref_out = ref_head(dense(flat).reshape(size * batch, fields * dim) + 1.0)
         ref_loss = torch.nn.functional.mse_loss(ref_out, y_all)
@@ -299,5 +301,6 @@ def _host_embedding_layer(rank, size):
     layer.close()
 
 
-def test_host_embedding_layer_matches_dense_model():
-    run_ranks(_host_embedding_layer, 2)
+@pytest.mark.parametrize("sync", [False, True])
+def test_host_embedding_layer_matches_dense_model(sync):
+    run_ranks(_host_embedding_layer, 2, sync)

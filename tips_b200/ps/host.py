@@ -340,8 +340,11 @@ class _HostLookupFn:
                 summed.index_add_(0, ctx.inverse, g)              # one gradient row per distinct key
                 if ctx.scale != 1.0:
                     summed *= ctx.scale
+                if t.sync:
+                    barrier()      # every rank has read its rows for this step before any rank changes one
                 call = t.table.push_async(ctx.k, summed.numpy())   # travels while the rest of backward runs
                 t._pending.append(call)
+                t._pushed = True
                 return None, None, None, None, None
 
         cls.fn = Fn
@@ -354,7 +357,8 @@ class HostEmbedding:
     [batch, num_fields * dim]; the backward pass sums the gradient rows per distinct key and pushes them, and the
     servers apply the update rule (SGD / Adagrad).  Rows are created on first pull, any 63-bit id is valid.
     Ranks are not synchronised with one another: a pull sees whatever pushes have reached the servers by then (the
-    reference's consistency model); put a barrier between the forward and the backward pass for a synchronous step.
+    reference's consistency model); ``sync=True`` makes the steps bulk-synchronous (a barrier before and after the
+    pushes of a step), which is what the GPU tables do by default.
     ``wait()`` after ``loss.backward()`` (or before the next pull of the same keys) makes sure the pushes have been
     applied; ``prefetch(ids)`` starts the pull of a later batch (it reads the rows as they are when the request
     arrives, i.e. possibly before the pushes of the step in between: the reference's asynchronous consistency).
@@ -364,8 +368,13 @@ class HostEmbedding:
     did; the GPU counterpart is ``tips_b200.ps.gpu.ShardedEmbedding`` / ``embedding_lookup``."""
 
     def __init__(self, name: str, num_fields: int, dim: int, route: Optional[Route] = None, optimizer: str = "adagrad",
-                 lr: float = 0.05, eps: float = 1e-8, local_shards: int = 2, average_over_ranks: bool = True):
+                 lr: float = 0.05, eps: float = 1e-8, local_shards: int = 2, average_over_ranks: bool = True,
+                 sync: bool = False):
         self.num_fields, self.dim = int(num_fields), int(dim)
+        # sync: bulk-synchronous steps like the GPU tables' default: a barrier before the pushes of a step and one
+        # after them (in wait()), so that every rank computes on the same rows; every rank must then run every step
+        self.sync = bool(sync)
+        self._pushed = False
         self.table = HostSparseTable(name, dim, route, optimizer, lr, eps, np.float32, local_shards)
         # every rank pushes its own gradient: with data-parallel averaging each contributes 1 / size of the step
         self.grad_scale = 1.0 / _lib.core().tips_size() if average_over_ranks else 1.0
@@ -389,6 +398,9 @@ class HostEmbedding:
         missing = 0
         while self._pending:
             missing += self._pending.pop().wait()
+        if self.sync and self._pushed:
+            self._pushed = False
+            barrier()              # every rank's pushes of this step have been applied
         return missing
 
     def close(self) -> None:

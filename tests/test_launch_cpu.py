@@ -70,3 +70,22 @@ time.sleep(120)          # stands for a rank waiting in a collective for the one
     t0 = time.time()
     code = L.launch(2, [script], grace=2.0)
     assert code == 3 and time.time() - t0 < 30
+
+
+def test_bind_process_to_the_numa_node_of_its_gpu(tmp_path):
+    """The in-process form of the binding, against a fake sysfs; run in a child so that this process keeps its CPUs."""
+    allowed = sorted(os.sched_getaffinity(0))
+    sysfs = tmp_path / "sys"
+    d = sysfs / "bus" / "pci" / "devices" / "0000:1b:00.0"
+    d.mkdir(parents=True)
+    (d / "numa_node").write_text("0\n")
+    node = sysfs / "devices" / "system" / "node" / "node0"
+    node.mkdir(parents=True)
+    (node / "cpulist").write_text(f"{allowed[0]},9999\n")     # one CPU we may use, one that does not exist here
+    code = (f"import os, sys; sys.path.insert(0, {ROOT!r}); from tips_b200 import runtime\n"
+            f"got = runtime.bind_to_gpu_numa_node(sysfs={str(sysfs)!r}, pci_bus_id='0000:1b:00.0')\n"
+            f"assert got == [{allowed[0]}] and sorted(os.sched_getaffinity(0)) == [{allowed[0]}], got\n"
+            f"assert runtime.bind_to_gpu_numa_node(sysfs={str(sysfs)!r}, pci_bus_id='0000:ff:00.0') is None\n"
+            "print('BOUND')")
+    r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=120)
+    assert r.returncode == 0 and "BOUND" in r.stdout, r.stderr[-2000:]

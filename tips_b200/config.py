@@ -38,6 +38,7 @@ class Config:
                                              # wait) and raises if a bounded wait ran out; sync: waits for the
                                              # collective first, so the failing step itself raises; off
     collective_timeout_s: float = 0.0        # >0: DistributedOptimizer.synchronize() gives up on a bucket after this long
+    numa_bind: bool = False                  # init() limits the process to the CPUs of its GPU's NUMA node
     # Parameter server
     ps_wire_dtype: str = "grad"              # grad: rows of a push cross NVLink in the dtype of the pushed gradients
                                              # (a rank's per-row sum is rounded to bf16 once when they are bf16);

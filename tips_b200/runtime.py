@@ -73,6 +73,37 @@ def init(rank: int | None = None, size: int | None = None, master_addr: str | No
     if device:
         from .parallel import device as _device
         _device_state = _device.setup()
+        if cfg.numa_bind:
+            bind_to_gpu_numa_node()
+
+
+def bind_to_gpu_numa_node(device_index: int | None = None, sysfs: str = "/sys", pci_bus_id: str | None = None):
+    """Limit this process to the CPUs of the NUMA node its GPU hangs off, so that pinned host buffers allocated from
+    here on sit next to the GPU that reads them (``numa_bind=True`` / ``TIPS_NUMA_BIND=1`` does this inside
+    ``init()``; ``python -m tips_b200.launch --bind numa`` does it before the process starts).  Returns the CPU list,
+    or None when the platform reports no node for the device or the node has no CPU this process may use."""
+    from .launch import gpu_numa_cpus
+    if not hasattr(os, "sched_setaffinity"):
+        return None
+    if pci_bus_id is None:
+        import torch
+        if not torch.cuda.is_available():
+            return None
+        props = torch.cuda.get_device_properties(torch.cuda.current_device() if device_index is None else device_index)
+        if not hasattr(props, "pci_bus_id"):
+            return None
+        pci_bus_id = f"{getattr(props, 'pci_domain_id', 0):04x}:{props.pci_bus_id:02x}:{props.pci_device_id:02x}.0"
+    cpus = gpu_numa_cpus(0, sysfs, [pci_bus_id])
+    if not cpus:
+        return None
+    cpus = sorted(set(cpus) & set(os.sched_getaffinity(0)))
+    if not cpus:
+        return None
+    try:
+        os.sched_setaffinity(0, cpus)
+    except OSError:
+        return None
+    return cpus
 
 
 def shutdown() -> None:

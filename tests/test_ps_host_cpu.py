@@ -304,3 +304,30 @@ def _host_embedding_layer(rank, size, sync=False):
 @pytest.mark.parametrize("sync", [False, True])
 def test_host_embedding_layer_matches_dense_model(sync):
     run_ranks(_host_embedding_layer, 2, sync)
+
+
+def _host_embedding_checkpoint(rank, size, folder, phase):
+    import torch
+    import tips_b200 as tips
+    from tips_b200.ps.host import HostEmbedding
+    layer = HostEmbedding("ckpt", 2, 4, optimizer="sgd", lr=1.0, average_over_ranks=False)
+    ids = torch.tensor([[1, 2], [3, 2], [1, 7]])
+    path = os.path.join(folder, "emb")
+    if phase == "write":
+        x = layer(ids)
+        (x * (rank + 1.0)).sum().backward()                   # d/dx = rank + 1 for every element
+        layer.save(path)
+    else:
+        layer.load(path, nfiles=3)                             # written by 3 ranks, read by 2
+    got = layer(ids).detach().reshape(3, 2, 4)
+    total = -sum(r + 1.0 for r in range(3))                    # every writer pushed -(r + 1) per occurrence
+    assert torch.allclose(got[0, 0], torch.full((4,), 2 * total))      # key (0, 1) occurs twice in the batch
+    assert torch.allclose(got[1, 0], torch.full((4,), total))          # key (0, 3) once
+    assert torch.allclose(got[0, 1], torch.full((4,), 2 * total))      # key (1, 2) twice
+    tips.barrier()
+    layer.close()
+
+
+def test_host_embedding_checkpoint_under_another_rank_count(tmp_path):
+    run_ranks(_host_embedding_checkpoint, 3, str(tmp_path), "write")
+    run_ranks(_host_embedding_checkpoint, 2, str(tmp_path), "read")

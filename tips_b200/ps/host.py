@@ -403,6 +403,23 @@ class HostEmbedding:
             barrier()              # every rank's pushes of this step have been applied
         return missing
 
+    def save(self, path: str, binary: bool = True) -> None:
+        """Checkpoint: every server rank writes the rows it serves to ``path.rank<r>`` (after the pushes in flight)."""
+        self.wait()
+        barrier()
+        self.table.save(f"{path}.rank{_lib.core().tips_rank()}", binary=binary)
+        barrier()
+
+    def load(self, path: str, nfiles: int, binary: bool = True) -> None:
+        """Restore from the files of a checkpoint written by `nfiles` ranks; each rank keeps the rows it serves under
+        the current routing, so the number of ranks may differ from the one that wrote the checkpoint."""
+        import os
+        for r in range(nfiles):
+            f = f"{path}.rank{r}"
+            if os.path.exists(f):
+                self.table.load(f, binary=binary)
+        barrier()
+
     def close(self) -> None:
         self.wait()
         for _, call in self._prefetched.values():
